@@ -1,0 +1,274 @@
+/*
+ * llmini_b200 — C ABI of the B200 (sm_100a) implementation of llmini's AMUSE/Muon matrix
+ * update + NVFP4 requantisation path.
+ *
+ * Every entry point replaces one method of the reference's Rust kernel host API
+ * (`OptimizerModule`, `Nvfp4QuantModule`) or one host helper beside it; the reference
+ * file:line is cited per declaration (paths relative to the reference repository root).
+ *
+ * Conventions
+ *  - Return value: int, 0 on success, otherwise a CUDA error code (the numeric values of
+ *    cudaError_t and CUresult coincide; precondition violations return 1 =
+ *    CUDA_ERROR_INVALID_VALUE where the reference panics with `assert!`).
+ *  - `stream` is a `cudaStream_t` / `CUstream` passed as `void*`; all work is enqueued on
+ *    it in program order and nothing synchronises unless stated.
+ *  - All pointers named `d_*` or typed as device buffers are device pointers owned by the
+ *    caller.  The library allocates no device memory: scratch comes from the caller-sized
+ *    workspace (`b2_muon_workspace_bytes`).
+ *  - No CPU fallback exists.  Without a CUDA device every compute entry point returns an
+ *    error.
+ */
+#ifndef LLMINI_B200_H
+#define LLMINI_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B2_ABI_VERSION 1u
+/* crates/cuda-kernels/src/gpt/optimizer/storage.rs:4 (MUON_STORAGE_LAYOUT_VERSION) */
+#define B2_MUON_STORAGE_LAYOUT_VERSION 1u
+
+#define B2_SUCCESS 0
+#define B2_ERROR_INVALID_VALUE 1
+#define B2_ERROR_NOT_SUPPORTED 801
+#define B2_ERROR_LAUNCH_TIMEOUT 702 /* a bounded device-side wait ran out */
+#define B2_ERROR_NO_DEVICE 100
+
+/* Per-matrix pointer table entry.  Same field order, sizes and 104-byte stride as
+ * `MuonSlotDescriptor` (crates/cuda-kernels/src/gpt/optimizer/args/muon.rs:3-21), so the
+ * reference's device-resident slot table can be passed through unchanged. */
+typedef struct b2_muon_slot_descriptor {
+    uint64_t grad;            /* f32 [rows][cols]; overwritten with y = z' + beta (x' - z') */
+    uint64_t momentum;        /* bf16 [rows][cols] */
+    uint64_t variance;        /* unused on this path (Muon-VS) */
+    uint64_t second_momentum; /* unused on this path (NorMuon) */
+    uint64_t z_master;        /* f32 */
+    uint64_t x_master;        /* f32 */
+    uint64_t schedule_amax;   /* f32[1]: max |y| */
+    uint64_t bytes;           /* u8 [len/2] packed E2M1 codes */
+    uint64_t scales;          /* u8: CSF block-scale storage with its 128-byte header
+                                 pre-filled, or a raw [len/16] plane (b2_muon_options) */
+    uint64_t global_scale;    /* f32[1] */
+    uint32_t rows;
+    uint32_t cols;
+    float learning_rate_multiplier;
+    uint32_t qk_clip_factor_offset; /* must be UINT32_MAX (qk-clip is outside this path) */
+    uint32_t qk_clip_head_dim;
+    uint32_t reserved_padding;
+} b2_muon_slot_descriptor;
+
+enum { B2_OPERAND_BF16 = 0, B2_OPERAND_F16 = 1 };
+enum { B2_SCALES_CSF = 0, B2_SCALES_RAW = 1 };
+enum { B2_QUANTIZE_X = 0, B2_QUANTIZE_Y = 1 };
+
+typedef struct b2_muon_options {
+    uint32_t operand_format;  /* B2_OPERAND_*: 16-bit type the Newton-Schulz GEMM operands are
+                                 rounded to (the reference rounds to F16:
+                                 .../muon/polar/fused/stage.rs:51-55) */
+    uint32_t scale_layout;    /* B2_SCALES_* */
+    uint32_t quantize_target; /* B2_QUANTIZE_X: the averaged weights x' (mega path,
+                                 .../muon/fused/body.rs:90-101); B2_QUANTIZE_Y: the
+                                 schedule-free training weights y */
+    uint32_t max_iterations;  /* upper bound on b2_muon_step_args.iterations (0 -> 5) */
+    uint32_t reserved[4];
+} b2_muon_options;
+
+/* Step scalars: `MuonMegaUpdateArgs` (.../optimizer/args/muon.rs:25-44) and
+ * `MuonUpdateScalars` (.../muon/fused/types.rs:55-63). */
+typedef struct b2_muon_step_args {
+    float mu;
+    float grad_scale;
+    float learning_rate;
+    float weight_decay;
+    float average_coefficient;
+    float schedule_beta;        /* the mega kernel passes 1.0 (.../muon/fused/body.rs:82) */
+    uint32_t iterations;
+    uint32_t nesterov;          /* the mega kernel passes true (.../muon/fused/body.rs:34) */
+    const float *coefficients;  /* host pointer, iterations x (a, b, c); NULL selects the
+                                   reference table (.../muon/polar/fused/coefficients.rs:9-42) */
+} b2_muon_step_args;
+
+typedef struct b2_muon_plan b2_muon_plan;
+
+/* ---- handshake ------------------------------------------------------------------- */
+uint32_t b2_abi_version(void);
+const char *b2_error_string(int code);
+/* `OptimizerModule::verify_storage_layout` (.../optimizer/launcher/mod.rs:43-56): a device
+ * kernel echoes the layout version and sizeof(b2_muon_slot_descriptor); synchronises. */
+int b2_verify_storage_layout(void *stream);
+
+/* ---- Muon matrix step ------------------------------------------------------------- */
+/* Scratch sizing replaces the reference's pre-sized buffers
+ * (src/training/optimizer_tc_scratch.rs:43-66). */
+size_t b2_muon_workspace_bytes(const uint32_t *rows, const uint32_t *cols, uint32_t slot_count,
+                               const b2_muon_options *options);
+/* Builds the tile lists and TMA descriptors for a fixed set of matrix shapes and uploads
+ * them into `d_workspace` (enqueued on `stream`; the plan must outlive queued work). */
+int b2_muon_plan_create(b2_muon_plan **plan, const uint32_t *rows, const uint32_t *cols,
+                        uint32_t slot_count, const b2_muon_options *options, void *d_workspace,
+                        size_t workspace_bytes, void *stream);
+void b2_muon_plan_destroy(b2_muon_plan *plan);
+
+/* `OptimizerModule::muon_mega_update` (.../optimizer/launcher/muon_mega.rs:24-51; device
+ * body .../muon/fused/body.rs:14-102): momentum -> normalise -> Newton-Schulz -> update ->
+ * NVFP4 requantisation for every slot with rows*cols > 0. */
+int b2_muon_mega_update(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_slots,
+                        const b2_muon_step_args *args, void *stream);
+/* The three stages on their own.  `b2_muon_prepare_polar`:
+ * `OptimizerModule::muon_tma_prepare_polar` (.../launcher/muon_mega.rs:53-115) without the
+ * variance-adaptive branch.  `b2_muon_polar`: the Newton-Schulz loop
+ * (.../muon/polar/fused.rs:64-92).  `b2_muon_finish_update[_deferred_quantization]`:
+ * `OptimizerModule::muon_tma_finish_update[_deferred_quantization]`
+ * (.../launcher/muon_mega.rs:139-165) without NorMuon / qk-clip / SymExpLin. */
+int b2_muon_prepare_polar(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_slots,
+                          const b2_muon_step_args *args, void *stream);
+int b2_muon_polar(b2_muon_plan *plan, const b2_muon_step_args *args, void *stream);
+int b2_muon_finish_update(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_slots,
+                          const b2_muon_step_args *args, void *stream);
+int b2_muon_finish_update_deferred_quantization(b2_muon_plan *plan,
+                                                const b2_muon_slot_descriptor *d_slots,
+                                                const b2_muon_step_args *args, void *stream);
+/* Scratch views for tests and tracing (the reference's `MUON_TMA_TRACE`,
+ * src/training/optimizer_muon/tma.rs:1210-1276).  which: 0 = X0 (16-bit, [rows][cols]),
+ * 1 = Newton-Schulz result U (f32, [rows][cols]), 2 = inverse norm (f32[1]),
+ * 3 = max|x'| (f32[1]), 4 = device status word (u32[1], plan-wide).
+ * 5 = Gram (16-bit, [n][ld]) and 6 = polynomial Q (16-bit, [n][ld]) of the LAST iteration. */
+int b2_muon_plan_scratch(b2_muon_plan *plan, uint32_t slot, uint32_t which, void **d_ptr,
+                         size_t *bytes);
+/* Reads back and clears the plan's device status word (synchronises `stream`): 0 when no
+ * bounded wait ran out, else B2_ERROR_LAUNCH_TIMEOUT. */
+int b2_muon_plan_status(b2_muon_plan *plan, void *stream);
+/* Algorithmic FLOPs of one Newton-Schulz iteration over all slots: sum of 4 n^2 m + 2 n^3. */
+double b2_muon_plan_flops_per_iteration(const b2_muon_plan *plan);
+
+/* ---- NVFP4 quantiser (Nvfp4QuantModule) -------------------------------------------- */
+/* `Nvfp4QuantModule::tensor_amax_f32` (crates/cuda-kernels/src/utils/nvfp4/quant/amax.rs:19-23;
+ * kernels .../quant/kernels/row_amax.rs:92-136).  chunk_amax needs ceil(n/2048) floats. */
+int b2_tensor_amax_f32(const float *d_x, float *d_chunk_amax, float *d_out, uint32_t element_count,
+                       void *stream);
+/* `Nvfp4QuantModule::tensor_amax_from_chunks_f32` (.../quant/amax.rs:25-39). */
+int b2_tensor_amax_from_chunks_f32(const float *d_chunk_amax, float *d_out, uint32_t chunk_count,
+                                   void *stream);
+/* `Nvfp4QuantModule::fp32_to_nvfp4_four_six` (.../quant/four_six.rs:19-30; kernel
+ * .../quant/kernels/four_six.rs:104-152,1838-1901, flat layout).  `d_out_scales` is CSF
+ * storage whose header the caller has filled (b2_csf_encode_host of zeros does that), or a
+ * raw plane when scale_layout == B2_SCALES_RAW. */
+int b2_fp32_to_nvfp4_four_six(const float *d_x, const float *d_amax, uint8_t *d_out_fp4,
+                              uint8_t *d_out_scales, float *d_out_global_scale,
+                              uint32_t group_count, uint32_t scale_layout, void *stream);
+
+/* ---- materialisation + AdamW (OptimizerModule) ------------------------------------- */
+/* `OptimizerModule::materialize_master` (.../optimizer/launcher/mod.rs:67-95). */
+int b2_materialize_master(uint8_t *d_bytes, uint8_t *d_scales, float *d_global_scale,
+                          const float *d_master, float *d_amax, float *d_chunk_amax, uint32_t len,
+                          uint32_t scale_layout, void *stream);
+
+/* `ScheduleFreeMaterializeArgs` / `...PrecomputedArgs`
+ * (.../optimizer/args/schedule_free.rs:13-45).  symexp_lin_beta must be 0 (identity). */
+typedef struct b2_schedule_free_materialize_args {
+    uint8_t *bytes;
+    uint8_t *scales;
+    float *global_scale;
+    const float *z_master;
+    const float *x_master;
+    const float *precomputed_values; /* precomputed variant only; may be NULL */
+    float *amax;                      /* written by materialize_schedule_free, read by _precomputed */
+    uint32_t len;
+    uint32_t scale_rows;
+    uint32_t scale_k;
+    float beta;
+    float symexp_lin_beta;
+    uint32_t scale_layout;
+} b2_schedule_free_materialize_args;
+/* `OptimizerModule::materialize_schedule_free` (.../launcher/update.rs:77-133). */
+int b2_materialize_schedule_free(const b2_schedule_free_materialize_args *args, void *stream);
+/* `OptimizerModule::materialize_schedule_free_precomputed` (.../launcher/update.rs:25-75). */
+int b2_materialize_schedule_free_precomputed(const b2_schedule_free_materialize_args *args,
+                                             void *stream);
+
+/* `AdamWUpdateArgs` / `Fp32AdamWUpdateArgs` (.../optimizer/args/adam.rs:3-45). */
+typedef struct b2_adamw_update_args {
+    uint8_t *bytes;
+    uint8_t *scales;
+    float *global_scale;
+    float *z_master;
+    float *x_master;
+    float *grad;
+    float grad_scale;
+    uint32_t scale_layout;
+    float *first_moment;
+    float *second_moment;
+    float *amax;
+    float *chunk_amax;
+    uint32_t len;
+    float learning_rate;
+    float weight_decay;
+    float beta1;
+    float beta2;
+    float beta1_correction;
+    float beta2_correction;
+    float eps;
+    float average_coefficient;
+    float schedule_beta;
+} b2_adamw_update_args;
+/* `OptimizerModule::apply_adamw_update` (.../launcher/adam.rs:9-21). */
+int b2_apply_adamw_update(const b2_adamw_update_args *args, void *stream);
+/* `OptimizerModule::apply_adamw_update_deferred_quantization` (.../launcher/adam.rs:23-28). */
+int b2_apply_adamw_update_deferred_quantization(const b2_adamw_update_args *args, void *stream);
+/* `OptimizerModule::apply_fp32_adamw_update` (.../launcher/adam.rs:45-72); uses z_master,
+ * x_master, grad, grad_scale, the moments, len and the scalar hyper-parameters only. */
+int b2_apply_fp32_adamw_update(const b2_adamw_update_args *args, void *stream);
+/* `OptimizerModule::zero_f32_pointer_table` (.../launcher/adam.rs:30-43). */
+int b2_zero_f32_pointer_table(const uint64_t *d_pointers, uint32_t pointer_count, void *stream);
+
+/* ---- CSF block-scale storage, host side -------------------------------------------- */
+/* crates/cuda-kernels/src/utils/nvfp4/csf.rs:8-17 (encoded_len). */
+size_t b2_csf_encoded_len(size_t rows, size_t k);
+/* csf.rs:36-95 (encode_host).  Returns bytes written, 0 on a violated precondition. */
+size_t b2_csf_encode_host(const uint8_t *raw, size_t raw_len, size_t rows, size_t k, uint8_t *out,
+                          size_t out_capacity);
+/* csf.rs:139-147 (scale_at). */
+uint8_t b2_csf_scale_at(const uint8_t *encoded, size_t group);
+
+/* ---- host schedules feeding the step scalars ---------------------------------------- */
+/* src/training/learning_rate/schedule.rs:24-34, :36-47 + :60-65, :49-58. */
+float b2_schedule_free_beta(uint32_t step, uint32_t warmup_steps, float beta1, float rho);
+float b2_schedule_free_average_coefficient(uint32_t step, uint32_t warmup_steps, float start_ratio,
+                                           float *weight_sum);
+float b2_warmup_multiplier(uint32_t step, uint32_t warmup_steps, float start_ratio);
+
+/* ---- multi-GPU: whole-matrix sharding + all-gather of packed weights ------------------ */
+/* No counterpart in the reference (single GPU).  Greedy longest-processing-time assignment
+ * of whole matrices to ranks by 4 n^2 m + 2 n^3; the slot order follows the reference's
+ * work sort (src/training/optimizer_muon/groups/slots.rs:104-106).  owner[i] in [0, world). */
+int b2_shard_plan(const uint32_t *rows, const uint32_t *cols, uint32_t slot_count, uint32_t world,
+                  uint32_t *owner, double *rank_flops);
+/* NCCL plumbing over the process's already-loaded libnccl (resolved with dlopen).
+ * unique_id is the 128-byte ncclUniqueId; rank 0 obtains it with b2_comm_unique_id and the
+ * caller broadcasts it out of band. */
+typedef struct b2_comm b2_comm;
+int b2_comm_unique_id(uint8_t unique_id[128]);
+int b2_comm_create(b2_comm **comm, const uint8_t unique_id[128], int rank, int world);
+void b2_comm_destroy(b2_comm *comm);
+/* In-place all-gather of equally sized per-rank arenas: rank r's packed codes, scales and
+ * tensor scales live at d_arena + r * bytes_per_rank. */
+int b2_allgather_nvfp4(b2_comm *comm, void *d_arena, size_t bytes_per_rank, void *stream);
+
+/* ---- debug helpers used by the parity tests ------------------------------------------- */
+/* Evaluates `rcp.approx.ftz.f32` (crates/cuda-kernels/src/utils/float_ptx.rs:31-33). */
+int b2_debug_rcp_approx_ftz(const float *d_in, float *d_out, uint32_t count, void *stream);
+/* Literal one-thread-per-group transcription of the reference quantiser
+ * (.../quant/kernels/four_six/helpers.rs:41-94), raw scale plane; the optimised kernels
+ * must equal it bit for bit. */
+int b2_debug_quantize_literal(const float *d_x, const float *d_amax, uint8_t *d_out_fp4,
+                              uint8_t *d_out_raw_scales, float *d_out_global_scale,
+                              uint32_t group_count, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LLMINI_B200_H */

@@ -1,0 +1,636 @@
+// C ABI of libllmini_b200.so: argument validation, the Muon plan (workspace carving, tile
+// lists, TMA descriptors) and the step driver.  Host side of the reference's
+// `OptimizerModule` / `Nvfp4QuantModule` launch wrappers
+// (crates/cuda-kernels/src/gpt/optimizer/launcher/*.rs, .../utils/nvfp4/quant/*.rs).
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <new>
+#include <vector>
+
+#include "internal.h"
+
+using namespace b2;
+
+namespace {
+
+constexpr uint32_t kChunkHost = 2048;  // values per streaming chunk (kChunk on the device side)
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+inline cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s); }
+
+struct DeviceInfo {
+    int device = -1;
+    int sm_count = 0;
+};
+// Current device and its SM count; fails when no CUDA device is usable.
+cudaError_t device_info(DeviceInfo &out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    static std::mutex mu;
+    static int cached[64];
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (cached[dev] == 0) {
+        int n = 0;
+        e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) return e;
+        cached[dev] = n;
+    }
+    out.device = dev;
+    out.sm_count = cached[dev];
+    return cudaSuccess;
+}
+int stream_grid_cap(const DeviceInfo &d) { return d.sm_count * 8; }  // 8 x 256 threads per SM
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+// 2-D row-major tensor [rows][cols] with `pitch_bytes` between rows; box = box_cols x box_rows,
+// 128-byte swizzle, zero fill outside the tensor.
+bool make_map(CUtensorMap *m, void *base, int elem_bytes, uint64_t rows, uint64_t cols, uint64_t pitch_bytes,
+              uint32_t box_cols, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {pitch_bytes};
+    cuuint32_t box[2] = {box_cols, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+    return fn(m, dt, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// crates/cuda-kernels/src/gpt/optimizer/muon/polar/fused/coefficients.rs:9-42
+void reference_coefficients(uint32_t iter, float &a, float &b, float &c) {
+    static const float raw[5][3] = {{8.287212f, -23.595886f, 17.300388f},
+                                    {4.107059f, -2.94785f, 0.5448431f},
+                                    {3.948691f, -2.9089022f, 0.55181915f},
+                                    {3.3184197f, -2.488488f, 0.5100489f},
+                                    {2.300652f, -1.668904f, 0.4188073f}};
+    if (iter < 5) {
+        a = raw[iter][0] / 1.01f;
+        b = raw[iter][1] / 1.030301f;
+        c = raw[iter][2] / 1.0510101f;
+    } else {
+        a = 1.875f; b = -1.25f; c = 0.375f;
+    }
+}
+
+double slot_flops(uint32_t rows, uint32_t cols) {
+    double n = std::min(rows, cols), m = std::max(rows, cols);
+    return 4.0 * n * n * m + 2.0 * n * n * n;
+}
+
+enum ProblemType { kGram0 = 0, kGram1, kPoly, kApply0, kApply1, kLast0, kLast1, kProblemTypes };
+enum MapKind { kLX0 = 0, kLX1, kLG, kLQ, kSX0, kSX1, kSG, kSQ, kSU, kMapsPerSlot };
+
+struct SlotLayout {
+    uint32_t rows, cols, n, m, ldg, tiles_m_nn, tiles_n_nn;
+    uint64_t len;
+    size_t off_x[2], off_u, off_g16, off_q16, off_frag;
+};
+struct Layout {
+    std::vector<SlotLayout> slots;
+    std::vector<uint32_t> chunk_prefix;  // slot_count + 1
+    uint32_t total_chunks = 0;
+    int bn = 256;
+    size_t off_prefix, off_partials, off_inv_norm, off_amax_x, off_status, off_x0_ptrs, off_u_ptrs, off_maps,
+        off_problems, off_tiles_nn, off_tiles_out, off_meta_end, total;
+    uint32_t tiles_nn = 0, tiles_out = 0;
+};
+
+bool valid_shape(uint32_t rows, uint32_t cols, const b2_muon_options &o) {
+    if ((uint64_t)rows * cols == 0) return true;  // padding slot, skipped
+    if (cols % 16 != 0) return false;
+    if ((uint64_t)rows * cols > 0xfffff000ull) return false;
+    if (o.scale_layout == B2_SCALES_CSF && cols % 128 != 0) return false;
+    return true;
+}
+
+int pick_block_n(const uint32_t *rows, const uint32_t *cols, uint32_t count, const b2_muon_options &o) {
+    if (o.reserved[0] == 128 || o.reserved[0] == 256) return (int)o.reserved[0];
+    // padded tensor work of the three GEMMs for each candidate width
+    double cost[2] = {0, 0};
+    const int cand[2] = {128, 256};
+    for (int ci = 0; ci < 2; ++ci) {
+        for (uint32_t s = 0; s < count; ++s) {
+            if ((uint64_t)rows[s] * cols[s] == 0) continue;
+            double n = std::min(rows[s], cols[s]), m = std::max(rows[s], cols[s]);
+            double bn = cand[ci];
+            double n128 = std::ceil(n / 128) * 128, nb = std::ceil(n / bn) * bn;
+            double m128 = std::ceil(m / 128) * 128, mb = std::ceil(m / bn) * bn;
+            bool tall = rows[s] > cols[s];
+            double out = tall ? m128 * nb : n128 * mb;
+            cost[ci] += n128 * nb * m + n128 * nb * n + out * n;
+        }
+    }
+    // a 128 x 256 tile streams operands ~25% more efficiently than 128 x 128
+    return cost[1] <= cost[0] * 1.25 ? 256 : 128;
+}
+
+bool build_layout(const uint32_t *rows, const uint32_t *cols, uint32_t count, const b2_muon_options &o, Layout &L) {
+    L.bn = pick_block_n(rows, cols, count, o);
+    L.slots.resize(count);
+    L.chunk_prefix.assign(count + 1, 0);
+    size_t off = 0;
+    auto take = [&](size_t bytes) {
+        size_t at = off;
+        off = align_up(off + bytes, 1024);
+        return at;
+    };
+    uint32_t chunks = 0;
+    for (uint32_t s = 0; s < count; ++s) {
+        if (!valid_shape(rows[s], cols[s], o)) return false;
+        L.chunk_prefix[s] = chunks;
+        chunks += (uint32_t)(((uint64_t)rows[s] * cols[s] + kChunkHost - 1) / kChunkHost);
+    }
+    L.chunk_prefix[count] = chunks;
+    L.total_chunks = chunks;
+    // ---- metadata region (uploaded at plan creation) ----
+    L.off_prefix = take((count + 1) * sizeof(uint32_t));
+    L.off_x0_ptrs = take(count * sizeof(uint64_t));
+    L.off_u_ptrs = take(count * sizeof(uint64_t));
+    L.off_maps = take((size_t)count * kMapsPerSlot * sizeof(CUtensorMap));
+    L.off_problems = take((size_t)kProblemTypes * count * sizeof(GemmProblem));
+    L.tiles_nn = L.tiles_out = 0;
+    for (uint32_t s = 0; s < count; ++s) {
+        SlotLayout &sl = L.slots[s];
+        sl.rows = rows[s]; sl.cols = cols[s];
+        sl.len = (uint64_t)rows[s] * cols[s];
+        sl.n = std::min(rows[s], cols[s]); sl.m = std::max(rows[s], cols[s]);
+        sl.ldg = (uint32_t)align_up(sl.n, 8);
+        sl.tiles_m_nn = (sl.n + kGemmBlockM - 1) / kGemmBlockM;
+        sl.tiles_n_nn = (sl.n + L.bn - 1) / L.bn;
+        if (sl.len == 0) continue;
+        L.tiles_nn += sl.tiles_m_nn * sl.tiles_n_nn;
+        uint32_t M = rows[s] > cols[s] ? sl.m : sl.n, N = rows[s] > cols[s] ? sl.n : sl.m;
+        L.tiles_out += ((M + kGemmBlockM - 1) / kGemmBlockM) * ((N + L.bn - 1) / L.bn);
+    }
+    L.off_tiles_nn = take((size_t)std::max(L.tiles_nn, 1u) * sizeof(GemmTile));
+    L.off_tiles_out = take((size_t)std::max(L.tiles_out, 1u) * sizeof(GemmTile));
+    L.off_meta_end = off;
+    // ---- per-step scratch ----
+    L.off_partials = take((size_t)std::max(chunks, 1u) * sizeof(double));
+    L.off_inv_norm = take(count * sizeof(float));
+    L.off_amax_x = take(count * sizeof(float));
+    L.off_status = take(sizeof(uint32_t));
+    for (uint32_t s = 0; s < count; ++s) {
+        SlotLayout &sl = L.slots[s];
+        if (sl.len == 0) continue;
+        sl.off_x[0] = take(sl.len * 2);
+        sl.off_x[1] = take(sl.len * 2);
+        sl.off_u = take(sl.len * 4);
+        sl.off_g16 = take((size_t)sl.n * sl.ldg * 2);
+        sl.off_q16 = take((size_t)sl.n * sl.ldg * 2);
+        sl.off_frag = take((size_t)sl.tiles_m_nn * sl.tiles_n_nn * kGemmBlockM * L.bn * 4);
+    }
+    L.total = off;
+    return true;
+}
+
+b2_muon_options normalized(const b2_muon_options *o) {
+    b2_muon_options r;
+    std::memset(&r, 0, sizeof(r));
+    if (o) r = *o;
+    if (r.max_iterations == 0) r.max_iterations = 5;
+    return r;
+}
+
+}  // namespace
+
+struct b2_muon_plan {
+    Layout layout;
+    b2_muon_options options;
+    DeviceInfo dev;
+    uint8_t *ws = nullptr;
+    std::vector<uint8_t> meta;  // host image of the metadata region
+    double flops_per_iteration = 0.0;
+
+    template <typename T>
+    T *at(size_t off) const { return reinterpret_cast<T *>(ws + off); }
+    SlotView view(const b2_muon_slot_descriptor *d_slots) const {
+        SlotView v;
+        v.slots = d_slots;
+        v.chunk_prefix = at<uint32_t>(layout.off_prefix);
+        v.slot_count = (uint32_t)layout.slots.size();
+        v.total_chunks = layout.total_chunks;
+        v.grid = stream_grid_cap(dev);
+        return v;
+    }
+};
+
+extern "C" {
+
+uint32_t b2_abi_version(void) { return B2_ABI_VERSION; }
+
+const char *b2_error_string(int code) {
+    if (code == B2_SUCCESS) return "success";
+    return cudaGetErrorString(static_cast<cudaError_t>(code));
+}
+
+int b2_verify_storage_layout(void *stream) {
+    DeviceInfo d;
+    cudaError_t e = device_info(d);
+    if (e != cudaSuccess) return (int)e;
+    // The echo needs three words of device memory; borrow them from a stream-ordered
+    // allocation-free place: a kernel argument cannot carry output, so use mapped pinned memory.
+    uint32_t *host = nullptr;
+    e = cudaHostAlloc(reinterpret_cast<void **>(&host), 3 * sizeof(uint32_t), cudaHostAllocMapped);
+    if (e != cudaSuccess) return (int)e;
+    host[0] = host[1] = host[2] = 0;
+    uint32_t *dev_view = nullptr;
+    e = cudaHostGetDevicePointer(reinterpret_cast<void **>(&dev_view), host, 0);
+    if (e == cudaSuccess) e = launch_layout_echo(dev_view, as_stream(stream));
+    if (e == cudaSuccess) e = cudaStreamSynchronize(as_stream(stream));
+    bool ok = e == cudaSuccess && host[0] == B2_MUON_STORAGE_LAYOUT_VERSION &&
+              host[1] == sizeof(b2_muon_slot_descriptor) && host[2] == B2_ABI_VERSION;
+    cudaFreeHost(host);
+    if (e != cudaSuccess) return (int)e;
+    return ok ? B2_SUCCESS : B2_ERROR_INVALID_VALUE;
+}
+
+size_t b2_muon_workspace_bytes(const uint32_t *rows, const uint32_t *cols, uint32_t slot_count,
+                               const b2_muon_options *options) {
+    if (!rows || !cols || slot_count == 0 || slot_count > 65535) return 0;
+    Layout L;
+    b2_muon_options o = normalized(options);
+    if (!build_layout(rows, cols, slot_count, o, L)) return 0;
+    return L.total;
+}
+
+int b2_muon_plan_create(b2_muon_plan **out, const uint32_t *rows, const uint32_t *cols, uint32_t slot_count,
+                        const b2_muon_options *options, void *d_workspace, size_t workspace_bytes, void *stream) {
+    if (!out || !rows || !cols || slot_count == 0 || slot_count > 65535 || !d_workspace) return B2_ERROR_INVALID_VALUE;
+    if (reinterpret_cast<uintptr_t>(d_workspace) % 1024 != 0) return B2_ERROR_INVALID_VALUE;
+    b2_muon_options o = normalized(options);
+    if (o.operand_format > B2_OPERAND_F16 || o.scale_layout > B2_SCALES_RAW || o.quantize_target > B2_QUANTIZE_Y)
+        return B2_ERROR_INVALID_VALUE;
+    b2_muon_plan *p = new (std::nothrow) b2_muon_plan();
+    if (!p) return (int)cudaErrorMemoryAllocation;
+    p->options = o;
+    cudaError_t e = device_info(p->dev);
+    if (e != cudaSuccess) { delete p; return (int)e; }
+    Layout &L = p->layout;
+    if (!build_layout(rows, cols, slot_count, o, L) || L.total > workspace_bytes) { delete p; return B2_ERROR_INVALID_VALUE; }
+    p->ws = static_cast<uint8_t *>(d_workspace);
+    e = gemm_configure(L.bn);
+    if (e != cudaSuccess) { delete p; return (int)e; }
+
+    p->meta.assign(L.off_meta_end, 0);
+    uint8_t *h = p->meta.data();
+    std::memcpy(h + L.off_prefix, L.chunk_prefix.data(), (slot_count + 1) * sizeof(uint32_t));
+    uint64_t *x0p = reinterpret_cast<uint64_t *>(h + L.off_x0_ptrs);
+    uint64_t *up = reinterpret_cast<uint64_t *>(h + L.off_u_ptrs);
+    CUtensorMap *maps = reinterpret_cast<CUtensorMap *>(h + L.off_maps);
+    GemmProblem *probs = reinterpret_cast<GemmProblem *>(h + L.off_problems);
+    auto dmap = [&](uint32_t s, int kind) {
+        return reinterpret_cast<uint64_t>(p->ws + L.off_maps + ((size_t)s * kMapsPerSlot + kind) * sizeof(CUtensorMap));
+    };
+    bool ok = true;
+    for (uint32_t s = 0; s < slot_count; ++s) {
+        const SlotLayout &sl = L.slots[s];
+        if (sl.len == 0) continue;
+        p->flops_per_iteration += slot_flops(sl.rows, sl.cols);
+        x0p[s] = reinterpret_cast<uint64_t>(p->ws + sl.off_x[0]);
+        up[s] = reinterpret_cast<uint64_t>(p->ws + sl.off_u);
+        CUtensorMap *ms = maps + (size_t)s * kMapsPerSlot;
+        const uint64_t xp = (uint64_t)sl.cols * 2, gp = (uint64_t)sl.ldg * 2;
+        ok &= make_map(ms + kLX0, p->ws + sl.off_x[0], 2, sl.rows, sl.cols, xp, 64, 64);
+        ok &= make_map(ms + kLX1, p->ws + sl.off_x[1], 2, sl.rows, sl.cols, xp, 64, 64);
+        ok &= make_map(ms + kLG, p->ws + sl.off_g16, 2, sl.n, sl.n, gp, 64, 64);
+        ok &= make_map(ms + kLQ, p->ws + sl.off_q16, 2, sl.n, sl.n, gp, 64, 64);
+        ok &= make_map(ms + kSX0, p->ws + sl.off_x[0], 2, sl.rows, sl.cols, xp, 64, 32);
+        ok &= make_map(ms + kSX1, p->ws + sl.off_x[1], 2, sl.rows, sl.cols, xp, 64, 32);
+        ok &= make_map(ms + kSG, p->ws + sl.off_g16, 2, sl.n, sl.n, gp, 64, 32);
+        ok &= make_map(ms + kSQ, p->ws + sl.off_q16, 2, sl.n, sl.n, gp, 64, 32);
+        ok &= make_map(ms + kSU, p->ws + sl.off_u, 4, sl.rows, sl.cols, (uint64_t)sl.cols * 4, 32, 32);
+        const bool tall = sl.rows > sl.cols;
+        const uint64_t frag = reinterpret_cast<uint64_t>(p->ws + sl.off_frag);
+        for (int b = 0; b < 2; ++b) {
+            GemmProblem &g = probs[(size_t)(kGram0 + b) * slot_count + s];
+            g.map_a = g.map_b = dmap(s, kLX0 + b);
+            g.map_out16 = dmap(s, kSG);
+            g.frag32 = frag;
+            g.M = g.N = sl.n; g.K = sl.m;
+            g.a_mn_major = g.b_mn_major = tall ? 1u : 0u;
+            g.tiles_n = sl.tiles_n_nn;
+            for (int last = 0; last < 2; ++last) {
+                GemmProblem &a = probs[(size_t)((last ? kLast0 : kApply0) + b) * slot_count + s];
+                if (tall) {  // Y' = Y Q : A = Y [m][n] K-major, B = Q [n][n] K-major
+                    a.map_a = dmap(s, kLX0 + b); a.map_b = dmap(s, kLQ);
+                    a.a_mn_major = 0; a.b_mn_major = 0;
+                    a.M = sl.m; a.N = sl.n;
+                } else {     // X' = Q X : A = Q K-major, B = X [n][m] read as MN-major
+                    a.map_a = dmap(s, kLQ); a.map_b = dmap(s, kLX0 + b);
+                    a.a_mn_major = 0; a.b_mn_major = 1;
+                    a.M = sl.n; a.N = sl.m;
+                }
+                a.K = sl.n;
+                a.map_out16 = dmap(s, kSX0 + (1 - b));
+                a.map_out32 = dmap(s, kSU);
+                a.tiles_n = (a.N + L.bn - 1) / L.bn;
+            }
+        }
+        GemmProblem &q = probs[(size_t)kPoly * slot_count + s];
+        q.map_a = q.map_b = dmap(s, kLG);
+        q.map_out16 = dmap(s, kSQ);
+        q.frag32 = frag;
+        q.M = q.N = q.K = sl.n;
+        q.tiles_n = sl.tiles_n_nn;
+    }
+    if (!ok) { delete p; return B2_ERROR_NOT_SUPPORTED; }
+    // tile lists, most expensive slots first so the round-robin over CTAs ends evenly
+    std::vector<uint32_t> order;
+    for (uint32_t s = 0; s < slot_count; ++s)
+        if (L.slots[s].len) order.push_back(s);
+    std::stable_sort(order.begin(), order.end(), [&](uint32_t a, uint32_t b) {
+        const SlotLayout &x = L.slots[a], &y = L.slots[b];
+        if (x.m != y.m) return x.m > y.m;
+        return x.n > y.n;
+    });
+    GemmTile *tnn = reinterpret_cast<GemmTile *>(h + L.off_tiles_nn);
+    GemmTile *tout = reinterpret_cast<GemmTile *>(h + L.off_tiles_out);
+    uint32_t inn = 0, iout = 0;
+    for (uint32_t s : order) {
+        const SlotLayout &sl = L.slots[s];
+        for (uint32_t i = 0; i < sl.tiles_m_nn; ++i)
+            for (uint32_t j = 0; j < sl.tiles_n_nn; ++j) tnn[inn++] = GemmTile{(uint16_t)s, (uint16_t)i, (uint16_t)j, 0};
+    }
+    std::stable_sort(order.begin(), order.end(), [&](uint32_t a, uint32_t b) { return L.slots[a].n > L.slots[b].n; });
+    for (uint32_t s : order) {
+        const SlotLayout &sl = L.slots[s];
+        const bool tall = sl.rows > sl.cols;
+        uint32_t M = tall ? sl.m : sl.n, N = tall ? sl.n : sl.m;
+        uint32_t tm = (M + kGemmBlockM - 1) / kGemmBlockM, tn = (N + L.bn - 1) / L.bn;
+        for (uint32_t i = 0; i < tm; ++i)
+            for (uint32_t j = 0; j < tn; ++j) tout[iout++] = GemmTile{(uint16_t)s, (uint16_t)i, (uint16_t)j, 0};
+    }
+    e = cudaMemcpyAsync(p->ws, h, L.off_meta_end, cudaMemcpyHostToDevice, as_stream(stream));
+    if (e == cudaSuccess) e = cudaMemsetAsync(p->ws + L.off_status, 0, sizeof(uint32_t), as_stream(stream));
+    if (e != cudaSuccess) { delete p; return (int)e; }
+    *out = p;
+    return B2_SUCCESS;
+}
+
+void b2_muon_plan_destroy(b2_muon_plan *plan) { delete plan; }
+
+double b2_muon_plan_flops_per_iteration(const b2_muon_plan *plan) { return plan ? plan->flops_per_iteration : 0.0; }
+
+static int check_step(const b2_muon_plan *plan, const b2_muon_step_args *a) {
+    if (!plan || !a) return B2_ERROR_INVALID_VALUE;
+    if (a->iterations == 0 || a->iterations > plan->options.max_iterations) return B2_ERROR_INVALID_VALUE;
+    return B2_SUCCESS;
+}
+
+int b2_muon_prepare_polar(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_slots, const b2_muon_step_args *a,
+                          void *stream) {
+    if (!plan || !a || !d_slots) return B2_ERROR_INVALID_VALUE;
+    const Layout &L = plan->layout;
+    cudaStream_t s = as_stream(stream);
+    SlotView v = plan->view(d_slots);
+    double *partials = plan->at<double>(L.off_partials);
+    float *inv = plan->at<float>(L.off_inv_norm);
+    cudaError_t e = launch_muon_sumsq(v, a->mu, a->grad_scale, (int)a->nesterov, partials,
+                                      plan->at<float>(L.off_amax_x), s);
+    if (e == cudaSuccess) e = launch_muon_inv_norm(v, partials, inv, s);
+    if (e == cudaSuccess)
+        e = launch_muon_momentum_normalize(v, a->mu, a->grad_scale, (int)a->nesterov, inv,
+                                           plan->at<uint64_t>(L.off_x0_ptrs),
+                                           plan->options.operand_format == B2_OPERAND_F16, s);
+    return (int)e;
+}
+
+int b2_muon_polar(b2_muon_plan *plan, const b2_muon_step_args *a, void *stream) {
+    int rc = check_step(plan, a);
+    if (rc) return rc;
+    const Layout &L = plan->layout;
+    cudaStream_t s = as_stream(stream);
+    const uint32_t count = (uint32_t)L.slots.size();
+    const GemmProblem *probs = plan->at<GemmProblem>(L.off_problems);
+    const GemmTile *tnn = plan->at<GemmTile>(L.off_tiles_nn), *tout = plan->at<GemmTile>(L.off_tiles_out);
+    uint32_t *status = plan->at<uint32_t>(L.off_status);
+    const int f16 = plan->options.operand_format == B2_OPERAND_F16;
+    const int grid = plan->dev.sm_count;
+    cudaError_t e = cudaSuccess;
+    for (uint32_t it = 0; it < a->iterations && e == cudaSuccess; ++it) {
+        float ca, cb, cc;
+        if (a->coefficients) {
+            ca = a->coefficients[3 * it]; cb = a->coefficients[3 * it + 1]; cc = a->coefficients[3 * it + 2];
+        } else {
+            reference_coefficients(it, ca, cb, cc);
+        }
+        const uint32_t b = it & 1u;
+        const bool last = it + 1 == a->iterations;
+        e = launch_ns_gemm(L.bn, probs + (size_t)(kGram0 + b) * count, tnn, L.tiles_nn, kEpiGram, f16, ca, cb, cc,
+                           status, grid, s);
+        if (e == cudaSuccess)
+            e = launch_ns_gemm(L.bn, probs + (size_t)kPoly * count, tnn, L.tiles_nn, kEpiPoly, f16, ca, cb, cc, status,
+                               grid, s);
+        if (e == cudaSuccess)
+            e = launch_ns_gemm(L.bn, probs + (size_t)((last ? kLast0 : kApply0) + b) * count, tout, L.tiles_out,
+                               last ? kEpiApplyLast : kEpiApply, f16, ca, cb, cc, status, grid, s);
+    }
+    return (int)e;
+}
+
+static int finish_impl(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_slots, const b2_muon_step_args *a,
+                       bool quantize, void *stream) {
+    if (!plan || !a || !d_slots) return B2_ERROR_INVALID_VALUE;
+    const Layout &L = plan->layout;
+    cudaStream_t s = as_stream(stream);
+    SlotView v = plan->view(d_slots);
+    float *amax_x = plan->at<float>(L.off_amax_x);
+    cudaError_t e = launch_muon_update(v, plan->at<uint64_t>(L.off_u_ptrs), amax_x, a->learning_rate, a->weight_decay,
+                                       a->average_coefficient, a->schedule_beta, s);
+    if (e == cudaSuccess && quantize)
+        e = launch_muon_encode(v, amax_x, plan->options.quantize_target == B2_QUANTIZE_Y,
+                               (int)plan->options.scale_layout, s);
+    return (int)e;
+}
+int b2_muon_finish_update(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_slots, const b2_muon_step_args *a,
+                          void *stream) {
+    return finish_impl(plan, d_slots, a, true, stream);
+}
+int b2_muon_finish_update_deferred_quantization(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_slots,
+                                                const b2_muon_step_args *a, void *stream) {
+    return finish_impl(plan, d_slots, a, false, stream);
+}
+
+int b2_muon_mega_update(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_slots, const b2_muon_step_args *a,
+                        void *stream) {
+    int rc = check_step(plan, a);
+    if (rc) return rc;
+    if (!d_slots) return B2_ERROR_INVALID_VALUE;
+    rc = b2_muon_prepare_polar(plan, d_slots, a, stream);
+    if (rc == 0) rc = b2_muon_polar(plan, a, stream);
+    if (rc == 0) rc = b2_muon_finish_update(plan, d_slots, a, stream);
+    return rc;
+}
+
+int b2_muon_plan_scratch(b2_muon_plan *plan, uint32_t slot, uint32_t which, void **d_ptr, size_t *bytes) {
+    if (!plan || !d_ptr || !bytes) return B2_ERROR_INVALID_VALUE;
+    const Layout &L = plan->layout;
+    if (which == 4) { *d_ptr = plan->ws + L.off_status; *bytes = 4; return B2_SUCCESS; }
+    if (slot >= L.slots.size()) return B2_ERROR_INVALID_VALUE;
+    const SlotLayout &sl = L.slots[slot];
+    if (sl.len == 0) return B2_ERROR_INVALID_VALUE;
+    switch (which) {
+        case 0: *d_ptr = plan->ws + sl.off_x[0]; *bytes = sl.len * 2; break;
+        case 1: *d_ptr = plan->ws + sl.off_u; *bytes = sl.len * 4; break;
+        case 2: *d_ptr = plan->ws + L.off_inv_norm + slot * 4; *bytes = 4; break;
+        case 3: *d_ptr = plan->ws + L.off_amax_x + slot * 4; *bytes = 4; break;
+        case 5: *d_ptr = plan->ws + sl.off_g16; *bytes = (size_t)sl.n * sl.ldg * 2; break;
+        case 6: *d_ptr = plan->ws + sl.off_q16; *bytes = (size_t)sl.n * sl.ldg * 2; break;
+        case 7: *d_ptr = plan->ws + sl.off_x[1]; *bytes = sl.len * 2; break;
+        default: return B2_ERROR_INVALID_VALUE;
+    }
+    return B2_SUCCESS;
+}
+
+int b2_muon_plan_status(b2_muon_plan *plan, void *stream) {
+    if (!plan) return B2_ERROR_INVALID_VALUE;
+    uint32_t st = 0;
+    cudaStream_t s = as_stream(stream);
+    uint32_t *d = plan->at<uint32_t>(plan->layout.off_status);
+    cudaError_t e = cudaMemcpyAsync(&st, d, 4, cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaMemsetAsync(d, 0, 4, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) return (int)e;
+    return st ? B2_ERROR_LAUNCH_TIMEOUT : B2_SUCCESS;
+}
+
+// ---- quantiser ------------------------------------------------------------------------------
+int b2_tensor_amax_f32(const float *d_x, float *d_chunk_amax, float *d_out, uint32_t n, void *stream) {
+    if (!d_x || !d_chunk_amax || !d_out) return B2_ERROR_INVALID_VALUE;
+    cudaError_t e = launch_tensor_chunk_amax(d_x, d_chunk_amax, n, as_stream(stream));
+    if (e == cudaSuccess) e = launch_tensor_amax_from_chunks(d_chunk_amax, d_out, (n + 2047) / 2048, as_stream(stream));
+    return (int)e;
+}
+int b2_tensor_amax_from_chunks_f32(const float *d_chunk_amax, float *d_out, uint32_t chunk_count, void *stream) {
+    if (!d_chunk_amax || !d_out) return B2_ERROR_INVALID_VALUE;
+    return (int)launch_tensor_amax_from_chunks(d_chunk_amax, d_out, chunk_count, as_stream(stream));
+}
+int b2_fp32_to_nvfp4_four_six(const float *d_x, const float *d_amax, uint8_t *d_out_fp4, uint8_t *d_out_scales,
+                              float *d_out_global_scale, uint32_t group_count, uint32_t scale_layout, void *stream) {
+    if (!d_x || !d_amax || !d_out_fp4 || !d_out_scales || !d_out_global_scale) return B2_ERROR_INVALID_VALUE;
+    if (scale_layout > B2_SCALES_RAW || group_count > 0x0fffffffu) return B2_ERROR_INVALID_VALUE;
+    if (scale_layout == B2_SCALES_CSF && group_count % 8 != 0) return B2_ERROR_INVALID_VALUE;
+    DeviceInfo d;
+    cudaError_t e = device_info(d);
+    if (e != cudaSuccess) return (int)e;
+    return (int)launch_quantize_flat(d_x, nullptr, nullptr, 0.f, 0, d_amax, d_out_fp4, d_out_scales, d_out_global_scale,
+                                     group_count, (int)scale_layout, stream_grid_cap(d), as_stream(stream));
+}
+int b2_materialize_master(uint8_t *d_bytes, uint8_t *d_scales, float *d_global_scale, const float *d_master,
+                          float *d_amax, float *d_chunk_amax, uint32_t len, uint32_t scale_layout, void *stream) {
+    if (len % 16 != 0) return B2_ERROR_INVALID_VALUE;
+    int rc = b2_tensor_amax_f32(d_master, d_chunk_amax, d_amax, len, stream);
+    if (rc) return rc;
+    return b2_fp32_to_nvfp4_four_six(d_master, d_amax, d_bytes, d_scales, d_global_scale, len / 16, scale_layout, stream);
+}
+
+static int check_sf(const b2_schedule_free_materialize_args *a) {
+    if (!a || !a->bytes || !a->scales || !a->global_scale || !a->z_master || !a->x_master || !a->amax)
+        return B2_ERROR_INVALID_VALUE;
+    if (a->len % 16 != 0 || a->scale_layout > B2_SCALES_RAW) return B2_ERROR_INVALID_VALUE;
+    if (a->scale_layout == B2_SCALES_CSF && a->len % 128 != 0) return B2_ERROR_INVALID_VALUE;
+    if ((uint64_t)a->scale_rows * a->scale_k < a->len) return B2_ERROR_INVALID_VALUE;
+    if (a->symexp_lin_beta != 0.0f) return B2_ERROR_NOT_SUPPORTED;  // SymExpLin is outside this path
+    return B2_SUCCESS;
+}
+int b2_materialize_schedule_free_precomputed(const b2_schedule_free_materialize_args *a, void *stream) {
+    int rc = check_sf(a);
+    if (rc) return rc;
+    DeviceInfo d;
+    cudaError_t e = device_info(d);
+    if (e != cudaSuccess) return (int)e;
+    if (a->precomputed_values)
+        return (int)launch_quantize_flat(a->precomputed_values, nullptr, nullptr, 0.f, 0, a->amax, a->bytes, a->scales,
+                                         a->global_scale, a->len / 16, (int)a->scale_layout, stream_grid_cap(d),
+                                         as_stream(stream));
+    return (int)launch_quantize_flat(nullptr, a->z_master, a->x_master, a->beta, 1, a->amax, a->bytes, a->scales,
+                                     a->global_scale, a->len / 16, (int)a->scale_layout, stream_grid_cap(d),
+                                     as_stream(stream));
+}
+int b2_materialize_schedule_free(const b2_schedule_free_materialize_args *a, void *stream) {
+    int rc = check_sf(a);
+    if (rc) return rc;
+    DeviceInfo d;
+    cudaError_t e = device_info(d);
+    if (e != cudaSuccess) return (int)e;
+    cudaStream_t s = as_stream(stream);
+    e = cudaMemsetAsync(a->amax, 0, sizeof(float), s);  // launcher/update.rs:14-23 (zero_amax)
+    if (e == cudaSuccess) e = launch_schedule_free_amax(a->z_master, a->x_master, a->beta, a->len, a->amax, stream_grid_cap(d), s);
+    if (e == cudaSuccess)
+        e = launch_quantize_flat(nullptr, a->z_master, a->x_master, a->beta, 1, a->amax, a->bytes, a->scales,
+                                 a->global_scale, a->len / 16, (int)a->scale_layout, stream_grid_cap(d), s);
+    return (int)e;
+}
+
+static int check_adam(const b2_adamw_update_args *a, bool need_quant, bool need_amax) {
+    if (!a || !a->z_master || !a->x_master || !a->grad || !a->first_moment || !a->second_moment)
+        return B2_ERROR_INVALID_VALUE;
+    if (need_quant && (a->len % 16 != 0 || !a->bytes || !a->scales || !a->global_scale || !a->amax || !a->chunk_amax))
+        return B2_ERROR_INVALID_VALUE;
+    if (need_amax && (a->len % 16 != 0 || !a->amax)) return B2_ERROR_INVALID_VALUE;
+    return B2_SUCCESS;
+}
+int b2_apply_fp32_adamw_update(const b2_adamw_update_args *a, void *stream) {
+    int rc = check_adam(a, false, false);
+    if (rc) return rc;
+    DeviceInfo d;
+    cudaError_t e = device_info(d);
+    if (e != cudaSuccess) return (int)e;
+    return (int)launch_adamw(*a, 0, stream_grid_cap(d), as_stream(stream));
+}
+int b2_apply_adamw_update(const b2_adamw_update_args *a, void *stream) {
+    int rc = check_adam(a, true, false);
+    if (rc) return rc;
+    rc = b2_apply_fp32_adamw_update(a, stream);
+    if (rc) return rc;
+    return b2_materialize_master(a->bytes, a->scales, a->global_scale, a->x_master, a->amax, a->chunk_amax, a->len,
+                                 a->scale_layout, stream);
+}
+int b2_apply_adamw_update_deferred_quantization(const b2_adamw_update_args *a, void *stream) {
+    int rc = check_adam(a, false, true);
+    if (rc) return rc;
+    DeviceInfo d;
+    cudaError_t e = device_info(d);
+    if (e != cudaSuccess) return (int)e;
+    return (int)launch_adamw(*a, 1, stream_grid_cap(d), as_stream(stream));
+}
+int b2_zero_f32_pointer_table(const uint64_t *d_pointers, uint32_t pointer_count, void *stream) {
+    if (!d_pointers && pointer_count) return B2_ERROR_INVALID_VALUE;
+    return (int)launch_zero_pointer_table(d_pointers, pointer_count, as_stream(stream));
+}
+
+int b2_debug_rcp_approx_ftz(const float *d_in, float *d_out, uint32_t count, void *stream) {
+    if (!d_in || !d_out) return B2_ERROR_INVALID_VALUE;
+    return (int)launch_debug_rcp(d_in, d_out, count, as_stream(stream));
+}
+int b2_debug_quantize_literal(const float *d_x, const float *d_amax, uint8_t *d_out_fp4, uint8_t *d_out_raw_scales,
+                              float *d_out_global_scale, uint32_t group_count, void *stream) {
+    if (!d_x || !d_amax || !d_out_fp4 || !d_out_raw_scales || !d_out_global_scale) return B2_ERROR_INVALID_VALUE;
+    return (int)launch_debug_quantize_literal(d_x, d_amax, d_out_fp4, d_out_raw_scales, d_out_global_scale, group_count,
+                                              as_stream(stream));
+}
+
+}  // extern "C"

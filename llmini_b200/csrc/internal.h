@@ -1,0 +1,90 @@
+// Host-side prototypes shared by the translation units of libllmini_b200.so.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "../../include/llmini_b200.h"
+
+namespace b2 {
+
+// ---- multi-slot streaming stages (stream_kernels.cu) --------------------------------------
+struct SlotView {
+    const b2_muon_slot_descriptor *slots;  // device
+    const uint32_t *chunk_prefix;          // device, slot_count + 1 entries
+    uint32_t slot_count;
+    uint32_t total_chunks;
+    int grid;                              // CTAs to launch (multiple of the SM count)
+};
+
+cudaError_t launch_muon_sumsq(const SlotView &v, float mu, float grad_scale, int nesterov,
+                              double *partials, float *amax_x, cudaStream_t s);
+cudaError_t launch_muon_inv_norm(const SlotView &v, const double *partials, float *inv_norm,
+                                 cudaStream_t s);
+cudaError_t launch_muon_momentum_normalize(const SlotView &v, float mu, float grad_scale,
+                                           int nesterov, const float *inv_norm,
+                                           const uint64_t *x0_ptrs, int f16, cudaStream_t s);
+cudaError_t launch_muon_update(const SlotView &v, const uint64_t *u_ptrs, float *amax_x, float lr,
+                               float wd, float c_avg, float beta, cudaStream_t s);
+cudaError_t launch_muon_encode(const SlotView &v, const float *amax_x, int quantize_y,
+                               int scale_layout, cudaStream_t s);
+
+// ---- single-tensor kernels (stream_kernels.cu) ---------------------------------------------
+cudaError_t launch_tensor_chunk_amax(const float *x, float *chunk_amax, uint32_t n, cudaStream_t s);
+cudaError_t launch_tensor_amax_from_chunks(const float *chunk_amax, float *out, uint32_t count,
+                                           cudaStream_t s);
+cudaError_t launch_quantize_flat(const float *x, const float *z, const float *xm, float beta,
+                                 int mode, const float *amax, uint8_t *fp4, uint8_t *scales,
+                                 float *gs, uint32_t group_count, int scale_layout, int grid_cap,
+                                 cudaStream_t s);
+cudaError_t launch_schedule_free_amax(const float *z, const float *x, float beta, uint32_t len,
+                                      float *amax, int grid_cap, cudaStream_t s);
+cudaError_t launch_adamw(const b2_adamw_update_args &a, int with_schedule, int grid_cap,
+                         cudaStream_t s);
+cudaError_t launch_zero_pointer_table(const uint64_t *ptrs, uint32_t n, cudaStream_t s);
+cudaError_t launch_layout_echo(uint32_t *out, cudaStream_t s);
+cudaError_t launch_debug_rcp(const float *in, float *out, uint32_t n, cudaStream_t s);
+cudaError_t launch_debug_quantize_literal(const float *x, const float *amax, uint8_t *fp4,
+                                          uint8_t *raw_scales, float *gs, uint32_t group_count,
+                                          cudaStream_t s);
+
+// ---- Newton-Schulz GEMMs (ns_gemm_sm100.cu) --------------------------------------------------
+enum GemmEpilogue : uint32_t {
+    kEpiGram = 0,   // out16 = r16(acc), frag32 = acc
+    kEpiPoly = 1,   // out16 = r16(fma(c, acc, fma(b, frag32, a * delta_ij)))
+    kEpiApply = 2,  // out16 = r16(acc)
+    kEpiApplyLast = 3,  // out32 = acc (f32, storage layout)
+};
+
+// One GEMM of one slot: D[M][N] = A * B^T with A, B described by TMA maps.  Lives in device
+// memory; built once per plan.
+struct alignas(16) GemmProblem {
+    uint64_t map_a;      // device address of the CUtensorMap of operand A (box 64x64, 16-bit)
+    uint64_t map_b;
+    uint64_t map_out16;  // store map, box 64 x 32 (16-bit) — unused for kEpiApplyLast
+    uint64_t map_out32;  // store map, box 32 x 32 (f32) — kEpiApplyLast only
+    uint64_t frag32;     // f32 accumulator tiles in fragment order (Gram writes, Poly reads)
+    uint32_t M, N, K;
+    uint32_t a_mn_major;  // 0: A is [M][K] K-contiguous; 1: A is [K][M] M-contiguous
+    uint32_t b_mn_major;  // 0: B is [N][K]; 1: B is [K][N]
+    uint32_t tiles_n;     // number of tile columns (for frag32 addressing)
+    uint32_t pad[2];
+};
+struct GemmTile {
+    uint16_t problem;
+    uint16_t tile_m;
+    uint16_t tile_n;
+    uint16_t reserved;
+};
+
+constexpr int kGemmBlockM = 128;
+constexpr int kGemmBlockK = 64;
+
+size_t gemm_smem_bytes(int block_n);
+cudaError_t gemm_configure(int block_n);
+cudaError_t launch_ns_gemm(int block_n, const GemmProblem *problems, const GemmTile *tiles,
+                           uint32_t tile_count, uint32_t epilogue, int f16, float ca, float cb,
+                           float cc, uint32_t *status, int grid, cudaStream_t s);
+
+}  // namespace b2

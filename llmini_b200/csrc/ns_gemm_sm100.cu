@@ -1,0 +1,439 @@
+// Newton-Schulz GEMMs for sm_100a: D[M][N] = A * B^T on the 5th-generation tensor cores.
+//
+//   tcgen05.mma (kind::f16, BF16 or F16 operands, FP32 accumulators in TMEM), operands staged
+//   in shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle), mbarrier pipeline,
+//   warp-specialised persistent CTAs walking a tile list that spans every matrix of the plan.
+//
+// One kernel, three uses per iteration (crates/cuda-kernels/src/gpt/optimizer/muon/polar/
+// fused.rs:64-92 in the reference):
+//   Gram   G = X X^T                     (reference: tiles/symmetric.rs:28-40)
+//   Poly   Q = c G G + b G + a I         (reference: tiles/symmetric.rs:42-65, store/plain.rs:175-178)
+//   Apply  X' = Q X                      (reference: tiles.rs:14-38)
+// Operands are read in their storage orientation: an operand whose reduction dimension is
+// the slow one is described to the tensor core as MN-major, so no transpose is ever
+// materialised.  16-bit results leave through shared memory and TMA stores; the FP32 Gram
+// tile that the polynomial epilogue needs is kept in a private fragment-ordered scratch so
+// both sides access it fully coalesced.
+//
+// Every mbarrier wait is bounded: on expiry the CTA raises a status word, drains and frees
+// its TMEM before returning.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "internal.h"
+
+namespace b2 {
+
+namespace {
+
+constexpr int kGemmThreads = 192;  // warp 0: TMA producer, warp 1: MMA issuer, warps 2-5: epilogue
+constexpr int kBoxBytes = 64 * 128;          // one TMA box: 64 rows x 128 bytes
+constexpr int kABytes = 2 * kBoxBytes;       // 128 x 64 16-bit operand tile
+constexpr int kSlabBytes = 32 * 128;         // per-warp store staging: 32 rows x 128 bytes
+constexpr int kStagingBytes = 4 * 2 * kSlabBytes;
+constexpr uint32_t kSpinLimit = 1u << 24;    // hard cap on polls, whatever the timer says
+constexpr uint64_t kWaitLimitNs = 2000000000ull;
+
+template <int BN>
+struct Cfg {
+    static constexpr int kBBytes = (BN / 64) * kBoxBytes;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kStages = (BN == 256) ? 4 : 6;
+    static constexpr int kTmemCols = 2 * BN;
+    static constexpr int kBarrierBytes = 256;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + kBarrierBytes + 1024;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
+// Bounded wait (about two seconds of wall clock).  Returns false when the limit ran out or
+// another role of this CTA already gave up.
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag) {
+#pragma unroll 1
+    for (int it = 0; it < 128; ++it)
+        if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t start = global_timer_ns();
+#pragma unroll 1
+    for (uint32_t it = 0; it < kSpinLimit; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (global_timer_ns() - start > kWaitLimitNs) break;
+        __nanosleep(it >= 1024 ? 256 : 32);
+    }
+    *abort_flag = 1;
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, uint64_t map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tma_store_2d(uint64_t map, uint32_t src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(src), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tensormap_acquire(uint64_t map) {
+    asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(map) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                       uint32_t accumulate) {
+    asm volatile(
+        "{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p; }"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// 32 lanes x 32 consecutive 32-bit columns: thread i of the warp receives row (lane base + i).
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t *r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1 (sm_100).
+//   K-major operand  (rows = M/N index, 128 bytes of K per row): 8-row groups are 1024 bytes
+//   apart (stride byte offset); the leading byte offset is unused.
+//   MN-major operand (rows = K index, 128 bytes = 64 M/N elements per row): 8-row groups of K
+//   are 1024 bytes apart (stride), 64-element groups of M/N are one TMA box (8192 bytes) apart
+//   (leading).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3ffffu) >> 4);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3fffu) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3fffu) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// Instruction descriptor for kind::f16: FP32 accumulate, A/B format F16 (0) or BF16 (1),
+// per-operand major bit, N >> 3 at bit 17, M >> 4 at bit 24.
+__device__ __forceinline__ uint32_t instr_desc(int bn, int f16, uint32_t a_mn, uint32_t b_mn) {
+    uint32_t fmt = f16 ? 0u : 1u;
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | (a_mn << 15) | (b_mn << 16) |
+           ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(kGemmBlockM >> 4) << 24);
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__ tiles,
+          uint32_t tile_count, uint32_t epilogue, int f16, float ca, float cb, float cc,
+          uint32_t *status) {
+    using C = Cfg<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t *stage_base = smem;
+    uint8_t *staging = smem + C::kStages * C::kStageBytes;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(staging + kStagingBytes);
+    // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * C::kStages + 4);
+    volatile uint32_t *abort_flag = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t bar0 = smem_u32(bars);
+    auto full_bar = [&](int s) { return bar0 + 8u * s; };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (C::kStages + s); };
+    auto tfull_bar = [&](int a) { return bar0 + 8u * (2 * C::kStages + a); };
+    auto tempty_bar = [&](int a) { return bar0 + 8u * (2 * C::kStages + 2 + a); };
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::kStages; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(tfull_bar(a), 1);
+            mbar_init(tempty_bar(a), 4);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_async_smem();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"((uint32_t)C::kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (uint32_t t = blockIdx.x; ok && t < tile_count; t += gridDim.x) {
+                const GemmTile tl = tiles[t];
+                const GemmProblem *p = problems + tl.problem;
+                const uint64_t map_a = p->map_a, map_b = p->map_b;
+                const uint32_t a_mn = p->a_mn_major, b_mn = p->b_mn_major, K = p->K;
+                tensormap_acquire(map_a);
+                tensormap_acquire(map_b);
+                const int m0 = tl.tile_m * kGemmBlockM, n0 = tl.tile_n * BN;
+                const int num_kb = (int)((K + kGemmBlockK - 1) / kGemmBlockK);
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
+                    const uint32_t fb = full_bar(stage);
+                    mbar_expect_tx(fb, (uint32_t)C::kStageBytes);
+                    const uint32_t sa = smem_u32(stage_base + stage * C::kStageBytes);
+                    const uint32_t sb = sa + kABytes;
+                    const int k0 = kb * kGemmBlockK;
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        if (a_mn) tma_load_2d(sa + j * kBoxBytes, map_a, fb, m0 + 64 * j, k0);
+                        else tma_load_2d(sa + j * kBoxBytes, map_a, fb, k0, m0 + 64 * j);
+                    }
+#pragma unroll
+                    for (int j = 0; j < BN / 64; ++j) {
+                        if (b_mn) tma_load_2d(sb + j * kBoxBytes, map_b, fb, n0 + 64 * j, k0);
+                        else tma_load_2d(sb + j * kBoxBytes, map_b, fb, k0, n0 + 64 * j);
+                    }
+                    if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+            bool ok = true;
+            for (uint32_t t = blockIdx.x; ok && t < tile_count; t += gridDim.x) {
+                const GemmTile tl = tiles[t];
+                const GemmProblem *p = problems + tl.problem;
+                const uint32_t a_mn = p->a_mn_major, b_mn = p->b_mn_major, K = p->K;
+                const int num_kb = (int)((K + kGemmBlockK - 1) / kGemmBlockK);
+                const uint32_t idesc = instr_desc(BN, f16, a_mn, b_mn);
+                if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(full_bar(stage), phase, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(stage_base + stage * C::kStageBytes);
+                    const uint32_t sb = sa + kABytes;
+#pragma unroll
+                    for (int k = 0; k < kGemmBlockK / 16; ++k) {
+                        const uint64_t ad = a_mn ? smem_desc(sa + k * 2048, kBoxBytes, 1024)
+                                                 : smem_desc(sa + k * 32, 16, 1024);
+                        const uint64_t bd = b_mn ? smem_desc(sb + k * 2048, kBoxBytes, 1024)
+                                                 : smem_desc(sb + k * 32, 16, 1024);
+                        tc_mma(d_tmem, ad, bd, idesc, (uint32_t)((kb | k) != 0));
+                    }
+                    tc_commit(empty_bar(stage));
+                    if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                tc_commit(tfull_bar(acc));
+                acc ^= 1u;
+                if (acc == 0) acc_phase ^= 1u;
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue warps
+        const int q = warp & 3;  // TMEM lane quarter this warp may read
+        uint8_t *slab0 = staging + (size_t)(warp - 2) * 2 * kSlabBytes;
+        uint32_t acc = 0, acc_phase = 0, buf = 0;
+        for (uint32_t t = blockIdx.x; t < tile_count; t += gridDim.x) {
+            const GemmTile tl = tiles[t];
+            const GemmProblem *p = problems + tl.problem;
+            const uint32_t M = p->M, N = p->N;
+            const uint64_t map16 = p->map_out16, map32 = p->map_out32;
+            float *frag = reinterpret_cast<float *>(p->frag32);
+            const uint32_t tile_lin = (uint32_t)tl.tile_m * p->tiles_n + tl.tile_n;
+            const int m0 = tl.tile_m * kGemmBlockM, n0 = tl.tile_n * BN;
+            const int row_in_tile = 32 * q + lane;
+            const int grow = m0 + row_in_tile;
+            const int slab_row0 = m0 + 32 * q;
+
+            bool ready = mbar_wait(tfull_bar(acc), acc_phase, abort_flag);
+            ready = __all_sync(0xffffffffu, ready);
+            if (!ready) break;
+            tc_fence_after();
+            if (lane == 0) tensormap_acquire(epilogue == kEpiApplyLast ? map32 : map16);
+            const uint32_t taddr = tmem_base + ((uint32_t)(32 * q) << 16) + acc * BN;
+
+            if (epilogue == kEpiApplyLast) {
+                // FP32 result in the storage layout: 32 columns (128 bytes) per staged slab
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    uint32_t v[32];
+                    tc_ld32(taddr + c0, v);
+                    tc_ld_wait();
+                    if (c0 + 32 >= BN) {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(tempty_bar(acc));
+                    }
+                    if (n0 + c0 >= (int)N || slab_row0 >= (int)M) continue;  // warp-uniform
+                    uint8_t *slab = slab0 + buf * kSlabBytes;
+                    if (lane == 0) tma_store_wait_read<1>();
+                    __syncwarp();
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        uint4 w = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                        *reinterpret_cast<uint4 *>(slab + lane * 128 + ((j ^ (lane & 7)) << 4)) = w;
+                    }
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(map32, smem_u32(slab), n0 + c0, slab_row0);
+                        tma_store_commit();
+                    }
+                    buf ^= 1u;
+                }
+            } else {
+                // 16-bit result: 64 columns (128 bytes) per staged slab
+                for (int c0 = 0; c0 < BN; c0 += 64) {
+                    uint32_t v[64];
+                    tc_ld32(taddr + c0, v);
+                    tc_ld32(taddr + c0 + 32, v + 32);
+                    tc_ld_wait();
+                    if (c0 + 64 >= BN) {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(tempty_bar(acc));
+                    }
+                    if (epilogue == kEpiGram || epilogue == kEpiPoly) {
+                        // fragment order: [tile][32-column unit][float4 index][row in tile]
+                        const size_t unit0 = ((size_t)tile_lin * (BN / 32) + (size_t)(c0 / 32)) * 8;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            float4 *fp = reinterpret_cast<float4 *>(frag) + (unit0 + j) * kGemmBlockM + row_in_tile;
+                            if (epilogue == kEpiGram) {
+                                *fp = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                                  __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+                            } else {
+                                const float4 g = *fp;
+                                const float gv[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    const int gcol = n0 + c0 + 4 * j + e;
+                                    const float ident = (gcol == grow) ? ca : 0.0f;
+                                    // store/plain.rs:175-178: fma(c, acc, fma(b, base, identity))
+                                    v[4 * j + e] = __float_as_uint(
+                                        fmaf(cc, __uint_as_float(v[4 * j + e]), fmaf(cb, gv[e], ident)));
+                                }
+                            }
+                        }
+                    }
+                    if (n0 + c0 >= (int)N || slab_row0 >= (int)M) continue;  // warp-uniform
+                    uint8_t *slab = slab0 + buf * kSlabBytes;
+                    if (lane == 0) tma_store_wait_read<1>();
+                    __syncwarp();
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        uint4 w;
+                        w.x = pack_operands(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]), f16);
+                        w.y = pack_operands(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]), f16);
+                        w.z = pack_operands(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]), f16);
+                        w.w = pack_operands(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]), f16);
+                        *reinterpret_cast<uint4 *>(slab + lane * 128 + ((j ^ (lane & 7)) << 4)) = w;
+                    }
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(map16, smem_u32(slab), n0 + c0, slab_row0);
+                        tma_store_commit();
+                    }
+                    buf ^= 1u;
+                }
+            }
+            acc ^= 1u;
+            if (acc == 0) acc_phase ^= 1u;
+        }
+        if (lane == 0) tma_store_wait_all();
+        __syncwarp();
+    }
+
+    __syncthreads();
+    if (*abort_flag) {
+        // A wait ran out: give copies and MMAs still in flight time to land before the shared
+        // memory and TMEM are released, then report.
+        for (int i = 0; i < 4096; ++i) __nanosleep(512);
+        if (threadIdx.x == 0) atomicExch(status, 1u);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                     "r"((uint32_t)C::kTmemCols)
+                     : "memory");
+    }
+}
+
+}  // namespace
+
+size_t gemm_smem_bytes(int block_n) {
+    return block_n == 256 ? (size_t)Cfg<256>::kSmemBytes : (size_t)Cfg<128>::kSmemBytes;
+}
+cudaError_t gemm_configure(int block_n) {
+    if (block_n == 256)
+        return cudaFuncSetAttribute(k_ns_gemm<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<256>::kSmemBytes);
+    if (block_n == 128)
+        return cudaFuncSetAttribute(k_ns_gemm<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<128>::kSmemBytes);
+    return cudaErrorInvalidValue;
+}
+cudaError_t launch_ns_gemm(int block_n, const GemmProblem *problems, const GemmTile *tiles,
+                           uint32_t tile_count, uint32_t epilogue, int f16, float ca, float cb,
+                           float cc, uint32_t *status, int grid, cudaStream_t s) {
+    if (tile_count == 0) return cudaSuccess;
+    if ((uint32_t)grid > tile_count) grid = (int)tile_count;
+    if (block_n == 256)
+        k_ns_gemm<256><<<grid, kGemmThreads, Cfg<256>::kSmemBytes, s>>>(problems, tiles, tile_count, epilogue, f16, ca, cb, cc, status);
+    else if (block_n == 128)
+        k_ns_gemm<128><<<grid, kGemmThreads, Cfg<128>::kSmemBytes, s>>>(problems, tiles, tile_count, epilogue, f16, ca, cb, cc, status);
+    else
+        return cudaErrorInvalidValue;
+    return cudaGetLastError();
+}
+
+}  // namespace b2

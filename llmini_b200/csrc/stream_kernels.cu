@@ -1,0 +1,618 @@
+// HBM-bound stages of the Muon + NVFP4 path as coalesced, 128-bit vectorised streaming
+// kernels: momentum / Nesterov / Frobenius norm (stages M+N), master update with the
+// schedule-free interpolation (stage U), NVFP4 absmax -> scale -> pack (stage Q), AdamW and
+// the stand-alone quantiser entry points.
+//
+// Multi-slot kernels walk a flat list of 2048-value chunks over every matrix of the plan
+// (grid-stride, grid = SM count x resident CTAs), so one launch covers the whole step.
+// The file is compiled with -fmad=false: `a*b + c` is never fused unless written as fmaf,
+// which is how the reference's Rust expressions behave.
+#include "common.cuh"
+#include "internal.h"
+
+namespace b2 {
+
+// ---------------------------------------------------------------------------------------------
+// stage M arithmetic: crates/cuda-kernels/src/gpt/optimizer/muon/fused/momentum.rs:46-55
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float momentum_update(float graw, float pm, float mu, float grad_scale,
+                                                 int nesterov, float &next_m) {
+    float g = graw * grad_scale;
+    float omg = (1.0f - mu) * g;
+    next_m = mu * pm + omg;
+    return nesterov ? mu * next_m + omg : next_m;
+}
+
+struct ChunkCtx {
+    uint32_t slot;
+    uint32_t local_chunk;
+    uint32_t len;
+    b2_muon_slot_descriptor d;
+};
+__device__ __forceinline__ ChunkCtx chunk_ctx(const b2_muon_slot_descriptor *slots,
+                                              const uint32_t *prefix, uint32_t slot_count,
+                                              uint32_t c) {
+    ChunkCtx x;
+    x.slot = find_slot(prefix, slot_count, c);
+    x.local_chunk = c - prefix[x.slot];
+    x.d = slots[x.slot];
+    x.len = x.d.rows * x.d.cols;
+    return x;
+}
+
+// Pass 1 of stages M+N: sum of u^2 per chunk, accumulated in double so the result does not
+// depend on the reduction order beyond the last f32 rounding.  Also clears the two amax
+// words the update kernel later raises with atomicMax.
+__global__ void __launch_bounds__(kThreads)
+k_muon_sumsq(const b2_muon_slot_descriptor *slots, const uint32_t *prefix, uint32_t slot_count,
+             uint32_t total_chunks, float mu, float grad_scale, int nesterov, double *partials,
+             float *amax_x) {
+    __shared__ double warp_part[kThreads / 32];
+    const int tid = threadIdx.x;
+    for (uint32_t c = blockIdx.x; c < total_chunks; c += gridDim.x) {
+        ChunkCtx cx = chunk_ctx(slots, prefix, slot_count, c);
+        const float *grad = reinterpret_cast<const float *>(cx.d.grad);
+        const uint16_t *mom = reinterpret_cast<const uint16_t *>(cx.d.momentum);
+        const uint32_t base = cx.local_chunk * kChunk;
+        double acc = 0.0;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            uint32_t i = base + h * (kChunk / 2) + tid * 4;
+            if (i < cx.len) {
+                float4 g = *reinterpret_cast<const float4 *>(grad + i);
+                uint2 m = *reinterpret_cast<const uint2 *>(mom + i);
+                float nm;
+                float u0 = momentum_update(g.x, bf16_bits_to_f32(m.x & 0xffffu), mu, grad_scale, nesterov, nm);
+                float u1 = momentum_update(g.y, bf16_bits_to_f32(m.x >> 16), mu, grad_scale, nesterov, nm);
+                float u2 = momentum_update(g.z, bf16_bits_to_f32(m.y & 0xffffu), mu, grad_scale, nesterov, nm);
+                float u3 = momentum_update(g.w, bf16_bits_to_f32(m.y >> 16), mu, grad_scale, nesterov, nm);
+                acc = fma((double)u0, (double)u0, acc);
+                acc = fma((double)u1, (double)u1, acc);
+                acc = fma((double)u2, (double)u2, acc);
+                acc = fma((double)u3, (double)u3, acc);
+            }
+        }
+        acc = warp_sum(acc);
+        if ((tid & 31) == 0) warp_part[tid >> 5] = acc;
+        __syncthreads();
+        if (tid == 0) {
+            double s = 0.0;
+#pragma unroll
+            for (int w = 0; w < kThreads / 32; ++w) s += warp_part[w];
+            partials[c] = s;
+            if (cx.local_chunk == 0) {
+                amax_x[cx.slot] = 0.0f;
+                *reinterpret_cast<float *>(cx.d.schedule_amax) = 0.0f;
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// One CTA per slot: fixed-order sum of the slot's chunk partials, then
+// inv = 1 / (sqrt(S) * 1.01 + 1e-7)
+// (crates/cuda-kernels/src/gpt/optimizer/muon/polar/fused/normalize.rs:8-9,82-86).
+__global__ void __launch_bounds__(kThreads)
+k_muon_inv_norm(const uint32_t *prefix, const double *partials, float *inv_norm) {
+    __shared__ double warp_part[kThreads / 32];
+    const uint32_t s = blockIdx.x;
+    const uint32_t begin = prefix[s], end = prefix[s + 1];
+    double acc = 0.0;
+    for (uint32_t c = begin + threadIdx.x; c < end; c += kThreads) acc += partials[c];
+    acc = warp_sum(acc);
+    if ((threadIdx.x & 31) == 0) warp_part[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double t = 0.0;
+#pragma unroll
+        for (int w = 0; w < kThreads / 32; ++w) t += warp_part[w];
+        float sum = (float)t;
+        inv_norm[s] = 1.0f / (sqrtf(sum) * 1.01f + 1.0e-7f);
+    }
+}
+
+// Pass 2 of stages M+N: stores the BF16 momentum state and X0 = r16(u * inv) in the storage
+// layout [rows][cols] (momentum.rs:56-63 and normalize.rs:137-143; operand rounding
+// .../polar/fused/stage.rs:51-55).  No transpose: the GEMMs read either orientation.
+__global__ void __launch_bounds__(kThreads)
+k_muon_momentum_normalize(const b2_muon_slot_descriptor *slots, const uint32_t *prefix,
+                          uint32_t slot_count, uint32_t total_chunks, float mu, float grad_scale,
+                          int nesterov, const float *inv_norm, const uint64_t *x0_ptrs, int f16) {
+    const int tid = threadIdx.x;
+    for (uint32_t c = blockIdx.x; c < total_chunks; c += gridDim.x) {
+        ChunkCtx cx = chunk_ctx(slots, prefix, slot_count, c);
+        const float *grad = reinterpret_cast<const float *>(cx.d.grad);
+        uint16_t *mom = reinterpret_cast<uint16_t *>(cx.d.momentum);
+        uint16_t *x0 = reinterpret_cast<uint16_t *>(x0_ptrs[cx.slot]);
+        const float inv = inv_norm[cx.slot];
+        const uint32_t base = cx.local_chunk * kChunk;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            uint32_t i = base + h * (kChunk / 2) + tid * 4;
+            if (i < cx.len) {
+                float4 g = __ldcs(reinterpret_cast<const float4 *>(grad + i));
+                uint2 m = *reinterpret_cast<const uint2 *>(mom + i);
+                float n0, n1, n2, n3;
+                float u0 = momentum_update(g.x, bf16_bits_to_f32(m.x & 0xffffu), mu, grad_scale, nesterov, n0);
+                float u1 = momentum_update(g.y, bf16_bits_to_f32(m.x >> 16), mu, grad_scale, nesterov, n1);
+                float u2 = momentum_update(g.z, bf16_bits_to_f32(m.y & 0xffffu), mu, grad_scale, nesterov, n2);
+                float u3 = momentum_update(g.w, bf16_bits_to_f32(m.y >> 16), mu, grad_scale, nesterov, n3);
+                uint2 mo;
+                mo.x = f32_to_bf16_bits(n0) | (f32_to_bf16_bits(n1) << 16);
+                mo.y = f32_to_bf16_bits(n2) | (f32_to_bf16_bits(n3) << 16);
+                *reinterpret_cast<uint2 *>(mom + i) = mo;
+                uint2 xo;
+                xo.x = pack_operands(u0 * inv, u1 * inv, f16);
+                xo.y = pack_operands(u2 * inv, u3 * inv, f16);
+                *reinterpret_cast<uint2 *>(x0 + i) = xo;
+            }
+        }
+    }
+}
+
+// Stage U: crates/cuda-kernels/src/gpt/optimizer/muon/fused/update/one.rs:46-85, scale from
+// .../fused/update.rs:54, per-slot learning rate from .../fused/mega/slot.rs:26-29.
+// U is in the storage layout, so every access is a coalesced 128-bit one.
+__global__ void __launch_bounds__(kThreads)
+k_muon_update(const b2_muon_slot_descriptor *slots, const uint32_t *prefix, uint32_t slot_count,
+              uint32_t total_chunks, const uint64_t *u_ptrs, float *amax_x, float lr, float wd,
+              float c_avg, float beta) {
+    __shared__ float warp_ax[kThreads / 32], warp_ay[kThreads / 32];
+    const int tid = threadIdx.x;
+    for (uint32_t c = blockIdx.x; c < total_chunks; c += gridDim.x) {
+        ChunkCtx cx = chunk_ctx(slots, prefix, slot_count, c);
+        const float *U = reinterpret_cast<const float *>(u_ptrs[cx.slot]);
+        float *z = reinterpret_cast<float *>(cx.d.z_master);
+        float *x = reinterpret_cast<float *>(cx.d.x_master);
+        float *y = reinterpret_cast<float *>(cx.d.grad);
+        const float lr_s = lr * cx.d.learning_rate_multiplier;
+        const float scale = 0.2f * sqrtf(fmaxf((float)cx.d.rows, (float)cx.d.cols));
+        const float decay = 1.0f - lr_s * wd;
+        const uint32_t base = cx.local_chunk * kChunk;
+        float ax = 0.0f, ay = 0.0f;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            uint32_t i = base + h * (kChunk / 2) + tid * 4;
+            if (i < cx.len) {
+                float4 u = ld_stream(U + i);
+                float4 zv = ld_stream(z + i);
+                float4 xv = ld_stream(x + i);
+                float uu[4] = {u.x, u.y, u.z, u.w};
+                float zz[4] = {zv.x, zv.y, zv.z, zv.w};
+                float xx[4] = {xv.x, xv.y, xv.z, xv.w};
+                float yy[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    float upd = scale * (uu[e] * 1.0f * 1.0f);
+                    float nz = zz[e] * decay - lr_s * upd;
+                    float nx = xx[e] + c_avg * (nz - xx[e]);
+                    float sv = nz + beta * (nx - nz);
+                    zz[e] = nz;
+                    xx[e] = nx;
+                    yy[e] = sv;
+                    ax = fmaxf(ax, fabsf(nx));
+                    ay = fmaxf(ay, fabsf(sv));
+                }
+                st_stream(z + i, make_float4(zz[0], zz[1], zz[2], zz[3]));
+                // x' is read again by the encode kernel: keep it cacheable
+                *reinterpret_cast<float4 *>(x + i) = make_float4(xx[0], xx[1], xx[2], xx[3]);
+                *reinterpret_cast<float4 *>(y + i) = make_float4(yy[0], yy[1], yy[2], yy[3]);
+            }
+        }
+        ax = warp_max(ax);
+        ay = warp_max(ay);
+        if ((tid & 31) == 0) {
+            warp_ax[tid >> 5] = ax;
+            warp_ay[tid >> 5] = ay;
+        }
+        __syncthreads();
+        if (tid == 0) {
+            float mx = 0.0f, my = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kThreads / 32; ++w) {
+                mx = fmaxf(mx, warp_ax[w]);
+                my = fmaxf(my, warp_ay[w]);
+            }
+            atomic_max_nonneg(amax_x + cx.slot, mx);
+            atomic_max_nonneg(reinterpret_cast<float *>(cx.d.schedule_amax), my);
+        }
+        __syncthreads();
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// stage Q: one 2048-value chunk = 128 groups of 16; four lanes per group, four values per
+// lane (crates/cuda-kernels/src/utils/nvfp4/quant/kernels/four_six/helpers.rs:41-94,
+// .../muon/fused/quant/encode.rs:37-60).
+// MODE 0: values come from `src`; MODE 1: values are z + beta (x - z) computed on the fly
+// (crates/cuda-kernels/src/gpt/optimizer/schedule_free/value.rs:21-34).
+// ---------------------------------------------------------------------------------------------
+template <int MODE>
+__device__ __forceinline__ void encode_chunk(const float *src, const float *z, const float *xm,
+                                             float beta, uint32_t len, uint32_t base, float gs,
+                                             uint8_t *fp4, uint8_t *scales, int scale_layout,
+                                             uint32_t csf_k, uint32_t csf_rows) {
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const uint32_t group = base / 16 + h * (kThreads / 4) + (tid >> 2);
+        const uint32_t i = group * 16 + (tid & 3) * 4;
+        const bool valid = i < len;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (valid) {
+            if (MODE == 0) {
+                v = ld_stream(src + i);
+            } else {
+                float4 zv = ld_stream(z + i), xv = ld_stream(xm + i);
+                v.x = zv.x + beta * (xv.x - zv.x);
+                v.y = zv.y + beta * (xv.y - zv.y);
+                v.z = zv.z + beta * (xv.z - zv.z);
+                v.w = zv.w + beta * (xv.w - zv.w);
+            }
+        }
+        float la = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+        la = fmaxf(la, __shfl_xor_sync(0xffffffffu, la, 1));
+        float ga = fmaxf(la, __shfl_xor_sync(0xffffffffu, la, 2));
+        float inv;
+        uint32_t sb = group_scale_and_inv(ga, gs, inv);
+        uint32_t payload = pack_quad(v.x, v.y, v.z, v.w, inv);
+        if (valid) reinterpret_cast<uint16_t *>(fp4)[i >> 2] = (uint16_t)payload;
+        if (scale_layout == B2_SCALES_RAW) {
+            if (valid && (tid & 3) == 0) scales[group] = (uint8_t)sb;
+        } else {
+            // lanes 0,4,8,12 carry groups 0..3 (word a), lanes 16,20,24,28 groups 4..7 (word b)
+            // (crates/cuda-kernels/src/utils/nvfp4/csf.rs:212-232)
+            uint32_t s0 = __shfl_sync(0xffffffffu, sb, 0), s1 = __shfl_sync(0xffffffffu, sb, 4);
+            uint32_t s2 = __shfl_sync(0xffffffffu, sb, 8), s3 = __shfl_sync(0xffffffffu, sb, 12);
+            uint32_t s4 = __shfl_sync(0xffffffffu, sb, 16), s5 = __shfl_sync(0xffffffffu, sb, 20);
+            uint32_t s6 = __shfl_sync(0xffffffffu, sb, 24), s7 = __shfl_sync(0xffffffffu, sb, 28);
+            if (lane == 0 && valid) {
+                uint32_t a = s0 | (s1 << 8) | (s2 << 16) | (s3 << 24);
+                uint32_t b = s4 | (s5 << 8) | (s6 << 16) | (s7 << 24);
+                csf_store_record(scales, csf_k, csf_rows, group, a, b);
+            }
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kThreads)
+k_muon_encode(const b2_muon_slot_descriptor *slots, const uint32_t *prefix, uint32_t slot_count,
+              uint32_t total_chunks, const float *amax_x, int quantize_y, int scale_layout) {
+    for (uint32_t c = blockIdx.x; c < total_chunks; c += gridDim.x) {
+        ChunkCtx cx = chunk_ctx(slots, prefix, slot_count, c);
+        const float *src = reinterpret_cast<const float *>(quantize_y ? cx.d.grad : cx.d.x_master);
+        const float amax = quantize_y ? *reinterpret_cast<const float *>(cx.d.schedule_amax)
+                                      : amax_x[cx.slot];
+        // crates/cuda-kernels/src/gpt/optimizer/muon/fused/quant/reduce_scale.rs:66-71
+        const float gs = four_six_global_scale(amax);
+        uint8_t *scales = reinterpret_cast<uint8_t *>(cx.d.scales);
+        uint32_t k = 0, rows = 0;
+        if (scale_layout == B2_SCALES_CSF) {
+            k = reinterpret_cast<const uint32_t *>(scales)[0];
+            rows = reinterpret_cast<const uint32_t *>(scales)[1];
+        }
+        if (cx.local_chunk == 0 && threadIdx.x == 0)
+            *reinterpret_cast<float *>(cx.d.global_scale) = gs;
+        encode_chunk<0>(src, nullptr, nullptr, 0.f, cx.len, cx.local_chunk * kChunk, gs,
+                        reinterpret_cast<uint8_t *>(cx.d.bytes), scales, scale_layout, k, rows);
+    }
+}
+
+// Stand-alone flat quantiser: `fp32_to_nvfp4_four_six_kernel`
+// (crates/cuda-kernels/src/utils/nvfp4/quant/kernels/four_six.rs:104-152) and
+// `schedule_free_four_six_kernel` (.../optimizer/schedule_free/four_six.rs:12-54).
+template <int MODE>
+__global__ void __launch_bounds__(kThreads)
+k_quantize_flat(const float *src, const float *z, const float *xm, float beta, const float *amax,
+                uint8_t *fp4, uint8_t *scales, float *out_gs, uint32_t group_count,
+                int scale_layout) {
+    const uint32_t len = group_count * 16;
+    const uint32_t chunks = (len + kChunk - 1) / kChunk;
+    const float gs = four_six_global_scale(amax[0]);
+    uint32_t k = 0, rows = 0;
+    if (scale_layout == B2_SCALES_CSF) {
+        k = reinterpret_cast<const uint32_t *>(scales)[0];
+        rows = reinterpret_cast<const uint32_t *>(scales)[1];
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0) out_gs[0] = gs;
+    for (uint32_t c = blockIdx.x; c < chunks; c += gridDim.x)
+        encode_chunk<MODE>(src, z, xm, beta, len, c * kChunk, gs, fp4, scales, scale_layout, k, rows);
+}
+
+// `tensor_chunk_amax_f32_kernel` / `tensor_amax_from_chunks_f32_kernel`
+// (crates/cuda-kernels/src/utils/nvfp4/quant/kernels/row_amax.rs:92-136).
+__global__ void __launch_bounds__(kThreads)
+k_tensor_chunk_amax(const float *x, float *chunk_amax, uint32_t n) {
+    __shared__ float warp_part[kThreads / 32];
+    const int tid = threadIdx.x;
+    const uint32_t base = blockIdx.x * kChunk;
+    float m = 0.0f;
+    if (base + kChunk <= n && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            float4 v = ld_stream(x + base + h * (kChunk / 2) + tid * 4);
+            m = fmaxf(m, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+        }
+    } else {
+        for (uint32_t i = base + tid; i < n && i < base + kChunk; i += kThreads) m = fmaxf(m, fabsf(x[i]));
+    }
+    m = warp_max(m);
+    if ((tid & 31) == 0) warp_part[tid >> 5] = m;
+    __syncthreads();
+    if (tid == 0) {
+        float r = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kThreads / 32; ++w) r = fmaxf(r, warp_part[w]);
+        chunk_amax[blockIdx.x] = r;
+    }
+}
+__global__ void __launch_bounds__(kThreads)
+k_tensor_amax_from_chunks(const float *chunk_amax, float *out, uint32_t count) {
+    __shared__ float warp_part[kThreads / 32];
+    float m = 0.0f;
+    for (uint32_t i = threadIdx.x; i < count; i += kThreads) m = fmaxf(m, chunk_amax[i]);
+    m = warp_max(m);
+    if ((threadIdx.x & 31) == 0) warp_part[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float r = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kThreads / 32; ++w) r = fmaxf(r, warp_part[w]);
+        out[0] = r;
+    }
+}
+
+// `schedule_free_amax_kernel` (crates/cuda-kernels/src/gpt/optimizer/schedule_free/amax.rs:16-68).
+__global__ void __launch_bounds__(kThreads)
+k_schedule_free_amax(const float *z, const float *x, float beta, uint32_t len, float *amax) {
+    __shared__ float warp_part[kThreads / 32];
+    const int tid = threadIdx.x;
+    const uint32_t chunks = (len + kChunk - 1) / kChunk;
+    float m = 0.0f;
+    for (uint32_t c = blockIdx.x; c < chunks; c += gridDim.x) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            uint32_t i = c * kChunk + h * (kChunk / 2) + tid * 4;
+            if (i + 4 <= len) {
+                float4 zv = ld_stream(z + i), xv = ld_stream(x + i);
+                m = fmaxf(m, fabsf(zv.x + beta * (xv.x - zv.x)));
+                m = fmaxf(m, fabsf(zv.y + beta * (xv.y - zv.y)));
+                m = fmaxf(m, fabsf(zv.z + beta * (xv.z - zv.z)));
+                m = fmaxf(m, fabsf(zv.w + beta * (xv.w - zv.w)));
+            } else {
+                for (uint32_t j = i; j < len && j < i + 4; ++j) m = fmaxf(m, fabsf(z[j] + beta * (x[j] - z[j])));
+            }
+        }
+    }
+    m = warp_max(m);
+    if ((tid & 31) == 0) warp_part[tid >> 5] = m;
+    __syncthreads();
+    if (tid == 0) {
+        float r = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kThreads / 32; ++w) r = fmaxf(r, warp_part[w]);
+        atomic_max_nonneg(amax, r);
+    }
+}
+
+// `fp32_adamw_update_kernel` / `fp32_adamw_update_schedule_amax_kernel`
+// (crates/cuda-kernels/src/gpt/optimizer/adam/mod.rs:28-131).
+struct AdamScalars {
+    float grad_scale, lr, wd, beta1, beta2, bc1, bc2, eps, c_avg, sched_beta;
+};
+__device__ __forceinline__ void adam_one(float &z, float &x, float &g_io, float &m1, float &m2,
+                                         const AdamScalars &a, float decay, float &sched) {
+    float g = g_io * a.grad_scale;
+    float m = a.beta1 * m1 + (1.0f - a.beta1) * g;
+    float v = a.beta2 * m2 + (1.0f - a.beta2) * g * g;
+    float update = (m / a.bc1) / (sqrtf(v / a.bc2) + a.eps);
+    float next = z * decay - a.lr * update;
+    float nx = x + a.c_avg * (next - x);
+    m1 = m;
+    m2 = v;
+    z = next;
+    x = nx;
+    sched = next + a.sched_beta * (nx - next);
+}
+template <int WITH_SCHEDULE>
+__global__ void __launch_bounds__(kThreads)
+k_adamw(float *z, float *x, float *grad, float *m1, float *m2, float *amax, AdamScalars a,
+        uint32_t len) {
+    __shared__ float warp_part[kThreads / 32];
+    const int tid = threadIdx.x;
+    const float decay = 1.0f - a.lr * a.wd;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(z) | reinterpret_cast<uintptr_t>(x) |
+                           reinterpret_cast<uintptr_t>(grad) | reinterpret_cast<uintptr_t>(m1) |
+                           reinterpret_cast<uintptr_t>(m2)) & 15) == 0;
+    const uint32_t chunks = (len + kChunk - 1) / kChunk;
+    float am = 0.0f;
+    for (uint32_t c = blockIdx.x; c < chunks; c += gridDim.x) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            uint32_t i = c * kChunk + h * (kChunk / 2) + tid * 4;
+            if (aligned && i + 4 <= len) {
+                float4 zv = ld_stream(z + i), xv = ld_stream(x + i), gv = ld_stream(grad + i);
+                float4 av = ld_stream(m1 + i), bv = ld_stream(m2 + i);
+                float4 sv;
+                adam_one(zv.x, xv.x, gv.x, av.x, bv.x, a, decay, sv.x);
+                adam_one(zv.y, xv.y, gv.y, av.y, bv.y, a, decay, sv.y);
+                adam_one(zv.z, xv.z, gv.z, av.z, bv.z, a, decay, sv.z);
+                adam_one(zv.w, xv.w, gv.w, av.w, bv.w, a, decay, sv.w);
+                st_stream(z + i, zv);
+                *reinterpret_cast<float4 *>(x + i) = xv;
+                st_stream(m1 + i, av);
+                st_stream(m2 + i, bv);
+                if (WITH_SCHEDULE) {
+                    *reinterpret_cast<float4 *>(grad + i) = sv;
+                    am = fmaxf(am, fmaxf(fmaxf(fabsf(sv.x), fabsf(sv.y)), fmaxf(fabsf(sv.z), fabsf(sv.w))));
+                }
+            } else {
+                for (uint32_t j = i; j < len && j < i + 4; ++j) {
+                    float zz = z[j], xx = x[j], gg = grad[j], aa = m1[j], bb = m2[j], ss;
+                    adam_one(zz, xx, gg, aa, bb, a, decay, ss);
+                    z[j] = zz; x[j] = xx; m1[j] = aa; m2[j] = bb;
+                    if (WITH_SCHEDULE) {
+                        grad[j] = ss;
+                        am = fmaxf(am, fabsf(ss));
+                    }
+                }
+            }
+        }
+    }
+    if (WITH_SCHEDULE) {
+        am = warp_max(am);
+        if ((tid & 31) == 0) warp_part[tid >> 5] = am;
+        __syncthreads();
+        if (tid == 0) {
+            float r = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kThreads / 32; ++w) r = fmaxf(r, warp_part[w]);
+            atomic_max_nonneg(amax, r);
+        }
+    }
+}
+
+// `zero_f32_pointer_table_kernel` (crates/cuda-kernels/src/gpt/optimizer/adam/mod.rs:18-26).
+__global__ void k_zero_pointer_table(const uint64_t *ptrs, uint32_t n) {
+    uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) *reinterpret_cast<float *>(ptrs[i]) = 0.0f;
+}
+// `muon_storage_layout_signature_kernel` (crates/cuda-kernels/src/gpt/optimizer/storage.rs:4-17).
+__global__ void k_layout_echo(uint32_t *out) {
+    if (threadIdx.x == 0) {
+        out[0] = B2_MUON_STORAGE_LAYOUT_VERSION;
+        out[1] = (uint32_t)sizeof(b2_muon_slot_descriptor);
+        out[2] = B2_ABI_VERSION;
+    }
+}
+__global__ void k_debug_rcp(const float *in, float *out, uint32_t n) {
+    uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = rcp_approx_ftz(in[i]);
+}
+// One thread per group, same instruction sequence as the reference, raw scale plane.
+__global__ void k_debug_quantize_literal(const float *x, const float *amax, uint8_t *fp4,
+                                         uint8_t *raw_scales, float *out_gs, uint32_t group_count) {
+    uint32_t g = blockIdx.x * blockDim.x + threadIdx.x;
+    const float gs = four_six_global_scale(amax[0]);
+    if (g == 0) out_gs[0] = gs;
+    if (g >= group_count) return;
+    const float *v = x + (size_t)g * 16;
+    float ga = 0.0f;
+    for (int i = 0; i < 16; ++i) ga = fmaxf(ga, fabsf(v[i]));
+    float inv;
+    uint32_t sb = group_scale_and_inv(ga, gs, inv);
+    raw_scales[g] = (uint8_t)sb;
+    for (int i = 0; i < 8; ++i) fp4[(size_t)g * 8 + i] = (uint8_t)cvt_e2m1x2(v[2 * i + 1] * inv, v[2 * i] * inv);
+}
+
+// ---------------------------------------------------------------------------------------------
+// launchers
+// ---------------------------------------------------------------------------------------------
+static inline int clamp_grid(uint32_t chunks, int cap) {
+    if (chunks == 0) return 0;
+    return (int)(chunks < (uint32_t)cap ? chunks : (uint32_t)cap);
+}
+
+cudaError_t launch_muon_sumsq(const SlotView &v, float mu, float grad_scale, int nesterov,
+                              double *partials, float *amax_x, cudaStream_t s) {
+    if (v.total_chunks == 0) return cudaSuccess;
+    k_muon_sumsq<<<clamp_grid(v.total_chunks, v.grid), kThreads, 0, s>>>(
+        v.slots, v.chunk_prefix, v.slot_count, v.total_chunks, mu, grad_scale, nesterov, partials, amax_x);
+    return cudaGetLastError();
+}
+cudaError_t launch_muon_inv_norm(const SlotView &v, const double *partials, float *inv_norm,
+                                 cudaStream_t s) {
+    if (v.slot_count == 0) return cudaSuccess;
+    k_muon_inv_norm<<<v.slot_count, kThreads, 0, s>>>(v.chunk_prefix, partials, inv_norm);
+    return cudaGetLastError();
+}
+cudaError_t launch_muon_momentum_normalize(const SlotView &v, float mu, float grad_scale,
+                                           int nesterov, const float *inv_norm,
+                                           const uint64_t *x0_ptrs, int f16, cudaStream_t s) {
+    if (v.total_chunks == 0) return cudaSuccess;
+    k_muon_momentum_normalize<<<clamp_grid(v.total_chunks, v.grid), kThreads, 0, s>>>(
+        v.slots, v.chunk_prefix, v.slot_count, v.total_chunks, mu, grad_scale, nesterov, inv_norm, x0_ptrs, f16);
+    return cudaGetLastError();
+}
+cudaError_t launch_muon_update(const SlotView &v, const uint64_t *u_ptrs, float *amax_x, float lr,
+                               float wd, float c_avg, float beta, cudaStream_t s) {
+    if (v.total_chunks == 0) return cudaSuccess;
+    k_muon_update<<<clamp_grid(v.total_chunks, v.grid), kThreads, 0, s>>>(
+        v.slots, v.chunk_prefix, v.slot_count, v.total_chunks, u_ptrs, amax_x, lr, wd, c_avg, beta);
+    return cudaGetLastError();
+}
+cudaError_t launch_muon_encode(const SlotView &v, const float *amax_x, int quantize_y,
+                               int scale_layout, cudaStream_t s) {
+    if (v.total_chunks == 0) return cudaSuccess;
+    k_muon_encode<<<clamp_grid(v.total_chunks, v.grid), kThreads, 0, s>>>(
+        v.slots, v.chunk_prefix, v.slot_count, v.total_chunks, amax_x, quantize_y, scale_layout);
+    return cudaGetLastError();
+}
+cudaError_t launch_tensor_chunk_amax(const float *x, float *chunk_amax, uint32_t n, cudaStream_t s) {
+    uint32_t chunks = (n + kChunk - 1) / kChunk;
+    if (chunks == 0) return cudaSuccess;
+    k_tensor_chunk_amax<<<chunks, kThreads, 0, s>>>(x, chunk_amax, n);
+    return cudaGetLastError();
+}
+cudaError_t launch_tensor_amax_from_chunks(const float *chunk_amax, float *out, uint32_t count,
+                                           cudaStream_t s) {
+    k_tensor_amax_from_chunks<<<1, kThreads, 0, s>>>(chunk_amax, out, count);
+    return cudaGetLastError();
+}
+cudaError_t launch_quantize_flat(const float *x, const float *z, const float *xm, float beta,
+                                 int mode, const float *amax, uint8_t *fp4, uint8_t *scales,
+                                 float *gs, uint32_t group_count, int scale_layout, int grid_cap,
+                                 cudaStream_t s) {
+    uint32_t chunks = (group_count * 16 + kChunk - 1) / kChunk;
+    int grid = clamp_grid(chunks, grid_cap);
+    if (grid == 0) grid = 1;  // still writes the global scale
+    if (mode == 0)
+        k_quantize_flat<0><<<grid, kThreads, 0, s>>>(x, z, xm, beta, amax, fp4, scales, gs, group_count, scale_layout);
+    else
+        k_quantize_flat<1><<<grid, kThreads, 0, s>>>(x, z, xm, beta, amax, fp4, scales, gs, group_count, scale_layout);
+    return cudaGetLastError();
+}
+cudaError_t launch_schedule_free_amax(const float *z, const float *x, float beta, uint32_t len,
+                                      float *amax, int grid_cap, cudaStream_t s) {
+    uint32_t chunks = (len + kChunk - 1) / kChunk;
+    if (chunks == 0) return cudaSuccess;
+    k_schedule_free_amax<<<clamp_grid(chunks, grid_cap), kThreads, 0, s>>>(z, x, beta, len, amax);
+    return cudaGetLastError();
+}
+cudaError_t launch_adamw(const b2_adamw_update_args &a, int with_schedule, int grid_cap,
+                         cudaStream_t s) {
+    uint32_t chunks = (a.len + kChunk - 1) / kChunk;
+    if (chunks == 0) return cudaSuccess;
+    AdamScalars sc{a.grad_scale, a.learning_rate, a.weight_decay, a.beta1, a.beta2,
+                   a.beta1_correction, a.beta2_correction, a.eps, a.average_coefficient, a.schedule_beta};
+    int grid = clamp_grid(chunks, grid_cap);
+    if (with_schedule)
+        k_adamw<1><<<grid, kThreads, 0, s>>>(a.z_master, a.x_master, a.grad, a.first_moment, a.second_moment, a.amax, sc, a.len);
+    else
+        k_adamw<0><<<grid, kThreads, 0, s>>>(a.z_master, a.x_master, a.grad, a.first_moment, a.second_moment, nullptr, sc, a.len);
+    return cudaGetLastError();
+}
+cudaError_t launch_zero_pointer_table(const uint64_t *ptrs, uint32_t n, cudaStream_t s) {
+    if (n == 0) return cudaSuccess;
+    k_zero_pointer_table<<<(n + 255) / 256, 256, 0, s>>>(ptrs, n);
+    return cudaGetLastError();
+}
+cudaError_t launch_layout_echo(uint32_t *out, cudaStream_t s) {
+    k_layout_echo<<<1, 32, 0, s>>>(out);
+    return cudaGetLastError();
+}
+cudaError_t launch_debug_rcp(const float *in, float *out, uint32_t n, cudaStream_t s) {
+    if (n == 0) return cudaSuccess;
+    k_debug_rcp<<<(n + 255) / 256, 256, 0, s>>>(in, out, n);
+    return cudaGetLastError();
+}
+cudaError_t launch_debug_quantize_literal(const float *x, const float *amax, uint8_t *fp4,
+                                          uint8_t *raw_scales, float *gs, uint32_t group_count,
+                                          cudaStream_t s) {
+    uint32_t blocks = group_count == 0 ? 1 : (group_count + 255) / 256;
+    k_debug_quantize_literal<<<blocks, 256, 0, s>>>(x, amax, fp4, raw_scales, gs, group_count);
+    return cudaGetLastError();
+}
+
+}  // namespace b2

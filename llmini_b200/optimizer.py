@@ -1,0 +1,278 @@
+"""Host mirror of the reference's `OptimizerModule` hot-path methods over the C ABI.
+
+Reference interface: crates/cuda-kernels/src/gpt/optimizer/launcher/{mod,muon_mega,update,adam}.rs
+with argument structs in .../optimizer/args/{muon,schedule_free,adam}.rs.  Method and field
+names follow the reference so its tests read the same here.  Tensors are torch CUDA tensors
+used purely as device buffers; all arithmetic happens inside libllmini_b200.so.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, field
+from typing import Optional, Sequence
+
+import numpy as np
+import torch
+
+from . import _ffi
+from ._ffi import (AdamWUpdateArgs as _CAdam, MuonOptions, MuonSlotDescriptor, MuonStepArgs, OPERAND_BF16,
+                   OPERAND_F16, QUANTIZE_X, QUANTIZE_Y, SCALES_CSF, SCALES_RAW,
+                   ScheduleFreeMaterializeArgs as _CSf, check)
+from .nvfp4 import Nvfp4QuantModule, zero_scales
+
+U32_MAX = 0xFFFFFFFF
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]) -> int:
+    if t is None:
+        return 0
+    assert t.is_cuda and t.is_contiguous()
+    return t.data_ptr()
+
+
+@dataclass
+class MuonSlot:
+    """Device buffers of one matrix (the fields of `MuonSlotDescriptor`)."""
+    grad: torch.Tensor           # f32 [rows, cols]; receives y
+    momentum: torch.Tensor       # bf16 [rows, cols]
+    z_master: torch.Tensor       # f32
+    x_master: torch.Tensor       # f32
+    schedule_amax: torch.Tensor  # f32[1]
+    bytes: torch.Tensor          # u8 [len/2]
+    scales: torch.Tensor         # u8 CSF (pre-headed) or raw plane
+    global_scale: torch.Tensor   # f32[1]
+    rows: int
+    cols: int
+    learning_rate_multiplier: float = 1.0
+
+    @staticmethod
+    def allocate(rows: int, cols: int, scale_layout: int = SCALES_CSF, device="cuda") -> "MuonSlot":
+        n = rows * cols
+        scales = zero_scales(rows, cols, device) if scale_layout == SCALES_CSF else \
+            torch.zeros(max(n // 16, 1), dtype=torch.uint8, device=device)
+        z = lambda *s, dt=torch.float32: torch.zeros(*s, dtype=dt, device=device)
+        return MuonSlot(z(rows, cols), z(rows, cols, dt=torch.bfloat16), z(rows, cols), z(rows, cols), z(1),
+                        torch.zeros(max(n // 2, 1), dtype=torch.uint8, device=device), scales, z(1), rows, cols)
+
+    def descriptor(self) -> MuonSlotDescriptor:
+        return MuonSlotDescriptor(_ptr(self.grad), _ptr(self.momentum), 0, 0, _ptr(self.z_master), _ptr(self.x_master),
+                                  _ptr(self.schedule_amax), _ptr(self.bytes), _ptr(self.scales), _ptr(self.global_scale),
+                                  self.rows, self.cols, self.learning_rate_multiplier, U32_MAX, 0, 0)
+
+
+def slot_table(slots: Sequence[MuonSlot], device="cuda") -> torch.Tensor:
+    """Device-resident `MuonSlotDescriptor` table (104 bytes per entry)."""
+    arr = (MuonSlotDescriptor * len(slots))(*[s.descriptor() for s in slots])
+    host = np.frombuffer(bytes(arr), dtype=np.uint8).copy()
+    return torch.from_numpy(host).to(device)
+
+
+@dataclass
+class MuonMegaUpdateArgs:
+    """`MuonMegaUpdateArgs` (args/muon.rs:25-44) minus the scratch buffers, which the plan owns."""
+    mu: float = 0.95
+    grad_scale: float = 1.0
+    learning_rate: float = 1.0e-4
+    weight_decay: float = 0.025
+    average_coefficient: float = 1.0
+    iterations: int = 5
+    schedule_beta: float = 1.0
+    nesterov: bool = True
+    coefficients: Optional[np.ndarray] = None  # iterations x 3; None = reference table
+
+    def c_args(self):
+        co = None
+        keep = None
+        if self.coefficients is not None:
+            keep = np.ascontiguousarray(self.coefficients, dtype=np.float32).reshape(-1)
+            assert keep.size >= 3 * self.iterations
+            co = keep.ctypes.data_as(C.POINTER(C.c_float))
+        a = MuonStepArgs(self.mu, self.grad_scale, self.learning_rate, self.weight_decay, self.average_coefficient,
+                         self.schedule_beta, self.iterations, int(self.nesterov), co)
+        return a, keep
+
+
+class MuonPlan:
+    """Shapes-only plan: workspace, tile lists and TMA descriptors for a fixed slot list."""
+
+    def __init__(self, shapes: Sequence[tuple[int, int]], operand_format: int = OPERAND_BF16,
+                 scale_layout: int = SCALES_CSF, quantize_target: int = QUANTIZE_X, max_iterations: int = 5,
+                 tile_n: int = 0, device="cuda"):
+        self._lib = _ffi.lib()
+        self.shapes = [(int(r), int(c)) for r, c in shapes]
+        n = len(self.shapes)
+        self._rows = (C.c_uint32 * n)(*[r for r, _ in self.shapes])
+        self._cols = (C.c_uint32 * n)(*[c for _, c in self.shapes])
+        self.options = MuonOptions(operand_format, scale_layout, quantize_target, max_iterations, (C.c_uint32 * 4)(tile_n, 0, 0, 0))
+        nbytes = self._lib.b2_muon_workspace_bytes(self._rows, self._cols, n, C.byref(self.options))
+        if nbytes == 0:
+            raise _ffi.B2Error(_ffi.ERROR_INVALID_VALUE, "muon_workspace_bytes")
+        self.workspace_bytes = int(nbytes)
+        # torch's caching allocator returns 512-byte aligned blocks; over-allocate and align to 1 KiB
+        self._buf = torch.empty(nbytes + 1024, dtype=torch.uint8, device=device)
+        base = (self._buf.data_ptr() + 1023) // 1024 * 1024
+        self._handle = C.c_void_p()
+        check(self._lib.b2_muon_plan_create(C.byref(self._handle), self._rows, self._cols, n, C.byref(self.options),
+                                            base, nbytes, _stream()), "muon_plan_create")
+
+    def close(self):
+        if getattr(self, "_handle", None) and self._handle.value:
+            torch.cuda.synchronize()
+            self._lib.b2_muon_plan_destroy(self._handle)
+            self._handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def handle(self):
+        return self._handle
+
+    def flops_per_iteration(self) -> float:
+        return float(self._lib.b2_muon_plan_flops_per_iteration(self._handle))
+
+    def status(self) -> int:
+        return int(self._lib.b2_muon_plan_status(self._handle, _stream()))
+
+    def scratch(self, slot: int, which: int) -> torch.Tensor:
+        """View of a scratch buffer as a torch tensor (see b2_muon_plan_scratch)."""
+        p, n = C.c_void_p(), C.c_size_t()
+        check(self._lib.b2_muon_plan_scratch(self._handle, slot, which, C.byref(p), C.byref(n)), "muon_plan_scratch")
+        off = p.value - self._buf.data_ptr()
+        raw = self._buf[off:off + n.value]
+        rows, cols = self.shapes[slot] if which != 4 else (0, 0)
+        if which in (0, 7):
+            dt = torch.float16 if self.options.operand_format == OPERAND_F16 else torch.bfloat16
+            return raw.view(dt).view(rows, cols)
+        if which == 1:
+            return raw.view(torch.float32).view(rows, cols)
+        if which in (5, 6):
+            dt = torch.float16 if self.options.operand_format == OPERAND_F16 else torch.bfloat16
+            n_ = min(rows, cols)
+            return raw.view(dt).view(n_, -1)[:, :n_]
+        if which == 4:
+            return raw.view(torch.int32)
+        return raw.view(torch.float32)
+
+
+class OptimizerModule:
+    """`OptimizerModule` (crates/cuda-kernels/src/gpt/optimizer/launcher/mod.rs:20-26)."""
+
+    def __init__(self):
+        self._lib = _ffi.lib()
+        self.quant = Nvfp4QuantModule()
+
+    # launcher/mod.rs:43-56
+    def verify_storage_layout(self) -> None:
+        check(self._lib.b2_verify_storage_layout(_stream()), "verify_storage_layout")
+
+    # launcher/muon_mega.rs:24-51
+    def muon_mega_update(self, plan: MuonPlan, slots: torch.Tensor, args: MuonMegaUpdateArgs) -> None:
+        a, keep = args.c_args()
+        check(self._lib.b2_muon_mega_update(plan.handle, _ptr(slots), C.byref(a), _stream()), "muon_mega_update")
+        del keep
+
+    # launcher/muon_mega.rs:53-115
+    def muon_tma_prepare_polar(self, plan: MuonPlan, slots: torch.Tensor, args: MuonMegaUpdateArgs) -> None:
+        a, keep = args.c_args()
+        check(self._lib.b2_muon_prepare_polar(plan.handle, _ptr(slots), C.byref(a), _stream()), "muon_prepare_polar")
+        del keep
+
+    def muon_polar(self, plan: MuonPlan, args: MuonMegaUpdateArgs) -> None:
+        a, keep = args.c_args()
+        check(self._lib.b2_muon_polar(plan.handle, C.byref(a), _stream()), "muon_polar")
+        del keep
+
+    # launcher/muon_mega.rs:139-157
+    def muon_tma_finish_update(self, plan: MuonPlan, slots: torch.Tensor, args: MuonMegaUpdateArgs) -> None:
+        a, keep = args.c_args()
+        check(self._lib.b2_muon_finish_update(plan.handle, _ptr(slots), C.byref(a), _stream()), "muon_finish_update")
+        del keep
+
+    # launcher/muon_mega.rs:159-165
+    def muon_tma_finish_update_deferred_quantization(self, plan: MuonPlan, slots: torch.Tensor,
+                                                     args: MuonMegaUpdateArgs) -> None:
+        a, keep = args.c_args()
+        check(self._lib.b2_muon_finish_update_deferred_quantization(plan.handle, _ptr(slots), C.byref(a), _stream()),
+              "muon_finish_update_deferred_quantization")
+        del keep
+
+    # launcher/mod.rs:67-95
+    def materialize_master(self, bytes_: torch.Tensor, scales: torch.Tensor, global_scale: torch.Tensor,
+                           master: torch.Tensor, amax: torch.Tensor, chunk_amax: torch.Tensor, len_: int,
+                           scale_layout: int = SCALES_CSF) -> None:
+        check(self._lib.b2_materialize_master(_ptr(bytes_), _ptr(scales), _ptr(global_scale), _ptr(master), _ptr(amax),
+                                              _ptr(chunk_amax), len_, scale_layout, _stream()), "materialize_master")
+
+    def _sf_args(self, *, bytes, scales, global_scale, z_master, x_master, amax, len, scale_rows, scale_k, beta,
+                 symexp_lin_beta=0.0, precomputed_values=None, scale_layout=SCALES_CSF, **_ignored):
+        return _CSf(_ptr(bytes), _ptr(scales), _ptr(global_scale), _ptr(z_master), _ptr(x_master),
+                    _ptr(precomputed_values), _ptr(amax), len, scale_rows, scale_k, beta, symexp_lin_beta, scale_layout)
+
+    # launcher/update.rs:77-133
+    def materialize_schedule_free(self, **kw) -> None:
+        a = self._sf_args(**kw)
+        check(self._lib.b2_materialize_schedule_free(C.byref(a), _stream()), "materialize_schedule_free")
+
+    # launcher/update.rs:25-75
+    def materialize_schedule_free_precomputed(self, **kw) -> None:
+        a = self._sf_args(**kw)
+        check(self._lib.b2_materialize_schedule_free_precomputed(C.byref(a), _stream()),
+              "materialize_schedule_free_precomputed")
+
+    def _adam_args(self, *, z_master, x_master, grad, grad_scale, first_moment, second_moment, len, learning_rate,
+                   weight_decay, beta1, beta2, beta1_correction, beta2_correction, eps, average_coefficient,
+                   schedule_beta=0.0, bytes=None, scales=None, global_scale=None, amax=None, chunk_amax=None,
+                   scale_layout=SCALES_CSF):
+        return _CAdam(_ptr(bytes), _ptr(scales), _ptr(global_scale), _ptr(z_master), _ptr(x_master), _ptr(grad),
+                      grad_scale, scale_layout, _ptr(first_moment), _ptr(second_moment), _ptr(amax), _ptr(chunk_amax),
+                      len, learning_rate, weight_decay, beta1, beta2, beta1_correction, beta2_correction, eps,
+                      average_coefficient, schedule_beta)
+
+    # launcher/adam.rs:9-21
+    def apply_adamw_update(self, **kw) -> None:
+        a = self._adam_args(**kw)
+        check(self._lib.b2_apply_adamw_update(C.byref(a), _stream()), "apply_adamw_update")
+
+    # launcher/adam.rs:23-28
+    def apply_adamw_update_deferred_quantization(self, **kw) -> None:
+        a = self._adam_args(**kw)
+        check(self._lib.b2_apply_adamw_update_deferred_quantization(C.byref(a), _stream()),
+              "apply_adamw_update_deferred_quantization")
+
+    # launcher/adam.rs:45-72
+    def apply_fp32_adamw_update(self, **kw) -> None:
+        a = self._adam_args(**kw)
+        check(self._lib.b2_apply_fp32_adamw_update(C.byref(a), _stream()), "apply_fp32_adamw_update")
+
+    # launcher/adam.rs:30-43
+    def zero_f32_pointer_table(self, pointers: torch.Tensor, pointer_count: int) -> None:
+        check(self._lib.b2_zero_f32_pointer_table(_ptr(pointers), pointer_count, _stream()), "zero_f32_pointer_table")
+
+
+# ---- host schedules (src/training/learning_rate/schedule.rs) ---------------------------------
+def schedule_free_beta(step: int, warmup_steps: int = 5, beta1: float = 0.2, rho: float = 0.5) -> float:
+    return float(_ffi.lib().b2_schedule_free_beta(step, warmup_steps, beta1, rho))
+
+
+def warmup_multiplier(step: int, warmup_steps: int = 5, start_ratio: float = 0.05) -> float:
+    return float(_ffi.lib().b2_warmup_multiplier(step, warmup_steps, start_ratio))
+
+
+class AverageCoefficient:
+    """Running `schedule_free_average_coefficient` (schedule.rs:36-47)."""
+
+    def __init__(self, warmup_steps: int = 5, start_ratio: float = 0.05):
+        self.warmup_steps, self.start_ratio = warmup_steps, start_ratio
+        self._sum = C.c_float(0.0)
+
+    def step(self, step: int) -> float:
+        return float(_ffi.lib().b2_schedule_free_average_coefficient(step, self.warmup_steps, self.start_ratio,
+                                                                     C.byref(self._sum)))

@@ -1,0 +1,152 @@
+"""Whole Muon + NVFP4 step through `muon_mega_update` against the oracle and the reference's
+own known answers."""
+import numpy as np
+import pytest
+import torch
+
+import llmini_b200 as b2
+from oracle import oracle as o
+from tests import _util as U
+from tests.gpu_util import bf16_bits, bf16_from_bits, decode_scales, dev, host, rcp_table
+
+pytestmark = pytest.mark.gpu
+F = np.float32
+
+
+def _slot(rows, cols, grad, mom_bits, z, x, layout):
+    s = b2.MuonSlot.allocate(rows, cols, layout)
+    s.grad.copy_(dev(grad).view(rows, cols))
+    s.momentum.copy_(bf16_from_bits(mom_bits).view(rows, cols))
+    s.z_master.copy_(dev(z).view(rows, cols))
+    s.x_master.copy_(dev(x).view(rows, cols))
+    return s
+
+
+@pytest.mark.parametrize("rows,cols", [(64, 64), (64, 32), (32, 64)])
+def test_reference_constant_gradient_recurrence(rows, cols):
+    # crates/cuda-kernels/tests/optimizer/muon/fixture.rs:12-63 — F16 operands, reference
+    # coefficient table, one iteration; every z and x within 1e-7 of the closed form.
+    n = rows * cols
+    layout = b2.SCALES_RAW if cols % 128 else b2.SCALES_CSF
+    s = _slot(rows, cols, np.full(n, 0.5, F), np.zeros(n, np.uint16), np.ones(n, F), np.ones(n, F), layout)
+    plan = b2.MuonPlan([(rows, cols)], operand_format=b2.OPERAND_F16, scale_layout=layout)
+    b2.OptimizerModule().muon_mega_update(plan, b2.slot_table([s]), b2.MuonMegaUpdateArgs(
+        mu=0.95, grad_scale=0.5, learning_rate=0.25, weight_decay=0.1, average_coefficient=1.0, iterations=1))
+    torch.cuda.synchronize()
+    assert plan.status() == 0
+    nest = (F(1.0) - F(0.95)) * (F(1.0) + F(0.95)) * F(0.5) * F(0.5)
+    upd = F(o.lib().orc_polar_first_iteration_scalar(F(nest), rows, cols))
+    expected = (F(1.0) - F(0.25) * F(0.1)) - F(0.25) * upd * (F(0.2) * np.sqrt(F(max(rows, cols))))
+    assert np.max(np.abs(host(s.z_master) - expected)) <= 1e-7
+    assert np.max(np.abs(host(s.x_master) - expected)) <= 1e-7
+    assert abs(host(s.global_scale)[0] - abs(expected) / F(1536.0)) <= 1e-8
+    assert host(s.bytes).any() and host(s.scales).any()
+    plan.close()
+
+
+def test_reference_nonconstant_wide_recurrence():
+    # crates/cuda-kernels/tests/optimizer/muon/nonconstant.rs:19-75 — 2e-3 absolute against the
+    # host three-product oracle with F16 rounding.
+    rows, cols, n = 32, 64, 32 * 64
+    i = np.arange(n)
+    grad = ((i % 37).astype(F) - F(18.0)) * F(0.0003) + (i // cols).astype(F) * F(0.00001)
+    s = _slot(rows, cols, grad, np.zeros(n, np.uint16), np.ones(n, F), np.ones(n, F), b2.SCALES_RAW)
+    plan = b2.MuonPlan([(rows, cols)], operand_format=b2.OPERAND_F16, scale_layout=b2.SCALES_RAW)
+    b2.OptimizerModule().muon_mega_update(plan, b2.slot_table([s]), b2.MuonMegaUpdateArgs(
+        mu=0.95, grad_scale=0.5, learning_rate=0.25, weight_decay=0.1, average_coefficient=1.0, iterations=5))
+    torch.cuda.synchronize()
+    sg = grad * F(0.5)
+    mu = F(0.95)
+    nest = np.array([np.float32(np.float64(F(1) - mu) * np.float64(g) + np.float64(mu * (F(1) - mu) * g)) for g in sg], F)
+    inv = F(1.0) / (np.sqrt(np.sum(nest * nest, dtype=F)) * F(1.01) + F(1.0e-7))
+    polar = o.polar((nest * inv).reshape(rows, cols), 5, o.polar_express_coefficients(5),
+                    round_mode=o.ROUND_F16_HOST, form="three_product").reshape(-1)
+    expected = (F(1.0) - F(0.25) * F(0.1)) - F(0.25) * (F(0.2) * np.sqrt(F(64.0))) * polar
+    assert np.max(np.abs(host(s.x_master).ravel() - expected)) <= 2e-3
+    assert np.max(np.abs(host(s.z_master).ravel() - expected)) <= 2e-3
+    plan.close()
+
+
+def _check_step(shapes, layout, fmt, coeffs, target=b2.QUANTIZE_X, seed=0, outliers=True):
+    rng = np.random.default_rng(seed)
+    hp = dict(mu=0.95, grad_scale=1.0, learning_rate=0.02, weight_decay=0.025, average_coefficient=0.5,
+              schedule_beta=0.2, iterations=5)
+    data, slots = [], []
+    for r, c in shapes:
+        z = U.weights(rng, r * c)
+        x = U.weights(rng, r * c)
+        g = U.gradients(rng, r * c, outlier_fraction=0.001 if outliers else 0.0)
+        m = o.bf16_bits(U.gradients(rng, r * c, outlier_fraction=0.0))
+        data.append((g, m, z, x))
+        slots.append(_slot(r, c, g, m, z, x, layout))
+    plan = b2.MuonPlan(shapes, operand_format=fmt, scale_layout=layout, quantize_target=target)
+    b2.OptimizerModule().muon_mega_update(plan, b2.slot_table(slots), b2.MuonMegaUpdateArgs(coefficients=coeffs, **hp))
+    torch.cuda.synchronize()
+    assert plan.status() == 0
+    mode = o.ROUND_BF16 if fmt == b2.OPERAND_BF16 else o.ROUND_F16
+    for i, (s, (r, c)) in enumerate(zip(slots, shapes)):
+        g, m, z, x = data[i]
+        ref = o.muon_step(g, m, z, x, r, c, mu=0.95, grad_scale=1.0, lr=0.02, wd=0.025, c_avg=0.5, sched_beta=0.2,
+                          iterations=5, coeffs=coeffs, round_mode=mode, quantize_y=(target == b2.QUANTIZE_Y))
+        assert np.array_equal(bf16_bits(s.momentum).ravel(), ref.momentum_bits)
+        Ug = host(plan.scratch(i, 1))
+        r2, mx = U.rel_l2(Ug, ref.U), U.max_rel_to_peak(Ug, ref.U)
+        print(f"slot {i} {r}x{c}: NS rel_l2 {r2:.3e} max/peak {mx:.3e}")
+        assert r2 <= 2e-2 and mx <= 2e-2          # Newton-Schulz in 16-bit operands
+        # elementwise stages given the device's own U: bit-exact
+        z2, x2, y2, ax, ay = o.update(Ug, z, x, r, c, 0.02, 0.025, 0.5, 0.2)
+        assert np.array_equal(host(s.z_master).ravel(), z2)
+        assert np.array_equal(host(s.x_master).ravel(), x2)
+        assert np.array_equal(host(s.grad).ravel(), y2)
+        assert host(s.schedule_amax)[0] == ay
+        # weights against the all-oracle step: bounded by lr * scale * NS error
+        scale = 0.2 * np.sqrt(max(r, c))
+        tol = 0.02 * scale * 2e-2 * np.max(np.abs(ref.U)) + 1e-7
+        assert np.max(np.abs(host(s.z_master).ravel() - ref.z)) <= tol
+        # NVFP4 output: bit-exact given identical FP32 pre-quantisation weights
+        src, am = (y2, ay) if target == b2.QUANTIZE_Y else (x2, ax)
+        gs = host(s.global_scale)[0]
+        codes, raw, ogs, misses = o.nvfp4_quantize(src, amax=am, rcp_table=rcp_table(gs))
+        assert misses == 0 and gs == ogs
+        assert np.array_equal(host(s.bytes)[: r * c // 2], codes)
+        assert np.array_equal(decode_scales(s.scales, r, c, layout), raw)
+    plan.close()
+
+
+def test_config1_single_mlp_matrix_fixed_triple_bf16():
+    # one GPT-2 MLP matrix 3072 x 768, fixed coefficient triple, BF16 operands, seed 0
+    _check_step([(3072, 768)], b2.SCALES_CSF, b2.OPERAND_BF16, o.fixed_coefficients(5), seed=0)
+
+
+def test_config1_reference_recipe_f16():
+    _check_step([(3072, 768)], b2.SCALES_CSF, b2.OPERAND_F16, o.polar_express_coefficients(5), seed=0)
+
+
+def test_one_gpt2_layer_mixed_shapes_quantise_y():
+    _check_step([(2304, 768), (768, 768), (3072, 768), (768, 3072), (0, 0)], b2.SCALES_CSF, b2.OPERAND_BF16,
+                o.fixed_coefficients(5), target=b2.QUANTIZE_Y, seed=1, outliers=False)
+
+
+def test_ragged_shapes_raw_scales():
+    _check_step([(1600, 320), (48, 1600), (200, 208)], b2.SCALES_RAW, b2.OPERAND_BF16, o.fixed_coefficients(5), seed=2)
+
+
+def test_second_step_chains_on_state():
+    # two consecutive steps: the momentum state and y written by step 1 feed step 2 correctly
+    rng = np.random.default_rng(3)
+    r, c = 256, 512
+    z, x = U.weights(rng, r * c), U.weights(rng, r * c)
+    g1, g2 = U.gradients(rng, r * c), U.gradients(rng, r * c)
+    s = _slot(r, c, g1, np.zeros(r * c, np.uint16), z, x, b2.SCALES_CSF)
+    plan = b2.MuonPlan([(r, c)])
+    opt, table = b2.OptimizerModule(), b2.slot_table([s])
+    args = b2.MuonMegaUpdateArgs(learning_rate=0.02, coefficients=o.fixed_coefficients(5))
+    opt.muon_mega_update(plan, table, args)
+    s.grad.copy_(dev(g2).view(r, c))
+    opt.muon_mega_update(plan, table, args)
+    torch.cuda.synchronize()
+    m1, _, _ = o.momentum(g1, np.zeros(r * c, np.uint16), 0.95, 1.0)
+    m2, _, _ = o.momentum(g2, m1, 0.95, 1.0)
+    assert np.array_equal(bf16_bits(s.momentum).ravel(), m2)
+    assert plan.status() == 0
+    plan.close()

@@ -1,0 +1,162 @@
+"""NVFP4 quantiser on the GPU against the oracle: bit-exact codes, block scales, tensor scale."""
+import numpy as np
+import pytest
+import torch
+
+import llmini_b200 as b2
+from oracle import oracle as o
+from tests import _util as U
+from tests.gpu_util import dev, host, rcp_table
+
+pytestmark = pytest.mark.gpu
+F = np.float32
+
+
+def _quantize_gpu(x, layout, rows=None, k=None):
+    q = b2.Nvfp4QuantModule()
+    n = x.size
+    xd = dev(x)
+    chunk = torch.zeros((n + 2047) // 2048, device="cuda")
+    amax = torch.zeros(1, device="cuda")
+    q.tensor_amax_f32(xd, chunk, amax, n)
+    fp4 = torch.zeros(n // 2, dtype=torch.uint8, device="cuda")
+    if layout == b2.SCALES_CSF:
+        scales = b2.zero_scales(rows, k)
+    else:
+        scales = torch.zeros(n // 16, dtype=torch.uint8, device="cuda")
+    gs = torch.zeros(1, device="cuda")
+    q.fp32_to_nvfp4_four_six(xd, amax, fp4, scales, gs, n // 16, layout)
+    torch.cuda.synchronize()
+    return host(fp4), host(scales), host(gs)[0], host(amax)[0], host(chunk)
+
+
+def test_abi_handshake():
+    b2.OptimizerModule().verify_storage_layout()
+
+
+def test_known_sixteen_values():
+    # crates/cuda-kernels/tests/nvfp4_quant.rs:21-53
+    x = np.array([-3.25, -2.0, -1.25, -0.5, -0.125, 0.0, 0.25, 0.75, 1.0, 1.5, 2.25, 3.0, 4.0, 5.0, 6.5, 8.0], F)
+    fp4, scales, gs, amax, _ = _quantize_gpu(x, b2.SCALES_RAW)
+    assert amax == 8.0 and abs(gs - F(8.0) / F(1536.0)) <= 1e-8
+    assert fp4.any() and scales.any()
+    codes, sc, ogs, _ = o.nvfp4_quantize(x, rcp_table=rcp_table(gs))
+    assert np.array_equal(fp4, codes) and np.array_equal(scales, sc) and gs == ogs
+
+
+def test_negative_underflow_keeps_sign_nibble():
+    # values that round to zero keep their sign bit (code 0x8), as the oracle assumes
+    x = np.zeros(16, F)
+    x[0], x[1], x[2], x[3], x[15] = -1e-9, -0.0, 1e-9, -0.2, 6.0
+    fp4, scales, gs, _, _ = _quantize_gpu(x, b2.SCALES_RAW)
+    codes, sc, _, _ = o.nvfp4_quantize(x, rcp_table=rcp_table(gs))
+    assert np.array_equal(fp4, codes), (fp4, codes)
+    assert np.array_equal(scales, sc)
+
+
+@pytest.mark.parametrize("rows,k,layout", [
+    (256, 4096, b2.SCALES_CSF), (1024, 4096, b2.SCALES_CSF), (3072, 768, b2.SCALES_CSF),
+    (129, 256, b2.SCALES_CSF), (1, 4096, b2.SCALES_CSF), (1, 128, b2.SCALES_CSF),
+    (7, 48, b2.SCALES_RAW), (1600, 1600, b2.SCALES_RAW), (1, 16, b2.SCALES_RAW), (4096, 4096, b2.SCALES_CSF),
+])
+def test_flat_quantiser_bit_exact(rows, k, layout):
+    rng = np.random.default_rng(rows * 131 + k)
+    x = U.with_outliers(rng, U.weights(rng, rows * k))
+    fp4, scales, gs, amax, chunk = _quantize_gpu(x, layout, rows, k)
+    assert amax == np.max(np.abs(x))
+    want_chunks = np.array([np.max(np.abs(x[i:i + 2048])) for i in range(0, x.size, 2048)], F)
+    assert np.array_equal(chunk, want_chunks)
+    codes, raw, ogs, misses = o.nvfp4_quantize(x, amax=amax, rcp_table=rcp_table(gs))
+    assert misses == 0 and gs == ogs
+    assert np.array_equal(fp4, codes)
+    got_raw = scales if layout == b2.SCALES_RAW else o.csf_decode_matrix(scales, rows, k)
+    assert np.array_equal(got_raw, raw)
+    if layout == b2.SCALES_CSF:  # whole storage, header and padding included
+        assert np.array_equal(scales, o.csf_encode(raw, rows, k))
+    # the optimised kernel equals the literal one-thread-per-group transcription bit for bit
+    q = b2.Nvfp4QuantModule()
+    l4, ls, lg = q.debug_quantize_literal(dev(x), dev(np.array([amax], F)))
+    assert np.array_equal(host(l4), fp4) and np.array_equal(host(ls), raw) and host(lg)[0] == gs
+    # how often the correctly rounded reciprocal would have differed (reported, not asserted)
+    c2, r2, _, _ = o.nvfp4_quantize(x, amax=amax)
+    print(f"exact-rcp mismatches: codes {int(np.count_nonzero(c2 != codes))} scales {int(np.count_nonzero(r2 != raw))} of {x.size}")
+
+
+def test_all_zero_tensor_and_empty():
+    x = np.zeros(4096, F)
+    fp4, scales, gs, amax, _ = _quantize_gpu(x, b2.SCALES_RAW)
+    assert gs == 1.0 and amax == 0.0 and not fp4.any() and not scales.any()
+    q = b2.Nvfp4QuantModule()
+    g = torch.zeros(1, device="cuda")
+    q.fp32_to_nvfp4_four_six(dev(x), dev(np.zeros(1, F)), torch.zeros(8, dtype=torch.uint8, device="cuda"),
+                             torch.zeros(8, dtype=torch.uint8, device="cuda"), g, 0, b2.SCALES_RAW)
+    torch.cuda.synchronize()
+    assert host(g)[0] == 1.0
+
+
+def test_materialize_master_and_schedule_free():
+    rng = np.random.default_rng(5)
+    rows, k = 384, 1024
+    n = rows * k
+    z, x = U.weights(rng, n), U.weights(rng, n)
+    opt = b2.OptimizerModule()
+    t = b2.Nvfp4Tensor.empty(rows, k)
+    amax, chunk = torch.zeros(1, device="cuda"), torch.zeros(n // 2048, device="cuda")
+    opt.materialize_master(t.bytes, t.scales, t.global_scale, dev(x), amax, chunk, n)
+    torch.cuda.synchronize()
+    gs = host(t.global_scale)[0]
+    codes, raw, ogs, _ = o.nvfp4_quantize(x, rcp_table=rcp_table(gs))
+    assert gs == ogs and np.array_equal(host(t.bytes), codes)
+    assert np.array_equal(host(t.scales), o.csf_encode(raw, rows, k))
+
+    beta = 0.4
+    y, am = o.schedule_free_values(z, x, beta)
+    t2 = b2.Nvfp4Tensor.empty(rows, k)
+    amax2 = torch.full((1,), 123.0, device="cuda")
+    kw = dict(bytes=t2.bytes, scales=t2.scales, global_scale=t2.global_scale, z_master=dev(z), x_master=dev(x),
+              amax=amax2, len=n, scale_rows=rows, scale_k=k, beta=beta)
+    opt.materialize_schedule_free(**kw)
+    torch.cuda.synchronize()
+    assert host(amax2)[0] == am
+    gs2 = host(t2.global_scale)[0]
+    codes2, raw2, ogs2, _ = o.nvfp4_quantize(y, amax=am, rcp_table=rcp_table(gs2))
+    assert gs2 == ogs2 and np.array_equal(host(t2.bytes), codes2)
+    assert np.array_equal(host(t2.scales), o.csf_encode(raw2, rows, k))
+    # precomputed values + cached amax (the production per-step requant): same bits
+    t3 = b2.Nvfp4Tensor.empty(rows, k)
+    kw.update(bytes=t3.bytes, scales=t3.scales, global_scale=t3.global_scale, precomputed_values=dev(y))
+    opt.materialize_schedule_free_precomputed(**kw)
+    torch.cuda.synchronize()
+    assert np.array_equal(host(t3.bytes), codes2) and np.array_equal(host(t3.scales), host(t2.scales))
+    # on-the-fly values from z, x with the cached amax
+    t4 = b2.Nvfp4Tensor.empty(rows, k)
+    kw.update(bytes=t4.bytes, scales=t4.scales, global_scale=t4.global_scale, precomputed_values=None)
+    opt.materialize_schedule_free_precomputed(**kw)
+    torch.cuda.synchronize()
+    assert np.array_equal(host(t4.bytes), codes2)
+    with pytest.raises(b2.B2Error):
+        kw.update(symexp_lin_beta=0.5)
+        opt.materialize_schedule_free(**kw)
+
+
+def test_quantise_round_trip_property_large():
+    # size-independent property at a bandwidth-sweep shape: |dequant - x| <= half a code step
+    rows, k = 16384, 4096
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn(rows * k, device="cuda", generator=g) * 0.02
+    q = b2.Nvfp4QuantModule()
+    chunk, amax = torch.zeros(rows * k // 2048, device="cuda"), torch.zeros(1, device="cuda")
+    q.tensor_amax_f32(x, chunk, amax, rows * k)
+    t = b2.Nvfp4Tensor.empty(rows, k, b2.SCALES_RAW)
+    q.fp32_to_nvfp4_four_six(x, amax, t.bytes, t.scales, t.global_scale, rows * k // 16, b2.SCALES_RAW)
+    torch.cuda.synchronize()
+    assert amax.item() == x.abs().max().item()
+    lut = torch.tensor([0, .5, 1, 1.5, 2, 3, 4, 6, -0., -.5, -1, -1.5, -2, -3, -4, -6], device="cuda")
+    codes = torch.stack([t.bytes & 15, t.bytes >> 4], dim=1).reshape(-1).long()
+    sc = t.scales.view(torch.float8_e4m3fn).float().repeat_interleave(16)
+    deq = lut[codes] * sc * t.global_scale
+    # per element: error at most half the largest code gap (2 at the top of the grid) times its scale,
+    # plus the E4M3 rounding of the block scale (relative 2^-4) on the block maximum
+    bound = sc * t.global_scale * 1.0 + 1e-12
+    blockmax = x.abs().view(-1, 16).max(dim=1).values.repeat_interleave(16)
+    assert bool(((deq - x).abs() <= bound + blockmax * 0.07).all())

@@ -1,0 +1,208 @@
+"""Elementwise stages on the GPU against the oracle: momentum / norm (M+N), update (U),
+requantisation (Q) through the plan entry points, AdamW, and the reference's known answers."""
+import numpy as np
+import pytest
+import torch
+
+import llmini_b200 as b2
+from oracle import oracle as o
+from tests import _util as U
+from tests.gpu_util import bf16_bits, bf16_from_bits, decode_scales, dev, host, rcp_table
+
+pytestmark = pytest.mark.gpu
+F = np.float32
+
+
+def _fill_slot(slot, grad, mom_bits, z, x):
+    slot.grad.copy_(dev(grad).view_as(slot.grad))
+    slot.momentum.copy_(bf16_from_bits(mom_bits).view_as(slot.momentum))
+    slot.z_master.copy_(dev(z).view_as(slot.z_master))
+    slot.x_master.copy_(dev(x).view_as(slot.x_master))
+
+
+@pytest.mark.parametrize("shapes,layout", [
+    ([(64, 128), (128, 64)], b2.SCALES_CSF),
+    ([(32, 64), (96, 48), (0, 0), (7, 16), (300, 1040)], b2.SCALES_RAW),
+])
+def test_prepare_matches_oracle(shapes, layout):
+    rng = np.random.default_rng(11)
+    opt = b2.OptimizerModule()
+    slots = [b2.MuonSlot.allocate(r, c, layout) for r, c in shapes]
+    inputs = []
+    for s, (r, c) in zip(slots, shapes):
+        g = U.gradients(rng, r * c)
+        m = o.bf16_bits(U.weights(rng, r * c, 1e-3))
+        _fill_slot(s, g, m, np.zeros(r * c, F), np.zeros(r * c, F))
+        inputs.append((g, m))
+    plan = b2.MuonPlan(shapes, scale_layout=layout)
+    table = b2.slot_table(slots)
+    for nesterov in (True, False):
+        args = b2.MuonMegaUpdateArgs(mu=0.9, grad_scale=0.125, iterations=1, nesterov=nesterov)
+        opt.muon_tma_prepare_polar(plan, table, args)
+        torch.cuda.synchronize()
+        for i, (s, (r, c)) in enumerate(zip(slots, shapes)):
+            if r * c == 0:
+                continue
+            g, m = inputs[i]
+            m2, u, ss = o.momentum(g, m, 0.9, 0.125, nesterov=nesterov)
+            assert np.array_equal(bf16_bits(s.momentum).ravel(), m2)  # BF16 state: bit-exact
+            inv = o.inv_norm(ss)
+            got_inv = host(plan.scratch(i, 2))[0]
+            assert abs(got_inv - inv) <= 1e-6 * inv
+            x0 = host(plan.scratch(i, 0).float()).ravel()
+            want = o.round_bf16(u * got_inv)
+            assert np.array_equal(x0, want)
+            inputs[i] = (g, m2)  # the next call chains on the stored state
+    plan.close()
+
+
+def test_momentum_chain_reference_case():
+    # crates/cuda-kernels/tests/optimizer/muon/tma_prepare.rs:87-208 (non-variance branch)
+    opt = b2.OptimizerModule()
+    for rows, cols in [(64, 128), (128, 64)]:
+        n = rows * cols
+        i = np.arange(n)
+        grad = ((i * 73 % 257).astype(F) - F(128.0)) / F(211.0)
+        mom = o.round_bf16(((i * 29 % 131).astype(F) - F(65.0)) / F(173.0))
+        slot = b2.MuonSlot.allocate(rows, cols)
+        _fill_slot(slot, grad, o.bf16_bits(mom), np.zeros(n, F), np.zeros(n, F))
+        plan = b2.MuonPlan([(rows, cols)])
+        table = b2.slot_table([slot])
+        expected_m = mom.copy()
+        for _ in range(6):
+            g = grad * F(0.125)
+            nxt = F(0.9) * expected_m + (F(1.0) - F(0.9)) * g
+            expected_m = o.round_bf16(nxt)
+            opt.muon_tma_prepare_polar(plan, table, b2.MuonMegaUpdateArgs(mu=0.9, grad_scale=0.125, iterations=1))
+            torch.cuda.synchronize()
+            assert np.array_equal(host(slot.momentum.float()).ravel(), expected_m)
+        plan.close()
+
+
+@pytest.mark.parametrize("layout,target", [(b2.SCALES_CSF, b2.QUANTIZE_X), (b2.SCALES_RAW, b2.QUANTIZE_Y)])
+def test_finish_update_matches_oracle(layout, target):
+    rng = np.random.default_rng(21)
+    shapes = [(256, 384), (384, 128), (128, 128)] if layout == b2.SCALES_CSF else [(100, 48), (33, 16), (512, 2064)]
+    opt = b2.OptimizerModule()
+    slots = [b2.MuonSlot.allocate(r, c, layout) for r, c in shapes]
+    plan = b2.MuonPlan(shapes, scale_layout=layout, quantize_target=target)
+    data = []
+    for i, (s, (r, c)) in enumerate(zip(slots, shapes)):
+        z, x = U.weights(rng, r * c), U.weights(rng, r * c)
+        Um = (rng.standard_normal(r * c) * 0.05).astype(F)
+        _fill_slot(s, np.zeros(r * c, F), np.zeros(r * c, np.uint16), z, x)
+        s.learning_rate_multiplier = 1.0 + 0.5 * i
+        plan.scratch(i, 1).copy_(dev(Um).view(r, c))
+        data.append((z, x, Um))
+    table = b2.slot_table(slots)
+    args = b2.MuonMegaUpdateArgs(learning_rate=0.02, weight_decay=0.025, average_coefficient=0.3, schedule_beta=0.6)
+    # the two amax words are cleared by the prepare stage; do the same here
+    opt.muon_tma_prepare_polar(plan, table, args)
+    for s, (z, x, _) in zip(slots, data):
+        s.grad.zero_()
+    for i, (r, c) in enumerate(shapes):
+        plan.scratch(i, 1).copy_(dev(data[i][2]).view(r, c))
+    opt.muon_tma_finish_update(plan, table, args)
+    torch.cuda.synchronize()
+    for i, (s, (r, c)) in enumerate(zip(slots, shapes)):
+        z, x, Um = data[i]
+        lr = F(0.02) * F(s.learning_rate_multiplier)
+        z2, x2, y2, ax, ay = o.update(Um, z, x, r, c, lr, 0.025, 0.3, 0.6)
+        assert np.array_equal(host(s.z_master).ravel(), z2)   # IEEE elementwise: bit-exact
+        assert np.array_equal(host(s.x_master).ravel(), x2)
+        assert np.array_equal(host(s.grad).ravel(), y2)
+        assert host(s.schedule_amax)[0] == ay and host(plan.scratch(i, 3))[0] == ax
+        src, am = (y2, ay) if target == b2.QUANTIZE_Y else (x2, ax)
+        gs = host(s.global_scale)[0]
+        codes, raw, ogs, misses = o.nvfp4_quantize(src, amax=am, rcp_table=rcp_table(gs))
+        assert misses == 0 and gs == ogs
+        assert np.array_equal(host(s.bytes)[: r * c // 2], codes)
+        assert np.array_equal(decode_scales(s.scales, r, c, layout), raw)
+    plan.close()
+
+
+def test_schedule_amax_reference_case():
+    # crates/cuda-kernels/tests/optimizer/muon/tma_finish.rs:23-99 (deferred: no quantisation)
+    n = 32 * 32
+    i = np.arange(n).astype(F)
+    z = (i - F(511.0)) / F(997.0)
+    x = (F(307.0) - i) / F(613.0)
+    expected = np.max(np.abs(z + F(0.4) * (x - z)))
+    opt = b2.OptimizerModule()
+    slot = b2.MuonSlot.allocate(32, 32, b2.SCALES_RAW)
+    _fill_slot(slot, np.zeros(n, F), np.zeros(n, np.uint16), z, x)
+    plan = b2.MuonPlan([(32, 32)], scale_layout=b2.SCALES_RAW)
+    table = b2.slot_table([slot])
+    args = b2.MuonMegaUpdateArgs(learning_rate=0.0, weight_decay=0.0, average_coefficient=0.0, schedule_beta=0.4)
+    opt.muon_tma_prepare_polar(plan, table, args)
+    plan.scratch(0, 1).zero_()
+    opt.muon_tma_finish_update_deferred_quantization(plan, table, args)
+    torch.cuda.synchronize()
+    assert abs(host(slot.schedule_amax)[0] - expected) <= 1e-7
+    assert np.array_equal(host(slot.z_master).ravel(), z) and np.array_equal(host(slot.x_master).ravel(), x)
+    assert not host(slot.bytes).any()
+    plan.close()
+
+
+def _adam_buffers(n, layout=b2.SCALES_RAW):
+    z = lambda v=0.0: torch.full((n,), v, device="cuda")
+    return dict(z_master=z(1.0), x_master=z(1.0), grad=z(0.5), first_moment=z(), second_moment=z(),
+                bytes=torch.zeros(n // 2, dtype=torch.uint8, device="cuda"),
+                scales=torch.zeros(max(n // 16, 1), dtype=torch.uint8, device="cuda"),
+                global_scale=torch.ones(1, device="cuda"), amax=torch.zeros(1, device="cuda"),
+                chunk_amax=torch.zeros((n + 2047) // 2048, device="cuda"), scale_layout=layout)
+
+
+ADAM = dict(grad_scale=0.5, learning_rate=0.25, weight_decay=0.1, beta1=0.9, beta2=0.95, beta1_correction=0.1,
+            beta2_correction=0.05, eps=1.0e-10)
+
+
+def test_adamw_reference_known_answers():
+    # crates/cuda-kernels/tests/optimizer/adam.rs:97-162
+    opt = b2.OptimizerModule()
+    buf = _adam_buffers(32)
+    opt.apply_adamw_update(len=32, average_coefficient=1.0, schedule_beta=0.0, **ADAM, **buf)
+    torch.cuda.synchronize()
+    close = lambda t, v: float((t - v).abs().max()) <= 1e-6
+    assert close(buf["z_master"], 0.725) and close(buf["x_master"], 0.725)
+    assert close(buf["first_moment"], 0.025) and close(buf["second_moment"], 0.003125)
+    assert host(buf["bytes"]).any() and host(buf["scales"]).any()
+    assert abs(host(buf["global_scale"])[0] - F(0.725) / F(1536.0)) <= 1e-8
+    buf = _adam_buffers(32)
+    opt.apply_adamw_update(len=32, average_coefficient=0.25, schedule_beta=0.0, **ADAM, **buf)
+    torch.cuda.synchronize()
+    assert close(buf["z_master"], 0.725) and close(buf["x_master"], 0.93125)
+    buf = _adam_buffers(32)
+    opt.apply_adamw_update_deferred_quantization(len=32, average_coefficient=0.25, schedule_beta=0.4, **ADAM, **buf)
+    torch.cuda.synchronize()
+    zz, xx = host(buf["z_master"])[0], host(buf["x_master"])[0]
+    want = abs(zz + F(0.4) * (xx - zz))
+    assert close(buf["amax"], want) and close(buf["grad"], want)
+    ptrs = torch.tensor([buf["amax"].data_ptr()], dtype=torch.int64, device="cuda")
+    opt.zero_f32_pointer_table(ptrs, 1)
+    torch.cuda.synchronize()
+    assert host(buf["amax"])[0] == 0.0
+
+
+@pytest.mark.parametrize("n", [16, 2048, 50304 * 16, 4099])
+def test_adamw_matches_oracle(n):
+    rng = np.random.default_rng(n)
+    z, x = U.weights(rng, n), U.weights(rng, n)
+    g, m1, m2 = U.gradients(rng, n), U.weights(rng, n, 1e-3), np.abs(U.weights(rng, n, 1e-6))
+    hp = dict(grad_scale=0.7, lr=2e-4, wd=0.005, beta1=0.9, beta2=0.95, bc1=0.19, bc2=0.0975, eps=1e-10)
+    z2, x2, y2, a2, b2_, am = o.adamw(z, x, g, m1, m2, c_avg=0.5, sched_beta=0.3, **hp)
+    opt = b2.OptimizerModule()
+    kw = dict(grad_scale=0.7, learning_rate=2e-4, weight_decay=0.005, beta1=0.9, beta2=0.95, beta1_correction=0.19,
+              beta2_correction=0.0975, eps=1e-10, average_coefficient=0.5, schedule_beta=0.3, len=n)
+    t = dict(z_master=dev(z), x_master=dev(x), grad=dev(g), first_moment=dev(m1), second_moment=dev(m2))
+    if n % 16 == 0:
+        amax = torch.zeros(1, device="cuda")
+        opt.apply_adamw_update_deferred_quantization(amax=amax, **kw, **t)
+        torch.cuda.synchronize()
+        assert host(amax)[0] == am and np.array_equal(host(t["grad"]), y2)
+    else:
+        opt.apply_fp32_adamw_update(**kw, **t)
+        torch.cuda.synchronize()
+        assert np.array_equal(host(t["grad"]), g)  # untouched without the schedule output
+    for key, want in (("z_master", z2), ("x_master", x2), ("first_moment", a2), ("second_moment", b2_)):
+        assert np.array_equal(host(t[key]), want), key  # IEEE elementwise: bit-exact
