@@ -74,7 +74,10 @@ typedef struct b2_muon_options {
                                  .../muon/fused/body.rs:90-101); B2_QUANTIZE_Y: the
                                  schedule-free training weights y */
     uint32_t max_iterations;  /* upper bound on b2_muon_step_args.iterations (0 -> 5) */
-    uint32_t reserved[4];
+    uint32_t reserved[4];     /* [0]: GEMM tile override (0 = choose; 128 / 256 = one CTA per
+                                 128 x N tile; 512 = two-CTA 256 x 256 tiles);
+                                 [1], [2]: measurement-only knobs (phase mask, kernel flags),
+                                 leave 0; [3]: must be 0 */
 } b2_muon_options;
 
 /* Step scalars: `MuonMegaUpdateArgs` (.../optimizer/args/muon.rs:25-44) and

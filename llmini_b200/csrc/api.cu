@@ -100,10 +100,11 @@ double slot_flops(uint32_t rows, uint32_t cols) {
 }
 
 enum ProblemType { kGram0 = 0, kGram1, kPoly, kApply0, kApply1, kLast0, kLast1, kProblemTypes };
-enum MapKind { kLX0 = 0, kLX1, kLG, kLQ, kSX0, kSX1, kSG, kSQ, kSU, kMapsPerSlot };
+// load maps: *K = box 64 (K) x 128 rows for K-major use, *M = box 64 x 64 for MN-major use
+enum MapKind { kLX0K = 0, kLX1K, kLX0M, kLX1M, kLG, kLQ, kSX0, kSX1, kSG, kSQ, kSU, kMapsPerSlot };
 
 struct SlotLayout {
-    uint32_t rows, cols, n, m, ldg, tiles_m_nn, tiles_n_nn;
+    uint32_t rows, cols, n, m, ldg, tiles_m_nn, tiles_n_nn, sub_m_nn;
     uint64_t len;
     size_t off_x[2], off_u, off_g16, off_q16, off_frag;
 };
@@ -112,6 +113,8 @@ struct Layout {
     std::vector<uint32_t> chunk_prefix;  // slot_count + 1
     uint32_t total_chunks = 0;
     int bn = 256;
+    int pair = 0;   // 1: two-CTA 256 x 256 tiles
+    int tile_m = 128;
     size_t off_prefix, off_partials, off_inv_norm, off_amax_x, off_status, off_x0_ptrs, off_u_ptrs, off_maps,
         off_problems, off_tiles_nn, off_tiles_out, off_meta_end, total;
     uint32_t tiles_nn = 0, tiles_out = 0;
@@ -125,29 +128,38 @@ bool valid_shape(uint32_t rows, uint32_t cols, const b2_muon_options &o) {
     return true;
 }
 
-int pick_block_n(const uint32_t *rows, const uint32_t *cols, uint32_t count, const b2_muon_options &o) {
-    if (o.reserved[0] == 128 || o.reserved[0] == 256) return (int)o.reserved[0];
-    // padded tensor work of the three GEMMs for each candidate width
-    double cost[2] = {0, 0};
-    const int cand[2] = {128, 256};
-    for (int ci = 0; ci < 2; ++ci) {
+// Tile configuration: reserved[0] = 128 / 256 forces the single-CTA kernel with that width,
+// 512 forces the two-CTA pair; 0 picks the cheapest by padded tensor work, weighted by how
+// well each configuration feeds the tensor core (measured: the pair streams 1.5x fewer bytes
+// per FLOP than 128 x 256, which in turn beats 128 x 128).
+void pick_tiles(const uint32_t *rows, const uint32_t *cols, uint32_t count, const b2_muon_options &o, int &bn,
+                int &pair) {
+    if (o.reserved[0] == 128 || o.reserved[0] == 256) { bn = (int)o.reserved[0]; pair = 0; return; }
+    if (o.reserved[0] == 512) { bn = 256; pair = 1; return; }
+    const int tm[3] = {128, 128, 256}, tn[3] = {128, 256, 256};
+    const double weight[3] = {1.9, 1.45, 1.0};
+    double cost[3] = {0, 0, 0};
+    for (int ci = 0; ci < 3; ++ci) {
         for (uint32_t s = 0; s < count; ++s) {
             if ((uint64_t)rows[s] * cols[s] == 0) continue;
             double n = std::min(rows[s], cols[s]), m = std::max(rows[s], cols[s]);
-            double bn = cand[ci];
-            double n128 = std::ceil(n / 128) * 128, nb = std::ceil(n / bn) * bn;
-            double m128 = std::ceil(m / 128) * 128, mb = std::ceil(m / bn) * bn;
+            auto pad = [](double v, double t) { return std::ceil(v / t) * t; };
             bool tall = rows[s] > cols[s];
-            double out = tall ? m128 * nb : n128 * mb;
-            cost[ci] += n128 * nb * m + n128 * nb * n + out * n;
+            double nn = pad(n, tm[ci]) * pad(n, tn[ci]);
+            double out = tall ? pad(m, tm[ci]) * pad(n, tn[ci]) : pad(n, tm[ci]) * pad(m, tn[ci]);
+            cost[ci] += weight[ci] * (nn * m + nn * n + out * n);
         }
     }
-    // a 128 x 256 tile streams operands ~25% more efficiently than 128 x 128
-    return cost[1] <= cost[0] * 1.25 ? 256 : 128;
+    int best = 0;
+    for (int ci = 1; ci < 3; ++ci)
+        if (cost[ci] < cost[best]) best = ci;
+    bn = tn[best];
+    pair = best == 2;
 }
 
 bool build_layout(const uint32_t *rows, const uint32_t *cols, uint32_t count, const b2_muon_options &o, Layout &L) {
-    L.bn = pick_block_n(rows, cols, count, o);
+    pick_tiles(rows, cols, count, o, L.bn, L.pair);
+    L.tile_m = L.pair ? 256 : 128;
     L.slots.resize(count);
     L.chunk_prefix.assign(count + 1, 0);
     size_t off = 0;
@@ -177,12 +189,13 @@ bool build_layout(const uint32_t *rows, const uint32_t *cols, uint32_t count, co
         sl.len = (uint64_t)rows[s] * cols[s];
         sl.n = std::min(rows[s], cols[s]); sl.m = std::max(rows[s], cols[s]);
         sl.ldg = (uint32_t)align_up(sl.n, 8);
-        sl.tiles_m_nn = (sl.n + kGemmBlockM - 1) / kGemmBlockM;
+        sl.tiles_m_nn = (sl.n + L.tile_m - 1) / L.tile_m;
         sl.tiles_n_nn = (sl.n + L.bn - 1) / L.bn;
+        sl.sub_m_nn = sl.tiles_m_nn * (L.tile_m / kGemmBlockM);  // 128-row sub-tiles (fragment scratch)
         if (sl.len == 0) continue;
         L.tiles_nn += sl.tiles_m_nn * sl.tiles_n_nn;
         uint32_t M = rows[s] > cols[s] ? sl.m : sl.n, N = rows[s] > cols[s] ? sl.n : sl.m;
-        L.tiles_out += ((M + kGemmBlockM - 1) / kGemmBlockM) * ((N + L.bn - 1) / L.bn);
+        L.tiles_out += ((M + L.tile_m - 1) / L.tile_m) * ((N + L.bn - 1) / L.bn);
     }
     L.off_tiles_nn = take((size_t)std::max(L.tiles_nn, 1u) * sizeof(GemmTile));
     L.off_tiles_out = take((size_t)std::max(L.tiles_out, 1u) * sizeof(GemmTile));
@@ -200,7 +213,7 @@ bool build_layout(const uint32_t *rows, const uint32_t *cols, uint32_t count, co
         sl.off_u = take(sl.len * 4);
         sl.off_g16 = take((size_t)sl.n * sl.ldg * 2);
         sl.off_q16 = take((size_t)sl.n * sl.ldg * 2);
-        sl.off_frag = take((size_t)sl.tiles_m_nn * sl.tiles_n_nn * kGemmBlockM * L.bn * 4);
+        sl.off_frag = take((size_t)sl.sub_m_nn * sl.tiles_n_nn * kGemmBlockM * L.bn * 4);
     }
     L.total = off;
     return true;
@@ -291,7 +304,7 @@ int b2_muon_plan_create(b2_muon_plan **out, const uint32_t *rows, const uint32_t
     Layout &L = p->layout;
     if (!build_layout(rows, cols, slot_count, o, L) || L.total > workspace_bytes) { delete p; return B2_ERROR_INVALID_VALUE; }
     p->ws = static_cast<uint8_t *>(d_workspace);
-    e = gemm_configure(L.bn);
+    e = gemm_configure(L.bn, L.pair);
     if (e != cudaSuccess) { delete p; return (int)e; }
 
     p->meta.assign(L.off_meta_end, 0);
@@ -313,10 +326,12 @@ int b2_muon_plan_create(b2_muon_plan **out, const uint32_t *rows, const uint32_t
         up[s] = reinterpret_cast<uint64_t>(p->ws + sl.off_u);
         CUtensorMap *ms = maps + (size_t)s * kMapsPerSlot;
         const uint64_t xp = (uint64_t)sl.cols * 2, gp = (uint64_t)sl.ldg * 2;
-        ok &= make_map(ms + kLX0, p->ws + sl.off_x[0], 2, sl.rows, sl.cols, xp, 64, 64);
-        ok &= make_map(ms + kLX1, p->ws + sl.off_x[1], 2, sl.rows, sl.cols, xp, 64, 64);
-        ok &= make_map(ms + kLG, p->ws + sl.off_g16, 2, sl.n, sl.n, gp, 64, 64);
-        ok &= make_map(ms + kLQ, p->ws + sl.off_q16, 2, sl.n, sl.n, gp, 64, 64);
+        ok &= make_map(ms + kLX0K, p->ws + sl.off_x[0], 2, sl.rows, sl.cols, xp, 64, 128);
+        ok &= make_map(ms + kLX1K, p->ws + sl.off_x[1], 2, sl.rows, sl.cols, xp, 64, 128);
+        ok &= make_map(ms + kLX0M, p->ws + sl.off_x[0], 2, sl.rows, sl.cols, xp, 64, 64);
+        ok &= make_map(ms + kLX1M, p->ws + sl.off_x[1], 2, sl.rows, sl.cols, xp, 64, 64);
+        ok &= make_map(ms + kLG, p->ws + sl.off_g16, 2, sl.n, sl.n, gp, 64, 128);
+        ok &= make_map(ms + kLQ, p->ws + sl.off_q16, 2, sl.n, sl.n, gp, 64, 128);
         ok &= make_map(ms + kSX0, p->ws + sl.off_x[0], 2, sl.rows, sl.cols, xp, 64, 32);
         ok &= make_map(ms + kSX1, p->ws + sl.off_x[1], 2, sl.rows, sl.cols, xp, 64, 32);
         ok &= make_map(ms + kSG, p->ws + sl.off_g16, 2, sl.n, sl.n, gp, 64, 32);
@@ -326,7 +341,7 @@ int b2_muon_plan_create(b2_muon_plan **out, const uint32_t *rows, const uint32_t
         const uint64_t frag = reinterpret_cast<uint64_t>(p->ws + sl.off_frag);
         for (int b = 0; b < 2; ++b) {
             GemmProblem &g = probs[(size_t)(kGram0 + b) * slot_count + s];
-            g.map_a = g.map_b = dmap(s, kLX0 + b);
+            g.map_a = g.map_b = dmap(s, (tall ? kLX0M : kLX0K) + b);
             g.map_out16 = dmap(s, kSG);
             g.frag32 = frag;
             g.M = g.N = sl.n; g.K = sl.m;
@@ -335,11 +350,11 @@ int b2_muon_plan_create(b2_muon_plan **out, const uint32_t *rows, const uint32_t
             for (int last = 0; last < 2; ++last) {
                 GemmProblem &a = probs[(size_t)((last ? kLast0 : kApply0) + b) * slot_count + s];
                 if (tall) {  // Y' = Y Q : A = Y [m][n] K-major, B = Q [n][n] K-major
-                    a.map_a = dmap(s, kLX0 + b); a.map_b = dmap(s, kLQ);
+                    a.map_a = dmap(s, kLX0K + b); a.map_b = dmap(s, kLQ);
                     a.a_mn_major = 0; a.b_mn_major = 0;
                     a.M = sl.m; a.N = sl.n;
                 } else {     // X' = Q X : A = Q K-major, B = X [n][m] read as MN-major
-                    a.map_a = dmap(s, kLQ); a.map_b = dmap(s, kLX0 + b);
+                    a.map_a = dmap(s, kLQ); a.map_b = dmap(s, kLX0M + b);
                     a.a_mn_major = 0; a.b_mn_major = 1;
                     a.M = sl.n; a.N = sl.m;
                 }
@@ -379,7 +394,7 @@ int b2_muon_plan_create(b2_muon_plan **out, const uint32_t *rows, const uint32_t
         const SlotLayout &sl = L.slots[s];
         const bool tall = sl.rows > sl.cols;
         uint32_t M = tall ? sl.m : sl.n, N = tall ? sl.n : sl.m;
-        uint32_t tm = (M + kGemmBlockM - 1) / kGemmBlockM, tn = (N + L.bn - 1) / L.bn;
+        uint32_t tm = (M + L.tile_m - 1) / L.tile_m, tn = (N + L.bn - 1) / L.bn;
         for (uint32_t i = 0; i < tm; ++i)
             for (uint32_t j = 0; j < tn; ++j) tout[iout++] = GemmTile{(uint16_t)s, (uint16_t)i, (uint16_t)j, 0};
     }
@@ -439,14 +454,19 @@ int b2_muon_polar(b2_muon_plan *plan, const b2_muon_step_args *a, void *stream) 
         }
         const uint32_t b = it & 1u;
         const bool last = it + 1 == a->iterations;
-        e = launch_ns_gemm(L.bn, probs + (size_t)(kGram0 + b) * count, tnn, L.tiles_nn, kEpiGram, f16, ca, cb, cc,
-                           status, grid, s);
-        if (e == cudaSuccess)
-            e = launch_ns_gemm(L.bn, probs + (size_t)kPoly * count, tnn, L.tiles_nn, kEpiPoly, f16, ca, cb, cc, status,
-                               grid, s);
-        if (e == cudaSuccess)
-            e = launch_ns_gemm(L.bn, probs + (size_t)((last ? kLast0 : kApply0) + b) * count, tout, L.tiles_out,
-                               last ? kEpiApplyLast : kEpiApply, f16, ca, cb, cc, status, grid, s);
+        // reserved[1]: measurement-only phase mask (1 Gram, 2 Poly, 4 Apply; 0 = all);
+        // reserved[2]: measurement-only kernel flags
+        const uint32_t mask = plan->options.reserved[1] ? plan->options.reserved[1] : 7u;
+        const uint32_t dbg = plan->options.reserved[2];
+        if (mask & 1u)
+            e = launch_ns_gemm(L.bn, L.pair, probs + (size_t)(kGram0 + b) * count, tnn, L.tiles_nn, kEpiGram, f16, ca, cb, cc,
+                               status, dbg, grid, s);
+        if (e == cudaSuccess && (mask & 2u))
+            e = launch_ns_gemm(L.bn, L.pair, probs + (size_t)kPoly * count, tnn, L.tiles_nn, kEpiPoly, f16, ca, cb, cc, status,
+                               dbg, grid, s);
+        if (e == cudaSuccess && (mask & 4u))
+            e = launch_ns_gemm(L.bn, L.pair, probs + (size_t)((last ? kLast0 : kApply0) + b) * count, tout, L.tiles_out,
+                               last ? kEpiApplyLast : kEpiApply, f16, ca, cb, cc, status, dbg, grid, s);
     }
     return (int)e;
 }

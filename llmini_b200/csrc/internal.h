@@ -60,7 +60,8 @@ enum GemmEpilogue : uint32_t {
 // One GEMM of one slot: D[M][N] = A * B^T with A, B described by TMA maps.  Lives in device
 // memory; built once per plan.
 struct alignas(16) GemmProblem {
-    uint64_t map_a;      // device address of the CUtensorMap of operand A (box 64x64, 16-bit)
+    uint64_t map_a;      // device address of the CUtensorMap of operand A (16-bit; box 64 x 128
+                         // rows when K-major, 64 x 64 when MN-major)
     uint64_t map_b;
     uint64_t map_out16;  // store map, box 64 x 32 (16-bit) — unused for kEpiApplyLast
     uint64_t map_out32;  // store map, box 32 x 32 (f32) — kEpiApplyLast only
@@ -68,7 +69,7 @@ struct alignas(16) GemmProblem {
     uint32_t M, N, K;
     uint32_t a_mn_major;  // 0: A is [M][K] K-contiguous; 1: A is [K][M] M-contiguous
     uint32_t b_mn_major;  // 0: B is [N][K]; 1: B is [K][N]
-    uint32_t tiles_n;     // number of tile columns (for frag32 addressing)
+    uint32_t tiles_n;     // number of BN-wide tile columns (for frag32 addressing)
     uint32_t pad[2];
 };
 struct GemmTile {
@@ -81,10 +82,9 @@ struct GemmTile {
 constexpr int kGemmBlockM = 128;
 constexpr int kGemmBlockK = 64;
 
-size_t gemm_smem_bytes(int block_n);
-cudaError_t gemm_configure(int block_n);
-cudaError_t launch_ns_gemm(int block_n, const GemmProblem *problems, const GemmTile *tiles,
+cudaError_t gemm_configure(int block_n, int pair);
+cudaError_t launch_ns_gemm(int block_n, int pair, const GemmProblem *problems, const GemmTile *tiles,
                            uint32_t tile_count, uint32_t epilogue, int f16, float ca, float cb,
-                           float cc, uint32_t *status, int grid, cudaStream_t s);
+                           float cc, uint32_t *status, uint32_t debug_flags, int grid, cudaStream_t s);
 
 }  // namespace b2

@@ -15,6 +15,13 @@
 // tile that the polynomial epilogue needs is kept in a private fragment-ordered scratch so
 // both sides access it fully coalesced.
 //
+// Two tile configurations:
+//   PAIR  : a cluster of two CTAs computes a 256 x 256 tile with cta_group::2 MMAs.  Each
+//           CTA stages its own 128 rows of A and half (128 rows) of B, so a k-block costs
+//           32 KB of loads per SM instead of 48 KB: the kernel is bound by the L2-to-SM
+//           path, and this raises FLOPs per loaded byte by 1.5x.  No multicast load is used.
+//   single: one CTA computes 128 x BN (BN = 128 or 256).
+//
 // Every mbarrier wait is bounded: on expiry the CTA raises a status word, drains and frees
 // its TMEM before returning.
 #include <cuda.h>
@@ -26,26 +33,43 @@ namespace b2 {
 
 namespace {
 
-constexpr int kGemmThreads = 192;  // warp 0: TMA producer, warp 1: MMA issuer, warps 2-5: epilogue
-constexpr int kBoxBytes = 64 * 128;          // one TMA box: 64 rows x 128 bytes
+constexpr int kEpiWarps = 8;
+constexpr int kGemmThreads = 32 * (2 + kEpiWarps);  // warp 0: TMA producer, warp 1: MMA issuer, rest: epilogue
+constexpr int kBoxBytes = 64 * 128;          // 64 rows x 128 bytes
 constexpr int kABytes = 2 * kBoxBytes;       // 128 x 64 16-bit operand tile
 constexpr int kSlabBytes = 32 * 128;         // per-warp store staging: 32 rows x 128 bytes
-constexpr int kStagingBytes = 4 * 2 * kSlabBytes;
+constexpr int kStagingBytes = kEpiWarps * kSlabBytes;
 constexpr uint32_t kSpinLimit = 1u << 24;    // hard cap on polls, whatever the timer says
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
-template <int BN>
+template <int BN, bool PAIR>
 struct Cfg {
-    static constexpr int kBBytes = (BN / 64) * kBoxBytes;
+    static constexpr int kBRows = PAIR ? 128 : BN;   // rows of B this CTA stages per k-block
+    static constexpr int kBBytes = (kBRows / 64) * kBoxBytes;
     static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kStages = (BN == 256) ? 4 : 6;
+    static constexpr int kStages = (kStageBytes == 32768) ? 6 : 4;
     static constexpr int kTmemCols = 2 * BN;
     static constexpr int kBarrierBytes = 256;
     static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + kBarrierBytes + 1024;
+    static constexpr int kTileM = PAIR ? 256 : 128;  // rows of the (cluster) tile
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return (uint32_t)__cvta_generic_to_shared(p);
+}
+// shared::cluster address of the same offset in CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
@@ -54,8 +78,9 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                  : "memory");
 }
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+// arrive on a barrier given by its shared::cluster address (own or peer CTA)
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
@@ -66,13 +91,13 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
         : "memory");
     return ok;
 }
-// Bounded wait (about two seconds of wall clock).  Returns false when the limit ran out or
-// another role of this CTA already gave up.
 __device__ __forceinline__ uint64_t global_timer_ns() {
     uint64_t t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
+// Bounded wait (about two seconds of wall clock).  Returns false when the limit ran out or
+// another role of this CTA already gave up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag) {
 #pragma unroll 1
     for (int it = 0; it < 128; ++it)
@@ -89,11 +114,18 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     return false;
 }
 
+template <bool PAIR>
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, uint64_t map, uint32_t bar, int x, int y) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
-        : "memory");
+    if (PAIR)
+        asm volatile(
+            "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+            ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+            : "memory");
+    else
+        asm volatile(
+            "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+            ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+            : "memory");
 }
 __device__ __forceinline__ void tma_store_2d(uint64_t map, uint32_t src, int x, int y) {
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
@@ -101,27 +133,37 @@ __device__ __forceinline__ void tma_store_2d(uint64_t map, uint32_t src, int x, 
                  : "memory");
 }
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void tma_store_wait_read() {
-    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
-}
+__device__ __forceinline__ void tma_store_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void tensormap_acquire(uint64_t map) {
-    asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(map) : "memory");
-}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// Arrive on `bar` once every MMA issued so far has retired.  PAIR: the arrival is delivered
+// to the barrier at this offset in both CTAs of the pair.
+template <bool PAIR>
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
-                 : "memory");
+    if (PAIR)
+        asm volatile(
+            "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+            ::"r"(bar), "h"((uint16_t)3)
+            : "memory");
+    else
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+                     : "memory");
 }
+template <bool PAIR>
 __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                        uint32_t accumulate) {
-    asm volatile(
-        "{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p; }"
-        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
+    if (PAIR)
+        asm volatile(
+            "{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p; }"
+            ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    else
+        asm volatile(
+            "{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p; }"
+            ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            : "memory");
 }
 // 32 lanes x 32 consecutive 32-bit columns: thread i of the warp receives row (lane base + i).
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t *r) {
@@ -142,8 +184,8 @@ __device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sy
 //   K-major operand  (rows = M/N index, 128 bytes of K per row): 8-row groups are 1024 bytes
 //   apart (stride byte offset); the leading byte offset is unused.
 //   MN-major operand (rows = K index, 128 bytes = 64 M/N elements per row): 8-row groups of K
-//   are 1024 bytes apart (stride), 64-element groups of M/N are one TMA box (8192 bytes) apart
-//   (leading).
+//   are 1024 bytes apart (stride), 64-element groups of M/N are one 64 x 64 box (8192 bytes)
+//   apart (leading).
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
     uint64_t d = 0;
     d |= (uint64_t)((addr & 0x3ffffu) >> 4);
@@ -155,18 +197,19 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes,
 }
 // Instruction descriptor for kind::f16: FP32 accumulate, A/B format F16 (0) or BF16 (1),
 // per-operand major bit, N >> 3 at bit 17, M >> 4 at bit 24.
-__device__ __forceinline__ uint32_t instr_desc(int bn, int f16, uint32_t a_mn, uint32_t b_mn) {
+__device__ __forceinline__ uint32_t instr_desc(int m, int n, int f16, uint32_t a_mn, uint32_t b_mn) {
     uint32_t fmt = f16 ? 0u : 1u;
     return (1u << 4) | (fmt << 7) | (fmt << 10) | (a_mn << 15) | (b_mn << 16) |
-           ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(kGemmBlockM >> 4) << 24);
+           ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
-template <int BN>
+template <int BN, bool PAIR>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__ tiles,
           uint32_t tile_count, uint32_t epilogue, int f16, float ca, float cb, float cc,
-          uint32_t *status) {
-    using C = Cfg<BN>;
+          uint32_t *status, uint32_t debug_flags) {
+    using C = Cfg<BN, PAIR>;
+    const bool dbg_no_store = debug_flags & 1u;   // measurement only: drop every epilogue store
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *stage_base = smem;
@@ -178,6 +221,9 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    const uint32_t rank = PAIR ? cluster_cta_rank() : 0u;       // 0 = leader of the pair
+    const uint32_t first_tile = PAIR ? blockIdx.x / 2 : blockIdx.x;
+    const uint32_t tile_stride = PAIR ? gridDim.x / 2 : gridDim.x;
     const uint32_t bar0 = smem_u32(bars);
     auto full_bar = [&](int s) { return bar0 + 8u * s; };
     auto empty_bar = [&](int s) { return bar0 + 8u * (C::kStages + s); };
@@ -191,20 +237,26 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(tfull_bar(a), 1);
-            mbar_init(tempty_bar(a), 4);
+            mbar_init(tempty_bar(a), PAIR ? 2 * kEpiWarps : kEpiWarps);
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_async_smem();
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                     "r"((uint32_t)C::kTmemCols)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if (PAIR) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                         "r"((uint32_t)C::kTmemCols) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                         "r"((uint32_t)C::kTmemCols) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all();  // the peer's barriers are initialised before anything signals them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
@@ -213,31 +265,37 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            for (uint32_t t = blockIdx.x; ok && t < tile_count; t += gridDim.x) {
+            for (uint32_t t = first_tile; ok && t < tile_count; t += tile_stride) {
                 const GemmTile tl = tiles[t];
                 const GemmProblem *p = problems + tl.problem;
                 const uint64_t map_a = p->map_a, map_b = p->map_b;
                 const uint32_t a_mn = p->a_mn_major, b_mn = p->b_mn_major, K = p->K;
-                tensormap_acquire(map_a);
-                tensormap_acquire(map_b);
-                const int m0 = tl.tile_m * kGemmBlockM, n0 = tl.tile_n * BN;
+                const int m0 = tl.tile_m * C::kTileM + (int)rank * 128;
+                const int n0 = tl.tile_n * BN + (PAIR ? (int)rank * 128 : 0);
                 const int num_kb = (int)((K + kGemmBlockK - 1) / kGemmBlockK);
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
-                    const uint32_t fb = full_bar(stage);
-                    mbar_expect_tx(fb, (uint32_t)C::kStageBytes);
+                    // PAIR: both CTAs' copies complete on the leader's barrier, which expects
+                    // the bytes of both
+                    const uint32_t fb = PAIR ? map_to_cta(full_bar(stage), 0) : full_bar(stage);
+                    if (!PAIR || rank == 0) mbar_expect_tx(full_bar(stage), (uint32_t)C::kStageBytes * (PAIR ? 2u : 1u));
                     const uint32_t sa = smem_u32(stage_base + stage * C::kStageBytes);
                     const uint32_t sb = sa + kABytes;
                     const int k0 = kb * kGemmBlockK;
-#pragma unroll
-                    for (int j = 0; j < 2; ++j) {
-                        if (a_mn) tma_load_2d(sa + j * kBoxBytes, map_a, fb, m0 + 64 * j, k0);
-                        else tma_load_2d(sa + j * kBoxBytes, map_a, fb, k0, m0 + 64 * j);
+                    if (a_mn) {  // 64 x 64 boxes: x = M index, y = K index
+                        tma_load_2d<PAIR>(sa, map_a, fb, m0, k0);
+                        tma_load_2d<PAIR>(sa + kBoxBytes, map_a, fb, m0 + 64, k0);
+                    } else {     // one 64 (K) x 128 (rows) box
+                        tma_load_2d<PAIR>(sa, map_a, fb, k0, m0);
                     }
 #pragma unroll
-                    for (int j = 0; j < BN / 64; ++j) {
-                        if (b_mn) tma_load_2d(sb + j * kBoxBytes, map_b, fb, n0 + 64 * j, k0);
-                        else tma_load_2d(sb + j * kBoxBytes, map_b, fb, k0, n0 + 64 * j);
+                    for (int j = 0; j < C::kBRows / 128; ++j) {
+                        if (b_mn) {
+                            tma_load_2d<PAIR>(sb + (2 * j) * kBoxBytes, map_b, fb, n0 + 128 * j, k0);
+                            tma_load_2d<PAIR>(sb + (2 * j + 1) * kBoxBytes, map_b, fb, n0 + 128 * j + 64, k0);
+                        } else {
+                            tma_load_2d<PAIR>(sb + (2 * j) * kBoxBytes, map_b, fb, k0, n0 + 128 * j);
+                        }
                     }
                     if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
                 }
@@ -245,15 +303,15 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
+        if (lane == 0 && rank == 0) {
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
-            for (uint32_t t = blockIdx.x; ok && t < tile_count; t += gridDim.x) {
+            for (uint32_t t = first_tile; ok && t < tile_count; t += tile_stride) {
                 const GemmTile tl = tiles[t];
                 const GemmProblem *p = problems + tl.problem;
                 const uint32_t a_mn = p->a_mn_major, b_mn = p->b_mn_major, K = p->K;
                 const int num_kb = (int)((K + kGemmBlockK - 1) / kGemmBlockK);
-                const uint32_t idesc = instr_desc(BN, f16, a_mn, b_mn);
+                const uint32_t idesc = instr_desc(C::kTileM, BN, f16, a_mn, b_mn);
                 if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
@@ -268,55 +326,72 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
                                                  : smem_desc(sa + k * 32, 16, 1024);
                         const uint64_t bd = b_mn ? smem_desc(sb + k * 2048, kBoxBytes, 1024)
                                                  : smem_desc(sb + k * 32, 16, 1024);
-                        tc_mma(d_tmem, ad, bd, idesc, (uint32_t)((kb | k) != 0));
+                        tc_mma<PAIR>(d_tmem, ad, bd, idesc, (uint32_t)((kb | k) != 0));
                     }
-                    tc_commit(empty_bar(stage));
+                    tc_commit<PAIR>(empty_bar(stage));
                     if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
                 }
                 if (!ok) break;
-                tc_commit(tfull_bar(acc));
+                tc_commit<PAIR>(tfull_bar(acc));
                 acc ^= 1u;
                 if (acc == 0) acc_phase ^= 1u;
             }
         }
     } else {
         // ------------------------------------------------------------------ epilogue warps
-        const int q = warp & 3;  // TMEM lane quarter this warp may read
-        uint8_t *slab0 = staging + (size_t)(warp - 2) * 2 * kSlabBytes;
-        uint32_t acc = 0, acc_phase = 0, buf = 0;
-        for (uint32_t t = blockIdx.x; t < tile_count; t += gridDim.x) {
+        // Warp w may read TMEM lanes 32 (w % 4) .. +31; two warps share a lane quarter and
+        // split the columns of the tile between them.
+        const int q = warp & 3;
+        const int half = (warp - 2) >> 2;
+        uint8_t *slab = staging + (size_t)(warp - 2) * kSlabBytes;
+        const uint32_t slab_u32 = smem_u32(slab);
+        const uint32_t tempty_leader0 = PAIR ? map_to_cta(tempty_bar(0), 0) : tempty_bar(0);
+        uint32_t acc = 0, acc_phase = 0;
+        constexpr int kHalfCols = BN / 2;
+        for (uint32_t t = first_tile; t < tile_count; t += tile_stride) {
             const GemmTile tl = tiles[t];
             const GemmProblem *p = problems + tl.problem;
             const uint32_t M = p->M, N = p->N;
             const uint64_t map16 = p->map_out16, map32 = p->map_out32;
-            float *frag = reinterpret_cast<float *>(p->frag32);
-            const uint32_t tile_lin = (uint32_t)tl.tile_m * p->tiles_n + tl.tile_n;
-            const int m0 = tl.tile_m * kGemmBlockM, n0 = tl.tile_n * BN;
+            const float4 *frag = reinterpret_cast<const float4 *>(p->frag32);
+            // fragment scratch is indexed by 128-row sub-tiles
+            const uint32_t sub_m = PAIR ? (uint32_t)tl.tile_m * 2 + rank : tl.tile_m;
+            const uint32_t tile_lin = sub_m * p->tiles_n + tl.tile_n;
+            const int m0 = tl.tile_m * C::kTileM + (int)rank * 128, n0 = tl.tile_n * BN;
             const int row_in_tile = 32 * q + lane;
             const int grow = m0 + row_in_tile;
             const int slab_row0 = m0 + 32 * q;
+            const int col_begin = half * kHalfCols;
+
+            // The polynomial epilogue needs the FP32 Gram tile: fetch the first 64 columns
+            // before the accumulator is ready so the latency hides behind the MMAs.
+            float4 g[16];
+            if (epilogue == kEpiPoly && !dbg_no_store) {
+                const size_t unit0 = ((size_t)tile_lin * (BN / 32) + (size_t)(col_begin / 32)) * 8;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) g[j] = __ldcg(frag + (unit0 + j) * kGemmBlockM + row_in_tile);
+            }
 
             bool ready = mbar_wait(tfull_bar(acc), acc_phase, abort_flag);
             ready = __all_sync(0xffffffffu, ready);
             if (!ready) break;
             tc_fence_after();
-            if (lane == 0) tensormap_acquire(epilogue == kEpiApplyLast ? map32 : map16);
             const uint32_t taddr = tmem_base + ((uint32_t)(32 * q) << 16) + acc * BN;
+            const uint32_t tempty = tempty_leader0 + 8u * acc;
 
             if (epilogue == kEpiApplyLast) {
                 // FP32 result in the storage layout: 32 columns (128 bytes) per staged slab
-                for (int c0 = 0; c0 < BN; c0 += 32) {
+                for (int c0 = col_begin; c0 < col_begin + kHalfCols; c0 += 32) {
                     uint32_t v[32];
                     tc_ld32(taddr + c0, v);
                     tc_ld_wait();
-                    if (c0 + 32 >= BN) {
+                    if (c0 + 32 >= col_begin + kHalfCols) {
                         tc_fence_before();
                         __syncwarp();
-                        if (lane == 0) mbar_arrive(tempty_bar(acc));
+                        if (lane == 0) mbar_arrive_cluster(tempty);
                     }
-                    if (n0 + c0 >= (int)N || slab_row0 >= (int)M) continue;  // warp-uniform
-                    uint8_t *slab = slab0 + buf * kSlabBytes;
-                    if (lane == 0) tma_store_wait_read<1>();
+                    if (n0 + c0 >= (int)N || slab_row0 >= (int)M || dbg_no_store) continue;  // warp-uniform
+                    if (lane == 0) tma_store_wait_read_all();
                     __syncwarp();
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
@@ -326,35 +401,37 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
                     fence_async_smem();
                     __syncwarp();
                     if (lane == 0) {
-                        tma_store_2d(map32, smem_u32(slab), n0 + c0, slab_row0);
+                        tma_store_2d(map32, slab_u32, n0 + c0, slab_row0);
                         tma_store_commit();
                     }
-                    buf ^= 1u;
                 }
             } else {
                 // 16-bit result: 64 columns (128 bytes) per staged slab
-                for (int c0 = 0; c0 < BN; c0 += 64) {
+                for (int c0 = col_begin; c0 < col_begin + kHalfCols; c0 += 64) {
                     uint32_t v[64];
                     tc_ld32(taddr + c0, v);
                     tc_ld32(taddr + c0 + 32, v + 32);
                     tc_ld_wait();
-                    if (c0 + 64 >= BN) {
+                    const bool last_chunk = c0 + 64 >= col_begin + kHalfCols;
+                    if (last_chunk) {
                         tc_fence_before();
                         __syncwarp();
-                        if (lane == 0) mbar_arrive(tempty_bar(acc));
+                        if (lane == 0) mbar_arrive_cluster(tempty);
                     }
-                    if (epilogue == kEpiGram || epilogue == kEpiPoly) {
-                        // fragment order: [tile][32-column unit][float4 index][row in tile]
+                    if ((epilogue == kEpiGram || epilogue == kEpiPoly) && !dbg_no_store) {
+                        // fragment order: [128-row sub-tile][32-column unit][float4 index][row]
                         const size_t unit0 = ((size_t)tile_lin * (BN / 32) + (size_t)(c0 / 32)) * 8;
+                        if (epilogue == kEpiGram) {
+                            float4 *fw = const_cast<float4 *>(frag);
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            float4 *fp = reinterpret_cast<float4 *>(frag) + (unit0 + j) * kGemmBlockM + row_in_tile;
-                            if (epilogue == kEpiGram) {
-                                *fp = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
-                                                  __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
-                            } else {
-                                const float4 g = *fp;
-                                const float gv[4] = {g.x, g.y, g.z, g.w};
+                            for (int j = 0; j < 16; ++j)
+                                __stcg(fw + (unit0 + j) * kGemmBlockM + row_in_tile,
+                                       make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                                   __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3])));
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) {
+                                const float gv[4] = {g[j].x, g[j].y, g[j].z, g[j].w};
 #pragma unroll
                                 for (int e = 0; e < 4; ++e) {
                                     const int gcol = n0 + c0 + 4 * j + e;
@@ -364,11 +441,15 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
                                         fmaf(cc, __uint_as_float(v[4 * j + e]), fmaf(cb, gv[e], ident)));
                                 }
                             }
+                            if (!last_chunk) {  // fetch the next 64 columns while this chunk is packed and stored
+                                const size_t unit1 = unit0 + 16;
+#pragma unroll
+                                for (int j = 0; j < 16; ++j) g[j] = __ldcg(frag + (unit1 + j) * kGemmBlockM + row_in_tile);
+                            }
                         }
                     }
-                    if (n0 + c0 >= (int)N || slab_row0 >= (int)M) continue;  // warp-uniform
-                    uint8_t *slab = slab0 + buf * kSlabBytes;
-                    if (lane == 0) tma_store_wait_read<1>();
+                    if (n0 + c0 >= (int)N || slab_row0 >= (int)M || dbg_no_store) continue;  // warp-uniform
+                    if (lane == 0) tma_store_wait_read_all();
                     __syncwarp();
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
@@ -382,10 +463,9 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
                     fence_async_smem();
                     __syncwarp();
                     if (lane == 0) {
-                        tma_store_2d(map16, smem_u32(slab), n0 + c0, slab_row0);
+                        tma_store_2d(map16, slab_u32, n0 + c0, slab_row0);
                         tma_store_commit();
                     }
-                    buf ^= 1u;
                 }
             }
             acc ^= 1u;
@@ -403,37 +483,67 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
         if (threadIdx.x == 0) atomicExch(status, 1u);
         __syncthreads();
     }
+    if (PAIR) cluster_sync_all();  // neither CTA leaves while its peer may still touch it
     if (warp == 1) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
-                     "r"((uint32_t)C::kTmemCols)
-                     : "memory");
+        if (PAIR)
+            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                         "r"((uint32_t)C::kTmemCols) : "memory");
+        else
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                         "r"((uint32_t)C::kTmemCols) : "memory");
     }
+}
+
+template <int BN, bool PAIR>
+cudaError_t launch_impl(const GemmProblem *problems, const GemmTile *tiles, uint32_t tile_count, uint32_t epilogue,
+                        int f16, float ca, float cb, float cc, uint32_t *status, uint32_t debug_flags, int grid,
+                        cudaStream_t s) {
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    if (PAIR) {
+        int clusters = grid / 2;
+        if ((uint32_t)clusters > tile_count) clusters = (int)tile_count;
+        if (clusters < 1) clusters = 1;
+        grid = 2 * clusters;
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    } else if ((uint32_t)grid > tile_count) {
+        grid = (int)tile_count;
+    }
+    cfg.gridDim = dim3((unsigned)grid, 1, 1);
+    cfg.blockDim = dim3(kGemmThreads, 1, 1);
+    cfg.dynamicSmemBytes = Cfg<BN, PAIR>::kSmemBytes;
+    cfg.stream = s;
+    return cudaLaunchKernelEx(&cfg, k_ns_gemm<BN, PAIR>, problems, tiles, tile_count, epilogue, f16, ca, cb, cc, status,
+                              debug_flags);
 }
 
 }  // namespace
 
-size_t gemm_smem_bytes(int block_n) {
-    return block_n == 256 ? (size_t)Cfg<256>::kSmemBytes : (size_t)Cfg<128>::kSmemBytes;
-}
-cudaError_t gemm_configure(int block_n) {
-    if (block_n == 256)
-        return cudaFuncSetAttribute(k_ns_gemm<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<256>::kSmemBytes);
-    if (block_n == 128)
-        return cudaFuncSetAttribute(k_ns_gemm<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<128>::kSmemBytes);
+cudaError_t gemm_configure(int block_n, int pair) {
+    if (pair && block_n == 256)
+        return cudaFuncSetAttribute(k_ns_gemm<256, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<256, true>::kSmemBytes);
+    if (!pair && block_n == 256)
+        return cudaFuncSetAttribute(k_ns_gemm<256, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<256, false>::kSmemBytes);
+    if (!pair && block_n == 128)
+        return cudaFuncSetAttribute(k_ns_gemm<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<128, false>::kSmemBytes);
     return cudaErrorInvalidValue;
 }
-cudaError_t launch_ns_gemm(int block_n, const GemmProblem *problems, const GemmTile *tiles,
+cudaError_t launch_ns_gemm(int block_n, int pair, const GemmProblem *problems, const GemmTile *tiles,
                            uint32_t tile_count, uint32_t epilogue, int f16, float ca, float cb,
-                           float cc, uint32_t *status, int grid, cudaStream_t s) {
+                           float cc, uint32_t *status, uint32_t debug_flags, int grid, cudaStream_t s) {
     if (tile_count == 0) return cudaSuccess;
-    if ((uint32_t)grid > tile_count) grid = (int)tile_count;
-    if (block_n == 256)
-        k_ns_gemm<256><<<grid, kGemmThreads, Cfg<256>::kSmemBytes, s>>>(problems, tiles, tile_count, epilogue, f16, ca, cb, cc, status);
-    else if (block_n == 128)
-        k_ns_gemm<128><<<grid, kGemmThreads, Cfg<128>::kSmemBytes, s>>>(problems, tiles, tile_count, epilogue, f16, ca, cb, cc, status);
-    else
-        return cudaErrorInvalidValue;
-    return cudaGetLastError();
+    if (pair && block_n == 256)
+        return launch_impl<256, true>(problems, tiles, tile_count, epilogue, f16, ca, cb, cc, status, debug_flags, grid, s);
+    if (!pair && block_n == 256)
+        return launch_impl<256, false>(problems, tiles, tile_count, epilogue, f16, ca, cb, cc, status, debug_flags, grid, s);
+    if (!pair && block_n == 128)
+        return launch_impl<128, false>(problems, tiles, tile_count, epilogue, f16, ca, cb, cc, status, debug_flags, grid, s);
+    return cudaErrorInvalidValue;
 }
 
 }  // namespace b2

@@ -52,8 +52,14 @@ class MuonSlot:
     @staticmethod
     def allocate(rows: int, cols: int, scale_layout: int = SCALES_CSF, device="cuda") -> "MuonSlot":
         n = rows * cols
-        scales = zero_scales(rows, cols, device) if scale_layout == SCALES_CSF else \
-            torch.zeros(max(n // 16, 1), dtype=torch.uint8, device=device)
+        if n == 0:  # padding slot: skipped by every kernel
+            scales = torch.zeros(1, dtype=torch.uint8, device=device)
+        elif scale_layout == SCALES_CSF:
+            if cols % 128 != 0:
+                raise ValueError("CSF block-scale storage needs cols % 128 == 0; use SCALES_RAW")
+            scales = zero_scales(rows, cols, device)
+        else:
+            scales = torch.zeros(max(n // 16, 1), dtype=torch.uint8, device=device)
         z = lambda *s, dt=torch.float32: torch.zeros(*s, dtype=dt, device=device)
         return MuonSlot(z(rows, cols), z(rows, cols, dt=torch.bfloat16), z(rows, cols), z(rows, cols), z(1),
                         torch.zeros(max(n // 2, 1), dtype=torch.uint8, device=device), scales, z(1), rows, cols)
@@ -101,13 +107,13 @@ class MuonPlan:
 
     def __init__(self, shapes: Sequence[tuple[int, int]], operand_format: int = OPERAND_BF16,
                  scale_layout: int = SCALES_CSF, quantize_target: int = QUANTIZE_X, max_iterations: int = 5,
-                 tile_n: int = 0, device="cuda"):
+                 tile_n: int = 0, device="cuda", debug_phase_mask: int = 0, debug_flags: int = 0):
         self._lib = _ffi.lib()
         self.shapes = [(int(r), int(c)) for r, c in shapes]
         n = len(self.shapes)
         self._rows = (C.c_uint32 * n)(*[r for r, _ in self.shapes])
         self._cols = (C.c_uint32 * n)(*[c for _, c in self.shapes])
-        self.options = MuonOptions(operand_format, scale_layout, quantize_target, max_iterations, (C.c_uint32 * 4)(tile_n, 0, 0, 0))
+        self.options = MuonOptions(operand_format, scale_layout, quantize_target, max_iterations, (C.c_uint32 * 4)(tile_n, debug_phase_mask, debug_flags, 0))
         nbytes = self._lib.b2_muon_workspace_bytes(self._rows, self._cols, n, C.byref(self.options))
         if nbytes == 0:
             raise _ffi.B2Error(_ffi.ERROR_INVALID_VALUE, "muon_workspace_bytes")

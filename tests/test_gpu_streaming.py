@@ -21,7 +21,7 @@ def _fill_slot(slot, grad, mom_bits, z, x):
 
 
 @pytest.mark.parametrize("shapes,layout", [
-    ([(64, 128), (128, 64)], b2.SCALES_CSF),
+    ([(64, 128), (128, 256)], b2.SCALES_CSF),
     ([(32, 64), (96, 48), (0, 0), (7, 16), (300, 1040)], b2.SCALES_RAW),
 ])
 def test_prepare_matches_oracle(shapes, layout):
@@ -64,9 +64,9 @@ def test_momentum_chain_reference_case():
         i = np.arange(n)
         grad = ((i * 73 % 257).astype(F) - F(128.0)) / F(211.0)
         mom = o.round_bf16(((i * 29 % 131).astype(F) - F(65.0)) / F(173.0))
-        slot = b2.MuonSlot.allocate(rows, cols)
+        slot = b2.MuonSlot.allocate(rows, cols, b2.SCALES_RAW)
         _fill_slot(slot, grad, o.bf16_bits(mom), np.zeros(n, F), np.zeros(n, F))
-        plan = b2.MuonPlan([(rows, cols)])
+        plan = b2.MuonPlan([(rows, cols)], scale_layout=b2.SCALES_RAW)
         table = b2.slot_table([slot])
         expected_m = mom.copy()
         for _ in range(6):
