@@ -170,6 +170,22 @@ int b2_materialize_master(uint8_t *d_bytes, uint8_t *d_scales, float *d_global_s
                           const float *d_master, float *d_amax, float *d_chunk_amax, uint32_t len,
                           uint32_t scale_layout, void *stream);
 
+/* No counterpart in the reference.  Same result as b2_materialize_master, for callers that
+ * cannot supply the two scratch buffers and cannot allocate them either: code that receives only
+ * the master tensor and the NVFP4 destination (an export or evaluation hook beside the trainer,
+ * an embedder whose device memory is fully reserved before the first step), where cudaMalloc
+ * would fail or would stall the training stream by synchronising the device.  The scratch is an
+ * array built into the library (about 128 KiB held on every GPU that loads it, until exit), which
+ * limits one call to B2_STATIC_MAX_ELEMENTS values; longer tensors are refused with
+ * B2_ERROR_INVALID_VALUE.  The call allocates nothing.  The first call on each device looks up the
+ * array's device address and should therefore be made outside any stream capture.  All calls on a
+ * device share the one array: it needs no clearing between calls, but two calls whose kernels can
+ * overlap on the GPU (different streams) race on it — serialise them. */
+#define B2_STATIC_MAX_ELEMENTS (1u << 26)
+int b2_materialize_master_static(uint8_t *d_bytes, uint8_t *d_scales, float *d_global_scale,
+                                 const float *d_master, uint32_t len, uint32_t scale_layout,
+                                 void *stream);
+
 /* `ScheduleFreeMaterializeArgs` / `...PrecomputedArgs`
  * (.../optimizer/args/schedule_free.rs:13-45).  symexp_lin_beta must be 0 (identity). */
 typedef struct b2_schedule_free_materialize_args {

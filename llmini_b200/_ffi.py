@@ -89,6 +89,7 @@ def _declare(L: C.CDLL) -> None:
         "b2_tensor_amax_from_chunks_f32": (i, [vp, vp, u32, vp]),
         "b2_fp32_to_nvfp4_four_six": (i, [vp, vp, vp, vp, vp, u32, u32, vp]),
         "b2_materialize_master": (i, [vp, vp, vp, vp, vp, vp, u32, u32, vp]),
+        "b2_materialize_master_static": (i, [vp, vp, vp, vp, u32, u32, vp]),
         "b2_materialize_schedule_free": (i, [C.POINTER(ScheduleFreeMaterializeArgs), vp]),
         "b2_materialize_schedule_free_precomputed": (i, [C.POINTER(ScheduleFreeMaterializeArgs), vp]),
         "b2_apply_adamw_update": (i, [C.POINTER(AdamWUpdateArgs), vp]),

@@ -217,6 +217,17 @@ class OptimizerModule:
         check(self._lib.b2_materialize_master(_ptr(bytes_), _ptr(scales), _ptr(global_scale), _ptr(master), _ptr(amax),
                                               _ptr(chunk_amax), len_, scale_layout, _stream()), "materialize_master")
 
+    STATIC_MAX_ELEMENTS = 1 << 26
+
+    def materialize_master_static(self, bytes_: torch.Tensor, scales: torch.Tensor, global_scale: torch.Tensor,
+                                  master: torch.Tensor, len_: int, scale_layout: int = SCALES_CSF) -> None:
+        """`materialize_master` for callers with no scratch to give and no way to allocate it (an
+        export or evaluation hook that only holds the weight buffers): the chunk maxima and the
+        tensor maximum live in an array inside the library, so `len_` is limited to
+        STATIC_MAX_ELEMENTS and calls that may overlap on the GPU must be serialised."""
+        check(self._lib.b2_materialize_master_static(_ptr(bytes_), _ptr(scales), _ptr(global_scale), _ptr(master),
+                                                     len_, scale_layout, _stream()), "materialize_master_static")
+
     def _sf_args(self, *, bytes, scales, global_scale, z_master, x_master, amax, len, scale_rows, scale_k, beta,
                  symexp_lin_beta=0.0, precomputed_values=None, scale_layout=SCALES_CSF, **_ignored):
         return _CSf(_ptr(bytes), _ptr(scales), _ptr(global_scale), _ptr(z_master), _ptr(x_master),
