@@ -221,62 +221,75 @@ k_muon_update(const b2_muon_slot_descriptor *slots, const uint32_t *prefix, uint
 }
 
 // ---------------------------------------------------------------------------------------------
-// stage Q: one 2048-value chunk = 128 groups of 16; four lanes per group, four values per
-// lane (crates/cuda-kernels/src/utils/nvfp4/quant/kernels/four_six/helpers.rs:41-94,
-// .../muon/fused/quant/encode.rs:37-60).
+// stage Q: one 2048-value chunk = 128 groups of 16, one thread per group (CTAs of 128 threads).
+// The arithmetic per group is that of
+// crates/cuda-kernels/src/utils/nvfp4/quant/kernels/four_six/helpers.rs:41-94 and
+// .../muon/fused/quant/encode.rs:37-60; the reference spreads a group over four lanes and
+// repeats the scale arithmetic in each, which makes the pass issue-bound on B200 — here the
+// scale is computed once per group and the 64 bytes of a group are read as four 128-bit loads
+// (the four loads of neighbouring lanes complete each other's sectors in L1).
 // MODE 0: values come from `src`; MODE 1: values are z + beta (x - z) computed on the fly
 // (crates/cuda-kernels/src/gpt/optimizer/schedule_free/value.rs:21-34).
 // ---------------------------------------------------------------------------------------------
+constexpr int kEncodeThreads = kChunk / 16;
+
 template <int MODE>
 __device__ __forceinline__ void encode_chunk(const float *src, const float *z, const float *xm,
                                              float beta, uint32_t len, uint32_t base, float gs,
                                              uint8_t *fp4, uint8_t *scales, int scale_layout,
                                              uint32_t csf_k, uint32_t csf_rows) {
-    const int tid = threadIdx.x;
-    const int lane = tid & 31;
+    const int lane = threadIdx.x & 31;
+    const uint32_t group = base / 16 + threadIdx.x;
+    const uint32_t i = group * 16;
+    const bool valid = i < len;
+    float v[16];
+#pragma unroll
+    for (int e = 0; e < 16; ++e) v[e] = 0.0f;
+    if (valid) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float4 t;
+            if (MODE == 0) {
+                t = __ldg(reinterpret_cast<const float4 *>(src + i) + j);
+            } else {
+                float4 zv = __ldg(reinterpret_cast<const float4 *>(z + i) + j);
+                float4 xv = __ldg(reinterpret_cast<const float4 *>(xm + i) + j);
+                t.x = zv.x + beta * (xv.x - zv.x);
+                t.y = zv.y + beta * (xv.y - zv.y);
+                t.z = zv.z + beta * (xv.z - zv.z);
+                t.w = zv.w + beta * (xv.w - zv.w);
+            }
+            v[4 * j] = t.x; v[4 * j + 1] = t.y; v[4 * j + 2] = t.z; v[4 * j + 3] = t.w;
+        }
+    }
+    float ga = 0.0f;
+#pragma unroll
+    for (int e = 0; e < 16; ++e) ga = fmaxf(ga, fabsf(v[e]));
+    float inv;
+    const uint32_t sb = group_scale_and_inv(ga, gs, inv);
+    uint32_t w[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-        const uint32_t group = base / 16 + h * (kThreads / 4) + (tid >> 2);
-        const uint32_t i = group * 16 + (tid & 3) * 4;
-        const bool valid = i < len;
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (valid) {
-            if (MODE == 0) {
-                v = ld_stream(src + i);
-            } else {
-                float4 zv = ld_stream(z + i), xv = ld_stream(xm + i);
-                v.x = zv.x + beta * (xv.x - zv.x);
-                v.y = zv.y + beta * (xv.y - zv.y);
-                v.z = zv.z + beta * (xv.z - zv.z);
-                v.w = zv.w + beta * (xv.w - zv.w);
-            }
-        }
-        float la = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
-        la = fmaxf(la, __shfl_xor_sync(0xffffffffu, la, 1));
-        float ga = fmaxf(la, __shfl_xor_sync(0xffffffffu, la, 2));
-        float inv;
-        uint32_t sb = group_scale_and_inv(ga, gs, inv);
-        uint32_t payload = pack_quad(v.x, v.y, v.z, v.w, inv);
-        if (valid) reinterpret_cast<uint16_t *>(fp4)[i >> 2] = (uint16_t)payload;
-        if (scale_layout == B2_SCALES_RAW) {
-            if (valid && (tid & 3) == 0) scales[group] = (uint8_t)sb;
-        } else {
-            // lanes 0,4,8,12 carry groups 0..3 (word a), lanes 16,20,24,28 groups 4..7 (word b)
-            // (crates/cuda-kernels/src/utils/nvfp4/csf.rs:212-232)
-            uint32_t s0 = __shfl_sync(0xffffffffu, sb, 0), s1 = __shfl_sync(0xffffffffu, sb, 4);
-            uint32_t s2 = __shfl_sync(0xffffffffu, sb, 8), s3 = __shfl_sync(0xffffffffu, sb, 12);
-            uint32_t s4 = __shfl_sync(0xffffffffu, sb, 16), s5 = __shfl_sync(0xffffffffu, sb, 20);
-            uint32_t s6 = __shfl_sync(0xffffffffu, sb, 24), s7 = __shfl_sync(0xffffffffu, sb, 28);
-            if (lane == 0 && valid) {
-                uint32_t a = s0 | (s1 << 8) | (s2 << 16) | (s3 << 24);
-                uint32_t b = s4 | (s5 << 8) | (s6 << 16) | (s7 << 24);
-                csf_store_record(scales, csf_k, csf_rows, group, a, b);
-            }
-        }
+        uint32_t p0 = cvt_e2m1x2(v[8 * h + 1] * inv, v[8 * h + 0] * inv);
+        uint32_t p1 = cvt_e2m1x2(v[8 * h + 3] * inv, v[8 * h + 2] * inv);
+        uint32_t p2 = cvt_e2m1x2(v[8 * h + 5] * inv, v[8 * h + 4] * inv);
+        uint32_t p3 = cvt_e2m1x2(v[8 * h + 7] * inv, v[8 * h + 6] * inv);
+        w[h] = p0 | (p1 << 8) | (p2 << 16) | (p3 << 24);
+    }
+    if (valid) *reinterpret_cast<uint2 *>(fp4 + (size_t)group * 8) = make_uint2(w[0], w[1]);
+    if (scale_layout == B2_SCALES_RAW) {
+        if (valid) scales[group] = (uint8_t)sb;
+    } else {
+        // eight consecutive groups (one CSF record, crates/cuda-kernels/src/utils/nvfp4/csf.rs:193-232)
+        // sit in eight consecutive lanes: fold their scale bytes into the first of them
+        uint32_t s2 = sb | (__shfl_down_sync(0xffffffffu, sb, 1) << 8);
+        uint32_t a = s2 | (__shfl_down_sync(0xffffffffu, s2, 2) << 16);
+        uint32_t b = __shfl_down_sync(0xffffffffu, a, 4);
+        if ((lane & 7) == 0 && valid) csf_store_record(scales, csf_k, csf_rows, group, a, b);
     }
 }
 
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kEncodeThreads)
 k_muon_encode(const b2_muon_slot_descriptor *slots, const uint32_t *prefix, uint32_t slot_count,
               uint32_t total_chunks, const float *amax_x, int quantize_y, int scale_layout) {
     for (uint32_t c = blockIdx.x; c < total_chunks; c += gridDim.x) {
@@ -303,7 +316,7 @@ k_muon_encode(const b2_muon_slot_descriptor *slots, const uint32_t *prefix, uint
 // (crates/cuda-kernels/src/utils/nvfp4/quant/kernels/four_six.rs:104-152) and
 // `schedule_free_four_six_kernel` (.../optimizer/schedule_free/four_six.rs:12-54).
 template <int MODE>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kEncodeThreads)
 k_quantize_flat(const float *src, const float *z, const float *xm, float beta, const float *amax,
                 uint8_t *fp4, uint8_t *scales, float *out_gs, uint32_t group_count,
                 int scale_layout) {
@@ -545,7 +558,7 @@ cudaError_t launch_muon_update(const SlotView &v, const uint64_t *u_ptrs, float 
 cudaError_t launch_muon_encode(const SlotView &v, const float *amax_x, int quantize_y,
                                int scale_layout, cudaStream_t s) {
     if (v.total_chunks == 0) return cudaSuccess;
-    k_muon_encode<<<clamp_grid(v.total_chunks, v.grid), kThreads, 0, s>>>(
+    k_muon_encode<<<clamp_grid(v.total_chunks, 2 * v.grid), kEncodeThreads, 0, s>>>(
         v.slots, v.chunk_prefix, v.slot_count, v.total_chunks, amax_x, quantize_y, scale_layout);
     return cudaGetLastError();
 }
@@ -565,12 +578,12 @@ cudaError_t launch_quantize_flat(const float *x, const float *z, const float *xm
                                  float *gs, uint32_t group_count, int scale_layout, int grid_cap,
                                  cudaStream_t s) {
     uint32_t chunks = (group_count * 16 + kChunk - 1) / kChunk;
-    int grid = clamp_grid(chunks, grid_cap);
+    int grid = clamp_grid(chunks, 2 * grid_cap);
     if (grid == 0) grid = 1;  // still writes the global scale
     if (mode == 0)
-        k_quantize_flat<0><<<grid, kThreads, 0, s>>>(x, z, xm, beta, amax, fp4, scales, gs, group_count, scale_layout);
+        k_quantize_flat<0><<<grid, kEncodeThreads, 0, s>>>(x, z, xm, beta, amax, fp4, scales, gs, group_count, scale_layout);
     else
-        k_quantize_flat<1><<<grid, kThreads, 0, s>>>(x, z, xm, beta, amax, fp4, scales, gs, group_count, scale_layout);
+        k_quantize_flat<1><<<grid, kEncodeThreads, 0, s>>>(x, z, xm, beta, amax, fp4, scales, gs, group_count, scale_layout);
     return cudaGetLastError();
 }
 cudaError_t launch_schedule_free_amax(const float *z, const float *x, float beta, uint32_t len,
