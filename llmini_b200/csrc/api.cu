@@ -66,7 +66,7 @@ EncodeTiledFn encode_tiled_fn() {
 // 2-D row-major tensor [rows][cols] with `pitch_bytes` between rows; box = box_cols x box_rows,
 // 128-byte swizzle, zero fill outside the tensor.
 bool make_map(CUtensorMap *m, void *base, int elem_bytes, uint64_t rows, uint64_t cols, uint64_t pitch_bytes,
-              uint32_t box_cols, uint32_t box_rows) {
+              uint32_t box_cols, uint32_t box_rows, bool swizzle = true) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return false;
     cuuint64_t dims[2] = {cols, rows};
@@ -74,7 +74,8 @@ bool make_map(CUtensorMap *m, void *base, int elem_bytes, uint64_t rows, uint64_
     cuuint32_t box[2] = {box_cols, box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
-    return fn(m, dt, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+    return fn(m, dt, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -101,7 +102,7 @@ double slot_flops(uint32_t rows, uint32_t cols) {
 
 enum ProblemType { kGram0 = 0, kGram1, kPoly, kApply0, kApply1, kLast0, kLast1, kProblemTypes };
 // load maps: *K = box 64 (K) x 128 rows for K-major use, *M = box 64 x 64 for MN-major use
-enum MapKind { kLX0K = 0, kLX1K, kLX0M, kLX1M, kLG, kLQ, kSX0, kSX1, kSG, kSQ, kSU, kMapsPerSlot };
+enum MapKind { kLX0K = 0, kLX1K, kLX0M, kLX1M, kLG, kLQ, kSX0, kSX1, kSG, kSQ, kSU, kSGT, kSQT, kMapsPerSlot };
 
 struct SlotLayout {
     uint32_t rows, cols, n, m, ldg, tiles_m_nn, tiles_n_nn, sub_m_nn;
@@ -114,6 +115,7 @@ struct Layout {
     uint32_t total_chunks = 0;
     int bn = 256;
     int pair = 0;   // 1: two-CTA 256 x 256 tiles
+    int symmetric = 0;  // 1: Gram / Poly compute the upper triangle of tiles only
     int tile_m = 128;
     size_t off_prefix, off_partials, off_inv_norm, off_amax_x, off_status, off_x0_ptrs, off_u_ptrs, off_maps,
         off_problems, off_tiles_nn, off_tiles_out, off_meta_end, total;
@@ -160,6 +162,7 @@ void pick_tiles(const uint32_t *rows, const uint32_t *cols, uint32_t count, cons
 bool build_layout(const uint32_t *rows, const uint32_t *cols, uint32_t count, const b2_muon_options &o, Layout &L) {
     pick_tiles(rows, cols, count, o, L.bn, L.pair);
     L.tile_m = L.pair ? 256 : 128;
+    L.symmetric = (L.pair && L.bn == 256 && !(o.reserved[2] & 4u)) ? 1 : 0;  // flag 4: measurement only, all tiles
     L.slots.resize(count);
     L.chunk_prefix.assign(count + 1, 0);
     size_t off = 0;
@@ -193,7 +196,7 @@ bool build_layout(const uint32_t *rows, const uint32_t *cols, uint32_t count, co
         sl.tiles_n_nn = (sl.n + L.bn - 1) / L.bn;
         sl.sub_m_nn = sl.tiles_m_nn * (L.tile_m / kGemmBlockM);  // 128-row sub-tiles (fragment scratch)
         if (sl.len == 0) continue;
-        L.tiles_nn += sl.tiles_m_nn * sl.tiles_n_nn;
+        L.tiles_nn += L.symmetric ? sl.tiles_m_nn * (sl.tiles_m_nn + 1) / 2 : sl.tiles_m_nn * sl.tiles_n_nn;
         uint32_t M = rows[s] > cols[s] ? sl.m : sl.n, N = rows[s] > cols[s] ? sl.n : sl.m;
         L.tiles_out += ((M + L.tile_m - 1) / L.tile_m) * ((N + L.bn - 1) / L.bn);
     }
@@ -337,12 +340,15 @@ int b2_muon_plan_create(b2_muon_plan **out, const uint32_t *rows, const uint32_t
         ok &= make_map(ms + kSG, p->ws + sl.off_g16, 2, sl.n, sl.n, gp, 64, 32);
         ok &= make_map(ms + kSQ, p->ws + sl.off_q16, 2, sl.n, sl.n, gp, 64, 32);
         ok &= make_map(ms + kSU, p->ws + sl.off_u, 4, sl.rows, sl.cols, (uint64_t)sl.cols * 4, 32, 32);
+        ok &= make_map(ms + kSGT, p->ws + sl.off_g16, 2, sl.n, sl.n, gp, 32, 64, false);
+        ok &= make_map(ms + kSQT, p->ws + sl.off_q16, 2, sl.n, sl.n, gp, 32, 64, false);
         const bool tall = sl.rows > sl.cols;
         const uint64_t frag = reinterpret_cast<uint64_t>(p->ws + sl.off_frag);
         for (int b = 0; b < 2; ++b) {
             GemmProblem &g = probs[(size_t)(kGram0 + b) * slot_count + s];
             g.map_a = g.map_b = dmap(s, (tall ? kLX0M : kLX0K) + b);
             g.map_out16 = dmap(s, kSG);
+            g.map_out16t = dmap(s, kSGT);
             g.frag32 = frag;
             g.M = g.N = sl.n; g.K = sl.m;
             g.a_mn_major = g.b_mn_major = tall ? 1u : 0u;
@@ -367,6 +373,7 @@ int b2_muon_plan_create(b2_muon_plan **out, const uint32_t *rows, const uint32_t
         GemmProblem &q = probs[(size_t)kPoly * slot_count + s];
         q.map_a = q.map_b = dmap(s, kLG);
         q.map_out16 = dmap(s, kSQ);
+        q.map_out16t = dmap(s, kSQT);
         q.frag32 = frag;
         q.M = q.N = q.K = sl.n;
         q.tiles_n = sl.tiles_n_nn;
@@ -387,7 +394,12 @@ int b2_muon_plan_create(b2_muon_plan **out, const uint32_t *rows, const uint32_t
     for (uint32_t s : order) {
         const SlotLayout &sl = L.slots[s];
         for (uint32_t i = 0; i < sl.tiles_m_nn; ++i)
-            for (uint32_t j = 0; j < sl.tiles_n_nn; ++j) tnn[inn++] = GemmTile{(uint16_t)s, (uint16_t)i, (uint16_t)j, 0};
+            for (uint32_t j = 0; j < sl.tiles_n_nn; ++j) {
+                // square 256 x 256 tiles: G and Q are symmetric, so only tiles on or above the
+                // diagonal are computed and the others are written as transposes
+                if (L.symmetric && j < i) continue;
+                tnn[inn++] = GemmTile{(uint16_t)s, (uint16_t)i, (uint16_t)j, (uint16_t)((L.symmetric && j > i) ? 1 : 0)};
+            }
     }
     std::stable_sort(order.begin(), order.end(), [&](uint32_t a, uint32_t b) { return L.slots[a].n > L.slots[b].n; });
     for (uint32_t s : order) {

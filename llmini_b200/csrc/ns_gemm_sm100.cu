@@ -352,7 +352,10 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
             const GemmTile tl = tiles[t];
             const GemmProblem *p = problems + tl.problem;
             const uint32_t M = p->M, N = p->N;
-            const uint64_t map16 = p->map_out16, map32 = p->map_out32;
+            const uint64_t map16 = p->map_out16, map32 = p->map_out32, map16t = p->map_out16t;
+            // symmetric outputs (Gram, Poly): tiles below the diagonal are not computed; the tile
+            // above writes them as its transpose (reference: tiles/symmetric.rs:76-92)
+            const bool mirror = tl.reserved != 0;
             const float4 *frag = reinterpret_cast<const float4 *>(p->frag32);
             // fragment scratch is indexed by 128-row sub-tiles
             const uint32_t sub_m = PAIR ? (uint32_t)tl.tile_m * 2 + rank : tl.tile_m;
@@ -465,6 +468,25 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
                     if (lane == 0) {
                         tma_store_2d(map16, slab_u32, n0 + c0, slab_row0);
                         tma_store_commit();
+                    }
+                    if (mirror) {
+                        // transposed 64 x 32 block (rows = this chunk's columns), plain row-major
+                        // 64-byte rows: lanes pair up so every lane stores two rows of one column
+                        if (lane == 0) tma_store_wait_read_all();
+                        __syncwarp();
+#pragma unroll
+                        for (int c = 0; c < 64; c += 2) {
+                            const uint32_t mine = pack_operands(__uint_as_float(v[c]), __uint_as_float(v[c + 1]), f16);
+                            const uint32_t other = __shfl_xor_sync(0xffffffffu, mine, 1);
+                            const uint32_t out = (lane & 1) ? __byte_perm(other, mine, 0x7632) : __byte_perm(mine, other, 0x5410);
+                            *reinterpret_cast<uint32_t *>(slab + (c + (lane & 1)) * 64 + (lane & ~1) * 2) = out;
+                        }
+                        fence_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            tma_store_2d(map16t, slab_u32, slab_row0, n0 + c0);
+                            tma_store_commit();
+                        }
                     }
                 }
             }
