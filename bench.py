@@ -377,9 +377,23 @@ def run_gpu(args):
     adam_elems = sum(t["len"] for _, t in adam_sets)
     adam_gbs = adam_elems * 36.0 / (adam_ms * 1e-3) / 1e9 if adam_ms > 0 else 0.0
 
+    def finish():
+        # Release the captured graph before the communicator: a graph that still holds NCCL
+        # kernels can keep the communicator's teardown waiting.  A watchdog ends the process if
+        # teardown stalls anyway; by then the result line has been printed.
+        nonlocal graph
+        if world == 1:
+            return
+        import threading
+        threading.Timer(30.0, lambda: os._exit(0)).start()
+        graph = None
+        torch.cuda.synchronize()
+        dist.barrier()
+        dist.destroy_process_group()
+        os._exit(0)
+
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
+        finish()
         return
     peak_tf = peaks["tf_sustained"]
     line = {
@@ -417,8 +431,7 @@ def run_gpu(args):
         cms, sample = cpu_sample_ms(args.workload, 1)
         line["cpu_baseline"] = {"value": cms, "unit": "ms", "cores": os.cpu_count() or 1, "kind": "port", "sample": sample}
     print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    finish()
 
 
 def main():
