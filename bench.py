@@ -262,7 +262,7 @@ def run_gpu(args):
     launches_per_step = 0
     if plan is not None:
         launches_per_step += 3 + 3 * HP["iterations"] + 2
-    launches_per_step += sum(4 if k == "quant" else 1 for k, _ in adam_sets)
+    launches_per_step += sum(2 if k == "quant" else 1 for k, _ in adam_sets)  # memsets are not counted
 
     stream = torch.cuda.current_stream()
     ev = lambda: torch.cuda.Event(enable_timing=True)
@@ -434,6 +434,49 @@ def run_gpu(args):
     finish()
 
 
+def run_sweep(args):
+    """Bandwidth sweep of the update + quantise pass on [R, 4096] tensors (R = 256 .. 262144):
+    one JSON line per shape.  Not part of the default run."""
+    import torch
+
+    import llmini_b200 as b2
+
+    torch.cuda.set_device(0)
+    peaks = load_peaks()
+    opt = b2.OptimizerModule()
+    for R in (256, 1024, 4096, 16384, 65536, 262144):
+        r, c = R, 4096
+        n = r * c
+        s = b2.MuonSlot.allocate(r, c)
+        g = torch.Generator(device="cuda").manual_seed(R)
+        s.z_master.copy_((torch.randn(n, device="cuda", generator=g) * 0.02).view(r, c))
+        s.x_master.copy_(s.z_master)
+        plan = b2.MuonPlan([(r, c)])
+        table = b2.slot_table([s])
+        margs = b2.MuonMegaUpdateArgs(**HP)
+        opt.muon_tma_prepare_polar(plan, table, margs)
+        plan.scratch(0, 1).copy_((torch.randn(n, device="cuda", generator=g) * 0.02).view(r, c))
+        reps = max(3, min(50, int(2e9 // n)))
+        for _ in range(3):
+            opt.muon_tma_finish_update(plan, table, margs)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            opt.muon_tma_finish_update(plan, table, margs)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / reps
+        gbs = n * 24.5625 / (ms * 1e-3) / 1e9
+        print(json.dumps({"sweep": "update_quantise", "rows": r, "cols": c, "elements": n, "ms": ms,
+                          "bytes_per_element": 24.5625, "gbs": gbs, "frac_of_measured_hbm": gbs / peaks["hbm"],
+                          "frac_of_nominal_8000": gbs / 8000.0,
+                          "note": "tensors under ~5 M elements stay in the 126 MB L2 between repetitions"}), flush=True)
+        plan.close()
+        del s, plan, table
+        torch.cuda.empty_cache()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -443,7 +486,11 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a CUDA graph replay")
+    ap.add_argument("--sweep", action="store_true", help="update+quantise bandwidth sweep over [R, 4096] tensors")
     args = ap.parse_args()
+    if args.sweep:
+        run_sweep(args)
+        return
     if args.impl == "reference":
         run_reference(args)
     else:

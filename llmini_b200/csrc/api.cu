@@ -636,10 +636,18 @@ int b2_apply_fp32_adamw_update(const b2_adamw_update_args *a, void *stream) {
 int b2_apply_adamw_update(const b2_adamw_update_args *a, void *stream) {
     int rc = check_adam(a, true, false);
     if (rc) return rc;
-    rc = b2_apply_fp32_adamw_update(a, stream);
-    if (rc) return rc;
-    return b2_materialize_master(a->bytes, a->scales, a->global_scale, a->x_master, a->amax, a->chunk_amax, a->len,
-                                 a->scale_layout, stream);
+    DeviceInfo d;
+    cudaError_t e = device_info(d);
+    if (e != cudaSuccess) return (int)e;
+    // The reference runs the update, then materialize_master (two amax kernels + encode).  Here
+    // the update kernel raises max|x'| itself (atomicMax, order-independent, so the same value),
+    // which saves the extra read of x'; `chunk_amax` is left untouched.
+    cudaStream_t s = as_stream(stream);
+    e = cudaMemsetAsync(a->amax, 0, sizeof(float), s);
+    if (e == cudaSuccess) e = launch_adamw(*a, 2, stream_grid_cap(d), s);
+    if (e != cudaSuccess) return (int)e;
+    return b2_fp32_to_nvfp4_four_six(a->x_master, a->amax, a->bytes, a->scales, a->global_scale, a->len / 16,
+                                     a->scale_layout, stream);
 }
 int b2_apply_adamw_update_deferred_quantization(const b2_adamw_update_args *a, void *stream) {
     int rc = check_adam(a, false, true);

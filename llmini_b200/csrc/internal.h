@@ -40,7 +40,7 @@ cudaError_t launch_quantize_flat(const float *x, const float *z, const float *xm
                                  cudaStream_t s);
 cudaError_t launch_schedule_free_amax(const float *z, const float *x, float beta, uint32_t len,
                                       float *amax, int grid_cap, cudaStream_t s);
-cudaError_t launch_adamw(const b2_adamw_update_args &a, int with_schedule, int grid_cap,
+cudaError_t launch_adamw(const b2_adamw_update_args &a, int mode, int grid_cap,
                          cudaStream_t s);
 cudaError_t launch_zero_pointer_table(const uint64_t *ptrs, uint32_t n, cudaStream_t s);
 cudaError_t launch_layout_echo(uint32_t *out, cudaStream_t s);

@@ -428,7 +428,10 @@ __device__ __forceinline__ void adam_one(float &z, float &x, float &g_io, float 
     x = nx;
     sched = next + a.sched_beta * (nx - next);
 }
-template <int WITH_SCHEDULE>
+// MODE 0: masters and moments only; 1: also y into the gradient buffer and max|y| (deferred
+// quantisation); 2: also max|x'|, which the requantisation that follows needs, so that x' is not
+// read a second time just for its maximum.
+template <int MODE>
 __global__ void __launch_bounds__(kThreads)
 k_adamw(float *z, float *x, float *grad, float *m1, float *m2, float *amax, AdamScalars a,
         uint32_t len) {
@@ -456,24 +459,28 @@ k_adamw(float *z, float *x, float *grad, float *m1, float *m2, float *amax, Adam
                 *reinterpret_cast<float4 *>(x + i) = xv;
                 st_stream(m1 + i, av);
                 st_stream(m2 + i, bv);
-                if (WITH_SCHEDULE) {
+                if (MODE == 1) {
                     *reinterpret_cast<float4 *>(grad + i) = sv;
                     am = fmaxf(am, fmaxf(fmaxf(fabsf(sv.x), fabsf(sv.y)), fmaxf(fabsf(sv.z), fabsf(sv.w))));
+                } else if (MODE == 2) {
+                    am = fmaxf(am, fmaxf(fmaxf(fabsf(xv.x), fabsf(xv.y)), fmaxf(fabsf(xv.z), fabsf(xv.w))));
                 }
             } else {
                 for (uint32_t j = i; j < len && j < i + 4; ++j) {
                     float zz = z[j], xx = x[j], gg = grad[j], aa = m1[j], bb = m2[j], ss;
                     adam_one(zz, xx, gg, aa, bb, a, decay, ss);
                     z[j] = zz; x[j] = xx; m1[j] = aa; m2[j] = bb;
-                    if (WITH_SCHEDULE) {
+                    if (MODE == 1) {
                         grad[j] = ss;
                         am = fmaxf(am, fabsf(ss));
+                    } else if (MODE == 2) {
+                        am = fmaxf(am, fabsf(xx));
                     }
                 }
             }
         }
     }
-    if (WITH_SCHEDULE) {
+    if (MODE != 0) {
         am = warp_max(am);
         if ((tid & 31) == 0) warp_part[tid >> 5] = am;
         __syncthreads();
@@ -593,15 +600,17 @@ cudaError_t launch_schedule_free_amax(const float *z, const float *x, float beta
     k_schedule_free_amax<<<clamp_grid(chunks, grid_cap), kThreads, 0, s>>>(z, x, beta, len, amax);
     return cudaGetLastError();
 }
-cudaError_t launch_adamw(const b2_adamw_update_args &a, int with_schedule, int grid_cap,
+cudaError_t launch_adamw(const b2_adamw_update_args &a, int mode, int grid_cap,
                          cudaStream_t s) {
     uint32_t chunks = (a.len + kChunk - 1) / kChunk;
     if (chunks == 0) return cudaSuccess;
     AdamScalars sc{a.grad_scale, a.learning_rate, a.weight_decay, a.beta1, a.beta2,
                    a.beta1_correction, a.beta2_correction, a.eps, a.average_coefficient, a.schedule_beta};
     int grid = clamp_grid(chunks, grid_cap);
-    if (with_schedule)
+    if (mode == 1)
         k_adamw<1><<<grid, kThreads, 0, s>>>(a.z_master, a.x_master, a.grad, a.first_moment, a.second_moment, a.amax, sc, a.len);
+    else if (mode == 2)
+        k_adamw<2><<<grid, kThreads, 0, s>>>(a.z_master, a.x_master, a.grad, a.first_moment, a.second_moment, a.amax, sc, a.len);
     else
         k_adamw<0><<<grid, kThreads, 0, s>>>(a.z_master, a.x_master, a.grad, a.first_moment, a.second_moment, nullptr, sc, a.len);
     return cudaGetLastError();

@@ -206,3 +206,72 @@ def test_adamw_matches_oracle(n):
         assert np.array_equal(host(t["grad"]), g)  # untouched without the schedule output
     for key, want in (("z_master", z2), ("x_master", x2), ("first_moment", a2), ("second_moment", b2_)):
         assert np.array_equal(host(t[key]), want), key  # IEEE elementwise: bit-exact
+
+
+@pytest.mark.parametrize("R", [256, 1024])
+def test_update_quantise_sweep_shapes_bit_exact(R):
+    # bandwidth-sweep shapes [R, 4096]: update input N(0, 0.02) with 0.1 % of entries x 50
+    rng = np.random.default_rng(R)
+    r, c = R, 4096
+    z, x = U.weights(rng, r * c), U.weights(rng, r * c)
+    Um = U.with_outliers(rng, U.weights(rng, r * c))
+    opt = b2.OptimizerModule()
+    s = b2.MuonSlot.allocate(r, c)
+    _fill_slot(s, np.zeros(r * c, F), np.zeros(r * c, np.uint16), z, x)
+    plan = b2.MuonPlan([(r, c)])
+    table = b2.slot_table([s])
+    args = b2.MuonMegaUpdateArgs(learning_rate=0.02, average_coefficient=0.5, schedule_beta=0.2)
+    opt.muon_tma_prepare_polar(plan, table, args)
+    plan.scratch(0, 1).copy_(dev(Um).view(r, c))
+    opt.muon_tma_finish_update(plan, table, args)
+    torch.cuda.synchronize()
+    z2, x2, y2, ax, ay = o.update(Um, z, x, r, c, 0.02, 0.025, 0.5, 0.2)
+    assert np.array_equal(host(s.z_master).ravel(), z2) and np.array_equal(host(s.x_master).ravel(), x2)
+    assert np.array_equal(host(s.grad).ravel(), y2)
+    gs = host(s.global_scale)[0]
+    codes, raw, ogs, misses = o.nvfp4_quantize(x2, amax=ax, rcp_table=rcp_table(gs))
+    assert misses == 0 and gs == ogs and np.array_equal(host(s.bytes), codes)
+    assert np.array_equal(host(s.scales), o.csf_encode(raw, r, c))
+    plan.close()
+
+
+def test_update_quantise_large_shape_properties():
+    # 65536 x 4096 (268 M elements): too large for the CPU oracle in a test, so the checks are
+    # size-independent: elementwise results against the same IEEE operations done by torch
+    # (separate mul / sub kernels, no contraction), tensor maxima, and the packed output against
+    # the literal one-thread-per-group device transcription of the reference quantiser.
+    r, c = 65536, 4096
+    n = r * c
+    g = torch.Generator(device="cuda").manual_seed(1)
+    z = torch.randn(n, device="cuda", generator=g) * 0.02
+    x = torch.randn(n, device="cuda", generator=g) * 0.02
+    Um = torch.randn(n, device="cuda", generator=g) * 0.02
+    s = b2.MuonSlot.allocate(r, c)
+    s.z_master.copy_(z.view(r, c)); s.x_master.copy_(x.view(r, c))
+    plan = b2.MuonPlan([(r, c)])
+    table = b2.slot_table([s])
+    opt = b2.OptimizerModule()
+    lr, wd, cavg, beta = 0.02, 0.025, 0.5, 0.2
+    args = b2.MuonMegaUpdateArgs(learning_rate=lr, weight_decay=wd, average_coefficient=cavg, schedule_beta=beta)
+    opt.muon_tma_prepare_polar(plan, table, args)
+    plan.scratch(0, 1).copy_(Um.view(r, c))
+    opt.muon_tma_finish_update(plan, table, args)
+    torch.cuda.synchronize()
+    f32 = lambda v: torch.tensor(v, dtype=torch.float32, device="cuda")
+    scale = f32(0.2) * torch.sqrt(f32(float(max(r, c))))
+    decay = f32(1.0) - f32(lr) * f32(wd)
+    nz = z * decay - f32(lr) * (scale * Um)
+    nx = x + f32(cavg) * (nz - x)
+    ny = nz + f32(beta) * (nx - nz)
+    assert torch.equal(s.z_master.view(-1), nz) and torch.equal(s.x_master.view(-1), nx)
+    assert torch.equal(s.grad.view(-1), ny)
+    assert s.schedule_amax.item() == ny.abs().max().item()
+    amax = nx.abs().max().reshape(1)
+    assert plan.scratch(0, 3).item() == amax.item()
+    del z, x, Um, nz, ny
+    lit4, lits, litg = b2.Nvfp4QuantModule().debug_quantize_literal(nx, amax)
+    torch.cuda.synchronize()
+    assert torch.equal(lit4, s.bytes) and torch.equal(litg, s.global_scale)
+    raw = o.csf_decode_matrix(host(s.scales), r, c)
+    assert np.array_equal(raw, host(lits))
+    plan.close()
