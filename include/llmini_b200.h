@@ -93,6 +93,9 @@ typedef struct b2_muon_step_args {
     uint32_t nesterov;          /* the mega kernel passes true (.../muon/fused/body.rs:34) */
     const float *coefficients;  /* host pointer, iterations x (a, b, c); NULL selects the
                                    reference table (.../muon/polar/fused/coefficients.rs:9-42) */
+    const float *d_grad_scale;  /* optional DEVICE pointer to the clip scale written by
+                                   b2_clip_gradients; when non-NULL it replaces `grad_scale`, so
+                                   the step needs no host read-back of the gradient norm */
 } b2_muon_step_args;
 
 typedef struct b2_muon_plan b2_muon_plan;
@@ -233,6 +236,7 @@ typedef struct b2_adamw_update_args {
     float eps;
     float average_coefficient;
     float schedule_beta;
+    const float *d_grad_scale; /* optional DEVICE pointer; replaces grad_scale when non-NULL */
 } b2_adamw_update_args;
 /* `OptimizerModule::apply_adamw_update` (.../launcher/adam.rs:9-21). */
 int b2_apply_adamw_update(const b2_adamw_update_args *args, void *stream);
@@ -243,6 +247,25 @@ int b2_apply_adamw_update_deferred_quantization(const b2_adamw_update_args *args
 int b2_apply_fp32_adamw_update(const b2_adamw_update_args *args, void *stream);
 /* `OptimizerModule::zero_f32_pointer_table` (.../launcher/adam.rs:30-43). */
 int b2_zero_f32_pointer_table(const uint64_t *d_pointers, uint32_t pointer_count, void *stream);
+
+/* ---- global gradient-norm clip (the producer of grad_scale) --------------------------------- */
+/* `GradientClipArgs` (crates/cuda-kernels/src/gpt/optimizer/args/grad_clip.rs:3-15). */
+typedef struct b2_gradient_clip_args {
+    const uint64_t *chunk_ptrs; /* device: f32 pointers, one per chunk (the reference cuts 4096-value chunks) */
+    const uint32_t *chunk_lens; /* device: values per chunk */
+    float *chunk_sums;          /* device scratch, chunk_count floats */
+    const float *extra_sums;    /* device: sums of squares computed elsewhere; may be NULL when count is 0 */
+    float *scale;               /* device f32[1]: norm > max_norm ? max_norm / (norm + 1e-6) : 1 */
+    float *norm;                /* device f32[1] */
+    uint32_t chunk_count;
+    uint32_t extra_sum_count;
+    float max_norm;
+    uint32_t apply;             /* non-zero: also multiply every chunk by the scale */
+} b2_gradient_clip_args;
+/* `OptimizerModule::clip_gradients` (kernels: .../optimizer/grad_clip/{sumsq,scale,apply}.rs).
+ * The reference reads `scale` back to the host after this call; here it can stay on the device
+ * and be passed to the step as `d_grad_scale`. */
+int b2_clip_gradients(const b2_gradient_clip_args *args, void *stream);
 
 /* ---- CSF block-scale storage, host side -------------------------------------------- */
 /* crates/cuda-kernels/src/utils/nvfp4/csf.rs:8-17 (encoded_len). */

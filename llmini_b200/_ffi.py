@@ -39,7 +39,8 @@ class MuonOptions(C.Structure):
 class MuonStepArgs(C.Structure):
     _fields_ = [("mu", C.c_float), ("grad_scale", C.c_float), ("learning_rate", C.c_float),
                 ("weight_decay", C.c_float), ("average_coefficient", C.c_float), ("schedule_beta", C.c_float),
-                ("iterations", C.c_uint32), ("nesterov", C.c_uint32), ("coefficients", C.POINTER(C.c_float))]
+                ("iterations", C.c_uint32), ("nesterov", C.c_uint32), ("coefficients", C.POINTER(C.c_float)),
+                ("d_grad_scale", C.c_void_p)]
 
 
 class ScheduleFreeMaterializeArgs(C.Structure):
@@ -57,7 +58,14 @@ class AdamWUpdateArgs(C.Structure):
                 ("chunk_amax", C.c_void_p), ("len", C.c_uint32), ("learning_rate", C.c_float),
                 ("weight_decay", C.c_float), ("beta1", C.c_float), ("beta2", C.c_float),
                 ("beta1_correction", C.c_float), ("beta2_correction", C.c_float), ("eps", C.c_float),
-                ("average_coefficient", C.c_float), ("schedule_beta", C.c_float)]
+                ("average_coefficient", C.c_float), ("schedule_beta", C.c_float), ("d_grad_scale", C.c_void_p)]
+
+
+class GradientClipArgs(C.Structure):
+    _fields_ = [("chunk_ptrs", C.c_void_p), ("chunk_lens", C.c_void_p), ("chunk_sums", C.c_void_p),
+                ("extra_sums", C.c_void_p), ("scale", C.c_void_p), ("norm", C.c_void_p),
+                ("chunk_count", C.c_uint32), ("extra_sum_count", C.c_uint32), ("max_norm", C.c_float),
+                ("apply", C.c_uint32)]
 
 
 def declared_symbols() -> list[str]:
@@ -96,6 +104,7 @@ def _declare(L: C.CDLL) -> None:
         "b2_apply_adamw_update_deferred_quantization": (i, [C.POINTER(AdamWUpdateArgs), vp]),
         "b2_apply_fp32_adamw_update": (i, [C.POINTER(AdamWUpdateArgs), vp]),
         "b2_zero_f32_pointer_table": (i, [vp, u32, vp]),
+        "b2_clip_gradients": (i, [C.POINTER(GradientClipArgs), vp]),
         "b2_csf_encoded_len": (sz, [sz, sz]),
         "b2_csf_encode_host": (sz, [u8p, sz, sz, sz, u8p, sz]),
         "b2_csf_scale_at": (C.c_uint8, [u8p, sz]),

@@ -435,11 +435,11 @@ int b2_muon_prepare_polar(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_s
     SlotView v = plan->view(d_slots);
     double *partials = plan->at<double>(L.off_partials);
     float *inv = plan->at<float>(L.off_inv_norm);
-    cudaError_t e = launch_muon_sumsq(v, a->mu, a->grad_scale, (int)a->nesterov, partials,
+    cudaError_t e = launch_muon_sumsq(v, a->mu, a->grad_scale, a->d_grad_scale, (int)a->nesterov, partials,
                                       plan->at<float>(L.off_amax_x), s);
     if (e == cudaSuccess) e = launch_muon_inv_norm(v, partials, inv, s);
     if (e == cudaSuccess)
-        e = launch_muon_momentum_normalize(v, a->mu, a->grad_scale, (int)a->nesterov, inv,
+        e = launch_muon_momentum_normalize(v, a->mu, a->grad_scale, a->d_grad_scale, (int)a->nesterov, inv,
                                            plan->at<uint64_t>(L.off_x0_ptrs),
                                            plan->options.operand_format == B2_OPERAND_F16, s);
     return (int)e;
@@ -656,6 +656,15 @@ int b2_apply_adamw_update_deferred_quantization(const b2_adamw_update_args *a, v
     cudaError_t e = device_info(d);
     if (e != cudaSuccess) return (int)e;
     return (int)launch_adamw(*a, 1, stream_grid_cap(d), as_stream(stream));
+}
+int b2_clip_gradients(const b2_gradient_clip_args *a, void *stream) {
+    if (!a || !a->scale || !a->norm) return B2_ERROR_INVALID_VALUE;
+    if (a->chunk_count && (!a->chunk_ptrs || !a->chunk_lens || !a->chunk_sums)) return B2_ERROR_INVALID_VALUE;
+    if (a->extra_sum_count && !a->extra_sums) return B2_ERROR_INVALID_VALUE;
+    DeviceInfo d;
+    cudaError_t e = device_info(d);
+    if (e != cudaSuccess) return (int)e;
+    return (int)launch_grad_clip(*a, stream_grid_cap(d), as_stream(stream));
 }
 int b2_zero_f32_pointer_table(const uint64_t *d_pointers, uint32_t pointer_count, void *stream) {
     if (!d_pointers && pointer_count) return B2_ERROR_INVALID_VALUE;

@@ -18,12 +18,12 @@ struct SlotView {
     int grid;                              // CTAs to launch (multiple of the SM count)
 };
 
-cudaError_t launch_muon_sumsq(const SlotView &v, float mu, float grad_scale, int nesterov,
-                              double *partials, float *amax_x, cudaStream_t s);
+cudaError_t launch_muon_sumsq(const SlotView &v, float mu, float grad_scale, const float *d_grad_scale,
+                              int nesterov, double *partials, float *amax_x, cudaStream_t s);
 cudaError_t launch_muon_inv_norm(const SlotView &v, const double *partials, float *inv_norm,
                                  cudaStream_t s);
 cudaError_t launch_muon_momentum_normalize(const SlotView &v, float mu, float grad_scale,
-                                           int nesterov, const float *inv_norm,
+                                           const float *d_grad_scale, int nesterov, const float *inv_norm,
                                            const uint64_t *x0_ptrs, int f16, cudaStream_t s);
 cudaError_t launch_muon_update(const SlotView &v, const uint64_t *u_ptrs, float *amax_x, float lr,
                                float wd, float c_avg, float beta, cudaStream_t s);
@@ -42,6 +42,7 @@ cudaError_t launch_schedule_free_amax(const float *z, const float *x, float beta
                                       float *amax, int grid_cap, cudaStream_t s);
 cudaError_t launch_adamw(const b2_adamw_update_args &a, int mode, int grid_cap,
                          cudaStream_t s);
+cudaError_t launch_grad_clip(const b2_gradient_clip_args &a, int grid_cap, cudaStream_t s);
 cudaError_t launch_zero_pointer_table(const uint64_t *ptrs, uint32_t n, cudaStream_t s);
 cudaError_t launch_layout_echo(uint32_t *out, cudaStream_t s);
 cudaError_t launch_debug_rcp(const float *in, float *out, uint32_t n, cudaStream_t s);

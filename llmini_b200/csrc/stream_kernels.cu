@@ -40,21 +40,22 @@ __device__ __forceinline__ ChunkCtx chunk_ctx(const b2_muon_slot_descriptor *slo
     return x;
 }
 
-// Pass 1 of stages M+N: sum of u^2 per chunk, accumulated in double so the result does not
-// depend on the reduction order beyond the last f32 rounding.  Also clears the two amax
+// Pass 1 of stages M+N: sum of u^2 per chunk: an f32 fma chain over a thread's eight values,
+// then f64 across threads, warps and chunks, so the grid shape does not change the result.  Also clears the two amax
 // words the update kernel later raises with atomicMax.
 __global__ void __launch_bounds__(kThreads)
 k_muon_sumsq(const b2_muon_slot_descriptor *slots, const uint32_t *prefix, uint32_t slot_count,
-             uint32_t total_chunks, float mu, float grad_scale, int nesterov, double *partials,
-             float *amax_x) {
+             uint32_t total_chunks, float mu, float grad_scale, const float *d_grad_scale, int nesterov,
+             double *partials, float *amax_x) {
     __shared__ double warp_part[kThreads / 32];
     const int tid = threadIdx.x;
+    if (d_grad_scale) grad_scale = __ldg(d_grad_scale);
     for (uint32_t c = blockIdx.x; c < total_chunks; c += gridDim.x) {
         ChunkCtx cx = chunk_ctx(slots, prefix, slot_count, c);
         const float *grad = reinterpret_cast<const float *>(cx.d.grad);
         const uint16_t *mom = reinterpret_cast<const uint16_t *>(cx.d.momentum);
         const uint32_t base = cx.local_chunk * kChunk;
-        double acc = 0.0;
+        float local = 0.0f;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             uint32_t i = base + h * (kChunk / 2) + tid * 4;
@@ -66,13 +67,15 @@ k_muon_sumsq(const b2_muon_slot_descriptor *slots, const uint32_t *prefix, uint3
                 float u1 = momentum_update(g.y, bf16_bits_to_f32(m.x >> 16), mu, grad_scale, nesterov, nm);
                 float u2 = momentum_update(g.z, bf16_bits_to_f32(m.y & 0xffffu), mu, grad_scale, nesterov, nm);
                 float u3 = momentum_update(g.w, bf16_bits_to_f32(m.y >> 16), mu, grad_scale, nesterov, nm);
-                acc = fma((double)u0, (double)u0, acc);
-                acc = fma((double)u1, (double)u1, acc);
-                acc = fma((double)u2, (double)u2, acc);
-                acc = fma((double)u3, (double)u3, acc);
+                // per-thread chain as in the reference (momentum.rs:63: fma(update, update, sum));
+                // eight terms at most, so the chain's rounding stays below 1e-7 relative
+                local = fmaf(u0, u0, local);
+                local = fmaf(u1, u1, local);
+                local = fmaf(u2, u2, local);
+                local = fmaf(u3, u3, local);
             }
         }
-        acc = warp_sum(acc);
+        double acc = warp_sum((double)local);
         if ((tid & 31) == 0) warp_part[tid >> 5] = acc;
         __syncthreads();
         if (tid == 0) {
@@ -117,8 +120,10 @@ k_muon_inv_norm(const uint32_t *prefix, const double *partials, float *inv_norm)
 __global__ void __launch_bounds__(kThreads)
 k_muon_momentum_normalize(const b2_muon_slot_descriptor *slots, const uint32_t *prefix,
                           uint32_t slot_count, uint32_t total_chunks, float mu, float grad_scale,
-                          int nesterov, const float *inv_norm, const uint64_t *x0_ptrs, int f16) {
+                          const float *d_grad_scale, int nesterov, const float *inv_norm,
+                          const uint64_t *x0_ptrs, int f16) {
     const int tid = threadIdx.x;
+    if (d_grad_scale) grad_scale = __ldg(d_grad_scale);
     for (uint32_t c = blockIdx.x; c < total_chunks; c += gridDim.x) {
         ChunkCtx cx = chunk_ctx(slots, prefix, slot_count, c);
         const float *grad = reinterpret_cast<const float *>(cx.d.grad);
@@ -226,8 +231,8 @@ k_muon_update(const b2_muon_slot_descriptor *slots, const uint32_t *prefix, uint
 // crates/cuda-kernels/src/utils/nvfp4/quant/kernels/four_six/helpers.rs:41-94 and
 // .../muon/fused/quant/encode.rs:37-60; the reference spreads a group over four lanes and
 // repeats the scale arithmetic in each, which makes the pass issue-bound on B200 — here the
-// scale is computed once per group and the 64 bytes of a group are read as four 128-bit loads
-// (the four loads of neighbouring lanes complete each other's sectors in L1).
+// scale is computed once per group; the loads stay fully coalesced through a per-warp
+// shared-memory exchange.
 // MODE 0: values come from `src`; MODE 1: values are z + beta (x - z) computed on the fly
 // (crates/cuda-kernels/src/gpt/optimizer/schedule_free/value.rs:21-34).
 // ---------------------------------------------------------------------------------------------
@@ -238,30 +243,43 @@ __device__ __forceinline__ void encode_chunk(const float *src, const float *z, c
                                              float beta, uint32_t len, uint32_t base, float gs,
                                              uint8_t *fp4, uint8_t *scales, int scale_layout,
                                              uint32_t csf_k, uint32_t csf_rows) {
+    // Each warp owns 32 consecutive groups = 2048 contiguous bytes.  It reads them with four
+    // fully coalesced 128-bit loads per lane, parks them in shared memory (16-byte slots XOR-ed
+    // with the group number so neither side conflicts) and every lane picks up its own group.
+    __shared__ float4 stage[kEncodeThreads / 32][128];
     const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
     const uint32_t group = base / 16 + threadIdx.x;
     const uint32_t i = group * 16;
     const bool valid = i < len;
+    const uint32_t warp_first = (base / 16 + warp * 32) * 16;   // first element of this warp's span
     float v[16];
 #pragma unroll
-    for (int e = 0; e < 16; ++e) v[e] = 0.0f;
-    if (valid) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            float4 t;
+    for (int j = 0; j < 4; ++j) {
+        const uint32_t f4 = j * 32 + lane;                       // float4 index inside the span
+        const uint32_t e = warp_first + f4 * 4;
+        float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (e < len) {
             if (MODE == 0) {
-                t = __ldg(reinterpret_cast<const float4 *>(src + i) + j);
+                t = ld_stream(src + e);
             } else {
-                float4 zv = __ldg(reinterpret_cast<const float4 *>(z + i) + j);
-                float4 xv = __ldg(reinterpret_cast<const float4 *>(xm + i) + j);
+                float4 zv = ld_stream(z + e), xv = ld_stream(xm + e);
                 t.x = zv.x + beta * (xv.x - zv.x);
                 t.y = zv.y + beta * (xv.y - zv.y);
                 t.z = zv.z + beta * (xv.z - zv.z);
                 t.w = zv.w + beta * (xv.w - zv.w);
             }
-            v[4 * j] = t.x; v[4 * j + 1] = t.y; v[4 * j + 2] = t.z; v[4 * j + 3] = t.w;
         }
+        const uint32_t g = f4 >> 2, k = f4 & 3;
+        stage[warp][g * 4 + (k ^ (g & 3))] = t;
     }
+    __syncwarp();
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float4 t = stage[warp][lane * 4 + (k ^ (lane & 3))];
+        v[4 * k] = t.x; v[4 * k + 1] = t.y; v[4 * k + 2] = t.z; v[4 * k + 3] = t.w;
+    }
+    __syncwarp();
     float ga = 0.0f;
 #pragma unroll
     for (int e = 0; e < 16; ++e) ga = fmaxf(ga, fabsf(v[e]));
@@ -434,8 +452,9 @@ __device__ __forceinline__ void adam_one(float &z, float &x, float &g_io, float 
 template <int MODE>
 __global__ void __launch_bounds__(kThreads)
 k_adamw(float *z, float *x, float *grad, float *m1, float *m2, float *amax, AdamScalars a,
-        uint32_t len) {
+        const float *d_grad_scale, uint32_t len) {
     __shared__ float warp_part[kThreads / 32];
+    if (d_grad_scale) a.grad_scale = __ldg(d_grad_scale);
     const int tid = threadIdx.x;
     const float decay = 1.0f - a.lr * a.wd;
     const bool aligned = ((reinterpret_cast<uintptr_t>(z) | reinterpret_cast<uintptr_t>(x) |
@@ -493,6 +512,70 @@ k_adamw(float *z, float *x, float *grad, float *m1, float *m2, float *amax, Adam
     }
 }
 
+// Global gradient-norm clip: per-chunk sums of squares, the scale, and the optional in-place
+// scaling (crates/cuda-kernels/src/gpt/optimizer/grad_clip/{sumsq,scale,apply}.rs).
+__global__ void __launch_bounds__(kThreads)
+k_grad_clip_sumsq(const uint64_t *chunk_ptrs, const uint32_t *chunk_lens, float *chunk_sums, uint32_t chunk_count) {
+    __shared__ float warp_part[kThreads / 32];
+    for (uint32_t c = blockIdx.x; c < chunk_count; c += gridDim.x) {
+        const float *p = reinterpret_cast<const float *>(chunk_ptrs[c]);
+        const uint32_t len = chunk_lens[c];
+        float local = 0.0f;
+        if ((reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+            for (uint32_t i = threadIdx.x * 4; i < len; i += kThreads * 4) {
+                if (i + 4 <= len) {
+                    float4 v = ld_stream(p + i);
+                    local += v.x * v.x; local += v.y * v.y; local += v.z * v.z; local += v.w * v.w;
+                } else {
+                    for (uint32_t j = i; j < len; ++j) local += p[j] * p[j];
+                }
+            }
+        } else {
+            for (uint32_t i = threadIdx.x; i < len; i += kThreads) local += p[i] * p[i];
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
+        if ((threadIdx.x & 31) == 0) warp_part[threadIdx.x >> 5] = local;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float sum = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kThreads / 32; ++w) sum += warp_part[w];
+            chunk_sums[c] = sum;
+        }
+        __syncthreads();
+    }
+}
+__global__ void __launch_bounds__(kThreads)
+k_grad_clip_scale(const float *chunk_sums, const float *extra_sums, float *scale, float *norm_out,
+                  uint32_t chunk_count, uint32_t extra_count, float max_norm) {
+    __shared__ double warp_part[kThreads / 32];
+    double local = 0.0;
+    for (uint32_t i = threadIdx.x; i < chunk_count; i += kThreads) local += (double)chunk_sums[i];
+    for (uint32_t i = threadIdx.x; i < extra_count; i += kThreads) local += (double)extra_sums[i];
+    local = warp_sum(local);
+    if ((threadIdx.x & 31) == 0) warp_part[threadIdx.x >> 5] = local;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double t = 0.0;
+#pragma unroll
+        for (int w = 0; w < kThreads / 32; ++w) t += warp_part[w];
+        const float norm = sqrtf((float)t);
+        scale[0] = norm > max_norm ? max_norm / (norm + 1.0e-6f) : 1.0f;  // grad_clip/scale.rs:38-43
+        norm_out[0] = norm;
+    }
+}
+__global__ void __launch_bounds__(kThreads)
+k_grad_clip_apply(const uint64_t *chunk_ptrs, const uint32_t *chunk_lens, const float *scale, uint32_t chunk_count) {
+    const float sc = scale[0];
+    if (sc == 1.0f) return;
+    for (uint32_t c = blockIdx.x; c < chunk_count; c += gridDim.x) {
+        float *p = reinterpret_cast<float *>(chunk_ptrs[c]);
+        const uint32_t len = chunk_lens[c];
+        for (uint32_t i = threadIdx.x; i < len; i += kThreads) p[i] *= sc;
+    }
+}
+
 // `zero_f32_pointer_table_kernel` (crates/cuda-kernels/src/gpt/optimizer/adam/mod.rs:18-26).
 __global__ void k_zero_pointer_table(const uint64_t *ptrs, uint32_t n) {
     uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -534,11 +617,11 @@ static inline int clamp_grid(uint32_t chunks, int cap) {
     return (int)(chunks < (uint32_t)cap ? chunks : (uint32_t)cap);
 }
 
-cudaError_t launch_muon_sumsq(const SlotView &v, float mu, float grad_scale, int nesterov,
-                              double *partials, float *amax_x, cudaStream_t s) {
+cudaError_t launch_muon_sumsq(const SlotView &v, float mu, float grad_scale, const float *d_grad_scale,
+                              int nesterov, double *partials, float *amax_x, cudaStream_t s) {
     if (v.total_chunks == 0) return cudaSuccess;
     k_muon_sumsq<<<clamp_grid(v.total_chunks, v.grid), kThreads, 0, s>>>(
-        v.slots, v.chunk_prefix, v.slot_count, v.total_chunks, mu, grad_scale, nesterov, partials, amax_x);
+        v.slots, v.chunk_prefix, v.slot_count, v.total_chunks, mu, grad_scale, d_grad_scale, nesterov, partials, amax_x);
     return cudaGetLastError();
 }
 cudaError_t launch_muon_inv_norm(const SlotView &v, const double *partials, float *inv_norm,
@@ -548,11 +631,11 @@ cudaError_t launch_muon_inv_norm(const SlotView &v, const double *partials, floa
     return cudaGetLastError();
 }
 cudaError_t launch_muon_momentum_normalize(const SlotView &v, float mu, float grad_scale,
-                                           int nesterov, const float *inv_norm,
+                                           const float *d_grad_scale, int nesterov, const float *inv_norm,
                                            const uint64_t *x0_ptrs, int f16, cudaStream_t s) {
     if (v.total_chunks == 0) return cudaSuccess;
     k_muon_momentum_normalize<<<clamp_grid(v.total_chunks, v.grid), kThreads, 0, s>>>(
-        v.slots, v.chunk_prefix, v.slot_count, v.total_chunks, mu, grad_scale, nesterov, inv_norm, x0_ptrs, f16);
+        v.slots, v.chunk_prefix, v.slot_count, v.total_chunks, mu, grad_scale, d_grad_scale, nesterov, inv_norm, x0_ptrs, f16);
     return cudaGetLastError();
 }
 cudaError_t launch_muon_update(const SlotView &v, const uint64_t *u_ptrs, float *amax_x, float lr,
@@ -608,11 +691,23 @@ cudaError_t launch_adamw(const b2_adamw_update_args &a, int mode, int grid_cap,
                    a.beta1_correction, a.beta2_correction, a.eps, a.average_coefficient, a.schedule_beta};
     int grid = clamp_grid(chunks, grid_cap);
     if (mode == 1)
-        k_adamw<1><<<grid, kThreads, 0, s>>>(a.z_master, a.x_master, a.grad, a.first_moment, a.second_moment, a.amax, sc, a.len);
+        k_adamw<1><<<grid, kThreads, 0, s>>>(a.z_master, a.x_master, a.grad, a.first_moment, a.second_moment, a.amax, sc, a.d_grad_scale, a.len);
     else if (mode == 2)
-        k_adamw<2><<<grid, kThreads, 0, s>>>(a.z_master, a.x_master, a.grad, a.first_moment, a.second_moment, a.amax, sc, a.len);
+        k_adamw<2><<<grid, kThreads, 0, s>>>(a.z_master, a.x_master, a.grad, a.first_moment, a.second_moment, a.amax, sc, a.d_grad_scale, a.len);
     else
-        k_adamw<0><<<grid, kThreads, 0, s>>>(a.z_master, a.x_master, a.grad, a.first_moment, a.second_moment, nullptr, sc, a.len);
+        k_adamw<0><<<grid, kThreads, 0, s>>>(a.z_master, a.x_master, a.grad, a.first_moment, a.second_moment, nullptr, sc, a.d_grad_scale, a.len);
+    return cudaGetLastError();
+}
+cudaError_t launch_grad_clip(const b2_gradient_clip_args &a, int grid_cap, cudaStream_t s) {
+    if (a.chunk_count) {
+        k_grad_clip_sumsq<<<clamp_grid(a.chunk_count, grid_cap), kThreads, 0, s>>>(a.chunk_ptrs, a.chunk_lens, a.chunk_sums, a.chunk_count);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+    }
+    k_grad_clip_scale<<<1, kThreads, 0, s>>>(a.chunk_sums, a.extra_sums, a.scale, a.norm, a.chunk_count, a.extra_sum_count, a.max_norm);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess || !a.apply || a.chunk_count == 0) return e;
+    k_grad_clip_apply<<<clamp_grid(a.chunk_count, grid_cap), kThreads, 0, s>>>(a.chunk_ptrs, a.chunk_lens, a.scale, a.chunk_count);
     return cudaGetLastError();
 }
 cudaError_t launch_zero_pointer_table(const uint64_t *ptrs, uint32_t n, cudaStream_t s) {

@@ -15,7 +15,7 @@ import numpy as np
 import torch
 
 from . import _ffi
-from ._ffi import (AdamWUpdateArgs as _CAdam, MuonOptions, MuonSlotDescriptor, MuonStepArgs, OPERAND_BF16,
+from ._ffi import (AdamWUpdateArgs as _CAdam, GradientClipArgs as _CClip, MuonOptions, MuonSlotDescriptor, MuonStepArgs, OPERAND_BF16,
                    OPERAND_F16, QUANTIZE_X, QUANTIZE_Y, SCALES_CSF, SCALES_RAW,
                    ScheduleFreeMaterializeArgs as _CSf, check)
 from .nvfp4 import Nvfp4QuantModule, zero_scales
@@ -89,6 +89,7 @@ class MuonMegaUpdateArgs:
     schedule_beta: float = 1.0
     nesterov: bool = True
     coefficients: Optional[np.ndarray] = None  # iterations x 3; None = reference table
+    grad_scale_device: Optional[torch.Tensor] = None  # f32[1] on the device; replaces grad_scale
 
     def c_args(self):
         co = None
@@ -98,7 +99,7 @@ class MuonMegaUpdateArgs:
             assert keep.size >= 3 * self.iterations
             co = keep.ctypes.data_as(C.POINTER(C.c_float))
         a = MuonStepArgs(self.mu, self.grad_scale, self.learning_rate, self.weight_decay, self.average_coefficient,
-                         self.schedule_beta, self.iterations, int(self.nesterov), co)
+                         self.schedule_beta, self.iterations, int(self.nesterov), co, _ptr(self.grad_scale_device))
         return a, keep
 
 
@@ -247,11 +248,11 @@ class OptimizerModule:
     def _adam_args(self, *, z_master, x_master, grad, grad_scale, first_moment, second_moment, len, learning_rate,
                    weight_decay, beta1, beta2, beta1_correction, beta2_correction, eps, average_coefficient,
                    schedule_beta=0.0, bytes=None, scales=None, global_scale=None, amax=None, chunk_amax=None,
-                   scale_layout=SCALES_CSF):
+                   scale_layout=SCALES_CSF, grad_scale_device=None):
         return _CAdam(_ptr(bytes), _ptr(scales), _ptr(global_scale), _ptr(z_master), _ptr(x_master), _ptr(grad),
                       grad_scale, scale_layout, _ptr(first_moment), _ptr(second_moment), _ptr(amax), _ptr(chunk_amax),
                       len, learning_rate, weight_decay, beta1, beta2, beta1_correction, beta2_correction, eps,
-                      average_coefficient, schedule_beta)
+                      average_coefficient, schedule_beta, _ptr(grad_scale_device))
 
     # launcher/adam.rs:9-21
     def apply_adamw_update(self, **kw) -> None:
@@ -268,6 +269,13 @@ class OptimizerModule:
     def apply_fp32_adamw_update(self, **kw) -> None:
         a = self._adam_args(**kw)
         check(self._lib.b2_apply_fp32_adamw_update(C.byref(a), _stream()), "apply_fp32_adamw_update")
+
+    # OptimizerModule::clip_gradients (args/grad_clip.rs:3-15)
+    def clip_gradients(self, *, chunk_ptrs, chunk_lens, chunk_sums, extra_sums, scale, norm, chunk_count,
+                       extra_sum_count, max_norm, apply) -> None:
+        a = _CClip(_ptr(chunk_ptrs), _ptr(chunk_lens), _ptr(chunk_sums), _ptr(extra_sums), _ptr(scale), _ptr(norm),
+                   chunk_count, extra_sum_count, max_norm, int(bool(apply)))
+        check(self._lib.b2_clip_gradients(C.byref(a), _stream()), "clip_gradients")
 
     # launcher/adam.rs:30-43
     def zero_f32_pointer_table(self, pointers: torch.Tensor, pointer_count: int) -> None:

@@ -727,6 +727,23 @@ uint64_t orc_muon_step(float *grad_inout_y, uint16_t *momentum, float *z, float 
     return orc_nvfp4_quantize(q, len, qa, p->contract, rcp, codes, raw_scales, global_scale);
 }
 
+/* Global gradient-norm clip: crates/cuda-kernels/src/gpt/optimizer/grad_clip/sumsq.rs:9-41
+ * (per-chunk sum of squares) and scale.rs:10-46 (norm and scale).  Sums are taken in double
+ * here; the reference sums in f32 in a grid-dependent order, so norm parity is a tolerance. */
+float orc_grad_clip(const float *const *chunks, const uint32_t *lens, uint32_t chunk_count,
+                    const float *extra_sums, uint32_t extra_count, float max_norm, float *norm_out) {
+    double t = 0.0;
+    for (uint32_t c = 0; c < chunk_count; ++c) {
+        double s = 0.0;
+        for (uint32_t i = 0; i < lens[c]; ++i) s += (double)chunks[c][i] * (double)chunks[c][i];
+        t += (double)(float)s;
+    }
+    for (uint32_t i = 0; i < extra_count; ++i) t += (double)extra_sums[i];
+    float norm = sqrtf((float)t);
+    if (norm_out) *norm_out = norm;
+    return norm > max_norm ? max_norm / (norm + 1.0e-6f) : 1.0f;
+}
+
 /* Host schedules: src/training/learning_rate/schedule.rs:24-65. */
 float orc_warmup_only(uint32_t step, uint32_t warmup_steps, float start_ratio) {
     if (step < 1) step = 1;

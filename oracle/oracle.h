@@ -78,6 +78,8 @@ uint64_t orc_muon_step(float *grad_inout_y, uint16_t *momentum, float *z, float 
                        uint8_t *codes, uint8_t *raw_scales, float *global_scale,
                        float *schedule_amax, float *U_out);
 
+float orc_grad_clip(const float *const *chunks, const uint32_t *lens, uint32_t chunk_count,
+                    const float *extra_sums, uint32_t extra_count, float max_norm, float *norm_out);
 float orc_warmup_only(uint32_t step, uint32_t warmup_steps, float start_ratio);
 float orc_schedule_free_beta(uint32_t step, uint32_t warmup_steps, float beta1, float rho);
 float orc_schedule_free_average_coefficient(uint32_t step, uint32_t warmup_steps, float start_ratio,

@@ -87,6 +87,8 @@ def lib() -> C.CDLL:
             "orc_polar_first_iteration_scalar": (C.c_float, [C.c_float, C.c_int, C.c_int]),
             "orc_polar_express_coefficients": (None, [C.c_int, f32p]),
             "orc_muon_step": (C.c_uint64, [f32p, u16p, f32p, f32p, C.c_uint32, C.c_uint32, C.POINTER(_MuonParams), C.POINTER(_RcpTable), u8p, u8p, f32p, f32p, f32p]),
+            "orc_grad_clip": (C.c_float, [C.POINTER(f32p), u32p, C.c_uint32, f32p, C.c_uint32, C.c_float, f32p]),
+            "orc_round_operand": (C.c_float, [C.c_float, C.c_int]),
             "orc_warmup_only": (C.c_float, [C.c_uint32, C.c_uint32, C.c_float]),
             "orc_schedule_free_beta": (C.c_float, [C.c_uint32, C.c_uint32, C.c_float, C.c_float]),
             "orc_schedule_free_average_coefficient": (C.c_float, [C.c_uint32, C.c_uint32, C.c_float, f32p]),
@@ -289,6 +291,18 @@ def adamw(z, x, grad, m1, m2, grad_scale, lr, wd, beta1, beta2, bc1, bc2, eps, c
                          _p(m2, C.c_float), z.size, f(grad_scale), f(lr), f(wd), f(beta1), f(beta2), f(bc1), f(bc2),
                          f(eps), f(c_avg), f(sched_beta), int(contract))
     return z, x, y, m1, m2, np.float32(am)
+
+
+def grad_clip(chunks, extra_sums, max_norm):
+    """-> (scale, norm) of the global gradient-norm clip over a list of f32 arrays."""
+    arrs = [_f32(c).reshape(-1) for c in chunks]
+    n = len(arrs)
+    ptrs = (C.POINTER(C.c_float) * max(n, 1))(*[_p(a, C.c_float) for a in arrs])
+    lens = (C.c_uint32 * max(n, 1))(*[a.size for a in arrs])
+    ex = _f32(extra_sums).reshape(-1) if extra_sums is not None and len(extra_sums) else np.zeros(0, np.float32)
+    norm = C.c_float(0)
+    sc = lib().orc_grad_clip(ptrs, lens, n, _p(ex, C.c_float) if ex.size else None, ex.size, np.float32(max_norm), C.byref(norm))
+    return np.float32(sc), np.float32(norm.value)
 
 
 @dataclass

@@ -275,3 +275,50 @@ def test_update_quantise_large_shape_properties():
     raw = o.csf_decode_matrix(host(s.scales), r, c)
     assert np.array_equal(raw, host(lits))
     plan.close()
+
+
+def test_grad_clip_reference_case_and_device_scale():
+    # crates/cuda-kernels/tests/optimizer/grad_clip.rs:9-44
+    opt = b2.OptimizerModule()
+    first = dev(np.array([3.0, 4.0, 0.0, 0.0], F))
+    second = dev(np.array([12.0, 0.0, 0.0, 0.0], F))
+    ptrs = torch.tensor([first.data_ptr(), second.data_ptr()], dtype=torch.int64, device="cuda")
+    lens = torch.tensor([4, 4], dtype=torch.int32, device="cuda")
+    sums, scale, norm = torch.zeros(2, device="cuda"), torch.zeros(1, device="cuda"), torch.zeros(1, device="cuda")
+    opt.clip_gradients(chunk_ptrs=ptrs, chunk_lens=lens, chunk_sums=sums, extra_sums=dev(np.array([27.0], F)),
+                       scale=scale, norm=norm, chunk_count=2, extra_sum_count=1, max_norm=7.0, apply=True)
+    torch.cuda.synchronize()
+    assert np.allclose(host(first), [1.5, 2.0, 0, 0], atol=1e-6) and np.allclose(host(second), [6.0, 0, 0, 0], atol=1e-6)
+    assert abs(host(scale)[0] - 0.5) <= 1e-6 and abs(host(norm)[0] - 14.0) <= 1e-6
+
+    # many ragged chunks against the oracle; then the step consumes the scale from device memory
+    rng = np.random.default_rng(9)
+    r, c = 192, 256
+    g = U.gradients(rng, r * c) * F(40.0)
+    gd = dev(g)
+    cuts = [0, 4096, 8192, 8195, 20000, r * c]
+    ptrs = torch.tensor([gd.data_ptr() + 4 * a for a in cuts[:-1]], dtype=torch.int64, device="cuda")
+    lens = torch.tensor([b - a for a, b in zip(cuts, cuts[1:])], dtype=torch.int32, device="cuda")
+    sums = torch.zeros(5, device="cuda")
+    opt.clip_gradients(chunk_ptrs=ptrs, chunk_lens=lens, chunk_sums=sums, extra_sums=None, scale=scale, norm=norm,
+                       chunk_count=5, extra_sum_count=0, max_norm=1.0, apply=False)
+    torch.cuda.synchronize()
+    want_scale, want_norm = o.grad_clip([g[a:b] for a, b in zip(cuts, cuts[1:])], None, 1.0)
+    assert want_scale < 1.0
+    assert abs(host(norm)[0] - want_norm) <= 1e-6 * want_norm and abs(host(scale)[0] - want_scale) <= 1e-6
+    assert np.array_equal(host(gd), g)  # apply = False leaves the gradients alone
+    sc = host(scale)[0]
+    results = []
+    for use_device in (False, True):
+        s = b2.MuonSlot.allocate(r, c)
+        _fill_slot(s, g, np.zeros(r * c, np.uint16), np.zeros(r * c, F), np.zeros(r * c, F))
+        plan = b2.MuonPlan([(r, c)])
+        args = b2.MuonMegaUpdateArgs(grad_scale=(123.0 if use_device else float(sc)),
+                                     grad_scale_device=(scale if use_device else None), iterations=1)
+        opt.muon_tma_prepare_polar(plan, b2.slot_table([s]), args)
+        torch.cuda.synchronize()
+        results.append((bf16_bits(s.momentum).copy(), host(plan.scratch(0, 0).float()).copy()))
+        plan.close()
+    assert np.array_equal(results[0][0], results[1][0]) and np.array_equal(results[0][1], results[1][1])
+    m2, _, _ = o.momentum(g, np.zeros(r * c, np.uint16), 0.95, sc)
+    assert np.array_equal(results[1][0].ravel(), m2)

@@ -183,3 +183,11 @@ def test_host_schedules():
     c2 = L.orc_schedule_free_average_coefficient(2, 5, F(0.05), C.byref(ws))
     w1, w2 = (0.05 + 0.95 * 0.2) ** 2, (0.05 + 0.95 * 0.4) ** 2
     assert abs(c2 - w2 / (w1 + w2)) < 1e-6
+
+
+def test_grad_clip_known_answer():
+    # crates/cuda-kernels/tests/optimizer/grad_clip.rs:9-44: norm 14 (with extra sum 27), max 7 -> 0.5
+    sc, norm = o.grad_clip([np.array([3.0, 4.0, 0.0, 0.0], F), np.array([12.0, 0.0, 0.0, 0.0], F)], [27.0], 7.0)
+    assert abs(norm - 14.0) <= 1e-6 and abs(sc - 0.5) <= 1e-6
+    sc, norm = o.grad_clip([np.array([0.3, 0.4], F)], None, 1.0)
+    assert sc == 1.0 and abs(norm - 0.5) <= 1e-6
