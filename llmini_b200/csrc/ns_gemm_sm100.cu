@@ -210,6 +210,7 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
           uint32_t *status, uint32_t debug_flags) {
     using C = Cfg<BN, PAIR>;
     const bool dbg_no_store = debug_flags & 1u;   // measurement only: drop every epilogue store
+    const bool dbg_no_global = debug_flags & 8u;  // measurement only: stage in shared memory but issue no global store
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *stage_base = smem;
@@ -403,7 +404,7 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
                     }
                     fence_async_smem();
                     __syncwarp();
-                    if (lane == 0) {
+                    if (lane == 0 && !dbg_no_global) {
                         tma_store_2d(map32, slab_u32, n0 + c0, slab_row0);
                         tma_store_commit();
                     }
@@ -424,14 +425,14 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
                     if ((epilogue == kEpiGram || epilogue == kEpiPoly) && !dbg_no_store) {
                         // fragment order: [128-row sub-tile][32-column unit][float4 index][row]
                         const size_t unit0 = ((size_t)tile_lin * (BN / 32) + (size_t)(c0 / 32)) * 8;
-                        if (epilogue == kEpiGram) {
+                        if (epilogue == kEpiGram && !dbg_no_global) {
                             float4 *fw = const_cast<float4 *>(frag);
 #pragma unroll
                             for (int j = 0; j < 16; ++j)
                                 __stcg(fw + (unit0 + j) * kGemmBlockM + row_in_tile,
                                        make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
                                                    __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3])));
-                        } else {
+                        } else if (epilogue == kEpiPoly) {
 #pragma unroll
                             for (int j = 0; j < 16; ++j) {
                                 const float gv[4] = {g[j].x, g[j].y, g[j].z, g[j].w};
@@ -465,7 +466,7 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
                     }
                     fence_async_smem();
                     __syncwarp();
-                    if (lane == 0) {
+                    if (lane == 0 && !dbg_no_global) {
                         tma_store_2d(map16, slab_u32, n0 + c0, slab_row0);
                         tma_store_commit();
                     }
@@ -483,7 +484,7 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
                         }
                         fence_async_smem();
                         __syncwarp();
-                        if (lane == 0) {
+                        if (lane == 0 && !dbg_no_global) {
                             tma_store_2d(map16t, slab_u32, slab_row0, n0 + c0);
                             tma_store_commit();
                         }
