@@ -259,10 +259,15 @@ def run_gpu(args):
                  first_moment=torch.zeros(vec, device=dev), second_moment=torch.zeros(vec, device=dev), len=vec)
         adam_sets.append(("fp32", t))
 
+    adam_table = adam_count = adam_chunks = None
+    if adam_sets:
+        # every AdamW tensor of the rank in one pointer table: three launches for all of them
+        adam_table, adam_count, adam_chunks = opt.adamw_table(
+            [dict(t, mode=2 if kind == "quant" else 0) for kind, t in adam_sets], dev)
     launches_per_step = 0
     if plan is not None:
         launches_per_step += 3 + 3 * HP["iterations"] + 2
-    launches_per_step += sum(2 if k == "quant" else 1 for k, _ in adam_sets)  # memsets are not counted
+    launches_per_step += 3 if adam_sets else 0
 
     stream = torch.cuda.current_stream()
     ev = lambda: torch.cuda.Event(enable_timing=True)
@@ -280,11 +285,8 @@ def run_gpu(args):
         if plan is not None:
             opt.muon_tma_finish_update(plan, table, margs)
         if record: marks[3].record(stream)
-        for kind, t in adam_sets:
-            if kind == "quant":
-                opt.apply_adamw_update(**ADAM, **t)
-            else:
-                opt.apply_fp32_adamw_update(**ADAM, **t)
+        if adam_sets:
+            opt.apply_adamw_update_multi(adam_table, adam_count, adam_chunks, **ADAM)
         if record: marks[4].record(stream)
         if world > 1:
             n = arena.bytes_per_rank

@@ -245,6 +245,31 @@ int b2_apply_adamw_update_deferred_quantization(const b2_adamw_update_args *args
 /* `OptimizerModule::apply_fp32_adamw_update` (.../launcher/adam.rs:45-72); uses z_master,
  * x_master, grad, grad_scale, the moments, len and the scalar hyper-parameters only. */
 int b2_apply_fp32_adamw_update(const b2_adamw_update_args *args, void *stream);
+/* Multi-tensor forms (no counterpart as a single call in the reference, which issues one to four
+ * launches per tensor: src/training/optimizer_apply/adam.rs:18-157,
+ * src/training/schedule_free/materialize.rs:44-91).  One device-resident table describes every
+ * AdamW tensor; three launches cover all of them.  mode: 0 = apply_fp32_adamw_update,
+ * 1 = apply_adamw_update_deferred_quantization (y into grad, max|y| into amax),
+ * 2 = apply_adamw_update (requantise x'; max|x'| into amax). */
+typedef struct b2_adamw_slot_descriptor {
+    uint64_t z_master, x_master, grad, first_moment, second_moment;
+    uint64_t amax;          /* f32[1]; modes 1 and 2 */
+    uint64_t bytes, scales, global_scale; /* mode 2 */
+    uint32_t len;
+    uint32_t chunk_begin;   /* filled by b2_adamw_table_prepare */
+    uint32_t mode;
+    uint32_t scale_layout;
+} b2_adamw_slot_descriptor;
+/* Fills chunk_begin of a HOST copy of the table (upload it afterwards); returns the chunk total. */
+int b2_adamw_table_prepare(b2_adamw_slot_descriptor *host_table, uint32_t count, uint32_t *total_chunks);
+/* Hyper-parameters are taken from `scalars` (pointer fields and len are ignored). */
+int b2_apply_adamw_update_multi(const b2_adamw_slot_descriptor *d_table, uint32_t count, uint32_t total_chunks,
+                                const b2_adamw_update_args *scalars, void *stream);
+/* `Materializer::muon_precomputed` for every matrix of the plan at once
+ * (src/training/schedule_free/tensor.rs:128-153): quantises the cached schedule-free values y
+ * (left in each slot's gradient buffer by the update) with the cached schedule_amax. */
+int b2_muon_materialize_training_weights(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_slots, void *stream);
+
 /* `OptimizerModule::zero_f32_pointer_table` (.../launcher/adam.rs:30-43). */
 int b2_zero_f32_pointer_table(const uint64_t *d_pointers, uint32_t pointer_count, void *stream);
 

@@ -61,6 +61,13 @@ class AdamWUpdateArgs(C.Structure):
                 ("average_coefficient", C.c_float), ("schedule_beta", C.c_float), ("d_grad_scale", C.c_void_p)]
 
 
+class AdamWSlotDescriptor(C.Structure):
+    _fields_ = [("z_master", C.c_uint64), ("x_master", C.c_uint64), ("grad", C.c_uint64),
+                ("first_moment", C.c_uint64), ("second_moment", C.c_uint64), ("amax", C.c_uint64),
+                ("bytes", C.c_uint64), ("scales", C.c_uint64), ("global_scale", C.c_uint64),
+                ("len", C.c_uint32), ("chunk_begin", C.c_uint32), ("mode", C.c_uint32), ("scale_layout", C.c_uint32)]
+
+
 class GradientClipArgs(C.Structure):
     _fields_ = [("chunk_ptrs", C.c_void_p), ("chunk_lens", C.c_void_p), ("chunk_sums", C.c_void_p),
                 ("extra_sums", C.c_void_p), ("scale", C.c_void_p), ("norm", C.c_void_p),
@@ -105,6 +112,9 @@ def _declare(L: C.CDLL) -> None:
         "b2_apply_fp32_adamw_update": (i, [C.POINTER(AdamWUpdateArgs), vp]),
         "b2_zero_f32_pointer_table": (i, [vp, u32, vp]),
         "b2_clip_gradients": (i, [C.POINTER(GradientClipArgs), vp]),
+        "b2_adamw_table_prepare": (i, [C.POINTER(AdamWSlotDescriptor), u32, u32p]),
+        "b2_apply_adamw_update_multi": (i, [vp, u32, u32, C.POINTER(AdamWUpdateArgs), vp]),
+        "b2_muon_materialize_training_weights": (i, [vp, vp, vp]),
         "b2_csf_encoded_len": (sz, [sz, sz]),
         "b2_csf_encode_host": (sz, [u8p, sz, sz, sz, u8p, sz]),
         "b2_csf_scale_at": (C.c_uint8, [u8p, sz]),

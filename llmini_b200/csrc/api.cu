@@ -657,6 +657,37 @@ int b2_apply_adamw_update_deferred_quantization(const b2_adamw_update_args *a, v
     if (e != cudaSuccess) return (int)e;
     return (int)launch_adamw(*a, 1, stream_grid_cap(d), as_stream(stream));
 }
+int b2_adamw_table_prepare(b2_adamw_slot_descriptor *t, uint32_t count, uint32_t *total_chunks) {
+    if ((!t && count) || !total_chunks) return B2_ERROR_INVALID_VALUE;
+    uint64_t chunks = 0;
+    for (uint32_t i = 0; i < count; ++i) {
+        if (t[i].mode > 2 || t[i].scale_layout > B2_SCALES_RAW) return B2_ERROR_INVALID_VALUE;
+        if (t[i].mode != 0 && (t[i].len % 16 != 0 || !t[i].amax)) return B2_ERROR_INVALID_VALUE;
+        if (t[i].mode == 2 && (!t[i].bytes || !t[i].scales || !t[i].global_scale)) return B2_ERROR_INVALID_VALUE;
+        if (t[i].mode == 2 && t[i].scale_layout == B2_SCALES_CSF && t[i].len % 128 != 0) return B2_ERROR_INVALID_VALUE;
+        if (t[i].len && (!t[i].z_master || !t[i].x_master || !t[i].grad || !t[i].first_moment || !t[i].second_moment))
+            return B2_ERROR_INVALID_VALUE;
+        t[i].chunk_begin = (uint32_t)chunks;
+        chunks += (t[i].len + kChunkHost - 1) / kChunkHost;
+        if (chunks > 0xffffffffull) return B2_ERROR_INVALID_VALUE;
+    }
+    *total_chunks = (uint32_t)chunks;
+    return B2_SUCCESS;
+}
+int b2_apply_adamw_update_multi(const b2_adamw_slot_descriptor *d_table, uint32_t count, uint32_t total_chunks,
+                                const b2_adamw_update_args *scalars, void *stream) {
+    if (!scalars || (!d_table && count)) return B2_ERROR_INVALID_VALUE;
+    DeviceInfo d;
+    cudaError_t e = device_info(d);
+    if (e != cudaSuccess) return (int)e;
+    return (int)launch_adamw_multi(d_table, count, total_chunks, *scalars, stream_grid_cap(d), as_stream(stream));
+}
+int b2_muon_materialize_training_weights(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_slots, void *stream) {
+    if (!plan || !d_slots) return B2_ERROR_INVALID_VALUE;
+    SlotView v = plan->view(d_slots);
+    return (int)launch_muon_encode(v, plan->at<float>(plan->layout.off_amax_x), 1, (int)plan->options.scale_layout,
+                                   as_stream(stream));
+}
 int b2_clip_gradients(const b2_gradient_clip_args *a, void *stream) {
     if (!a || !a->scale || !a->norm) return B2_ERROR_INVALID_VALUE;
     if (a->chunk_count && (!a->chunk_ptrs || !a->chunk_lens || !a->chunk_sums)) return B2_ERROR_INVALID_VALUE;

@@ -512,6 +512,103 @@ k_adamw(float *z, float *x, float *grad, float *m1, float *m2, float *amax, Adam
     }
 }
 
+// Multi-tensor AdamW: one table entry per tensor, chunks of all tensors in one flat list.
+__device__ __forceinline__ uint32_t find_adam_slot(const b2_adamw_slot_descriptor *t, uint32_t count, uint32_t c) {
+    uint32_t lo = 0, hi = count;
+    while (hi - lo > 1) {
+        uint32_t mid = (lo + hi) >> 1;
+        if (t[mid].chunk_begin <= c) lo = mid;
+        else hi = mid;
+    }
+    return lo;
+}
+__global__ void k_adamw_multi_reset(const b2_adamw_slot_descriptor *t, uint32_t count) {
+    uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < count && t[i].mode != 0 && t[i].len != 0) *reinterpret_cast<float *>(t[i].amax) = 0.0f;
+}
+__global__ void __launch_bounds__(kThreads)
+k_adamw_multi(const b2_adamw_slot_descriptor *t, uint32_t count, uint32_t total_chunks, AdamScalars a,
+              const float *d_grad_scale) {
+    __shared__ float warp_part[kThreads / 32];
+    const int tid = threadIdx.x;
+    if (d_grad_scale) a.grad_scale = __ldg(d_grad_scale);
+    const float decay = 1.0f - a.lr * a.wd;
+    for (uint32_t c = blockIdx.x; c < total_chunks; c += gridDim.x) {
+        const uint32_t slot = find_adam_slot(t, count, c);
+        const b2_adamw_slot_descriptor d = t[slot];
+        float *z = reinterpret_cast<float *>(d.z_master), *x = reinterpret_cast<float *>(d.x_master);
+        float *grad = reinterpret_cast<float *>(d.grad);
+        float *m1 = reinterpret_cast<float *>(d.first_moment), *m2 = reinterpret_cast<float *>(d.second_moment);
+        const uint32_t base = (c - d.chunk_begin) * kChunk;
+        float am = 0.0f;
+        const bool aligned = ((d.z_master | d.x_master | d.grad | d.first_moment | d.second_moment) & 15) == 0;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint32_t i = base + h * (kChunk / 2) + tid * 4;
+            if (aligned && i + 4 <= d.len) {
+                float4 zv = ld_stream(z + i), xv = ld_stream(x + i), gv = ld_stream(grad + i);
+                float4 av = ld_stream(m1 + i), bv = ld_stream(m2 + i);
+                float4 sv;
+                adam_one(zv.x, xv.x, gv.x, av.x, bv.x, a, decay, sv.x);
+                adam_one(zv.y, xv.y, gv.y, av.y, bv.y, a, decay, sv.y);
+                adam_one(zv.z, xv.z, gv.z, av.z, bv.z, a, decay, sv.z);
+                adam_one(zv.w, xv.w, gv.w, av.w, bv.w, a, decay, sv.w);
+                st_stream(z + i, zv);
+                *reinterpret_cast<float4 *>(x + i) = xv;
+                st_stream(m1 + i, av);
+                st_stream(m2 + i, bv);
+                if (d.mode == 1) {
+                    *reinterpret_cast<float4 *>(grad + i) = sv;
+                    am = fmaxf(am, fmaxf(fmaxf(fabsf(sv.x), fabsf(sv.y)), fmaxf(fabsf(sv.z), fabsf(sv.w))));
+                } else if (d.mode == 2) {
+                    am = fmaxf(am, fmaxf(fmaxf(fabsf(xv.x), fabsf(xv.y)), fmaxf(fabsf(xv.z), fabsf(xv.w))));
+                }
+            } else {
+                for (uint32_t j = i; j < d.len && j < i + 4; ++j) {
+                    float zz = z[j], xx = x[j], gg = grad[j], aa = m1[j], bb = m2[j], ss;
+                    adam_one(zz, xx, gg, aa, bb, a, decay, ss);
+                    z[j] = zz; x[j] = xx; m1[j] = aa; m2[j] = bb;
+                    if (d.mode == 1) {
+                        grad[j] = ss;
+                        am = fmaxf(am, fabsf(ss));
+                    } else if (d.mode == 2) {
+                        am = fmaxf(am, fabsf(xx));
+                    }
+                }
+            }
+        }
+        am = warp_max(am);
+        if ((tid & 31) == 0) warp_part[tid >> 5] = am;
+        __syncthreads();
+        if (tid == 0 && d.mode != 0) {
+            float r = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kThreads / 32; ++w) r = fmaxf(r, warp_part[w]);
+            atomic_max_nonneg(reinterpret_cast<float *>(d.amax), r);
+        }
+        __syncthreads();
+    }
+}
+__global__ void __launch_bounds__(kEncodeThreads)
+k_adamw_multi_encode(const b2_adamw_slot_descriptor *t, uint32_t count, uint32_t total_chunks) {
+    for (uint32_t c = blockIdx.x; c < total_chunks; c += gridDim.x) {
+        const uint32_t slot = find_adam_slot(t, count, c);
+        const b2_adamw_slot_descriptor d = t[slot];
+        if (d.mode != 2) continue;  // uniform per CTA iteration
+        const float gs = four_six_global_scale(*reinterpret_cast<const float *>(d.amax));
+        uint8_t *scales = reinterpret_cast<uint8_t *>(d.scales);
+        uint32_t k = 0, rows = 0;
+        if (d.scale_layout == B2_SCALES_CSF) {
+            k = reinterpret_cast<const uint32_t *>(scales)[0];
+            rows = reinterpret_cast<const uint32_t *>(scales)[1];
+        }
+        if (c == d.chunk_begin && threadIdx.x == 0) *reinterpret_cast<float *>(d.global_scale) = gs;
+        encode_chunk<0>(reinterpret_cast<const float *>(d.x_master), nullptr, nullptr, 0.f, d.len,
+                        (c - d.chunk_begin) * kChunk, gs, reinterpret_cast<uint8_t *>(d.bytes), scales,
+                        (int)d.scale_layout, k, rows);
+    }
+}
+
 // Global gradient-norm clip: per-chunk sums of squares, the scale, and the optional in-place
 // scaling (crates/cuda-kernels/src/gpt/optimizer/grad_clip/{sumsq,scale,apply}.rs).
 __global__ void __launch_bounds__(kThreads)
@@ -696,6 +793,16 @@ cudaError_t launch_adamw(const b2_adamw_update_args &a, int mode, int grid_cap,
         k_adamw<2><<<grid, kThreads, 0, s>>>(a.z_master, a.x_master, a.grad, a.first_moment, a.second_moment, a.amax, sc, a.d_grad_scale, a.len);
     else
         k_adamw<0><<<grid, kThreads, 0, s>>>(a.z_master, a.x_master, a.grad, a.first_moment, a.second_moment, nullptr, sc, a.d_grad_scale, a.len);
+    return cudaGetLastError();
+}
+cudaError_t launch_adamw_multi(const b2_adamw_slot_descriptor *table, uint32_t count, uint32_t total_chunks,
+                              const b2_adamw_update_args &a, int grid_cap, cudaStream_t s) {
+    if (count == 0 || total_chunks == 0) return cudaSuccess;
+    AdamScalars sc{a.grad_scale, a.learning_rate, a.weight_decay, a.beta1, a.beta2,
+                   a.beta1_correction, a.beta2_correction, a.eps, a.average_coefficient, a.schedule_beta};
+    k_adamw_multi_reset<<<(count + 255) / 256, 256, 0, s>>>(table, count);
+    k_adamw_multi<<<clamp_grid(total_chunks, grid_cap), kThreads, 0, s>>>(table, count, total_chunks, sc, a.d_grad_scale);
+    k_adamw_multi_encode<<<clamp_grid(total_chunks, 2 * grid_cap), kEncodeThreads, 0, s>>>(table, count, total_chunks);
     return cudaGetLastError();
 }
 cudaError_t launch_grad_clip(const b2_gradient_clip_args &a, int grid_cap, cudaStream_t s) {

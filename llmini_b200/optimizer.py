@@ -15,7 +15,7 @@ import numpy as np
 import torch
 
 from . import _ffi
-from ._ffi import (AdamWUpdateArgs as _CAdam, GradientClipArgs as _CClip, MuonOptions, MuonSlotDescriptor, MuonStepArgs, OPERAND_BF16,
+from ._ffi import (AdamWSlotDescriptor, AdamWUpdateArgs as _CAdam, GradientClipArgs as _CClip, MuonOptions, MuonSlotDescriptor, MuonStepArgs, OPERAND_BF16,
                    OPERAND_F16, QUANTIZE_X, QUANTIZE_Y, SCALES_CSF, SCALES_RAW,
                    ScheduleFreeMaterializeArgs as _CSf, check)
 from .nvfp4 import Nvfp4QuantModule, zero_scales
@@ -269,6 +269,31 @@ class OptimizerModule:
     def apply_fp32_adamw_update(self, **kw) -> None:
         a = self._adam_args(**kw)
         check(self._lib.b2_apply_fp32_adamw_update(C.byref(a), _stream()), "apply_fp32_adamw_update")
+
+    def adamw_table(self, tensors: Sequence[dict], device="cuda"):
+        """Builds the device table for `apply_adamw_update_multi` from dicts with the tensor fields
+        of `AdamWUpdateArgs` plus `mode` (0 fp32 only, 1 deferred, 2 requantise).
+        -> (device table tensor, count, total_chunks)."""
+        n = len(tensors)
+        arr = (AdamWSlotDescriptor * n)()
+        for d, t in zip(arr, tensors):
+            for k in ("z_master", "x_master", "grad", "first_moment", "second_moment", "amax", "bytes", "scales", "global_scale"):
+                setattr(d, k, _ptr(t.get(k)))
+            d.len, d.mode, d.scale_layout = t["len"], t.get("mode", 0), t.get("scale_layout", SCALES_CSF)
+        total = C.c_uint32(0)
+        check(self._lib.b2_adamw_table_prepare(arr, n, C.byref(total)), "adamw_table_prepare")
+        host = np.frombuffer(bytes(arr), dtype=np.uint8).copy()
+        return torch.from_numpy(host).to(device), n, int(total.value)
+
+    def apply_adamw_update_multi(self, table: torch.Tensor, count: int, total_chunks: int, **scalars) -> None:
+        a = self._adam_args(z_master=None, x_master=None, grad=None, first_moment=None, second_moment=None, len=0, **scalars)
+        check(self._lib.b2_apply_adamw_update_multi(_ptr(table), count, total_chunks, C.byref(a), _stream()),
+              "apply_adamw_update_multi")
+
+    # Materializer::muon_precomputed for all matrices (src/training/schedule_free/tensor.rs:128-153)
+    def muon_materialize_training_weights(self, plan: "MuonPlan", slots: torch.Tensor) -> None:
+        check(self._lib.b2_muon_materialize_training_weights(plan.handle, _ptr(slots), _stream()),
+              "muon_materialize_training_weights")
 
     # OptimizerModule::clip_gradients (args/grad_clip.rs:3-15)
     def clip_gradients(self, *, chunk_ptrs, chunk_lens, chunk_sums, extra_sums, scale, norm, chunk_count,

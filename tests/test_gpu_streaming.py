@@ -322,3 +322,76 @@ def test_grad_clip_reference_case_and_device_scale():
     assert np.array_equal(results[0][0], results[1][0]) and np.array_equal(results[0][1], results[1][1])
     m2, _, _ = o.momentum(g, np.zeros(r * c, np.uint16), 0.95, sc)
     assert np.array_equal(results[1][0].ravel(), m2)
+
+
+def test_multi_tensor_adamw_equals_per_tensor_calls():
+    rng = np.random.default_rng(31)
+    opt = b2.OptimizerModule()
+    specs = [(768, 0), (4099, 0), (16 * 301, 1), (128 * 40, 2), (2048 * 3, 2), (0, 0), (16, 1)]
+    hp = dict(grad_scale=0.7, learning_rate=2e-4, weight_decay=0.005, beta1=0.9, beta2=0.95, beta1_correction=0.19,
+              beta2_correction=0.0975, eps=1e-10, average_coefficient=0.5, schedule_beta=0.3)
+
+    def make(stale_amax):
+        rng2 = np.random.default_rng(5)
+        out = []
+        for n, mode in specs:
+            t = dict(z_master=dev(U.weights(rng2, n)), x_master=dev(U.weights(rng2, n)), grad=dev(U.gradients(rng2, n)),
+                     first_moment=dev(U.weights(rng2, n, 1e-3)), second_moment=dev(np.abs(U.weights(rng2, n, 1e-6))),
+                     len=n, mode=mode)
+            if mode:
+                t["amax"] = torch.full((1,), stale_amax, device="cuda")
+            if mode == 2:
+                q = b2.Nvfp4Tensor.empty(n // 128, 128)
+                t.update(bytes=q.bytes, scales=q.scales, global_scale=q.global_scale,
+                         chunk_amax=torch.zeros((n + 2047) // 2048, device="cuda"))
+            out.append(t)
+        return out
+
+    # the multi-tensor call clears the amax words itself; the per-tensor deferred call raises
+    # whatever the caller left there (the reference clears it with zero_f32_pointer_table)
+    a, b = make(7.0), make(0.0)
+    table, count, chunks = opt.adamw_table(a)
+    opt.apply_adamw_update_multi(table, count, chunks, **hp)
+    for t in b:
+        if t["len"] == 0:
+            continue
+        kw = {k: v for k, v in t.items() if k != "mode"}
+        if t["mode"] == 0:
+            opt.apply_fp32_adamw_update(**hp, **kw)
+        elif t["mode"] == 1:
+            opt.apply_adamw_update_deferred_quantization(**hp, **kw)
+        else:
+            opt.apply_adamw_update(**hp, **kw)
+    torch.cuda.synchronize()
+    for ta, tb in zip(a, b):
+        for key in ("z_master", "x_master", "grad", "first_moment", "second_moment", "amax", "bytes", "scales", "global_scale"):
+            if key in ta:
+                assert torch.equal(ta[key], tb[key]), (ta["len"], ta["mode"], key)
+
+
+def test_materialize_training_weights_for_all_slots():
+    # deferred finish, then one launch that quantises every slot's cached y with its schedule_amax
+    rng = np.random.default_rng(41)
+    shapes = [(128, 256), (384, 128)]
+    opt = b2.OptimizerModule()
+    slots = [b2.MuonSlot.allocate(r, c) for r, c in shapes]
+    plan = b2.MuonPlan(shapes)
+    for i, (s, (r, c)) in enumerate(zip(slots, shapes)):
+        _fill_slot(s, np.zeros(r * c, F), np.zeros(r * c, np.uint16), U.weights(rng, r * c), U.weights(rng, r * c))
+    table = b2.slot_table(slots)
+    args = b2.MuonMegaUpdateArgs(learning_rate=0.02, average_coefficient=0.5, schedule_beta=0.3)
+    opt.muon_tma_prepare_polar(plan, table, args)
+    for i, (r, c) in enumerate(shapes):
+        plan.scratch(i, 1).copy_(dev((rng.standard_normal(r * c) * 0.05).astype(F)).view(r, c))
+    opt.muon_tma_finish_update_deferred_quantization(plan, table, args)
+    opt.muon_materialize_training_weights(plan, table)
+    torch.cuda.synchronize()
+    for s, (r, c) in zip(slots, shapes):
+        y = host(s.grad).ravel()
+        am = host(s.schedule_amax)[0]
+        assert am == np.max(np.abs(y))
+        gs = host(s.global_scale)[0]
+        codes, raw, ogs, _ = o.nvfp4_quantize(y, amax=am, rcp_table=rcp_table(gs))
+        assert gs == ogs and np.array_equal(host(s.bytes), codes)
+        assert np.array_equal(host(s.scales), o.csf_encode(raw, r, c))
+    plan.close()
