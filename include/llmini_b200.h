@@ -44,7 +44,7 @@ extern "C" {
 typedef struct b2_muon_slot_descriptor {
     uint64_t grad;            /* f32 [rows][cols]; overwritten with y = z' + beta (x' - z') */
     uint64_t momentum;        /* bf16 [rows][cols] */
-    uint64_t variance;        /* unused on this path (Muon-VS) */
+    uint64_t variance;        /* bf16 [rows][cols]; read and written only with variance_adaptive */
     uint64_t second_momentum; /* unused on this path (NorMuon) */
     uint64_t z_master;        /* f32 */
     uint64_t x_master;        /* f32 */
@@ -56,7 +56,8 @@ typedef struct b2_muon_slot_descriptor {
     uint32_t rows;
     uint32_t cols;
     float learning_rate_multiplier;
-    uint32_t qk_clip_factor_offset; /* must be UINT32_MAX (qk-clip is outside this path) */
+    uint32_t qk_clip_factor_offset; /* UINT32_MAX = no qk-clip; else index of this slot's first head
+                                       in b2_muon_step_args.d_qk_clip_factors */
     uint32_t qk_clip_head_dim;
     uint32_t reserved_padding;
 } b2_muon_slot_descriptor;
@@ -96,6 +97,13 @@ typedef struct b2_muon_step_args {
     const float *d_grad_scale;  /* optional DEVICE pointer to the clip scale written by
                                    b2_clip_gradients; when non-NULL it replaces `grad_scale`, so
                                    the step needs no host read-back of the gradient norm */
+    uint32_t variance_adaptive; /* Muon-VS (.../muon/fused/momentum.rs:72-158): slots carry a bf16
+                                   `variance` buffer; `MuonTmaPrepareArgs::variance_adaptive` */
+    float bias_correction_inv;  /* `MuonTmaPrepareArgs::bias_correction_inv`; used with Muon-VS */
+    const float *d_qk_clip_factors; /* optional DEVICE table of per-head factors (`qk_clip_factors` of
+                                   `MuonTmaFinishArgs`): slots whose qk_clip_factor_offset is not
+                                   UINT32_MAX scale z', x', momentum (and variance) of their query/key
+                                   rows (row < 2*cols, head = (row % cols) / qk_clip_head_dim) */
 } b2_muon_step_args;
 
 typedef struct b2_muon_plan b2_muon_plan;
@@ -138,6 +146,12 @@ int b2_muon_finish_update(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_s
 int b2_muon_finish_update_deferred_quantization(b2_muon_plan *plan,
                                                 const b2_muon_slot_descriptor *d_slots,
                                                 const b2_muon_step_args *args, void *stream);
+/* `OptimizerModule::muon_tma_sign_update_deferred_quantization` (.../launcher/muon_mega.rs:229-283;
+ * device code .../muon/fused/update/one.rs:88-167) for every slot of the plan: momentum (and
+ * variance) update, z' = z (1 - lr wd) - lr sign(m'), x', y into the gradient buffer, both amax
+ * words.  No Newton-Schulz, no quantisation. */
+int b2_muon_sign_update_deferred_quantization(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_slots,
+                                              const b2_muon_step_args *args, void *stream);
 /* Scratch views for tests and tracing (the reference's `MUON_TMA_TRACE`,
  * src/training/optimizer_muon/tma.rs:1210-1276).  which: 0 = X0 (16-bit, [rows][cols]),
  * 1 = Newton-Schulz result U (f32, [rows][cols]), 2 = inverse norm (f32[1]),

@@ -427,6 +427,27 @@ static int check_step(const b2_muon_plan *plan, const b2_muon_step_args *a) {
     return B2_SUCCESS;
 }
 
+static MomentumParams momentum_params(const b2_muon_step_args *a) {
+    MomentumParams mp;
+    mp.mu = a->mu;
+    mp.grad_scale = a->grad_scale;
+    mp.d_grad_scale = a->d_grad_scale;
+    mp.nesterov = (int)a->nesterov;
+    mp.variance_adaptive = a->variance_adaptive ? 1 : 0;
+    mp.bias_correction_inv = a->variance_adaptive ? a->bias_correction_inv : 1.0f;
+    return mp;
+}
+static UpdateParams update_params(const b2_muon_step_args *a) {
+    UpdateParams up;
+    up.lr = a->learning_rate;
+    up.wd = a->weight_decay;
+    up.c_avg = a->average_coefficient;
+    up.beta = a->schedule_beta;
+    up.d_qk_clip_factors = a->d_qk_clip_factors;
+    up.variance_adaptive = a->variance_adaptive ? 1 : 0;
+    return up;
+}
+
 int b2_muon_prepare_polar(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_slots, const b2_muon_step_args *a,
                           void *stream) {
     if (!plan || !a || !d_slots) return B2_ERROR_INVALID_VALUE;
@@ -435,12 +456,11 @@ int b2_muon_prepare_polar(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_s
     SlotView v = plan->view(d_slots);
     double *partials = plan->at<double>(L.off_partials);
     float *inv = plan->at<float>(L.off_inv_norm);
-    cudaError_t e = launch_muon_sumsq(v, a->mu, a->grad_scale, a->d_grad_scale, (int)a->nesterov, partials,
-                                      plan->at<float>(L.off_amax_x), s);
+    const MomentumParams mp = momentum_params(a);
+    cudaError_t e = launch_muon_sumsq(v, mp, partials, plan->at<float>(L.off_amax_x), s);
     if (e == cudaSuccess) e = launch_muon_inv_norm(v, partials, inv, s);
     if (e == cudaSuccess)
-        e = launch_muon_momentum_normalize(v, a->mu, a->grad_scale, a->d_grad_scale, (int)a->nesterov, inv,
-                                           plan->at<uint64_t>(L.off_x0_ptrs),
+        e = launch_muon_momentum_normalize(v, mp, inv, plan->at<uint64_t>(L.off_x0_ptrs),
                                            plan->options.operand_format == B2_OPERAND_F16, s);
     return (int)e;
 }
@@ -490,8 +510,7 @@ static int finish_impl(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_slot
     cudaStream_t s = as_stream(stream);
     SlotView v = plan->view(d_slots);
     float *amax_x = plan->at<float>(L.off_amax_x);
-    cudaError_t e = launch_muon_update(v, plan->at<uint64_t>(L.off_u_ptrs), amax_x, a->learning_rate, a->weight_decay,
-                                       a->average_coefficient, a->schedule_beta, s);
+    cudaError_t e = launch_muon_update(v, plan->at<uint64_t>(L.off_u_ptrs), amax_x, update_params(a), s);
     if (e == cudaSuccess && quantize)
         e = launch_muon_encode(v, amax_x, plan->options.quantize_target == B2_QUANTIZE_Y,
                                (int)plan->options.scale_layout, s);
@@ -504,6 +523,14 @@ int b2_muon_finish_update(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_s
 int b2_muon_finish_update_deferred_quantization(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_slots,
                                                 const b2_muon_step_args *a, void *stream) {
     return finish_impl(plan, d_slots, a, false, stream);
+}
+
+int b2_muon_sign_update_deferred_quantization(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_slots,
+                                              const b2_muon_step_args *a, void *stream) {
+    if (!plan || !a || !d_slots) return B2_ERROR_INVALID_VALUE;
+    SlotView v = plan->view(d_slots);
+    return (int)launch_muon_sign_update(v, momentum_params(a), update_params(a),
+                                        plan->at<float>(plan->layout.off_amax_x), as_stream(stream));
 }
 
 int b2_muon_mega_update(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_slots, const b2_muon_step_args *a,

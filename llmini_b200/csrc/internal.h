@@ -18,15 +18,27 @@ struct SlotView {
     int grid;                              // CTAs to launch (multiple of the SM count)
 };
 
-cudaError_t launch_muon_sumsq(const SlotView &v, float mu, float grad_scale, const float *d_grad_scale,
-                              int nesterov, double *partials, float *amax_x, cudaStream_t s);
+struct MomentumParams {
+    float mu, grad_scale;
+    const float *d_grad_scale;
+    int nesterov, variance_adaptive;
+    float bias_correction_inv;
+};
+struct UpdateParams {
+    float lr, wd, c_avg, beta;
+    const float *d_qk_clip_factors;
+    int variance_adaptive;
+};
+cudaError_t launch_muon_sumsq(const SlotView &v, const MomentumParams &mp, double *partials, float *amax_x,
+                              cudaStream_t s);
 cudaError_t launch_muon_inv_norm(const SlotView &v, const double *partials, float *inv_norm,
                                  cudaStream_t s);
-cudaError_t launch_muon_momentum_normalize(const SlotView &v, float mu, float grad_scale,
-                                           const float *d_grad_scale, int nesterov, const float *inv_norm,
+cudaError_t launch_muon_momentum_normalize(const SlotView &v, const MomentumParams &mp, const float *inv_norm,
                                            const uint64_t *x0_ptrs, int f16, cudaStream_t s);
-cudaError_t launch_muon_update(const SlotView &v, const uint64_t *u_ptrs, float *amax_x, float lr,
-                               float wd, float c_avg, float beta, cudaStream_t s);
+cudaError_t launch_muon_update(const SlotView &v, const uint64_t *u_ptrs, float *amax_x, const UpdateParams &up,
+                               cudaStream_t s);
+cudaError_t launch_muon_sign_update(const SlotView &v, const MomentumParams &mp, const UpdateParams &up,
+                                    float *amax_x, cudaStream_t s);
 cudaError_t launch_muon_encode(const SlotView &v, const float *amax_x, int quantize_y,
                                int scale_layout, cudaStream_t s);
 

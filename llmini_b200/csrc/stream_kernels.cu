@@ -23,6 +23,63 @@ __device__ __forceinline__ float momentum_update(float graw, float pm, float mu,
     return nesterov ? mu * next_m + omg : next_m;
 }
 
+// Same stage with the variance-adaptive branch (Muon-VS, momentum.rs:86-133); `next_v` is the
+// new variance state.  Operation order follows the reference expression by expression.
+__device__ __forceinline__ float momentum_update_vs(float graw, float pm, float pv, float mu, float grad_scale,
+                                                    int nesterov, float bias_correction_inv, float &next_m,
+                                                    float &next_v) {
+    const float g = graw * grad_scale;
+    const float one_minus_mu = 1.0f - mu;
+    const float variance_factor = mu * one_minus_mu;
+    next_m = mu * pm + one_minus_mu * g;
+    const float innovation = pm - g;
+    next_v = mu * pv + variance_factor * innovation * innovation;
+    const float corrected = next_m * bias_correction_inv;
+    const float numerator = nesterov ? g + (mu / one_minus_mu) * corrected : corrected;
+    return numerator / (sqrtf(fmaxf(next_v * bias_correction_inv, 0.0f)) + 1.0e-8f);
+}
+// Four consecutive elements of stage M in either variant.
+struct Quad { float u[4], m[4], v[4]; };
+__device__ __forceinline__ Quad momentum_quad(const float *grad, const uint16_t *mom, const uint16_t *var, uint32_t i,
+                                              const MomentumParams &mp, bool streaming) {
+    Quad q;
+    const float4 g = streaming ? __ldcs(reinterpret_cast<const float4 *>(grad + i))
+                               : *reinterpret_cast<const float4 *>(grad + i);
+    const uint2 m = *reinterpret_cast<const uint2 *>(mom + i);
+    const float gr[4] = {g.x, g.y, g.z, g.w};
+    const float pm[4] = {bf16_bits_to_f32(m.x & 0xffffu), bf16_bits_to_f32(m.x >> 16),
+                         bf16_bits_to_f32(m.y & 0xffffu), bf16_bits_to_f32(m.y >> 16)};
+    if (mp.variance_adaptive) {
+        const uint2 v = *reinterpret_cast<const uint2 *>(var + i);
+        const float pv[4] = {bf16_bits_to_f32(v.x & 0xffffu), bf16_bits_to_f32(v.x >> 16),
+                             bf16_bits_to_f32(v.y & 0xffffu), bf16_bits_to_f32(v.y >> 16)};
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+            q.u[e] = momentum_update_vs(gr[e], pm[e], pv[e], mp.mu, mp.grad_scale, mp.nesterov,
+                                        mp.bias_correction_inv, q.m[e], q.v[e]);
+    } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            q.u[e] = momentum_update(gr[e], pm[e], mp.mu, mp.grad_scale, mp.nesterov, q.m[e]);
+            q.v[e] = 0.0f;
+        }
+    }
+    return q;
+}
+__device__ __forceinline__ uint2 pack_bf16x4(const float *v) {
+    uint2 o;
+    o.x = f32_to_bf16_bits(v[0]) | (f32_to_bf16_bits(v[1]) << 16);
+    o.y = f32_to_bf16_bits(v[2]) | (f32_to_bf16_bits(v[3]) << 16);
+    return o;
+}
+// Per-head qk-clip factor of element `i` (update.rs:58-66; one row of `cols` values per chunk there).
+__device__ __forceinline__ float qk_clip_factor(const b2_muon_slot_descriptor &d, const float *factors, uint32_t i) {
+    if (factors == nullptr || d.qk_clip_factor_offset == 0xffffffffu || d.qk_clip_head_dim == 0) return 1.0f;
+    const uint32_t row = i / d.cols;
+    if (row >= 2u * d.cols) return 1.0f;
+    return __ldg(factors + d.qk_clip_factor_offset + (row % d.cols) / d.qk_clip_head_dim);
+}
+
 struct ChunkCtx {
     uint32_t slot;
     uint32_t local_chunk;
@@ -45,34 +102,26 @@ __device__ __forceinline__ ChunkCtx chunk_ctx(const b2_muon_slot_descriptor *slo
 // words the update kernel later raises with atomicMax.
 __global__ void __launch_bounds__(kThreads)
 k_muon_sumsq(const b2_muon_slot_descriptor *slots, const uint32_t *prefix, uint32_t slot_count,
-             uint32_t total_chunks, float mu, float grad_scale, const float *d_grad_scale, int nesterov,
-             double *partials, float *amax_x) {
+             uint32_t total_chunks, MomentumParams mp, double *partials, float *amax_x) {
     __shared__ double warp_part[kThreads / 32];
     const int tid = threadIdx.x;
-    if (d_grad_scale) grad_scale = __ldg(d_grad_scale);
+    if (mp.d_grad_scale) mp.grad_scale = __ldg(mp.d_grad_scale);
     for (uint32_t c = blockIdx.x; c < total_chunks; c += gridDim.x) {
         ChunkCtx cx = chunk_ctx(slots, prefix, slot_count, c);
         const float *grad = reinterpret_cast<const float *>(cx.d.grad);
         const uint16_t *mom = reinterpret_cast<const uint16_t *>(cx.d.momentum);
+        const uint16_t *var = reinterpret_cast<const uint16_t *>(cx.d.variance);
         const uint32_t base = cx.local_chunk * kChunk;
         float local = 0.0f;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             uint32_t i = base + h * (kChunk / 2) + tid * 4;
             if (i < cx.len) {
-                float4 g = *reinterpret_cast<const float4 *>(grad + i);
-                uint2 m = *reinterpret_cast<const uint2 *>(mom + i);
-                float nm;
-                float u0 = momentum_update(g.x, bf16_bits_to_f32(m.x & 0xffffu), mu, grad_scale, nesterov, nm);
-                float u1 = momentum_update(g.y, bf16_bits_to_f32(m.x >> 16), mu, grad_scale, nesterov, nm);
-                float u2 = momentum_update(g.z, bf16_bits_to_f32(m.y & 0xffffu), mu, grad_scale, nesterov, nm);
-                float u3 = momentum_update(g.w, bf16_bits_to_f32(m.y >> 16), mu, grad_scale, nesterov, nm);
+                const Quad q = momentum_quad(grad, mom, var, i, mp, false);
                 // per-thread chain as in the reference (momentum.rs:63: fma(update, update, sum));
                 // eight terms at most, so the chain's rounding stays below 1e-7 relative
-                local = fmaf(u0, u0, local);
-                local = fmaf(u1, u1, local);
-                local = fmaf(u2, u2, local);
-                local = fmaf(u3, u3, local);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) local = fmaf(q.u[e], q.u[e], local);
             }
         }
         double acc = warp_sum((double)local);
@@ -119,15 +168,15 @@ k_muon_inv_norm(const uint32_t *prefix, const double *partials, float *inv_norm)
 // .../polar/fused/stage.rs:51-55).  No transpose: the GEMMs read either orientation.
 __global__ void __launch_bounds__(kThreads)
 k_muon_momentum_normalize(const b2_muon_slot_descriptor *slots, const uint32_t *prefix,
-                          uint32_t slot_count, uint32_t total_chunks, float mu, float grad_scale,
-                          const float *d_grad_scale, int nesterov, const float *inv_norm,
-                          const uint64_t *x0_ptrs, int f16) {
+                          uint32_t slot_count, uint32_t total_chunks, MomentumParams mp,
+                          const float *inv_norm, const uint64_t *x0_ptrs, int f16) {
     const int tid = threadIdx.x;
-    if (d_grad_scale) grad_scale = __ldg(d_grad_scale);
+    if (mp.d_grad_scale) mp.grad_scale = __ldg(mp.d_grad_scale);
     for (uint32_t c = blockIdx.x; c < total_chunks; c += gridDim.x) {
         ChunkCtx cx = chunk_ctx(slots, prefix, slot_count, c);
         const float *grad = reinterpret_cast<const float *>(cx.d.grad);
         uint16_t *mom = reinterpret_cast<uint16_t *>(cx.d.momentum);
+        uint16_t *var = reinterpret_cast<uint16_t *>(cx.d.variance);
         uint16_t *x0 = reinterpret_cast<uint16_t *>(x0_ptrs[cx.slot]);
         const float inv = inv_norm[cx.slot];
         const uint32_t base = cx.local_chunk * kChunk;
@@ -135,20 +184,12 @@ k_muon_momentum_normalize(const b2_muon_slot_descriptor *slots, const uint32_t *
         for (int h = 0; h < 2; ++h) {
             uint32_t i = base + h * (kChunk / 2) + tid * 4;
             if (i < cx.len) {
-                float4 g = __ldcs(reinterpret_cast<const float4 *>(grad + i));
-                uint2 m = *reinterpret_cast<const uint2 *>(mom + i);
-                float n0, n1, n2, n3;
-                float u0 = momentum_update(g.x, bf16_bits_to_f32(m.x & 0xffffu), mu, grad_scale, nesterov, n0);
-                float u1 = momentum_update(g.y, bf16_bits_to_f32(m.x >> 16), mu, grad_scale, nesterov, n1);
-                float u2 = momentum_update(g.z, bf16_bits_to_f32(m.y & 0xffffu), mu, grad_scale, nesterov, n2);
-                float u3 = momentum_update(g.w, bf16_bits_to_f32(m.y >> 16), mu, grad_scale, nesterov, n3);
-                uint2 mo;
-                mo.x = f32_to_bf16_bits(n0) | (f32_to_bf16_bits(n1) << 16);
-                mo.y = f32_to_bf16_bits(n2) | (f32_to_bf16_bits(n3) << 16);
-                *reinterpret_cast<uint2 *>(mom + i) = mo;
+                const Quad q = momentum_quad(grad, mom, var, i, mp, true);
+                *reinterpret_cast<uint2 *>(mom + i) = pack_bf16x4(q.m);
+                if (mp.variance_adaptive) *reinterpret_cast<uint2 *>(var + i) = pack_bf16x4(q.v);
                 uint2 xo;
-                xo.x = pack_operands(u0 * inv, u1 * inv, f16);
-                xo.y = pack_operands(u2 * inv, u3 * inv, f16);
+                xo.x = pack_operands(q.u[0] * inv, q.u[1] * inv, f16);
+                xo.y = pack_operands(q.u[2] * inv, q.u[3] * inv, f16);
                 *reinterpret_cast<uint2 *>(x0 + i) = xo;
             }
         }
@@ -160,9 +201,9 @@ k_muon_momentum_normalize(const b2_muon_slot_descriptor *slots, const uint32_t *
 // U is in the storage layout, so every access is a coalesced 128-bit one.
 __global__ void __launch_bounds__(kThreads)
 k_muon_update(const b2_muon_slot_descriptor *slots, const uint32_t *prefix, uint32_t slot_count,
-              uint32_t total_chunks, const uint64_t *u_ptrs, float *amax_x, float lr, float wd,
-              float c_avg, float beta) {
+              uint32_t total_chunks, const uint64_t *u_ptrs, float *amax_x, UpdateParams up) {
     __shared__ float warp_ax[kThreads / 32], warp_ay[kThreads / 32];
+    const float lr = up.lr, wd = up.wd, c_avg = up.c_avg, beta = up.beta;
     const int tid = threadIdx.x;
     for (uint32_t c = blockIdx.x; c < total_chunks; c += gridDim.x) {
         ChunkCtx cx = chunk_ctx(slots, prefix, slot_count, c);
@@ -186,11 +227,31 @@ k_muon_update(const b2_muon_slot_descriptor *slots, const uint32_t *prefix, uint
                 float zz[4] = {zv.x, zv.y, zv.z, zv.w};
                 float xx[4] = {xv.x, xv.y, xv.z, xv.w};
                 float yy[4];
+                // the four elements share a row (cols % 16 == 0), hence one clip factor
+                const float clip = qk_clip_factor(cx.d, up.d_qk_clip_factors, i);
+                if (clip != 1.0f) {  // one.rs:63-72: momentum (and variance) follow the clipped weights
+                    uint16_t *mom = reinterpret_cast<uint16_t *>(cx.d.momentum);
+                    const uint2 m = *reinterpret_cast<const uint2 *>(mom + i);
+                    const float cm[4] = {bf16_bits_to_f32(m.x & 0xffffu) * clip, bf16_bits_to_f32(m.x >> 16) * clip,
+                                         bf16_bits_to_f32(m.y & 0xffffu) * clip, bf16_bits_to_f32(m.y >> 16) * clip};
+                    *reinterpret_cast<uint2 *>(mom + i) = pack_bf16x4(cm);
+                    if (cx.d.variance != 0) {
+                        uint16_t *var = reinterpret_cast<uint16_t *>(cx.d.variance);
+                        const uint2 v = *reinterpret_cast<const uint2 *>(var + i);
+                        const float cv[4] = {bf16_bits_to_f32(v.x & 0xffffu) * clip * clip, bf16_bits_to_f32(v.x >> 16) * clip * clip,
+                                             bf16_bits_to_f32(v.y & 0xffffu) * clip * clip, bf16_bits_to_f32(v.y >> 16) * clip * clip};
+                        *reinterpret_cast<uint2 *>(var + i) = pack_bf16x4(cv);
+                    }
+                }
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     float upd = scale * (uu[e] * 1.0f * 1.0f);
                     float nz = zz[e] * decay - lr_s * upd;
                     float nx = xx[e] + c_avg * (nz - xx[e]);
+                    if (clip != 1.0f) {
+                        nz *= clip;
+                        nx *= clip;
+                    }
                     float sv = nz + beta * (nx - nz);
                     zz[e] = nz;
                     xx[e] = nx;
@@ -202,6 +263,105 @@ k_muon_update(const b2_muon_slot_descriptor *slots, const uint32_t *prefix, uint
                 // x' is read again by the encode kernel: keep it cacheable
                 *reinterpret_cast<float4 *>(x + i) = make_float4(xx[0], xx[1], xx[2], xx[3]);
                 *reinterpret_cast<float4 *>(y + i) = make_float4(yy[0], yy[1], yy[2], yy[3]);
+            }
+        }
+        ax = warp_max(ax);
+        ay = warp_max(ay);
+        if ((tid & 31) == 0) {
+            warp_ax[tid >> 5] = ax;
+            warp_ay[tid >> 5] = ay;
+        }
+        __syncthreads();
+        if (tid == 0) {
+            float mx = 0.0f, my = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kThreads / 32; ++w) {
+                mx = fmaxf(mx, warp_ax[w]);
+                my = fmaxf(my, warp_ay[w]);
+            }
+            atomic_max_nonneg(amax_x + cx.slot, mx);
+            atomic_max_nonneg(reinterpret_cast<float *>(cx.d.schedule_amax), my);
+        }
+        __syncthreads();
+    }
+}
+
+// Clears the two amax words of every slot (the prepare stage does this on the Newton-Schulz path).
+__global__ void k_muon_reset_amax(const b2_muon_slot_descriptor *slots, uint32_t slot_count, float *amax_x) {
+    uint32_t s = blockIdx.x * blockDim.x + threadIdx.x;
+    if (s < slot_count && slots[s].rows * slots[s].cols != 0) {
+        amax_x[s] = 0.0f;
+        *reinterpret_cast<float *>(slots[s].schedule_amax) = 0.0f;
+    }
+}
+
+// sign-Muon: crates/cuda-kernels/src/gpt/optimizer/muon/fused/update/one.rs:88-167
+// (update_one_sign / update_sign_pair): the direction is sign(m'), no orthogonalisation.
+__global__ void __launch_bounds__(kThreads)
+k_muon_sign_update(const b2_muon_slot_descriptor *slots, const uint32_t *prefix, uint32_t slot_count,
+                   uint32_t total_chunks, MomentumParams mp, UpdateParams up, float *amax_x) {
+    __shared__ float warp_ax[kThreads / 32], warp_ay[kThreads / 32];
+    const int tid = threadIdx.x;
+    if (mp.d_grad_scale) mp.grad_scale = __ldg(mp.d_grad_scale);
+    for (uint32_t c = blockIdx.x; c < total_chunks; c += gridDim.x) {
+        ChunkCtx cx = chunk_ctx(slots, prefix, slot_count, c);
+        float *grad = reinterpret_cast<float *>(cx.d.grad);
+        uint16_t *mom = reinterpret_cast<uint16_t *>(cx.d.momentum);
+        uint16_t *var = reinterpret_cast<uint16_t *>(cx.d.variance);
+        float *z = reinterpret_cast<float *>(cx.d.z_master);
+        float *x = reinterpret_cast<float *>(cx.d.x_master);
+        const float lr_s = up.lr * cx.d.learning_rate_multiplier;
+        const float decay = 1.0f - lr_s * up.wd;
+        const float one_minus_mu = 1.0f - mp.mu;
+        const uint32_t base = cx.local_chunk * kChunk;
+        float ax = 0.0f, ay = 0.0f;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            uint32_t i = base + h * (kChunk / 2) + tid * 4;
+            if (i < cx.len) {
+                const float4 gv = ld_stream(grad + i);
+                const uint2 mb = *reinterpret_cast<const uint2 *>(mom + i);
+                const float4 zv = ld_stream(z + i), xv = ld_stream(x + i);
+                const float gr[4] = {gv.x, gv.y, gv.z, gv.w};
+                const float pm[4] = {bf16_bits_to_f32(mb.x & 0xffffu), bf16_bits_to_f32(mb.x >> 16),
+                                     bf16_bits_to_f32(mb.y & 0xffffu), bf16_bits_to_f32(mb.y >> 16)};
+                float pv[4] = {0.f, 0.f, 0.f, 0.f};
+                if (mp.variance_adaptive) {
+                    const uint2 vb = *reinterpret_cast<const uint2 *>(var + i);
+                    pv[0] = bf16_bits_to_f32(vb.x & 0xffffu); pv[1] = bf16_bits_to_f32(vb.x >> 16);
+                    pv[2] = bf16_bits_to_f32(vb.y & 0xffffu); pv[3] = bf16_bits_to_f32(vb.y >> 16);
+                }
+                float zz[4] = {zv.x, zv.y, zv.z, zv.w}, xx[4] = {xv.x, xv.y, xv.z, xv.w};
+                float nm[4], nv[4], yy[4];
+                const float clip = qk_clip_factor(cx.d, up.d_qk_clip_factors, i);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float g = gr[e] * mp.grad_scale;
+                    nm[e] = mp.mu * pm[e] + one_minus_mu * g;
+                    nv[e] = 0.0f;
+                    if (mp.variance_adaptive) {
+                        const float innovation = pm[e] - g;
+                        nv[e] = mp.mu * pv[e] + (mp.mu * one_minus_mu) * innovation * innovation;
+                    }
+                    const float dir = nm[e] > 0.0f ? 1.0f : (nm[e] < 0.0f ? -1.0f : 0.0f);
+                    float nz = zz[e] * decay - lr_s * dir;
+                    float nx = xx[e] + up.c_avg * (nz - xx[e]);
+                    if (clip != 1.0f) {
+                        nz *= clip;
+                        nx *= clip;
+                        nm[e] *= clip;
+                        if (mp.variance_adaptive) nv[e] *= clip * clip;
+                    }
+                    const float sv = nz + up.beta * (nx - nz);
+                    zz[e] = nz; xx[e] = nx; yy[e] = sv;
+                    ax = fmaxf(ax, fabsf(nx));
+                    ay = fmaxf(ay, fabsf(sv));
+                }
+                if (mp.variance_adaptive) *reinterpret_cast<uint2 *>(var + i) = pack_bf16x4(nv);
+                *reinterpret_cast<uint2 *>(mom + i) = pack_bf16x4(nm);
+                st_stream(z + i, make_float4(zz[0], zz[1], zz[2], zz[3]));
+                *reinterpret_cast<float4 *>(x + i) = make_float4(xx[0], xx[1], xx[2], xx[3]);
+                *reinterpret_cast<float4 *>(grad + i) = make_float4(yy[0], yy[1], yy[2], yy[3]);
             }
         }
         ax = warp_max(ax);
@@ -714,11 +874,11 @@ static inline int clamp_grid(uint32_t chunks, int cap) {
     return (int)(chunks < (uint32_t)cap ? chunks : (uint32_t)cap);
 }
 
-cudaError_t launch_muon_sumsq(const SlotView &v, float mu, float grad_scale, const float *d_grad_scale,
-                              int nesterov, double *partials, float *amax_x, cudaStream_t s) {
+cudaError_t launch_muon_sumsq(const SlotView &v, const MomentumParams &mp, double *partials, float *amax_x,
+                              cudaStream_t s) {
     if (v.total_chunks == 0) return cudaSuccess;
     k_muon_sumsq<<<clamp_grid(v.total_chunks, v.grid), kThreads, 0, s>>>(
-        v.slots, v.chunk_prefix, v.slot_count, v.total_chunks, mu, grad_scale, d_grad_scale, nesterov, partials, amax_x);
+        v.slots, v.chunk_prefix, v.slot_count, v.total_chunks, mp, partials, amax_x);
     return cudaGetLastError();
 }
 cudaError_t launch_muon_inv_norm(const SlotView &v, const double *partials, float *inv_norm,
@@ -727,19 +887,26 @@ cudaError_t launch_muon_inv_norm(const SlotView &v, const double *partials, floa
     k_muon_inv_norm<<<v.slot_count, kThreads, 0, s>>>(v.chunk_prefix, partials, inv_norm);
     return cudaGetLastError();
 }
-cudaError_t launch_muon_momentum_normalize(const SlotView &v, float mu, float grad_scale,
-                                           const float *d_grad_scale, int nesterov, const float *inv_norm,
+cudaError_t launch_muon_momentum_normalize(const SlotView &v, const MomentumParams &mp, const float *inv_norm,
                                            const uint64_t *x0_ptrs, int f16, cudaStream_t s) {
     if (v.total_chunks == 0) return cudaSuccess;
     k_muon_momentum_normalize<<<clamp_grid(v.total_chunks, v.grid), kThreads, 0, s>>>(
-        v.slots, v.chunk_prefix, v.slot_count, v.total_chunks, mu, grad_scale, d_grad_scale, nesterov, inv_norm, x0_ptrs, f16);
+        v.slots, v.chunk_prefix, v.slot_count, v.total_chunks, mp, inv_norm, x0_ptrs, f16);
     return cudaGetLastError();
 }
-cudaError_t launch_muon_update(const SlotView &v, const uint64_t *u_ptrs, float *amax_x, float lr,
-                               float wd, float c_avg, float beta, cudaStream_t s) {
+cudaError_t launch_muon_update(const SlotView &v, const uint64_t *u_ptrs, float *amax_x, const UpdateParams &up,
+                               cudaStream_t s) {
     if (v.total_chunks == 0) return cudaSuccess;
     k_muon_update<<<clamp_grid(v.total_chunks, v.grid), kThreads, 0, s>>>(
-        v.slots, v.chunk_prefix, v.slot_count, v.total_chunks, u_ptrs, amax_x, lr, wd, c_avg, beta);
+        v.slots, v.chunk_prefix, v.slot_count, v.total_chunks, u_ptrs, amax_x, up);
+    return cudaGetLastError();
+}
+cudaError_t launch_muon_sign_update(const SlotView &v, const MomentumParams &mp, const UpdateParams &up,
+                                    float *amax_x, cudaStream_t s) {
+    if (v.total_chunks == 0) return cudaSuccess;
+    k_muon_reset_amax<<<(v.slot_count + 255) / 256, 256, 0, s>>>(v.slots, v.slot_count, amax_x);
+    k_muon_sign_update<<<clamp_grid(v.total_chunks, v.grid), kThreads, 0, s>>>(
+        v.slots, v.chunk_prefix, v.slot_count, v.total_chunks, mp, up, amax_x);
     return cudaGetLastError();
 }
 cudaError_t launch_muon_encode(const SlotView &v, const float *amax_x, int quantize_y,

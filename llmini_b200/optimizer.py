@@ -48,6 +48,9 @@ class MuonSlot:
     rows: int
     cols: int
     learning_rate_multiplier: float = 1.0
+    variance: Optional[torch.Tensor] = None  # bf16 [rows, cols], Muon-VS only
+    qk_clip_factor_offset: int = U32_MAX
+    qk_clip_head_dim: int = 0
 
     @staticmethod
     def allocate(rows: int, cols: int, scale_layout: int = SCALES_CSF, device="cuda") -> "MuonSlot":
@@ -65,9 +68,10 @@ class MuonSlot:
                         torch.zeros(max(n // 2, 1), dtype=torch.uint8, device=device), scales, z(1), rows, cols)
 
     def descriptor(self) -> MuonSlotDescriptor:
-        return MuonSlotDescriptor(_ptr(self.grad), _ptr(self.momentum), 0, 0, _ptr(self.z_master), _ptr(self.x_master),
-                                  _ptr(self.schedule_amax), _ptr(self.bytes), _ptr(self.scales), _ptr(self.global_scale),
-                                  self.rows, self.cols, self.learning_rate_multiplier, U32_MAX, 0, 0)
+        return MuonSlotDescriptor(_ptr(self.grad), _ptr(self.momentum), _ptr(self.variance), 0, _ptr(self.z_master),
+                                  _ptr(self.x_master), _ptr(self.schedule_amax), _ptr(self.bytes), _ptr(self.scales),
+                                  _ptr(self.global_scale), self.rows, self.cols, self.learning_rate_multiplier,
+                                  self.qk_clip_factor_offset, self.qk_clip_head_dim, 0)
 
 
 def slot_table(slots: Sequence[MuonSlot], device="cuda") -> torch.Tensor:
@@ -90,6 +94,9 @@ class MuonMegaUpdateArgs:
     nesterov: bool = True
     coefficients: Optional[np.ndarray] = None  # iterations x 3; None = reference table
     grad_scale_device: Optional[torch.Tensor] = None  # f32[1] on the device; replaces grad_scale
+    variance_adaptive: bool = False                    # Muon-VS; slots need a `variance` buffer
+    bias_correction_inv: float = 1.0
+    qk_clip_factors: Optional[torch.Tensor] = None     # f32 per-head factors on the device
 
     def c_args(self):
         co = None
@@ -99,7 +106,8 @@ class MuonMegaUpdateArgs:
             assert keep.size >= 3 * self.iterations
             co = keep.ctypes.data_as(C.POINTER(C.c_float))
         a = MuonStepArgs(self.mu, self.grad_scale, self.learning_rate, self.weight_decay, self.average_coefficient,
-                         self.schedule_beta, self.iterations, int(self.nesterov), co, _ptr(self.grad_scale_device))
+                         self.schedule_beta, self.iterations, int(self.nesterov), co, _ptr(self.grad_scale_device),
+                         int(self.variance_adaptive), self.bias_correction_inv, _ptr(self.qk_clip_factors))
         return a, keep
 
 
@@ -209,6 +217,14 @@ class OptimizerModule:
         a, keep = args.c_args()
         check(self._lib.b2_muon_finish_update_deferred_quantization(plan.handle, _ptr(slots), C.byref(a), _stream()),
               "muon_finish_update_deferred_quantization")
+        del keep
+
+    # launcher/muon_mega.rs:229-283
+    def muon_tma_sign_update_deferred_quantization(self, plan: MuonPlan, slots: torch.Tensor,
+                                                   args: MuonMegaUpdateArgs) -> None:
+        a, keep = args.c_args()
+        check(self._lib.b2_muon_sign_update_deferred_quantization(plan.handle, _ptr(slots), C.byref(a), _stream()),
+              "muon_sign_update_deferred_quantization")
         del keep
 
     # launcher/mod.rs:67-95

@@ -419,6 +419,136 @@ double orc_momentum(const float *grad, uint16_t *momentum_bf16, float *u_out, ui
     return s;
 }
 
+/* Stage M, variance-adaptive branch (Muon-VS):
+ * crates/cuda-kernels/src/gpt/optimizer/muon/fused/momentum.rs:72-158. */
+double orc_momentum_vs(const float *grad, uint16_t *momentum_bf16, uint16_t *variance_bf16, float *u_out,
+                       uint64_t len, float mu, float grad_scale, int nesterov, float bias_correction_inv) {
+    double s = 0.0;
+    volatile float one_minus_mu = 1.0f - mu;
+    volatile float variance_factor = mu * one_minus_mu;
+    volatile float nesterov_factor = mu / one_minus_mu;
+    for (uint64_t i = 0; i < len; ++i) {
+        volatile float g = grad[i] * grad_scale;
+        float pm = orc_bf16_bits_to_f32(momentum_bf16[i]);
+        float pv = orc_bf16_bits_to_f32(variance_bf16[i]);
+        volatile float a = mu * pm, b = one_minus_mu * g;
+        float nm = a + b;
+        volatile float innovation = pm - g;
+        volatile float c0 = mu * pv, c1 = variance_factor * innovation;
+        volatile float c2 = c1 * innovation;
+        float nv = c0 + c2;
+        volatile float corrected = nm * bias_correction_inv;
+        float numerator;
+        if (nesterov) { volatile float t = nesterov_factor * corrected; numerator = g + t; }
+        else numerator = corrected;
+        volatile float vb = nv * bias_correction_inv;
+        float root = sqrtf(vb > 0.0f ? vb : 0.0f);
+        float u = numerator / (root + 1.0e-8f);
+        momentum_bf16[i] = orc_f32_to_bf16_bits(nm);
+        variance_bf16[i] = orc_f32_to_bf16_bits(nv);
+        u_out[i] = u;
+        s += (double)u * (double)u;
+    }
+    return s;
+}
+
+static float qk_factor(const float *factors, uint32_t offset, uint32_t head_dim, uint32_t rows, uint32_t cols,
+                       uint64_t index) {
+    /* update.rs:58-66 with cols == one chunk: rows below 2*cols are query/key rows, one factor per head */
+    (void)rows;
+    if (!factors || offset == 0xffffffffu || head_dim == 0) return 1.0f;
+    uint64_t row = index / cols;
+    if (row >= 2ull * cols) return 1.0f;
+    return factors[offset + (uint32_t)((row % cols) / head_dim)];
+}
+
+/* Stage U with qk-clip: crates/cuda-kernels/src/gpt/optimizer/muon/fused/update/one.rs:46-85.
+ * momentum (and variance when given) are rescaled for clipped rows. */
+void orc_update_clip(const float *U, float *z, float *x, float *y, uint16_t *momentum_bf16, uint16_t *variance_bf16,
+                     uint64_t len, uint32_t rows, uint32_t cols, float lr, float wd, float c_avg, float beta,
+                     const float *factors, uint32_t offset, uint32_t head_dim, float *amax) {
+    float fr = (float)rows, fc = (float)cols;
+    float scale = 0.2f * sqrtf(fr > fc ? fr : fc);
+    volatile float lw = lr * wd;
+    float decay = 1.0f - lw;
+    float ax = 0.0f, ay = 0.0f;
+    for (uint64_t i = 0; i < len; ++i) {
+        volatile float upd = scale * U[i];
+        volatile float p1 = z[i] * decay, p2 = lr * upd;
+        volatile float nz = p1 - p2;
+        volatile float d1 = nz - x[i];
+        volatile float p3 = c_avg * d1;
+        volatile float nx = x[i] + p3;
+        float f = qk_factor(factors, offset, head_dim, rows, cols, i);
+        if (f != 1.0f) {
+            nz = nz * f;
+            nx = nx * f;
+            volatile float cm = orc_bf16_bits_to_f32(momentum_bf16[i]) * f;
+            momentum_bf16[i] = orc_f32_to_bf16_bits(cm);
+            if (variance_bf16) {
+                volatile float cv = orc_bf16_bits_to_f32(variance_bf16[i]) * f;
+                volatile float cv2 = cv * f;
+                variance_bf16[i] = orc_f32_to_bf16_bits(cv2);
+            }
+        }
+        volatile float d2 = nx - nz;
+        volatile float p4 = beta * d2;
+        float yy = nz + p4;
+        z[i] = nz; x[i] = nx;
+        if (y) y[i] = yy;
+        if (fabsf(nx) > ax) ax = fabsf(nx);
+        if (fabsf(yy) > ay) ay = fabsf(yy);
+    }
+    amax[0] = ax; amax[1] = ay;
+}
+
+/* sign-Muon: crates/cuda-kernels/src/gpt/optimizer/muon/fused/update/one.rs:88-167 (update_one_sign). */
+void orc_sign_update(float *grad_inout_y, uint16_t *momentum_bf16, uint16_t *variance_bf16, float *z, float *x,
+                     uint64_t len, uint32_t rows, uint32_t cols, float mu, float grad_scale, int variance_adaptive,
+                     float lr, float wd, float c_avg, float beta, const float *factors, uint32_t offset,
+                     uint32_t head_dim, float *amax) {
+    volatile float one_minus_mu = 1.0f - mu;
+    volatile float lw = lr * wd;
+    float decay = 1.0f - lw;
+    float ax = 0.0f, ay = 0.0f;
+    for (uint64_t i = 0; i < len; ++i) {
+        volatile float g = grad_inout_y[i] * grad_scale;
+        float pm = orc_bf16_bits_to_f32(momentum_bf16[i]);
+        volatile float a = mu * pm, b = one_minus_mu * g;
+        volatile float nm = a + b;
+        volatile float nv = 0.0f;
+        if (variance_adaptive) {
+            volatile float innovation = pm - g;
+            volatile float c0 = mu * orc_bf16_bits_to_f32(variance_bf16[i]);
+            volatile float vf = mu * one_minus_mu;
+            volatile float c1 = vf * innovation;
+            volatile float c2 = c1 * innovation;
+            nv = c0 + c2;
+        }
+        float dir = nm > 0.0f ? 1.0f : (nm < 0.0f ? -1.0f : 0.0f);
+        volatile float p1 = z[i] * decay, p2 = lr * dir;
+        volatile float nz = p1 - p2;
+        volatile float d1 = nz - x[i];
+        volatile float p3 = c_avg * d1;
+        volatile float nx = x[i] + p3;
+        volatile float cm = nm;
+        float f = qk_factor(factors, offset, head_dim, rows, cols, i);
+        if (f != 1.0f) {
+            nz = nz * f; nx = nx * f; cm = cm * f;
+            if (variance_adaptive) { volatile float ff = f * f; nv = nv * ff; }
+        }
+        if (variance_adaptive) variance_bf16[i] = orc_f32_to_bf16_bits(nv);
+        momentum_bf16[i] = orc_f32_to_bf16_bits(cm);
+        volatile float d2 = nx - nz;
+        volatile float p4 = beta * d2;
+        float yy = nz + p4;
+        z[i] = nz; x[i] = nx; grad_inout_y[i] = yy;
+        if (fabsf(nx) > ax) ax = fabsf(nx);
+        if (fabsf(yy) > ay) ay = fabsf(yy);
+    }
+    amax[0] = ax; amax[1] = ay;
+}
+
 /* Stage N scalar: crates/cuda-kernels/src/gpt/optimizer/muon/polar/fused/normalize.rs:8-9,82-86. */
 float orc_inv_norm(float sumsq, int contract) {
     float r = sqrtf(sumsq);

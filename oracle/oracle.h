@@ -59,6 +59,15 @@ uint8_t orc_csf_scale_at(const uint8_t *s, uint64_t g);
 double orc_momentum(const float *grad, uint16_t *momentum_bf16, float *u_out, uint64_t len,
                     float mu, float grad_scale, int nesterov, int contract);
 float orc_inv_norm(float sumsq, int contract);
+double orc_momentum_vs(const float *grad, uint16_t *momentum_bf16, uint16_t *variance_bf16, float *u_out,
+                       uint64_t len, float mu, float grad_scale, int nesterov, float bias_correction_inv);
+void orc_update_clip(const float *U, float *z, float *x, float *y, uint16_t *momentum_bf16, uint16_t *variance_bf16,
+                     uint64_t len, uint32_t rows, uint32_t cols, float lr, float wd, float c_avg, float beta,
+                     const float *factors, uint32_t offset, uint32_t head_dim, float *amax);
+void orc_sign_update(float *grad_inout_y, uint16_t *momentum_bf16, uint16_t *variance_bf16, float *z, float *x,
+                     uint64_t len, uint32_t rows, uint32_t cols, float mu, float grad_scale, int variance_adaptive,
+                     float lr, float wd, float c_avg, float beta, const float *factors, uint32_t offset,
+                     uint32_t head_dim, float *amax);
 void orc_polar_gram(float *X, int n, int m, int iterations, const float *coeffs, int round_mode);
 void orc_polar_gram_tall(float *Y, int m, int n, int iterations, const float *coeffs, int round_mode);
 void orc_polar_three_product(float *X, int n, int m, int iterations, const float *coeffs,

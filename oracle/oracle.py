@@ -78,6 +78,9 @@ def lib() -> C.CDLL:
             "orc_csf_scale_at": (C.c_uint8, [u8p, C.c_uint64]),
             "orc_momentum": (C.c_double, [f32p, u16p, f32p, C.c_uint64, C.c_float, C.c_float, C.c_int, C.c_int]),
             "orc_inv_norm": (C.c_float, [C.c_float, C.c_int]),
+            "orc_momentum_vs": (C.c_double, [f32p, u16p, u16p, f32p, C.c_uint64, C.c_float, C.c_float, C.c_int, C.c_float]),
+            "orc_update_clip": (None, [f32p, f32p, f32p, f32p, u16p, u16p, C.c_uint64, C.c_uint32, C.c_uint32] + [C.c_float] * 4 + [f32p, C.c_uint32, C.c_uint32, f32p]),
+            "orc_sign_update": (None, [f32p, u16p, u16p, f32p, f32p, C.c_uint64, C.c_uint32, C.c_uint32, C.c_float, C.c_float, C.c_int] + [C.c_float] * 4 + [f32p, C.c_uint32, C.c_uint32, f32p]),
             "orc_polar_gram": (None, [f32p, C.c_int, C.c_int, C.c_int, f32p, C.c_int]),
             "orc_polar_gram_tall": (None, [f32p, C.c_int, C.c_int, C.c_int, f32p, C.c_int]),
             "orc_polar_three_product": (None, [f32p, C.c_int, C.c_int, C.c_int, f32p, C.c_int]),
@@ -233,6 +236,46 @@ def momentum(grad, momentum_bits, mu, grad_scale, nesterov=True, contract=False)
     s = lib().orc_momentum(_p(g, C.c_float), _p(m, C.c_uint16), _p(u, C.c_float), g.size,
                            np.float32(mu), np.float32(grad_scale), int(nesterov), int(contract))
     return m, u, float(s)
+
+
+def momentum_vs(grad, momentum_bits, variance_bits, mu, grad_scale, nesterov, bias_correction_inv):
+    """Muon-VS branch -> (momentum' bits, variance' bits, u, sumsq)."""
+    g = _f32(grad).reshape(-1)
+    m = np.ascontiguousarray(momentum_bits, dtype=np.uint16).reshape(-1).copy()
+    v = np.ascontiguousarray(variance_bits, dtype=np.uint16).reshape(-1).copy()
+    u = np.zeros_like(g)
+    s = lib().orc_momentum_vs(_p(g, C.c_float), _p(m, C.c_uint16), _p(v, C.c_uint16), _p(u, C.c_float), g.size,
+                              np.float32(mu), np.float32(grad_scale), int(nesterov), np.float32(bias_correction_inv))
+    return m, v, u, float(s)
+
+
+def update_clip(U, z, x, momentum_bits, variance_bits, rows, cols, lr, wd, c_avg, beta, factors, offset, head_dim):
+    """Stage U with qk-clip -> (z', x', y, momentum bits, variance bits or None, amax_x, amax_y)."""
+    U = _f32(U).reshape(-1); z = _f32(z).reshape(-1).copy(); x = _f32(x).reshape(-1).copy()
+    y = np.zeros_like(z); am = np.zeros(2, np.float32)
+    m = np.ascontiguousarray(momentum_bits, dtype=np.uint16).reshape(-1).copy()
+    v = None if variance_bits is None else np.ascontiguousarray(variance_bits, dtype=np.uint16).reshape(-1).copy()
+    fa = _f32(factors).reshape(-1)
+    f = np.float32
+    lib().orc_update_clip(_p(U, C.c_float), _p(z, C.c_float), _p(x, C.c_float), _p(y, C.c_float), _p(m, C.c_uint16),
+                          None if v is None else _p(v, C.c_uint16), z.size, rows, cols, f(lr), f(wd), f(c_avg), f(beta),
+                          _p(fa, C.c_float), offset, head_dim, _p(am, C.c_float))
+    return z, x, y, m, v, am[0], am[1]
+
+
+def sign_update(grad, momentum_bits, variance_bits, z, x, rows, cols, mu, grad_scale, variance_adaptive, lr, wd, c_avg,
+                beta, factors=None, offset=0xFFFFFFFF, head_dim=0):
+    """sign-Muon -> (y, momentum bits, variance bits, z', x', amax_x, amax_y)."""
+    g = _f32(grad).reshape(-1).copy(); z = _f32(z).reshape(-1).copy(); x = _f32(x).reshape(-1).copy()
+    m = np.ascontiguousarray(momentum_bits, dtype=np.uint16).reshape(-1).copy()
+    v = np.ascontiguousarray(variance_bits if variance_bits is not None else np.zeros(g.size, np.uint16), dtype=np.uint16).reshape(-1).copy()
+    am = np.zeros(2, np.float32)
+    fa = None if factors is None else _f32(factors).reshape(-1)
+    f = np.float32
+    lib().orc_sign_update(_p(g, C.c_float), _p(m, C.c_uint16), _p(v, C.c_uint16), _p(z, C.c_float), _p(x, C.c_float),
+                          g.size, rows, cols, f(mu), f(grad_scale), int(variance_adaptive), f(lr), f(wd), f(c_avg),
+                          f(beta), None if fa is None else _p(fa, C.c_float), offset, head_dim, _p(am, C.c_float))
+    return g, m, v, z, x, am[0], am[1]
 
 
 def inv_norm(sumsq, contract=False) -> np.float32:

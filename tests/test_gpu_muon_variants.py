@@ -1,0 +1,166 @@
+"""Muon variants on the GPU through the plan entry points: variance-adaptive momentum (Muon-VS),
+qk-clip inside the update stage, and sign-Muon; each against the oracle and against the
+reference's own test recurrences."""
+import numpy as np
+import pytest
+import torch
+
+import llmini_b200 as b2
+from oracle import oracle as o
+from tests import _util as U
+from tests.gpu_util import bf16_bits, bf16_from_bits, dev, host
+
+pytestmark = pytest.mark.gpu
+F = np.float32
+
+
+def _slot(rows, cols, grad, mom_bits, z, x, var_bits=None):
+    s = b2.MuonSlot.allocate(rows, cols, b2.SCALES_RAW)
+    s.grad.copy_(dev(grad).view_as(s.grad))
+    s.momentum.copy_(bf16_from_bits(mom_bits).view_as(s.momentum))
+    s.z_master.copy_(dev(z).view_as(s.z_master))
+    s.x_master.copy_(dev(x).view_as(s.x_master))
+    if var_bits is not None:
+        s.variance = bf16_from_bits(var_bits).view(rows, cols).contiguous()
+    return s
+
+
+def _powi(base, n):
+    r = F(1.0)
+    for _ in range(n):
+        r = F(r * base)
+    return r
+
+
+@pytest.mark.parametrize("rows,cols", [(64, 128), (128, 64)])
+@pytest.mark.parametrize("nesterov", [True, False])
+def test_muon_vs_prepare_reference_case(rows, cols, nesterov):
+    # crates/cuda-kernels/tests/optimizer/muon/tma_prepare.rs:87-208, variance_adaptive = true:
+    # six chained steps; BF16 states bit-exact, normalised direction against the oracle
+    n = rows * cols
+    i = np.arange(n)
+    grad = ((i * 73 % 257).astype(F) - F(128.0)) / F(211.0)
+    m_bits = o.bf16_bits(((i * 29 % 131).astype(F) - F(65.0)) / F(173.0))
+    v_bits = o.bf16_bits(F(0.01) + (i * 17 % 97).astype(F) / F(503.0))
+    slot = _slot(rows, cols, grad, m_bits, np.zeros(n, F), np.zeros(n, F), v_bits)
+    plan = b2.MuonPlan([(rows, cols)], scale_layout=b2.SCALES_RAW)
+    table = b2.slot_table([slot])
+    opt = b2.OptimizerModule()
+    for step in range(3, 9):
+        bci = F(1.0) / (F(1.0) - _powi(F(0.9), step))
+        args = b2.MuonMegaUpdateArgs(mu=0.9, grad_scale=0.125, iterations=1, nesterov=nesterov,
+                                     variance_adaptive=True, bias_correction_inv=float(bci))
+        opt.muon_tma_prepare_polar(plan, table, args)
+        torch.cuda.synchronize()
+        m_bits, v_bits, u, ss = o.momentum_vs(grad, m_bits, v_bits, 0.9, 0.125, nesterov, bci)
+        assert np.array_equal(bf16_bits(slot.momentum).ravel(), m_bits)
+        assert np.array_equal(bf16_bits(slot.variance).ravel(), v_bits)
+        inv = o.inv_norm(ss)
+        got_inv = host(plan.scratch(0, 2))[0]
+        assert abs(got_inv - inv) <= 1e-6 * inv
+        x0 = host(plan.scratch(0, 0).float()).ravel()
+        # sqrt/div are IEEE on both sides; allow one operand ulp for the odd last-bit difference
+        want = u * got_inv
+        assert np.max(np.abs(x0 - want)) <= np.max(np.abs(want)) * 2.0 ** -7
+        assert np.mean(x0 == o.round_bf16(want)) > 0.999
+    plan.close()
+
+
+@pytest.mark.parametrize("variance_adaptive", [False, True])
+def test_sign_update_reference_case(variance_adaptive):
+    # crates/cuda-kernels/tests/optimizer/muon/tma_finish.rs:686-840
+    n = 32 * 32
+    i = np.arange(n)
+    grad = ((i * 41 % 97).astype(F) - F(48.0)) / F(37.0)
+    m_bits = o.bf16_bits(((i * 17 % 61).astype(F) - F(30.0)) / F(53.0))
+    v_bits = o.bf16_bits(F(0.02) + (i * 19 % 89).astype(F) / F(401.0))
+    z = (i.astype(F) - F(511.0)) / F(997.0)
+    x = (F(307.0) - i.astype(F)) / F(613.0)
+    slot = _slot(32, 32, grad, m_bits, z, x, v_bits)
+    slot.learning_rate_multiplier = 0.75
+    slot.schedule_amax.fill_(9.0)   # stale value: the call has to reset it
+    plan = b2.MuonPlan([(32, 32)], scale_layout=b2.SCALES_RAW)
+    table = b2.slot_table([slot])
+    args = b2.MuonMegaUpdateArgs(mu=0.9, grad_scale=0.25, learning_rate=0.004, weight_decay=0.1,
+                                 average_coefficient=0.3, schedule_beta=0.4, variance_adaptive=variance_adaptive)
+    b2.OptimizerModule().muon_tma_sign_update_deferred_quantization(plan, table, args)
+    torch.cuda.synchronize()
+    y, mb, vb, z2, x2, ax, ay = o.sign_update(grad, m_bits, v_bits, z, x, 32, 32, 0.9, 0.25, variance_adaptive,
+                                               F(0.004) * F(0.75), 0.1, 0.3, 0.4)
+    assert np.array_equal(bf16_bits(slot.momentum).ravel(), mb)
+    assert np.array_equal(bf16_bits(slot.variance).ravel(), vb)
+    assert np.array_equal(host(slot.z_master).ravel(), z2) and np.array_equal(host(slot.x_master).ravel(), x2)
+    assert np.array_equal(host(slot.grad).ravel(), y)
+    assert host(slot.schedule_amax)[0] == ay and host(plan.scratch(0, 3))[0] == ax
+    assert not host(slot.bytes).any()   # deferred: nothing quantised
+    plan.close()
+
+
+@pytest.mark.parametrize("input_dim,output_dim", [(2048, 64), (2048, 6272), (64, 256)])
+def test_qk_clip_reference_case(input_dim, output_dim):
+    # crates/cuda-kernels/tests/optimizer/muon/tma_finish.rs:112-262 (exact equality there too)
+    rows, cols, head = output_dim, input_dim, 32
+    n = rows * cols
+    factors = np.where(np.arange(input_dim // head) % 2 == 0, F(0.5), F(0.25)).astype(F)
+    m_bits, v_bits = o.bf16_bits(np.full(n, 3.0, F)), o.bf16_bits(np.full(n, 4.0, F))
+    slot = _slot(rows, cols, np.zeros(n, F), m_bits, np.full(n, 1.0, F), np.full(n, 2.0, F), v_bits)
+    slot.qk_clip_factor_offset, slot.qk_clip_head_dim = 0, head
+    plan = b2.MuonPlan([(rows, cols)], scale_layout=b2.SCALES_RAW)
+    table = b2.slot_table([slot])
+    args = b2.MuonMegaUpdateArgs(learning_rate=0.0, weight_decay=0.0, average_coefficient=0.0, schedule_beta=0.4,
+                                 qk_clip_factors=dev(factors))
+    opt = b2.OptimizerModule()
+    opt.muon_tma_prepare_polar(plan, table, b2.MuonMegaUpdateArgs(mu=1.0, grad_scale=0.0, iterations=1))
+    slot.momentum.copy_(bf16_from_bits(m_bits).view_as(slot.momentum))
+    plan.scratch(0, 1).zero_()
+    opt.muon_tma_finish_update_deferred_quantization(plan, table, args)
+    torch.cuda.synchronize()
+    row_factor = np.ones(rows, F)
+    for r in range(min(rows, 2 * cols)):
+        row_factor[r] = factors[(r % cols) // head]
+    f = np.repeat(row_factor, cols)
+    ez, ex = np.full(n, 1.0, F) * f, np.full(n, 2.0, F) * f
+    assert np.array_equal(host(slot.z_master).ravel(), ez) and np.array_equal(host(slot.x_master).ravel(), ex)
+    assert np.array_equal(bf16_bits(slot.momentum).ravel(), o.bf16_bits(np.full(n, 3.0, F) * f))
+    assert np.array_equal(bf16_bits(slot.variance).ravel(), o.bf16_bits(np.full(n, 4.0, F) * f * f))
+    assert host(slot.schedule_amax)[0] == np.max(np.abs(ez + F(0.4) * (ex - ez)))
+    plan.close()
+
+
+def test_update_with_clip_and_variance_matches_oracle():
+    # random data, two slots (one clipped, one not), non-zero learning rate
+    rng = np.random.default_rng(5)
+    shapes = [(192, 64), (64, 128)]
+    factors = (0.25 + 0.75 * rng.random(8)).astype(F)
+    factors[5] = 1.0
+    slots, data = [], []
+    for k, (r, c) in enumerate(shapes):
+        z, x = U.weights(rng, r * c), U.weights(rng, r * c)
+        mb, vb = o.bf16_bits(U.weights(rng, r * c, 1e-2)), o.bf16_bits(np.abs(U.weights(rng, r * c, 1e-3)))
+        s = _slot(r, c, np.zeros(r * c, F), mb, z, x, vb)
+        if k == 0:
+            s.qk_clip_factor_offset, s.qk_clip_head_dim = 4, 16   # 64 / 16 = 4 heads at offset 4
+        slots.append(s)
+        data.append((z, x, mb, vb, (rng.standard_normal(r * c) * 0.05).astype(F)))
+    plan = b2.MuonPlan(shapes, scale_layout=b2.SCALES_RAW)
+    table = b2.slot_table(slots)
+    opt = b2.OptimizerModule()
+    opt.muon_tma_prepare_polar(plan, table, b2.MuonMegaUpdateArgs(mu=1.0, grad_scale=0.0, iterations=1))
+    for k, (s, (r, c)) in enumerate(zip(slots, shapes)):
+        s.momentum.copy_(bf16_from_bits(data[k][2]).view_as(s.momentum))
+        s.variance.copy_(bf16_from_bits(data[k][3]).view_as(s.variance))
+        plan.scratch(k, 1).copy_(dev(data[k][4]).view(r, c))
+    args = b2.MuonMegaUpdateArgs(learning_rate=0.02, weight_decay=0.025, average_coefficient=0.3, schedule_beta=0.6,
+                                 qk_clip_factors=dev(factors), variance_adaptive=True)
+    opt.muon_tma_finish_update_deferred_quantization(plan, table, args)
+    torch.cuda.synchronize()
+    for k, (s, (r, c)) in enumerate(zip(slots, shapes)):
+        z, x, mb, vb, Um = data[k]
+        off, hd = (4, 16) if k == 0 else (0xFFFFFFFF, 0)
+        z2, x2, y2, m2, v2, ax, ay = o.update_clip(Um, z, x, mb, vb, r, c, 0.02, 0.025, 0.3, 0.6, factors, off, hd)
+        assert np.array_equal(host(s.z_master).ravel(), z2) and np.array_equal(host(s.x_master).ravel(), x2)
+        assert np.array_equal(host(s.grad).ravel(), y2)
+        assert np.array_equal(bf16_bits(s.momentum).ravel(), m2)
+        assert np.array_equal(bf16_bits(s.variance).ravel(), v2)
+        assert host(s.schedule_amax)[0] == ay and host(plan.scratch(k, 3))[0] == ax
+    plan.close()
