@@ -45,7 +45,8 @@ typedef struct b2_muon_slot_descriptor {
     uint64_t grad;            /* f32 [rows][cols]; overwritten with y = z' + beta (x' - z') */
     uint64_t momentum;        /* bf16 [rows][cols] */
     uint64_t variance;        /* bf16 [rows][cols]; read and written only with variance_adaptive */
-    uint64_t second_momentum; /* unused on this path (NorMuon) */
+    uint64_t second_momentum; /* f32 [max(rows, cols)]: NorMuon per-neuron second moment; read and written
+                                 only with b2_muon_step_args.normuon or the Hyperball finish */
     uint64_t z_master;        /* f32 */
     uint64_t x_master;        /* f32 */
     uint64_t schedule_amax;   /* f32[1]: max |y| */
@@ -104,6 +105,12 @@ typedef struct b2_muon_step_args {
                                    `MuonTmaFinishArgs`): slots whose qk_clip_factor_offset is not
                                    UINT32_MAX scale z', x', momentum (and variance) of their query/key
                                    rows (row < 2*cols, head = (row % cols) / qk_clip_head_dim) */
+    uint32_t normuon;           /* 1: the finish stage first updates every slot's `second_momentum`
+                                   (beta2 0.95) from the orthogonalised update and scales each neuron by
+                                   1/sqrt(second moment), renormalised to the update's Frobenius norm
+                                   (`muon_tma_normuon`, .../launcher/muon_mega.rs:283-325; the reference's
+                                   split finish always does, its mega kernel never) */
+    uint32_t reserved_padding;
 } b2_muon_step_args;
 
 typedef struct b2_muon_plan b2_muon_plan;
@@ -150,13 +157,23 @@ int b2_muon_finish_update_deferred_quantization(b2_muon_plan *plan,
  * device code .../muon/fused/update/one.rs:88-167) for every slot of the plan: momentum (and
  * variance) update, z' = z (1 - lr wd) - lr sign(m'), x', y into the gradient buffer, both amax
  * words.  No Newton-Schulz, no quantisation. */
+/* `OptimizerModule::muon_tma_finish_hyperball_update_deferred_quantization`
+ * (.../launcher/muon_mega.rs:166-228): NorMuon factors, then a step of relative size
+ * learning_rate along the update followed by projection back onto the sphere of the matrix's
+ * Frobenius radius; x' averages towards z' when use_schedule_free, else x' = z'.  No weight decay. */
+int b2_muon_finish_hyperball_update_deferred_quantization(b2_muon_plan *plan,
+                                                          const b2_muon_slot_descriptor *d_slots,
+                                                          const b2_muon_step_args *args,
+                                                          uint32_t use_schedule_free, void *stream);
 int b2_muon_sign_update_deferred_quantization(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_slots,
                                               const b2_muon_step_args *args, void *stream);
 /* Scratch views for tests and tracing (the reference's `MUON_TMA_TRACE`,
  * src/training/optimizer_muon/tma.rs:1210-1276).  which: 0 = X0 (16-bit, [rows][cols]),
  * 1 = Newton-Schulz result U (f32, [rows][cols]), 2 = inverse norm (f32[1]),
  * 3 = max|x'| (f32[1]), 4 = device status word (u32[1], plan-wide).
- * 5 = Gram (16-bit, [n][ld]) and 6 = polynomial Q (16-bit, [n][ld]) of the LAST iteration. */
+ * 5 = Gram (16-bit, [n][ld]) and 6 = polynomial Q (16-bit, [n][ld]) of the LAST iteration,
+ * 7 = the second operand buffer X1, 8 = NorMuon factors (f32[max(rows, cols)]),
+ * 9 = NorMuon / Hyperball slot scalars (f32[4]: normuon_scale, update_norm, radius, dot). */
 int b2_muon_plan_scratch(b2_muon_plan *plan, uint32_t slot, uint32_t which, void **d_ptr,
                          size_t *bytes);
 /* Reads back and clears the plan's device status word (synchronises `stream`): 0 when no

@@ -41,7 +41,7 @@ class MuonStepArgs(C.Structure):
                 ("weight_decay", C.c_float), ("average_coefficient", C.c_float), ("schedule_beta", C.c_float),
                 ("iterations", C.c_uint32), ("nesterov", C.c_uint32), ("coefficients", C.POINTER(C.c_float)),
                 ("d_grad_scale", C.c_void_p), ("variance_adaptive", C.c_uint32), ("bias_correction_inv", C.c_float),
-                ("d_qk_clip_factors", C.c_void_p)]
+                ("d_qk_clip_factors", C.c_void_p), ("normuon", C.c_uint32), ("reserved_padding", C.c_uint32)]
 
 
 class ScheduleFreeMaterializeArgs(C.Structure):
@@ -98,6 +98,7 @@ def _declare(L: C.CDLL) -> None:
         "b2_muon_polar": (i, [vp, C.POINTER(MuonStepArgs), vp]),
         "b2_muon_finish_update": (i, [vp, vp, C.POINTER(MuonStepArgs), vp]),
         "b2_muon_finish_update_deferred_quantization": (i, [vp, vp, C.POINTER(MuonStepArgs), vp]),
+        "b2_muon_finish_hyperball_update_deferred_quantization": (i, [vp, vp, C.POINTER(MuonStepArgs), C.c_uint32, vp]),
         "b2_muon_sign_update_deferred_quantization": (i, [vp, vp, C.POINTER(MuonStepArgs), vp]),
         "b2_muon_plan_scratch": (i, [vp, u32, u32, C.POINTER(vp), C.POINTER(sz)]),
         "b2_muon_plan_status": (i, [vp, vp]),

@@ -107,18 +107,20 @@ enum MapKind { kLX0K = 0, kLX1K, kLX0M, kLX1M, kLG, kLQ, kSX0, kSX1, kSG, kSQ, k
 struct SlotLayout {
     uint32_t rows, cols, n, m, ldg, tiles_m_nn, tiles_n_nn, sub_m_nn;
     uint64_t len;
-    size_t off_x[2], off_u, off_g16, off_q16, off_frag;
+    size_t off_x[2], off_u, off_g16, off_q16, off_frag, off_factors;
 };
 struct Layout {
     std::vector<SlotLayout> slots;
     std::vector<uint32_t> chunk_prefix;  // slot_count + 1
+    std::vector<uint32_t> unit_prefix;   // slot_count + 1: NorMuon work units (8 rows or 128 columns)
     uint32_t total_chunks = 0;
     int bn = 256;
     int pair = 0;   // 1: two-CTA 256 x 256 tiles
     int symmetric = 0;  // 1: Gram / Poly compute the upper triangle of tiles only
     int tile_m = 128;
     size_t off_prefix, off_partials, off_inv_norm, off_amax_x, off_status, off_x0_ptrs, off_u_ptrs, off_maps,
-        off_problems, off_tiles_nn, off_tiles_out, off_meta_end, total;
+        off_problems, off_tiles_nn, off_tiles_out, off_unit_prefix, off_factor_ptrs, off_unit_partials, off_slot_stats,
+        off_meta_end, total;
     uint32_t tiles_nn = 0, tiles_out = 0;
 };
 
@@ -179,10 +181,18 @@ bool build_layout(const uint32_t *rows, const uint32_t *cols, uint32_t count, co
     }
     L.chunk_prefix[count] = chunks;
     L.total_chunks = chunks;
+    L.unit_prefix.assign(count + 1, 0);
+    for (uint32_t s = 0; s < count; ++s) {
+        uint32_t units = 0;
+        if ((uint64_t)rows[s] * cols[s] != 0) units = rows[s] >= cols[s] ? (rows[s] + 7) / 8 : (cols[s] + 127) / 128;
+        L.unit_prefix[s + 1] = L.unit_prefix[s] + units;
+    }
     // ---- metadata region (uploaded at plan creation) ----
     L.off_prefix = take((count + 1) * sizeof(uint32_t));
     L.off_x0_ptrs = take(count * sizeof(uint64_t));
     L.off_u_ptrs = take(count * sizeof(uint64_t));
+    L.off_unit_prefix = take((count + 1) * sizeof(uint32_t));
+    L.off_factor_ptrs = take(count * sizeof(uint64_t));
     L.off_maps = take((size_t)count * kMapsPerSlot * sizeof(CUtensorMap));
     L.off_problems = take((size_t)kProblemTypes * count * sizeof(GemmProblem));
     L.tiles_nn = L.tiles_out = 0;
@@ -208,6 +218,8 @@ bool build_layout(const uint32_t *rows, const uint32_t *cols, uint32_t count, co
     L.off_inv_norm = take(count * sizeof(float));
     L.off_amax_x = take(count * sizeof(float));
     L.off_status = take(sizeof(uint32_t));
+    L.off_unit_partials = take((size_t)std::max(L.unit_prefix[count], 1u) * 4 * sizeof(double));
+    L.off_slot_stats = take((size_t)count * 4 * sizeof(float));
     for (uint32_t s = 0; s < count; ++s) {
         SlotLayout &sl = L.slots[s];
         if (sl.len == 0) continue;
@@ -217,6 +229,7 @@ bool build_layout(const uint32_t *rows, const uint32_t *cols, uint32_t count, co
         sl.off_g16 = take((size_t)sl.n * sl.ldg * 2);
         sl.off_q16 = take((size_t)sl.n * sl.ldg * 2);
         sl.off_frag = take((size_t)sl.sub_m_nn * sl.tiles_n_nn * kGemmBlockM * L.bn * 4);
+        sl.off_factors = take((size_t)sl.m * 4);
     }
     L.total = off;
     return true;
@@ -250,6 +263,15 @@ struct b2_muon_plan {
         v.total_chunks = layout.total_chunks;
         v.grid = stream_grid_cap(dev);
         return v;
+    }
+    NeuronView neurons() const {
+        NeuronView nv;
+        nv.unit_prefix = at<uint32_t>(layout.off_unit_prefix);
+        nv.total_units = layout.unit_prefix.back();
+        nv.factor_ptrs = at<uint64_t>(layout.off_factor_ptrs);
+        nv.partials = at<double>(layout.off_unit_partials);
+        nv.slot_stats = at<float>(layout.off_slot_stats);
+        return nv;
     }
 };
 
@@ -315,6 +337,8 @@ int b2_muon_plan_create(b2_muon_plan **out, const uint32_t *rows, const uint32_t
     std::memcpy(h + L.off_prefix, L.chunk_prefix.data(), (slot_count + 1) * sizeof(uint32_t));
     uint64_t *x0p = reinterpret_cast<uint64_t *>(h + L.off_x0_ptrs);
     uint64_t *up = reinterpret_cast<uint64_t *>(h + L.off_u_ptrs);
+    uint64_t *fp = reinterpret_cast<uint64_t *>(h + L.off_factor_ptrs);
+    std::memcpy(h + L.off_unit_prefix, L.unit_prefix.data(), (slot_count + 1) * sizeof(uint32_t));
     CUtensorMap *maps = reinterpret_cast<CUtensorMap *>(h + L.off_maps);
     GemmProblem *probs = reinterpret_cast<GemmProblem *>(h + L.off_problems);
     auto dmap = [&](uint32_t s, int kind) {
@@ -327,6 +351,7 @@ int b2_muon_plan_create(b2_muon_plan **out, const uint32_t *rows, const uint32_t
         p->flops_per_iteration += slot_flops(sl.rows, sl.cols);
         x0p[s] = reinterpret_cast<uint64_t>(p->ws + sl.off_x[0]);
         up[s] = reinterpret_cast<uint64_t>(p->ws + sl.off_u);
+        fp[s] = reinterpret_cast<uint64_t>(p->ws + sl.off_factors);
         CUtensorMap *ms = maps + (size_t)s * kMapsPerSlot;
         const uint64_t xp = (uint64_t)sl.cols * 2, gp = (uint64_t)sl.ldg * 2;
         ok &= make_map(ms + kLX0K, p->ws + sl.off_x[0], 2, sl.rows, sl.cols, xp, 64, 128);
@@ -445,6 +470,9 @@ static UpdateParams update_params(const b2_muon_step_args *a) {
     up.beta = a->schedule_beta;
     up.d_qk_clip_factors = a->d_qk_clip_factors;
     up.variance_adaptive = a->variance_adaptive ? 1 : 0;
+    up.normuon = 0;
+    up.factor_ptrs = nullptr;
+    up.slot_stats = nullptr;
     return up;
 }
 
@@ -510,7 +538,16 @@ static int finish_impl(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_slot
     cudaStream_t s = as_stream(stream);
     SlotView v = plan->view(d_slots);
     float *amax_x = plan->at<float>(L.off_amax_x);
-    cudaError_t e = launch_muon_update(v, plan->at<uint64_t>(L.off_u_ptrs), amax_x, update_params(a), s);
+    UpdateParams up = update_params(a);
+    cudaError_t e = cudaSuccess;
+    if (a->normuon) {
+        const NeuronView nv = plan->neurons();
+        e = launch_normuon_stats(v, nv, plan->at<uint64_t>(L.off_u_ptrs), 0, s);
+        up.normuon = 1;
+        up.factor_ptrs = nv.factor_ptrs;
+        up.slot_stats = nv.slot_stats;
+    }
+    if (e == cudaSuccess) e = launch_muon_update(v, plan->at<uint64_t>(L.off_u_ptrs), amax_x, up, s);
     if (e == cudaSuccess && quantize)
         e = launch_muon_encode(v, amax_x, plan->options.quantize_target == B2_QUANTIZE_Y,
                                (int)plan->options.scale_layout, s);
@@ -523,6 +560,25 @@ int b2_muon_finish_update(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_s
 int b2_muon_finish_update_deferred_quantization(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_slots,
                                                 const b2_muon_step_args *a, void *stream) {
     return finish_impl(plan, d_slots, a, false, stream);
+}
+
+int b2_muon_finish_hyperball_update_deferred_quantization(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_slots,
+                                                          const b2_muon_step_args *a, uint32_t use_schedule_free,
+                                                          void *stream) {
+    if (!plan || !a || !d_slots) return B2_ERROR_INVALID_VALUE;
+    const Layout &L = plan->layout;
+    cudaStream_t s = as_stream(stream);
+    SlotView v = plan->view(d_slots);
+    const NeuronView nv = plan->neurons();
+    UpdateParams up = update_params(a);
+    up.normuon = 1;
+    up.factor_ptrs = nv.factor_ptrs;
+    up.slot_stats = nv.slot_stats;
+    cudaError_t e = launch_normuon_stats(v, nv, plan->at<uint64_t>(L.off_u_ptrs), 1, s);
+    if (e == cudaSuccess)
+        e = launch_muon_hyperball_update(v, plan->at<uint64_t>(L.off_u_ptrs), plan->at<float>(L.off_amax_x), up,
+                                         use_schedule_free ? 1 : 0, s);
+    return (int)e;
 }
 
 int b2_muon_sign_update_deferred_quantization(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_slots,
@@ -559,6 +615,8 @@ int b2_muon_plan_scratch(b2_muon_plan *plan, uint32_t slot, uint32_t which, void
         case 5: *d_ptr = plan->ws + sl.off_g16; *bytes = (size_t)sl.n * sl.ldg * 2; break;
         case 6: *d_ptr = plan->ws + sl.off_q16; *bytes = (size_t)sl.n * sl.ldg * 2; break;
         case 7: *d_ptr = plan->ws + sl.off_x[1]; *bytes = sl.len * 2; break;
+        case 8: *d_ptr = plan->ws + sl.off_factors; *bytes = (size_t)sl.m * 4; break;
+        case 9: *d_ptr = plan->ws + L.off_slot_stats + (size_t)slot * 16; *bytes = 16; break;
         default: return B2_ERROR_INVALID_VALUE;
     }
     return B2_SUCCESS;

@@ -24,10 +24,22 @@ struct MomentumParams {
     int nesterov, variance_adaptive;
     float bias_correction_inv;
 };
+// NorMuon / Hyperball scratch of a plan: work units are 8 rows (slots with rows >= cols) or 128
+// columns (rows < cols) of one slot; `unit_prefix` counts them like `chunk_prefix` counts chunks.
+struct NeuronView {
+    const uint32_t *unit_prefix;   // device, slot_count + 1 entries
+    uint32_t total_units;
+    const uint64_t *factor_ptrs;   // device, per slot: f32[max(rows, cols)] factors
+    double *partials;              // device, 4 per unit: raw, scaled, parameter, dot
+    float *slot_stats;             // device, 4 per slot: normuon_scale, update_norm, radius, dot
+};
 struct UpdateParams {
     float lr, wd, c_avg, beta;
     const float *d_qk_clip_factors;
     int variance_adaptive;
+    int normuon;                   // 1: scale U by factor[neuron] * normuon_scale
+    const uint64_t *factor_ptrs;
+    const float *slot_stats;
 };
 cudaError_t launch_muon_sumsq(const SlotView &v, const MomentumParams &mp, double *partials, float *amax_x,
                               cudaStream_t s);
@@ -37,6 +49,10 @@ cudaError_t launch_muon_momentum_normalize(const SlotView &v, const MomentumPara
                                            const uint64_t *x0_ptrs, int f16, cudaStream_t s);
 cudaError_t launch_muon_update(const SlotView &v, const uint64_t *u_ptrs, float *amax_x, const UpdateParams &up,
                                cudaStream_t s);
+cudaError_t launch_normuon_stats(const SlotView &v, const NeuronView &nv, const uint64_t *u_ptrs, int hyperball,
+                                 cudaStream_t s);
+cudaError_t launch_muon_hyperball_update(const SlotView &v, const uint64_t *u_ptrs, float *amax_x,
+                                         const UpdateParams &up, int use_schedule_free, cudaStream_t s);
 cudaError_t launch_muon_sign_update(const SlotView &v, const MomentumParams &mp, const UpdateParams &up,
                                     float *amax_x, cudaStream_t s);
 cudaError_t launch_muon_encode(const SlotView &v, const float *amax_x, int quantize_y,

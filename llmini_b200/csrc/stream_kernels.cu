@@ -196,6 +196,28 @@ k_muon_momentum_normalize(const b2_muon_slot_descriptor *slots, const uint32_t *
     }
 }
 
+// NorMuon factors of four consecutive elements (update/one.rs:48-56): the neuron is the row when
+// rows >= cols, else the column; `with_scale` multiplies in the per-slot normuon_scale.
+__device__ __forceinline__ void neuron_factors(const ChunkCtx &cx, const UpdateParams &up, uint32_t i, int with_scale,
+                                               float *nf) {
+    nf[0] = nf[1] = nf[2] = nf[3] = 1.0f;
+    if (!up.normuon) return;
+    const float *fp = reinterpret_cast<const float *>(up.factor_ptrs[cx.slot]);
+    const float sc = with_scale ? up.slot_stats[cx.slot * 4] : 1.0f;
+    const uint32_t row = i / cx.d.cols;
+    if (cx.d.rows >= cx.d.cols) {
+        const float f = with_scale ? __ldg(fp + row) * sc : __ldg(fp + row);
+        nf[0] = nf[1] = nf[2] = nf[3] = f;
+    } else {
+        const float4 f = __ldg(reinterpret_cast<const float4 *>(fp + (i - row * cx.d.cols)));
+        nf[0] = f.x; nf[1] = f.y; nf[2] = f.z; nf[3] = f.w;
+        if (with_scale) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) nf[e] *= sc;
+        }
+    }
+}
+
 // Stage U: crates/cuda-kernels/src/gpt/optimizer/muon/fused/update/one.rs:46-85, scale from
 // .../fused/update.rs:54, per-slot learning rate from .../fused/mega/slot.rs:26-29.
 // U is in the storage layout, so every access is a coalesced 128-bit one.
@@ -228,6 +250,8 @@ k_muon_update(const b2_muon_slot_descriptor *slots, const uint32_t *prefix, uint
                 float xx[4] = {xv.x, xv.y, xv.z, xv.w};
                 float yy[4];
                 // the four elements share a row (cols % 16 == 0), hence one clip factor
+                float nf[4];
+                neuron_factors(cx, up, i, 1, nf);
                 const float clip = qk_clip_factor(cx.d, up.d_qk_clip_factors, i);
                 if (clip != 1.0f) {  // one.rs:63-72: momentum (and variance) follow the clipped weights
                     uint16_t *mom = reinterpret_cast<uint16_t *>(cx.d.momentum);
@@ -245,7 +269,7 @@ k_muon_update(const b2_muon_slot_descriptor *slots, const uint32_t *prefix, uint
                 }
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    float upd = scale * (uu[e] * 1.0f * 1.0f);
+                    float upd = scale * (uu[e] * 1.0f * nf[e]);
                     float nz = zz[e] * decay - lr_s * upd;
                     float nx = xx[e] + c_avg * (nz - xx[e]);
                     if (clip != 1.0f) {
@@ -261,6 +285,240 @@ k_muon_update(const b2_muon_slot_descriptor *slots, const uint32_t *prefix, uint
                 }
                 st_stream(z + i, make_float4(zz[0], zz[1], zz[2], zz[3]));
                 // x' is read again by the encode kernel: keep it cacheable
+                *reinterpret_cast<float4 *>(x + i) = make_float4(xx[0], xx[1], xx[2], xx[3]);
+                *reinterpret_cast<float4 *>(y + i) = make_float4(yy[0], yy[1], yy[2], yy[3]);
+            }
+        }
+        ax = warp_max(ax);
+        ay = warp_max(ay);
+        if ((tid & 31) == 0) {
+            warp_ax[tid >> 5] = ax;
+            warp_ay[tid >> 5] = ay;
+        }
+        __syncthreads();
+        if (tid == 0) {
+            float mx = 0.0f, my = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kThreads / 32; ++w) {
+                mx = fmaxf(mx, warp_ax[w]);
+                my = fmaxf(my, warp_ay[w]);
+            }
+            atomic_max_nonneg(amax_x + cx.slot, mx);
+            atomic_max_nonneg(reinterpret_cast<float *>(cx.d.schedule_amax), my);
+        }
+        __syncthreads();
+    }
+}
+
+// NorMuon second moment per neuron, and the Hyperball statistics when `hyperball` is set:
+// crates/cuda-kernels/src/gpt/optimizer/muon/fused/tma_split.rs:285-443.  U is in the storage
+// layout here, so a neuron's values are one row (rows >= cols: a warp per row) or one column
+// (rows < cols: 128 columns per CTA, the eight warps striding over the rows); both read whole
+// 512-byte row segments.  Per unit four partial sums leave the CTA: raw, scaled, parameter, dot.
+__global__ void __launch_bounds__(kThreads)
+k_normuon_stats(const b2_muon_slot_descriptor *slots, uint32_t slot_count, NeuronView nv, const uint64_t *u_ptrs,
+                int hyperball) {
+    __shared__ float col_raw[kThreads / 32][128], col_dot[kThreads / 32][128];
+    __shared__ double part[kThreads / 32][4];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (uint32_t unit = blockIdx.x; unit < nv.total_units; unit += gridDim.x) {
+        const uint32_t slot = find_slot(nv.unit_prefix, slot_count, unit);
+        const b2_muon_slot_descriptor d = slots[slot];
+        const uint32_t local = unit - nv.unit_prefix[slot];
+        const float *U = reinterpret_cast<const float *>(u_ptrs[slot]);
+        const float *z = reinterpret_cast<const float *>(d.z_master);
+        float *state = reinterpret_cast<float *>(d.second_momentum);
+        float *factors = reinterpret_cast<float *>(nv.factor_ptrs[slot]);
+        double s_raw = 0.0, s_scaled = 0.0, s_param = 0.0, s_dot = 0.0;  // meaningful on one thread per neuron
+        if (d.rows >= d.cols) {
+            const uint32_t row = local * (kThreads / 32) + warp;
+            if (row < d.rows) {
+                float raw = 0.0f, param = 0.0f, dot = 0.0f;
+                const size_t base = (size_t)row * d.cols;
+                for (uint32_t c = lane * 4; c < d.cols; c += 128) {
+                    const float4 u = *reinterpret_cast<const float4 *>(U + base + c);
+                    raw = fmaf(u.x, u.x, raw); raw = fmaf(u.y, u.y, raw);
+                    raw = fmaf(u.z, u.z, raw); raw = fmaf(u.w, u.w, raw);
+                    if (hyperball) {
+                        const float4 p = *reinterpret_cast<const float4 *>(z + base + c);
+                        param = fmaf(p.x, p.x, param); param = fmaf(p.y, p.y, param);
+                        param = fmaf(p.z, p.z, param); param = fmaf(p.w, p.w, param);
+                        dot = fmaf(p.x, u.x, dot); dot = fmaf(p.y, u.y, dot);
+                        dot = fmaf(p.z, u.z, dot); dot = fmaf(p.w, u.w, dot);
+                    }
+                }
+                const double r = warp_sum((double)raw), pp = warp_sum((double)param), dd = warp_sum((double)dot);
+                if (lane == 0) {
+                    float factor = 1.0f;
+                    if (state) {
+                        const float mean = (float)r / (float)d.cols;
+                        const float next = 0.95f * state[row] + (1.0f - 0.95f) * mean;
+                        factor = 1.0f / sqrtf(fmaxf(next, 1.0e-10f));
+                        state[row] = next;
+                    }
+                    factors[row] = factor;
+                    s_raw = r; s_scaled = (double)((float)r * factor * factor);
+                    s_param = pp; s_dot = (double)((float)dd * factor);
+                }
+            }
+        } else {
+            const uint32_t c0 = local * 128 + lane * 4;
+            float raw[4] = {0.f, 0.f, 0.f, 0.f}, dot[4] = {0.f, 0.f, 0.f, 0.f}, param = 0.0f;
+            if (c0 < d.cols) {
+                for (uint32_t r = warp; r < d.rows; r += kThreads / 32) {
+                    const size_t at = (size_t)r * d.cols + c0;
+                    const float4 u = *reinterpret_cast<const float4 *>(U + at);
+                    const float uu[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) raw[e] = fmaf(uu[e], uu[e], raw[e]);
+                    if (hyperball) {
+                        const float4 p = *reinterpret_cast<const float4 *>(z + at);
+                        const float pp[4] = {p.x, p.y, p.z, p.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            param = fmaf(pp[e], pp[e], param);
+                            dot[e] = fmaf(pp[e], uu[e], dot[e]);
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                col_raw[warp][lane * 4 + e] = raw[e];
+                col_dot[warp][lane * 4 + e] = dot[e];
+            }
+            s_param = (double)param;
+            __syncthreads();
+            const uint32_t col = local * 128 + tid;
+            if (tid < 128 && col < d.cols) {
+                double r = 0.0, dd = 0.0;
+#pragma unroll
+                for (int w = 0; w < kThreads / 32; ++w) {
+                    r += (double)col_raw[w][tid];
+                    dd += (double)col_dot[w][tid];
+                }
+                float factor = 1.0f;
+                if (state) {
+                    const float mean = (float)r / (float)d.rows;
+                    const float next = 0.95f * state[col] + (1.0f - 0.95f) * mean;
+                    factor = 1.0f / sqrtf(fmaxf(next, 1.0e-10f));
+                    state[col] = next;
+                }
+                factors[col] = factor;
+                s_raw = r; s_scaled = (double)((float)r * factor * factor);
+                s_dot = (double)((float)dd * factor);
+            }
+        }
+        s_raw = warp_sum(s_raw); s_scaled = warp_sum(s_scaled);
+        s_param = warp_sum(s_param); s_dot = warp_sum(s_dot);
+        if (lane == 0) {
+            part[warp][0] = s_raw; part[warp][1] = s_scaled; part[warp][2] = s_param; part[warp][3] = s_dot;
+        }
+        __syncthreads();
+        if (tid < 4) {
+            double t = 0.0;
+#pragma unroll
+            for (int w = 0; w < kThreads / 32; ++w) t += part[w][tid];
+            nv.partials[(size_t)unit * 4 + tid] = t;
+        }
+        __syncthreads();
+    }
+}
+
+// One CTA per slot: fixed-order sums of the unit partials, then the four slot scalars
+// (tma_split.rs:445-477 and hyperball.rs:78-105).
+__global__ void __launch_bounds__(kThreads)
+k_normuon_reduce(const b2_muon_slot_descriptor *slots, NeuronView nv) {
+    __shared__ double part[kThreads / 32][4];
+    const uint32_t slot = blockIdx.x;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t lo = nv.unit_prefix[slot], hi = nv.unit_prefix[slot + 1];
+    if (lo == hi) return;
+    double acc[4] = {0.0, 0.0, 0.0, 0.0};
+    for (uint32_t u = lo + tid; u < hi; u += kThreads)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) acc[k] += nv.partials[(size_t)u * 4 + k];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) acc[k] = warp_sum(acc[k]);
+    if (lane == 0)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) part[warp][k] = acc[k];
+    __syncthreads();
+    if (tid == 0) {
+        double t[4] = {0.0, 0.0, 0.0, 0.0};
+        for (int w = 0; w < kThreads / 32; ++w)
+#pragma unroll
+            for (int k = 0; k < 4; ++k) t[k] += part[w][k];
+        const float scaled = fmaxf((float)t[1], 1.0e-10f);
+        float *st = nv.slot_stats + slot * 4;
+        st[0] = sqrtf((float)t[0] / scaled);
+        st[1] = sqrtf(scaled);
+        st[2] = sqrtf(fmaxf((float)t[2], 1.0e-10f));
+        st[3] = (float)t[3];
+    }
+}
+
+// Hyperball: the step keeps the matrix on the sphere of its current Frobenius radius
+// (tma_split.rs:498-558 scalars, hyperball.rs:107-173 elements).  No weight decay on this path.
+__global__ void __launch_bounds__(kThreads)
+k_muon_hyperball_update(const b2_muon_slot_descriptor *slots, const uint32_t *prefix, uint32_t slot_count,
+                        uint32_t total_chunks, const uint64_t *u_ptrs, float *amax_x, UpdateParams up,
+                        int use_schedule_free) {
+    __shared__ float warp_ax[kThreads / 32], warp_ay[kThreads / 32];
+    const int tid = threadIdx.x;
+    for (uint32_t c = blockIdx.x; c < total_chunks; c += gridDim.x) {
+        ChunkCtx cx = chunk_ctx(slots, prefix, slot_count, c);
+        const float *U = reinterpret_cast<const float *>(u_ptrs[cx.slot]);
+        float *z = reinterpret_cast<float *>(cx.d.z_master);
+        float *x = reinterpret_cast<float *>(cx.d.x_master);
+        float *y = reinterpret_cast<float *>(cx.d.grad);
+        const float *st = up.slot_stats + cx.slot * 4;
+        const float radius = st[2], dot = st[3];
+        const float update_norm = fmaxf(st[1], 1.0e-10f);
+        const float step_scale = up.lr * cx.d.learning_rate_multiplier * radius / update_norm;
+        const float candidate = fmaxf(radius * radius - 2.0f * step_scale * dot +
+                                          step_scale * step_scale * update_norm * update_norm, 1.0e-10f);
+        const float projection = radius / sqrtf(candidate);
+        const uint32_t base = cx.local_chunk * kChunk;
+        float ax = 0.0f, ay = 0.0f;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            uint32_t i = base + h * (kChunk / 2) + tid * 4;
+            if (i < cx.len) {
+                const float4 u = ld_stream(U + i), zv = ld_stream(z + i), xv = ld_stream(x + i);
+                const float uu[4] = {u.x, u.y, u.z, u.w};
+                float zz[4] = {zv.x, zv.y, zv.z, zv.w}, xx[4] = {xv.x, xv.y, xv.z, xv.w}, yy[4], nf[4];
+                neuron_factors(cx, up, i, 0, nf);
+                const float clip = qk_clip_factor(cx.d, up.d_qk_clip_factors, i);
+                if (clip != 1.0f) {
+                    uint16_t *mom = reinterpret_cast<uint16_t *>(cx.d.momentum);
+                    const uint2 m = *reinterpret_cast<const uint2 *>(mom + i);
+                    const float cm[4] = {bf16_bits_to_f32(m.x & 0xffffu) * clip, bf16_bits_to_f32(m.x >> 16) * clip,
+                                         bf16_bits_to_f32(m.y & 0xffffu) * clip, bf16_bits_to_f32(m.y >> 16) * clip};
+                    *reinterpret_cast<uint2 *>(mom + i) = pack_bf16x4(cm);
+                    if (cx.d.variance != 0) {
+                        uint16_t *var = reinterpret_cast<uint16_t *>(cx.d.variance);
+                        const uint2 v = *reinterpret_cast<const uint2 *>(var + i);
+                        const float cv[4] = {bf16_bits_to_f32(v.x & 0xffffu) * clip * clip, bf16_bits_to_f32(v.x >> 16) * clip * clip,
+                                             bf16_bits_to_f32(v.y & 0xffffu) * clip * clip, bf16_bits_to_f32(v.y >> 16) * clip * clip};
+                        *reinterpret_cast<uint2 *>(var + i) = pack_bf16x4(cv);
+                    }
+                }
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float direction = uu[e] * nf[e];
+                    float pz = (zz[e] - step_scale * direction) * projection;
+                    float nx = use_schedule_free ? xx[e] + up.c_avg * (pz - xx[e]) : pz;
+                    if (clip != 1.0f) {
+                        pz *= clip;
+                        nx *= clip;
+                    }
+                    const float sv = pz + up.beta * (nx - pz);
+                    zz[e] = pz; xx[e] = nx; yy[e] = sv;
+                    ax = fmaxf(ax, fabsf(nx));
+                    ay = fmaxf(ay, fabsf(sv));
+                }
+                st_stream(z + i, make_float4(zz[0], zz[1], zz[2], zz[3]));
                 *reinterpret_cast<float4 *>(x + i) = make_float4(xx[0], xx[1], xx[2], xx[3]);
                 *reinterpret_cast<float4 *>(y + i) = make_float4(yy[0], yy[1], yy[2], yy[3]);
             }
@@ -899,6 +1157,20 @@ cudaError_t launch_muon_update(const SlotView &v, const uint64_t *u_ptrs, float 
     if (v.total_chunks == 0) return cudaSuccess;
     k_muon_update<<<clamp_grid(v.total_chunks, v.grid), kThreads, 0, s>>>(
         v.slots, v.chunk_prefix, v.slot_count, v.total_chunks, u_ptrs, amax_x, up);
+    return cudaGetLastError();
+}
+cudaError_t launch_normuon_stats(const SlotView &v, const NeuronView &nv, const uint64_t *u_ptrs, int hyperball,
+                                 cudaStream_t s) {
+    if (nv.total_units == 0) return cudaSuccess;
+    k_normuon_stats<<<clamp_grid(nv.total_units, v.grid), kThreads, 0, s>>>(v.slots, v.slot_count, nv, u_ptrs, hyperball);
+    k_normuon_reduce<<<v.slot_count, kThreads, 0, s>>>(v.slots, nv);
+    return cudaGetLastError();
+}
+cudaError_t launch_muon_hyperball_update(const SlotView &v, const uint64_t *u_ptrs, float *amax_x,
+                                         const UpdateParams &up, int use_schedule_free, cudaStream_t s) {
+    if (v.total_chunks == 0) return cudaSuccess;
+    k_muon_hyperball_update<<<clamp_grid(v.total_chunks, v.grid), kThreads, 0, s>>>(
+        v.slots, v.chunk_prefix, v.slot_count, v.total_chunks, u_ptrs, amax_x, up, use_schedule_free);
     return cudaGetLastError();
 }
 cudaError_t launch_muon_sign_update(const SlotView &v, const MomentumParams &mp, const UpdateParams &up,

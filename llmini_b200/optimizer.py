@@ -49,6 +49,7 @@ class MuonSlot:
     cols: int
     learning_rate_multiplier: float = 1.0
     variance: Optional[torch.Tensor] = None  # bf16 [rows, cols], Muon-VS only
+    second_momentum: Optional[torch.Tensor] = None  # f32 [max(rows, cols)], NorMuon / Hyperball only
     qk_clip_factor_offset: int = U32_MAX
     qk_clip_head_dim: int = 0
 
@@ -68,7 +69,8 @@ class MuonSlot:
                         torch.zeros(max(n // 2, 1), dtype=torch.uint8, device=device), scales, z(1), rows, cols)
 
     def descriptor(self) -> MuonSlotDescriptor:
-        return MuonSlotDescriptor(_ptr(self.grad), _ptr(self.momentum), _ptr(self.variance), 0, _ptr(self.z_master),
+        return MuonSlotDescriptor(_ptr(self.grad), _ptr(self.momentum), _ptr(self.variance),
+                                  _ptr(self.second_momentum), _ptr(self.z_master),
                                   _ptr(self.x_master), _ptr(self.schedule_amax), _ptr(self.bytes), _ptr(self.scales),
                                   _ptr(self.global_scale), self.rows, self.cols, self.learning_rate_multiplier,
                                   self.qk_clip_factor_offset, self.qk_clip_head_dim, 0)
@@ -97,6 +99,7 @@ class MuonMegaUpdateArgs:
     variance_adaptive: bool = False                    # Muon-VS; slots need a `variance` buffer
     bias_correction_inv: float = 1.0
     qk_clip_factors: Optional[torch.Tensor] = None     # f32 per-head factors on the device
+    normuon: bool = False                              # slots need a `second_momentum` buffer
 
     def c_args(self):
         co = None
@@ -107,7 +110,8 @@ class MuonMegaUpdateArgs:
             co = keep.ctypes.data_as(C.POINTER(C.c_float))
         a = MuonStepArgs(self.mu, self.grad_scale, self.learning_rate, self.weight_decay, self.average_coefficient,
                          self.schedule_beta, self.iterations, int(self.nesterov), co, _ptr(self.grad_scale_device),
-                         int(self.variance_adaptive), self.bias_correction_inv, _ptr(self.qk_clip_factors))
+                         int(self.variance_adaptive), self.bias_correction_inv, _ptr(self.qk_clip_factors),
+                         int(self.normuon), 0)
         return a, keep
 
 
@@ -217,6 +221,15 @@ class OptimizerModule:
         a, keep = args.c_args()
         check(self._lib.b2_muon_finish_update_deferred_quantization(plan.handle, _ptr(slots), C.byref(a), _stream()),
               "muon_finish_update_deferred_quantization")
+        del keep
+
+    # launcher/muon_mega.rs:166-228
+    def muon_tma_finish_hyperball_update_deferred_quantization(self, plan: MuonPlan, slots: torch.Tensor,
+                                                               args: MuonMegaUpdateArgs,
+                                                               use_schedule_free: bool = True) -> None:
+        a, keep = args.c_args()
+        check(self._lib.b2_muon_finish_hyperball_update_deferred_quantization(
+            plan.handle, _ptr(slots), C.byref(a), int(use_schedule_free), _stream()), "muon_finish_hyperball_update")
         del keep
 
     # launcher/muon_mega.rs:229-283

@@ -502,6 +502,126 @@ void orc_update_clip(const float *U, float *z, float *x, float *y, uint16_t *mom
     amax[0] = ax; amax[1] = ay;
 }
 
+/* NorMuon per-neuron second moment and Hyperball statistics:
+ * crates/cuda-kernels/src/gpt/optimizer/muon/fused/tma_split.rs:285-477.
+ * U is given in STORAGE orientation [rows][cols]; a neuron is an index along the larger dimension
+ * (a row when rows >= cols, else a column: update/one.rs:48-53), its mean is taken over the
+ * smaller one.  Sums are accumulated in double (the kernel's summation order is not part of the
+ * contract; the reference's own tests allow 2e-6 / 2e-5).  stats = { normuon_scale,
+ * update_norm, radius, dot }; radius and dot only when z is given. */
+void orc_normuon_stats(const float *U, const float *z, uint32_t rows, uint32_t cols, float *second_momentum,
+                       float *factors, float *stats) {
+    const uint32_t neurons = rows >= cols ? rows : cols, span = rows >= cols ? cols : rows;
+    double raw_total = 0.0, scaled_total = 0.0, param_total = 0.0, dot_total = 0.0;
+    for (uint32_t nidx = 0; nidx < neurons; ++nidx) {
+        double raw = 0.0, dot = 0.0;
+        for (uint32_t k = 0; k < span; ++k) {
+            uint64_t i = rows >= cols ? (uint64_t)nidx * cols + k : (uint64_t)k * cols + nidx;
+            raw += (double)U[i] * U[i];
+            if (z) { param_total += (double)z[i] * z[i]; dot += (double)z[i] * U[i]; }
+        }
+        volatile float mean = (float)raw / (float)span;
+        volatile float a = 0.95f * second_momentum[nidx], b = (1.0f - 0.95f) * mean;
+        float next = a + b;
+        float factor = 1.0f / sqrtf(fmaxf(next, 1.0e-10f));
+        second_momentum[nidx] = next;
+        factors[nidx] = factor;
+        raw_total += raw;
+        scaled_total += (double)((float)raw * factor * factor);
+        dot_total += (double)((float)dot * factor);
+    }
+    float scaled = fmaxf((float)scaled_total, 1.0e-10f);
+    stats[0] = sqrtf((float)raw_total / scaled);
+    stats[1] = sqrtf(scaled);
+    stats[2] = z ? sqrtf(fmaxf((float)param_total, 1.0e-10f)) : 0.0f;
+    stats[3] = z ? (float)dot_total : 0.0f;
+}
+
+/* Stage U with NorMuon factors: update/one.rs:46-60; factors == NULL is the plain update. */
+void orc_update_normuon(const float *U, float *z, float *x, float *y, uint64_t len, uint32_t rows, uint32_t cols,
+                        float lr, float wd, float c_avg, float beta, const float *factors, float normuon_scale,
+                        float *amax) {
+    float fr = (float)rows, fc = (float)cols;
+    float scale = 0.2f * sqrtf(fr > fc ? fr : fc);
+    volatile float lw = lr * wd;
+    float decay = 1.0f - lw;
+    float ax = 0.0f, ay = 0.0f;
+    for (uint64_t i = 0; i < len; ++i) {
+        uint32_t row = (uint32_t)(i / cols), col = (uint32_t)(i - (uint64_t)row * cols);
+        volatile float nf = factors ? factors[rows >= cols ? row : col] * normuon_scale : 1.0f;
+        volatile float un = U[i] * nf;
+        volatile float upd = scale * un;
+        volatile float p1 = z[i] * decay, p2 = lr * upd;
+        volatile float nz = p1 - p2;
+        volatile float d1 = nz - x[i];
+        volatile float p3 = c_avg * d1;
+        volatile float nx = x[i] + p3;
+        volatile float d2 = nx - nz;
+        volatile float p4 = beta * d2;
+        float yy = nz + p4;
+        z[i] = nz; x[i] = nx;
+        if (y) y[i] = yy;
+        if (fabsf(nx) > ax) ax = fabsf(nx);
+        if (fabsf(yy) > ay) ay = fabsf(yy);
+    }
+    amax[0] = ax; amax[1] = ay;
+}
+
+/* Hyperball projection: tma_split.rs:516-527 (scalars) and hyperball.rs:107-173 (elements).
+ * lr is learning_rate * learning_rate_multiplier; stats as written by orc_normuon_stats. */
+void orc_hyperball_update(const float *U, float *z, float *x, float *y, uint16_t *momentum_bf16,
+                          uint16_t *variance_bf16, uint32_t rows, uint32_t cols, float lr, float c_avg, float beta,
+                          int use_schedule_free, const float *factors, const float *stats, const float *clip_factors,
+                          uint32_t offset, uint32_t head_dim, float *amax) {
+    const uint64_t len = (uint64_t)rows * cols;
+    const float radius = stats[2], dot = stats[3];
+    const float update_norm = fmaxf(stats[1], 1.0e-10f);
+    volatile float s0 = lr * radius;
+    const float step_scale = s0 / update_norm;
+    volatile float c0 = radius * radius;
+    volatile float c1 = 2.0f * step_scale;
+    volatile float c2 = c1 * dot;
+    volatile float c3 = step_scale * step_scale;
+    volatile float c4 = c3 * update_norm;
+    volatile float c5 = c4 * update_norm;
+    volatile float c6 = c0 - c2;
+    volatile float c7 = c6 + c5;
+    const float projection = radius / sqrtf(fmaxf(c7, 1.0e-10f));
+    float ax = 0.0f, ay = 0.0f;
+    for (uint64_t i = 0; i < len; ++i) {
+        uint32_t row = (uint32_t)(i / cols), col = (uint32_t)(i - (uint64_t)row * cols);
+        volatile float direction = U[i] * factors[rows >= cols ? row : col];
+        volatile float p0 = step_scale * direction;
+        volatile float p1 = z[i] - p0;
+        volatile float pz = p1 * projection;
+        volatile float nx = pz;
+        if (use_schedule_free) {
+            volatile float d1 = pz - x[i];
+            volatile float p3 = c_avg * d1;
+            nx = x[i] + p3;
+        }
+        float f = qk_factor(clip_factors, offset, head_dim, rows, cols, i);
+        if (f != 1.0f) {
+            volatile float cm = orc_bf16_bits_to_f32(momentum_bf16[i]) * f;
+            momentum_bf16[i] = orc_f32_to_bf16_bits(cm);
+            if (variance_bf16) {
+                volatile float cv = orc_bf16_bits_to_f32(variance_bf16[i]) * f;
+                volatile float cv2 = cv * f;
+                variance_bf16[i] = orc_f32_to_bf16_bits(cv2);
+            }
+            pz = pz * f; nx = nx * f;
+        }
+        volatile float d2 = nx - pz;
+        volatile float p4 = beta * d2;
+        float yy = pz + p4;
+        z[i] = pz; x[i] = nx;
+        if (y) y[i] = yy;
+        if (fabsf(nx) > ax) ax = fabsf(nx);
+        if (fabsf(yy) > ay) ay = fabsf(yy);
+    }
+    amax[0] = ax; amax[1] = ay;
+}
+
 /* sign-Muon: crates/cuda-kernels/src/gpt/optimizer/muon/fused/update/one.rs:88-167 (update_one_sign). */
 void orc_sign_update(float *grad_inout_y, uint16_t *momentum_bf16, uint16_t *variance_bf16, float *z, float *x,
                      uint64_t len, uint32_t rows, uint32_t cols, float mu, float grad_scale, int variance_adaptive,

@@ -68,6 +68,15 @@ void orc_sign_update(float *grad_inout_y, uint16_t *momentum_bf16, uint16_t *var
                      uint64_t len, uint32_t rows, uint32_t cols, float mu, float grad_scale, int variance_adaptive,
                      float lr, float wd, float c_avg, float beta, const float *factors, uint32_t offset,
                      uint32_t head_dim, float *amax);
+void orc_normuon_stats(const float *U, const float *z, uint32_t rows, uint32_t cols, float *second_momentum,
+                       float *factors, float *stats);
+void orc_update_normuon(const float *U, float *z, float *x, float *y, uint64_t len, uint32_t rows, uint32_t cols,
+                        float lr, float wd, float c_avg, float beta, const float *factors, float normuon_scale,
+                        float *amax);
+void orc_hyperball_update(const float *U, float *z, float *x, float *y, uint16_t *momentum_bf16,
+                          uint16_t *variance_bf16, uint32_t rows, uint32_t cols, float lr, float c_avg, float beta,
+                          int use_schedule_free, const float *factors, const float *stats, const float *clip_factors,
+                          uint32_t offset, uint32_t head_dim, float *amax);
 void orc_polar_gram(float *X, int n, int m, int iterations, const float *coeffs, int round_mode);
 void orc_polar_gram_tall(float *Y, int m, int n, int iterations, const float *coeffs, int round_mode);
 void orc_polar_three_product(float *X, int n, int m, int iterations, const float *coeffs,

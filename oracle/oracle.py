@@ -80,6 +80,9 @@ def lib() -> C.CDLL:
             "orc_inv_norm": (C.c_float, [C.c_float, C.c_int]),
             "orc_momentum_vs": (C.c_double, [f32p, u16p, u16p, f32p, C.c_uint64, C.c_float, C.c_float, C.c_int, C.c_float]),
             "orc_update_clip": (None, [f32p, f32p, f32p, f32p, u16p, u16p, C.c_uint64, C.c_uint32, C.c_uint32] + [C.c_float] * 4 + [f32p, C.c_uint32, C.c_uint32, f32p]),
+            "orc_normuon_stats": (None, [f32p, f32p, C.c_uint32, C.c_uint32, f32p, f32p, f32p]),
+            "orc_update_normuon": (None, [f32p, f32p, f32p, f32p, C.c_uint64, C.c_uint32, C.c_uint32] + [C.c_float] * 4 + [f32p, C.c_float, f32p]),
+            "orc_hyperball_update": (None, [f32p, f32p, f32p, f32p, u16p, u16p, C.c_uint32, C.c_uint32] + [C.c_float] * 3 + [C.c_int, f32p, f32p, f32p, C.c_uint32, C.c_uint32, f32p]),
             "orc_sign_update": (None, [f32p, u16p, u16p, f32p, f32p, C.c_uint64, C.c_uint32, C.c_uint32, C.c_float, C.c_float, C.c_int] + [C.c_float] * 4 + [f32p, C.c_uint32, C.c_uint32, f32p]),
             "orc_polar_gram": (None, [f32p, C.c_int, C.c_int, C.c_int, f32p, C.c_int]),
             "orc_polar_gram_tall": (None, [f32p, C.c_int, C.c_int, C.c_int, f32p, C.c_int]),
@@ -276,6 +279,46 @@ def sign_update(grad, momentum_bits, variance_bits, z, x, rows, cols, mu, grad_s
                           g.size, rows, cols, f(mu), f(grad_scale), int(variance_adaptive), f(lr), f(wd), f(c_avg),
                           f(beta), None if fa is None else _p(fa, C.c_float), offset, head_dim, _p(am, C.c_float))
     return g, m, v, z, x, am[0], am[1]
+
+
+def normuon_stats(U, rows, cols, second_momentum, z=None):
+    """NorMuon second moment (+ Hyperball statistics when z is given); U in storage orientation.
+    -> (second_momentum', factors, stats[normuon_scale, update_norm, radius, dot])."""
+    U = _f32(U).reshape(-1)
+    sm = _f32(second_momentum).reshape(-1).copy()
+    assert sm.size == max(rows, cols) and U.size == rows * cols
+    fa = np.zeros_like(sm); st = np.zeros(4, np.float32)
+    zz = None if z is None else _f32(z).reshape(-1)
+    lib().orc_normuon_stats(_p(U, C.c_float), None if zz is None else _p(zz, C.c_float), rows, cols,
+                            _p(sm, C.c_float), _p(fa, C.c_float), _p(st, C.c_float))
+    return sm, fa, st
+
+
+def update_normuon(U, z, x, rows, cols, lr, wd, c_avg, beta, factors, normuon_scale):
+    """Stage U with NorMuon factors -> (z', x', y, amax_x, amax_y)."""
+    U = _f32(U).reshape(-1); z = _f32(z).reshape(-1).copy(); x = _f32(x).reshape(-1).copy()
+    y = np.zeros_like(z); am = np.zeros(2, np.float32); fa = _f32(factors).reshape(-1)
+    f = np.float32
+    lib().orc_update_normuon(_p(U, C.c_float), _p(z, C.c_float), _p(x, C.c_float), _p(y, C.c_float), z.size, rows, cols,
+                             f(lr), f(wd), f(c_avg), f(beta), _p(fa, C.c_float), f(normuon_scale), _p(am, C.c_float))
+    return z, x, y, am[0], am[1]
+
+
+def hyperball_update(U, z, x, rows, cols, lr, c_avg, beta, use_schedule_free, factors, stats, momentum_bits=None,
+                     variance_bits=None, clip_factors=None, offset=0xFFFFFFFF, head_dim=0):
+    """Hyperball projection -> (z', x', y, momentum bits, variance bits, amax_x, amax_y)."""
+    U = _f32(U).reshape(-1); z = _f32(z).reshape(-1).copy(); x = _f32(x).reshape(-1).copy()
+    y = np.zeros_like(z); am = np.zeros(2, np.float32)
+    fa = _f32(factors).reshape(-1); st = _f32(stats).reshape(-1)
+    m = np.zeros(z.size, np.uint16) if momentum_bits is None else np.ascontiguousarray(momentum_bits, dtype=np.uint16).reshape(-1).copy()
+    v = None if variance_bits is None else np.ascontiguousarray(variance_bits, dtype=np.uint16).reshape(-1).copy()
+    cf = None if clip_factors is None else _f32(clip_factors).reshape(-1)
+    f = np.float32
+    lib().orc_hyperball_update(_p(U, C.c_float), _p(z, C.c_float), _p(x, C.c_float), _p(y, C.c_float), _p(m, C.c_uint16),
+                               None if v is None else _p(v, C.c_uint16), rows, cols, f(lr), f(c_avg), f(beta),
+                               int(use_schedule_free), _p(fa, C.c_float), _p(st, C.c_float),
+                               None if cf is None else _p(cf, C.c_float), offset, head_dim, _p(am, C.c_float))
+    return z, x, y, m, v, am[0], am[1]
 
 
 def inv_norm(sumsq, contract=False) -> np.float32:

@@ -164,3 +164,142 @@ def test_update_with_clip_and_variance_matches_oracle():
         assert np.array_equal(bf16_bits(s.variance).ravel(), v2)
         assert host(s.schedule_amax)[0] == ay and host(plan.scratch(k, 3))[0] == ax
     plan.close()
+
+
+def _stage_u_inputs(plan, slots, shapes, Us):
+    """Resets the amax words through the prepare stage, then places the given updates."""
+    opt = b2.OptimizerModule()
+    opt.muon_tma_prepare_polar(plan, b2.slot_table(slots), b2.MuonMegaUpdateArgs(mu=1.0, grad_scale=0.0, iterations=1))
+    for k, (r, c) in enumerate(shapes):
+        plan.scratch(k, 1).copy_(dev(Us[k]).view(r, c))
+    return opt
+
+
+def test_normuon_reference_case():
+    # crates/cuda-kernels/tests/optimizer/muon/tma_finish.rs:264-384
+    n, lr = 32, F(0.01)
+    idx = np.arange(n * n)
+    update = ((idx // n + 1).astype(F) * (idx % n % 7 + 1).astype(F) / F(128.0)).astype(F)
+    old = (F(0.01) + np.arange(n).astype(F) / F(10000.0)).astype(F)
+    slot = _slot(n, n, np.zeros(n * n, F), np.zeros(n * n, np.uint16), np.zeros(n * n, F), np.zeros(n * n, F))
+    slot.second_momentum = dev(old)
+    plan = b2.MuonPlan([(n, n)], scale_layout=b2.SCALES_RAW)
+    opt = _stage_u_inputs(plan, [slot], [(n, n)], [update])
+    args = b2.MuonMegaUpdateArgs(learning_rate=float(lr), weight_decay=0.0, average_coefficient=1.0, schedule_beta=0.4,
+                                 normuon=True)
+    opt.muon_tma_finish_update_deferred_quantization(plan, b2.slot_table([slot]), args)
+    torch.cuda.synchronize()
+    sm, fa, st = o.normuon_stats(update, n, n, old)
+    got_f, got_s = host(plan.scratch(0, 8).view(torch.float32)), host(plan.scratch(0, 9).view(torch.float32))
+    assert np.max(np.abs(host(slot.second_momentum) - sm)) <= 2e-6
+    assert np.max(np.abs(got_f - fa)) <= 2e-5 and abs(got_s[0] - st[0]) <= 2e-6
+    # elementwise stage: bit-exact given the device's own factors and scale
+    z2, x2, y2, ax, ay = o.update_normuon(update, np.zeros(n * n, F), np.zeros(n * n, F), n, n, lr, 0.0, 1.0, 0.4,
+                                          got_f, got_s[0])
+    assert np.array_equal(host(slot.z_master).ravel(), z2) and np.array_equal(host(slot.x_master).ravel(), x2)
+    assert np.array_equal(host(slot.grad).ravel(), y2) and host(slot.schedule_amax)[0] == ay
+    want = -lr * (F(0.2) * np.sqrt(F(n))) * update * np.repeat(fa, n) * st[0]
+    assert np.max(np.abs(host(slot.z_master).ravel() - want)) <= 2e-6
+    plan.close()
+
+
+@pytest.mark.parametrize("hyperball", [False, True])
+def test_normuon_and_hyperball_match_oracle_on_mixed_shapes(hyperball):
+    # tall, wide (column neurons, ragged 128-column unit), square; random data, second call chains the state
+    rng = np.random.default_rng(17)
+    shapes = [(384, 128), (96, 400), (128, 128), (0, 0), (40, 48)]
+    slots, data = [], []
+    for r, c in shapes:
+        n = r * c
+        z, x = U.weights(rng, n), U.weights(rng, n)
+        s = _slot(r, c, np.zeros(n, F), np.zeros(n, np.uint16), z, x) if n else b2.MuonSlot.allocate(0, 0, b2.SCALES_RAW)
+        sm = (0.01 + 0.02 * rng.random(max(r, c))).astype(F)
+        if n:
+            s.second_momentum = dev(sm)
+        s.learning_rate_multiplier = 0.75
+        slots.append(s)
+        data.append([z, x, sm])
+    plan = b2.MuonPlan(shapes, scale_layout=b2.SCALES_RAW)
+    table = b2.slot_table(slots)
+    for step in range(2):
+        Us = [(rng.standard_normal(r * c) * 0.05).astype(F) for r, c in shapes]
+        opt = b2.OptimizerModule()
+        opt.muon_tma_prepare_polar(plan, table, b2.MuonMegaUpdateArgs(mu=1.0, grad_scale=0.0, iterations=1))
+        for k, (r, c) in enumerate(shapes):
+            if r * c:
+                plan.scratch(k, 1).copy_(dev(Us[k]).view(r, c))
+        args = b2.MuonMegaUpdateArgs(learning_rate=0.02, weight_decay=0.0 if hyperball else 0.025,
+                                     average_coefficient=0.3, schedule_beta=0.6, normuon=True)
+        if hyperball:
+            opt.muon_tma_finish_hyperball_update_deferred_quantization(plan, table, args, use_schedule_free=step == 0)
+        else:
+            opt.muon_tma_finish_update_deferred_quantization(plan, table, args)
+        torch.cuda.synchronize()
+        for k, (s, (r, c)) in enumerate(zip(slots, shapes)):
+            if r * c == 0:
+                continue
+            z, x, sm = data[k]
+            sm2, fa, st = o.normuon_stats(Us[k], r, c, sm, z=z if hyperball else None)
+            got_f, got_s = host(plan.scratch(k, 8).view(torch.float32)), host(plan.scratch(k, 9).view(torch.float32))
+            assert np.allclose(host(s.second_momentum), sm2, rtol=2e-6, atol=0)
+            assert np.allclose(got_f, fa, rtol=2e-6, atol=0)
+            assert np.allclose(got_s[:2], st[:2], rtol=2e-6, atol=0)
+            lr = F(0.02) * F(0.75)
+            if hyperball:
+                assert np.allclose(got_s[2:], st[2:], rtol=1e-5, atol=1e-6)
+                z2, x2, y2, _, _, ax, ay = o.hyperball_update(Us[k], z, x, r, c, lr, 0.3, 0.6, step == 0, got_f, got_s)
+                assert abs(np.sqrt(np.sum(z2.astype(np.float64) ** 2)) - got_s[2]) <= 1e-5 * got_s[2]
+            else:
+                z2, x2, y2, ax, ay = o.update_normuon(Us[k], z, x, r, c, lr, 0.025, 0.3, 0.6, got_f, got_s[0])
+            assert np.array_equal(host(s.z_master).ravel(), z2) and np.array_equal(host(s.x_master).ravel(), x2)
+            assert np.array_equal(host(s.grad).ravel(), y2)
+            assert host(s.schedule_amax)[0] == ay and host(plan.scratch(k, 3))[0] == ax
+            data[k] = [z2, x2, host(s.second_momentum).copy()]
+    plan.close()
+
+
+@pytest.mark.parametrize("rows,cols", [(32, 32), (32, 64), (64, 32)])
+def test_hyperball_reference_cases(rows, cols):
+    # crates/cuda-kernels/tests/optimizer/muon/tma_finish.rs:386-676 (square with schedule-free
+    # averaging; rectangular without), tolerances as stated there
+    n = rows * cols
+    idx = np.arange(n)
+    pr, pc = min(rows, cols), max(rows, cols)
+    if rows == cols:
+        storage = (((idx // cols * 13 + idx % cols * 7) % 41).astype(F) / F(37.0) - F(0.5)).astype(F)
+        old = (F(0.02) + np.arange(pc).astype(F) / F(20000.0)).astype(F)
+        z = (((idx * 29 % 211).astype(F) - F(105.0)) / F(173.0)).astype(F)
+        x = (((idx * 17 % 157).astype(F) - F(78.0)) / F(199.0)).astype(F)
+        mult, c_avg, use_sf, tol = 0.75, 0.3, True, 3e-5
+    else:
+        polar = (((idx * 23 % 101).astype(F) - F(50.0)) / F(71.0)).astype(F).reshape(pr, pc)
+        storage = (polar.T if rows > cols else polar).reshape(-1).copy()
+        old = (F(0.015) + np.arange(pc).astype(F) / F(30000.0)).astype(F)
+        z = (((idx * 31 % 193).astype(F) - F(96.0)) / F(151.0)).astype(F)
+        x = np.zeros(n, F)
+        mult, c_avg, use_sf, tol = 0.625, 1.0, False, 4e-5
+    slot = _slot(rows, cols, np.zeros(n, F), np.zeros(n, np.uint16), z, x)
+    slot.second_momentum = dev(old)
+    slot.learning_rate_multiplier = mult
+    plan = b2.MuonPlan([(rows, cols)], scale_layout=b2.SCALES_RAW)
+    opt = _stage_u_inputs(plan, [slot], [(rows, cols)], [storage])
+    args = b2.MuonMegaUpdateArgs(learning_rate=0.018, average_coefficient=c_avg, schedule_beta=0.4)
+    opt.muon_tma_finish_hyperball_update_deferred_quantization(plan, b2.slot_table([slot]), args, use_schedule_free=use_sf)
+    torch.cuda.synchronize()
+    # host recurrence of the reference test in float64 (its float32 sums agree to the stated tolerance)
+    U2 = storage.reshape(rows, cols).astype(np.float64)
+    sumsq = (U2 ** 2).sum(axis=1 if rows >= cols else 0)
+    fac = 1.0 / np.sqrt(np.maximum(0.95 * old + (1.0 - 0.95) * sumsq / pr, 1e-10))
+    direction = (U2 * (fac[:, None] if rows >= cols else fac[None, :])).ravel()
+    radius, unorm = np.sqrt(np.sum(z.astype(np.float64) ** 2)), np.sqrt(np.sum(direction ** 2))
+    step = float(F(0.018) * F(mult)) * radius / unorm
+    cand = z - step * direction
+    ez = cand * radius / np.sqrt(np.sum(cand ** 2))
+    ex = x + c_avg * (ez - x) if use_sf else ez
+    gz, gx = host(slot.z_master).ravel(), host(slot.x_master).ravel()
+    assert np.max(np.abs(gz - ez)) <= tol and np.max(np.abs(gx - ex)) <= tol
+    assert abs(np.sqrt(np.sum(gz.astype(np.float64) ** 2)) - radius) <= radius * tol
+    assert abs(host(plan.scratch(0, 9).view(torch.float32))[1] - unorm) <= unorm * 3e-5
+    assert abs(host(slot.schedule_amax)[0] - np.max(np.abs(ez + 0.4 * (ex - ez)))) <= 3e-5
+    assert not host(slot.bytes).any()
+    plan.close()

@@ -101,3 +101,88 @@ def test_qk_clip_reference_case(input_dim, output_dim):
     assert np.array_equal(mb, o.bf16_bits(_bf16(m * f)))
     assert np.array_equal(vb, o.bf16_bits(_bf16(v * f * f)))
     assert ay == np.max(np.abs(z2 + F(0.4) * (x2 - z2)))
+
+
+def _seq_sum(v):
+    """Left-to-right float32 sum, like `iter().sum::<f32>()`."""
+    return np.cumsum(np.asarray(v, F), dtype=F)[-1]
+
+
+def test_normuon_reference_case():
+    # crates/cuda-kernels/tests/optimizer/muon/tma_finish.rs:264-384 (32 x 32, beta2 0.95)
+    n, lr = 32, F(0.01)
+    idx = np.arange(n * n)
+    update = ((idx // n + 1).astype(F) * (idx % n % 7 + 1).astype(F) / F(128.0)).astype(F)
+    old = (F(0.01) + np.arange(n).astype(F) / F(10000.0)).astype(F)
+    U = update.reshape(n, n)
+    row_sumsq = np.array([_seq_sum(U[r] ** 2) for r in range(n)], F)
+    nxt = F(0.95) * old + (F(1.0) - F(0.95)) * (row_sumsq / F(n))
+    fac = F(1.0) / np.sqrt(np.maximum(nxt, F(1e-10)))
+    raw, scaled = _seq_sum(row_sumsq), _seq_sum(row_sumsq * fac * fac)
+    scale = np.sqrt(raw / max(scaled, F(1e-10)))
+    sm, fa, st = o.normuon_stats(update, n, n, old)
+    assert np.max(np.abs(sm - nxt)) <= 2e-6 and np.max(np.abs(fa - fac)) <= 2e-5
+    assert abs(st[0] - scale) <= 2e-6
+    z2, x2, y, ax, ay = o.update_normuon(update, np.zeros(n * n, F), np.zeros(n * n, F), n, n, lr, 0.0, 1.0, 0.4,
+                                         fa, st[0])
+    want = -lr * (F(0.2) * np.sqrt(F(n))) * update * np.repeat(fac, n) * scale
+    assert np.max(np.abs(z2 - want)) <= 2e-6 and np.max(np.abs(x2 - want)) <= 2e-6
+    # NorMuon keeps the update's Frobenius norm
+    t = update * np.repeat(fa, n) * st[0]
+    assert abs(float(np.sum(t.astype(np.float64) ** 2)) - raw) <= raw * 2e-5
+
+
+def _hyperball_expected(update_storage, factors_neuron, z, x, rows, cols, lr_eff, c_avg, use_sf):
+    neuron = (np.arange(rows * cols) // cols) if rows >= cols else (np.arange(rows * cols) % cols)
+    direction = update_storage * factors_neuron[neuron]
+    radius = np.sqrt(_seq_sum(z * z))
+    update_norm = np.sqrt(_seq_sum(direction * direction))
+    step = lr_eff * radius / update_norm
+    cand = z - step * direction
+    proj = radius / np.sqrt(_seq_sum(cand * cand))
+    ez = cand * proj
+    ex = x + c_avg * (ez - x) if use_sf else ez
+    return ez.astype(F), ex.astype(F), radius, update_norm
+
+
+def test_hyperball_reference_case_square():
+    # crates/cuda-kernels/tests/optimizer/muon/tma_finish.rs:386-531
+    n = 32
+    idx = np.arange(n * n)
+    update = (((idx // n * 13 + idx % n * 7) % 41).astype(F) / F(37.0) - F(0.5)).astype(F)
+    old = (F(0.02) + np.arange(n).astype(F) / F(20000.0)).astype(F)
+    z = (((idx * 29 % 211).astype(F) - F(105.0)) / F(173.0)).astype(F)
+    x = (((idx * 17 % 157).astype(F) - F(78.0)) / F(199.0)).astype(F)
+    sm, fa, st = o.normuon_stats(update, n, n, old, z=z)
+    rows_sumsq = np.array([_seq_sum(update.reshape(n, n)[r] ** 2) for r in range(n)], F)
+    fac = F(1.0) / np.sqrt(np.maximum(F(0.95) * old + (F(1.0) - F(0.95)) * rows_sumsq / F(n), F(1e-10)))
+    ez, ex, radius, unorm = _hyperball_expected(update, fac, z, x, n, n, F(0.018) * F(0.75), F(0.3), True)
+    assert abs(st[1] - unorm) <= unorm * 3e-5 and abs(st[2] - radius) <= radius * 3e-5
+    z2, x2, y, _, _, ax, ay = o.hyperball_update(update, z, x, n, n, F(0.018) * F(0.75), 0.3, 0.4, True, fa, st)
+    assert np.max(np.abs(z2 - ez)) <= 3e-5 and np.max(np.abs(x2 - ex)) <= 3e-5
+    r2 = np.sqrt(np.sum(z2.astype(np.float64) ** 2))
+    assert abs(r2 - radius) <= radius * 3e-5
+    assert abs(ay - np.max(np.abs(ez + F(0.4) * (ex - ez)))) <= 3e-5
+
+
+@pytest.mark.parametrize("rows,cols", [(32, 64), (64, 32)])
+def test_hyperball_reference_case_rectangular(rows, cols):
+    # crates/cuda-kernels/tests/optimizer/muon/tma_finish.rs:533-676; the reference hands the update
+    # over in polar orientation [min][max], this build keeps it in storage orientation
+    n = rows * cols
+    pr, pc = min(rows, cols), max(rows, cols)
+    idx = np.arange(n)
+    polar = (((idx * 23 % 101).astype(F) - F(50.0)) / F(71.0)).astype(F).reshape(pr, pc)
+    storage = (polar.T if rows > cols else polar).reshape(-1).copy()
+    old = (F(0.015) + np.arange(pc).astype(F) / F(30000.0)).astype(F)
+    z = (((idx * 31 % 193).astype(F) - F(96.0)) / F(151.0)).astype(F)
+    col_sumsq = np.array([_seq_sum(polar[:, k] ** 2) for k in range(pc)], F)
+    fac = F(1.0) / np.sqrt(np.maximum(F(0.95) * old + (F(1.0) - F(0.95)) * col_sumsq / F(pr), F(1e-10)))
+    ez, _, radius, _ = _hyperball_expected(storage, fac, z, np.zeros(n, F), rows, cols, F(0.018) * F(0.625), F(1.0),
+                                           False)
+    sm, fa, st = o.normuon_stats(storage, rows, cols, old, z=z)
+    assert np.max(np.abs(fa - fac)) <= 2e-5
+    z2, x2, *_ = o.hyperball_update(storage, z, np.zeros(n, F), rows, cols, F(0.018) * F(0.625), 1.0, 0.4, False, fa,
+                                    st)
+    assert np.max(np.abs(z2 - ez)) <= 4e-5 and np.array_equal(z2, x2)
+    assert abs(np.sqrt(np.sum(z2.astype(np.float64) ** 2)) - radius) <= radius * 4e-5
