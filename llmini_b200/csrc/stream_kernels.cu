@@ -40,6 +40,7 @@ __device__ __forceinline__ float momentum_update_vs(float graw, float pm, float 
 }
 // Four consecutive elements of stage M in either variant.
 struct Quad { float u[4], m[4], v[4]; };
+template <int VS>
 __device__ __forceinline__ Quad momentum_quad(const float *grad, const uint16_t *mom, const uint16_t *var, uint32_t i,
                                               const MomentumParams &mp, bool streaming) {
     Quad q;
@@ -49,7 +50,7 @@ __device__ __forceinline__ Quad momentum_quad(const float *grad, const uint16_t 
     const float gr[4] = {g.x, g.y, g.z, g.w};
     const float pm[4] = {bf16_bits_to_f32(m.x & 0xffffu), bf16_bits_to_f32(m.x >> 16),
                          bf16_bits_to_f32(m.y & 0xffffu), bf16_bits_to_f32(m.y >> 16)};
-    if (mp.variance_adaptive) {
+    if (VS) {
         const uint2 v = *reinterpret_cast<const uint2 *>(var + i);
         const float pv[4] = {bf16_bits_to_f32(v.x & 0xffffu), bf16_bits_to_f32(v.x >> 16),
                              bf16_bits_to_f32(v.y & 0xffffu), bf16_bits_to_f32(v.y >> 16)};
@@ -100,7 +101,8 @@ __device__ __forceinline__ ChunkCtx chunk_ctx(const b2_muon_slot_descriptor *slo
 // Pass 1 of stages M+N: sum of u^2 per chunk: an f32 fma chain over a thread's eight values,
 // then f64 across threads, warps and chunks, so the grid shape does not change the result.  Also clears the two amax
 // words the update kernel later raises with atomicMax.
-__global__ void __launch_bounds__(kThreads)
+template <int VS>
+__global__ void __launch_bounds__(kThreads, VS ? 4 : 8)
 k_muon_sumsq(const b2_muon_slot_descriptor *slots, const uint32_t *prefix, uint32_t slot_count,
              uint32_t total_chunks, MomentumParams mp, double *partials, float *amax_x) {
     __shared__ double warp_part[kThreads / 32];
@@ -117,7 +119,7 @@ k_muon_sumsq(const b2_muon_slot_descriptor *slots, const uint32_t *prefix, uint3
         for (int h = 0; h < 2; ++h) {
             uint32_t i = base + h * (kChunk / 2) + tid * 4;
             if (i < cx.len) {
-                const Quad q = momentum_quad(grad, mom, var, i, mp, false);
+                const Quad q = momentum_quad<VS>(grad, mom, var, i, mp, false);
                 // per-thread chain as in the reference (momentum.rs:63: fma(update, update, sum));
                 // eight terms at most, so the chain's rounding stays below 1e-7 relative
 #pragma unroll
@@ -166,7 +168,8 @@ k_muon_inv_norm(const uint32_t *prefix, const double *partials, float *inv_norm)
 // Pass 2 of stages M+N: stores the BF16 momentum state and X0 = r16(u * inv) in the storage
 // layout [rows][cols] (momentum.rs:56-63 and normalize.rs:137-143; operand rounding
 // .../polar/fused/stage.rs:51-55).  No transpose: the GEMMs read either orientation.
-__global__ void __launch_bounds__(kThreads)
+template <int VS>
+__global__ void __launch_bounds__(kThreads, VS ? 4 : 8)
 k_muon_momentum_normalize(const b2_muon_slot_descriptor *slots, const uint32_t *prefix,
                           uint32_t slot_count, uint32_t total_chunks, MomentumParams mp,
                           const float *inv_norm, const uint64_t *x0_ptrs, int f16) {
@@ -184,9 +187,9 @@ k_muon_momentum_normalize(const b2_muon_slot_descriptor *slots, const uint32_t *
         for (int h = 0; h < 2; ++h) {
             uint32_t i = base + h * (kChunk / 2) + tid * 4;
             if (i < cx.len) {
-                const Quad q = momentum_quad(grad, mom, var, i, mp, true);
+                const Quad q = momentum_quad<VS>(grad, mom, var, i, mp, true);
                 *reinterpret_cast<uint2 *>(mom + i) = pack_bf16x4(q.m);
-                if (mp.variance_adaptive) *reinterpret_cast<uint2 *>(var + i) = pack_bf16x4(q.v);
+                if (VS) *reinterpret_cast<uint2 *>(var + i) = pack_bf16x4(q.v);
                 uint2 xo;
                 xo.x = pack_operands(q.u[0] * inv, q.u[1] * inv, f16);
                 xo.y = pack_operands(q.u[2] * inv, q.u[3] * inv, f16);
@@ -221,6 +224,7 @@ __device__ __forceinline__ void neuron_factors(const ChunkCtx &cx, const UpdateP
 // Stage U: crates/cuda-kernels/src/gpt/optimizer/muon/fused/update/one.rs:46-85, scale from
 // .../fused/update.rs:54, per-slot learning rate from .../fused/mega/slot.rs:26-29.
 // U is in the storage layout, so every access is a coalesced 128-bit one.
+template <int EXT>  // EXT = 1: NorMuon factors and / or qk-clip are in play
 __global__ void __launch_bounds__(kThreads)
 k_muon_update(const b2_muon_slot_descriptor *slots, const uint32_t *prefix, uint32_t slot_count,
               uint32_t total_chunks, const uint64_t *u_ptrs, float *amax_x, UpdateParams up) {
@@ -250,9 +254,9 @@ k_muon_update(const b2_muon_slot_descriptor *slots, const uint32_t *prefix, uint
                 float xx[4] = {xv.x, xv.y, xv.z, xv.w};
                 float yy[4];
                 // the four elements share a row (cols % 16 == 0), hence one clip factor
-                float nf[4];
-                neuron_factors(cx, up, i, 1, nf);
-                const float clip = qk_clip_factor(cx.d, up.d_qk_clip_factors, i);
+                float nf[4] = {1.0f, 1.0f, 1.0f, 1.0f};
+                if (EXT) neuron_factors(cx, up, i, 1, nf);
+                const float clip = EXT ? qk_clip_factor(cx.d, up.d_qk_clip_factors, i) : 1.0f;
                 if (clip != 1.0f) {  // one.rs:63-72: momentum (and variance) follow the clipped weights
                     uint16_t *mom = reinterpret_cast<uint16_t *>(cx.d.momentum);
                     const uint2 m = *reinterpret_cast<const uint2 *>(mom + i);
@@ -1135,8 +1139,12 @@ static inline int clamp_grid(uint32_t chunks, int cap) {
 cudaError_t launch_muon_sumsq(const SlotView &v, const MomentumParams &mp, double *partials, float *amax_x,
                               cudaStream_t s) {
     if (v.total_chunks == 0) return cudaSuccess;
-    k_muon_sumsq<<<clamp_grid(v.total_chunks, v.grid), kThreads, 0, s>>>(
-        v.slots, v.chunk_prefix, v.slot_count, v.total_chunks, mp, partials, amax_x);
+    if (mp.variance_adaptive)
+        k_muon_sumsq<1><<<clamp_grid(v.total_chunks, v.grid), kThreads, 0, s>>>(
+            v.slots, v.chunk_prefix, v.slot_count, v.total_chunks, mp, partials, amax_x);
+    else
+        k_muon_sumsq<0><<<clamp_grid(v.total_chunks, v.grid), kThreads, 0, s>>>(
+            v.slots, v.chunk_prefix, v.slot_count, v.total_chunks, mp, partials, amax_x);
     return cudaGetLastError();
 }
 cudaError_t launch_muon_inv_norm(const SlotView &v, const double *partials, float *inv_norm,
@@ -1148,15 +1156,23 @@ cudaError_t launch_muon_inv_norm(const SlotView &v, const double *partials, floa
 cudaError_t launch_muon_momentum_normalize(const SlotView &v, const MomentumParams &mp, const float *inv_norm,
                                            const uint64_t *x0_ptrs, int f16, cudaStream_t s) {
     if (v.total_chunks == 0) return cudaSuccess;
-    k_muon_momentum_normalize<<<clamp_grid(v.total_chunks, v.grid), kThreads, 0, s>>>(
-        v.slots, v.chunk_prefix, v.slot_count, v.total_chunks, mp, inv_norm, x0_ptrs, f16);
+    if (mp.variance_adaptive)
+        k_muon_momentum_normalize<1><<<clamp_grid(v.total_chunks, v.grid), kThreads, 0, s>>>(
+            v.slots, v.chunk_prefix, v.slot_count, v.total_chunks, mp, inv_norm, x0_ptrs, f16);
+    else
+        k_muon_momentum_normalize<0><<<clamp_grid(v.total_chunks, v.grid), kThreads, 0, s>>>(
+            v.slots, v.chunk_prefix, v.slot_count, v.total_chunks, mp, inv_norm, x0_ptrs, f16);
     return cudaGetLastError();
 }
 cudaError_t launch_muon_update(const SlotView &v, const uint64_t *u_ptrs, float *amax_x, const UpdateParams &up,
                                cudaStream_t s) {
     if (v.total_chunks == 0) return cudaSuccess;
-    k_muon_update<<<clamp_grid(v.total_chunks, v.grid), kThreads, 0, s>>>(
-        v.slots, v.chunk_prefix, v.slot_count, v.total_chunks, u_ptrs, amax_x, up);
+    if (up.normuon || up.d_qk_clip_factors)
+        k_muon_update<1><<<clamp_grid(v.total_chunks, v.grid), kThreads, 0, s>>>(
+            v.slots, v.chunk_prefix, v.slot_count, v.total_chunks, u_ptrs, amax_x, up);
+    else
+        k_muon_update<0><<<clamp_grid(v.total_chunks, v.grid), kThreads, 0, s>>>(
+            v.slots, v.chunk_prefix, v.slot_count, v.total_chunks, u_ptrs, amax_x, up);
     return cudaGetLastError();
 }
 cudaError_t launch_normuon_stats(const SlotView &v, const NeuronView &nv, const uint64_t *u_ptrs, int hyperball,
