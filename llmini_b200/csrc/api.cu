@@ -113,6 +113,7 @@ struct Layout {
     std::vector<SlotLayout> slots;
     std::vector<uint32_t> chunk_prefix;  // slot_count + 1
     std::vector<uint32_t> unit_prefix;   // slot_count + 1: NorMuon work units (8 rows or 128 columns)
+    std::vector<uint32_t> items;         // work list of the fused update + encode launch
     uint32_t total_chunks = 0;
     int bn = 256;
     int pair = 0;   // 1: two-CTA 256 x 256 tiles
@@ -120,7 +121,7 @@ struct Layout {
     int tile_m = 128;
     size_t off_prefix, off_partials, off_inv_norm, off_amax_x, off_status, off_x0_ptrs, off_u_ptrs, off_maps,
         off_problems, off_tiles_nn, off_tiles_out, off_unit_prefix, off_factor_ptrs, off_unit_partials, off_slot_stats,
-        off_meta_end, total;
+        off_items, off_fused_sync, off_meta_end, total;
     uint32_t tiles_nn = 0, tiles_out = 0;
 };
 
@@ -191,6 +192,29 @@ bool build_layout(const uint32_t *rows, const uint32_t *cols, uint32_t count, co
     L.off_prefix = take((count + 1) * sizeof(uint32_t));
     L.off_x0_ptrs = take(count * sizeof(uint64_t));
     L.off_u_ptrs = take(count * sizeof(uint64_t));
+    // Fused update + encode: a matrix's encode spans (B2_FUSED_ENCODE_SPAN chunks each) enter the list kLag update
+    // chunks into the NEXT matrix, late enough that they never wait in practice and early enough
+    // that the updated weights are still in L2.
+    {
+        const uint32_t kLag = 1200, kEncodeFlag = 0x80000000u;
+        L.items.clear();
+        int prev = -1;
+        auto push_encode = [&](int s) {
+            for (uint32_t c = L.chunk_prefix[s]; c < L.chunk_prefix[s + 1]; c += B2_FUSED_ENCODE_SPAN)
+                L.items.push_back(kEncodeFlag | c);
+        };
+        for (uint32_t s = 0; s < count; ++s) {
+            const uint32_t lo = L.chunk_prefix[s], hi = L.chunk_prefix[s + 1];
+            if (lo == hi) continue;
+            const uint32_t split = std::min(hi, lo + kLag);
+            for (uint32_t c = lo; c < split; ++c) L.items.push_back(c);
+            if (prev >= 0) push_encode(prev);
+            for (uint32_t c = split; c < hi; ++c) L.items.push_back(c);
+            prev = (int)s;
+        }
+        if (prev >= 0) push_encode(prev);
+    }
+    L.off_items = take(std::max<size_t>(L.items.size(), 1) * sizeof(uint32_t));
     L.off_unit_prefix = take((count + 1) * sizeof(uint32_t));
     L.off_factor_ptrs = take(count * sizeof(uint64_t));
     L.off_maps = take((size_t)count * kMapsPerSlot * sizeof(CUtensorMap));
@@ -220,6 +244,7 @@ bool build_layout(const uint32_t *rows, const uint32_t *cols, uint32_t count, co
     L.off_status = take(sizeof(uint32_t));
     L.off_unit_partials = take((size_t)std::max(L.unit_prefix[count], 1u) * 4 * sizeof(double));
     L.off_slot_stats = take((size_t)count * 4 * sizeof(float));
+    L.off_fused_sync = take(fused_sync_bytes(count));
     for (uint32_t s = 0; s < count; ++s) {
         SlotLayout &sl = L.slots[s];
         if (sl.len == 0) continue;
@@ -339,6 +364,7 @@ int b2_muon_plan_create(b2_muon_plan **out, const uint32_t *rows, const uint32_t
     uint64_t *up = reinterpret_cast<uint64_t *>(h + L.off_u_ptrs);
     uint64_t *fp = reinterpret_cast<uint64_t *>(h + L.off_factor_ptrs);
     std::memcpy(h + L.off_unit_prefix, L.unit_prefix.data(), (slot_count + 1) * sizeof(uint32_t));
+    if (!L.items.empty()) std::memcpy(h + L.off_items, L.items.data(), L.items.size() * sizeof(uint32_t));
     CUtensorMap *maps = reinterpret_cast<CUtensorMap *>(h + L.off_maps);
     GemmProblem *probs = reinterpret_cast<GemmProblem *>(h + L.off_problems);
     auto dmap = [&](uint32_t s, int kind) {
@@ -547,10 +573,18 @@ static int finish_impl(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_slot
         up.factor_ptrs = nv.factor_ptrs;
         up.slot_stats = nv.slot_stats;
     }
+    const int quantize_y = plan->options.quantize_target == B2_QUANTIZE_Y;
+    if (quantize && !(plan->options.reserved[2] & 16u)) {  // flag 16: measurement only, two launches
+        if (e == cudaSuccess)
+            e = launch_muon_update_encode(v, plan->at<uint32_t>(L.off_items), (uint32_t)L.items.size(),
+                                          plan->at<uint64_t>(L.off_u_ptrs), amax_x, up, quantize_y,
+                                          (int)plan->options.scale_layout, plan->ws + L.off_fused_sync,
+                                          plan->at<uint32_t>(L.off_status), s);
+        return (int)e;
+    }
     if (e == cudaSuccess) e = launch_muon_update(v, plan->at<uint64_t>(L.off_u_ptrs), amax_x, up, s);
     if (e == cudaSuccess && quantize)
-        e = launch_muon_encode(v, amax_x, plan->options.quantize_target == B2_QUANTIZE_Y,
-                               (int)plan->options.scale_layout, s);
+        e = launch_muon_encode(v, amax_x, quantize_y, (int)plan->options.scale_layout, s);
     return (int)e;
 }
 int b2_muon_finish_update(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_slots, const b2_muon_step_args *a,

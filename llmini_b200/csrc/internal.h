@@ -49,6 +49,13 @@ cudaError_t launch_muon_momentum_normalize(const SlotView &v, const MomentumPara
                                            const uint64_t *x0_ptrs, int f16, cudaStream_t s);
 cudaError_t launch_muon_update(const SlotView &v, const uint64_t *u_ptrs, float *amax_x, const UpdateParams &up,
                                cudaStream_t s);
+// Stages U and Q in one launch over an item list (bit 31: encode span of B2_FUSED_ENCODE_SPAN chunks, else update
+// chunk; low bits: flat chunk index).  `sync` is fused_sync_bytes(slot_count) of device scratch.
+#define B2_FUSED_ENCODE_SPAN 4
+size_t fused_sync_bytes(uint32_t slot_count);
+cudaError_t launch_muon_update_encode(const SlotView &v, const uint32_t *items, uint32_t item_count,
+                                      const uint64_t *u_ptrs, float *amax_x, const UpdateParams &up, int quantize_y,
+                                      int scale_layout, void *sync, uint32_t *status, cudaStream_t s);
 cudaError_t launch_normuon_stats(const SlotView &v, const NeuronView &nv, const uint64_t *u_ptrs, int hyperball,
                                  cudaStream_t s);
 cudaError_t launch_muon_hyperball_update(const SlotView &v, const uint64_t *u_ptrs, float *amax_x,

@@ -224,92 +224,107 @@ __device__ __forceinline__ void neuron_factors(const ChunkCtx &cx, const UpdateP
 // Stage U: crates/cuda-kernels/src/gpt/optimizer/muon/fused/update/one.rs:46-85, scale from
 // .../fused/update.rs:54, per-slot learning rate from .../fused/mega/slot.rs:26-29.
 // U is in the storage layout, so every access is a coalesced 128-bit one.
-template <int EXT>  // EXT = 1: NorMuon factors and / or qk-clip are in play
+// update_chunk: one 2048-value chunk, including the CTA's contribution to both maxima.
+// EXT = 1: NorMuon factors and / or qk-clip are in play.  keep_y: y is the tensor that gets
+// quantised next, so y stays cacheable and x' is streamed; otherwise the other way round.
+template <int EXT>
+__device__ __forceinline__ void update_chunk(const ChunkCtx &cx, const uint64_t *u_ptrs, float *amax_x,
+                                             const UpdateParams &up, bool keep_y, float *warp_ax, float *warp_ay) {
+    const float lr = up.lr, wd = up.wd, c_avg = up.c_avg, beta = up.beta;
+    const int tid = threadIdx.x;
+    const float *U = reinterpret_cast<const float *>(u_ptrs[cx.slot]);
+    float *z = reinterpret_cast<float *>(cx.d.z_master);
+    float *x = reinterpret_cast<float *>(cx.d.x_master);
+    float *y = reinterpret_cast<float *>(cx.d.grad);
+    const float lr_s = lr * cx.d.learning_rate_multiplier;
+    const float scale = 0.2f * sqrtf(fmaxf((float)cx.d.rows, (float)cx.d.cols));
+    const float decay = 1.0f - lr_s * wd;
+    const uint32_t base = cx.local_chunk * kChunk;
+    float ax = 0.0f, ay = 0.0f;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        uint32_t i = base + h * (kChunk / 2) + tid * 4;
+        if (i < cx.len) {
+            float4 u = ld_stream(U + i);
+            float4 zv = ld_stream(z + i);
+            float4 xv = ld_stream(x + i);
+            float uu[4] = {u.x, u.y, u.z, u.w};
+            float zz[4] = {zv.x, zv.y, zv.z, zv.w};
+            float xx[4] = {xv.x, xv.y, xv.z, xv.w};
+            float yy[4];
+            // the four elements share a row (cols % 16 == 0), hence one clip factor
+            float nf[4] = {1.0f, 1.0f, 1.0f, 1.0f};
+            if (EXT) neuron_factors(cx, up, i, 1, nf);
+            const float clip = EXT ? qk_clip_factor(cx.d, up.d_qk_clip_factors, i) : 1.0f;
+            if (clip != 1.0f) {  // one.rs:63-72: momentum (and variance) follow the clipped weights
+                uint16_t *mom = reinterpret_cast<uint16_t *>(cx.d.momentum);
+                const uint2 m = *reinterpret_cast<const uint2 *>(mom + i);
+                const float cm[4] = {bf16_bits_to_f32(m.x & 0xffffu) * clip, bf16_bits_to_f32(m.x >> 16) * clip,
+                                     bf16_bits_to_f32(m.y & 0xffffu) * clip, bf16_bits_to_f32(m.y >> 16) * clip};
+                *reinterpret_cast<uint2 *>(mom + i) = pack_bf16x4(cm);
+                if (cx.d.variance != 0) {
+                    uint16_t *var = reinterpret_cast<uint16_t *>(cx.d.variance);
+                    const uint2 v = *reinterpret_cast<const uint2 *>(var + i);
+                    const float cv[4] = {bf16_bits_to_f32(v.x & 0xffffu) * clip * clip, bf16_bits_to_f32(v.x >> 16) * clip * clip,
+                                         bf16_bits_to_f32(v.y & 0xffffu) * clip * clip, bf16_bits_to_f32(v.y >> 16) * clip * clip};
+                    *reinterpret_cast<uint2 *>(var + i) = pack_bf16x4(cv);
+                }
+            }
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float upd = scale * (uu[e] * 1.0f * nf[e]);
+                float nz = zz[e] * decay - lr_s * upd;
+                float nx = xx[e] + c_avg * (nz - xx[e]);
+                if (clip != 1.0f) {
+                    nz *= clip;
+                    nx *= clip;
+                }
+                float sv = nz + beta * (nx - nz);
+                zz[e] = nz;
+                xx[e] = nx;
+                yy[e] = sv;
+                ax = fmaxf(ax, fabsf(nx));
+                ay = fmaxf(ay, fabsf(sv));
+            }
+            const float4 xo = make_float4(xx[0], xx[1], xx[2], xx[3]), yo = make_float4(yy[0], yy[1], yy[2], yy[3]);
+            st_stream(z + i, make_float4(zz[0], zz[1], zz[2], zz[3]));
+            // the tensor that the encode pass reads again stays cacheable
+            if (keep_y) {
+                st_stream(x + i, xo);
+                *reinterpret_cast<float4 *>(y + i) = yo;
+            } else {
+                *reinterpret_cast<float4 *>(x + i) = xo;
+                st_stream(y + i, yo);
+            }
+        }
+    }
+    ax = warp_max(ax);
+    ay = warp_max(ay);
+    if ((tid & 31) == 0) {
+        warp_ax[tid >> 5] = ax;
+        warp_ay[tid >> 5] = ay;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        float mx = 0.0f, my = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kThreads / 32; ++w) {
+            mx = fmaxf(mx, warp_ax[w]);
+            my = fmaxf(my, warp_ay[w]);
+        }
+        atomic_max_nonneg(amax_x + cx.slot, mx);
+        atomic_max_nonneg(reinterpret_cast<float *>(cx.d.schedule_amax), my);
+    }
+}
+
+template <int EXT>
 __global__ void __launch_bounds__(kThreads)
 k_muon_update(const b2_muon_slot_descriptor *slots, const uint32_t *prefix, uint32_t slot_count,
               uint32_t total_chunks, const uint64_t *u_ptrs, float *amax_x, UpdateParams up) {
     __shared__ float warp_ax[kThreads / 32], warp_ay[kThreads / 32];
-    const float lr = up.lr, wd = up.wd, c_avg = up.c_avg, beta = up.beta;
-    const int tid = threadIdx.x;
     for (uint32_t c = blockIdx.x; c < total_chunks; c += gridDim.x) {
         ChunkCtx cx = chunk_ctx(slots, prefix, slot_count, c);
-        const float *U = reinterpret_cast<const float *>(u_ptrs[cx.slot]);
-        float *z = reinterpret_cast<float *>(cx.d.z_master);
-        float *x = reinterpret_cast<float *>(cx.d.x_master);
-        float *y = reinterpret_cast<float *>(cx.d.grad);
-        const float lr_s = lr * cx.d.learning_rate_multiplier;
-        const float scale = 0.2f * sqrtf(fmaxf((float)cx.d.rows, (float)cx.d.cols));
-        const float decay = 1.0f - lr_s * wd;
-        const uint32_t base = cx.local_chunk * kChunk;
-        float ax = 0.0f, ay = 0.0f;
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            uint32_t i = base + h * (kChunk / 2) + tid * 4;
-            if (i < cx.len) {
-                float4 u = ld_stream(U + i);
-                float4 zv = ld_stream(z + i);
-                float4 xv = ld_stream(x + i);
-                float uu[4] = {u.x, u.y, u.z, u.w};
-                float zz[4] = {zv.x, zv.y, zv.z, zv.w};
-                float xx[4] = {xv.x, xv.y, xv.z, xv.w};
-                float yy[4];
-                // the four elements share a row (cols % 16 == 0), hence one clip factor
-                float nf[4] = {1.0f, 1.0f, 1.0f, 1.0f};
-                if (EXT) neuron_factors(cx, up, i, 1, nf);
-                const float clip = EXT ? qk_clip_factor(cx.d, up.d_qk_clip_factors, i) : 1.0f;
-                if (clip != 1.0f) {  // one.rs:63-72: momentum (and variance) follow the clipped weights
-                    uint16_t *mom = reinterpret_cast<uint16_t *>(cx.d.momentum);
-                    const uint2 m = *reinterpret_cast<const uint2 *>(mom + i);
-                    const float cm[4] = {bf16_bits_to_f32(m.x & 0xffffu) * clip, bf16_bits_to_f32(m.x >> 16) * clip,
-                                         bf16_bits_to_f32(m.y & 0xffffu) * clip, bf16_bits_to_f32(m.y >> 16) * clip};
-                    *reinterpret_cast<uint2 *>(mom + i) = pack_bf16x4(cm);
-                    if (cx.d.variance != 0) {
-                        uint16_t *var = reinterpret_cast<uint16_t *>(cx.d.variance);
-                        const uint2 v = *reinterpret_cast<const uint2 *>(var + i);
-                        const float cv[4] = {bf16_bits_to_f32(v.x & 0xffffu) * clip * clip, bf16_bits_to_f32(v.x >> 16) * clip * clip,
-                                             bf16_bits_to_f32(v.y & 0xffffu) * clip * clip, bf16_bits_to_f32(v.y >> 16) * clip * clip};
-                        *reinterpret_cast<uint2 *>(var + i) = pack_bf16x4(cv);
-                    }
-                }
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    float upd = scale * (uu[e] * 1.0f * nf[e]);
-                    float nz = zz[e] * decay - lr_s * upd;
-                    float nx = xx[e] + c_avg * (nz - xx[e]);
-                    if (clip != 1.0f) {
-                        nz *= clip;
-                        nx *= clip;
-                    }
-                    float sv = nz + beta * (nx - nz);
-                    zz[e] = nz;
-                    xx[e] = nx;
-                    yy[e] = sv;
-                    ax = fmaxf(ax, fabsf(nx));
-                    ay = fmaxf(ay, fabsf(sv));
-                }
-                st_stream(z + i, make_float4(zz[0], zz[1], zz[2], zz[3]));
-                // x' is read again by the encode kernel: keep it cacheable
-                *reinterpret_cast<float4 *>(x + i) = make_float4(xx[0], xx[1], xx[2], xx[3]);
-                *reinterpret_cast<float4 *>(y + i) = make_float4(yy[0], yy[1], yy[2], yy[3]);
-            }
-        }
-        ax = warp_max(ax);
-        ay = warp_max(ay);
-        if ((tid & 31) == 0) {
-            warp_ax[tid >> 5] = ax;
-            warp_ay[tid >> 5] = ay;
-        }
-        __syncthreads();
-        if (tid == 0) {
-            float mx = 0.0f, my = 0.0f;
-#pragma unroll
-            for (int w = 0; w < kThreads / 32; ++w) {
-                mx = fmaxf(mx, warp_ax[w]);
-                my = fmaxf(my, warp_ay[w]);
-            }
-            atomic_max_nonneg(amax_x + cx.slot, mx);
-            atomic_max_nonneg(reinterpret_cast<float *>(cx.d.schedule_amax), my);
-        }
+        update_chunk<EXT>(cx, u_ptrs, amax_x, up, false, warp_ax, warp_ay);
         __syncthreads();
     }
 }
@@ -660,7 +675,7 @@ k_muon_sign_update(const b2_muon_slot_descriptor *slots, const uint32_t *prefix,
 // ---------------------------------------------------------------------------------------------
 constexpr int kEncodeThreads = kChunk / 16;
 
-template <int MODE>
+template <int MODE, int THREADS = kEncodeThreads, bool L2_ONLY = false>
 __device__ __forceinline__ void encode_chunk(const float *src, const float *z, const float *xm,
                                              float beta, uint32_t len, uint32_t base, float gs,
                                              uint8_t *fp4, uint8_t *scales, int scale_layout,
@@ -668,7 +683,7 @@ __device__ __forceinline__ void encode_chunk(const float *src, const float *z, c
     // Each warp owns 32 consecutive groups = 2048 contiguous bytes.  It reads them with four
     // fully coalesced 128-bit loads per lane, parks them in shared memory (16-byte slots XOR-ed
     // with the group number so neither side conflicts) and every lane picks up its own group.
-    __shared__ float4 stage[kEncodeThreads / 32][128];
+    __shared__ float4 stage[THREADS / 32][128];
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const uint32_t group = base / 16 + threadIdx.x;
@@ -683,7 +698,7 @@ __device__ __forceinline__ void encode_chunk(const float *src, const float *z, c
         float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
         if (e < len) {
             if (MODE == 0) {
-                t = ld_stream(src + e);
+                t = L2_ONLY ? __ldcg(reinterpret_cast<const float4 *>(src + e)) : ld_stream(src + e);
             } else {
                 float4 zv = ld_stream(z + e), xv = ld_stream(xm + e);
                 t.x = zv.x + beta * (xv.x - zv.x);
@@ -755,6 +770,112 @@ k_muon_encode(const b2_muon_slot_descriptor *slots, const uint32_t *prefix, uint
 // Stand-alone flat quantiser: `fp32_to_nvfp4_four_six_kernel`
 // (crates/cuda-kernels/src/utils/nvfp4/quant/kernels/four_six.rs:104-152) and
 // `schedule_free_four_six_kernel` (.../optimizer/schedule_free/four_six.rs:12-54).
+// Stages U and Q of every slot in ONE launch.  The tensor scale of a matrix depends on the maximum
+// over the whole matrix, so its blocks can only be encoded once every update chunk of that matrix
+// is done.  Work items (update chunk / encode span of 4096 values) sit in a list built with the
+// plan, ordered so that the encode items of a matrix follow its own update items by a few hundred
+// positions: the updated weights are then still in L2 when they are read back, and DRAM sees each
+// weight once.  CTAs claim items in list order through an atomic ticket; an encode item waits
+// (bounded) on its matrix's completion counter.  Every item such a wait depends on has a smaller
+// ticket, hence is held by a running CTA and never waits itself, so the kernel makes progress
+// whatever the number of resident CTAs.
+__device__ __forceinline__ uint64_t stream_globaltimer() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ uint32_t ld_acquire_u32(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+struct FusedSync {
+    uint32_t ticket;
+    uint32_t abort;
+    uint32_t reserved[2];
+    uint32_t done[1];  // slot_count entries: update chunks of the slot that are complete
+};
+constexpr uint32_t kItemEncode = 0x80000000u;
+constexpr uint32_t kEncodeSpan = B2_FUSED_ENCODE_SPAN;  // chunks per encode item (list built by the plan)
+constexpr uint64_t kFusedWaitNs = 2000000000ull;
+
+template <int EXT>
+__global__ void __launch_bounds__(kThreads)
+k_muon_update_encode(const b2_muon_slot_descriptor *slots, const uint32_t *prefix, uint32_t slot_count,
+                     const uint32_t *items, uint32_t item_count, const uint64_t *u_ptrs, float *amax_x,
+                     UpdateParams up, int quantize_y, int scale_layout, FusedSync *sync, uint32_t *status) {
+    __shared__ float warp_ax[kThreads / 32], warp_ay[kThreads / 32];
+    __shared__ uint32_t s_ticket[2], s_ok;
+    const int tid = threadIdx.x;
+    if (tid == 0) s_ticket[0] = atomicAdd(&sync->ticket, 1u);
+    __syncthreads();
+    for (uint32_t it = 0;; ++it) {
+        const uint32_t t = s_ticket[it & 1];
+        if (t >= item_count) break;
+        // claim the next item now and park it in a register; its latency hides behind this item
+        uint32_t next_ticket = 0;
+        if (tid == 0) next_ticket = atomicAdd(&sync->ticket, 1u);
+        const uint32_t item = items[t];
+        const uint32_t c = item & ~kItemEncode;
+        ChunkCtx cx = chunk_ctx(slots, prefix, slot_count, c);
+        if (!(item & kItemEncode)) {
+            update_chunk<EXT>(cx, u_ptrs, amax_x, up, quantize_y != 0, warp_ax, warp_ay);
+            // Publish.  The barrier orders every thread's stores before thread 0's fence, which is
+            // cumulative; thread 0 raised the two maxima before it.  (Letting the other warps run
+            // ahead of the fence, or publishing one item late, both measured slower.)
+            __syncthreads();
+            if (tid == 0) {
+                __threadfence();
+                atomicAdd(&sync->done[cx.slot], 1u);
+            }
+        } else {
+            if (tid == 0) {
+                const uint32_t need = prefix[cx.slot + 1] - prefix[cx.slot];
+                uint32_t ok = 1;
+                if (ld_acquire_u32(&sync->done[cx.slot]) < need) {
+                    const uint64_t start = stream_globaltimer();
+                    while (ld_acquire_u32(&sync->done[cx.slot]) < need) {
+                        if (ld_acquire_u32(&sync->abort) != 0 || stream_globaltimer() - start > kFusedWaitNs) {
+                            ok = 0;
+                            break;
+                        }
+                        __nanosleep(200);
+                    }
+                }
+                if (!ok) {
+                    atomicExch(&sync->abort, 1u);
+                    atomicExch(status, 1u);
+                }
+                __threadfence();
+                s_ok = ok;
+            }
+            __syncthreads();
+            if (!s_ok) break;   // uniform: s_ok is shared
+            const float *src = reinterpret_cast<const float *>(quantize_y ? cx.d.grad : cx.d.x_master);
+            const float amax = __ldcg(quantize_y ? reinterpret_cast<const float *>(cx.d.schedule_amax)
+                                                 : amax_x + cx.slot);
+            const float gs = four_six_global_scale(amax);
+            uint8_t *scales = reinterpret_cast<uint8_t *>(cx.d.scales);
+            uint32_t k = 0, rows = 0;
+            if (scale_layout == B2_SCALES_CSF) {
+                k = reinterpret_cast<const uint32_t *>(scales)[0];
+                rows = reinterpret_cast<const uint32_t *>(scales)[1];
+            }
+            if (cx.local_chunk == 0 && tid == 0) *reinterpret_cast<float *>(cx.d.global_scale) = gs;
+            // 256 threads x one 16-value group per call: kEncodeSpan chunks of the same slot
+#pragma unroll
+            for (uint32_t part = 0; part < kEncodeSpan / 2; ++part) {
+                const uint32_t base = (cx.local_chunk + 2 * part) * kChunk;
+                if (base < cx.len)
+                    encode_chunk<0, kThreads, true>(src, nullptr, nullptr, 0.f, cx.len, base, gs,
+                                                    reinterpret_cast<uint8_t *>(cx.d.bytes), scales, scale_layout, k, rows);
+            }
+        }
+        if (tid == 0) s_ticket[(it + 1) & 1] = next_ticket;
+        __syncthreads();
+    }
+}
+
 template <int MODE>
 __global__ void __launch_bounds__(kEncodeThreads)
 k_quantize_flat(const float *src, const float *z, const float *xm, float beta, const float *amax,
@@ -1173,6 +1294,24 @@ cudaError_t launch_muon_update(const SlotView &v, const uint64_t *u_ptrs, float 
     else
         k_muon_update<0><<<clamp_grid(v.total_chunks, v.grid), kThreads, 0, s>>>(
             v.slots, v.chunk_prefix, v.slot_count, v.total_chunks, u_ptrs, amax_x, up);
+    return cudaGetLastError();
+}
+size_t fused_sync_bytes(uint32_t slot_count) { return sizeof(FusedSync) + sizeof(uint32_t) * slot_count; }
+cudaError_t launch_muon_update_encode(const SlotView &v, const uint32_t *items, uint32_t item_count,
+                                      const uint64_t *u_ptrs, float *amax_x, const UpdateParams &up, int quantize_y,
+                                      int scale_layout, void *sync, uint32_t *status, cudaStream_t s) {
+    if (item_count == 0) return cudaSuccess;
+    cudaError_t e = cudaMemsetAsync(sync, 0, fused_sync_bytes(v.slot_count), s);
+    if (e != cudaSuccess) return e;
+    const int grid = clamp_grid(item_count, v.grid);
+    if (up.normuon || up.d_qk_clip_factors)
+        k_muon_update_encode<1><<<grid, kThreads, 0, s>>>(v.slots, v.chunk_prefix, v.slot_count, items, item_count,
+                                                         u_ptrs, amax_x, up, quantize_y, scale_layout,
+                                                         static_cast<FusedSync *>(sync), status);
+    else
+        k_muon_update_encode<0><<<grid, kThreads, 0, s>>>(v.slots, v.chunk_prefix, v.slot_count, items, item_count,
+                                                         u_ptrs, amax_x, up, quantize_y, scale_layout,
+                                                         static_cast<FusedSync *>(sync), status);
     return cudaGetLastError();
 }
 cudaError_t launch_normuon_stats(const SlotView &v, const NeuronView &nv, const uint64_t *u_ptrs, int hyperball,

@@ -303,3 +303,54 @@ def test_hyperball_reference_cases(rows, cols):
     assert abs(host(slot.schedule_amax)[0] - np.max(np.abs(ez + 0.4 * (ex - ez)))) <= 3e-5
     assert not host(slot.bytes).any()
     plan.close()
+
+
+@pytest.mark.parametrize("target", [b2.QUANTIZE_X, b2.QUANTIZE_Y])
+@pytest.mark.parametrize("ext", [False, True])
+def test_fused_update_encode_equals_two_launches(target, ext):
+    # the one-launch update + encode (ticketed work list) against the two-kernel form (debug flag 16):
+    # masters, y, maxima, tensor scales, codes and block scales bit for bit, on matrices of very
+    # different sizes (odd chunk counts, one chunk, an empty slot)
+    rng = np.random.default_rng(23)
+    shapes = [(768, 768), (40, 48), (0, 0), (2304, 768), (128, 1040), (16, 16), (768, 3072)]
+    factors = dev((0.25 + 0.75 * rng.random(64)).astype(F))
+    results = []
+    for flags in (0, 16):
+        rng2 = np.random.default_rng(29)
+        slots = []
+        for k, (r, c) in enumerate(shapes):
+            n = r * c
+            s = b2.MuonSlot.allocate(r, c, b2.SCALES_RAW)
+            if n:
+                s.z_master.copy_(dev(U.weights(rng2, n)).view_as(s.z_master))
+                s.x_master.copy_(dev(U.weights(rng2, n)).view_as(s.x_master))
+                s.momentum.copy_(bf16_from_bits(o.bf16_bits(U.weights(rng2, n, 1e-2))).view_as(s.momentum))
+                s.second_momentum = dev((0.01 + 0.02 * rng2.random(max(r, c))).astype(F))
+                if ext and k == 3:
+                    s.qk_clip_factor_offset, s.qk_clip_head_dim = 0, 64
+            s.learning_rate_multiplier = 1.0 + 0.25 * k
+            slots.append(s)
+        plan = b2.MuonPlan(shapes, scale_layout=b2.SCALES_RAW, quantize_target=target, debug_flags=flags)
+        table = b2.slot_table(slots)
+        opt = b2.OptimizerModule()
+        opt.muon_tma_prepare_polar(plan, table, b2.MuonMegaUpdateArgs(mu=1.0, grad_scale=0.0, iterations=1))
+        for k, (r, c) in enumerate(shapes):
+            if r * c:
+                plan.scratch(k, 1).copy_(dev((rng2.standard_normal(r * c) * 0.05).astype(F)).view(r, c))
+        args = b2.MuonMegaUpdateArgs(learning_rate=0.02, weight_decay=0.025, average_coefficient=0.3, schedule_beta=0.6,
+                                     normuon=ext, qk_clip_factors=factors if ext else None)
+        opt.muon_tma_finish_update(plan, table, args)
+        torch.cuda.synchronize()
+        assert plan.status() == 0
+        out = []
+        for k, (s, (r, c)) in enumerate(zip(slots, shapes)):
+            if r * c == 0:
+                continue
+            out.append([host(t).copy() for t in (s.z_master, s.x_master, s.grad, s.schedule_amax, s.global_scale,
+                                                 s.bytes, s.scales, plan.scratch(k, 3))] + [bf16_bits(s.momentum)])
+        results.append(out)
+        plan.close()
+    for a, b in zip(*results):
+        for u, v in zip(a, b):
+            assert np.array_equal(u, v)
+        assert a[5].any() and a[4][0] > 0
