@@ -232,7 +232,7 @@ def run_gpu(args):
         if layout == b2.SCALES_CSF:
             s.scales.copy_(b2.zero_scales(r, c, dev))
         slots.append(s)
-    plan = b2.MuonPlan(my_shapes, scale_layout=layout, device=dev) if my_shapes else None
+    plan = b2.MuonPlan(my_shapes, scale_layout=layout, device=dev, debug_flags=args.plan_flags) if my_shapes else None
     table = b2.slot_table(slots, dev) if slots else None
     opt = b2.OptimizerModule()
     margs = b2.MuonMegaUpdateArgs(coefficients=np.tile(np.asarray([3.4445, -4.7750, 2.0315], np.float32), (5, 1)), **HP)
@@ -488,6 +488,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a CUDA graph replay")
+    ap.add_argument("--plan-flags", type=int, default=0,
+                    help="measurement only: kernel flags of the plan (16 = update and encode as two launches)")
     ap.add_argument("--sweep", action="store_true", help="update+quantise bandwidth sweep over [R, 4096] tensors")
     args = ap.parse_args()
     if args.sweep:

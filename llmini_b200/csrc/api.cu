@@ -463,6 +463,8 @@ int b2_muon_plan_create(b2_muon_plan **out, const uint32_t *rows, const uint32_t
     }
     e = cudaMemcpyAsync(p->ws, h, L.off_meta_end, cudaMemcpyHostToDevice, as_stream(stream));
     if (e == cudaSuccess) e = cudaMemsetAsync(p->ws + L.off_status, 0, sizeof(uint32_t), as_stream(stream));
+    if (e == cudaSuccess)
+        e = cudaMemsetAsync(p->ws + L.off_fused_sync, 0, fused_sync_bytes(slot_count), as_stream(stream));
     if (e != cudaSuccess) { delete p; return (int)e; }
     *out = p;
     return B2_SUCCESS;

@@ -50,7 +50,8 @@ cudaError_t launch_muon_momentum_normalize(const SlotView &v, const MomentumPara
 cudaError_t launch_muon_update(const SlotView &v, const uint64_t *u_ptrs, float *amax_x, const UpdateParams &up,
                                cudaStream_t s);
 // Stages U and Q in one launch over an item list (bit 31: encode span of B2_FUSED_ENCODE_SPAN chunks, else update
-// chunk; low bits: flat chunk index).  `sync` is fused_sync_bytes(slot_count) of device scratch.
+// chunk; low bits: flat chunk index).  `sync` is fused_sync_bytes(slot_count) of device scratch,
+// zeroed once by the owner; every launch leaves it zeroed again.
 #define B2_FUSED_ENCODE_SPAN 4
 size_t fused_sync_bytes(uint32_t slot_count);
 cudaError_t launch_muon_update_encode(const SlotView &v, const uint32_t *items, uint32_t item_count,

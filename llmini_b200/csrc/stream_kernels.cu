@@ -241,13 +241,23 @@ __device__ __forceinline__ void update_chunk(const ChunkCtx &cx, const uint64_t 
     const float decay = 1.0f - lr_s * wd;
     const uint32_t base = cx.local_chunk * kChunk;
     float ax = 0.0f, ay = 0.0f;
+    // all six loads of the thread go out before the first store: the stores below could alias
+    // them as far as the compiler knows, so it would not hoist the second half by itself
+    float4 lu[2], lz[2], lx[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const uint32_t i = base + h * (kChunk / 2) + tid * 4;
+        if (i < cx.len) {
+            lu[h] = ld_stream(U + i);
+            lz[h] = ld_stream(z + i);
+            lx[h] = ld_stream(x + i);
+        }
+    }
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         uint32_t i = base + h * (kChunk / 2) + tid * 4;
         if (i < cx.len) {
-            float4 u = ld_stream(U + i);
-            float4 zv = ld_stream(z + i);
-            float4 xv = ld_stream(x + i);
+            const float4 u = lu[h], zv = lz[h], xv = lx[h];
             float uu[4] = {u.x, u.y, u.z, u.w};
             float zz[4] = {zv.x, zv.y, zv.z, zv.w};
             float xx[4] = {xv.x, xv.y, xv.z, xv.w};
@@ -318,7 +328,7 @@ __device__ __forceinline__ void update_chunk(const ChunkCtx &cx, const uint64_t 
 }
 
 template <int EXT>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 5)
 k_muon_update(const b2_muon_slot_descriptor *slots, const uint32_t *prefix, uint32_t slot_count,
               uint32_t total_chunks, const uint64_t *u_ptrs, float *amax_x, UpdateParams up) {
     __shared__ float warp_ax[kThreads / 32], warp_ay[kThreads / 32];
@@ -789,10 +799,11 @@ __device__ __forceinline__ uint32_t ld_acquire_u32(const uint32_t *p) {
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
-struct FusedSync {
+struct FusedSync {   // all zero between launches: the last CTA to leave clears it again
     uint32_t ticket;
     uint32_t abort;
-    uint32_t reserved[2];
+    uint32_t exited;
+    uint32_t reserved;
     uint32_t done[1];  // slot_count entries: update chunks of the slot that are complete
 };
 constexpr uint32_t kItemEncode = 0x80000000u;
@@ -800,7 +811,7 @@ constexpr uint32_t kEncodeSpan = B2_FUSED_ENCODE_SPAN;  // chunks per encode ite
 constexpr uint64_t kFusedWaitNs = 2000000000ull;
 
 template <int EXT>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 5)
 k_muon_update_encode(const b2_muon_slot_descriptor *slots, const uint32_t *prefix, uint32_t slot_count,
                      const uint32_t *items, uint32_t item_count, const uint64_t *u_ptrs, float *amax_x,
                      UpdateParams up, int quantize_y, int scale_layout, FusedSync *sync, uint32_t *status) {
@@ -873,6 +884,16 @@ k_muon_update_encode(const b2_muon_slot_descriptor *slots, const uint32_t *prefi
         }
         if (tid == 0) s_ticket[(it + 1) & 1] = next_ticket;
         __syncthreads();
+    }
+    // leave the words as the next launch expects them (a memset node per step costs more)
+    if (tid == 0) {
+        __threadfence();
+        if (atomicAdd(&sync->exited, 1u) == gridDim.x - 1) {
+            for (uint32_t k = 0; k < slot_count; ++k) sync->done[k] = 0;
+            sync->ticket = 0;
+            sync->abort = 0;
+            sync->exited = 0;
+        }
     }
 }
 
@@ -1301,8 +1322,6 @@ cudaError_t launch_muon_update_encode(const SlotView &v, const uint32_t *items, 
                                       const uint64_t *u_ptrs, float *amax_x, const UpdateParams &up, int quantize_y,
                                       int scale_layout, void *sync, uint32_t *status, cudaStream_t s) {
     if (item_count == 0) return cudaSuccess;
-    cudaError_t e = cudaMemsetAsync(sync, 0, fused_sync_bytes(v.slot_count), s);
-    if (e != cudaSuccess) return e;
     const int grid = clamp_grid(item_count, v.grid);
     if (up.normuon || up.d_qk_clip_factors)
         k_muon_update_encode<1><<<grid, kThreads, 0, s>>>(v.slots, v.chunk_prefix, v.slot_count, items, item_count,
