@@ -273,8 +273,7 @@ def run_gpu(args):
     ev = lambda: torch.cuda.Event(enable_timing=True)
     stage_events = []
 
-    def step(record=False):
-        marks = [ev() for _ in range(5)] if record else None
+    def step_muon(record=False, marks=None):
         if record: marks[0].record(stream)
         if plan is not None:
             opt.muon_tma_prepare_polar(plan, table, margs)
@@ -285,12 +284,19 @@ def run_gpu(args):
         if plan is not None:
             opt.muon_tma_finish_update(plan, table, margs)
         if record: marks[3].record(stream)
+
+    def step_adam(record=False, marks=None):
         if adam_sets:
             opt.apply_adamw_update_multi(adam_table, adam_count, adam_chunks, **ADAM)
         if record: marks[4].record(stream)
         if world > 1:
             n = arena.bytes_per_rank
             dist.all_gather_into_tensor(arena_v, arena_v[rank * n:(rank + 1) * n])
+
+    def step(record=False):
+        marks = [ev() for _ in range(5)] if record else None
+        step_muon(record, marks)
+        step_adam(record, marks)
         if record: stage_events.append(marks)
 
     def barrier():
@@ -326,7 +332,7 @@ def run_gpu(args):
     # The whole step is stream-ordered with no host synchronisation, so it is captured once in a
     # CUDA graph and replayed: the headline number is the replay, the per-stage breakdown (and
     # the roofline figure) comes from the eager pass above, whose events sit between stages.
-    graph = None
+    graph = graph_muon = graph_adam = None
     ms_step = ms_eager
     if not args.no_graph:
         try:
@@ -335,11 +341,23 @@ def run_gpu(args):
                 step()
             graph.replay()
             ms_step = timed(graph.replay, args.steps)
+            # the two halves on their own, for the pipelined end-to-end step below
+            graph_muon, graph_adam = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph_muon):
+                step_muon()
+            with torch.cuda.graph(graph_adam):
+                step_adam()
         except Exception as exc:  # capture is an optimisation; report why it was skipped
-            graph = None
+            graph = graph_muon = graph_adam = None
             graph_error = repr(exc)[:200]
 
     # ---- end to end: host gradients in, packed weights out, every step ----
+    # What a caller with host-resident gradients does with the same public calls: the matrix
+    # gradients go up first; while the Muon stages run, a second stream brings up the AdamW
+    # gradients, and a third takes the packed matrices down (PCIe is full duplex); AdamW and its
+    # outputs follow.  Every copy is inside the timed region; the step ends when the last byte is on
+    # the host.
+    n_slots = len(slots)
     grad_dev = [s.grad for s in slots] + [t["grad"] for _, t in adam_sets]
     grad_host = [torch.empty(g.shape, dtype=g.dtype, pin_memory=True).copy_(g) for g in grad_dev]
     n_mine = arena.bytes_per_rank
@@ -348,16 +366,39 @@ def run_gpu(args):
     out_host = [torch.empty(o_.shape, dtype=o_.dtype, pin_memory=True) for o_ in out_dev]
     h2d = sum(g.numel() * g.element_size() for g in grad_dev)
     d2h = sum(o_.numel() * o_.element_size() for o_ in out_dev)
+    up_stream, down_stream = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+    adam_done = torch.cuda.Event()
+    adam_done.record(stream)
 
     def step_e2e():
-        for gd, gh in zip(grad_dev, grad_host):
+        for gd, gh in zip(grad_dev[:n_slots], grad_host[:n_slots]):
             gd.copy_(gh, non_blocking=True)
-        if graph is not None:
-            graph.replay()
+        up_stream.wait_event(adam_done)          # the previous step's AdamW has consumed its gradients
+        with torch.cuda.stream(up_stream):
+            for gd, gh in zip(grad_dev[n_slots:], grad_host[n_slots:]):
+                gd.copy_(gh, non_blocking=True)
+            adam_up = torch.cuda.Event()
+            adam_up.record(up_stream)
+        if graph_muon is not None:
+            graph_muon.replay()
         else:
-            step()
-        for od, oh in zip(out_dev, out_host):
+            step_muon()
+        muon_done = torch.cuda.Event()
+        muon_done.record(stream)
+        down_stream.wait_event(muon_done)
+        with torch.cuda.stream(down_stream):
+            out_host[0].copy_(out_dev[0], non_blocking=True)
+            down_done = torch.cuda.Event()
+            down_done.record(down_stream)
+        stream.wait_event(adam_up)
+        if graph_adam is not None:
+            graph_adam.replay()
+        else:
+            step_adam()
+        adam_done.record(stream)
+        for od, oh in zip(out_dev[1:], out_host[1:]):
             oh.copy_(od, non_blocking=True)
+        stream.wait_event(down_done)
 
     step_e2e()
     ms_e2e = timed(step_e2e, args.steps)
@@ -383,12 +424,12 @@ def run_gpu(args):
         # Release the captured graph before the communicator: a graph that still holds NCCL
         # kernels can keep the communicator's teardown waiting.  A watchdog ends the process if
         # teardown stalls anyway; by then the result line has been printed.
-        nonlocal graph
+        nonlocal graph, graph_muon, graph_adam
         if world == 1:
             return
         import threading
         threading.Timer(30.0, lambda: os._exit(0)).start()
-        graph = None
+        graph = graph_muon = graph_adam = None
         torch.cuda.synchronize()
         dist.barrier()
         dist.destroy_process_group()
