@@ -64,7 +64,13 @@ typedef struct b2_muon_slot_descriptor {
 } b2_muon_slot_descriptor;
 
 enum { B2_OPERAND_BF16 = 0, B2_OPERAND_F16 = 1 };
-enum { B2_SCALES_CSF = 0, B2_SCALES_RAW = 1 };
+enum { B2_SCALES_CSF = 0, B2_SCALES_RAW = 1,
+       B2_SCALES_SM100 = 2 /* the block-scale operand layout of sm_100a's `tcgen05.mma
+                              kind::mxf4nvf4.block_scale` (what cuBLASLt calls VEC16_UE4M3): 512-byte
+                              tiles of 128 rows x 4 scale columns, tile (row/128, kblock/4) row-major,
+                              byte (row%32)*16 + (row%128)/32*4 + kblock%4 inside a tile; rows padded
+                              to 128 and scale columns to 4 (padding bytes are never written: zero the
+                              buffer once).  Accepted by the Muon plan only */ };
 enum { B2_QUANTIZE_X = 0, B2_QUANTIZE_Y = 1 };
 
 typedef struct b2_muon_options {
@@ -200,6 +206,13 @@ int b2_fp32_to_nvfp4_four_six(const float *d_x, const float *d_amax, uint8_t *d_
 
 /* ---- materialisation + AdamW (OptimizerModule) ------------------------------------- */
 /* `OptimizerModule::materialize_master` (.../optimizer/launcher/mod.rs:67-95). */
+/* No single counterpart in the reference, whose forward GEMMs run on sm_120a and repack scales with
+ * crates/cuda-kernels/src/utils/nvfp4_tma_matmul/scale_pack.rs:29-175: size of, and conversion into,
+ * the B2_SCALES_SM100 layout from a raw plane or CSF storage of a [rows][cols] tensor (cols % 16 == 0;
+ * CSF: cols % 128 == 0).  The converter writes every byte of the destination, padding as zero. */
+size_t b2_nvfp4_sm100_scales_bytes(uint32_t rows, uint32_t cols);
+int b2_nvfp4_scales_to_sm100(const uint8_t *d_scales, uint32_t src_layout, uint32_t rows, uint32_t cols,
+                             uint8_t *d_out, void *stream);
 int b2_materialize_master(uint8_t *d_bytes, uint8_t *d_scales, float *d_global_scale,
                           const float *d_master, float *d_amax, float *d_chunk_amax, uint32_t len,
                           uint32_t scale_layout, void *stream);

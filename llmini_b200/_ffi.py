@@ -13,7 +13,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "_lib", "libllmini_b200.so")
 HEADER_PATH = os.path.join(os.path.dirname(_HERE), "include", "llmini_b200.h")
 
-SCALES_CSF, SCALES_RAW = 0, 1
+SCALES_CSF, SCALES_RAW, SCALES_SM100 = 0, 1, 2
 OPERAND_BF16, OPERAND_F16 = 0, 1
 QUANTIZE_X, QUANTIZE_Y = 0, 1
 ERROR_INVALID_VALUE, ERROR_NOT_SUPPORTED, ERROR_LAUNCH_TIMEOUT = 1, 801, 702
@@ -100,6 +100,8 @@ def _declare(L: C.CDLL) -> None:
         "b2_muon_finish_update_deferred_quantization": (i, [vp, vp, C.POINTER(MuonStepArgs), vp]),
         "b2_muon_finish_hyperball_update_deferred_quantization": (i, [vp, vp, C.POINTER(MuonStepArgs), C.c_uint32, vp]),
         "b2_muon_sign_update_deferred_quantization": (i, [vp, vp, C.POINTER(MuonStepArgs), vp]),
+        "b2_nvfp4_sm100_scales_bytes": (C.c_size_t, [C.c_uint32, C.c_uint32]),
+        "b2_nvfp4_scales_to_sm100": (i, [vp, C.c_uint32, C.c_uint32, C.c_uint32, vp, vp]),
         "b2_muon_plan_scratch": (i, [vp, u32, u32, C.POINTER(vp), C.POINTER(sz)]),
         "b2_muon_plan_status": (i, [vp, vp]),
         "b2_muon_plan_flops_per_iteration": (C.c_double, [vp]),

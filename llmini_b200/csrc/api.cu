@@ -344,7 +344,7 @@ int b2_muon_plan_create(b2_muon_plan **out, const uint32_t *rows, const uint32_t
     if (!out || !rows || !cols || slot_count == 0 || slot_count > 65535 || !d_workspace) return B2_ERROR_INVALID_VALUE;
     if (reinterpret_cast<uintptr_t>(d_workspace) % 1024 != 0) return B2_ERROR_INVALID_VALUE;
     b2_muon_options o = normalized(options);
-    if (o.operand_format > B2_OPERAND_F16 || o.scale_layout > B2_SCALES_RAW || o.quantize_target > B2_QUANTIZE_Y)
+    if (o.operand_format > B2_OPERAND_F16 || o.scale_layout > B2_SCALES_SM100 || o.quantize_target > B2_QUANTIZE_Y)
         return B2_ERROR_INVALID_VALUE;
     b2_muon_plan *p = new (std::nothrow) b2_muon_plan();
     if (!p) return (int)cudaErrorMemoryAllocation;
@@ -691,6 +691,20 @@ int b2_fp32_to_nvfp4_four_six(const float *d_x, const float *d_amax, uint8_t *d_
     if (e != cudaSuccess) return (int)e;
     return (int)launch_quantize_flat(d_x, nullptr, nullptr, 0.f, 0, d_amax, d_out_fp4, d_out_scales, d_out_global_scale,
                                      group_count, (int)scale_layout, stream_grid_cap(d), as_stream(stream));
+}
+size_t b2_nvfp4_sm100_scales_bytes(uint32_t rows, uint32_t cols) {
+    return (size_t)((rows + 127) / 128) * ((cols / 16 + 3) / 4) * 512;
+}
+int b2_nvfp4_scales_to_sm100(const uint8_t *d_scales, uint32_t src_layout, uint32_t rows, uint32_t cols,
+                             uint8_t *d_out, void *stream) {
+    if (!d_scales || !d_out || src_layout > B2_SCALES_RAW) return B2_ERROR_INVALID_VALUE;
+    if (cols % 16 != 0 || (src_layout == B2_SCALES_CSF && cols % 128 != 0)) return B2_ERROR_INVALID_VALUE;
+    if ((uint64_t)rows * cols > 0xfffff000ull) return B2_ERROR_INVALID_VALUE;
+    DeviceInfo d;
+    cudaError_t e = device_info(d);
+    if (e != cudaSuccess) return (int)e;
+    return (int)launch_scales_to_sm100(d_scales, src_layout == B2_SCALES_CSF, rows, cols, d_out, stream_grid_cap(d),
+                                       as_stream(stream));
 }
 int b2_materialize_master(uint8_t *d_bytes, uint8_t *d_scales, float *d_global_scale, const float *d_master,
                           float *d_amax, float *d_chunk_amax, uint32_t len, uint32_t scale_layout, void *stream) {

@@ -123,6 +123,29 @@ __device__ __forceinline__ void csf_store_record(uint8_t *scales, uint32_t k, ui
     d[t * 896 + 768 + r] = (uint8_t)(csf_high1(a) | (csf_high1(b) << 4));
 }
 
+// One block scale out of CSF storage (the device twin of b2_csf_scale_at).
+__device__ __forceinline__ uint32_t csf_load_scale(const uint8_t *s, uint32_t g) {
+    if (s[8] == 255) return s[128 + g];
+    const uint32_t k = reinterpret_cast<const uint32_t *>(s)[0], groups = k / 16;
+    const uint32_t row = g / groups, kg = g - row * groups;
+    const uint32_t bytes = (uint32_t)s[9] - 6;
+    const uint8_t *d = s + 128;
+    const uint32_t t = row / 128 * (k / 128) + kg / 8, r = row % 128, stride = 768 + 128 * bytes;
+    const size_t at = (size_t)t * stride + csf_code_offset(r) + (kg % 8 / 4) * 6;
+    const uint32_t shift = (kg % 4) * 6, bits = shift % 8;
+    const size_t byte = at + shift / 8;
+    const uint32_t lo = d[byte], hi = bits > 2 ? d[byte + 1] : 0;
+    const uint32_t q = ((lo | (hi << 8)) >> bits) & 63u;
+    const size_t am = (size_t)t * stride + 768 + (size_t)r * bytes;
+    if (bytes == 1) return q | (((d[am] >> (kg % 8)) & 1u) << 6);
+    return q | (((d[am + kg % 8 / 4] >> ((kg % 4) * 2)) & 3u) << 6);
+}
+// Byte offset of the scale of (row, 16-value block kb) in the sm_100 block-scale operand layout:
+// 512-byte tiles of 128 rows x 4 blocks, `kb_tiles` = ceil(blocks per row / 4) tiles per row band.
+__device__ __forceinline__ size_t sm100_scale_offset(uint32_t row, uint32_t kb, uint32_t kb_tiles) {
+    return ((size_t)(row >> 7) * kb_tiles + (kb >> 2)) * 512 + (row & 31u) * 16 + ((row >> 5) & 3u) * 4 + (kb & 3u);
+}
+
 // ---- reductions ----------------------------------------------------------------------------
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll

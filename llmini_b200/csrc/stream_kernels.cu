@@ -7,6 +7,8 @@
 // (grid-stride, grid = SM count x resident CTAs), so one launch covers the whole step.
 // The file is compiled with -fmad=false: `a*b + c` is never fused unless written as fmaf,
 // which is how the reference's Rust expressions behave.
+#include <algorithm>
+
 #include "common.cuh"
 #include "internal.h"
 
@@ -744,6 +746,10 @@ __device__ __forceinline__ void encode_chunk(const float *src, const float *z, c
     if (valid) *reinterpret_cast<uint2 *>(fp4 + (size_t)group * 8) = make_uint2(w[0], w[1]);
     if (scale_layout == B2_SCALES_RAW) {
         if (valid) scales[group] = (uint8_t)sb;
+    } else if (scale_layout == B2_SCALES_SM100) {
+        // csf_k carries the row length here; a warp's 32 groups land in eight 4-byte runs
+        const uint32_t per_row = csf_k / 16, row = group / per_row, kb = group - row * per_row;
+        if (valid) scales[sm100_scale_offset(row, kb, (per_row + 3) / 4)] = (uint8_t)sb;
     } else {
         // eight consecutive groups (one CSF record, crates/cuda-kernels/src/utils/nvfp4/csf.rs:193-232)
         // sit in eight consecutive lanes: fold their scale bytes into the first of them
@@ -769,6 +775,9 @@ k_muon_encode(const b2_muon_slot_descriptor *slots, const uint32_t *prefix, uint
         if (scale_layout == B2_SCALES_CSF) {
             k = reinterpret_cast<const uint32_t *>(scales)[0];
             rows = reinterpret_cast<const uint32_t *>(scales)[1];
+        } else if (scale_layout == B2_SCALES_SM100) {
+            k = cx.d.cols;
+            rows = cx.d.rows;
         }
         if (cx.local_chunk == 0 && threadIdx.x == 0)
             *reinterpret_cast<float *>(cx.d.global_scale) = gs;
@@ -871,6 +880,9 @@ k_muon_update_encode(const b2_muon_slot_descriptor *slots, const uint32_t *prefi
             if (scale_layout == B2_SCALES_CSF) {
                 k = reinterpret_cast<const uint32_t *>(scales)[0];
                 rows = reinterpret_cast<const uint32_t *>(scales)[1];
+            } else if (scale_layout == B2_SCALES_SM100) {
+                k = cx.d.cols;
+                rows = cx.d.rows;
             }
             if (cx.local_chunk == 0 && tid == 0) *reinterpret_cast<float *>(cx.d.global_scale) = gs;
             // 256 threads x one 16-value group per call: kEncodeSpan chunks of the same slot
@@ -1315,6 +1327,34 @@ cudaError_t launch_muon_update(const SlotView &v, const uint64_t *u_ptrs, float 
     else
         k_muon_update<0><<<clamp_grid(v.total_chunks, v.grid), kThreads, 0, s>>>(
             v.slots, v.chunk_prefix, v.slot_count, v.total_chunks, u_ptrs, amax_x, up);
+    return cudaGetLastError();
+}
+// Raw plane or CSF storage -> sm_100 block-scale operand layout; one thread per destination byte,
+// so the padding of the last row band and scale-column group is written (as zero) too.
+__global__ void __launch_bounds__(kThreads)
+k_scales_to_sm100(const uint8_t *src, int src_csf, uint32_t rows, uint32_t per_row, uint32_t kb_tiles,
+                  uint8_t *out, size_t out_bytes) {
+    for (size_t o = (size_t)blockIdx.x * kThreads + threadIdx.x; o < out_bytes; o += (size_t)gridDim.x * kThreads) {
+        const size_t tile = o >> 9;
+        const uint32_t in = (uint32_t)(o & 511u);
+        const uint32_t row = (uint32_t)(tile / kb_tiles) * 128 + ((in >> 2) & 3u) * 32 + (in >> 4);
+        const uint32_t kb = (uint32_t)(tile % kb_tiles) * 4 + (in & 3u);
+        uint32_t v = 0;
+        if (row < rows && kb < per_row) {
+            const uint32_t g = row * per_row + kb;
+            v = src_csf ? csf_load_scale(src, g) : src[g];
+        }
+        out[o] = (uint8_t)v;
+    }
+}
+cudaError_t launch_scales_to_sm100(const uint8_t *src, int src_csf, uint32_t rows, uint32_t cols, uint8_t *out,
+                                   int grid_cap, cudaStream_t s) {
+    const uint32_t per_row = cols / 16, kb_tiles = (per_row + 3) / 4;
+    const size_t bytes = (size_t)((rows + 127) / 128) * kb_tiles * 512;
+    if (bytes == 0) return cudaSuccess;
+    const size_t blocks = (bytes + kThreads - 1) / kThreads;
+    k_scales_to_sm100<<<(unsigned)std::min<size_t>(blocks, (size_t)grid_cap), kThreads, 0, s>>>(src, src_csf, rows, per_row,
+                                                                                            kb_tiles, out, bytes);
     return cudaGetLastError();
 }
 size_t fused_sync_bytes(uint32_t slot_count) { return sizeof(FusedSync) + sizeof(uint32_t) * slot_count; }

@@ -14,7 +14,7 @@ import numpy as np
 import torch
 
 from . import _ffi
-from ._ffi import SCALES_CSF, SCALES_RAW, check
+from ._ffi import SCALES_CSF, SCALES_RAW, SCALES_SM100, check
 
 
 def _stream() -> int:
@@ -55,6 +55,20 @@ def zero_scales(rows: int, k: int, device="cuda") -> torch.Tensor:
     (crates/cuda-kernels/tests/optimizer/muon/buffers.rs:135-142)."""
     enc = csf_encode_host(np.zeros(rows * k // 16, np.uint8), rows, k)
     return torch.from_numpy(enc).to(device)
+
+
+def sm100_scales_bytes(rows: int, cols: int) -> int:
+    """Bytes of the sm_100 block-scale operand layout of a [rows][cols] tensor (128 x 4 tiles, padded)."""
+    return int(_ffi.lib().b2_nvfp4_sm100_scales_bytes(rows, cols))
+
+
+def scales_to_sm100(scales: torch.Tensor, src_layout: int, rows: int, cols: int) -> torch.Tensor:
+    """Block scales (raw plane or CSF storage, on the device) -> the layout `tcgen05.mma
+    kind::mxf4nvf4.block_scale` operands use; every byte of the result is written."""
+    out = torch.empty(sm100_scales_bytes(rows, cols), dtype=torch.uint8, device=scales.device)
+    check(_ffi.lib().b2_nvfp4_scales_to_sm100(scales.data_ptr(), src_layout, rows, cols, out.data_ptr(),
+                                              torch.cuda.current_stream().cuda_stream), "nvfp4_scales_to_sm100")
+    return out
 
 
 @dataclass

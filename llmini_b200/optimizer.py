@@ -16,9 +16,9 @@ import torch
 
 from . import _ffi
 from ._ffi import (AdamWSlotDescriptor, AdamWUpdateArgs as _CAdam, GradientClipArgs as _CClip, MuonOptions, MuonSlotDescriptor, MuonStepArgs, OPERAND_BF16,
-                   OPERAND_F16, QUANTIZE_X, QUANTIZE_Y, SCALES_CSF, SCALES_RAW,
+                   OPERAND_F16, QUANTIZE_X, QUANTIZE_Y, SCALES_CSF, SCALES_RAW, SCALES_SM100,
                    ScheduleFreeMaterializeArgs as _CSf, check)
-from .nvfp4 import Nvfp4QuantModule, zero_scales
+from .nvfp4 import Nvfp4QuantModule, sm100_scales_bytes, zero_scales
 
 U32_MAX = 0xFFFFFFFF
 
@@ -62,6 +62,8 @@ class MuonSlot:
             if cols % 128 != 0:
                 raise ValueError("CSF block-scale storage needs cols % 128 == 0; use SCALES_RAW")
             scales = zero_scales(rows, cols, device)
+        elif scale_layout == SCALES_SM100:  # padding bytes stay zero: the kernels never write them
+            scales = torch.zeros(sm100_scales_bytes(rows, cols), dtype=torch.uint8, device=device)
         else:
             scales = torch.zeros(max(n // 16, 1), dtype=torch.uint8, device=device)
         z = lambda *s, dt=torch.float32: torch.zeros(*s, dtype=dt, device=device)

@@ -321,6 +321,29 @@ def hyperball_update(U, z, x, rows, cols, lr, c_avg, beta, use_schedule_free, fa
     return z, x, y, m, v, am[0], am[1]
 
 
+def sm100_blocked(raw_scales, rows, cols):
+    """Block scales [rows][cols/16] -> the block-scale operand layout of sm_100 tensor cores, as
+    published for cuBLASLt's VEC16_UE4M3 scale mode and restated by PyTorch / torchao as
+    `to_blocked`: pad to 128 rows x 4 columns, tiles (row/128, col/4) row-major, and inside a
+    512-byte tile byte (row % 32) * 16 + (row % 128) // 32 * 4 + col % 4."""
+    per_row = cols // 16
+    a = np.asarray(raw_scales, np.uint8).reshape(rows, per_row)
+    rb, cb = -(-rows // 128), -(-per_row // 4)
+    pad = np.zeros((rb * 128, cb * 4), np.uint8)
+    pad[:rows, :per_row] = a
+    t = pad.reshape(rb, 128, cb, 4).transpose(0, 2, 1, 3)      # [rb][cb][128][4]
+    t = t.reshape(rb * cb, 4, 32, 4).transpose(0, 2, 1, 3)       # [tile][32][4][4]
+    return np.ascontiguousarray(t).reshape(-1)
+
+
+def sm100_unblocked(blocked, rows, cols):
+    """Inverse of `sm100_blocked` (drops the padding)."""
+    per_row = cols // 16
+    rb, cb = -(-rows // 128), -(-per_row // 4)
+    t = np.asarray(blocked, np.uint8).reshape(rb * cb, 32, 4, 4).transpose(0, 2, 1, 3).reshape(rb, cb, 128, 4)
+    return np.ascontiguousarray(t.transpose(0, 2, 1, 3).reshape(rb * 128, cb * 4)[:rows, :per_row]).reshape(-1)
+
+
 def inv_norm(sumsq, contract=False) -> np.float32:
     return np.float32(lib().orc_inv_norm(np.float32(sumsq), int(contract)))
 
