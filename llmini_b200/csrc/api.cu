@@ -497,7 +497,6 @@ static UpdateParams update_params(const b2_muon_step_args *a) {
     up.c_avg = a->average_coefficient;
     up.beta = a->schedule_beta;
     up.d_qk_clip_factors = a->d_qk_clip_factors;
-    up.variance_adaptive = a->variance_adaptive ? 1 : 0;
     up.normuon = 0;
     up.factor_ptrs = nullptr;
     up.slot_stats = nullptr;

@@ -36,7 +36,6 @@ struct NeuronView {
 struct UpdateParams {
     float lr, wd, c_avg, beta;
     const float *d_qk_clip_factors;
-    int variance_adaptive;
     int normuon;                   // 1: scale U by factor[neuron] * normuon_scale
     const uint64_t *factor_ptrs;
     const float *slot_stats;
