@@ -530,7 +530,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a CUDA graph replay")
     ap.add_argument("--plan-flags", type=int, default=0,
-                    help="measurement only: kernel flags of the plan (16 = update and encode as two launches)")
+                    help="measurement only: kernel flags of the plan (16 = update and encode as two launches, "
+                         "32 = no programmatic dependent launch between the GEMMs)")
     ap.add_argument("--sweep", action="store_true", help="update+quantise bandwidth sweep over [R, 4096] tensors")
     args = ap.parse_args()
     if args.sweep:

@@ -84,7 +84,9 @@ typedef struct b2_muon_options {
     uint32_t max_iterations;  /* upper bound on b2_muon_step_args.iterations (0 -> 5) */
     uint32_t reserved[4];     /* [0]: GEMM tile override (0 = choose; 128 / 256 = one CTA per
                                  128 x N tile; 512 = two-CTA 256 x 256 tiles);
-                                 [1], [2]: measurement-only knobs (phase mask, kernel flags),
+                                 [1], [2]: measurement-only knobs (phase mask; kernel flags: 1 / 8 drop
+                                 GEMM epilogue stores, 4 all tiles of symmetric outputs, 16 update and
+                                 encode as two launches, 32 no programmatic dependent launch),
                                  leave 0; [3]: must be 0 */
 } b2_muon_options;
 

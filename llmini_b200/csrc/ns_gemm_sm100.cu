@@ -260,6 +260,11 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
     if (PAIR) cluster_sync_all();  // the peer's barriers are initialised before anything signals them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Programmatic dependent launch: the next launch of the stream may start its own prologue on
+    // SMs this grid has left; nothing above reads what the previous launch wrote, everything
+    // below may, so the wait for that launch (a no-op without the launch attribute) sits here.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -522,21 +527,28 @@ cudaError_t launch_impl(const GemmProblem *problems, const GemmTile *tiles, uint
                         int f16, float ca, float cb, float cc, uint32_t *status, uint32_t debug_flags, int grid,
                         cudaStream_t s) {
     cudaLaunchConfig_t cfg = {};
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
+    unsigned n_attr = 0;
+    if (!(debug_flags & 32u)) {  // flag 32: measurement only, plain stream order
+        attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+        ++n_attr;
+    }
     if (PAIR) {
         int clusters = grid / 2;
         if ((uint32_t)clusters > tile_count) clusters = (int)tile_count;
         if (clusters < 1) clusters = 1;
         grid = 2 * clusters;
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = 2;
-        attr[0].val.clusterDim.y = 1;
-        attr[0].val.clusterDim.z = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
+        attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+        attr[n_attr].val.clusterDim.x = 2;
+        attr[n_attr].val.clusterDim.y = 1;
+        attr[n_attr].val.clusterDim.z = 1;
+        ++n_attr;
     } else if ((uint32_t)grid > tile_count) {
         grid = (int)tile_count;
     }
+    cfg.attrs = attr;
+    cfg.numAttrs = n_attr;
     cfg.gridDim = dim3((unsigned)grid, 1, 1);
     cfg.blockDim = dim3(kGemmThreads, 1, 1);
     cfg.dynamicSmemBytes = Cfg<BN, PAIR>::kSmemBytes;
