@@ -266,7 +266,8 @@ def run_gpu(args):
             [dict(t, mode=2 if kind == "quant" else 0) for kind, t in adam_sets], dev)
     launches_per_step = 0
     if plan is not None:
-        launches_per_step += 3 + 3 * HP["iterations"] + 2
+        # sumsq, inv_norm, momentum_normalize; three GEMMs per iteration; update + encode in one launch
+        launches_per_step += 3 + 3 * HP["iterations"] + (2 if args.plan_flags & 16 else 1)
     launches_per_step += 3 if adam_sets else 0
 
     stream = torch.cuda.current_stream()

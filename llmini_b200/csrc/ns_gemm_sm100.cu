@@ -38,18 +38,22 @@ constexpr int kGemmThreads = 32 * (2 + kEpiWarps);  // warp 0: TMA producer, war
 constexpr int kBoxBytes = 64 * 128;          // 64 rows x 128 bytes
 constexpr int kABytes = 2 * kBoxBytes;       // 128 x 64 16-bit operand tile
 constexpr int kSlabBytes = 32 * 128;         // per-warp store staging: 32 rows x 128 bytes
-constexpr int kStagingBytes = kEpiWarps * kSlabBytes;
+constexpr int kSmemLimit = 227 * 1024;
 constexpr uint32_t kSpinLimit = 1u << 24;    // hard cap on polls, whatever the timer says
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
-template <int BN, bool PAIR>
+// SLABS = 2: every epilogue warp has two store slabs and fills one while the TMA store engine
+// still reads the other; it costs one pipeline stage.  Used where the epilogue, not the
+// mainloop, bounds the tile (the symmetric Gram / polynomial launches of the pair kernel).
+template <int BN, bool PAIR, int SLABS = 1>
 struct Cfg {
     static constexpr int kBRows = PAIR ? 128 : BN;   // rows of B this CTA stages per k-block
     static constexpr int kBBytes = (kBRows / 64) * kBoxBytes;
     static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kStages = (kStageBytes == 32768) ? 6 : 4;
+    static constexpr int kStagingBytes = SLABS * kEpiWarps * kSlabBytes;
     static constexpr int kTmemCols = 2 * BN;
     static constexpr int kBarrierBytes = 256;
+    static constexpr int kStages = (kSmemLimit - kStagingBytes - kBarrierBytes - 1024) / kStageBytes;
     static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + kBarrierBytes + 1024;
     static constexpr int kTileM = PAIR ? 256 : 128;  // rows of the (cluster) tile
 };
@@ -134,6 +138,8 @@ __device__ __forceinline__ void tma_store_2d(uint64_t map, uint32_t src, int x, 
 }
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// all but the most recent store of this thread have read their shared-memory source
+__device__ __forceinline__ void tma_store_wait_read_older() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -203,19 +209,19 @@ __device__ __forceinline__ uint32_t instr_desc(int m, int n, int f16, uint32_t a
            ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
-template <int BN, bool PAIR>
+template <int BN, bool PAIR, int SLABS>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__ tiles,
           uint32_t tile_count, uint32_t epilogue, int f16, float ca, float cb, float cc,
           uint32_t *status, uint32_t debug_flags) {
-    using C = Cfg<BN, PAIR>;
+    using C = Cfg<BN, PAIR, SLABS>;
     const bool dbg_no_store = debug_flags & 1u;   // measurement only: drop every epilogue store
     const bool dbg_no_global = debug_flags & 8u;  // measurement only: stage in shared memory but issue no global store
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *stage_base = smem;
     uint8_t *staging = smem + C::kStages * C::kStageBytes;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(staging + kStagingBytes);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(staging + C::kStagingBytes);
     // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * C::kStages + 4);
     volatile uint32_t *abort_flag = tmem_slot + 1;
@@ -349,8 +355,19 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
         // split the columns of the tile between them.
         const int q = warp & 3;
         const int half = (warp - 2) >> 2;
-        uint8_t *slab = staging + (size_t)(warp - 2) * kSlabBytes;
-        const uint32_t slab_u32 = smem_u32(slab);
+        // With two slabs per warp they are used in turn: before one is refilled only the store
+        // before the last has to be done with it, so a store's shared-memory read overlaps the
+        // next fill.
+        uint8_t *slab_pair = staging + (size_t)(warp - 2) * SLABS * kSlabBytes;
+        uint32_t sb = 0;
+        auto slab_wait = [&]() {
+            if (lane == 0) {
+                if (SLABS == 2) tma_store_wait_read_older();
+                else tma_store_wait_read_all();
+            }
+            __syncwarp();
+        };
+        auto slab_next = [&]() { if (SLABS == 2) sb ^= 1u; };
         const uint32_t tempty_leader0 = PAIR ? map_to_cta(tempty_bar(0), 0) : tempty_bar(0);
         uint32_t acc = 0, acc_phase = 0;
         constexpr int kHalfCols = BN / 2;
@@ -400,8 +417,8 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
                         if (lane == 0) mbar_arrive_cluster(tempty);
                     }
                     if (n0 + c0 >= (int)N || slab_row0 >= (int)M || dbg_no_store) continue;  // warp-uniform
-                    if (lane == 0) tma_store_wait_read_all();
-                    __syncwarp();
+                    slab_wait();
+                    uint8_t *slab = slab_pair + sb * kSlabBytes;
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
                         uint4 w = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
@@ -410,9 +427,10 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
                     fence_async_smem();
                     __syncwarp();
                     if (lane == 0 && !dbg_no_global) {
-                        tma_store_2d(map32, slab_u32, n0 + c0, slab_row0);
+                        tma_store_2d(map32, smem_u32(slab), n0 + c0, slab_row0);
                         tma_store_commit();
                     }
+                    slab_next();
                 }
             } else {
                 // 16-bit result: 64 columns (128 bytes) per staged slab
@@ -458,8 +476,8 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
                         }
                     }
                     if (n0 + c0 >= (int)N || slab_row0 >= (int)M || dbg_no_store) continue;  // warp-uniform
-                    if (lane == 0) tma_store_wait_read_all();
-                    __syncwarp();
+                    slab_wait();
+                    uint8_t *slab = slab_pair + sb * kSlabBytes;
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
                         uint4 w;
@@ -472,27 +490,29 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
                     fence_async_smem();
                     __syncwarp();
                     if (lane == 0 && !dbg_no_global) {
-                        tma_store_2d(map16, slab_u32, n0 + c0, slab_row0);
+                        tma_store_2d(map16, smem_u32(slab), n0 + c0, slab_row0);
                         tma_store_commit();
                     }
+                    slab_next();
                     if (mirror) {
                         // transposed 64 x 32 block (rows = this chunk's columns), plain row-major
                         // 64-byte rows: lanes pair up so every lane stores two rows of one column
-                        if (lane == 0) tma_store_wait_read_all();
-                        __syncwarp();
+                        slab_wait();
+                        uint8_t *slab_t = slab_pair + sb * kSlabBytes;
 #pragma unroll
                         for (int c = 0; c < 64; c += 2) {
                             const uint32_t mine = pack_operands(__uint_as_float(v[c]), __uint_as_float(v[c + 1]), f16);
                             const uint32_t other = __shfl_xor_sync(0xffffffffu, mine, 1);
                             const uint32_t out = (lane & 1) ? __byte_perm(other, mine, 0x7632) : __byte_perm(mine, other, 0x5410);
-                            *reinterpret_cast<uint32_t *>(slab + (c + (lane & 1)) * 64 + (lane & ~1) * 2) = out;
+                            *reinterpret_cast<uint32_t *>(slab_t + (c + (lane & 1)) * 64 + (lane & ~1) * 2) = out;
                         }
                         fence_async_smem();
                         __syncwarp();
                         if (lane == 0 && !dbg_no_global) {
-                            tma_store_2d(map16t, slab_u32, slab_row0, n0 + c0);
+                            tma_store_2d(map16t, smem_u32(slab_t), slab_row0, n0 + c0);
                             tma_store_commit();
                         }
+                        slab_next();
                     }
                 }
             }
@@ -522,7 +542,7 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
     }
 }
 
-template <int BN, bool PAIR>
+template <int BN, bool PAIR, int SLABS>
 cudaError_t launch_impl(const GemmProblem *problems, const GemmTile *tiles, uint32_t tile_count, uint32_t epilogue,
                         int f16, float ca, float cb, float cc, uint32_t *status, uint32_t debug_flags, int grid,
                         cudaStream_t s) {
@@ -551,33 +571,43 @@ cudaError_t launch_impl(const GemmProblem *problems, const GemmTile *tiles, uint
     cfg.numAttrs = n_attr;
     cfg.gridDim = dim3((unsigned)grid, 1, 1);
     cfg.blockDim = dim3(kGemmThreads, 1, 1);
-    cfg.dynamicSmemBytes = Cfg<BN, PAIR>::kSmemBytes;
+    cfg.dynamicSmemBytes = Cfg<BN, PAIR, SLABS>::kSmemBytes;
     cfg.stream = s;
-    return cudaLaunchKernelEx(&cfg, k_ns_gemm<BN, PAIR>, problems, tiles, tile_count, epilogue, f16, ca, cb, cc, status,
+    return cudaLaunchKernelEx(&cfg, k_ns_gemm<BN, PAIR, SLABS>, problems, tiles, tile_count, epilogue, f16, ca, cb, cc, status,
                               debug_flags);
 }
 
 }  // namespace
 
 cudaError_t gemm_configure(int block_n, int pair) {
-    if (pair && block_n == 256)
-        return cudaFuncSetAttribute(k_ns_gemm<256, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<256, true>::kSmemBytes);
+    if (pair && block_n == 256) {
+        cudaError_t e = cudaFuncSetAttribute(k_ns_gemm<256, true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             Cfg<256, true, 1>::kSmemBytes);
+        if (e != cudaSuccess) return e;
+        return cudaFuncSetAttribute(k_ns_gemm<256, true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    Cfg<256, true, 2>::kSmemBytes);
+    }
     if (!pair && block_n == 256)
-        return cudaFuncSetAttribute(k_ns_gemm<256, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<256, false>::kSmemBytes);
+        return cudaFuncSetAttribute(k_ns_gemm<256, false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    Cfg<256, false, 1>::kSmemBytes);
     if (!pair && block_n == 128)
-        return cudaFuncSetAttribute(k_ns_gemm<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<128, false>::kSmemBytes);
+        return cudaFuncSetAttribute(k_ns_gemm<128, false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    Cfg<128, false, 1>::kSmemBytes);
     return cudaErrorInvalidValue;
 }
 cudaError_t launch_ns_gemm(int block_n, int pair, const GemmProblem *problems, const GemmTile *tiles,
                            uint32_t tile_count, uint32_t epilogue, int f16, float ca, float cb,
                            float cc, uint32_t *status, uint32_t debug_flags, int grid, cudaStream_t s) {
     if (tile_count == 0) return cudaSuccess;
-    if (pair && block_n == 256)
-        return launch_impl<256, true>(problems, tiles, tile_count, epilogue, f16, ca, cb, cc, status, debug_flags, grid, s);
+    if (pair && block_n == 256) {
+        if (epilogue == kEpiGram || epilogue == kEpiPoly)
+            return launch_impl<256, true, 2>(problems, tiles, tile_count, epilogue, f16, ca, cb, cc, status, debug_flags, grid, s);
+        return launch_impl<256, true, 1>(problems, tiles, tile_count, epilogue, f16, ca, cb, cc, status, debug_flags, grid, s);
+    }
     if (!pair && block_n == 256)
-        return launch_impl<256, false>(problems, tiles, tile_count, epilogue, f16, ca, cb, cc, status, debug_flags, grid, s);
+        return launch_impl<256, false, 1>(problems, tiles, tile_count, epilogue, f16, ca, cb, cc, status, debug_flags, grid, s);
     if (!pair && block_n == 128)
-        return launch_impl<128, false>(problems, tiles, tile_count, epilogue, f16, ca, cb, cc, status, debug_flags, grid, s);
+        return launch_impl<128, false, 1>(problems, tiles, tile_count, epilogue, f16, ca, cb, cc, status, debug_flags, grid, s);
     return cudaErrorInvalidValue;
 }
 
