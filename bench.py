@@ -56,6 +56,21 @@ def model_shapes(name):
     return mats, emb, vec
 
 
+def workload_config(name, world):
+    """The `config` object of the JSON line; both arms print the same one."""
+    mats, emb, vec = model_shapes(name)
+    d_model = MODELS[name][1]
+    return {
+        "workload": f"{name}: {len(mats)} weight matrices (Muon, 5 Newton-Schulz iterations, fixed triple "
+                    f"3.4445/-4.7750/2.0315, BF16 operands) + AdamW on embeddings/LayerNorm/bias, NVFP4 requant of "
+                    f"all matrices and embeddings",
+        "matrix_elements": int(sum(r * c for r, c in mats)), "adamw_elements": int(sum(r * c for r, c in emb) + vec),
+        "sharding": "whole matrices, greedy by NS FLOPs" if world > 1 else "single GPU",
+        "scale_layout": "csf" if d_model % 128 == 0 else "raw",
+        "l2": "per-step working set (>2 GB) exceeds the 126 MB L2; no flush needed",
+    }
+
+
 def ns_flops(shapes, iterations=5):
     f = 0.0
     for r, c in shapes:
@@ -172,8 +187,9 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": ms, "unit": "ms", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"{args.workload} full optimizer step (CPU oracle port of the reference path; the "
-                               "reference itself is Rust + cuda-oxide and cannot be built in this image)"},
+        "config": workload_config(args.workload, args.gpus),
+        "note": "CPU oracle port of the reference path on the host cores (the reference itself is Rust + cuda-oxide "
+                "and cannot be built in this image); rank 0 only, whatever --gpus says",
         "cpu_baseline": {"value": ms, "unit": "ms", "cores": cores, "kind": "port", "sample": t[0][1]},
         "e2e": {"value": ms, "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -444,18 +460,13 @@ def run_gpu(args):
         "metric": METRIC, "value": ms_step, "unit": "ms", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": False, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {
-            "workload": f"{args.workload}: {len(mats)} weight matrices (Muon, 5 Newton-Schulz iterations, fixed triple "
-                        f"3.4445/-4.7750/2.0315, BF16 operands) + AdamW on embeddings/LayerNorm/bias, NVFP4 requant of "
-                        f"all matrices and embeddings",
-            "matrix_elements": int(sum(r * c for r, c in mats)), "adamw_elements": int(sum(r * c for r, c in emb) + vec),
-            "sharding": "whole matrices, greedy by NS FLOPs" if world > 1 else "single GPU",
-            "scale_layout": "csf" if layout == b2.SCALES_CSF else "raw",
-            "l2": "per-step working set (>2 GB) exceeds the 126 MB L2; no flush needed",
-        },
+        "config": workload_config(args.workload, world),
         "roofline": {
             "bound": "tensor", "kernel": "k_ns_gemm (15 launches per step)", "achieved": ns_tflops, "peak": peak_tf,
-            "unit": "TFLOP/s", "frac": ns_tflops / peak_tf, "traffic": None,
+            "unit": "TFLOP/s", "frac": ns_tflops / peak_tf,
+            # DRAM bytes per launch, mean of the Gram / Poly / Apply launches in the committed ncu capture
+            # (profiles/k_ns_gemm_pair_gpt2-small.md); known for this workload on one GPU only
+            "traffic": 262.0e6 if (args.workload == "gpt2-small" and world == 1) else None,
             "peak_source": f"{peaks['source']} bf16 sustained (kernel timed inside a long step)",
             "frac_of_nominal_2250": ns_tflops / 2250.0,
         },
