@@ -532,6 +532,97 @@ def run_sweep(args):
         torch.cuda.empty_cache()
 
 
+def run_extras(args):
+    """Device time of the entry points beside the headline step (the trainer's per-step variants,
+    the clip, the cached-weight materialisation, the sm_100 scale converter) on the GPT-2-small matrix
+    set: one JSON line each, bytes as the algorithmic minimum the call has to move.  Not part of
+    the default run."""
+    import torch
+
+    import llmini_b200 as b2
+
+    torch.cuda.set_device(0)
+    dev = "cuda"
+    peaks = load_peaks()
+    mats, _, _ = model_shapes(args.workload)
+    n_el = sum(r * c for r, c in mats)
+    opt = b2.OptimizerModule()
+    g = torch.Generator(device=dev).manual_seed(0)
+    randn = lambda n, std: torch.randn(n, device=dev, generator=g) * std
+    layout = b2.SCALES_CSF if MODELS[args.workload][1] % 128 == 0 else b2.SCALES_RAW
+    slots = []
+    for r, c in mats:
+        s = b2.MuonSlot.allocate(r, c, layout)
+        s.grad.copy_(randn(r * c, 1e-3).view(r, c))
+        s.z_master.copy_(randn(r * c, 0.02).view(r, c))
+        s.x_master.copy_(s.z_master)
+        s.variance = torch.full((r, c), 1e-6, dtype=torch.bfloat16, device=dev)
+        s.second_momentum = torch.full((max(r, c),), 1e-2, device=dev)
+        slots.append(s)
+    # fused QKV matrices (3d x d) take the per-head clip; 64-wide heads
+    d_model = MODELS[args.workload][1]
+    heads = d_model // 64
+    for i, (s, (r, c)) in enumerate(zip(slots, mats)):
+        if r == 3 * c:
+            s.qk_clip_factor_offset, s.qk_clip_head_dim = (i // 4) * heads, 64
+    factors = 0.5 + 0.5 * torch.rand(len(mats) // 4 * heads, device=dev, generator=g)
+    plan = b2.MuonPlan(mats, scale_layout=layout, debug_flags=args.plan_flags)
+    table = b2.slot_table(slots)
+    base = dict(HP)
+    for i in range(len(mats)):
+        plan.scratch(i, 1).copy_(randn(mats[i][0] * mats[i][1], 0.05).view(*mats[i]))
+    # the reference's trainer hands the clip 4096-value chunks (src/training/grad_clip.rs)
+    cuts = [(s.grad.data_ptr() + 4 * a, min(4096, s.rows * s.cols - a)) for s in slots
+            for a in range(0, s.rows * s.cols, 4096)]
+    ptrs = torch.tensor([p for p, _ in cuts], dtype=torch.int64, device=dev)
+    lens = torch.tensor([n for _, n in cuts], dtype=torch.int32, device=dev)
+    sums, scale, norm = torch.zeros(len(cuts), device=dev), torch.zeros(1, device=dev), torch.zeros(1, device=dev)
+    raw_scales = torch.randint(0, 127, (n_el // 16,), dtype=torch.uint8, device=dev, generator=g)
+
+    A = b2.MuonMegaUpdateArgs
+    cases = [
+        ("prepare (plain)", 16.0, lambda: opt.muon_tma_prepare_polar(plan, table, A(**base))),
+        ("prepare (Muon-VS)", 20.0, lambda: opt.muon_tma_prepare_polar(
+            plan, table, A(variance_adaptive=True, bias_correction_inv=1.5, **base))),
+        ("finish, deferred quantisation (plain)", 24.0,
+         lambda: opt.muon_tma_finish_update_deferred_quantization(plan, table, A(**base))),
+        ("finish, deferred (NorMuon + qk-clip)", 28.0,
+         lambda: opt.muon_tma_finish_update_deferred_quantization(plan, table, A(normuon=True, qk_clip_factors=factors, **base))),
+        ("finish, deferred (NorMuon only)", 28.0,
+         lambda: opt.muon_tma_finish_update_deferred_quantization(plan, table, A(normuon=True, **base))),
+        ("finish, deferred (qk-clip only)", 24.0,
+         lambda: opt.muon_tma_finish_update_deferred_quantization(plan, table, A(qk_clip_factors=factors, **base))),
+        ("finish + quantise (plain)", 24.5625, lambda: opt.muon_tma_finish_update(plan, table, A(**base))),
+        ("finish + quantise (NorMuon + qk-clip)", 28.5625,
+         lambda: opt.muon_tma_finish_update(plan, table, A(normuon=True, qk_clip_factors=factors, **base))),
+        ("finish, Hyperball", 32.0,
+         lambda: opt.muon_tma_finish_hyperball_update_deferred_quantization(plan, table, A(**base))),
+        ("sign-Muon update", 26.0, lambda: opt.muon_tma_sign_update_deferred_quantization(plan, table, A(**base))),
+        ("materialize training weights (y -> NVFP4)", 4.5625, lambda: opt.muon_materialize_training_weights(plan, table)),
+        ("clip_gradients (norm + scale, gradients left alone)", 4.0,
+         lambda: opt.clip_gradients(chunk_ptrs=ptrs, chunk_lens=lens, chunk_sums=sums, extra_sums=None, scale=scale,
+                                    norm=norm, chunk_count=len(cuts), extra_sum_count=0, max_norm=1.0, apply=False)),
+        ("scales_to_sm100 (raw plane, all matrices as one [n/768, 768] tensor)", 2.0 / 16.0,
+         lambda: b2.scales_to_sm100(raw_scales, b2.SCALES_RAW, n_el // 768, 768)),
+    ]
+    for name, bpe, fn in cases:
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 10
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / reps
+        gbs = n_el * bpe / (ms * 1e-3) / 1e9
+        print(json.dumps({"extra": name, "workload": args.workload, "elements": n_el, "ms": ms, "bytes_per_element": bpe,
+                          "gbs": gbs, "frac_of_measured_hbm": gbs / peaks["hbm"], "status": plan.status()}), flush=True)
+    plan.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -545,9 +636,14 @@ def main():
                     help="measurement only: kernel flags of the plan (16 = update and encode as two launches, "
                          "32 = no programmatic dependent launch between the GEMMs)")
     ap.add_argument("--sweep", action="store_true", help="update+quantise bandwidth sweep over [R, 4096] tensors")
+    ap.add_argument("--extras", action="store_true",
+                    help="time the entry points beside the headline step (variants, clip, materialisation, converter)")
     args = ap.parse_args()
     if args.sweep:
         run_sweep(args)
+        return
+    if args.extras:
+        run_extras(args)
         return
     if args.impl == "reference":
         run_reference(args)

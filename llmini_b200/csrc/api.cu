@@ -575,7 +575,8 @@ static int finish_impl(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_slot
         up.slot_stats = nv.slot_stats;
     }
     const int quantize_y = plan->options.quantize_target == B2_QUANTIZE_Y;
-    if (quantize && !(plan->options.reserved[2] & 16u)) {  // flag 16: measurement only, two launches
+    // one launch for the plain update; NorMuon / qk-clip steps (and measurement flag 16) take two
+    if (quantize && !(plan->options.reserved[2] & 16u) && !up.normuon && !up.d_qk_clip_factors) {
         if (e == cudaSuccess)
             e = launch_muon_update_encode(v, plan->at<uint32_t>(L.off_items), (uint32_t)L.items.size(),
                                           plan->at<uint64_t>(L.off_u_ptrs), amax_x, up, quantize_y,

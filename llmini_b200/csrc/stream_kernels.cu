@@ -76,11 +76,13 @@ __device__ __forceinline__ uint2 pack_bf16x4(const float *v) {
     return o;
 }
 // Per-head qk-clip factor of element `i` (update.rs:58-66; one row of `cols` values per chunk there).
-__device__ __forceinline__ float qk_clip_factor(const b2_muon_slot_descriptor &d, const float *factors, uint32_t i) {
+// `row` = element index / cols, computed once by the caller (integer division is the expensive
+// part of this stage's index arithmetic).
+__device__ __forceinline__ float qk_clip_factor(const b2_muon_slot_descriptor &d, const float *factors, uint32_t row) {
     if (factors == nullptr || d.qk_clip_factor_offset == 0xffffffffu || d.qk_clip_head_dim == 0) return 1.0f;
-    const uint32_t row = i / d.cols;
     if (row >= 2u * d.cols) return 1.0f;
-    return __ldg(factors + d.qk_clip_factor_offset + (row % d.cols) / d.qk_clip_head_dim);
+    const uint32_t in_block = row >= d.cols ? row - d.cols : row;   // row % cols for row < 2 cols
+    return __ldg(factors + d.qk_clip_factor_offset + in_block / d.qk_clip_head_dim);
 }
 
 struct ChunkCtx {
@@ -203,13 +205,12 @@ k_muon_momentum_normalize(const b2_muon_slot_descriptor *slots, const uint32_t *
 
 // NorMuon factors of four consecutive elements (update/one.rs:48-56): the neuron is the row when
 // rows >= cols, else the column; `with_scale` multiplies in the per-slot normuon_scale.
-__device__ __forceinline__ void neuron_factors(const ChunkCtx &cx, const UpdateParams &up, uint32_t i, int with_scale,
-                                               float *nf) {
+__device__ __forceinline__ void neuron_factors(const ChunkCtx &cx, const UpdateParams &up, uint32_t i, uint32_t row,
+                                               int with_scale, float *nf) {
     nf[0] = nf[1] = nf[2] = nf[3] = 1.0f;
     if (!up.normuon) return;
     const float *fp = reinterpret_cast<const float *>(up.factor_ptrs[cx.slot]);
     const float sc = with_scale ? up.slot_stats[cx.slot * 4] : 1.0f;
-    const uint32_t row = i / cx.d.cols;
     if (cx.d.rows >= cx.d.cols) {
         const float f = with_scale ? __ldg(fp + row) * sc : __ldg(fp + row);
         nf[0] = nf[1] = nf[2] = nf[3] = f;
@@ -266,8 +267,9 @@ __device__ __forceinline__ void update_chunk(const ChunkCtx &cx, const uint64_t 
             float yy[4];
             // the four elements share a row (cols % 16 == 0), hence one clip factor
             float nf[4] = {1.0f, 1.0f, 1.0f, 1.0f};
-            if (EXT) neuron_factors(cx, up, i, 1, nf);
-            const float clip = EXT ? qk_clip_factor(cx.d, up.d_qk_clip_factors, i) : 1.0f;
+            const uint32_t row = EXT ? i / cx.d.cols : 0u;
+            if (EXT) neuron_factors(cx, up, i, row, 1, nf);
+            const float clip = EXT ? qk_clip_factor(cx.d, up.d_qk_clip_factors, row) : 1.0f;
             if (clip != 1.0f) {  // one.rs:63-72: momentum (and variance) follow the clipped weights
                 uint16_t *mom = reinterpret_cast<uint16_t *>(cx.d.momentum);
                 const uint2 m = *reinterpret_cast<const uint2 *>(mom + i);
@@ -346,14 +348,19 @@ k_muon_update(const b2_muon_slot_descriptor *slots, const uint32_t *prefix, uint
 // layout here, so a neuron's values are one row (rows >= cols: a warp per row) or one column
 // (rows < cols: 128 columns per CTA, the eight warps striding over the rows); both read whole
 // 512-byte row segments.  Per unit four partial sums leave the CTA: raw, scaled, parameter, dot.
-__global__ void __launch_bounds__(kThreads)
+// COLS = 0 handles the row-neuron units, COLS = 1 the column-neuron ones; each instance skips the
+// other's units, so the register-hungry column form (eight loads in flight per thread) does not
+// take the occupancy of the row form down with it.
+template <int COLS>
+__global__ void __launch_bounds__(kThreads, COLS ? 2 : 4)
 k_normuon_stats(const b2_muon_slot_descriptor *slots, uint32_t slot_count, NeuronView nv, const uint64_t *u_ptrs,
                 int hyperball) {
-    __shared__ float col_raw[kThreads / 32][128], col_dot[kThreads / 32][128];
+    __shared__ float col_raw[COLS ? kThreads / 32 : 1][128], col_dot[COLS ? kThreads / 32 : 1][128];
     __shared__ double part[kThreads / 32][4];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     for (uint32_t unit = blockIdx.x; unit < nv.total_units; unit += gridDim.x) {
         const uint32_t slot = find_slot(nv.unit_prefix, slot_count, unit);
+        if ((slots[slot].rows < slots[slot].cols) != (COLS != 0)) continue;   // CTA-uniform
         const b2_muon_slot_descriptor d = slots[slot];
         const uint32_t local = unit - nv.unit_prefix[slot];
         const float *U = reinterpret_cast<const float *>(u_ptrs[slot]);
@@ -361,11 +368,14 @@ k_normuon_stats(const b2_muon_slot_descriptor *slots, uint32_t slot_count, Neuro
         float *state = reinterpret_cast<float *>(d.second_momentum);
         float *factors = reinterpret_cast<float *>(nv.factor_ptrs[slot]);
         double s_raw = 0.0, s_scaled = 0.0, s_param = 0.0, s_dot = 0.0;  // meaningful on one thread per neuron
-        if (d.rows >= d.cols) {
+        if (!COLS) {
             const uint32_t row = local * (kThreads / 32) + warp;
             if (row < d.rows) {
                 float raw = 0.0f, param = 0.0f, dot = 0.0f;
+                // the old second moment is needed last: ask for it first
+                const float old_state = (lane == 0 && state) ? __ldcg(state + row) : 0.0f;
                 const size_t base = (size_t)row * d.cols;
+#pragma unroll 4
                 for (uint32_t c = lane * 4; c < d.cols; c += 128) {
                     const float4 u = *reinterpret_cast<const float4 *>(U + base + c);
                     raw = fmaf(u.x, u.x, raw); raw = fmaf(u.y, u.y, raw);
@@ -383,7 +393,7 @@ k_normuon_stats(const b2_muon_slot_descriptor *slots, uint32_t slot_count, Neuro
                     float factor = 1.0f;
                     if (state) {
                         const float mean = (float)r / (float)d.cols;
-                        const float next = 0.95f * state[row] + (1.0f - 0.95f) * mean;
+                        const float next = 0.95f * old_state + (1.0f - 0.95f) * mean;
                         factor = 1.0f / sqrtf(fmaxf(next, 1.0e-10f));
                         state[row] = next;
                     }
@@ -396,19 +406,31 @@ k_normuon_stats(const b2_muon_slot_descriptor *slots, uint32_t slot_count, Neuro
             const uint32_t c0 = local * 128 + lane * 4;
             float raw[4] = {0.f, 0.f, 0.f, 0.f}, dot[4] = {0.f, 0.f, 0.f, 0.f}, param = 0.0f;
             if (c0 < d.cols) {
-                for (uint32_t r = warp; r < d.rows; r += kThreads / 32) {
-                    const size_t at = (size_t)r * d.cols + c0;
-                    const float4 u = *reinterpret_cast<const float4 *>(U + at);
-                    const float uu[4] = {u.x, u.y, u.z, u.w};
+                // eight rows per step and warp: eight independent 128-bit loads in flight per thread
+                // (one at a time left each 128-column unit latency-bound at about 100 us)
+                constexpr uint32_t kRowsInFlight = 8, kWarps = kThreads / 32;
+                for (uint32_t r0 = warp; r0 < d.rows; r0 += kWarps * kRowsInFlight) {
+                    float4 u[kRowsInFlight], p[kRowsInFlight];
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) raw[e] = fmaf(uu[e], uu[e], raw[e]);
-                    if (hyperball) {
-                        const float4 p = *reinterpret_cast<const float4 *>(z + at);
-                        const float pp[4] = {p.x, p.y, p.z, p.w};
+                    for (uint32_t k = 0; k < kRowsInFlight; ++k) {
+                        const uint32_t r = r0 + k * kWarps;
+                        const size_t at = (size_t)r * d.cols + c0;
+                        u[k] = r < d.rows ? *reinterpret_cast<const float4 *>(U + at) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (hyperball)
+                            p[k] = r < d.rows ? *reinterpret_cast<const float4 *>(z + at) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            param = fmaf(pp[e], pp[e], param);
-                            dot[e] = fmaf(pp[e], uu[e], dot[e]);
+                    for (uint32_t k = 0; k < kRowsInFlight; ++k) {
+                        const float uu[4] = {u[k].x, u[k].y, u[k].z, u[k].w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) raw[e] = fmaf(uu[e], uu[e], raw[e]);
+                        if (hyperball) {
+                            const float pp[4] = {p[k].x, p[k].y, p[k].z, p[k].w};
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                param = fmaf(pp[e], pp[e], param);
+                                dot[e] = fmaf(pp[e], uu[e], dot[e]);
+                            }
                         }
                     }
                 }
@@ -519,8 +541,9 @@ k_muon_hyperball_update(const b2_muon_slot_descriptor *slots, const uint32_t *pr
                 const float4 u = ld_stream(U + i), zv = ld_stream(z + i), xv = ld_stream(x + i);
                 const float uu[4] = {u.x, u.y, u.z, u.w};
                 float zz[4] = {zv.x, zv.y, zv.z, zv.w}, xx[4] = {xv.x, xv.y, xv.z, xv.w}, yy[4], nf[4];
-                neuron_factors(cx, up, i, 0, nf);
-                const float clip = qk_clip_factor(cx.d, up.d_qk_clip_factors, i);
+                const uint32_t row = i / cx.d.cols;
+                neuron_factors(cx, up, i, row, 0, nf);
+                const float clip = qk_clip_factor(cx.d, up.d_qk_clip_factors, row);
                 if (clip != 1.0f) {
                     uint16_t *mom = reinterpret_cast<uint16_t *>(cx.d.momentum);
                     const uint2 m = *reinterpret_cast<const uint2 *>(mom + i);
@@ -622,7 +645,7 @@ k_muon_sign_update(const b2_muon_slot_descriptor *slots, const uint32_t *prefix,
                 }
                 float zz[4] = {zv.x, zv.y, zv.z, zv.w}, xx[4] = {xv.x, xv.y, xv.z, xv.w};
                 float nm[4], nv[4], yy[4];
-                const float clip = qk_clip_factor(cx.d, up.d_qk_clip_factors, i);
+                const float clip = up.d_qk_clip_factors ? qk_clip_factor(cx.d, up.d_qk_clip_factors, i / cx.d.cols) : 1.0f;
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const float g = gr[e] * mp.grad_scale;
@@ -819,7 +842,6 @@ constexpr uint32_t kItemEncode = 0x80000000u;
 constexpr uint32_t kEncodeSpan = B2_FUSED_ENCODE_SPAN;  // chunks per encode item (list built by the plan)
 constexpr uint64_t kFusedWaitNs = 2000000000ull;
 
-template <int EXT>
 __global__ void __launch_bounds__(kThreads, 5)
 k_muon_update_encode(const b2_muon_slot_descriptor *slots, const uint32_t *prefix, uint32_t slot_count,
                      const uint32_t *items, uint32_t item_count, const uint64_t *u_ptrs, float *amax_x,
@@ -839,7 +861,7 @@ k_muon_update_encode(const b2_muon_slot_descriptor *slots, const uint32_t *prefi
         const uint32_t c = item & ~kItemEncode;
         ChunkCtx cx = chunk_ctx(slots, prefix, slot_count, c);
         if (!(item & kItemEncode)) {
-            update_chunk<EXT>(cx, u_ptrs, amax_x, up, quantize_y != 0, warp_ax, warp_ay);
+            update_chunk<0>(cx, u_ptrs, amax_x, up, quantize_y != 0, warp_ax, warp_ay);
             // Publish.  The barrier orders every thread's stores before thread 0's fence, which is
             // cumulative; thread 0 raised the two maxima before it.  (Letting the other warps run
             // ahead of the fence, or publishing one item late, both measured slower.)
@@ -1362,21 +1384,19 @@ cudaError_t launch_muon_update_encode(const SlotView &v, const uint32_t *items, 
                                       const uint64_t *u_ptrs, float *amax_x, const UpdateParams &up, int quantize_y,
                                       int scale_layout, void *sync, uint32_t *status, cudaStream_t s) {
     if (item_count == 0) return cudaSuccess;
+    // the plain update only: with NorMuon factors or qk-clip the two-launch form measured faster
+    if (up.normuon || up.d_qk_clip_factors) return cudaErrorInvalidValue;
     const int grid = clamp_grid(item_count, v.grid);
-    if (up.normuon || up.d_qk_clip_factors)
-        k_muon_update_encode<1><<<grid, kThreads, 0, s>>>(v.slots, v.chunk_prefix, v.slot_count, items, item_count,
-                                                         u_ptrs, amax_x, up, quantize_y, scale_layout,
-                                                         static_cast<FusedSync *>(sync), status);
-    else
-        k_muon_update_encode<0><<<grid, kThreads, 0, s>>>(v.slots, v.chunk_prefix, v.slot_count, items, item_count,
-                                                         u_ptrs, amax_x, up, quantize_y, scale_layout,
-                                                         static_cast<FusedSync *>(sync), status);
+    k_muon_update_encode<<<grid, kThreads, 0, s>>>(v.slots, v.chunk_prefix, v.slot_count, items, item_count, u_ptrs,
+                                                  amax_x, up, quantize_y, scale_layout,
+                                                  static_cast<FusedSync *>(sync), status);
     return cudaGetLastError();
 }
 cudaError_t launch_normuon_stats(const SlotView &v, const NeuronView &nv, const uint64_t *u_ptrs, int hyperball,
                                  cudaStream_t s) {
     if (nv.total_units == 0) return cudaSuccess;
-    k_normuon_stats<<<clamp_grid(nv.total_units, v.grid), kThreads, 0, s>>>(v.slots, v.slot_count, nv, u_ptrs, hyperball);
+    k_normuon_stats<0><<<clamp_grid(nv.total_units, v.grid), kThreads, 0, s>>>(v.slots, v.slot_count, nv, u_ptrs, hyperball);
+    k_normuon_stats<1><<<clamp_grid(nv.total_units, v.grid), kThreads, 0, s>>>(v.slots, v.slot_count, nv, u_ptrs, hyperball);
     k_normuon_reduce<<<v.slot_count, kThreads, 0, s>>>(v.slots, nv);
     return cudaGetLastError();
 }
