@@ -236,7 +236,10 @@ int b2_materialize_master_static(uint8_t *d_bytes, uint8_t *d_scales, float *d_g
                                  void *stream);
 
 /* `ScheduleFreeMaterializeArgs` / `...PrecomputedArgs`
- * (.../optimizer/args/schedule_free.rs:13-45).  symexp_lin_beta must be 0 (identity). */
+ * (.../optimizer/args/schedule_free.rs:13-45).  symexp_lin_beta > 0 applies the SymExpLin forward
+ * transform (.../optimizer/symexp_lin.rs:8-26) to every schedule value before it is measured and
+ * quantised; symexp_lin_scales are the six device scalars of `SymExpLinScaleRefs` (exponential z, x;
+ * linear z, x; curvature z, x), all NULL for the unit scales the reference uses without them. */
 typedef struct b2_schedule_free_materialize_args {
     uint8_t *bytes;
     uint8_t *scales;
@@ -251,6 +254,7 @@ typedef struct b2_schedule_free_materialize_args {
     float beta;
     float symexp_lin_beta;
     uint32_t scale_layout;
+    const float *symexp_lin_scales[6];
 } b2_schedule_free_materialize_args;
 /* `OptimizerModule::materialize_schedule_free` (.../launcher/update.rs:77-133). */
 int b2_materialize_schedule_free(const b2_schedule_free_materialize_args *args, void *stream);

@@ -48,7 +48,8 @@ class ScheduleFreeMaterializeArgs(C.Structure):
     _fields_ = [("bytes", C.c_void_p), ("scales", C.c_void_p), ("global_scale", C.c_void_p),
                 ("z_master", C.c_void_p), ("x_master", C.c_void_p), ("precomputed_values", C.c_void_p),
                 ("amax", C.c_void_p), ("len", C.c_uint32), ("scale_rows", C.c_uint32), ("scale_k", C.c_uint32),
-                ("beta", C.c_float), ("symexp_lin_beta", C.c_float), ("scale_layout", C.c_uint32)]
+                ("beta", C.c_float), ("symexp_lin_beta", C.c_float), ("scale_layout", C.c_uint32),
+                ("symexp_lin_scales", C.c_void_p * 6)]
 
 
 class AdamWUpdateArgs(C.Structure):

@@ -720,8 +720,17 @@ static int check_sf(const b2_schedule_free_materialize_args *a) {
     if (a->len % 16 != 0 || a->scale_layout > B2_SCALES_RAW) return B2_ERROR_INVALID_VALUE;
     if (a->scale_layout == B2_SCALES_CSF && a->len % 128 != 0) return B2_ERROR_INVALID_VALUE;
     if ((uint64_t)a->scale_rows * a->scale_k < a->len) return B2_ERROR_INVALID_VALUE;
-    if (a->symexp_lin_beta != 0.0f) return B2_ERROR_NOT_SUPPORTED;  // SymExpLin is outside this path
+    if (!(a->symexp_lin_beta >= 0.0f)) return B2_ERROR_INVALID_VALUE;
+    const bool any = a->symexp_lin_scales[0] != nullptr;
+    for (int k = 0; k < 6; ++k)   // the six scale scalars come together or not at all
+        if ((a->symexp_lin_scales[k] != nullptr) != any) return B2_ERROR_INVALID_VALUE;
     return B2_SUCCESS;
+}
+static SymExpLinParams symexp_params(const b2_schedule_free_materialize_args *a) {
+    SymExpLinParams sp;
+    sp.beta = a->symexp_lin_beta;
+    for (int k = 0; k < 6; ++k) sp.scales[k] = a->symexp_lin_scales[k];
+    return sp;
 }
 int b2_materialize_schedule_free_precomputed(const b2_schedule_free_materialize_args *a, void *stream) {
     int rc = check_sf(a);
@@ -733,9 +742,10 @@ int b2_materialize_schedule_free_precomputed(const b2_schedule_free_materialize_
         return (int)launch_quantize_flat(a->precomputed_values, nullptr, nullptr, 0.f, 0, a->amax, a->bytes, a->scales,
                                          a->global_scale, a->len / 16, (int)a->scale_layout, stream_grid_cap(d),
                                          as_stream(stream));
+    const SymExpLinParams sp = symexp_params(a);
     return (int)launch_quantize_flat(nullptr, a->z_master, a->x_master, a->beta, 1, a->amax, a->bytes, a->scales,
                                      a->global_scale, a->len / 16, (int)a->scale_layout, stream_grid_cap(d),
-                                     as_stream(stream));
+                                     as_stream(stream), &sp);
 }
 int b2_materialize_schedule_free(const b2_schedule_free_materialize_args *a, void *stream) {
     int rc = check_sf(a);
@@ -745,10 +755,12 @@ int b2_materialize_schedule_free(const b2_schedule_free_materialize_args *a, voi
     if (e != cudaSuccess) return (int)e;
     cudaStream_t s = as_stream(stream);
     e = cudaMemsetAsync(a->amax, 0, sizeof(float), s);  // launcher/update.rs:14-23 (zero_amax)
-    if (e == cudaSuccess) e = launch_schedule_free_amax(a->z_master, a->x_master, a->beta, a->len, a->amax, stream_grid_cap(d), s);
+    const SymExpLinParams sp = symexp_params(a);
+    if (e == cudaSuccess)
+        e = launch_schedule_free_amax(a->z_master, a->x_master, a->beta, a->len, a->amax, stream_grid_cap(d), s, &sp);
     if (e == cudaSuccess)
         e = launch_quantize_flat(nullptr, a->z_master, a->x_master, a->beta, 1, a->amax, a->bytes, a->scales,
-                                 a->global_scale, a->len / 16, (int)a->scale_layout, stream_grid_cap(d), s);
+                                 a->global_scale, a->len / 16, (int)a->scale_layout, stream_grid_cap(d), s, &sp);
     return (int)e;
 }
 

@@ -146,6 +146,24 @@ __device__ __forceinline__ size_t sm100_scale_offset(uint32_t row, uint32_t kb, 
     return ((size_t)(row >> 7) * kb_tiles + (kb >> 2)) * 512 + (row & 31u) * 16 + ((row >> 5) & 3u) * 4 + (kb & 3u);
 }
 
+// ---- SymExpLin forward (crates/cuda-kernels/src/gpt/optimizer/symexp_lin.rs:8-26) -------------
+struct SymExpLin {
+    float beta, exponential, linear, curvature;
+};
+// exp_f32 of the reference: ex2.approx.ftz.f32(x * log2(e)) (crates/cuda-kernels/src/utils/float_ptx.rs:46-51)
+__device__ __forceinline__ float exp_approx(float x) {
+    float r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x * 1.4426950408889634f));
+    return r;
+}
+__device__ __forceinline__ float symexp_forward(float raw, const SymExpLin &s) {
+    if (s.beta <= 0.0f) return raw;
+    const float sign = raw > 0.0f ? 1.0f : (raw < 0.0f ? -1.0f : 0.0f);
+    if (sign == 0.0f) return 0.0f;
+    const float exponential = s.exponential * (exp_approx(s.beta * s.curvature * fabsf(raw)) - 1.0f) / s.beta;
+    return sign * (exponential + s.linear * raw / s.beta);
+}
+
 // ---- reductions ----------------------------------------------------------------------------
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll

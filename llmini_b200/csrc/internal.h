@@ -69,12 +69,19 @@ cudaError_t launch_muon_encode(const SlotView &v, const float *amax_x, int quant
 cudaError_t launch_tensor_chunk_amax(const float *x, float *chunk_amax, uint32_t n, cudaStream_t s);
 cudaError_t launch_tensor_amax_from_chunks(const float *chunk_amax, float *out, uint32_t count,
                                            cudaStream_t s);
+// SymExpLin forward of the schedule values: beta <= 0 is the identity; scale pointers as in
+// b2_schedule_free_materialize_args (all NULL = unit scales).
+struct SymExpLinParams {
+    float beta;
+    const float *scales[6];
+};
 cudaError_t launch_quantize_flat(const float *x, const float *z, const float *xm, float beta,
                                  int mode, const float *amax, uint8_t *fp4, uint8_t *scales,
                                  float *gs, uint32_t group_count, int scale_layout, int grid_cap,
-                                 cudaStream_t s);
+                                 cudaStream_t s, const SymExpLinParams *symexp = nullptr);
 cudaError_t launch_schedule_free_amax(const float *z, const float *x, float beta, uint32_t len,
-                                      float *amax, int grid_cap, cudaStream_t s);
+                                      float *amax, int grid_cap, cudaStream_t s,
+                                      const SymExpLinParams *symexp = nullptr);
 cudaError_t launch_adamw(const b2_adamw_update_args &a, int mode, int grid_cap,
                          cudaStream_t s);
 cudaError_t launch_adamw_multi(const b2_adamw_slot_descriptor *table, uint32_t count, uint32_t total_chunks,

@@ -710,11 +710,28 @@ k_muon_sign_update(const b2_muon_slot_descriptor *slots, const uint32_t *prefix,
 // ---------------------------------------------------------------------------------------------
 constexpr int kEncodeThreads = kChunk / 16;
 
+// Scalars of the transform: the three scales are schedule-free pairs themselves
+// (symexp_lin.rs:164-196: z + beta (x - z) with the SCHEDULE beta); no pointers = unit scales.
+__device__ __forceinline__ SymExpLin symexp_resolve(const SymExpLinParams &p, float schedule_beta) {
+    SymExpLin s = {p.beta, 1.0f, 1.0f, 1.0f};
+    if (p.beta > 0.0f && p.scales[0] != nullptr) {
+        float v[3];
+#pragma unroll
+        for (int k = 0; k < 3; ++k) {
+            const float z = __ldg(p.scales[2 * k]), x = __ldg(p.scales[2 * k + 1]);
+            v[k] = z + schedule_beta * (x - z);
+        }
+        s.exponential = v[0]; s.linear = v[1]; s.curvature = v[2];
+    }
+    return s;
+}
+
 template <int MODE, int THREADS = kEncodeThreads, bool L2_ONLY = false>
 __device__ __forceinline__ void encode_chunk(const float *src, const float *z, const float *xm,
                                              float beta, uint32_t len, uint32_t base, float gs,
                                              uint8_t *fp4, uint8_t *scales, int scale_layout,
-                                             uint32_t csf_k, uint32_t csf_rows) {
+                                             uint32_t csf_k, uint32_t csf_rows,
+                                             const SymExpLin sx = SymExpLin{0.0f, 1.0f, 1.0f, 1.0f}) {
     // Each warp owns 32 consecutive groups = 2048 contiguous bytes.  It reads them with four
     // fully coalesced 128-bit loads per lane, parks them in shared memory (16-byte slots XOR-ed
     // with the group number so neither side conflicts) and every lane picks up its own group.
@@ -736,10 +753,10 @@ __device__ __forceinline__ void encode_chunk(const float *src, const float *z, c
                 t = L2_ONLY ? __ldcg(reinterpret_cast<const float4 *>(src + e)) : ld_stream(src + e);
             } else {
                 float4 zv = ld_stream(z + e), xv = ld_stream(xm + e);
-                t.x = zv.x + beta * (xv.x - zv.x);
-                t.y = zv.y + beta * (xv.y - zv.y);
-                t.z = zv.z + beta * (xv.z - zv.z);
-                t.w = zv.w + beta * (xv.w - zv.w);
+                t.x = symexp_forward(zv.x + beta * (xv.x - zv.x), sx);
+                t.y = symexp_forward(zv.y + beta * (xv.y - zv.y), sx);
+                t.z = symexp_forward(zv.z + beta * (xv.z - zv.z), sx);
+                t.w = symexp_forward(zv.w + beta * (xv.w - zv.w), sx);
             }
         }
         const uint32_t g = f4 >> 2, k = f4 & 3;
@@ -935,7 +952,8 @@ template <int MODE>
 __global__ void __launch_bounds__(kEncodeThreads)
 k_quantize_flat(const float *src, const float *z, const float *xm, float beta, const float *amax,
                 uint8_t *fp4, uint8_t *scales, float *out_gs, uint32_t group_count,
-                int scale_layout) {
+                int scale_layout, SymExpLinParams sp) {
+    const SymExpLin sx = symexp_resolve(sp, beta);
     const uint32_t len = group_count * 16;
     const uint32_t chunks = (len + kChunk - 1) / kChunk;
     const float gs = four_six_global_scale(amax[0]);
@@ -946,7 +964,7 @@ k_quantize_flat(const float *src, const float *z, const float *xm, float beta, c
     }
     if (blockIdx.x == 0 && threadIdx.x == 0) out_gs[0] = gs;
     for (uint32_t c = blockIdx.x; c < chunks; c += gridDim.x)
-        encode_chunk<MODE>(src, z, xm, beta, len, c * kChunk, gs, fp4, scales, scale_layout, k, rows);
+        encode_chunk<MODE>(src, z, xm, beta, len, c * kChunk, gs, fp4, scales, scale_layout, k, rows, sx);
 }
 
 // `tensor_chunk_amax_f32_kernel` / `tensor_amax_from_chunks_f32_kernel`
@@ -994,8 +1012,9 @@ k_tensor_amax_from_chunks(const float *chunk_amax, float *out, uint32_t count) {
 
 // `schedule_free_amax_kernel` (crates/cuda-kernels/src/gpt/optimizer/schedule_free/amax.rs:16-68).
 __global__ void __launch_bounds__(kThreads)
-k_schedule_free_amax(const float *z, const float *x, float beta, uint32_t len, float *amax) {
+k_schedule_free_amax(const float *z, const float *x, float beta, uint32_t len, float *amax, SymExpLinParams sp) {
     __shared__ float warp_part[kThreads / 32];
+    const SymExpLin sx = symexp_resolve(sp, beta);
     const int tid = threadIdx.x;
     const uint32_t chunks = (len + kChunk - 1) / kChunk;
     float m = 0.0f;
@@ -1005,12 +1024,13 @@ k_schedule_free_amax(const float *z, const float *x, float beta, uint32_t len, f
             uint32_t i = c * kChunk + h * (kChunk / 2) + tid * 4;
             if (i + 4 <= len) {
                 float4 zv = ld_stream(z + i), xv = ld_stream(x + i);
-                m = fmaxf(m, fabsf(zv.x + beta * (xv.x - zv.x)));
-                m = fmaxf(m, fabsf(zv.y + beta * (xv.y - zv.y)));
-                m = fmaxf(m, fabsf(zv.z + beta * (xv.z - zv.z)));
-                m = fmaxf(m, fabsf(zv.w + beta * (xv.w - zv.w)));
+                m = fmaxf(m, fabsf(symexp_forward(zv.x + beta * (xv.x - zv.x), sx)));
+                m = fmaxf(m, fabsf(symexp_forward(zv.y + beta * (xv.y - zv.y), sx)));
+                m = fmaxf(m, fabsf(symexp_forward(zv.z + beta * (xv.z - zv.z), sx)));
+                m = fmaxf(m, fabsf(symexp_forward(zv.w + beta * (xv.w - zv.w), sx)));
             } else {
-                for (uint32_t j = i; j < len && j < i + 4; ++j) m = fmaxf(m, fabsf(z[j] + beta * (x[j] - z[j])));
+                for (uint32_t j = i; j < len && j < i + 4; ++j)
+                    m = fmaxf(m, fabsf(symexp_forward(z[j] + beta * (x[j] - z[j]), sx)));
             }
         }
     }
@@ -1436,21 +1456,25 @@ cudaError_t launch_tensor_amax_from_chunks(const float *chunk_amax, float *out, 
 cudaError_t launch_quantize_flat(const float *x, const float *z, const float *xm, float beta,
                                  int mode, const float *amax, uint8_t *fp4, uint8_t *scales,
                                  float *gs, uint32_t group_count, int scale_layout, int grid_cap,
-                                 cudaStream_t s) {
+                                 cudaStream_t s, const SymExpLinParams *symexp) {
+    SymExpLinParams sp = {};
+    if (symexp) sp = *symexp;
     uint32_t chunks = (group_count * 16 + kChunk - 1) / kChunk;
     int grid = clamp_grid(chunks, 2 * grid_cap);
     if (grid == 0) grid = 1;  // still writes the global scale
     if (mode == 0)
-        k_quantize_flat<0><<<grid, kEncodeThreads, 0, s>>>(x, z, xm, beta, amax, fp4, scales, gs, group_count, scale_layout);
+        k_quantize_flat<0><<<grid, kEncodeThreads, 0, s>>>(x, z, xm, beta, amax, fp4, scales, gs, group_count, scale_layout, sp);
     else
-        k_quantize_flat<1><<<grid, kEncodeThreads, 0, s>>>(x, z, xm, beta, amax, fp4, scales, gs, group_count, scale_layout);
+        k_quantize_flat<1><<<grid, kEncodeThreads, 0, s>>>(x, z, xm, beta, amax, fp4, scales, gs, group_count, scale_layout, sp);
     return cudaGetLastError();
 }
 cudaError_t launch_schedule_free_amax(const float *z, const float *x, float beta, uint32_t len,
-                                      float *amax, int grid_cap, cudaStream_t s) {
+                                      float *amax, int grid_cap, cudaStream_t s, const SymExpLinParams *symexp) {
+    SymExpLinParams sp = {};
+    if (symexp) sp = *symexp;
     uint32_t chunks = (len + kChunk - 1) / kChunk;
     if (chunks == 0) return cudaSuccess;
-    k_schedule_free_amax<<<clamp_grid(chunks, grid_cap), kThreads, 0, s>>>(z, x, beta, len, amax);
+    k_schedule_free_amax<<<clamp_grid(chunks, grid_cap), kThreads, 0, s>>>(z, x, beta, len, amax, sp);
     return cudaGetLastError();
 }
 cudaError_t launch_adamw(const b2_adamw_update_args &a, int mode, int grid_cap,

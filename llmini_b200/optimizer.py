@@ -261,9 +261,14 @@ class OptimizerModule:
                                                      len_, scale_layout, _stream()), "materialize_master_static")
 
     def _sf_args(self, *, bytes, scales, global_scale, z_master, x_master, amax, len, scale_rows, scale_k, beta,
-                 symexp_lin_beta=0.0, precomputed_values=None, scale_layout=SCALES_CSF, **_ignored):
+                 symexp_lin_beta=0.0, symexp_lin_scales=None, precomputed_values=None, scale_layout=SCALES_CSF,
+                 **_ignored):
+        # symexp_lin_scales: `SymExpLinScaleRefs`, six f32[1] device tensors (exponential z, x; linear z, x;
+        # curvature z, x), or None for unit scales
+        ptrs = (C.c_void_p * 6)(*[_ptr(t) for t in (symexp_lin_scales or [None] * 6)])
         return _CSf(_ptr(bytes), _ptr(scales), _ptr(global_scale), _ptr(z_master), _ptr(x_master),
-                    _ptr(precomputed_values), _ptr(amax), len, scale_rows, scale_k, beta, symexp_lin_beta, scale_layout)
+                    _ptr(precomputed_values), _ptr(amax), len, scale_rows, scale_k, beta, symexp_lin_beta, scale_layout,
+                    ptrs)
 
     # launcher/update.rs:77-133
     def materialize_schedule_free(self, **kw) -> None:

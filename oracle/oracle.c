@@ -9,12 +9,15 @@
  * 971e353af258a05279aee7f805dfcfe8e95a0e30 in Cargo.lock) and cannot be built or run where
  * this oracle was written, so the oracle is pinned against the known answers that the
  * reference's own tests hold (see tests/test_oracle_known_answers.py) and not against
- * reference outputs.  For the NVFP4 codes and block scales the reference holds no
- * host-side golden at all: for those two outputs parity is UNPINNED and this oracle is the
- * arbiter.  Two things cannot be read from the reference's source and are switches here:
- * whether `a*b + c` expressions are contracted to FMA (`contract`), and the exact result
- * of `rcp.approx.ftz.f32` (hardware-defined; callers may pass a table of reciprocals
- * taken from the GPU, otherwise the correctly rounded reciprocal is used).
+ * reference outputs.  The NVFP4 codes, block scales and tensor scale ARE pinned against a
+ * reference output: the FNV-1a digest that crates/cuda-kernels/tests/csf_quantization.rs:526
+ * holds for `fp32_to_nvfp4_four_six` on a 128 x 128 tensor, captured from the reference's own
+ * PTX, is reproduced by orc_nvfp4_quantize (tests/test_reference_digests.py).  Two things
+ * cannot be read from the reference's source and are switches here: whether `a*b + c`
+ * expressions are contracted to FMA (`contract`; the second digest of that test, which the
+ * GPU library reproduces, says they are not), and the exact result of `rcp.approx.ftz.f32`
+ * (hardware-defined; callers may pass a table of reciprocals taken from the GPU, otherwise
+ * the correctly rounded reciprocal is used).
  *
  * Each function cites the reference file:line it follows (paths relative to the
  * reference's repository root).

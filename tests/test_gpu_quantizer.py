@@ -134,9 +134,24 @@ def test_materialize_master_and_schedule_free():
     opt.materialize_schedule_free_precomputed(**kw)
     torch.cuda.synchronize()
     assert np.array_equal(host(t4.bytes), codes2)
-    with pytest.raises(b2.B2Error):
-        kw.update(symexp_lin_beta=0.5)
+    with pytest.raises(b2.B2Error):   # a negative SymExpLin beta is an argument error
+        kw.update(symexp_lin_beta=-0.5)
         opt.materialize_schedule_free(**kw)
+    # SymExpLin with explicit scale scalars against its definition (symexp_lin.rs:8-26); exp() here is
+    # the exact one, the device uses ex2.approx: values agree to a few ulp, so compare dequantised
+    kw.update(symexp_lin_beta=4.0)
+    one = lambda v: torch.full((1,), v, device="cuda")
+    sc = [one(1.25), one(0.75), one(0.5), one(1.5), one(2.0), one(1.0)]   # (z, x) of exponential, linear, curvature
+    kw.update(symexp_lin_scales=sc)
+    opt.materialize_schedule_free(**kw)
+    torch.cuda.synchronize()
+    e_, l_, c_ = [zz + beta * (xx - zz) for zz, xx in ((1.25, 0.75), (0.5, 1.5), (2.0, 1.0))]
+    y64 = y.astype(np.float64)
+    want = np.sign(y64) * (e_ * (np.exp(4.0 * c_ * np.abs(y64)) - 1.0) / 4.0 + l_ * y64 / 4.0)
+    assert abs(host(amax2)[0] - np.max(np.abs(want))) <= 1e-5 * np.max(np.abs(want))
+    deq = o.nvfp4_dequantize(host(t4.bytes), o.csf_decode_matrix(host(t4.scales), rows, k), host(t4.global_scale)[0])
+    assert np.max(np.abs(deq - want)) <= 0.26 * np.max(np.abs(want))   # an E2M1 step at the top of the range
+    assert np.corrcoef(deq, want)[0, 1] > 0.99
 
 
 def test_quantise_round_trip_property_large():

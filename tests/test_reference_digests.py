@@ -1,0 +1,74 @@
+"""Golden digests the reference holds for the four-six NVFP4 quantiser: FNV-1a over the packed
+E2M1 bytes, the decoded E4M3 block-scale bytes and the little-endian FP32 tensor scale, captured
+from the reference's own PTX (crates/cuda-kernels/tests/csf_quantization.rs:505-572,
+`persistent_materialization_128_columns_preserves_original_bytes`).  They pin codes, block scales
+and tensor scale of the oracle (CPU) and of this build's kernels (GPU) bit for bit."""
+import numpy as np
+import pytest
+
+import llmini_b200 as b2
+from oracle import oracle as o
+
+F = np.float32
+LEN = 128 * 128
+DIRECT_DIGEST = 0x8B6E8A7E1DFFF073       # fp32_to_nvfp4_four_six on x
+SCHEDULED_DIGEST = 0xD8F0E69E822B79DF    # materialize_schedule_free, beta 0.7, symexp_lin_beta 12.5, no scale slots
+
+
+def fnv1a(*parts) -> int:
+    h = 0xCBF29CE484222325
+    for part in parts:
+        for byte in bytes(part):
+            h = ((h ^ byte) * 0x100000001B3) & 0xFFFFFFFFFFFFFFFF
+    return h
+
+
+def inputs():
+    i = np.arange(LEN)
+    x = (((i * 17 + 13) % 251).astype(F) - F(125.0)) * F(0.001)
+    z = (((i * 29 + 7) % 277).astype(F) - F(138.0)) * F(0.001)
+    return x.astype(F), z.astype(F)
+
+
+def test_oracle_quantiser_reproduces_the_reference_digest():
+    x, _ = inputs()
+    codes, raw, gs, _ = o.nvfp4_quantize(x, amax=np.max(np.abs(x)))
+    assert codes.size + raw.size + 4 == 9220
+    assert fnv1a(codes.tobytes(), raw.tobytes(), F(gs).tobytes()) == DIRECT_DIGEST
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("layout", [b2.SCALES_CSF, b2.SCALES_RAW])
+def test_gpu_quantiser_reproduces_the_reference_digest(layout):
+    import torch
+    from tests.gpu_util import dev, host
+    x, _ = inputs()
+    q = b2.Nvfp4QuantModule()
+    t = b2.Nvfp4Tensor.empty(128, 128, layout)
+    amax = dev(np.array([np.max(np.abs(x))], F))
+    q.fp32_to_nvfp4_four_six(dev(x), amax, t.bytes, t.scales, t.global_scale, LEN // 16, layout)
+    torch.cuda.synchronize()
+    stored = host(t.scales)
+    raw = stored[: LEN // 16] if layout == b2.SCALES_RAW else \
+        np.array([b2.csf_scale_at(stored, g) for g in range(LEN // 16)], np.uint8)
+    assert fnv1a(host(t.bytes).tobytes(), raw.tobytes(), host(t.global_scale).tobytes()) == DIRECT_DIGEST
+
+
+@pytest.mark.gpu
+def test_gpu_schedule_free_materialisation_with_symexp_lin_reproduces_the_reference_digest():
+    # the second digest of the same reference test: y = SymExpLin(z + beta (x - z)) with beta 0.7,
+    # symexp_lin_beta 12.5 and no scale slots, measured and quantised by materialize_schedule_free.
+    # It goes through ex2.approx, un-fused multiply-adds and IEEE division exactly as assumed here.
+    import torch
+    from tests.gpu_util import dev, host
+    x, z = inputs()
+    opt = b2.OptimizerModule()
+    t = b2.Nvfp4Tensor.empty(128, 128, b2.SCALES_CSF)
+    amax = dev(np.array([np.max(np.abs(x))], F))
+    opt.materialize_schedule_free(bytes=t.bytes, scales=t.scales, global_scale=t.global_scale, z_master=dev(z),
+                                  x_master=dev(x), amax=amax, len=LEN, scale_rows=128, scale_k=128, beta=0.7,
+                                  symexp_lin_beta=12.5, scale_layout=b2.SCALES_CSF)
+    torch.cuda.synchronize()
+    stored = host(t.scales)
+    raw = np.array([b2.csf_scale_at(stored, g) for g in range(LEN // 16)], np.uint8)
+    assert fnv1a(host(t.bytes).tobytes(), raw.tobytes(), host(t.global_scale).tobytes()) == SCHEDULED_DIGEST
