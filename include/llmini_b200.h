@@ -63,6 +63,17 @@ typedef struct b2_muon_slot_descriptor {
     uint32_t reserved_padding;
 } b2_muon_slot_descriptor;
 
+/* Same field order and 152-byte stride as `SymExpLinSlotDescriptor`
+ * (crates/cuda-kernels/src/gpt/optimizer/args/symexp_lin.rs:5-26).  Only the six scale scalars
+ * (f32[1] each, as schedule-free z / x pairs) are read on this path. */
+typedef struct b2_symexp_lin_slot_descriptor {
+    uint64_t grad, z_master, x_master;
+    uint64_t exponential_z, exponential_x, exponential_grad, exponential_first, exponential_second;
+    uint64_t linear_z, linear_x, linear_grad, linear_first, linear_second;
+    uint64_t curvature_z, curvature_x, curvature_grad, curvature_first, curvature_second;
+    uint32_t rows, cols;
+} b2_symexp_lin_slot_descriptor;
+
 enum { B2_OPERAND_BF16 = 0, B2_OPERAND_F16 = 1 };
 enum { B2_SCALES_CSF = 0, B2_SCALES_RAW = 1,
        B2_SCALES_SM100 = 2 /* the block-scale operand layout of sm_100a's `tcgen05.mma
@@ -113,6 +124,11 @@ typedef struct b2_muon_step_args {
                                    `MuonTmaFinishArgs`): slots whose qk_clip_factor_offset is not
                                    UINT32_MAX scale z', x', momentum (and variance) of their query/key
                                    rows (row < 2*cols, head = (row % cols) / qk_clip_head_dim) */
+    float symexp_lin_beta;      /* > 0: y = SymExpLin(z' + beta (x' - z')) (.../optimizer/symexp_lin.rs:8-26) in
+                                   the finish, Hyperball and sign entry points; 0 = identity */
+    const struct b2_symexp_lin_slot_descriptor *d_symexp_lin_slots; /* DEVICE table, one entry per slot
+                                   (`symexp_lin_slots` of MuonTmaFinishArgs); NULL or an entry whose
+                                   exponential_z is 0 means unit scales */
     uint32_t normuon;           /* 1: the finish stage first updates every slot's `second_momentum`
                                    (beta2 0.95) from the orthogonalised update and scales each neuron by
                                    1/sqrt(second moment), renormalised to the update's Frobenius norm

@@ -41,7 +41,16 @@ class MuonStepArgs(C.Structure):
                 ("weight_decay", C.c_float), ("average_coefficient", C.c_float), ("schedule_beta", C.c_float),
                 ("iterations", C.c_uint32), ("nesterov", C.c_uint32), ("coefficients", C.POINTER(C.c_float)),
                 ("d_grad_scale", C.c_void_p), ("variance_adaptive", C.c_uint32), ("bias_correction_inv", C.c_float),
-                ("d_qk_clip_factors", C.c_void_p), ("normuon", C.c_uint32), ("reserved_padding", C.c_uint32)]
+                ("d_qk_clip_factors", C.c_void_p), ("symexp_lin_beta", C.c_float),
+                ("d_symexp_lin_slots", C.c_void_p), ("normuon", C.c_uint32), ("reserved_padding", C.c_uint32)]
+
+
+class SymExpLinSlotDescriptor(C.Structure):
+    """`SymExpLinSlotDescriptor` (args/symexp_lin.rs:5-26), 152 bytes."""
+    _fields_ = [(n, C.c_uint64) for n in (
+        "grad", "z_master", "x_master", "exponential_z", "exponential_x", "exponential_grad", "exponential_first",
+        "exponential_second", "linear_z", "linear_x", "linear_grad", "linear_first", "linear_second", "curvature_z",
+        "curvature_x", "curvature_grad", "curvature_first", "curvature_second")] + [("rows", C.c_uint32), ("cols", C.c_uint32)]
 
 
 class ScheduleFreeMaterializeArgs(C.Structure):

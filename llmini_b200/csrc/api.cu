@@ -500,6 +500,8 @@ static UpdateParams update_params(const b2_muon_step_args *a) {
     up.normuon = 0;
     up.factor_ptrs = nullptr;
     up.slot_stats = nullptr;
+    up.symexp_beta = a->symexp_lin_beta > 0.0f ? a->symexp_lin_beta : 0.0f;
+    up.symexp_slots = a->d_symexp_lin_slots;
     return up;
 }
 
@@ -576,7 +578,8 @@ static int finish_impl(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_slot
     }
     const int quantize_y = plan->options.quantize_target == B2_QUANTIZE_Y;
     // one launch for the plain update; NorMuon / qk-clip steps (and measurement flag 16) take two
-    if (quantize && !(plan->options.reserved[2] & 16u) && !up.normuon && !up.d_qk_clip_factors) {
+    if (quantize && !(plan->options.reserved[2] & 16u) && !up.normuon && !up.d_qk_clip_factors &&
+        up.symexp_beta == 0.0f) {
         if (e == cudaSuccess)
             e = launch_muon_update_encode(v, plan->at<uint32_t>(L.off_items), (uint32_t)L.items.size(),
                                           plan->at<uint64_t>(L.off_u_ptrs), amax_x, up, quantize_y,

@@ -39,6 +39,8 @@ struct UpdateParams {
     int normuon;                   // 1: scale U by factor[neuron] * normuon_scale
     const uint64_t *factor_ptrs;
     const float *slot_stats;
+    float symexp_beta;             // > 0: SymExpLin forward on y, scales from the slot table (or unit)
+    const b2_symexp_lin_slot_descriptor *symexp_slots;
 };
 cudaError_t launch_muon_sumsq(const SlotView &v, const MomentumParams &mp, double *partials, float *amax_x,
                               cudaStream_t s);

@@ -203,6 +203,27 @@ k_muon_momentum_normalize(const b2_muon_slot_descriptor *slots, const uint32_t *
     }
 }
 
+// Per-slot SymExpLin scalars for the update kernels (tma_split.rs:38-55): identity unless the step
+// asks for the transform; unit scales unless the slot's entry carries scale scalars.
+__device__ __forceinline__ SymExpLin symexp_for_slot(const UpdateParams &up, uint32_t slot) {
+    SymExpLin s = {up.symexp_beta, 1.0f, 1.0f, 1.0f};
+    if (up.symexp_beta > 0.0f && up.symexp_slots != nullptr) {
+        const b2_symexp_lin_slot_descriptor &d = up.symexp_slots[slot];
+        if (d.exponential_z != 0) {
+            const uint64_t p[6] = {d.exponential_z, d.exponential_x, d.linear_z, d.linear_x, d.curvature_z, d.curvature_x};
+            float v[3];
+#pragma unroll
+            for (int k = 0; k < 3; ++k) {
+                const float z = __ldg(reinterpret_cast<const float *>(p[2 * k]));
+                const float x = __ldg(reinterpret_cast<const float *>(p[2 * k + 1]));
+                v[k] = z + up.beta * (x - z);
+            }
+            s.exponential = v[0]; s.linear = v[1]; s.curvature = v[2];
+        }
+    }
+    return s;
+}
+
 // NorMuon factors of four consecutive elements (update/one.rs:48-56): the neuron is the row when
 // rows >= cols, else the column; `with_scale` multiplies in the per-slot normuon_scale.
 __device__ __forceinline__ void neuron_factors(const ChunkCtx &cx, const UpdateParams &up, uint32_t i, uint32_t row,
@@ -243,6 +264,7 @@ __device__ __forceinline__ void update_chunk(const ChunkCtx &cx, const uint64_t 
     const float scale = 0.2f * sqrtf(fmaxf((float)cx.d.rows, (float)cx.d.cols));
     const float decay = 1.0f - lr_s * wd;
     const uint32_t base = cx.local_chunk * kChunk;
+    const SymExpLin sx = EXT ? symexp_for_slot(up, cx.slot) : SymExpLin{0.0f, 1.0f, 1.0f, 1.0f};
     float ax = 0.0f, ay = 0.0f;
     // all six loads of the thread go out before the first store: the stores below could alias
     // them as far as the compiler knows, so it would not hoist the second half by itself
@@ -294,6 +316,7 @@ __device__ __forceinline__ void update_chunk(const ChunkCtx &cx, const uint64_t 
                     nx *= clip;
                 }
                 float sv = nz + beta * (nx - nz);
+                if (EXT) sv = symexp_forward(sv, sx);
                 zz[e] = nz;
                 xx[e] = nx;
                 yy[e] = sv;
@@ -532,6 +555,7 @@ k_muon_hyperball_update(const b2_muon_slot_descriptor *slots, const uint32_t *pr
         const float candidate = fmaxf(radius * radius - 2.0f * step_scale * dot +
                                           step_scale * step_scale * update_norm * update_norm, 1.0e-10f);
         const float projection = radius / sqrtf(candidate);
+        const SymExpLin sx = symexp_for_slot(up, cx.slot);
         const uint32_t base = cx.local_chunk * kChunk;
         float ax = 0.0f, ay = 0.0f;
 #pragma unroll
@@ -567,7 +591,7 @@ k_muon_hyperball_update(const b2_muon_slot_descriptor *slots, const uint32_t *pr
                         pz *= clip;
                         nx *= clip;
                     }
-                    const float sv = pz + up.beta * (nx - pz);
+                    const float sv = symexp_forward(pz + up.beta * (nx - pz), sx);
                     zz[e] = pz; xx[e] = nx; yy[e] = sv;
                     ax = fmaxf(ax, fabsf(nx));
                     ay = fmaxf(ay, fabsf(sv));
@@ -625,6 +649,7 @@ k_muon_sign_update(const b2_muon_slot_descriptor *slots, const uint32_t *prefix,
         const float lr_s = up.lr * cx.d.learning_rate_multiplier;
         const float decay = 1.0f - lr_s * up.wd;
         const float one_minus_mu = 1.0f - mp.mu;
+        const SymExpLin sx = symexp_for_slot(up, cx.slot);
         const uint32_t base = cx.local_chunk * kChunk;
         float ax = 0.0f, ay = 0.0f;
 #pragma unroll
@@ -664,7 +689,7 @@ k_muon_sign_update(const b2_muon_slot_descriptor *slots, const uint32_t *prefix,
                         nm[e] *= clip;
                         if (mp.variance_adaptive) nv[e] *= clip * clip;
                     }
-                    const float sv = nz + up.beta * (nx - nz);
+                    const float sv = symexp_forward(nz + up.beta * (nx - nz), sx);
                     zz[e] = nz; xx[e] = nx; yy[e] = sv;
                     ax = fmaxf(ax, fabsf(nx));
                     ay = fmaxf(ay, fabsf(sv));
@@ -1363,7 +1388,7 @@ cudaError_t launch_muon_momentum_normalize(const SlotView &v, const MomentumPara
 cudaError_t launch_muon_update(const SlotView &v, const uint64_t *u_ptrs, float *amax_x, const UpdateParams &up,
                                cudaStream_t s) {
     if (v.total_chunks == 0) return cudaSuccess;
-    if (up.normuon || up.d_qk_clip_factors)
+    if (up.normuon || up.d_qk_clip_factors || up.symexp_beta > 0.0f)
         k_muon_update<1><<<clamp_grid(v.total_chunks, v.grid), kThreads, 0, s>>>(
             v.slots, v.chunk_prefix, v.slot_count, v.total_chunks, u_ptrs, amax_x, up);
     else
@@ -1405,7 +1430,7 @@ cudaError_t launch_muon_update_encode(const SlotView &v, const uint32_t *items, 
                                       int scale_layout, void *sync, uint32_t *status, cudaStream_t s) {
     if (item_count == 0) return cudaSuccess;
     // the plain update only: with NorMuon factors or qk-clip the two-launch form measured faster
-    if (up.normuon || up.d_qk_clip_factors) return cudaErrorInvalidValue;
+    if (up.normuon || up.d_qk_clip_factors || up.symexp_beta > 0.0f) return cudaErrorInvalidValue;
     const int grid = clamp_grid(item_count, v.grid);
     k_muon_update_encode<<<grid, kThreads, 0, s>>>(v.slots, v.chunk_prefix, v.slot_count, items, item_count, u_ptrs,
                                                   amax_x, up, quantize_y, scale_layout,

@@ -102,6 +102,8 @@ class MuonMegaUpdateArgs:
     bias_correction_inv: float = 1.0
     qk_clip_factors: Optional[torch.Tensor] = None     # f32 per-head factors on the device
     normuon: bool = False                              # slots need a `second_momentum` buffer
+    symexp_lin_beta: float = 0.0                       # > 0: SymExpLin forward on y
+    symexp_lin_slots: Optional[torch.Tensor] = None    # device table of SymExpLinSlotDescriptor, or None
 
     def c_args(self):
         co = None
@@ -113,7 +115,7 @@ class MuonMegaUpdateArgs:
         a = MuonStepArgs(self.mu, self.grad_scale, self.learning_rate, self.weight_decay, self.average_coefficient,
                          self.schedule_beta, self.iterations, int(self.nesterov), co, _ptr(self.grad_scale_device),
                          int(self.variance_adaptive), self.bias_correction_inv, _ptr(self.qk_clip_factors),
-                         int(self.normuon), 0)
+                         self.symexp_lin_beta, _ptr(self.symexp_lin_slots), int(self.normuon), 0)
         return a, keep
 
 

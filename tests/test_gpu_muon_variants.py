@@ -354,3 +354,72 @@ def test_fused_update_encode_equals_two_launches(target, ext):
         for u, v in zip(a, b):
             assert np.array_equal(u, v)
         assert a[5].any() and a[4][0] > 0
+
+
+def _symexp(raw, beta, e=1.0, l=1.0, c=1.0):
+    """SymExpLin forward (crates/cuda-kernels/src/gpt/optimizer/symexp_lin.rs:8-26) in float64."""
+    raw = raw.astype(np.float64)
+    return np.sign(raw) * (e * (np.exp(beta * c * np.abs(raw)) - 1.0) / beta + l * raw / beta)
+
+
+@pytest.mark.parametrize("entry", ["finish", "hyperball", "sign"])
+def test_symexp_lin_forward_in_the_update_kernels(entry):
+    # y = SymExpLin(z' + beta (x' - z')) with per-slot scale scalars (slot 0) and unit scales (slot 1);
+    # masters stay bit-exact, y follows the definition to the accuracy of ex2.approx
+    import ctypes as C
+    from llmini_b200 import _ffi
+    rng = np.random.default_rng(41)
+    shapes = [(96, 64), (64, 128)]
+    sbeta, sym_beta = 0.6, 6.0
+    one = lambda v: torch.full((1,), v, device="cuda")
+    pairs = [(1.25, 0.75), (0.5, 1.5), (2.0, 1.0)]          # (z, x) of exponential, linear, curvature
+    keep = [one(v) for pr in pairs for v in pr]
+    descs = (_ffi.SymExpLinSlotDescriptor * 2)()
+    for name, t in zip(("exponential_z", "exponential_x", "linear_z", "linear_x", "curvature_z", "curvature_x"), keep):
+        setattr(descs[0], name, t.data_ptr())
+    table_sx = torch.from_numpy(np.frombuffer(bytes(descs), dtype=np.uint8).copy()).cuda()
+    scal = [tuple(zz + sbeta * (xx - zz) for zz, xx in pairs), (1.0, 1.0, 1.0)]
+    slots, data = [], []
+    for r, c in shapes:
+        n = r * c
+        z, x = U.weights(rng, n) * F(20.0), U.weights(rng, n) * F(20.0)   # magnitudes where exp() bends
+        g = U.gradients(rng, n)
+        mb = o.bf16_bits(U.weights(rng, n, 1e-3))
+        s = _slot(r, c, g, mb, z, x)
+        s.second_momentum = dev(np.full(max(r, c), 1e-2, F))
+        slots.append(s)
+        data.append((z, x, g, mb, (rng.standard_normal(n) * 0.05).astype(F)))
+    plan = b2.MuonPlan(shapes, scale_layout=b2.SCALES_RAW)
+    table = b2.slot_table(slots)
+    opt = _stage_u_inputs(plan, slots, shapes, [d[4] for d in data])
+    for s, d in zip(slots, data):       # the prepare call above moved the momentum: put it back
+        s.momentum.copy_(bf16_from_bits(d[3]).view_as(s.momentum))
+        s.grad.copy_(dev(d[2]).view_as(s.grad))
+    args = b2.MuonMegaUpdateArgs(mu=0.9, grad_scale=0.5, learning_rate=0.02, weight_decay=0.0 if entry == "hyperball" else 0.025,
+                                 average_coefficient=0.3, schedule_beta=sbeta, symexp_lin_beta=sym_beta,
+                                 symexp_lin_slots=table_sx)
+    if entry == "finish":
+        opt.muon_tma_finish_update_deferred_quantization(plan, table, args)
+    elif entry == "hyperball":
+        opt.muon_tma_finish_hyperball_update_deferred_quantization(plan, table, args, use_schedule_free=True)
+    else:
+        opt.muon_tma_sign_update_deferred_quantization(plan, table, args)
+    torch.cuda.synchronize()
+    for k, (s, (r, c)) in enumerate(zip(slots, shapes)):
+        z, x, g, mb, Um = data[k]
+        if entry == "finish":
+            z2, x2, y_raw, ax, _ = o.update(Um, z, x, r, c, 0.02, 0.025, 0.3, sbeta)
+        elif entry == "hyperball":
+            fa, st = host(plan.scratch(k, 8).view(torch.float32)), host(plan.scratch(k, 9).view(torch.float32))
+            z2, x2, y_raw, _, _, ax, _ = o.hyperball_update(Um, z, x, r, c, 0.02, 0.3, sbeta, True, fa, st)
+        else:
+            y_raw, _, _, z2, x2, ax, _ = o.sign_update(g, mb, None, z, x, r, c, 0.9, 0.5, False, 0.02, 0.025, 0.3, sbeta)
+        assert np.array_equal(host(s.z_master).ravel(), z2) and np.array_equal(host(s.x_master).ravel(), x2)
+        want = _symexp(y_raw, sym_beta, *scal[k])
+        got = host(s.grad).ravel().astype(np.float64)
+        assert np.max(np.abs(got - want)) <= 4e-6 * np.max(np.abs(want))
+        assert np.max(np.abs(want - y_raw)) > 0.05 * np.max(np.abs(y_raw))        # the transform did something
+        assert abs(host(s.schedule_amax)[0] - np.max(np.abs(want))) <= 4e-6 * np.max(np.abs(want))
+        assert host(plan.scratch(k, 3))[0] == ax
+    del keep
+    plan.close()
