@@ -339,6 +339,30 @@ int b2_muon_materialize_training_weights(b2_muon_plan *plan, const b2_muon_slot_
 /* `OptimizerModule::zero_f32_pointer_table` (.../launcher/adam.rs:30-43). */
 int b2_zero_f32_pointer_table(const uint64_t *d_pointers, uint32_t pointer_count, void *stream);
 
+/* ---- SymExpLin scale scalars ------------------------------------------------------------------ */
+/* `OptimizerModule::symexp_lin_zero_scale_grads` (.../launcher/symexp_lin.rs:9-22): clears the three
+ * scale gradients of every slot that has scale scalars. */
+int b2_symexp_lin_zero_scale_grads(const b2_symexp_lin_slot_descriptor *d_slots, uint32_t slot_count, void *stream);
+/* `OptimizerModule::symexp_lin_scale_adamw_update` (.../launcher/symexp_lin.rs:24-59): schedule-free
+ * AdamW on the exponential, linear (same learning rate, with weight decay) and curvature (own learning
+ * rate, no weight decay) scalars of every slot. */
+typedef struct b2_symexp_lin_adamw_args {
+    float grad_scale;
+    float exponential_linear_learning_rate;
+    float curvature_learning_rate;
+    float weight_decay;
+    float beta1, beta2;
+    float beta1_correction, beta2_correction;
+    float eps;
+    float average_coefficient;
+} b2_symexp_lin_adamw_args;
+int b2_symexp_lin_scale_adamw_update(const b2_symexp_lin_slot_descriptor *d_slots, uint32_t slot_count,
+                                     const b2_symexp_lin_adamw_args *args, void *stream);
+/* `OptimizerModule::symexp_lin_congruent_inverse_in_place` (.../launcher/symexp_lin.rs:61-75): replaces
+ * every value t by the r with (exp(beta r) - 1 + r) / beta = t (sign kept), ten Newton steps from
+ * log1p(beta |t|) / beta. */
+int b2_symexp_lin_congruent_inverse_in_place(float *d_raw, uint32_t len, float beta, void *stream);
+
 /* ---- global gradient-norm clip (the producer of grad_scale) --------------------------------- */
 /* `GradientClipArgs` (crates/cuda-kernels/src/gpt/optimizer/args/grad_clip.rs:3-15). */
 typedef struct b2_gradient_clip_args {

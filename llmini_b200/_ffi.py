@@ -53,6 +53,12 @@ class SymExpLinSlotDescriptor(C.Structure):
         "curvature_x", "curvature_grad", "curvature_first", "curvature_second")] + [("rows", C.c_uint32), ("cols", C.c_uint32)]
 
 
+class SymExpLinAdamWArgs(C.Structure):
+    _fields_ = [(n, C.c_float) for n in (
+        "grad_scale", "exponential_linear_learning_rate", "curvature_learning_rate", "weight_decay", "beta1", "beta2",
+        "beta1_correction", "beta2_correction", "eps", "average_coefficient")]
+
+
 class ScheduleFreeMaterializeArgs(C.Structure):
     _fields_ = [("bytes", C.c_void_p), ("scales", C.c_void_p), ("global_scale", C.c_void_p),
                 ("z_master", C.c_void_p), ("x_master", C.c_void_p), ("precomputed_values", C.c_void_p),
@@ -112,6 +118,9 @@ def _declare(L: C.CDLL) -> None:
         "b2_muon_sign_update_deferred_quantization": (i, [vp, vp, C.POINTER(MuonStepArgs), vp]),
         "b2_nvfp4_sm100_scales_bytes": (C.c_size_t, [C.c_uint32, C.c_uint32]),
         "b2_nvfp4_scales_to_sm100": (i, [vp, C.c_uint32, C.c_uint32, C.c_uint32, vp, vp]),
+        "b2_symexp_lin_zero_scale_grads": (i, [vp, C.c_uint32, vp]),
+        "b2_symexp_lin_scale_adamw_update": (i, [vp, C.c_uint32, C.POINTER(SymExpLinAdamWArgs), vp]),
+        "b2_symexp_lin_congruent_inverse_in_place": (i, [vp, C.c_uint32, C.c_float, vp]),
         "b2_muon_plan_scratch": (i, [vp, u32, u32, C.POINTER(vp), C.POINTER(sz)]),
         "b2_muon_plan_status": (i, [vp, vp]),
         "b2_muon_plan_flops_per_iteration": (C.c_double, [vp]),

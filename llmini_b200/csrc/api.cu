@@ -838,6 +838,28 @@ int b2_muon_materialize_training_weights(b2_muon_plan *plan, const b2_muon_slot_
     return (int)launch_muon_encode(v, plan->at<float>(plan->layout.off_amax_x), 1, (int)plan->options.scale_layout,
                                    as_stream(stream));
 }
+int b2_symexp_lin_zero_scale_grads(const b2_symexp_lin_slot_descriptor *d_slots, uint32_t slot_count, void *stream) {
+    if (!d_slots && slot_count) return B2_ERROR_INVALID_VALUE;
+    DeviceInfo d;
+    cudaError_t e = device_info(d);
+    if (e != cudaSuccess) return (int)e;
+    return (int)launch_symexp_zero_scale_grads(d_slots, slot_count, as_stream(stream));
+}
+int b2_symexp_lin_scale_adamw_update(const b2_symexp_lin_slot_descriptor *d_slots, uint32_t slot_count,
+                                     const b2_symexp_lin_adamw_args *args, void *stream) {
+    if (!args || (!d_slots && slot_count)) return B2_ERROR_INVALID_VALUE;
+    DeviceInfo d;
+    cudaError_t e = device_info(d);
+    if (e != cudaSuccess) return (int)e;
+    return (int)launch_symexp_scale_adamw(d_slots, slot_count, *args, as_stream(stream));
+}
+int b2_symexp_lin_congruent_inverse_in_place(float *d_raw, uint32_t len, float beta, void *stream) {
+    if ((!d_raw && len) || !(beta > 0.0f) || !std::isfinite(beta)) return B2_ERROR_INVALID_VALUE;  // symexp_lin.rs:67
+    DeviceInfo d;
+    cudaError_t e = device_info(d);
+    if (e != cudaSuccess) return (int)e;
+    return (int)launch_symexp_congruent_inverse(d_raw, len, beta, as_stream(stream));
+}
 int b2_clip_gradients(const b2_gradient_clip_args *a, void *stream) {
     if (!a || !a->scale || !a->norm) return B2_ERROR_INVALID_VALUE;
     if (a->chunk_count && (!a->chunk_ptrs || !a->chunk_lens || !a->chunk_sums)) return B2_ERROR_INVALID_VALUE;

@@ -156,6 +156,16 @@ __device__ __forceinline__ float exp_approx(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x * 1.4426950408889634f));
     return r;
 }
+// ln_f32 / log1p_f32 of the reference (float_ptx.rs:53-57, 103-108)
+__device__ __forceinline__ float ln_approx(float x) {
+    float r;
+    asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r * 0.6931471805599453f;
+}
+__device__ __forceinline__ float log1p_compensated(float x) {
+    const float u = 1.0f + x;
+    return u == 1.0f ? x : ln_approx(u) * (x / (u - 1.0f));
+}
 __device__ __forceinline__ float symexp_forward(float raw, const SymExpLin &s) {
     if (s.beta <= 0.0f) return raw;
     const float sign = raw > 0.0f ? 1.0f : (raw < 0.0f ? -1.0f : 0.0f);

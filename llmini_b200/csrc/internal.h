@@ -91,6 +91,10 @@ cudaError_t launch_adamw_multi(const b2_adamw_slot_descriptor *table, uint32_t c
 cudaError_t launch_grad_clip(const b2_gradient_clip_args &a, int grid_cap, cudaStream_t s);
 cudaError_t launch_scales_to_sm100(const uint8_t *src, int src_csf, uint32_t rows, uint32_t cols, uint8_t *out,
                                    int grid_cap, cudaStream_t s);
+cudaError_t launch_symexp_scale_adamw(const b2_symexp_lin_slot_descriptor *slots, uint32_t n,
+                                      const b2_symexp_lin_adamw_args &a, cudaStream_t s);
+cudaError_t launch_symexp_zero_scale_grads(const b2_symexp_lin_slot_descriptor *slots, uint32_t n, cudaStream_t s);
+cudaError_t launch_symexp_congruent_inverse(float *raw, uint32_t len, float beta, cudaStream_t s);
 cudaError_t launch_zero_pointer_table(const uint64_t *ptrs, uint32_t n, cudaStream_t s);
 cudaError_t launch_layout_echo(uint32_t *out, cudaStream_t s);
 cudaError_t launch_debug_rcp(const float *in, float *out, uint32_t n, cudaStream_t s);

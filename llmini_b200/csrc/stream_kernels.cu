@@ -1396,6 +1396,78 @@ cudaError_t launch_muon_update(const SlotView &v, const uint64_t *u_ptrs, float 
             v.slots, v.chunk_prefix, v.slot_count, v.total_chunks, u_ptrs, amax_x, up);
     return cudaGetLastError();
 }
+// ---- SymExpLin scale scalars (crates/cuda-kernels/src/gpt/optimizer/symexp_lin.rs:98-283) -----
+__device__ __forceinline__ void scalar_adamw(uint64_t z_p, uint64_t x_p, uint64_t g_p, uint64_t m1_p, uint64_t m2_p,
+                                             const b2_symexp_lin_adamw_args &a, float lr, float wd) {
+    float *z = reinterpret_cast<float *>(z_p), *x = reinterpret_cast<float *>(x_p);
+    float *m1 = reinterpret_cast<float *>(m1_p), *m2 = reinterpret_cast<float *>(m2_p);
+    const float g = *reinterpret_cast<const float *>(g_p) * a.grad_scale;
+    const float m = a.beta1 * *m1 + (1.0f - a.beta1) * g;
+    const float v = a.beta2 * *m2 + (1.0f - a.beta2) * g * g;
+    const float update = (m / a.beta1_correction) / (sqrtf(v / a.beta2_correction) + a.eps);
+    const float decay = 1.0f - lr * wd;
+    const float next = *z * decay - lr * update;
+    const float xv = *x;
+    *m1 = m;
+    *m2 = v;
+    *z = next;
+    *x = xv + a.average_coefficient * (next - xv);
+}
+__global__ void k_symexp_scale_adamw(const b2_symexp_lin_slot_descriptor *slots, uint32_t slot_count,
+                                     b2_symexp_lin_adamw_args a) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= slot_count) return;
+    const b2_symexp_lin_slot_descriptor d = slots[i];
+    if (d.exponential_z == 0) return;
+    scalar_adamw(d.exponential_z, d.exponential_x, d.exponential_grad, d.exponential_first, d.exponential_second, a,
+                 a.exponential_linear_learning_rate, a.weight_decay);
+    scalar_adamw(d.linear_z, d.linear_x, d.linear_grad, d.linear_first, d.linear_second, a,
+                 a.exponential_linear_learning_rate, a.weight_decay);
+    scalar_adamw(d.curvature_z, d.curvature_x, d.curvature_grad, d.curvature_first, d.curvature_second, a,
+                 a.curvature_learning_rate, 0.0f);
+}
+__global__ void k_symexp_zero_scale_grads(const b2_symexp_lin_slot_descriptor *slots, uint32_t slot_count) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= slot_count) return;
+    const b2_symexp_lin_slot_descriptor d = slots[i];
+    if (d.exponential_grad == 0) return;
+    *reinterpret_cast<float *>(d.exponential_grad) = 0.0f;
+    *reinterpret_cast<float *>(d.linear_grad) = 0.0f;
+    *reinterpret_cast<float *>(d.curvature_grad) = 0.0f;
+}
+__global__ void k_symexp_congruent_inverse(float *raw, uint32_t len, float beta) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= len) return;
+    const float target = raw[i];
+    if (beta <= 0.0f || target == 0.0f) return;
+    const float sign = target > 0.0f ? 1.0f : -1.0f;
+    const float t = fabsf(target), inv_beta = 1.0f / beta;
+    float mag = log1p_compensated(beta * t) * inv_beta;   // a tight upper bound to start from
+    for (int it = 0; it < 10; ++it) {
+        const float ex = exp_approx(beta * mag);
+        const float residual = (ex - 1.0f + mag) * inv_beta - t;
+        mag -= residual / (ex + inv_beta);
+        if (mag < 0.0f) mag = 0.0f;
+    }
+    raw[i] = sign * mag;
+}
+cudaError_t launch_symexp_scale_adamw(const b2_symexp_lin_slot_descriptor *slots, uint32_t n,
+                                      const b2_symexp_lin_adamw_args &a, cudaStream_t s) {
+    if (n == 0) return cudaSuccess;
+    k_symexp_scale_adamw<<<(n + 255) / 256, 256, 0, s>>>(slots, n, a);
+    return cudaGetLastError();
+}
+cudaError_t launch_symexp_zero_scale_grads(const b2_symexp_lin_slot_descriptor *slots, uint32_t n, cudaStream_t s) {
+    if (n == 0) return cudaSuccess;
+    k_symexp_zero_scale_grads<<<(n + 255) / 256, 256, 0, s>>>(slots, n);
+    return cudaGetLastError();
+}
+cudaError_t launch_symexp_congruent_inverse(float *raw, uint32_t len, float beta, cudaStream_t s) {
+    if (len == 0) return cudaSuccess;
+    k_symexp_congruent_inverse<<<(len + 255) / 256, 256, 0, s>>>(raw, len, beta);
+    return cudaGetLastError();
+}
+
 // Raw plane or CSF storage -> sm_100 block-scale operand layout; one thread per destination byte,
 // so the padding of the last row band and scale-column group is written (as zero) too.
 __global__ void __launch_bounds__(kThreads)

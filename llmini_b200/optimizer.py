@@ -340,6 +340,23 @@ class OptimizerModule:
                    chunk_count, extra_sum_count, max_norm, int(bool(apply)))
         check(self._lib.b2_clip_gradients(C.byref(a), _stream()), "clip_gradients")
 
+    # launcher/symexp_lin.rs:9-75
+    def symexp_lin_zero_scale_grads(self, slots: torch.Tensor, slot_count: int) -> None:
+        check(self._lib.b2_symexp_lin_zero_scale_grads(_ptr(slots), slot_count, _stream()), "symexp_lin_zero_scale_grads")
+
+    def symexp_lin_scale_adamw_update(self, slots: torch.Tensor, slot_count: int, grad_scale: float,
+                                      exponential_linear_learning_rate: float, curvature_learning_rate: float,
+                                      weight_decay: float, beta1: float, beta2: float, beta1_correction: float,
+                                      beta2_correction: float, eps: float, average_coefficient: float) -> None:
+        a = _ffi.SymExpLinAdamWArgs(grad_scale, exponential_linear_learning_rate, curvature_learning_rate, weight_decay,
+                                    beta1, beta2, beta1_correction, beta2_correction, eps, average_coefficient)
+        check(self._lib.b2_symexp_lin_scale_adamw_update(_ptr(slots), slot_count, C.byref(a), _stream()),
+              "symexp_lin_scale_adamw_update")
+
+    def symexp_lin_congruent_inverse_in_place(self, raw: torch.Tensor, beta: float) -> None:
+        check(self._lib.b2_symexp_lin_congruent_inverse_in_place(_ptr(raw), raw.numel(), beta, _stream()),
+              "symexp_lin_congruent_inverse_in_place")
+
     # launcher/adam.rs:30-43
     def zero_f32_pointer_table(self, pointers: torch.Tensor, pointer_count: int) -> None:
         check(self._lib.b2_zero_f32_pointer_table(_ptr(pointers), pointer_count, _stream()), "zero_f32_pointer_table")

@@ -423,3 +423,39 @@ def test_symexp_lin_forward_in_the_update_kernels(entry):
         assert host(plan.scratch(k, 3))[0] == ax
     del keep
     plan.close()
+
+
+def test_symexp_lin_scalar_adam_reference_case():
+    # crates/cuda-kernels/tests/optimizer/adam.rs:165-213 (symexp_lin_batched_scalar_adam_matches_independent_updates)
+    from llmini_b200 import _ffi
+    one = lambda v: torch.full((1,), float(v), device="cuda")
+    fix = {name: dict(z=one(1.0), x=one(1.0), grad=one(g), first=one(0.0), second=one(0.0))
+           for name, g in (("exponential", 0.5), ("linear", -0.25), ("curvature", 0.75))}
+    descs = (_ffi.SymExpLinSlotDescriptor * 2)()      # entry 1 has no scale scalars and must be skipped
+    for name, f in fix.items():
+        for field, key in (("z", "z"), ("x", "x"), ("grad", "grad"), ("first", "first"), ("second", "second")):
+            setattr(descs[0], f"{name}_{field}", f[key].data_ptr())
+    table = torch.from_numpy(np.frombuffer(bytes(descs), dtype=np.uint8).copy()).cuda()
+    opt = b2.OptimizerModule()
+    opt.symexp_lin_scale_adamw_update(table, 2, 0.5, 0.25, 0.1, 0.1, 0.9, 0.95, 0.1, 0.05, 1.0e-10, 0.25)
+    torch.cuda.synchronize()
+    for name, z, x in (("exponential", 0.725, 0.93125), ("linear", 1.225, 1.05625), ("curvature", 0.9, 0.975)):
+        assert abs(host(fix[name]["z"])[0] - z) <= 1e-6 and abs(host(fix[name]["x"])[0] - x) <= 1e-6
+    opt.symexp_lin_zero_scale_grads(table, 2)
+    torch.cuda.synchronize()
+    assert all(host(f["grad"])[0] == 0.0 for f in fix.values())
+
+
+def test_symexp_lin_congruent_inverse_inverts_the_unit_forward():
+    # r -> t = sign(r) ((exp(beta |r|) - 1) + |r|) / beta is what the inverse undoes (symexp_lin.rs:60-84)
+    beta = 12.5
+    r = np.concatenate([np.linspace(-0.4, 0.4, 4001), [0.0, 1e-7, -3e-4]]).astype(F)
+    t = (np.sign(r) * ((np.exp(beta * np.abs(r.astype(np.float64))) - 1.0) + np.abs(r)) / beta).astype(F)
+    buf = dev(t)
+    b2.OptimizerModule().symexp_lin_congruent_inverse_in_place(buf, beta)
+    torch.cuda.synchronize()
+    got = host(buf)
+    assert np.max(np.abs(got - r)) <= 2e-6 + 2e-5 * np.max(np.abs(r))
+    assert got[4001] == 0.0
+    with pytest.raises(b2.B2Error):
+        b2.OptimizerModule().symexp_lin_congruent_inverse_in_place(buf, 0.0)

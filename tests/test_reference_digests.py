@@ -72,3 +72,41 @@ def test_gpu_schedule_free_materialisation_with_symexp_lin_reproduces_the_refere
     stored = host(t.scales)
     raw = np.array([b2.csf_scale_at(stored, g) for g in range(LEN // 16)], np.uint8)
     assert fnv1a(host(t.bytes).tobytes(), raw.tobytes(), host(t.global_scale).tobytes()) == SCHEDULED_DIGEST
+
+
+# Digests of the reference's row-wise quantiser (csf_quantization.rs:574-655): the same four-six
+# arithmetic with every row as its own tensor (tensor scale = row amax / 1536, zero rows included),
+# FNV-1a over all packed bytes, then each row's block-scale bytes, then the row scales.
+ROWWISE = [(1, 16, 0x7AE32C9F6169785E), (3, 80, 0xF787EA4CA1E768FC), (3, 128, 0xBA595E1D681332C4),
+           (129, 256, 0x484EB3D70045C086), (17, 2048, 0xABE7DBF7EA809134), (17, 8192, 0x65FA8FFA758B9DC1)]
+
+
+def rowwise_input(rows, cols):
+    i = np.arange(rows * cols)
+    return np.where((i // cols) % 17 == 0, F(0.0), (((i * 17 + 13) % 251).astype(F) - F(125.0)) * F(0.003)).astype(F)
+
+
+@pytest.mark.parametrize("rows,cols,digest", ROWWISE)
+def test_oracle_reproduces_the_rowwise_digests(rows, cols, digest):
+    x = rowwise_input(rows, cols).reshape(rows, cols)
+    out = [o.nvfp4_quantize(row, amax=np.max(np.abs(row))) for row in x]
+    assert fnv1a(*[c.tobytes() for c, _, _, _ in out], *[s.tobytes() for _, s, _, _ in out],
+                 *[F(gs).tobytes() for _, _, gs, _ in out]) == digest
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows,cols,digest", ROWWISE)
+def test_gpu_quantiser_reproduces_the_rowwise_digests(rows, cols, digest):
+    import torch
+    from tests.gpu_util import dev, host
+    x = rowwise_input(rows, cols).reshape(rows, cols)
+    q = b2.Nvfp4QuantModule()
+    xd = dev(x)
+    codes = torch.zeros(rows, cols // 2, dtype=torch.uint8, device="cuda")
+    scales = torch.zeros(rows, cols // 16, dtype=torch.uint8, device="cuda")
+    gs = torch.zeros(rows, device="cuda")
+    amax = xd.abs().amax(dim=1).contiguous()
+    for r in range(rows):   # every row through the tensor quantiser with the row's own maximum
+        q.fp32_to_nvfp4_four_six(xd[r], amax[r:r + 1], codes[r], scales[r], gs[r:r + 1], cols // 16, b2.SCALES_RAW)
+    torch.cuda.synchronize()
+    assert fnv1a(host(codes).tobytes(), host(scales).tobytes(), host(gs).tobytes()) == digest
