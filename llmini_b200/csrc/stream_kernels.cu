@@ -247,10 +247,10 @@ __device__ __forceinline__ void neuron_factors(const ChunkCtx &cx, const UpdateP
 
 // Stage U: crates/cuda-kernels/src/gpt/optimizer/muon/fused/update/one.rs:46-85, scale from
 // .../fused/update.rs:54, per-slot learning rate from .../fused/mega/slot.rs:26-29.
-// U is in the storage layout, so every access is a coalesced 128-bit one.
-// update_chunk: one 2048-value chunk, including the CTA's contribution to both maxima.
-// EXT = 1: NorMuon factors and / or qk-clip are in play.  keep_y: y is the tensor that gets
-// quantised next, so y stays cacheable and x' is streamed; otherwise the other way round.
+// U is in the storage layout, so every access is a coalesced 128-bit one.  One call handles one
+// 2048-value chunk, including the CTA's contribution to both maxima.  EXT = 1: NorMuon factors,
+// qk-clip or the SymExpLin transform are in play.  keep_y: y is the tensor that gets quantised
+// next, so y stays cacheable and x' is streamed; otherwise the other way round.
 template <int EXT>
 __device__ __forceinline__ void update_chunk(const ChunkCtx &cx, const uint64_t *u_ptrs, float *amax_x,
                                              const UpdateParams &up, bool keep_y, float *warp_ax, float *warp_ay) {
