@@ -605,6 +605,20 @@ def run_extras(args):
         ("scales_to_sm100 (raw plane, all matrices as one [n/768, 768] tensor)", 2.0 / 16.0,
          lambda: b2.scales_to_sm100(raw_scales, b2.SCALES_RAW, n_el // 768, 768)),
     ]
+    co5 = np.tile(np.asarray([3.4445, -4.7750, 2.0315], np.float32), (5, 1))
+
+    def production_step():
+        # the reference trainer's order for a Muon group (src/training/optimizer_muon/tma.rs:38-201): prepare,
+        # five Newton-Schulz iterations, finish with NorMuon + qk-clip and deferred quantisation, then the
+        # cached training weights y are materialised as NVFP4
+        a = A(normuon=True, qk_clip_factors=factors, coefficients=co5, **base)
+        opt.muon_tma_prepare_polar(plan, table, a)
+        opt.muon_polar(plan, a)
+        opt.muon_tma_finish_update_deferred_quantization(plan, table, a)
+        opt.muon_materialize_training_weights(plan, table)
+
+    cases.append(("production-order step: prepare + 5x NS + finish (NorMuon, qk-clip, deferred) + materialise y", 0.0,
+                  production_step))
     for name, bpe, fn in cases:
         for _ in range(3):
             fn()
