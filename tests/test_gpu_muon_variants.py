@@ -459,3 +459,29 @@ def test_symexp_lin_congruent_inverse_inverts_the_unit_forward():
     assert got[4001] == 0.0
     with pytest.raises(b2.B2Error):
         b2.OptimizerModule().symexp_lin_congruent_inverse_in_place(buf, 0.0)
+
+
+def test_normuon_without_state_buffer_is_the_plain_update():
+    # a slot whose `second_momentum` is NULL keeps factor 1 and scale 1: bit-identical to the plain finish
+    rng = np.random.default_rng(53)
+    shapes = [(96, 64), (64, 128)]
+    outs = []
+    for normuon in (False, True):
+        rng2 = np.random.default_rng(59)
+        slots = []
+        for r, c in shapes:
+            n = r * c
+            slots.append(_slot(r, c, np.zeros(n, F), np.zeros(n, np.uint16), U.weights(rng2, n), U.weights(rng2, n)))
+        plan = b2.MuonPlan(shapes, scale_layout=b2.SCALES_RAW)
+        opt = _stage_u_inputs(plan, slots, shapes, [(rng2.standard_normal(r * c) * 0.05).astype(F) for r, c in shapes])
+        opt.muon_tma_finish_update(plan, b2.slot_table(slots),
+                                   b2.MuonMegaUpdateArgs(learning_rate=0.02, average_coefficient=0.3, schedule_beta=0.6,
+                                                         normuon=normuon))
+        torch.cuda.synchronize()
+        assert plan.status() == 0
+        outs.append([[host(t).copy() for t in (s.z_master, s.x_master, s.grad, s.bytes, s.scales, s.global_scale)]
+                     for s in slots])
+        plan.close()
+    for a, b in zip(*outs):
+        for u, v in zip(a, b):
+            assert np.array_equal(u, v)
