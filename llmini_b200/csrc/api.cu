@@ -112,7 +112,7 @@ struct SlotLayout {
 struct Layout {
     std::vector<SlotLayout> slots;
     std::vector<uint32_t> chunk_prefix;  // slot_count + 1
-    std::vector<uint32_t> unit_prefix;   // slot_count + 1: NorMuon work units (8 rows or 128 columns)
+    std::vector<uint32_t> unit_prefix;   // slot_count + 1: NorMuon work units (32 rows or 128 columns)
     std::vector<uint32_t> items;         // work list of the fused update + encode launch
     uint32_t total_chunks = 0;
     int bn = 256;
@@ -185,7 +185,7 @@ bool build_layout(const uint32_t *rows, const uint32_t *cols, uint32_t count, co
     L.unit_prefix.assign(count + 1, 0);
     for (uint32_t s = 0; s < count; ++s) {
         uint32_t units = 0;
-        if ((uint64_t)rows[s] * cols[s] != 0) units = rows[s] >= cols[s] ? (rows[s] + 7) / 8 : (cols[s] + 127) / 128;
+        if ((uint64_t)rows[s] * cols[s] != 0) units = rows[s] >= cols[s] ? (rows[s] + B2_NORMUON_ROWS_PER_UNIT - 1) / B2_NORMUON_ROWS_PER_UNIT : (cols[s] + 127) / 128;
         L.unit_prefix[s + 1] = L.unit_prefix[s] + units;
     }
     // ---- metadata region (uploaded at plan creation) ----

@@ -24,7 +24,8 @@ struct MomentumParams {
     int nesterov, variance_adaptive;
     float bias_correction_inv;
 };
-// NorMuon / Hyperball scratch of a plan: work units are 8 rows (slots with rows >= cols) or 128
+#define B2_NORMUON_ROWS_PER_UNIT 32
+// NorMuon / Hyperball scratch of a plan: work units are B2_NORMUON_ROWS_PER_UNIT rows (slots with rows >= cols) or 128
 // columns (rows < cols) of one slot; `unit_prefix` counts them like `chunk_prefix` counts chunks.
 struct NeuronView {
     const uint32_t *unit_prefix;   // device, slot_count + 1 entries

@@ -392,11 +392,20 @@ k_normuon_stats(const b2_muon_slot_descriptor *slots, uint32_t slot_count, Neuro
         float *factors = reinterpret_cast<float *>(nv.factor_ptrs[slot]);
         double s_raw = 0.0, s_scaled = 0.0, s_param = 0.0, s_dot = 0.0;  // meaningful on one thread per neuron
         if (!COLS) {
-            const uint32_t row = local * (kThreads / 32) + warp;
-            if (row < d.rows) {
+            // B2_NORMUON_ROWS_PER_UNIT rows per unit, kRowsPerWarp per warp, one after the other: the
+            // unit's fixed cost (slot lookup, descriptor, block reduction) is paid once for all of them
+            constexpr uint32_t kRowsPerWarp = B2_NORMUON_ROWS_PER_UNIT / (kThreads / 32);
+            const uint32_t row0 = local * B2_NORMUON_ROWS_PER_UNIT + warp * kRowsPerWarp;
+            // the old second moments are needed last: ask for them first
+            float old_state[kRowsPerWarp];
+#pragma unroll
+            for (uint32_t j = 0; j < kRowsPerWarp; ++j)
+                old_state[j] = (lane == 0 && state && row0 + j < d.rows) ? __ldcg(state + row0 + j) : 0.0f;
+#pragma unroll
+            for (uint32_t j = 0; j < kRowsPerWarp; ++j) {
+                const uint32_t row = row0 + j;
+                if (row >= d.rows) break;   // warp-uniform
                 float raw = 0.0f, param = 0.0f, dot = 0.0f;
-                // the old second moment is needed last: ask for it first
-                const float old_state = (lane == 0 && state) ? __ldcg(state + row) : 0.0f;
                 const size_t base = (size_t)row * d.cols;
 #pragma unroll 4
                 for (uint32_t c = lane * 4; c < d.cols; c += 128) {
@@ -416,13 +425,13 @@ k_normuon_stats(const b2_muon_slot_descriptor *slots, uint32_t slot_count, Neuro
                     float factor = 1.0f;
                     if (state) {
                         const float mean = (float)r / (float)d.cols;
-                        const float next = 0.95f * old_state + (1.0f - 0.95f) * mean;
+                        const float next = 0.95f * old_state[j] + (1.0f - 0.95f) * mean;
                         factor = 1.0f / sqrtf(fmaxf(next, 1.0e-10f));
                         state[row] = next;
                     }
                     factors[row] = factor;
-                    s_raw = r; s_scaled = (double)((float)r * factor * factor);
-                    s_param = pp; s_dot = (double)((float)dd * factor);
+                    s_raw += r; s_scaled += (double)((float)r * factor * factor);
+                    s_param += pp; s_dot += (double)((float)dd * factor);
                 }
             }
         } else {
