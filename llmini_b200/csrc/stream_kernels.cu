@@ -106,41 +106,60 @@ __device__ __forceinline__ ChunkCtx chunk_ctx(const b2_muon_slot_descriptor *slo
 // then f64 across threads, warps and chunks, so the grid shape does not change the result.  Also clears the two amax
 // words the update kernel later raises with atomicMax.
 template <int VS>
-__global__ void __launch_bounds__(kThreads, VS ? 4 : 8)
+__global__ void __launch_bounds__(kThreads, VS ? 4 : 6)
 k_muon_sumsq(const b2_muon_slot_descriptor *slots, const uint32_t *prefix, uint32_t slot_count,
              uint32_t total_chunks, MomentumParams mp, double *partials, float *amax_x) {
-    __shared__ double warp_part[kThreads / 32];
+    // Two chunks per trip: both chunks' loads are in flight together and one pair of barriers
+    // serves both block reductions.  Every chunk still leaves its own partial, summed in the same
+    // order as before, so the result does not depend on the pairing.
+    __shared__ double warp_part[2][kThreads / 32];
     const int tid = threadIdx.x;
     if (mp.d_grad_scale) mp.grad_scale = __ldg(mp.d_grad_scale);
-    for (uint32_t c = blockIdx.x; c < total_chunks; c += gridDim.x) {
-        ChunkCtx cx = chunk_ctx(slots, prefix, slot_count, c);
-        const float *grad = reinterpret_cast<const float *>(cx.d.grad);
-        const uint16_t *mom = reinterpret_cast<const uint16_t *>(cx.d.momentum);
-        const uint16_t *var = reinterpret_cast<const uint16_t *>(cx.d.variance);
-        const uint32_t base = cx.local_chunk * kChunk;
-        float local = 0.0f;
+    for (uint32_t c0 = 2 * blockIdx.x; c0 < total_chunks; c0 += 2 * gridDim.x) {
+        float local[2] = {0.0f, 0.0f};
+        uint32_t reset_slot[2] = {0xffffffffu, 0xffffffffu};
+        uint64_t reset_amax[2] = {0, 0};
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            uint32_t i = base + h * (kChunk / 2) + tid * 4;
-            if (i < cx.len) {
-                const Quad q = momentum_quad<VS>(grad, mom, var, i, mp, false);
-                // per-thread chain as in the reference (momentum.rs:63: fma(update, update, sum));
-                // eight terms at most, so the chain's rounding stays below 1e-7 relative
+        for (int k = 0; k < 2; ++k) {
+            const uint32_t c = c0 + k;
+            if (c >= total_chunks) break;   // CTA-uniform
+            ChunkCtx cx = chunk_ctx(slots, prefix, slot_count, c);
+            const float *grad = reinterpret_cast<const float *>(cx.d.grad);
+            const uint16_t *mom = reinterpret_cast<const uint16_t *>(cx.d.momentum);
+            const uint16_t *var = reinterpret_cast<const uint16_t *>(cx.d.variance);
+            const uint32_t base = cx.local_chunk * kChunk;
+            if (cx.local_chunk == 0) {
+                reset_slot[k] = cx.slot;
+                reset_amax[k] = cx.d.schedule_amax;
+            }
 #pragma unroll
-                for (int e = 0; e < 4; ++e) local = fmaf(q.u[e], q.u[e], local);
+            for (int h = 0; h < 2; ++h) {
+                uint32_t i = base + h * (kChunk / 2) + tid * 4;
+                if (i < cx.len) {
+                    const Quad q = momentum_quad<VS>(grad, mom, var, i, mp, false);
+                    // per-thread chain as in the reference (momentum.rs:63: fma(update, update, sum));
+                    // eight terms at most, so the chain's rounding stays below 1e-7 relative
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) local[k] = fmaf(q.u[e], q.u[e], local[k]);
+                }
             }
         }
-        double acc = warp_sum((double)local);
-        if ((tid & 31) == 0) warp_part[tid >> 5] = acc;
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const double acc = warp_sum((double)local[k]);
+            if ((tid & 31) == 0) warp_part[k][tid >> 5] = acc;
+        }
         __syncthreads();
-        if (tid == 0) {
+        if (tid < 2 && c0 + tid < total_chunks) {
             double s = 0.0;
 #pragma unroll
-            for (int w = 0; w < kThreads / 32; ++w) s += warp_part[w];
-            partials[c] = s;
-            if (cx.local_chunk == 0) {
-                amax_x[cx.slot] = 0.0f;
-                *reinterpret_cast<float *>(cx.d.schedule_amax) = 0.0f;
+            for (int w = 0; w < kThreads / 32; ++w) s += warp_part[tid][w];
+            partials[c0 + tid] = s;
+            const uint32_t rs = tid == 0 ? reset_slot[0] : reset_slot[1];
+            const uint64_t ra = tid == 0 ? reset_amax[0] : reset_amax[1];
+            if (rs != 0xffffffffu) {
+                amax_x[rs] = 0.0f;
+                *reinterpret_cast<float *>(ra) = 0.0f;
             }
         }
         __syncthreads();
@@ -1370,10 +1389,10 @@ cudaError_t launch_muon_sumsq(const SlotView &v, const MomentumParams &mp, doubl
                               cudaStream_t s) {
     if (v.total_chunks == 0) return cudaSuccess;
     if (mp.variance_adaptive)
-        k_muon_sumsq<1><<<clamp_grid(v.total_chunks, v.grid), kThreads, 0, s>>>(
+        k_muon_sumsq<1><<<clamp_grid((v.total_chunks + 1) / 2, v.grid), kThreads, 0, s>>>(
             v.slots, v.chunk_prefix, v.slot_count, v.total_chunks, mp, partials, amax_x);
     else
-        k_muon_sumsq<0><<<clamp_grid(v.total_chunks, v.grid), kThreads, 0, s>>>(
+        k_muon_sumsq<0><<<clamp_grid((v.total_chunks + 1) / 2, v.grid), kThreads, 0, s>>>(
             v.slots, v.chunk_prefix, v.slot_count, v.total_chunks, mp, partials, amax_x);
     return cudaGetLastError();
 }
