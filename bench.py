@@ -390,6 +390,11 @@ def run_gpu(args):
     def step_e2e():
         for gd, gh in zip(grad_dev[:n_slots], grad_host[:n_slots]):
             gd.copy_(gh, non_blocking=True)
+        matrices_up = torch.cuda.Event()
+        matrices_up.record(stream)
+        # the AdamW gradients go second: sharing the link with the matrix gradients would only delay the
+        # Muon stages, which are what hides this upload
+        up_stream.wait_event(matrices_up)
         up_stream.wait_event(adam_done)          # the previous step's AdamW has consumed its gradients
         with torch.cuda.stream(up_stream):
             for gd, gh in zip(grad_dev[n_slots:], grad_host[n_slots:]):
