@@ -285,12 +285,17 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
                 const int m0 = tl.tile_m * C::kTileM + (int)rank * 128;
                 const int n0 = tl.tile_n * BN + (PAIR ? (int)rank * 128 : 0);
                 const int num_kb = (int)((K + kGemmBlockK - 1) / kGemmBlockK);
+                // A diagonal tile of X X^T or G G: this CTA's 128 rows of B are its 128 rows of A, in
+                // the same shared-memory layout.  They are loaded once and the MMA reads them twice.
+                const bool shared_operand = PAIR && tl.tile_m == tl.tile_n && map_a == map_b && a_mn == b_mn;
+                const uint32_t stage_tx = shared_operand ? 2u * (uint32_t)kABytes
+                                                         : (uint32_t)C::kStageBytes * (PAIR ? 2u : 1u);
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
                     // PAIR: both CTAs' copies complete on the leader's barrier, which expects
                     // the bytes of both
                     const uint32_t fb = PAIR ? map_to_cta(full_bar(stage), 0) : full_bar(stage);
-                    if (!PAIR || rank == 0) mbar_expect_tx(full_bar(stage), (uint32_t)C::kStageBytes * (PAIR ? 2u : 1u));
+                    if (!PAIR || rank == 0) mbar_expect_tx(full_bar(stage), stage_tx);
                     const uint32_t sa = smem_u32(stage_base + stage * C::kStageBytes);
                     const uint32_t sb = sa + kABytes;
                     const int k0 = kb * kGemmBlockK;
@@ -302,6 +307,7 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
                     }
 #pragma unroll
                     for (int j = 0; j < C::kBRows / 128; ++j) {
+                        if (shared_operand) break;
                         if (b_mn) {
                             tma_load_2d<PAIR>(sb + (2 * j) * kBoxBytes, map_b, fb, n0 + 128 * j, k0);
                             tma_load_2d<PAIR>(sb + (2 * j + 1) * kBoxBytes, map_b, fb, n0 + 128 * j + 64, k0);
@@ -324,6 +330,7 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
                 const uint32_t a_mn = p->a_mn_major, b_mn = p->b_mn_major, K = p->K;
                 const int num_kb = (int)((K + kGemmBlockK - 1) / kGemmBlockK);
                 const uint32_t idesc = instr_desc(C::kTileM, BN, f16, a_mn, b_mn);
+                const bool shared_operand = PAIR && tl.tile_m == tl.tile_n && p->map_a == p->map_b && a_mn == b_mn;
                 if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
@@ -331,7 +338,7 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
                     if (!mbar_wait(full_bar(stage), phase, abort_flag)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t sa = smem_u32(stage_base + stage * C::kStageBytes);
-                    const uint32_t sb = sa + kABytes;
+                    const uint32_t sb = shared_operand ? sa : sa + kABytes;
 #pragma unroll
                     for (int k = 0; k < kGemmBlockK / 16; ++k) {
                         const uint64_t ad = a_mn ? smem_desc(sa + k * 2048, kBoxBytes, 1024)
