@@ -33,8 +33,6 @@ namespace b2 {
 
 namespace {
 
-constexpr int kEpiWarps = 8;
-constexpr int kGemmThreads = 32 * (2 + kEpiWarps);  // warp 0: TMA producer, warp 1: MMA issuer, rest: epilogue
 constexpr int kBoxBytes = 64 * 128;          // 64 rows x 128 bytes
 constexpr int kABytes = 2 * kBoxBytes;       // 128 x 64 16-bit operand tile
 constexpr int kSlabBytes = 32 * 128;         // per-warp store staging: 32 rows x 128 bytes
@@ -50,6 +48,10 @@ struct Cfg {
     static constexpr int kBRows = PAIR ? 128 : BN;   // rows of B this CTA stages per k-block
     static constexpr int kBBytes = (kBRows / 64) * kBoxBytes;
     static constexpr int kStageBytes = kABytes + kBBytes;
+    // warp 0: TMA producer, warp 1: MMA issuer, then four epilogue warps (one per TMEM lane
+    // quarter) for every 64 columns of the tile
+    static constexpr int kEpiWarps = 4 * (BN / 64);
+    static constexpr int kThreads = 32 * (2 + kEpiWarps);
     static constexpr int kStagingBytes = SLABS * kEpiWarps * kSlabBytes;
     static constexpr int kTmemCols = 2 * BN;
     static constexpr int kBarrierBytes = 256;
@@ -210,7 +212,7 @@ __device__ __forceinline__ uint32_t instr_desc(int m, int n, int f16, uint32_t a
 }
 
 template <int BN, bool PAIR, int SLABS>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__((Cfg<BN, PAIR, SLABS>::kThreads), 1)
 k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__ tiles,
           uint32_t tile_count, uint32_t epilogue, int f16, float ca, float cb, float cc,
           uint32_t *status, uint32_t debug_flags) {
@@ -244,7 +246,7 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(tfull_bar(a), 1);
-            mbar_init(tempty_bar(a), PAIR ? 2 * kEpiWarps : kEpiWarps);
+            mbar_init(tempty_bar(a), PAIR ? 2 * C::kEpiWarps : C::kEpiWarps);
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -358,10 +360,12 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
         }
     } else {
         // ------------------------------------------------------------------ epilogue warps
-        // Warp w may read TMEM lanes 32 (w % 4) .. +31; two warps share a lane quarter and
-        // split the columns of the tile between them.
+        // Warp w may read TMEM lanes 32 (w % 4) .. +31; the four warps of a lane quarter each take
+        // one 64-column chunk of the tile, so an accumulator buffer is free again after ONE chunk
+        // has been read and a tile's epilogue takes a quarter of the time it would on one warp.
         const int q = warp & 3;
-        const int half = (warp - 2) >> 2;
+        const int chunk = (warp - 2) >> 2;
+        const int c0 = chunk * 64;
         // With two slabs per warp they are used in turn: before one is refilled only the store
         // before the last has to be done with it, so a store's shared-memory read overlaps the
         // next fill.
@@ -377,7 +381,6 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
         auto slab_next = [&]() { if (SLABS == 2) sb ^= 1u; };
         const uint32_t tempty_leader0 = PAIR ? map_to_cta(tempty_bar(0), 0) : tempty_bar(0);
         uint32_t acc = 0, acc_phase = 0;
-        constexpr int kHalfCols = BN / 2;
         for (uint32_t t = first_tile; t < tile_count; t += tile_stride) {
             const GemmTile tl = tiles[t];
             const GemmProblem *p = problems + tl.problem;
@@ -394,36 +397,38 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
             const int row_in_tile = 32 * q + lane;
             const int grow = m0 + row_in_tile;
             const int slab_row0 = m0 + 32 * q;
-            const int col_begin = half * kHalfCols;
+            // fragment order: [128-row sub-tile][32-column unit][float4 index][row]
+            const size_t unit0 = ((size_t)tile_lin * (BN / 32) + (size_t)(c0 / 32)) * 8;
 
-            // The polynomial epilogue needs the FP32 Gram tile: fetch the first 64 columns
-            // before the accumulator is ready so the latency hides behind the MMAs.
-            float4 g[16];
+            // The polynomial epilogue needs the FP32 Gram tile: fetch the first 32 columns before
+            // the accumulator is ready so the latency hides behind the MMAs.
+            float4 g[8];
             if (epilogue == kEpiPoly && !dbg_no_store) {
-                const size_t unit0 = ((size_t)tile_lin * (BN / 32) + (size_t)(col_begin / 32)) * 8;
 #pragma unroll
-                for (int j = 0; j < 16; ++j) g[j] = __ldcg(frag + (unit0 + j) * kGemmBlockM + row_in_tile);
+                for (int j = 0; j < 8; ++j) g[j] = __ldcg(frag + (unit0 + j) * kGemmBlockM + row_in_tile);
             }
 
             bool ready = mbar_wait(tfull_bar(acc), acc_phase, abort_flag);
             ready = __all_sync(0xffffffffu, ready);
             if (!ready) break;
             tc_fence_after();
-            const uint32_t taddr = tmem_base + ((uint32_t)(32 * q) << 16) + acc * BN;
+            const uint32_t taddr = tmem_base + ((uint32_t)(32 * q) << 16) + acc * BN + c0;
             const uint32_t tempty = tempty_leader0 + 8u * acc;
+            const bool in_range = n0 + c0 < (int)N && slab_row0 < (int)M && !dbg_no_store;   // warp-uniform
 
             if (epilogue == kEpiApplyLast) {
                 // FP32 result in the storage layout: 32 columns (128 bytes) per staged slab
-                for (int c0 = col_begin; c0 < col_begin + kHalfCols; c0 += 32) {
+#pragma unroll 1
+                for (int sub = 0; sub < 2; ++sub) {
                     uint32_t v[32];
-                    tc_ld32(taddr + c0, v);
+                    tc_ld32(taddr + 32 * sub, v);
                     tc_ld_wait();
-                    if (c0 + 32 >= col_begin + kHalfCols) {
+                    if (sub == 1) {
                         tc_fence_before();
                         __syncwarp();
                         if (lane == 0) mbar_arrive_cluster(tempty);
                     }
-                    if (n0 + c0 >= (int)N || slab_row0 >= (int)M || dbg_no_store) continue;  // warp-uniform
+                    if (!in_range || n0 + c0 + 32 * sub >= (int)N) continue;
                     slab_wait();
                     uint8_t *slab = slab_pair + sb * kSlabBytes;
 #pragma unroll
@@ -434,64 +439,64 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
                     fence_async_smem();
                     __syncwarp();
                     if (lane == 0 && !dbg_no_global) {
-                        tma_store_2d(map32, smem_u32(slab), n0 + c0, slab_row0);
+                        tma_store_2d(map32, smem_u32(slab), n0 + c0 + 32 * sub, slab_row0);
                         tma_store_commit();
                     }
                     slab_next();
                 }
             } else {
-                // 16-bit result: 64 columns (128 bytes) per staged slab
-                for (int c0 = col_begin; c0 < col_begin + kHalfCols; c0 += 64) {
-                    uint32_t v[64];
-                    tc_ld32(taddr + c0, v);
-                    tc_ld32(taddr + c0 + 32, v + 32);
+                // 16-bit result: the chunk's 64 columns are read in two halves of 32 and packed
+                uint32_t packed[32];
+#pragma unroll
+                for (int sub = 0; sub < 2; ++sub) {
+                    uint32_t v[32];
+                    tc_ld32(taddr + 32 * sub, v);
                     tc_ld_wait();
-                    const bool last_chunk = c0 + 64 >= col_begin + kHalfCols;
-                    if (last_chunk) {
+                    if (sub == 1) {
                         tc_fence_before();
                         __syncwarp();
                         if (lane == 0) mbar_arrive_cluster(tempty);
                     }
                     if ((epilogue == kEpiGram || epilogue == kEpiPoly) && !dbg_no_store) {
-                        // fragment order: [128-row sub-tile][32-column unit][float4 index][row]
-                        const size_t unit0 = ((size_t)tile_lin * (BN / 32) + (size_t)(c0 / 32)) * 8;
-                        if (epilogue == kEpiGram && !dbg_no_global) {
-                            float4 *fw = const_cast<float4 *>(frag);
+                        const size_t unit = unit0 + 8 * sub;
+                        if (epilogue == kEpiGram) {
+                            if (!dbg_no_global) {
+                                float4 *fw = const_cast<float4 *>(frag);
 #pragma unroll
-                            for (int j = 0; j < 16; ++j)
-                                __stcg(fw + (unit0 + j) * kGemmBlockM + row_in_tile,
-                                       make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
-                                                   __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3])));
-                        } else if (epilogue == kEpiPoly) {
+                                for (int j = 0; j < 8; ++j)
+                                    __stcg(fw + (unit + j) * kGemmBlockM + row_in_tile,
+                                           make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                                       __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3])));
+                            }
+                        } else {
 #pragma unroll
-                            for (int j = 0; j < 16; ++j) {
+                            for (int j = 0; j < 8; ++j) {
                                 const float gv[4] = {g[j].x, g[j].y, g[j].z, g[j].w};
 #pragma unroll
                                 for (int e = 0; e < 4; ++e) {
-                                    const int gcol = n0 + c0 + 4 * j + e;
+                                    const int gcol = n0 + c0 + 32 * sub + 4 * j + e;
                                     const float ident = (gcol == grow) ? ca : 0.0f;
                                     // store/plain.rs:175-178: fma(c, acc, fma(b, base, identity))
                                     v[4 * j + e] = __float_as_uint(
                                         fmaf(cc, __uint_as_float(v[4 * j + e]), fmaf(cb, gv[e], ident)));
                                 }
                             }
-                            if (!last_chunk) {  // fetch the next 64 columns while this chunk is packed and stored
-                                const size_t unit1 = unit0 + 16;
+                            if (sub == 0) {   // the other 32 columns, while this half is packed
 #pragma unroll
-                                for (int j = 0; j < 16; ++j) g[j] = __ldcg(frag + (unit1 + j) * kGemmBlockM + row_in_tile);
+                                for (int j = 0; j < 8; ++j) g[j] = __ldcg(frag + (unit + 8 + j) * kGemmBlockM + row_in_tile);
                             }
                         }
                     }
-                    if (n0 + c0 >= (int)N || slab_row0 >= (int)M || dbg_no_store) continue;  // warp-uniform
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        packed[16 * sub + j] = pack_operands(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]), f16);
+                }
+                if (in_range) {
                     slab_wait();
                     uint8_t *slab = slab_pair + sb * kSlabBytes;
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
-                        uint4 w;
-                        w.x = pack_operands(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]), f16);
-                        w.y = pack_operands(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]), f16);
-                        w.z = pack_operands(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]), f16);
-                        w.w = pack_operands(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]), f16);
+                        const uint4 w = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
                         *reinterpret_cast<uint4 *>(slab + lane * 128 + ((j ^ (lane & 7)) << 4)) = w;
                     }
                     fence_async_smem();
@@ -508,7 +513,7 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
                         uint8_t *slab_t = slab_pair + sb * kSlabBytes;
 #pragma unroll
                         for (int c = 0; c < 64; c += 2) {
-                            const uint32_t mine = pack_operands(__uint_as_float(v[c]), __uint_as_float(v[c + 1]), f16);
+                            const uint32_t mine = packed[c >> 1];
                             const uint32_t other = __shfl_xor_sync(0xffffffffu, mine, 1);
                             const uint32_t out = (lane & 1) ? __byte_perm(other, mine, 0x7632) : __byte_perm(mine, other, 0x5410);
                             *reinterpret_cast<uint32_t *>(slab_t + (c + (lane & 1)) * 64 + (lane & ~1) * 2) = out;
@@ -577,7 +582,7 @@ cudaError_t launch_impl(const GemmProblem *problems, const GemmTile *tiles, uint
     cfg.attrs = attr;
     cfg.numAttrs = n_attr;
     cfg.gridDim = dim3((unsigned)grid, 1, 1);
-    cfg.blockDim = dim3(kGemmThreads, 1, 1);
+    cfg.blockDim = dim3((unsigned)Cfg<BN, PAIR, SLABS>::kThreads, 1, 1);
     cfg.dynamicSmemBytes = Cfg<BN, PAIR, SLABS>::kSmemBytes;
     cfg.stream = s;
     return cudaLaunchKernelEx(&cfg, k_ns_gemm<BN, PAIR, SLABS>, problems, tiles, tile_count, epilogue, f16, ca, cb, cc, status,
@@ -588,11 +593,8 @@ cudaError_t launch_impl(const GemmProblem *problems, const GemmTile *tiles, uint
 
 cudaError_t gemm_configure(int block_n, int pair) {
     if (pair && block_n == 256) {
-        cudaError_t e = cudaFuncSetAttribute(k_ns_gemm<256, true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             Cfg<256, true, 1>::kSmemBytes);
-        if (e != cudaSuccess) return e;
-        return cudaFuncSetAttribute(k_ns_gemm<256, true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    Cfg<256, true, 2>::kSmemBytes);
+        return cudaFuncSetAttribute(k_ns_gemm<256, true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    Cfg<256, true, 1>::kSmemBytes);
     }
     if (!pair && block_n == 256)
         return cudaFuncSetAttribute(k_ns_gemm<256, false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -607,8 +609,6 @@ cudaError_t launch_ns_gemm(int block_n, int pair, const GemmProblem *problems, c
                            float cc, uint32_t *status, uint32_t debug_flags, int grid, cudaStream_t s) {
     if (tile_count == 0) return cudaSuccess;
     if (pair && block_n == 256) {
-        if (epilogue == kEpiGram || epilogue == kEpiPoly)
-            return launch_impl<256, true, 2>(problems, tiles, tile_count, epilogue, f16, ca, cb, cc, status, debug_flags, grid, s);
         return launch_impl<256, true, 1>(problems, tiles, tile_count, epilogue, f16, ca, cb, cc, status, debug_flags, grid, s);
     }
     if (!pair && block_n == 256)
