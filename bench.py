@@ -549,7 +549,7 @@ def run_extras(args):
     torch.cuda.set_device(0)
     dev = "cuda"
     peaks = load_peaks()
-    mats, _, _ = model_shapes(args.workload)
+    mats, emb, _ = model_shapes(args.workload)
     n_el = sum(r * c for r, c in mats)
     opt = b2.OptimizerModule()
     g = torch.Generator(device=dev).manual_seed(0)
@@ -610,6 +610,27 @@ def run_extras(args):
         ("scales_to_sm100 (raw plane, all matrices as one [n/768, 768] tensor)", 2.0 / 16.0,
          lambda: b2.scales_to_sm100(raw_scales, b2.SCALES_RAW, n_el // 768, 768)),
     ]
+    # the embeddings as deferred AdamW tensors (the trainer's mode): update with y cached in the gradient
+    # buffer, then every tensor's y quantised by one launch (src/training/schedule_free/tensor.rs:71-89)
+    emb_sets = []
+    for rows, cols in emb:
+        n = rows * cols
+        emb_sets.append(dict(z_master=randn(n, 0.02), x_master=randn(n, 0.02), grad=randn(n, 1e-3),
+                             first_moment=torch.zeros(n, device=dev), second_moment=torch.zeros(n, device=dev),
+                             bytes=torch.zeros(n // 2, dtype=torch.uint8, device=dev),
+                             scales=(b2.zero_scales(rows, cols, dev) if layout == b2.SCALES_CSF else
+                                     torch.zeros(n // 16, dtype=torch.uint8, device=dev)),
+                             global_scale=torch.zeros(1, device=dev), amax=torch.zeros(1, device=dev),
+                             scale_layout=layout, len=n, mode=1))
+    emb_el = sum(t["len"] for t in emb_sets)
+    emb_table, emb_count, emb_chunks = opt.adamw_table(emb_sets, dev)
+    adam_hp = dict(ADAM)
+    cases += [
+        ("AdamW, deferred quantisation, all embeddings in one table", 40.0 * emb_el / n_el,
+         lambda: opt.apply_adamw_update_multi(emb_table, emb_count, emb_chunks, **adam_hp)),
+        ("AdamW tensors: materialize training weights (cached y -> NVFP4), one launch", 4.5625 * emb_el / n_el,
+         lambda: opt.adamw_materialize_training_weights(emb_table, emb_count, emb_chunks, ADAM["schedule_beta"])),
+    ]
     co5 = np.tile(np.asarray([3.4445, -4.7750, 2.0315], np.float32), (5, 1))
 
     def production_step():
@@ -625,6 +646,8 @@ def run_extras(args):
     cases.append(("production-order step: prepare + 5x NS + finish (NorMuon, qk-clip, deferred) + materialise y", 0.0,
                   production_step))
     for name, bpe, fn in cases:
+        if args.only and args.only not in name:
+            continue
         for _ in range(3):
             fn()
         torch.cuda.synchronize()
@@ -657,6 +680,7 @@ def main():
     ap.add_argument("--sweep", action="store_true", help="update+quantise bandwidth sweep over [R, 4096] tensors")
     ap.add_argument("--extras", action="store_true",
                     help="time the entry points beside the headline step (variants, clip, materialisation, converter)")
+    ap.add_argument("--only", default="", help="with --extras: run only the cases whose name contains this text")
     args = ap.parse_args()
     if args.sweep:
         run_sweep(args)

@@ -320,7 +320,7 @@ int b2_apply_fp32_adamw_update(const b2_adamw_update_args *args, void *stream);
 typedef struct b2_adamw_slot_descriptor {
     uint64_t z_master, x_master, grad, first_moment, second_moment;
     uint64_t amax;          /* f32[1]; modes 1 and 2 */
-    uint64_t bytes, scales, global_scale; /* mode 2 */
+    uint64_t bytes, scales, global_scale; /* mode 2; mode 1 when materialised later */
     uint32_t len;
     uint32_t chunk_begin;   /* filled by b2_adamw_table_prepare */
     uint32_t mode;
@@ -331,6 +331,15 @@ int b2_adamw_table_prepare(b2_adamw_slot_descriptor *host_table, uint32_t count,
 /* Hyper-parameters are taken from `scalars` (pointer fields and len are ignored). */
 int b2_apply_adamw_update_multi(const b2_adamw_slot_descriptor *d_table, uint32_t count, uint32_t total_chunks,
                                 const b2_adamw_update_args *scalars, void *stream);
+/* `Materializer::adam` for every mode-1 entry of the table at once
+ * (src/training/schedule_free/tensor.rs:71-89): quantises the schedule-free values with the max|y|
+ * the deferred update left in `amax` into bytes / scales / global_scale.  values_cached != 0 reads
+ * y from each entry's gradient buffer (where the update left it); 0 rebuilds
+ * y = z + schedule_beta * (x - z) from the masters, as the reference does when its cached values
+ * are stale (`scheduled_values_valid`, tensor.rs:245).  Entries of other modes are skipped. */
+int b2_adamw_materialize_training_weights(const b2_adamw_slot_descriptor *d_table, uint32_t count,
+                                          uint32_t total_chunks, float schedule_beta, int values_cached,
+                                          void *stream);
 /* `Materializer::muon_precomputed` for every matrix of the plan at once
  * (src/training/schedule_free/tensor.rs:128-153): quantises the cached schedule-free values y
  * (left in each slot's gradient buffer by the update) with the cached schedule_amax. */

@@ -836,6 +836,17 @@ int b2_apply_adamw_update_multi(const b2_adamw_slot_descriptor *d_table, uint32_
     if (e != cudaSuccess) return (int)e;
     return (int)launch_adamw_multi(d_table, count, total_chunks, *scalars, stream_grid_cap(d), as_stream(stream));
 }
+int b2_adamw_materialize_training_weights(const b2_adamw_slot_descriptor *d_table, uint32_t count,
+                                          uint32_t total_chunks, float schedule_beta, int values_cached,
+                                          void *stream) {
+    if (!d_table && count) return B2_ERROR_INVALID_VALUE;
+    if (!std::isfinite(schedule_beta)) return B2_ERROR_INVALID_VALUE;
+    DeviceInfo d;
+    cudaError_t e = device_info(d);
+    if (e != cudaSuccess) return (int)e;
+    return (int)launch_adamw_multi_materialize(d_table, count, total_chunks, schedule_beta, values_cached != 0,
+                                               stream_grid_cap(d), as_stream(stream));
+}
 int b2_muon_materialize_training_weights(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_slots, void *stream) {
     if (!plan || !d_slots) return B2_ERROR_INVALID_VALUE;
     SlotView v = plan->view(d_slots);

@@ -102,9 +102,16 @@ __device__ __forceinline__ void csf_store24(uint8_t *d, uint32_t v) {
     d[1] = (uint8_t)(v >> 8);
     d[2] = (uint8_t)(v >> 16);
 }
+// floor(2^32 / groups-per-row) (one less for a power of two): the multiplier csf_store_record
+// divides by.  Computed once per tensor, not once per record.
+__device__ __forceinline__ uint32_t csf_row_magic(uint32_t k, uint32_t rows) {
+    return (rows == 1 || k < 16) ? 0u : 0xffffffffu / (k / 16);
+}
 // Eight consecutive block scales (a = groups 0..3, b = groups 4..7) of flat group index g0
-// (a multiple of 8).  `scales` points at the CSF header; k and rows are read from it.
-__device__ __forceinline__ void csf_store_record(uint8_t *scales, uint32_t k, uint32_t rows,
+// (a multiple of 8).  `scales` points at the CSF header; k and rows are read from it, and
+// magic = csf_row_magic(k, rows) when USE_MAGIC (ignored otherwise).
+template <bool USE_MAGIC>
+__device__ __forceinline__ void csf_store_record(uint8_t *scales, uint32_t k, uint32_t rows, uint32_t magic,
                                                  uint32_t g0, uint32_t a, uint32_t b) {
     if (rows == 1) {
         uint32_t *p = reinterpret_cast<uint32_t *>(scales + 128 + g0);
@@ -112,8 +119,20 @@ __device__ __forceinline__ void csf_store_record(uint8_t *scales, uint32_t k, ui
         p[1] = b;
         return;
     }
-    uint32_t groups = k / 16;
-    uint32_t row = g0 / groups, kg = g0 - row * groups;
+    const uint32_t groups = k / 16;
+    uint32_t row, kg;
+    if (USE_MAGIC) {
+        // row = g0 / groups by multiplication: floor(g0 * magic / 2^32) is the quotient or one less
+        row = __umulhi(g0, magic);
+        kg = g0 - row * groups;
+        if (kg >= groups) {
+            ++row;
+            kg -= groups;
+        }
+    } else {
+        row = g0 / groups;
+        kg = g0 - row * groups;
+    }
     uint32_t t = row / 128 * (k / 128) + kg / 8;
     uint32_t r = row % 128;
     uint8_t *d = scales + 128;

@@ -89,6 +89,9 @@ cudaError_t launch_adamw(const b2_adamw_update_args &a, int mode, int grid_cap,
                          cudaStream_t s);
 cudaError_t launch_adamw_multi(const b2_adamw_slot_descriptor *table, uint32_t count, uint32_t total_chunks,
                               const b2_adamw_update_args &scalars, int grid_cap, cudaStream_t s);
+cudaError_t launch_adamw_multi_materialize(const b2_adamw_slot_descriptor *table, uint32_t count,
+                                          uint32_t total_chunks, float beta, bool cached, int grid_cap,
+                                          cudaStream_t s);
 cudaError_t launch_grad_clip(const b2_gradient_clip_args &a, int grid_cap, cudaStream_t s);
 cudaError_t launch_scales_to_sm100(const uint8_t *src, int src_csf, uint32_t rows, uint32_t cols, uint8_t *out,
                                    int grid_cap, cudaStream_t s);

@@ -779,14 +779,55 @@ __device__ __forceinline__ SymExpLin symexp_resolve(const SymExpLinParams &p, fl
     return s;
 }
 
-template <int MODE, int THREADS = kEncodeThreads, bool L2_ONLY = false>
-__device__ __forceinline__ void encode_chunk(const float *src, const float *z, const float *xm,
-                                             float beta, uint32_t len, uint32_t base, float gs,
-                                             uint8_t *fp4, uint8_t *scales, int scale_layout,
-                                             uint32_t csf_k, uint32_t csf_rows,
-                                             const SymExpLin sx = SymExpLin{0.0f, 1.0f, 1.0f, 1.0f}) {
-    // Each warp owns 32 consecutive groups = 2048 contiguous bytes.  It reads them with four
-    // fully coalesced 128-bit loads per lane, parks them in shared memory (16-byte slots XOR-ed
+// The raw loads of one warp's span of a chunk (four float4 per lane, eight in MODE 1), kept apart
+// from the arithmetic so that a kernel can have the next chunk's loads in flight while it encodes
+// the current one.
+template <int MODE>
+struct EncodeRaw {
+    float4 a[4];
+    float4 b[MODE == 1 ? 4 : 1];
+};
+template <int MODE, bool L2_ONLY = false>
+__device__ __forceinline__ void encode_fetch(EncodeRaw<MODE> &r, const float *src, const float *z, const float *xm,
+                                             uint32_t len, uint32_t base) {
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const uint32_t warp_first = (base / 16 + warp * 32) * 16;   // first element of this warp's span
+    if (!L2_ONLY && warp_first + 512 <= len) {                  // the whole span exists (warp-uniform)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t e = warp_first + (j * 32 + lane) * 4;
+            if (MODE == 0) {
+                r.a[j] = L2_ONLY ? __ldcg(reinterpret_cast<const float4 *>(src + e)) : ld_stream(src + e);
+            } else {
+                r.a[j] = ld_stream(z + e);
+                r.b[j] = ld_stream(xm + e);
+            }
+        }
+        return;
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint32_t e = warp_first + (j * 32 + lane) * 4;
+        r.a[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (MODE == 1) r.b[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (e < len) {
+            if (MODE == 0) {
+                r.a[j] = L2_ONLY ? __ldcg(reinterpret_cast<const float4 *>(src + e)) : ld_stream(src + e);
+            } else {
+                r.a[j] = ld_stream(z + e);
+                r.b[j] = ld_stream(xm + e);
+            }
+        }
+    }
+}
+template <int MODE, int THREADS = kEncodeThreads, bool USE_MAGIC = true>
+__device__ __forceinline__ void encode_finish(const EncodeRaw<MODE> &r, float beta, uint32_t len, uint32_t base,
+                                              float gs, uint8_t *fp4, uint8_t *scales, int scale_layout,
+                                              uint32_t csf_k, uint32_t csf_rows, uint32_t csf_magic,
+                                              const SymExpLin sx) {
+    // Each warp owns 32 consecutive groups = 2048 contiguous bytes.  It has read them with four
+    // fully coalesced 128-bit loads per lane; it parks them in shared memory (16-byte slots XOR-ed
     // with the group number so neither side conflicts) and every lane picks up its own group.
     __shared__ float4 stage[THREADS / 32][128];
     const int lane = threadIdx.x & 31;
@@ -794,23 +835,17 @@ __device__ __forceinline__ void encode_chunk(const float *src, const float *z, c
     const uint32_t group = base / 16 + threadIdx.x;
     const uint32_t i = group * 16;
     const bool valid = i < len;
-    const uint32_t warp_first = (base / 16 + warp * 32) * 16;   // first element of this warp's span
     float v[16];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
         const uint32_t f4 = j * 32 + lane;                       // float4 index inside the span
-        const uint32_t e = warp_first + f4 * 4;
-        float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (e < len) {
-            if (MODE == 0) {
-                t = L2_ONLY ? __ldcg(reinterpret_cast<const float4 *>(src + e)) : ld_stream(src + e);
-            } else {
-                float4 zv = ld_stream(z + e), xv = ld_stream(xm + e);
-                t.x = symexp_forward(zv.x + beta * (xv.x - zv.x), sx);
-                t.y = symexp_forward(zv.y + beta * (xv.y - zv.y), sx);
-                t.z = symexp_forward(zv.z + beta * (xv.z - zv.z), sx);
-                t.w = symexp_forward(zv.w + beta * (xv.w - zv.w), sx);
-            }
+        float4 t = r.a[j];
+        if (MODE == 1) {
+            const float4 zv = r.a[j], xv = r.b[j];
+            t.x = symexp_forward(zv.x + beta * (xv.x - zv.x), sx);
+            t.y = symexp_forward(zv.y + beta * (xv.y - zv.y), sx);
+            t.z = symexp_forward(zv.z + beta * (xv.z - zv.z), sx);
+            t.w = symexp_forward(zv.w + beta * (xv.w - zv.w), sx);
         }
         const uint32_t g = f4 >> 2, k = f4 & 3;
         stage[warp][g * 4 + (k ^ (g & 3))] = t;
@@ -849,34 +884,97 @@ __device__ __forceinline__ void encode_chunk(const float *src, const float *z, c
         uint32_t s2 = sb | (__shfl_down_sync(0xffffffffu, sb, 1) << 8);
         uint32_t a = s2 | (__shfl_down_sync(0xffffffffu, s2, 2) << 16);
         uint32_t b = __shfl_down_sync(0xffffffffu, a, 4);
-        if ((lane & 7) == 0 && valid) csf_store_record(scales, csf_k, csf_rows, group, a, b);
+        if ((lane & 7) == 0 && valid) csf_store_record<USE_MAGIC>(scales, csf_k, csf_rows, csf_magic, group, a, b);
+    }
+}
+template <int MODE, int THREADS = kEncodeThreads, bool L2_ONLY = false>
+__device__ __forceinline__ void encode_chunk(const float *src, const float *z, const float *xm,
+                                             float beta, uint32_t len, uint32_t base, float gs,
+                                             uint8_t *fp4, uint8_t *scales, int scale_layout,
+                                             uint32_t csf_k, uint32_t csf_rows,
+                                             const SymExpLin sx = SymExpLin{0.0f, 1.0f, 1.0f, 1.0f}) {
+    EncodeRaw<MODE> r;
+    encode_fetch<MODE, L2_ONLY>(r, src, z, xm, len, base);
+    encode_finish<MODE, THREADS, false>(r, beta, len, base, gs, fp4, scales, scale_layout, csf_k, csf_rows, 0u, sx);
+}
+
+// Where one chunk of a stand-alone encode pass reads and writes.  `skip` marks a chunk the pass
+// leaves alone (len and base are valid all the same).
+struct EncodeTarget {
+    const float *src, *z, *xm;
+    uint8_t *fp4, *scales;
+    float *gs_out;           // written by thread 0 of the tensor's first chunk
+    uint32_t len, base, k, rows, magic;
+    float gs;
+    int layout;
+    bool skip;
+};
+// The chunk loop of a stand-alone encode pass.  Every CTA takes one contiguous share of the chunk
+// list, so the description of a tensor (descriptor, tensor maximum, scale header: a chain of
+// dependent loads and a division) is worked out once per tensor and CTA and a step to the next
+// chunk is one addition; `target_of(c)` gives the full description of chunk c.  Within a tensor
+// the loop is software-pipelined one chunk deep: the loads of the next chunk are issued before the
+// current one is encoded, so a CTA always has 8 KB (16 KB in MODE 1) in flight.  The two buffers
+// swap roles in the unrolled body instead of being copied; the pipeline drains where the share
+// crosses into the next tensor.
+template <int MODE, typename F>
+__device__ __forceinline__ void encode_pipeline(uint32_t total_chunks, float beta, const SymExpLin sx, F target_of) {
+    const uint32_t per = total_chunks / gridDim.x, rem = total_chunks % gridDim.x;
+    uint32_t c = blockIdx.x * per + min(blockIdx.x, rem);
+    const uint32_t end = c + per + (blockIdx.x < rem ? 1u : 0u);
+    EncodeRaw<MODE> ra, rb;
+    while (c < end) {
+        EncodeTarget t = target_of(c);
+        // chunks of this tensor inside the share
+        const uint32_t left = (t.len - t.base + kChunk - 1) / kChunk;
+        uint32_t n = max(min(left, end - c), 1u);   // never stands still, whatever the table says
+        c += n;
+        if (t.skip) continue;
+        if (t.base == 0 && threadIdx.x == 0) *t.gs_out = t.gs;
+        encode_fetch<MODE>(ra, t.src, t.z, t.xm, t.len, t.base);
+        for (;;) {
+            if (n > 1) encode_fetch<MODE>(rb, t.src, t.z, t.xm, t.len, t.base + kChunk);
+            encode_finish<MODE>(ra, beta, t.len, t.base, t.gs, t.fp4, t.scales, t.layout, t.k, t.rows, t.magic, sx);
+            if (--n == 0) break;
+            t.base += kChunk;
+            if (n > 1) encode_fetch<MODE>(ra, t.src, t.z, t.xm, t.len, t.base + kChunk);
+            encode_finish<MODE>(rb, beta, t.len, t.base, t.gs, t.fp4, t.scales, t.layout, t.k, t.rows, t.magic, sx);
+            if (--n == 0) break;
+            t.base += kChunk;
+        }
     }
 }
 
 __global__ void __launch_bounds__(kEncodeThreads)
 k_muon_encode(const b2_muon_slot_descriptor *slots, const uint32_t *prefix, uint32_t slot_count,
               uint32_t total_chunks, const float *amax_x, int quantize_y, int scale_layout) {
-    for (uint32_t c = blockIdx.x; c < total_chunks; c += gridDim.x) {
-        ChunkCtx cx = chunk_ctx(slots, prefix, slot_count, c);
-        const float *src = reinterpret_cast<const float *>(quantize_y ? cx.d.grad : cx.d.x_master);
-        const float amax = quantize_y ? *reinterpret_cast<const float *>(cx.d.schedule_amax)
-                                      : amax_x[cx.slot];
+    encode_pipeline<0>(total_chunks, 0.f, SymExpLin{0.0f, 1.0f, 1.0f, 1.0f}, [&](uint32_t c) {
+        const uint32_t slot = find_slot(prefix, slot_count, c);
+        const b2_muon_slot_descriptor *d = slots + slot;
+        EncodeTarget t;
+        t.src = reinterpret_cast<const float *>(quantize_y ? d->grad : d->x_master);
+        t.z = t.xm = nullptr;
+        const float amax = quantize_y ? *reinterpret_cast<const float *>(d->schedule_amax) : amax_x[slot];
         // crates/cuda-kernels/src/gpt/optimizer/muon/fused/quant/reduce_scale.rs:66-71
-        const float gs = four_six_global_scale(amax);
-        uint8_t *scales = reinterpret_cast<uint8_t *>(cx.d.scales);
-        uint32_t k = 0, rows = 0;
+        t.gs = four_six_global_scale(amax);
+        t.scales = reinterpret_cast<uint8_t *>(d->scales);
+        t.fp4 = reinterpret_cast<uint8_t *>(d->bytes);
+        t.gs_out = reinterpret_cast<float *>(d->global_scale);
+        t.k = t.rows = 0;
         if (scale_layout == B2_SCALES_CSF) {
-            k = reinterpret_cast<const uint32_t *>(scales)[0];
-            rows = reinterpret_cast<const uint32_t *>(scales)[1];
+            t.k = reinterpret_cast<const uint32_t *>(t.scales)[0];
+            t.rows = reinterpret_cast<const uint32_t *>(t.scales)[1];
         } else if (scale_layout == B2_SCALES_SM100) {
-            k = cx.d.cols;
-            rows = cx.d.rows;
+            t.k = d->cols;
+            t.rows = d->rows;
         }
-        if (cx.local_chunk == 0 && threadIdx.x == 0)
-            *reinterpret_cast<float *>(cx.d.global_scale) = gs;
-        encode_chunk<0>(src, nullptr, nullptr, 0.f, cx.len, cx.local_chunk * kChunk, gs,
-                        reinterpret_cast<uint8_t *>(cx.d.bytes), scales, scale_layout, k, rows);
-    }
+        t.magic = scale_layout == B2_SCALES_CSF ? csf_row_magic(t.k, t.rows) : 0u;
+        t.len = d->rows * d->cols;
+        t.base = (c - prefix[slot]) * kChunk;
+        t.layout = scale_layout;
+        t.skip = false;
+        return t;
+    });
 }
 
 // Stand-alone flat quantiser: `fp32_to_nvfp4_four_six_kernel`
@@ -1015,9 +1113,14 @@ k_quantize_flat(const float *src, const float *z, const float *xm, float beta, c
         k = reinterpret_cast<const uint32_t *>(scales)[0];
         rows = reinterpret_cast<const uint32_t *>(scales)[1];
     }
-    if (blockIdx.x == 0 && threadIdx.x == 0) out_gs[0] = gs;
-    for (uint32_t c = blockIdx.x; c < chunks; c += gridDim.x)
-        encode_chunk<MODE>(src, z, xm, beta, len, c * kChunk, gs, fp4, scales, scale_layout, k, rows, sx);
+    const uint32_t magic = scale_layout == B2_SCALES_CSF ? csf_row_magic(k, rows) : 0u;
+    if (chunks == 0) {  // an empty tensor still gets its global scale
+        if (blockIdx.x == 0 && threadIdx.x == 0) out_gs[0] = gs;
+        return;
+    }
+    encode_pipeline<MODE>(chunks, beta, sx, [&](uint32_t c) {
+        return EncodeTarget{src, z, xm, fp4, scales, out_gs, len, c * kChunk, k, rows, magic, gs, scale_layout, false};
+    });
 }
 
 // `tensor_chunk_amax_f32_kernel` / `tensor_amax_from_chunks_f32_kernel`
@@ -1260,24 +1363,50 @@ k_adamw_multi(const b2_adamw_slot_descriptor *t, uint32_t count, uint32_t total_
         __syncthreads();
     }
 }
+// mode 2 entries: x' -> NVFP4; with `deferred` set, mode 1 entries instead: the schedule-free values
+// (cached in the gradient buffer when MODE == 0, rebuilt from the masters when MODE == 1).
+template <int MODE>
+__device__ __forceinline__ EncodeTarget adam_encode_target(const b2_adamw_slot_descriptor *t, uint32_t count,
+                                                           uint32_t c, bool deferred) {
+    const uint32_t slot = find_adam_slot(t, count, c);
+    const b2_adamw_slot_descriptor *d = t + slot;
+    EncodeTarget e;
+    e.len = d->len;
+    e.base = (c - d->chunk_begin) * kChunk;
+    e.skip = d->mode != (deferred ? 1u : 2u);
+    if (e.skip) return e;
+    e.src = reinterpret_cast<const float *>(deferred ? d->grad : d->x_master);
+    e.z = reinterpret_cast<const float *>(d->z_master);
+    e.xm = reinterpret_cast<const float *>(d->x_master);
+    e.gs = four_six_global_scale(*reinterpret_cast<const float *>(d->amax));
+    e.scales = reinterpret_cast<uint8_t *>(d->scales);
+    e.fp4 = reinterpret_cast<uint8_t *>(d->bytes);
+    e.gs_out = reinterpret_cast<float *>(d->global_scale);
+    e.layout = (int)d->scale_layout;
+    e.k = e.rows = 0;
+    if (d->scale_layout == B2_SCALES_CSF) {
+        e.k = reinterpret_cast<const uint32_t *>(e.scales)[0];
+        e.rows = reinterpret_cast<const uint32_t *>(e.scales)[1];
+    }
+    e.magic = d->scale_layout == B2_SCALES_CSF ? csf_row_magic(e.k, e.rows) : 0u;
+    return e;
+}
 __global__ void __launch_bounds__(kEncodeThreads)
 k_adamw_multi_encode(const b2_adamw_slot_descriptor *t, uint32_t count, uint32_t total_chunks) {
-    for (uint32_t c = blockIdx.x; c < total_chunks; c += gridDim.x) {
-        const uint32_t slot = find_adam_slot(t, count, c);
-        const b2_adamw_slot_descriptor d = t[slot];
-        if (d.mode != 2) continue;  // uniform per CTA iteration
-        const float gs = four_six_global_scale(*reinterpret_cast<const float *>(d.amax));
-        uint8_t *scales = reinterpret_cast<uint8_t *>(d.scales);
-        uint32_t k = 0, rows = 0;
-        if (d.scale_layout == B2_SCALES_CSF) {
-            k = reinterpret_cast<const uint32_t *>(scales)[0];
-            rows = reinterpret_cast<const uint32_t *>(scales)[1];
-        }
-        if (c == d.chunk_begin && threadIdx.x == 0) *reinterpret_cast<float *>(d.global_scale) = gs;
-        encode_chunk<0>(reinterpret_cast<const float *>(d.x_master), nullptr, nullptr, 0.f, d.len,
-                        (c - d.chunk_begin) * kChunk, gs, reinterpret_cast<uint8_t *>(d.bytes), scales,
-                        (int)d.scale_layout, k, rows);
-    }
+    encode_pipeline<0>(total_chunks, 0.f, SymExpLin{0.0f, 1.0f, 1.0f, 1.0f},
+                       [&](uint32_t c) { return adam_encode_target<0>(t, count, c, false); });
+}
+
+// `Materializer::adam` for every deferred (mode 1) entry of the table at once
+// (src/training/schedule_free/tensor.rs:71-89 -> materialize_schedule_free_precomputed):
+// quantises the schedule-free values with the max|y| the update left in `amax`.  CACHED reads y
+// from the gradient buffer; otherwise y = z + beta * (x - z) is rebuilt from the masters.
+template <bool CACHED>
+__global__ void __launch_bounds__(kEncodeThreads)
+k_adamw_multi_materialize(const b2_adamw_slot_descriptor *t, uint32_t count, uint32_t total_chunks, float beta) {
+    encode_pipeline<CACHED ? 0 : 1>(total_chunks, beta, SymExpLin{0.0f, 1.0f, 1.0f, 1.0f}, [&](uint32_t c) {
+        return adam_encode_target<CACHED ? 0 : 1>(t, count, c, true);
+    });
 }
 
 // Global gradient-norm clip: per-chunk sums of squares, the scale, and the optional in-place
@@ -1560,10 +1689,19 @@ cudaError_t launch_muon_sign_update(const SlotView &v, const MomentumParams &mp,
         v.slots, v.chunk_prefix, v.slot_count, v.total_chunks, mp, up, amax_x);
     return cudaGetLastError();
 }
+// Grid of a pipelined encode pass: exactly the CTAs that are resident at once (the pass is a
+// grid-stride loop, so a second wave would only add a tail).  grid_cap is 8 CTAs per SM.
+template <typename K>
+static int encode_grid(K kernel, uint32_t chunks, int grid_cap) {
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kEncodeThreads, 0) != cudaSuccess || per_sm < 1)
+        per_sm = 4;
+    return clamp_grid(chunks, (grid_cap / 8) * per_sm);
+}
 cudaError_t launch_muon_encode(const SlotView &v, const float *amax_x, int quantize_y,
                                int scale_layout, cudaStream_t s) {
     if (v.total_chunks == 0) return cudaSuccess;
-    k_muon_encode<<<clamp_grid(v.total_chunks, 2 * v.grid), kEncodeThreads, 0, s>>>(
+    k_muon_encode<<<encode_grid(k_muon_encode, v.total_chunks, v.grid), kEncodeThreads, 0, s>>>(
         v.slots, v.chunk_prefix, v.slot_count, v.total_chunks, amax_x, quantize_y, scale_layout);
     return cudaGetLastError();
 }
@@ -1585,7 +1723,7 @@ cudaError_t launch_quantize_flat(const float *x, const float *z, const float *xm
     SymExpLinParams sp = {};
     if (symexp) sp = *symexp;
     uint32_t chunks = (group_count * 16 + kChunk - 1) / kChunk;
-    int grid = clamp_grid(chunks, 2 * grid_cap);
+    int grid = mode == 0 ? encode_grid(k_quantize_flat<0>, chunks, grid_cap) : encode_grid(k_quantize_flat<1>, chunks, grid_cap);
     if (grid == 0) grid = 1;  // still writes the global scale
     if (mode == 0)
         k_quantize_flat<0><<<grid, kEncodeThreads, 0, s>>>(x, z, xm, beta, amax, fp4, scales, gs, group_count, scale_layout, sp);
@@ -1624,7 +1762,19 @@ cudaError_t launch_adamw_multi(const b2_adamw_slot_descriptor *table, uint32_t c
                    a.beta1_correction, a.beta2_correction, a.eps, a.average_coefficient, a.schedule_beta};
     k_adamw_multi_reset<<<(count + 255) / 256, 256, 0, s>>>(table, count);
     k_adamw_multi<<<clamp_grid(total_chunks, grid_cap), kThreads, 0, s>>>(table, count, total_chunks, sc, a.d_grad_scale);
-    k_adamw_multi_encode<<<clamp_grid(total_chunks, 2 * grid_cap), kEncodeThreads, 0, s>>>(table, count, total_chunks);
+    k_adamw_multi_encode<<<encode_grid(k_adamw_multi_encode, total_chunks, grid_cap), kEncodeThreads, 0, s>>>(table, count, total_chunks);
+    return cudaGetLastError();
+}
+cudaError_t launch_adamw_multi_materialize(const b2_adamw_slot_descriptor *table, uint32_t count,
+                                          uint32_t total_chunks, float beta, bool cached, int grid_cap,
+                                          cudaStream_t s) {
+    if (count == 0 || total_chunks == 0) return cudaSuccess;
+    if (cached)
+        k_adamw_multi_materialize<true><<<encode_grid(k_adamw_multi_materialize<true>, total_chunks, grid_cap),
+                                          kEncodeThreads, 0, s>>>(table, count, total_chunks, beta);
+    else
+        k_adamw_multi_materialize<false><<<encode_grid(k_adamw_multi_materialize<false>, total_chunks, grid_cap),
+                                           kEncodeThreads, 0, s>>>(table, count, total_chunks, beta);
     return cudaGetLastError();
 }
 cudaError_t launch_grad_clip(const b2_gradient_clip_args &a, int grid_cap, cudaStream_t s) {

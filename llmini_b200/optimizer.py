@@ -328,6 +328,13 @@ class OptimizerModule:
         check(self._lib.b2_apply_adamw_update_multi(_ptr(table), count, total_chunks, C.byref(a), _stream()),
               "apply_adamw_update_multi")
 
+    # Materializer::adam for all deferred tensors of the table (src/training/schedule_free/tensor.rs:71-89)
+    def adamw_materialize_training_weights(self, table: torch.Tensor, count: int, total_chunks: int,
+                                           schedule_beta: float, values_cached: bool = True) -> None:
+        check(self._lib.b2_adamw_materialize_training_weights(_ptr(table), count, total_chunks, schedule_beta,
+                                                              int(values_cached), _stream()),
+              "adamw_materialize_training_weights")
+
     # Materializer::muon_precomputed for all matrices (src/training/schedule_free/tensor.rs:128-153)
     def muon_materialize_training_weights(self, plan: "MuonPlan", slots: torch.Tensor) -> None:
         check(self._lib.b2_muon_materialize_training_weights(plan.handle, _ptr(slots), _stream()),

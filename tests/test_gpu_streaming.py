@@ -369,6 +369,62 @@ def test_multi_tensor_adamw_equals_per_tensor_calls():
                 assert torch.equal(ta[key], tb[key]), (ta["len"], ta["mode"], key)
 
 
+def test_multi_tensor_adamw_materialize_equals_per_tensor_precomputed():
+    # deferred multi-tensor update, then ONE launch that quantises every deferred tensor's cached
+    # y with its cached amax == materialize_schedule_free_precomputed per tensor, with the cached
+    # values and with y rebuilt from the masters
+    opt = b2.OptimizerModule()
+    specs = [(128 * 6, 1), (128 * 40, 1), (4099, 0), (2048 * 3 + 128, 1), (128 * 8, 2)]
+    hp = dict(grad_scale=0.7, learning_rate=2e-4, weight_decay=0.005, beta1=0.9, beta2=0.95, beta1_correction=0.19,
+              beta2_correction=0.0975, eps=1e-10, average_coefficient=0.5, schedule_beta=0.3)
+    rng = np.random.default_rng(77)
+    tensors = []
+    for n, mode in specs:
+        t = dict(z_master=dev(U.weights(rng, n)), x_master=dev(U.weights(rng, n)), grad=dev(U.gradients(rng, n)),
+                 first_moment=dev(U.weights(rng, n, 1e-3)), second_moment=dev(np.abs(U.weights(rng, n, 1e-6))),
+                 len=n, mode=mode)
+        if mode:
+            t["amax"] = torch.zeros(1, device="cuda")
+            q = b2.Nvfp4Tensor.empty(n // 128, 128)
+            t.update(bytes=q.bytes, scales=q.scales, global_scale=q.global_scale, q=q)
+        tensors.append(t)
+    table, count, chunks = opt.adamw_table(tensors)
+    opt.apply_adamw_update_multi(table, count, chunks, **hp)
+    torch.cuda.synchronize()
+    untouched = {i: (t["bytes"].clone(), t["global_scale"].clone()) for i, t in enumerate(tensors) if t["mode"] == 2}
+    for cached in (True, False):
+        for t in tensors:
+            if t["mode"] == 1:
+                t["bytes"].zero_()
+                t["global_scale"].zero_()
+                t["scales"][128:].zero_()
+        opt.adamw_materialize_training_weights(table, count, chunks, hp["schedule_beta"], values_cached=cached)
+        torch.cuda.synchronize()
+        for i, t in enumerate(tensors):
+            if t["mode"] == 2:  # other modes are left alone
+                assert torch.equal(t["bytes"], untouched[i][0]) and torch.equal(t["global_scale"], untouched[i][1])
+            if t["mode"] != 1:
+                continue
+            n = t["len"]
+            ref = b2.Nvfp4Tensor.empty(n // 128, 128)
+            opt.materialize_schedule_free_precomputed(
+                bytes=ref.bytes, scales=ref.scales, global_scale=ref.global_scale, z_master=t["z_master"],
+                x_master=t["x_master"], precomputed_values=(t["grad"] if cached else None), amax=t["amax"], len=n,
+                scale_rows=n // 128, scale_k=128, beta=hp["schedule_beta"])
+            torch.cuda.synchronize()
+            assert torch.equal(t["bytes"], ref.bytes), (n, cached)
+            assert torch.equal(t["scales"], ref.scales), (n, cached)
+            assert torch.equal(t["global_scale"], ref.global_scale), (n, cached)
+            if cached:  # and against the oracle on the cached values
+                y = host(t["grad"]).ravel()
+                am = host(t["amax"])[0]
+                assert am == np.max(np.abs(y))
+                gs = host(t["global_scale"])[0]
+                codes, raw, ogs, _ = o.nvfp4_quantize(y, amax=am, rcp_table=rcp_table(gs))
+                assert gs == ogs and np.array_equal(host(t["bytes"]), codes)
+                assert np.array_equal(host(t["scales"]), o.csf_encode(raw, n // 128, 128))
+
+
 def test_materialize_training_weights_for_all_slots():
     # deferred finish, then one launch that quantises every slot's cached y with its schedule_amax
     rng = np.random.default_rng(41)
