@@ -827,8 +827,11 @@ __device__ __forceinline__ void encode_finish(const EncodeRaw<MODE> &r, float be
                                               uint32_t csf_k, uint32_t csf_rows, uint32_t csf_magic,
                                               const SymExpLin sx) {
     // Each warp owns 32 consecutive groups = 2048 contiguous bytes.  It has read them with four
-    // fully coalesced 128-bit loads per lane; it parks them in shared memory (16-byte slots XOR-ed
-    // with the group number so neither side conflicts) and every lane picks up its own group.
+    // fully coalesced 128-bit loads per lane; it parks them in shared memory and every lane picks
+    // up its own group.  A 128-bit access is served a quarter-warp at a time, and a group's four
+    // 16-byte slots cover half of the 32 banks, so slot k of group g sits at k ^ ((g >> 1) & 3):
+    // eight consecutive lanes then touch eight different bank quads on the read side (lanes =
+    // groups) as well as on the write side (lanes = two groups x four slots).
     __shared__ float4 stage[THREADS / 32][128];
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
@@ -848,12 +851,12 @@ __device__ __forceinline__ void encode_finish(const EncodeRaw<MODE> &r, float be
             t.w = symexp_forward(zv.w + beta * (xv.w - zv.w), sx);
         }
         const uint32_t g = f4 >> 2, k = f4 & 3;
-        stage[warp][g * 4 + (k ^ (g & 3))] = t;
+        stage[warp][g * 4 + (k ^ ((g >> 1) & 3))] = t;
     }
     __syncwarp();
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
-        const float4 t = stage[warp][lane * 4 + (k ^ (lane & 3))];
+        const float4 t = stage[warp][lane * 4 + (k ^ ((lane >> 1) & 3))];
         v[4 * k] = t.x; v[4 * k + 1] = t.y; v[4 * k + 2] = t.z; v[4 * k + 3] = t.w;
     }
     __syncwarp();
