@@ -331,6 +331,14 @@ int b2_adamw_table_prepare(b2_adamw_slot_descriptor *host_table, uint32_t count,
 /* Hyper-parameters are taken from `scalars` (pointer fields and len are ignored). */
 int b2_apply_adamw_update_multi(const b2_adamw_slot_descriptor *d_table, uint32_t count, uint32_t total_chunks,
                                 const b2_adamw_update_args *scalars, void *stream);
+/* The same update with the same results, launched as ONE 128-thread CTA per SM: small enough to
+ * be resident beside a Newton-Schulz GEMM CTA (which leaves 10,240 registers and under 2 KB of
+ * shared memory free on its SM).  Enqueue it on a second stream while b2_muon_polar runs on the
+ * first and the AdamW tensors stream through HBM while the tensor cores work out of L2; join the
+ * two streams with an event before anything reads the results.  On its own it is slower than
+ * b2_apply_adamw_update_multi. */
+int b2_apply_adamw_update_multi_beside(const b2_adamw_slot_descriptor *d_table, uint32_t count,
+                                       uint32_t total_chunks, const b2_adamw_update_args *scalars, void *stream);
 /* `Materializer::adam` for every mode-1 entry of the table at once
  * (src/training/schedule_free/tensor.rs:71-89): quantises the schedule-free values with the max|y|
  * the deferred update left in `amax` into bytes / scales / global_scale.  values_cached != 0 reads

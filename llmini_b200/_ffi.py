@@ -138,6 +138,7 @@ def _declare(L: C.CDLL) -> None:
         "b2_clip_gradients": (i, [C.POINTER(GradientClipArgs), vp]),
         "b2_adamw_table_prepare": (i, [C.POINTER(AdamWSlotDescriptor), u32, u32p]),
         "b2_apply_adamw_update_multi": (i, [vp, u32, u32, C.POINTER(AdamWUpdateArgs), vp]),
+        "b2_apply_adamw_update_multi_beside": (i, [vp, u32, u32, C.POINTER(AdamWUpdateArgs), vp]),
         "b2_adamw_materialize_training_weights": (i, [vp, u32, u32, C.c_float, C.c_int, vp]),
         "b2_muon_materialize_training_weights": (i, [vp, vp, vp]),
         "b2_csf_encoded_len": (sz, [sz, sz]),

@@ -834,7 +834,15 @@ int b2_apply_adamw_update_multi(const b2_adamw_slot_descriptor *d_table, uint32_
     DeviceInfo d;
     cudaError_t e = device_info(d);
     if (e != cudaSuccess) return (int)e;
-    return (int)launch_adamw_multi(d_table, count, total_chunks, *scalars, stream_grid_cap(d), as_stream(stream));
+    return (int)launch_adamw_multi(d_table, count, total_chunks, *scalars, stream_grid_cap(d), false, as_stream(stream));
+}
+int b2_apply_adamw_update_multi_beside(const b2_adamw_slot_descriptor *d_table, uint32_t count, uint32_t total_chunks,
+                                       const b2_adamw_update_args *scalars, void *stream) {
+    if (!scalars || (!d_table && count)) return B2_ERROR_INVALID_VALUE;
+    DeviceInfo d;
+    cudaError_t e = device_info(d);
+    if (e != cudaSuccess) return (int)e;
+    return (int)launch_adamw_multi(d_table, count, total_chunks, *scalars, stream_grid_cap(d), true, as_stream(stream));
 }
 int b2_adamw_materialize_training_weights(const b2_adamw_slot_descriptor *d_table, uint32_t count,
                                           uint32_t total_chunks, float schedule_beta, int values_cached,

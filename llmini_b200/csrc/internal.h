@@ -88,7 +88,7 @@ cudaError_t launch_schedule_free_amax(const float *z, const float *x, float beta
 cudaError_t launch_adamw(const b2_adamw_update_args &a, int mode, int grid_cap,
                          cudaStream_t s);
 cudaError_t launch_adamw_multi(const b2_adamw_slot_descriptor *table, uint32_t count, uint32_t total_chunks,
-                              const b2_adamw_update_args &scalars, int grid_cap, cudaStream_t s);
+                              const b2_adamw_update_args &scalars, int grid_cap, bool beside, cudaStream_t s);
 cudaError_t launch_adamw_multi_materialize(const b2_adamw_slot_descriptor *table, uint32_t count,
                                           uint32_t total_chunks, float beta, bool cached, int grid_cap,
                                           cudaStream_t s);
