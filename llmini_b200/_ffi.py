@@ -114,6 +114,7 @@ def _declare(L: C.CDLL) -> None:
         "b2_muon_polar": (i, [vp, C.POINTER(MuonStepArgs), vp]),
         "b2_muon_finish_update": (i, [vp, vp, C.POINTER(MuonStepArgs), vp]),
         "b2_muon_finish_update_deferred_quantization": (i, [vp, vp, C.POINTER(MuonStepArgs), vp]),
+        "b2_muon_finish_update_deferred_quantization_beside": (i, [vp, vp, C.POINTER(MuonStepArgs), vp]),
         "b2_muon_finish_hyperball_update_deferred_quantization": (i, [vp, vp, C.POINTER(MuonStepArgs), C.c_uint32, vp]),
         "b2_muon_sign_update_deferred_quantization": (i, [vp, vp, C.POINTER(MuonStepArgs), vp]),
         "b2_nvfp4_sm100_scales_bytes": (C.c_size_t, [C.c_uint32, C.c_uint32]),
@@ -141,6 +142,7 @@ def _declare(L: C.CDLL) -> None:
         "b2_apply_adamw_update_multi_beside": (i, [vp, u32, u32, C.POINTER(AdamWUpdateArgs), vp]),
         "b2_adamw_materialize_training_weights": (i, [vp, u32, u32, C.c_float, C.c_int, vp]),
         "b2_muon_materialize_training_weights": (i, [vp, vp, vp]),
+        "b2_muon_materialize_master_weights": (i, [vp, vp, vp]),
         "b2_csf_encoded_len": (sz, [sz, sz]),
         "b2_csf_encode_host": (sz, [u8p, sz, sz, sz, u8p, sz]),
         "b2_csf_scale_at": (C.c_uint8, [u8p, sz]),

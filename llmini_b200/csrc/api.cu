@@ -605,6 +605,22 @@ int b2_muon_finish_update_deferred_quantization(b2_muon_plan *plan, const b2_muo
     return finish_impl(plan, d_slots, a, false, stream);
 }
 
+int b2_muon_finish_update_deferred_quantization_beside(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_slots,
+                                                       const b2_muon_step_args *a, void *stream) {
+    if (!plan || !a || !d_slots) return B2_ERROR_INVALID_VALUE;
+    if (a->normuon) return B2_ERROR_INVALID_VALUE;
+    const Layout &L = plan->layout;
+    SlotView v = plan->view(d_slots);
+    return (int)launch_muon_update_beside(v, plan->at<uint64_t>(L.off_u_ptrs), plan->at<float>(L.off_amax_x),
+                                          update_params(a), as_stream(stream));
+}
+int b2_muon_materialize_master_weights(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_slots, void *stream) {
+    if (!plan || !d_slots) return B2_ERROR_INVALID_VALUE;
+    SlotView v = plan->view(d_slots);
+    return (int)launch_muon_encode(v, plan->at<float>(plan->layout.off_amax_x), 0, (int)plan->options.scale_layout,
+                                   as_stream(stream));
+}
+
 int b2_muon_finish_hyperball_update_deferred_quantization(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_slots,
                                                           const b2_muon_step_args *a, uint32_t use_schedule_free,
                                                           void *stream) {

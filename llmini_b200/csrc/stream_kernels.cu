@@ -373,8 +373,11 @@ __device__ __forceinline__ void update_chunk(const ChunkCtx &cx, const uint64_t 
     }
 }
 
-template <int EXT>
-__global__ void __launch_bounds__(kThreads, 5)
+// BESIDE: the form that runs next to the Newton-Schulz GEMMs of ANOTHER group of matrices on a
+// second stream.  256 threads x 40 registers is exactly what a GEMM CTA (576 threads x 96
+// registers) leaves of an SM's register file, so with one CTA per SM both kernels hold every SM.
+template <int EXT, bool BESIDE = false>
+__global__ void __launch_bounds__(kThreads, BESIDE ? 6 : 5)
 k_muon_update(const b2_muon_slot_descriptor *slots, const uint32_t *prefix, uint32_t slot_count,
               uint32_t total_chunks, const uint64_t *u_ptrs, float *amax_x, UpdateParams up) {
     __shared__ float warp_ax[kThreads / 32], warp_ay[kThreads / 32];
@@ -1552,6 +1555,18 @@ cudaError_t launch_muon_momentum_normalize(const SlotView &v, const MomentumPara
     else
         k_muon_momentum_normalize<0><<<clamp_grid(v.total_chunks, v.grid), kThreads, 0, s>>>(
             v.slots, v.chunk_prefix, v.slot_count, v.total_chunks, mp, inv_norm, x0_ptrs, f16);
+    return cudaGetLastError();
+}
+cudaError_t launch_muon_update_beside(const SlotView &v, const uint64_t *u_ptrs, float *amax_x, const UpdateParams &up,
+                                      cudaStream_t s) {
+    if (v.total_chunks == 0) return cudaSuccess;
+    if (up.normuon || up.d_qk_clip_factors || up.symexp_beta > 0.0f) return cudaErrorInvalidValue;
+    // the shared-memory split the GEMM asks for: kernels with different splits are not co-resident
+    static const cudaError_t carve = cudaFuncSetAttribute(k_muon_update<0, true>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                                          cudaSharedmemCarveoutMaxShared);
+    if (carve != cudaSuccess) return carve;
+    k_muon_update<0, true><<<clamp_grid(v.total_chunks, v.grid / 8), kThreads, 0, s>>>(
+        v.slots, v.chunk_prefix, v.slot_count, v.total_chunks, u_ptrs, amax_x, up);
     return cudaGetLastError();
 }
 cudaError_t launch_muon_update(const SlotView &v, const uint64_t *u_ptrs, float *amax_x, const UpdateParams &up,

@@ -221,11 +221,20 @@ class OptimizerModule:
 
     # launcher/muon_mega.rs:159-165
     def muon_tma_finish_update_deferred_quantization(self, plan: MuonPlan, slots: torch.Tensor,
-                                                     args: MuonMegaUpdateArgs) -> None:
+                                                     args: MuonMegaUpdateArgs, beside: bool = False) -> None:
+        """beside=True launches the form that fits on the SMs next to the Newton-Schulz GEMMs of
+        another plan (plain update only): call it on a second stream while that plan's
+        `muon_polar` runs on the first."""
         a, keep = args.c_args()
-        check(self._lib.b2_muon_finish_update_deferred_quantization(plan.handle, _ptr(slots), C.byref(a), _stream()),
-              "muon_finish_update_deferred_quantization")
+        fn = (self._lib.b2_muon_finish_update_deferred_quantization_beside if beside
+              else self._lib.b2_muon_finish_update_deferred_quantization)
+        check(fn(plan.handle, _ptr(slots), C.byref(a), _stream()), "muon_finish_update_deferred_quantization")
         del keep
+
+    # stages Q1 + Q2 of every matrix from x' and the max|x'| the last finish left in the plan
+    def muon_materialize_master_weights(self, plan: MuonPlan, slots: torch.Tensor) -> None:
+        check(self._lib.b2_muon_materialize_master_weights(plan.handle, _ptr(slots), _stream()),
+              "muon_materialize_master_weights")
 
     # launcher/muon_mega.rs:166-228
     def muon_tma_finish_hyperball_update_deferred_quantization(self, plan: MuonPlan, slots: torch.Tensor,

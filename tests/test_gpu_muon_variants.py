@@ -356,6 +356,52 @@ def test_fused_update_encode_equals_two_launches(target, ext):
         assert a[5].any() and a[4][0] > 0
 
 
+@pytest.mark.parametrize("beside", [False, True])
+def test_deferred_finish_then_master_materialise_equals_finish_update(beside):
+    # the split a caller uses to run the update of one group of matrices beside the Newton-Schulz
+    # GEMMs of another (beside = the launch form with one small CTA per SM): masters, y, maxima,
+    # tensor scales, codes and block scales bit for bit against the one-call finish
+    shapes = [(768, 768), (40, 48), (0, 0), (2304, 768), (128, 1040), (16, 16)]
+    results = []
+    for split in (False, True):
+        rng2 = np.random.default_rng(61)
+        slots = []
+        for k, (r, c) in enumerate(shapes):
+            n = r * c
+            s = b2.MuonSlot.allocate(r, c, b2.SCALES_RAW)
+            if n:
+                s.z_master.copy_(dev(U.weights(rng2, n)).view_as(s.z_master))
+                s.x_master.copy_(dev(U.weights(rng2, n)).view_as(s.x_master))
+            s.learning_rate_multiplier = 1.0 + 0.25 * k
+            slots.append(s)
+        plan = b2.MuonPlan(shapes, scale_layout=b2.SCALES_RAW)
+        table = b2.slot_table(slots)
+        opt = b2.OptimizerModule()
+        opt.muon_tma_prepare_polar(plan, table, b2.MuonMegaUpdateArgs(mu=1.0, grad_scale=0.0, iterations=1))
+        for k, (r, c) in enumerate(shapes):
+            if r * c:
+                plan.scratch(k, 1).copy_(dev((rng2.standard_normal(r * c) * 0.05).astype(F)).view(r, c))
+        args = b2.MuonMegaUpdateArgs(learning_rate=0.02, weight_decay=0.025, average_coefficient=0.3, schedule_beta=0.6)
+        if split:
+            opt.muon_tma_finish_update_deferred_quantization(plan, table, args, beside=beside)
+            opt.muon_materialize_master_weights(plan, table)
+        else:
+            opt.muon_tma_finish_update(plan, table, args)
+        torch.cuda.synchronize()
+        assert plan.status() == 0
+        out = []
+        for k, (s, (r, c)) in enumerate(zip(slots, shapes)):
+            if r * c:
+                out.append([host(t).copy() for t in (s.z_master, s.x_master, s.grad, s.schedule_amax, s.global_scale,
+                                                     s.bytes, s.scales)])
+        results.append(out)
+        plan.close()
+    for a, b in zip(*results):
+        for u, v in zip(a, b):
+            assert np.array_equal(u, v)
+        assert a[5].any() and a[4][0] > 0
+
+
 def _symexp(raw, beta, e=1.0, l=1.0, c=1.0):
     """SymExpLin forward (crates/cuda-kernels/src/gpt/optimizer/symexp_lin.rs:8-26) in float64."""
     raw = raw.astype(np.float64)
