@@ -302,70 +302,15 @@ def run_gpu(args):
             opt.muon_tma_finish_update(plan, table, margs)
         if record: marks[3].record(stream)
 
-    def step_gather():
-        if world > 1:
-            n = arena.bytes_per_rank
-            dist.all_gather_into_tensor(arena_v, arena_v[rank * n:(rank + 1) * n])
-
     def step_adam(record=False, marks=None):
         if adam_sets:
             opt.apply_adamw_update_multi(adam_table, adam_count, adam_chunks, **ADAM)
         if record: marks[4].record(stream)
-        step_gather()
+        if world > 1:
+            n = arena.bytes_per_rank
+            dist.all_gather_into_tensor(arena_v, arena_v[rank * n:(rank + 1) * n])
 
-    side_stream = torch.cuda.Stream(device=dev)
-    overlap = not args.no_overlap and plan is not None and bool(adam_sets)
-
-    def step_overlapped():
-        # AdamW touches none of the matrices, so it runs on a second stream BESIDE the Newton-Schulz
-        # GEMMs, in the launch form whose CTAs fit on the SMs next to the GEMM's: the tensor cores
-        # work out of L2 while the AdamW tensors stream through HBM.  Same calls, same results.
-        opt.muon_tma_prepare_polar(plan, table, margs)
-        side_stream.wait_stream(stream)
-        with torch.cuda.stream(side_stream):
-            opt.apply_adamw_update_multi(adam_table, adam_count, adam_chunks, beside=True, **ADAM)
-        opt.muon_polar(plan, margs)
-        opt.muon_tma_finish_update(plan, table, margs)
-        stream.wait_stream(side_stream)
-        step_gather()
-
-    # Two groups of matrices (two plans over the same slots): the update of group A runs beside the
-    # Newton-Schulz GEMMs of group B.
-    groups = None
-    if overlap and args.groups == 2 and len(slots) >= 2:
-        half = len(slots) // 2
-        groups = []
-        for part in (slice(0, half), slice(half, len(slots))):
-            groups.append((b2.MuonPlan(my_shapes[part], scale_layout=layout, device=dev, debug_flags=args.plan_flags),
-                           b2.slot_table(slots[part], dev)))
-
-    def step_two_groups():
-        (plan_a, table_a), (plan_b, table_b) = groups
-        opt.muon_tma_prepare_polar(plan_a, table_a, margs)
-        opt.muon_tma_prepare_polar(plan_b, table_b, margs)
-        side_stream.wait_stream(stream)
-        with torch.cuda.stream(side_stream):
-            opt.apply_adamw_update_multi(adam_table, adam_count, adam_chunks, beside=True, **ADAM)
-        opt.muon_polar(plan_a, margs)
-        side_stream.wait_stream(stream)
-        with torch.cuda.stream(side_stream):
-            opt.muon_tma_finish_update_deferred_quantization(plan_a, table_a, margs, beside=True)
-        opt.muon_polar(plan_b, margs)
-        opt.muon_tma_finish_update(plan_b, table_b, margs)
-        stream.wait_stream(side_stream)
-        opt.muon_materialize_master_weights(plan_a, table_a)
-        step_gather()
-
-    # The two-stream forms are used inside the captured graph only: replayed as a graph the small
-    # CTAs share the SMs with the GEMM CTAs; launched eagerly on two streams the same kernels took
-    # turns on the SMs instead (2.9 ms per step).
-    def step(record=False, two_streams=False):
-        if two_streams and groups is not None:
-            step_two_groups()
-            return
-        if two_streams and overlap:
-            step_overlapped()
-            return
+    def step(record=False):
         marks = [ev() for _ in range(5)] if record else None
         step_muon(record, marks)
         step_adam(record, marks)
@@ -393,8 +338,6 @@ def run_gpu(args):
 
     for _ in range(max(args.warmup, 3)):
         step()
-    if overlap and not args.no_graph:
-        step(two_streams=True)   # every kernel of the captured form has run once before the capture
     barrier()
     if plan is not None and plan.status() != 0:
         raise SystemExit("a bounded device-side wait ran out during warm-up")
@@ -407,14 +350,53 @@ def run_gpu(args):
     # CUDA graph and replayed: the headline number is the replay, the per-stage breakdown (and
     # the roofline figure) comes from the eager pass above, whose events sit between stages.
     graph = graph_muon = graph_adam = None
+    modes_match = None
     ms_step = ms_eager
     if not args.no_graph:
         try:
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
-                step(two_streams=True)
+                step()
             graph.replay()
             ms_step = timed(graph.replay, args.steps)
+            # the replayed step against the same calls launched one by one, from the same state: every
+            # master, moment, cached y, code, scale byte and tensor scale bit for bit (a capture that
+            # silently left work out would show here)
+            state, names = [], []
+            for i_, s_ in enumerate(slots):
+                for k in ("grad", "momentum", "z_master", "x_master", "schedule_amax"):
+                    state.append(getattr(s_, k))
+                    names.append(f"matrix {i_} {k}")
+            for i_, (_, t_) in enumerate(adam_sets):
+                for k in ("z_master", "x_master", "grad", "first_moment", "second_moment", "amax", "bytes", "scales",
+                          "global_scale"):
+                    if k in t_:
+                        state.append(t_[k])
+                        names.append(f"adamw tensor {i_} {k}")
+            state.append(arena_t)
+            names.append("arena of codes, scales and tensor scales")
+            if sum(t_.numel() * t_.element_size() for t_ in state) <= (8 << 30):   # three copies are held
+                saved = [t_.clone() for t_ in state]
+
+                def outcome(run):
+                    for t_, s_ in zip(state, saved):
+                        t_.copy_(s_)
+                    run()
+                    barrier()
+                    return [t_.clone() for t_ in state]
+
+                first, second = outcome(step), outcome(graph.replay)
+                differing = [n_ for n_, a_, b_ in zip(names, first, second) if not torch.equal(a_, b_)]
+                changed = sum(int(not torch.equal(a_, s_)) for a_, s_ in zip(second, saved))
+                modes_match = not differing and changed > 0
+                if world > 1:
+                    flag = torch.tensor([int(modes_match)], device=dev)
+                    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+                    modes_match = bool(flag.item())
+                del saved, first, second
+                if not modes_match:
+                    raise SystemExit("the replayed step and the eagerly launched step disagree in: "
+                                     + "; ".join(differing[:12]) + f" ({len(differing)} tensors)")
             # the two halves on their own, for the pipelined end-to-end step below
             graph_muon, graph_adam = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph_muon):
@@ -482,7 +464,7 @@ def run_gpu(args):
     step_e2e()
     ms_e2e = timed(step_e2e, args.steps)
     clocks = sampler.stop() if rank == 0 else None
-    if any(p.status() != 0 for p in ([plan] if plan is not None else []) + [g[0] for g in (groups or [])]):
+    if plan is not None and plan.status() != 0:
         raise SystemExit("a bounded device-side wait ran out during the timed region")
 
     # ---- per-stage device times (this rank) ----
@@ -542,10 +524,7 @@ def run_gpu(args):
         "clocks": clocks,
         "eager_ms_per_step": ms_eager,
         "cuda_graph": graph is not None,
-        # the timed step runs AdamW on a second stream beside the Newton-Schulz GEMMs; the per-stage
-        # figures above come from the eager pass, where the stages run one after another
-        "adamw_beside_newton_schulz": bool(overlap and graph is not None),
-        "matrix_groups": 2 if (groups is not None and graph is not None) else 1,
+        "replayed_step_matches_eager": modes_match,
     }
     if world == 1 and not args.no_cpu:
         os.environ.setdefault("OMP_NUM_THREADS", str(os.cpu_count() or 1))
@@ -723,45 +702,6 @@ def run_extras(args):
         gbs = n_el * bpe / (ms * 1e-3) / 1e9
         print(json.dumps({"extra": name, "workload": args.workload, "elements": n_el, "ms": ms, "bytes_per_element": bpe,
                           "gbs": gbs, "frac_of_measured_hbm": gbs / peaks["hbm"], "status": plan.status()}), flush=True)
-    if not args.only or args.only in "beside":
-        # how fast the beside launch forms move their bytes while the Newton-Schulz GEMMs hold the SMs:
-        # GEMMs on the current stream, the beside kernel on a second one, timed by events on that stream
-        cur, side = torch.cuda.current_stream(), torch.cuda.Stream()
-        a5 = A(coefficients=co5, **base)
-        beside_cases = [
-            ("nothing beside the Newton-Schulz GEMMs (the harness alone)", 0.0, lambda: None),
-            ("AdamW (deferred, embeddings) beside the Newton-Schulz GEMMs", 40.0 * emb_el,
-             lambda: opt.apply_adamw_update_multi(emb_table, emb_count, emb_chunks, beside=True, **adam_hp)),
-            ("Muon finish (deferred) beside the Newton-Schulz GEMMs", 24.0 * n_el,
-             lambda: opt.muon_tma_finish_update_deferred_quantization(plan, table, A(**base), beside=True)),
-        ]
-        for name, nbytes, fn in beside_cases:
-            for gemm_first in (False, True):
-                times, ns_times = [], []
-                for rep in range(6):
-                    e0, e1, m0, m1 = (torch.cuda.Event(enable_timing=True) for _ in range(4))
-                    torch.cuda.synchronize()
-                    m0.record(cur)
-                    side.wait_stream(cur)
-                    if gemm_first:
-                        opt.muon_polar(plan, a5)
-                        m1.record(cur)
-                    with torch.cuda.stream(side):
-                        e0.record(side)
-                        fn()
-                        e1.record(side)
-                    if not gemm_first:
-                        opt.muon_polar(plan, a5)
-                        m1.record(cur)
-                    cur.wait_stream(side)
-                    torch.cuda.synchronize()
-                    if rep >= 2:
-                        times.append(e0.elapsed_time(e1))
-                        ns_times.append(m0.elapsed_time(m1))
-                ms, ns_ms = float(np.median(times)), float(np.median(ns_times))
-                print(json.dumps({"extra": name + (" (GEMMs enqueued first)" if gemm_first else " (enqueued first)"),
-                                  "workload": args.workload, "ms": ms, "gbs": nbytes / (ms * 1e-3) / 1e9,
-                                  "newton_schulz_ms_meanwhile": ns_ms, "status": plan.status()}), flush=True)
     plan.close()
 
 
@@ -780,11 +720,6 @@ def main():
     ap.add_argument("--sweep", action="store_true", help="update+quantise bandwidth sweep over [R, 4096] tensors")
     ap.add_argument("--extras", action="store_true",
                     help="time the entry points beside the headline step (variants, clip, materialisation, converter)")
-    ap.add_argument("--no-overlap", action="store_true",
-                    help="run AdamW after the Muon stages instead of beside the Newton-Schulz GEMMs")
-    ap.add_argument("--groups", type=int, default=1, choices=(1, 2),
-                    help="2 = split the matrices into two plans and run the update of the first beside the "
-                         "Newton-Schulz GEMMs of the second")
     ap.add_argument("--only", default="", help="with --extras: run only the cases whose name contains this text")
     args = ap.parse_args()
     if args.sweep:

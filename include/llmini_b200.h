@@ -331,15 +331,6 @@ int b2_adamw_table_prepare(b2_adamw_slot_descriptor *host_table, uint32_t count,
 /* Hyper-parameters are taken from `scalars` (pointer fields and len are ignored). */
 int b2_apply_adamw_update_multi(const b2_adamw_slot_descriptor *d_table, uint32_t count, uint32_t total_chunks,
                                 const b2_adamw_update_args *scalars, void *stream);
-/* The same update with the same results, launched as ONE 128-thread CTA per SM: small enough to
- * be resident beside a Newton-Schulz GEMM CTA (which leaves 10,240 registers and under 2 KB of
- * shared memory free on its SM).  Enqueue it on a second stream while b2_muon_polar runs on the
- * first and the AdamW tensors stream through HBM while the tensor cores work out of L2; join the
- * two streams with an event before anything reads the results.  Measured inside a captured CUDA
- * graph; launched eagerly on two streams the two kernels took turns on the SMs instead.  On its
- * own it is slower than b2_apply_adamw_update_multi. */
-int b2_apply_adamw_update_multi_beside(const b2_adamw_slot_descriptor *d_table, uint32_t count,
-                                       uint32_t total_chunks, const b2_adamw_update_args *scalars, void *stream);
 /* `Materializer::adam` for every mode-1 entry of the table at once
  * (src/training/schedule_free/tensor.rs:71-89): quantises the schedule-free values with the max|y|
  * the deferred update left in `amax` into bytes / scales / global_scale.  values_cached != 0 reads
@@ -349,13 +340,6 @@ int b2_apply_adamw_update_multi_beside(const b2_adamw_slot_descriptor *d_table, 
 int b2_adamw_materialize_training_weights(const b2_adamw_slot_descriptor *d_table, uint32_t count,
                                           uint32_t total_chunks, float schedule_beta, int values_cached,
                                           void *stream);
-/* The deferred finish (plain update only: no NorMuon, qk-clip or SymExpLin) in the launch form that
- * fits beside the Newton-Schulz GEMMs of ANOTHER plan: one CTA of 256 threads x 40 registers per
- * SM, which is what a GEMM CTA leaves free.  With the matrices split over two plans, enqueue this
- * for plan A on a second stream while b2_muon_polar of plan B runs on the first.  Same results as
- * b2_muon_finish_update_deferred_quantization; on its own it is slower. */
-int b2_muon_finish_update_deferred_quantization_beside(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_slots,
-                                                       const b2_muon_step_args *args, void *stream);
 /* Stages Q1 + Q2 for every matrix of the plan from the masters x' and the max|x'| the last finish of
  * this plan left in the workspace: a deferred finish followed by this call writes what
  * b2_muon_finish_update writes (crates/cuda-kernels/src/gpt/optimizer/muon/fused/quant/encode.rs:13-60). */

@@ -114,7 +114,6 @@ def _declare(L: C.CDLL) -> None:
         "b2_muon_polar": (i, [vp, C.POINTER(MuonStepArgs), vp]),
         "b2_muon_finish_update": (i, [vp, vp, C.POINTER(MuonStepArgs), vp]),
         "b2_muon_finish_update_deferred_quantization": (i, [vp, vp, C.POINTER(MuonStepArgs), vp]),
-        "b2_muon_finish_update_deferred_quantization_beside": (i, [vp, vp, C.POINTER(MuonStepArgs), vp]),
         "b2_muon_finish_hyperball_update_deferred_quantization": (i, [vp, vp, C.POINTER(MuonStepArgs), C.c_uint32, vp]),
         "b2_muon_sign_update_deferred_quantization": (i, [vp, vp, C.POINTER(MuonStepArgs), vp]),
         "b2_nvfp4_sm100_scales_bytes": (C.c_size_t, [C.c_uint32, C.c_uint32]),
@@ -139,7 +138,6 @@ def _declare(L: C.CDLL) -> None:
         "b2_clip_gradients": (i, [C.POINTER(GradientClipArgs), vp]),
         "b2_adamw_table_prepare": (i, [C.POINTER(AdamWSlotDescriptor), u32, u32p]),
         "b2_apply_adamw_update_multi": (i, [vp, u32, u32, C.POINTER(AdamWUpdateArgs), vp]),
-        "b2_apply_adamw_update_multi_beside": (i, [vp, u32, u32, C.POINTER(AdamWUpdateArgs), vp]),
         "b2_adamw_materialize_training_weights": (i, [vp, u32, u32, C.c_float, C.c_int, vp]),
         "b2_muon_materialize_training_weights": (i, [vp, vp, vp]),
         "b2_muon_materialize_master_weights": (i, [vp, vp, vp]),

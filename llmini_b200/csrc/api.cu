@@ -605,15 +605,6 @@ int b2_muon_finish_update_deferred_quantization(b2_muon_plan *plan, const b2_muo
     return finish_impl(plan, d_slots, a, false, stream);
 }
 
-int b2_muon_finish_update_deferred_quantization_beside(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_slots,
-                                                       const b2_muon_step_args *a, void *stream) {
-    if (!plan || !a || !d_slots) return B2_ERROR_INVALID_VALUE;
-    if (a->normuon) return B2_ERROR_INVALID_VALUE;
-    const Layout &L = plan->layout;
-    SlotView v = plan->view(d_slots);
-    return (int)launch_muon_update_beside(v, plan->at<uint64_t>(L.off_u_ptrs), plan->at<float>(L.off_amax_x),
-                                          update_params(a), as_stream(stream));
-}
 int b2_muon_materialize_master_weights(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_slots, void *stream) {
     if (!plan || !d_slots) return B2_ERROR_INVALID_VALUE;
     SlotView v = plan->view(d_slots);
@@ -850,15 +841,7 @@ int b2_apply_adamw_update_multi(const b2_adamw_slot_descriptor *d_table, uint32_
     DeviceInfo d;
     cudaError_t e = device_info(d);
     if (e != cudaSuccess) return (int)e;
-    return (int)launch_adamw_multi(d_table, count, total_chunks, *scalars, stream_grid_cap(d), false, as_stream(stream));
-}
-int b2_apply_adamw_update_multi_beside(const b2_adamw_slot_descriptor *d_table, uint32_t count, uint32_t total_chunks,
-                                       const b2_adamw_update_args *scalars, void *stream) {
-    if (!scalars || (!d_table && count)) return B2_ERROR_INVALID_VALUE;
-    DeviceInfo d;
-    cudaError_t e = device_info(d);
-    if (e != cudaSuccess) return (int)e;
-    return (int)launch_adamw_multi(d_table, count, total_chunks, *scalars, stream_grid_cap(d), true, as_stream(stream));
+    return (int)launch_adamw_multi(d_table, count, total_chunks, *scalars, stream_grid_cap(d), as_stream(stream));
 }
 int b2_adamw_materialize_training_weights(const b2_adamw_slot_descriptor *d_table, uint32_t count,
                                           uint32_t total_chunks, float schedule_beta, int values_cached,

@@ -51,8 +51,6 @@ cudaError_t launch_muon_momentum_normalize(const SlotView &v, const MomentumPara
                                            const uint64_t *x0_ptrs, int f16, cudaStream_t s);
 cudaError_t launch_muon_update(const SlotView &v, const uint64_t *u_ptrs, float *amax_x, const UpdateParams &up,
                                cudaStream_t s);
-cudaError_t launch_muon_update_beside(const SlotView &v, const uint64_t *u_ptrs, float *amax_x, const UpdateParams &up,
-                               cudaStream_t s);
 // Stages U and Q in one launch over an item list (bit 31: encode span of B2_FUSED_ENCODE_SPAN chunks, else update
 // chunk; low bits: flat chunk index).  `sync` is fused_sync_bytes(slot_count) of device scratch,
 // zeroed once by the owner; every launch leaves it zeroed again.
@@ -90,7 +88,7 @@ cudaError_t launch_schedule_free_amax(const float *z, const float *x, float beta
 cudaError_t launch_adamw(const b2_adamw_update_args &a, int mode, int grid_cap,
                          cudaStream_t s);
 cudaError_t launch_adamw_multi(const b2_adamw_slot_descriptor *table, uint32_t count, uint32_t total_chunks,
-                              const b2_adamw_update_args &scalars, int grid_cap, bool beside, cudaStream_t s);
+                              const b2_adamw_update_args &scalars, int grid_cap, cudaStream_t s);
 cudaError_t launch_adamw_multi_materialize(const b2_adamw_slot_descriptor *table, uint32_t count,
                                           uint32_t total_chunks, float beta, bool cached, int grid_cap,
                                           cudaStream_t s);

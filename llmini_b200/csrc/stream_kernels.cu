@@ -373,11 +373,8 @@ __device__ __forceinline__ void update_chunk(const ChunkCtx &cx, const uint64_t 
     }
 }
 
-// BESIDE: the form that runs next to the Newton-Schulz GEMMs of ANOTHER group of matrices on a
-// second stream.  256 threads x 40 registers is exactly what a GEMM CTA (576 threads x 96
-// registers) leaves of an SM's register file, so with one CTA per SM both kernels hold every SM.
-template <int EXT, bool BESIDE = false>
-__global__ void __launch_bounds__(kThreads, BESIDE ? 6 : 5)
+template <int EXT>
+__global__ void __launch_bounds__(kThreads, 5)
 k_muon_update(const b2_muon_slot_descriptor *slots, const uint32_t *prefix, uint32_t slot_count,
               uint32_t total_chunks, const uint64_t *u_ptrs, float *amax_x, UpdateParams up) {
     __shared__ float warp_ax[kThreads / 32], warp_ay[kThreads / 32];
@@ -1306,16 +1303,10 @@ __global__ void k_adamw_multi_reset(const b2_adamw_slot_descriptor *t, uint32_t 
     uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < count && t[i].mode != 0 && t[i].len != 0) *reinterpret_cast<float *>(t[i].amax) = 0.0f;
 }
-// THREADS = 256 is the stand-alone form.  THREADS = 128 is the form that runs BESIDE the
-// Newton-Schulz GEMMs when the caller enqueues it on a second stream: one CTA of 128 threads x 64
-// registers and a few bytes of shared memory per SM is what a GEMM CTA (576 threads x 96 registers,
-// 225 KB) leaves free, so the two kernels share every SM and this one streams through HBM while the
-// tensor cores work out of L2.
-template <int THREADS>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(kThreads)
 k_adamw_multi(const b2_adamw_slot_descriptor *t, uint32_t count, uint32_t total_chunks, AdamScalars a,
               const float *d_grad_scale) {
-    __shared__ float warp_part[THREADS / 32];
+    __shared__ float warp_part[kThreads / 32];
     const int tid = threadIdx.x;
     if (d_grad_scale) a.grad_scale = __ldg(d_grad_scale);
     const float decay = 1.0f - a.lr * a.wd;
@@ -1328,11 +1319,9 @@ k_adamw_multi(const b2_adamw_slot_descriptor *t, uint32_t count, uint32_t total_
         const uint32_t base = (c - d.chunk_begin) * kChunk;
         float am = 0.0f;
         const bool aligned = ((d.z_master | d.x_master | d.grad | d.first_moment | d.second_moment) & 15) == 0;
-#pragma unroll 1
-        for (int hh = 0; hh < kChunk / (THREADS * 8); ++hh) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-            const uint32_t i = base + (2 * hh + h) * (THREADS * 4) + tid * 4;
+            const uint32_t i = base + h * (kChunk / 2) + tid * 4;
             if (aligned && i + 4 <= d.len) {
                 float4 zv = ld_stream(z + i), xv = ld_stream(x + i), gv = ld_stream(grad + i);
                 float4 av = ld_stream(m1 + i), bv = ld_stream(m2 + i);
@@ -1365,14 +1354,13 @@ k_adamw_multi(const b2_adamw_slot_descriptor *t, uint32_t count, uint32_t total_
                 }
             }
         }
-        }
         am = warp_max(am);
         if ((tid & 31) == 0) warp_part[tid >> 5] = am;
         __syncthreads();
         if (tid == 0 && d.mode != 0) {
             float r = 0.0f;
 #pragma unroll
-            for (int w = 0; w < THREADS / 32; ++w) r = fmaxf(r, warp_part[w]);
+            for (int w = 0; w < kThreads / 32; ++w) r = fmaxf(r, warp_part[w]);
             atomic_max_nonneg(reinterpret_cast<float *>(d.amax), r);
         }
         __syncthreads();
@@ -1555,18 +1543,6 @@ cudaError_t launch_muon_momentum_normalize(const SlotView &v, const MomentumPara
     else
         k_muon_momentum_normalize<0><<<clamp_grid(v.total_chunks, v.grid), kThreads, 0, s>>>(
             v.slots, v.chunk_prefix, v.slot_count, v.total_chunks, mp, inv_norm, x0_ptrs, f16);
-    return cudaGetLastError();
-}
-cudaError_t launch_muon_update_beside(const SlotView &v, const uint64_t *u_ptrs, float *amax_x, const UpdateParams &up,
-                                      cudaStream_t s) {
-    if (v.total_chunks == 0) return cudaSuccess;
-    if (up.normuon || up.d_qk_clip_factors || up.symexp_beta > 0.0f) return cudaErrorInvalidValue;
-    // the shared-memory split the GEMM asks for: kernels with different splits are not co-resident
-    static const cudaError_t carve = cudaFuncSetAttribute(k_muon_update<0, true>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                                          cudaSharedmemCarveoutMaxShared);
-    if (carve != cudaSuccess) return carve;
-    k_muon_update<0, true><<<clamp_grid(v.total_chunks, v.grid / 8), kThreads, 0, s>>>(
-        v.slots, v.chunk_prefix, v.slot_count, v.total_chunks, u_ptrs, amax_x, up);
     return cudaGetLastError();
 }
 cudaError_t launch_muon_update(const SlotView &v, const uint64_t *u_ptrs, float *amax_x, const UpdateParams &up,
@@ -1783,30 +1759,13 @@ cudaError_t launch_adamw(const b2_adamw_update_args &a, int mode, int grid_cap,
     return cudaGetLastError();
 }
 cudaError_t launch_adamw_multi(const b2_adamw_slot_descriptor *table, uint32_t count, uint32_t total_chunks,
-                              const b2_adamw_update_args &a, int grid_cap, bool beside, cudaStream_t s) {
+                              const b2_adamw_update_args &a, int grid_cap, cudaStream_t s) {
     if (count == 0 || total_chunks == 0) return cudaSuccess;
     AdamScalars sc{a.grad_scale, a.learning_rate, a.weight_decay, a.beta1, a.beta2,
                    a.beta1_correction, a.beta2_correction, a.eps, a.average_coefficient, a.schedule_beta};
     k_adamw_multi_reset<<<(count + 255) / 256, 256, 0, s>>>(table, count);
-    if (beside) {
-        // one small CTA per SM, and the shared-memory split the GEMM asks for: two kernels with
-        // different splits cannot be resident on one SM
-        static const cudaError_t carve = [] {
-            cudaError_t e = cudaFuncSetAttribute(k_adamw_multi<128>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                                 cudaSharedmemCarveoutMaxShared);
-            if (e == cudaSuccess)
-                e = cudaFuncSetAttribute(k_adamw_multi_encode, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                         cudaSharedmemCarveoutMaxShared);
-            return e;
-        }();
-        if (carve != cudaSuccess) return carve;
-        const int sms = grid_cap / 8;
-        k_adamw_multi<128><<<clamp_grid(total_chunks, sms), 128, 0, s>>>(table, count, total_chunks, sc, a.d_grad_scale);
-        k_adamw_multi_encode<<<clamp_grid(total_chunks, sms), kEncodeThreads, 0, s>>>(table, count, total_chunks);
-    } else {
-        k_adamw_multi<kThreads><<<clamp_grid(total_chunks, grid_cap), kThreads, 0, s>>>(table, count, total_chunks, sc, a.d_grad_scale);
-        k_adamw_multi_encode<<<encode_grid(k_adamw_multi_encode, total_chunks, grid_cap), kEncodeThreads, 0, s>>>(table, count, total_chunks);
-    }
+    k_adamw_multi<<<clamp_grid(total_chunks, grid_cap), kThreads, 0, s>>>(table, count, total_chunks, sc, a.d_grad_scale);
+    k_adamw_multi_encode<<<encode_grid(k_adamw_multi_encode, total_chunks, grid_cap), kEncodeThreads, 0, s>>>(table, count, total_chunks);
     return cudaGetLastError();
 }
 cudaError_t launch_adamw_multi_materialize(const b2_adamw_slot_descriptor *table, uint32_t count,

@@ -221,14 +221,10 @@ class OptimizerModule:
 
     # launcher/muon_mega.rs:159-165
     def muon_tma_finish_update_deferred_quantization(self, plan: MuonPlan, slots: torch.Tensor,
-                                                     args: MuonMegaUpdateArgs, beside: bool = False) -> None:
-        """beside=True launches the form that fits on the SMs next to the Newton-Schulz GEMMs of
-        another plan (plain update only): call it on a second stream while that plan's
-        `muon_polar` runs on the first."""
+                                                     args: MuonMegaUpdateArgs) -> None:
         a, keep = args.c_args()
-        fn = (self._lib.b2_muon_finish_update_deferred_quantization_beside if beside
-              else self._lib.b2_muon_finish_update_deferred_quantization)
-        check(fn(plan.handle, _ptr(slots), C.byref(a), _stream()), "muon_finish_update_deferred_quantization")
+        check(self._lib.b2_muon_finish_update_deferred_quantization(plan.handle, _ptr(slots), C.byref(a), _stream()),
+              "muon_finish_update_deferred_quantization")
         del keep
 
     # stages Q1 + Q2 of every matrix from x' and the max|x'| the last finish left in the plan
@@ -332,13 +328,10 @@ class OptimizerModule:
         host = np.frombuffer(bytes(arr), dtype=np.uint8).copy()
         return torch.from_numpy(host).to(device), n, int(total.value)
 
-    def apply_adamw_update_multi(self, table: torch.Tensor, count: int, total_chunks: int, beside: bool = False,
-                                 **scalars) -> None:
-        """beside=True launches the form that fits on the SMs next to the Newton-Schulz GEMMs (one
-        small CTA per SM): call it on a second stream while `muon_polar` runs on the first."""
+    def apply_adamw_update_multi(self, table: torch.Tensor, count: int, total_chunks: int, **scalars) -> None:
         a = self._adam_args(z_master=None, x_master=None, grad=None, first_moment=None, second_moment=None, len=0, **scalars)
-        fn = self._lib.b2_apply_adamw_update_multi_beside if beside else self._lib.b2_apply_adamw_update_multi
-        check(fn(_ptr(table), count, total_chunks, C.byref(a), _stream()), "apply_adamw_update_multi")
+        check(self._lib.b2_apply_adamw_update_multi(_ptr(table), count, total_chunks, C.byref(a), _stream()),
+              "apply_adamw_update_multi")
 
     # Materializer::adam for all deferred tensors of the table (src/training/schedule_free/tensor.rs:71-89)
     def adamw_materialize_training_weights(self, table: torch.Tensor, count: int, total_chunks: int,

@@ -356,11 +356,9 @@ def test_fused_update_encode_equals_two_launches(target, ext):
         assert a[5].any() and a[4][0] > 0
 
 
-@pytest.mark.parametrize("beside", [False, True])
-def test_deferred_finish_then_master_materialise_equals_finish_update(beside):
-    # the split a caller uses to run the update of one group of matrices beside the Newton-Schulz
-    # GEMMs of another (beside = the launch form with one small CTA per SM): masters, y, maxima,
-    # tensor scales, codes and block scales bit for bit against the one-call finish
+def test_deferred_finish_then_master_materialise_equals_finish_update():
+    # the deferred finish followed by the stand-alone encode of x' against the one-call finish:
+    # masters, y, maxima, tensor scales, codes and block scales bit for bit
     shapes = [(768, 768), (40, 48), (0, 0), (2304, 768), (128, 1040), (16, 16)]
     results = []
     for split in (False, True):
@@ -383,7 +381,7 @@ def test_deferred_finish_then_master_materialise_equals_finish_update(beside):
                 plan.scratch(k, 1).copy_(dev((rng2.standard_normal(r * c) * 0.05).astype(F)).view(r, c))
         args = b2.MuonMegaUpdateArgs(learning_rate=0.02, weight_decay=0.025, average_coefficient=0.3, schedule_beta=0.6)
         if split:
-            opt.muon_tma_finish_update_deferred_quantization(plan, table, args, beside=beside)
+            opt.muon_tma_finish_update_deferred_quantization(plan, table, args)
             opt.muon_materialize_master_weights(plan, table)
         else:
             opt.muon_tma_finish_update(plan, table, args)

@@ -324,9 +324,7 @@ def test_grad_clip_reference_case_and_device_scale():
     assert np.array_equal(results[1][0].ravel(), m2)
 
 
-@pytest.mark.parametrize("beside", [False, True])
-def test_multi_tensor_adamw_equals_per_tensor_calls(beside):
-    # beside = the launch form that fits next to the Newton-Schulz GEMM CTAs (128-thread CTAs, one per SM)
+def test_multi_tensor_adamw_equals_per_tensor_calls():
     rng = np.random.default_rng(31)
     opt = b2.OptimizerModule()
     specs = [(768, 0), (4099, 0), (16 * 301, 1), (128 * 40, 2), (2048 * 3, 2), (0, 0), (16, 1)]
@@ -353,7 +351,7 @@ def test_multi_tensor_adamw_equals_per_tensor_calls(beside):
     # whatever the caller left there (the reference clears it with zero_f32_pointer_table)
     a, b = make(7.0), make(0.0)
     table, count, chunks = opt.adamw_table(a)
-    opt.apply_adamw_update_multi(table, count, chunks, beside=beside, **hp)
+    opt.apply_adamw_update_multi(table, count, chunks, **hp)
     for t in b:
         if t["len"] == 0:
             continue
