@@ -17,6 +17,9 @@
  *    workspace (`b2_muon_workspace_bytes`).
  *  - No CPU fallback exists.  Without a CUDA device every compute entry point returns an
  *    error.
+ *  - Sizes: a tensor has at most 0xfffff000 elements (elements and 2048-value chunks are indexed in
+ *    32 bits) and a matrix at most 65535 * 128 rows or columns; larger arguments are refused with
+ *    B2_ERROR_INVALID_VALUE.
  */
 #ifndef LLMINI_B200_H
 #define LLMINI_B200_H
@@ -83,6 +86,13 @@ enum { B2_SCALES_CSF = 0, B2_SCALES_RAW = 1,
                               to 128 and scale columns to 4 (padding bytes are never written: zero the
                               buffer once).  Accepted by the Muon plan only */ };
 enum { B2_QUANTIZE_X = 0, B2_QUANTIZE_Y = 1 };
+/* Where the Frobenius normalisation of stage N is applied.
+ * B2_NORMALIZE_TWO_PASS: X0 = r16(u * s), the reference's rounding point
+ *   (crates/cuda-kernels/src/gpt/optimizer/muon/polar/fused/normalize.rs:91-145); the gradients are read twice.
+ * B2_NORMALIZE_DEFERRED: one pass over the gradients writes X0 = r16(u); s enters through the first
+ *   Newton-Schulz iteration, which is linear in it (G = s^2 X0 X0^T, X1 = s Q X0).  Same algebra, the operand
+ *   is rounded before instead of after the scaling; BF16 operands only. */
+enum { B2_NORMALIZE_TWO_PASS = 0, B2_NORMALIZE_DEFERRED = 1 };
 
 typedef struct b2_muon_options {
     uint32_t operand_format;  /* B2_OPERAND_*: 16-bit type the Newton-Schulz GEMM operands are
@@ -93,12 +103,11 @@ typedef struct b2_muon_options {
                                  .../muon/fused/body.rs:90-101); B2_QUANTIZE_Y: the
                                  schedule-free training weights y */
     uint32_t max_iterations;  /* upper bound on b2_muon_step_args.iterations (0 -> 5) */
-    uint32_t reserved[4];     /* [0]: GEMM tile override (0 = choose; 128 / 256 = one CTA per
-                                 128 x N tile; 512 = two-CTA 256 x 256 tiles);
-                                 [1], [2]: measurement-only knobs (phase mask; kernel flags: 1 / 8 drop
-                                 GEMM epilogue stores, 4 all tiles of symmetric outputs, 16 update and
-                                 encode as two launches, 32 no programmatic dependent launch),
-                                 leave 0; [3]: must be 0 */
+    uint32_t tile_override;   /* GEMM tile shape: 0 = choose; 128 / 256 = one CTA per 128 x N tile;
+                                 512 = two-CTA 256 x 256 tiles */
+    uint32_t measure_phase_mask; /* leave 0.  Read only by a library built with -DB2_MEASURE: which GEMMs of an */
+    uint32_t measure_flags;      /* iteration run, and kernel variants used to attribute time */
+    uint32_t normalize_mode;  /* B2_NORMALIZE_* */
 } b2_muon_options;
 
 /* Step scalars: `MuonMegaUpdateArgs` (.../optimizer/args/muon.rs:25-44) and
@@ -177,10 +186,6 @@ int b2_muon_finish_update(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_s
 int b2_muon_finish_update_deferred_quantization(b2_muon_plan *plan,
                                                 const b2_muon_slot_descriptor *d_slots,
                                                 const b2_muon_step_args *args, void *stream);
-/* `OptimizerModule::muon_tma_sign_update_deferred_quantization` (.../launcher/muon_mega.rs:229-283;
- * device code .../muon/fused/update/one.rs:88-167) for every slot of the plan: momentum (and
- * variance) update, z' = z (1 - lr wd) - lr sign(m'), x', y into the gradient buffer, both amax
- * words.  No Newton-Schulz, no quantisation. */
 /* `OptimizerModule::muon_tma_finish_hyperball_update_deferred_quantization`
  * (.../launcher/muon_mega.rs:166-228): NorMuon factors, then a step of relative size
  * learning_rate along the update followed by projection back onto the sphere of the matrix's
@@ -189,6 +194,10 @@ int b2_muon_finish_hyperball_update_deferred_quantization(b2_muon_plan *plan,
                                                           const b2_muon_slot_descriptor *d_slots,
                                                           const b2_muon_step_args *args,
                                                           uint32_t use_schedule_free, void *stream);
+/* `OptimizerModule::muon_tma_sign_update_deferred_quantization` (.../launcher/muon_mega.rs:229-283;
+ * device code .../muon/fused/update/one.rs:88-167) for every slot of the plan: momentum (and
+ * variance) update, z' = z (1 - lr wd) - lr sign(m'), x', y into the gradient buffer, both amax
+ * words.  No Newton-Schulz, no quantisation. */
 int b2_muon_sign_update_deferred_quantization(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_slots,
                                               const b2_muon_step_args *args, void *stream);
 /* Scratch views for tests and tracing (the reference's `MUON_TMA_TRACE`,
@@ -197,7 +206,9 @@ int b2_muon_sign_update_deferred_quantization(b2_muon_plan *plan, const b2_muon_
  * 3 = max|x'| (f32[1]), 4 = device status word (u32[1], plan-wide).
  * 5 = Gram (16-bit, [n][ld]) and 6 = polynomial Q (16-bit, [n][ld]) of the LAST iteration,
  * 7 = the second operand buffer X1, 8 = NorMuon factors (f32[max(rows, cols)]),
- * 9 = NorMuon / Hyperball slot scalars (f32[4]: normuon_scale, update_norm, radius, dot). */
+ * 9 = NorMuon / Hyperball slot scalars (f32[4]: normuon_scale, update_norm, radius, dot),
+ * 10 = the ticket, abort and completion words of the one-launch update + encode (u32[4 + slots], plan-wide;
+ * all zero between launches). */
 int b2_muon_plan_scratch(b2_muon_plan *plan, uint32_t slot, uint32_t which, void **d_ptr,
                          size_t *bytes);
 /* Reads back and clears the plan's device status word (synchronises `stream`): 0 when no
@@ -223,7 +234,6 @@ int b2_fp32_to_nvfp4_four_six(const float *d_x, const float *d_amax, uint8_t *d_
                               uint32_t group_count, uint32_t scale_layout, void *stream);
 
 /* ---- materialisation + AdamW (OptimizerModule) ------------------------------------- */
-/* `OptimizerModule::materialize_master` (.../optimizer/launcher/mod.rs:67-95). */
 /* No single counterpart in the reference, whose forward GEMMs run on sm_120a and repack scales with
  * crates/cuda-kernels/src/utils/nvfp4_tma_matmul/scale_pack.rs:29-175: size of, and conversion into,
  * the B2_SCALES_SM100 layout from a raw plane or CSF storage of a [rows][cols] tensor (cols % 16 == 0;
@@ -231,6 +241,8 @@ int b2_fp32_to_nvfp4_four_six(const float *d_x, const float *d_amax, uint8_t *d_
 size_t b2_nvfp4_sm100_scales_bytes(uint32_t rows, uint32_t cols);
 int b2_nvfp4_scales_to_sm100(const uint8_t *d_scales, uint32_t src_layout, uint32_t rows, uint32_t cols,
                              uint8_t *d_out, void *stream);
+/* `OptimizerModule::materialize_master` (.../optimizer/launcher/mod.rs:67-95): tensor maximum (two
+ * kernels over `d_chunk_amax`, ceil(len/2048) floats) and the four-six quantiser.  len % 16 == 0. */
 int b2_materialize_master(uint8_t *d_bytes, uint8_t *d_scales, float *d_global_scale,
                           const float *d_master, float *d_amax, float *d_chunk_amax, uint32_t len,
                           uint32_t scale_layout, void *stream);
@@ -240,12 +252,18 @@ int b2_materialize_master(uint8_t *d_bytes, uint8_t *d_scales, float *d_global_s
  * the master tensor and the NVFP4 destination (an export or evaluation hook beside the trainer,
  * an embedder whose device memory is fully reserved before the first step), where cudaMalloc
  * would fail or would stall the training stream by synchronising the device.  The scratch is an
- * array built into the library (about 128 KiB held on every GPU that loads it, until exit), which
+ * array built into the library (about 128 KiB on every GPU the library's module is loaded on, until exit), which
  * limits one call to B2_STATIC_MAX_ELEMENTS values; longer tensors are refused with
  * B2_ERROR_INVALID_VALUE.  The call allocates nothing.  The first call on each device looks up the
- * array's device address and should therefore be made outside any stream capture.  All calls on a
- * device share the one array: it needs no clearing between calls, but two calls whose kernels can
- * overlap on the GPU (different streams) race on it — serialise them. */
+ * array's device address and should therefore be made outside any stream capture.  That first call is
+ * also the moment the CUDA runtime loads the library's module onto the device (modules load lazily by
+ * default), which is when the driver sets the array's 128 KiB aside: a process that is about to reserve
+ * all device memory should make one warm-up call (len = 0 is enough) at start-up, before that
+ * reservation, or the first real call can fail with an out-of-memory error.  From the second call on a
+ * device nothing is looked up, loaded or reserved.  The looked-up address is kept for the life of the
+ * process; after cudaDeviceReset it is stale.  All calls on a device share the one array: it needs no
+ * clearing between calls, but two calls whose kernels can overlap on the GPU (different streams) race
+ * on it — serialise them. */
 #define B2_STATIC_MAX_ELEMENTS (1u << 26)
 int b2_materialize_master_static(uint8_t *d_bytes, uint8_t *d_scales, float *d_global_scale,
                                  const float *d_master, uint32_t len, uint32_t scale_layout,
@@ -429,6 +447,14 @@ void b2_comm_destroy(b2_comm *comm);
 int b2_allgather_nvfp4(b2_comm *comm, void *d_arena, size_t bytes_per_rank, void *stream);
 
 /* ---- debug helpers used by the parity tests ------------------------------------------- */
+/* Makes the bounded completion-counter wait of the one-launch update + encode run out, harmlessly:
+ * launches that kernel as ONE CTA on a one-item list (the encode span at `slot`'s first chunk, none of the
+ * slot's update chunks), so the count it waits for is never reached; after `wait_ns` (at most 1e9) the CTA
+ * raises the abort and status words, leaves, and clears the ticket and completion words as every launch
+ * does.  Nothing is updated or encoded.  b2_muon_plan_status then reports B2_ERROR_LAUNCH_TIMEOUT once.
+ * Synchronises `stream` before the launch. */
+int b2_debug_muon_fused_wait_expiry(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_slots, uint32_t slot,
+                                    uint64_t wait_ns, void *stream);
 /* Evaluates `rcp.approx.ftz.f32` (crates/cuda-kernels/src/utils/float_ptx.rs:31-33). */
 int b2_debug_rcp_approx_ftz(const float *d_in, float *d_out, uint32_t count, void *stream);
 /* Literal one-thread-per-group transcription of the reference quantiser

@@ -16,6 +16,7 @@ HEADER_PATH = os.path.join(os.path.dirname(_HERE), "include", "llmini_b200.h")
 SCALES_CSF, SCALES_RAW, SCALES_SM100 = 0, 1, 2
 OPERAND_BF16, OPERAND_F16 = 0, 1
 QUANTIZE_X, QUANTIZE_Y = 0, 1
+NORMALIZE_TWO_PASS, NORMALIZE_DEFERRED = 0, 1
 ERROR_INVALID_VALUE, ERROR_NOT_SUPPORTED, ERROR_LAUNCH_TIMEOUT = 1, 801, 702
 
 
@@ -33,7 +34,8 @@ class MuonSlotDescriptor(C.Structure):
 
 class MuonOptions(C.Structure):
     _fields_ = [("operand_format", C.c_uint32), ("scale_layout", C.c_uint32), ("quantize_target", C.c_uint32),
-                ("max_iterations", C.c_uint32), ("reserved", C.c_uint32 * 4)]
+                ("max_iterations", C.c_uint32), ("tile_override", C.c_uint32), ("measure_phase_mask", C.c_uint32),
+                ("measure_flags", C.c_uint32), ("normalize_mode", C.c_uint32)]
 
 
 class MuonStepArgs(C.Structure):
@@ -152,6 +154,7 @@ def _declare(L: C.CDLL) -> None:
         "b2_comm_create": (i, [C.POINTER(vp), u8p, i, i]),
         "b2_comm_destroy": (None, [vp]),
         "b2_allgather_nvfp4": (i, [vp, vp, sz, vp]),
+        "b2_debug_muon_fused_wait_expiry": (i, [vp, vp, u32, u64, vp]),
         "b2_debug_rcp_approx_ftz": (i, [vp, vp, u32, vp]),
         "b2_debug_quantize_literal": (i, [vp, vp, vp, vp, vp, u32, vp]),
     }

@@ -16,9 +16,13 @@ LIB_PATH = os.path.join(OUT_DIR, "libllmini_b200.so")
 SOURCES = ["stream_kernels.cu", "ns_gemm_sm100.cu", "api.cu", "host.cu", "no_alloc.cu"]
 HEADERS = ["common.cuh", "internal.h", os.path.join("..", "..", "include", "llmini_b200.h")]
 # -fmad=false: `a*b + c` is fused only where the source says fmaf, matching the reference's
-# Rust arithmetic; -lineinfo keeps ncu source correlation.
+# Rust arithmetic.  B2_MEASURE=1 in the environment adds -DB2_MEASURE: the kernel variants used to
+# attribute time (phase mask, store suppression, two-launch finish) are compiled in; the default
+# build has none of them.
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-fmad=false",
               "-Xcompiler", "-fPIC"]
+if os.environ.get("B2_MEASURE") == "1":
+    NVCC_FLAGS.append("-DB2_MEASURE")
 
 
 def _nvcc() -> str:

@@ -20,6 +20,9 @@ using namespace b2;
 namespace {
 
 constexpr uint32_t kChunkHost = 2048;  // values per streaming chunk (kChunk on the device side)
+// Largest tensor any entry point accepts: the kernels index elements and chunks in 32 bits, and
+// (len + 2047) / 2048 must not wrap.
+constexpr uint64_t kMaxFlatElements = 0xfffff000ull;
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 inline cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s); }
 
@@ -128,7 +131,9 @@ struct Layout {
 bool valid_shape(uint32_t rows, uint32_t cols, const b2_muon_options &o) {
     if ((uint64_t)rows * cols == 0) return true;  // padding slot, skipped
     if (cols % 16 != 0) return false;
-    if ((uint64_t)rows * cols > 0xfffff000ull) return false;
+    if ((uint64_t)rows * cols > kMaxFlatElements) return false;
+    // tile indices are 16-bit (GemmTile): at most 65535 tiles of 128 along either dimension
+    if ((std::max(rows, cols) + 127u) / 128u > 65535u) return false;
     if (o.scale_layout == B2_SCALES_CSF && cols % 128 != 0) return false;
     return true;
 }
@@ -139,8 +144,8 @@ bool valid_shape(uint32_t rows, uint32_t cols, const b2_muon_options &o) {
 // per FLOP than 128 x 256, which in turn beats 128 x 128).
 void pick_tiles(const uint32_t *rows, const uint32_t *cols, uint32_t count, const b2_muon_options &o, int &bn,
                 int &pair) {
-    if (o.reserved[0] == 128 || o.reserved[0] == 256) { bn = (int)o.reserved[0]; pair = 0; return; }
-    if (o.reserved[0] == 512) { bn = 256; pair = 1; return; }
+    if (o.tile_override == 128 || o.tile_override == 256) { bn = (int)o.tile_override; pair = 0; return; }
+    if (o.tile_override == 512) { bn = 256; pair = 1; return; }
     const int tm[3] = {128, 128, 256}, tn[3] = {128, 256, 256};
     const double weight[3] = {1.9, 1.45, 1.0};
     double cost[3] = {0, 0, 0};
@@ -165,7 +170,10 @@ void pick_tiles(const uint32_t *rows, const uint32_t *cols, uint32_t count, cons
 bool build_layout(const uint32_t *rows, const uint32_t *cols, uint32_t count, const b2_muon_options &o, Layout &L) {
     pick_tiles(rows, cols, count, o, L.bn, L.pair);
     L.tile_m = L.pair ? 256 : 128;
-    L.symmetric = (L.pair && L.bn == 256 && !(o.reserved[2] & 4u)) ? 1 : 0;  // flag 4: measurement only, all tiles
+    L.symmetric = (L.pair && L.bn == 256) ? 1 : 0;
+#ifdef B2_MEASURE
+    if (o.measure_flags & 4u) L.symmetric = 0;   // all tiles of the symmetric outputs
+#endif
     L.slots.resize(count);
     L.chunk_prefix.assign(count + 1, 0);
     size_t off = 0;
@@ -269,6 +277,9 @@ b2_muon_options normalized(const b2_muon_options *o) {
     std::memset(&r, 0, sizeof(r));
     if (o) r = *o;
     if (r.max_iterations == 0) r.max_iterations = 5;
+#ifndef B2_MEASURE
+    r.measure_phase_mask = r.measure_flags = 0;   // honoured only by a library built with -DB2_MEASURE
+#endif
     return r;
 }
 
@@ -281,6 +292,7 @@ struct b2_muon_plan {
     uint8_t *ws = nullptr;
     std::vector<uint8_t> meta;  // host image of the metadata region
     double flops_per_iteration = 0.0;
+    uint64_t fused_wait_ns = 2000000000ull;   // limit of the completion-counter wait in the update + encode launch
 
     template <typename T>
     T *at(size_t off) const { return reinterpret_cast<T *>(ws + off); }
@@ -348,8 +360,11 @@ int b2_muon_plan_create(b2_muon_plan **out, const uint32_t *rows, const uint32_t
     if (!out || !rows || !cols || slot_count == 0 || slot_count > 65535 || !d_workspace) return B2_ERROR_INVALID_VALUE;
     if (reinterpret_cast<uintptr_t>(d_workspace) % 1024 != 0) return B2_ERROR_INVALID_VALUE;
     b2_muon_options o = normalized(options);
-    if (o.operand_format > B2_OPERAND_F16 || o.scale_layout > B2_SCALES_SM100 || o.quantize_target > B2_QUANTIZE_Y)
+    if (o.operand_format > B2_OPERAND_F16 || o.scale_layout > B2_SCALES_SM100 || o.quantize_target > B2_QUANTIZE_Y ||
+        o.normalize_mode > B2_NORMALIZE_DEFERRED)
         return B2_ERROR_INVALID_VALUE;
+    // an un-normalised update can leave F16's range: the one-pass prepare is for BF16 operands
+    if (o.normalize_mode == B2_NORMALIZE_DEFERRED && o.operand_format != B2_OPERAND_BF16) return B2_ERROR_INVALID_VALUE;
     b2_muon_plan *p = new (std::nothrow) b2_muon_plan();
     if (!p) return (int)cudaErrorMemoryAllocation;
     p->options = o;
@@ -518,6 +533,13 @@ int b2_muon_prepare_polar(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_s
     double *partials = plan->at<double>(L.off_partials);
     float *inv = plan->at<float>(L.off_inv_norm);
     const MomentumParams mp = momentum_params(a);
+    if (plan->options.normalize_mode == B2_NORMALIZE_DEFERRED) {
+        // one pass over the gradients; the scalar goes to the first Newton-Schulz iteration (b2_muon_polar)
+        cudaError_t e = launch_muon_momentum_sumsq(v, mp, plan->at<uint64_t>(L.off_x0_ptrs), partials,
+                                                   plan->at<float>(L.off_amax_x), s);
+        if (e == cudaSuccess) e = launch_muon_inv_norm(v, partials, inv, s);
+        return (int)e;
+    }
     cudaError_t e = launch_muon_sumsq(v, mp, partials, plan->at<float>(L.off_amax_x), s);
     if (e == cudaSuccess) e = launch_muon_inv_norm(v, partials, inv, s);
     if (e == cudaSuccess)
@@ -547,19 +569,22 @@ int b2_muon_polar(b2_muon_plan *plan, const b2_muon_step_args *a, void *stream) 
         }
         const uint32_t b = it & 1u;
         const bool last = it + 1 == a->iterations;
-        // reserved[1]: measurement-only phase mask (1 Gram, 2 Poly, 4 Apply; 0 = all);
-        // reserved[2]: measurement-only kernel flags
-        const uint32_t mask = plan->options.reserved[1] ? plan->options.reserved[1] : 7u;
-        const uint32_t dbg = plan->options.reserved[2];
+        // measurement builds only: phase mask (1 Gram, 2 Poly, 4 Apply; 0 = all) and kernel flags
+        const uint32_t mask = plan->options.measure_phase_mask ? plan->options.measure_phase_mask : 7u;
+        const uint32_t dbg = plan->options.measure_flags;
+        // after a one-pass prepare the first iteration's operand is not normalised: its Gram output takes
+        // s^2 and its Apply output s, s = inv_norm[slot]
+        const float *scale = (it == 0 && plan->options.normalize_mode == B2_NORMALIZE_DEFERRED)
+                                 ? plan->at<float>(L.off_inv_norm) : nullptr;
         if (mask & 1u)
             e = launch_ns_gemm(L.bn, L.pair, probs + (size_t)(kGram0 + b) * count, tnn, L.tiles_nn, kEpiGram, f16, ca, cb, cc,
-                               status, dbg, grid, s);
+                               scale, 2u, status, dbg, grid, s);
         if (e == cudaSuccess && (mask & 2u))
-            e = launch_ns_gemm(L.bn, L.pair, probs + (size_t)kPoly * count, tnn, L.tiles_nn, kEpiPoly, f16, ca, cb, cc, status,
-                               dbg, grid, s);
+            e = launch_ns_gemm(L.bn, L.pair, probs + (size_t)kPoly * count, tnn, L.tiles_nn, kEpiPoly, f16, ca, cb, cc,
+                               nullptr, 0u, status, dbg, grid, s);
         if (e == cudaSuccess && (mask & 4u))
             e = launch_ns_gemm(L.bn, L.pair, probs + (size_t)((last ? kLast0 : kApply0) + b) * count, tout, L.tiles_out,
-                               last ? kEpiApplyLast : kEpiApply, f16, ca, cb, cc, status, dbg, grid, s);
+                               last ? kEpiApplyLast : kEpiApply, f16, ca, cb, cc, scale, 1u, status, dbg, grid, s);
     }
     return (int)e;
 }
@@ -582,13 +607,13 @@ static int finish_impl(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_slot
     }
     const int quantize_y = plan->options.quantize_target == B2_QUANTIZE_Y;
     // one launch for the plain update; NorMuon / qk-clip steps (and measurement flag 16) take two
-    if (quantize && !(plan->options.reserved[2] & 16u) && !up.normuon && !up.d_qk_clip_factors &&
+    if (quantize && !(plan->options.measure_flags & 16u) && !up.normuon && !up.d_qk_clip_factors &&
         up.symexp_beta == 0.0f) {
         if (e == cudaSuccess)
             e = launch_muon_update_encode(v, plan->at<uint32_t>(L.off_items), (uint32_t)L.items.size(),
                                           plan->at<uint64_t>(L.off_u_ptrs), amax_x, up, quantize_y,
                                           (int)plan->options.scale_layout, plan->ws + L.off_fused_sync,
-                                          plan->at<uint32_t>(L.off_status), s);
+                                          plan->at<uint32_t>(L.off_status), plan->fused_wait_ns, s);
         return (int)e;
     }
     if (e == cudaSuccess) e = launch_muon_update(v, plan->at<uint64_t>(L.off_u_ptrs), amax_x, up, s);
@@ -654,6 +679,11 @@ int b2_muon_plan_scratch(b2_muon_plan *plan, uint32_t slot, uint32_t which, void
     if (!plan || !d_ptr || !bytes) return B2_ERROR_INVALID_VALUE;
     const Layout &L = plan->layout;
     if (which == 4) { *d_ptr = plan->ws + L.off_status; *bytes = 4; return B2_SUCCESS; }
+    if (which == 10) {
+        *d_ptr = plan->ws + L.off_fused_sync;
+        *bytes = fused_sync_bytes((uint32_t)L.slots.size());
+        return B2_SUCCESS;
+    }
     if (slot >= L.slots.size()) return B2_ERROR_INVALID_VALUE;
     const SlotLayout &sl = L.slots[slot];
     if (sl.len == 0) return B2_ERROR_INVALID_VALUE;
@@ -686,7 +716,7 @@ int b2_muon_plan_status(b2_muon_plan *plan, void *stream) {
 
 // ---- quantiser ------------------------------------------------------------------------------
 int b2_tensor_amax_f32(const float *d_x, float *d_chunk_amax, float *d_out, uint32_t n, void *stream) {
-    if (!d_x || !d_chunk_amax || !d_out) return B2_ERROR_INVALID_VALUE;
+    if (!d_x || !d_chunk_amax || !d_out || n > kMaxFlatElements) return B2_ERROR_INVALID_VALUE;
     cudaError_t e = launch_tensor_chunk_amax(d_x, d_chunk_amax, n, as_stream(stream));
     if (e == cudaSuccess) e = launch_tensor_amax_from_chunks(d_chunk_amax, d_out, (n + 2047) / 2048, as_stream(stream));
     return (int)e;
@@ -698,7 +728,7 @@ int b2_tensor_amax_from_chunks_f32(const float *d_chunk_amax, float *d_out, uint
 int b2_fp32_to_nvfp4_four_six(const float *d_x, const float *d_amax, uint8_t *d_out_fp4, uint8_t *d_out_scales,
                               float *d_out_global_scale, uint32_t group_count, uint32_t scale_layout, void *stream) {
     if (!d_x || !d_amax || !d_out_fp4 || !d_out_scales || !d_out_global_scale) return B2_ERROR_INVALID_VALUE;
-    if (scale_layout > B2_SCALES_RAW || group_count > 0x0fffffffu) return B2_ERROR_INVALID_VALUE;
+    if (scale_layout > B2_SCALES_RAW || group_count > kMaxFlatElements / 16) return B2_ERROR_INVALID_VALUE;
     if (scale_layout == B2_SCALES_CSF && group_count % 8 != 0) return B2_ERROR_INVALID_VALUE;
     DeviceInfo d;
     cudaError_t e = device_info(d);
@@ -722,7 +752,7 @@ int b2_nvfp4_scales_to_sm100(const uint8_t *d_scales, uint32_t src_layout, uint3
 }
 int b2_materialize_master(uint8_t *d_bytes, uint8_t *d_scales, float *d_global_scale, const float *d_master,
                           float *d_amax, float *d_chunk_amax, uint32_t len, uint32_t scale_layout, void *stream) {
-    if (len % 16 != 0) return B2_ERROR_INVALID_VALUE;
+    if (len % 16 != 0 || len > kMaxFlatElements) return B2_ERROR_INVALID_VALUE;
     int rc = b2_tensor_amax_f32(d_master, d_chunk_amax, d_amax, len, stream);
     if (rc) return rc;
     return b2_fp32_to_nvfp4_four_six(d_master, d_amax, d_bytes, d_scales, d_global_scale, len / 16, scale_layout, stream);
@@ -731,7 +761,7 @@ int b2_materialize_master(uint8_t *d_bytes, uint8_t *d_scales, float *d_global_s
 static int check_sf(const b2_schedule_free_materialize_args *a) {
     if (!a || !a->bytes || !a->scales || !a->global_scale || !a->z_master || !a->x_master || !a->amax)
         return B2_ERROR_INVALID_VALUE;
-    if (a->len % 16 != 0 || a->scale_layout > B2_SCALES_RAW) return B2_ERROR_INVALID_VALUE;
+    if (a->len % 16 != 0 || a->len > kMaxFlatElements || a->scale_layout > B2_SCALES_RAW) return B2_ERROR_INVALID_VALUE;
     if (a->scale_layout == B2_SCALES_CSF && a->len % 128 != 0) return B2_ERROR_INVALID_VALUE;
     if ((uint64_t)a->scale_rows * a->scale_k < a->len) return B2_ERROR_INVALID_VALUE;
     if (!(a->symexp_lin_beta >= 0.0f)) return B2_ERROR_INVALID_VALUE;
@@ -781,6 +811,7 @@ int b2_materialize_schedule_free(const b2_schedule_free_materialize_args *a, voi
 static int check_adam(const b2_adamw_update_args *a, bool need_quant, bool need_amax) {
     if (!a || !a->z_master || !a->x_master || !a->grad || !a->first_moment || !a->second_moment)
         return B2_ERROR_INVALID_VALUE;
+    if (a->len > kMaxFlatElements) return B2_ERROR_INVALID_VALUE;
     if (need_quant && (a->len % 16 != 0 || !a->bytes || !a->scales || !a->global_scale || !a->amax || !a->chunk_amax))
         return B2_ERROR_INVALID_VALUE;
     if (need_amax && (a->len % 16 != 0 || !a->amax)) return B2_ERROR_INVALID_VALUE;
@@ -822,7 +853,7 @@ int b2_adamw_table_prepare(b2_adamw_slot_descriptor *t, uint32_t count, uint32_t
     if ((!t && count) || !total_chunks) return B2_ERROR_INVALID_VALUE;
     uint64_t chunks = 0;
     for (uint32_t i = 0; i < count; ++i) {
-        if (t[i].mode > 2 || t[i].scale_layout > B2_SCALES_RAW) return B2_ERROR_INVALID_VALUE;
+        if (t[i].mode > 2 || t[i].scale_layout > B2_SCALES_RAW || t[i].len > kMaxFlatElements) return B2_ERROR_INVALID_VALUE;
         if (t[i].mode != 0 && (t[i].len % 16 != 0 || !t[i].amax)) return B2_ERROR_INVALID_VALUE;
         if (t[i].mode == 2 && (!t[i].bytes || !t[i].scales || !t[i].global_scale)) return B2_ERROR_INVALID_VALUE;
         if (t[i].mode == 2 && t[i].scale_layout == B2_SCALES_CSF && t[i].len % 128 != 0) return B2_ERROR_INVALID_VALUE;
@@ -894,6 +925,30 @@ int b2_clip_gradients(const b2_gradient_clip_args *a, void *stream) {
 int b2_zero_f32_pointer_table(const uint64_t *d_pointers, uint32_t pointer_count, void *stream) {
     if (!d_pointers && pointer_count) return B2_ERROR_INVALID_VALUE;
     return (int)launch_zero_pointer_table(d_pointers, pointer_count, as_stream(stream));
+}
+
+int b2_debug_muon_fused_wait_expiry(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_slots, uint32_t slot,
+                                    uint64_t wait_ns, void *stream) {
+    if (!plan || !d_slots || wait_ns == 0 || wait_ns > 1000000000ull) return B2_ERROR_INVALID_VALUE;
+    const Layout &L = plan->layout;
+    if (slot >= L.slots.size() || L.slots[slot].len == 0) return B2_ERROR_INVALID_VALUE;
+    cudaStream_t s = as_stream(stream);
+    // A one-item list: the encode span at the slot's first chunk, with none of the slot's update chunks in
+    // the list, so the completion count it waits for is never reached.  The list borrows the first
+    // word of the per-step partial sums (rewritten by the next prepare).
+    const uint32_t item = 0x80000000u | L.chunk_prefix[slot];
+    uint32_t *d_item = plan->at<uint32_t>(L.off_partials);
+    cudaError_t e = cudaMemcpyAsync(d_item, &item, sizeof(item), cudaMemcpyHostToDevice, s);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaStreamSynchronize(s);   // `item` lives on this frame
+    if (e != cudaSuccess) return (int)e;
+    SlotView v = plan->view(d_slots);
+    b2_muon_step_args zero;
+    std::memset(&zero, 0, sizeof(zero));
+    const UpdateParams up = update_params(&zero);
+    return (int)launch_muon_update_encode(v, d_item, 1u, plan->at<uint64_t>(L.off_u_ptrs), plan->at<float>(L.off_amax_x),
+                                          up, 0, (int)plan->options.scale_layout, plan->ws + L.off_fused_sync,
+                                          plan->at<uint32_t>(L.off_status), wait_ns, s);
 }
 
 int b2_debug_rcp_approx_ftz(const float *d_in, float *d_out, uint32_t count, void *stream) {

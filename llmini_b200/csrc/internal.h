@@ -45,6 +45,9 @@ struct UpdateParams {
 };
 cudaError_t launch_muon_sumsq(const SlotView &v, const MomentumParams &mp, double *partials, float *amax_x,
                               cudaStream_t s);
+// One-pass form of stages M+N: momentum state, un-normalised BF16 operand and the chunk sums in one launch.
+cudaError_t launch_muon_momentum_sumsq(const SlotView &v, const MomentumParams &mp, const uint64_t *x0_ptrs,
+                                       double *partials, float *amax_x, cudaStream_t s);
 cudaError_t launch_muon_inv_norm(const SlotView &v, const double *partials, float *inv_norm,
                                  cudaStream_t s);
 cudaError_t launch_muon_momentum_normalize(const SlotView &v, const MomentumParams &mp, const float *inv_norm,
@@ -53,12 +56,14 @@ cudaError_t launch_muon_update(const SlotView &v, const uint64_t *u_ptrs, float 
                                cudaStream_t s);
 // Stages U and Q in one launch over an item list (bit 31: encode span of B2_FUSED_ENCODE_SPAN chunks, else update
 // chunk; low bits: flat chunk index).  `sync` is fused_sync_bytes(slot_count) of device scratch,
-// zeroed once by the owner; every launch leaves it zeroed again.
+// zeroed once by the owner; every launch leaves it zeroed again.  `wait_ns` bounds an encode span's wait for
+// its matrix's update chunks; when it runs out the launch sets *status and returns.
 #define B2_FUSED_ENCODE_SPAN 4
 size_t fused_sync_bytes(uint32_t slot_count);
 cudaError_t launch_muon_update_encode(const SlotView &v, const uint32_t *items, uint32_t item_count,
                                       const uint64_t *u_ptrs, float *amax_x, const UpdateParams &up, int quantize_y,
-                                      int scale_layout, void *sync, uint32_t *status, cudaStream_t s);
+                                      int scale_layout, void *sync, uint32_t *status, uint64_t wait_ns,
+                                      cudaStream_t s);
 cudaError_t launch_normuon_stats(const SlotView &v, const NeuronView &nv, const uint64_t *u_ptrs, int hyperball,
                                  cudaStream_t s);
 cudaError_t launch_muon_hyperball_update(const SlotView &v, const uint64_t *u_ptrs, float *amax_x,
@@ -141,8 +146,12 @@ constexpr int kGemmBlockM = 128;
 constexpr int kGemmBlockK = 64;
 
 cudaError_t gemm_configure(int block_n, int pair);
+// `slot_scale` (may be null): per-slot scalars s; the Gram epilogue multiplies the accumulator by s^scale_pow
+// (scale_pow = 2) and the Apply epilogues by s (scale_pow = 1).  Used by the first iteration after a
+// one-pass prepare, whose operand is not normalised yet.
 cudaError_t launch_ns_gemm(int block_n, int pair, const GemmProblem *problems, const GemmTile *tiles,
                            uint32_t tile_count, uint32_t epilogue, int f16, float ca, float cb,
-                           float cc, uint32_t *status, uint32_t debug_flags, int grid, cudaStream_t s);
+                           float cc, const float *slot_scale, uint32_t scale_pow, uint32_t *status,
+                           uint32_t debug_flags, int grid, cudaStream_t s);
 
 }  // namespace b2

@@ -9,9 +9,16 @@
 // and the regular entry point b2_materialize_master wants two scratch buffers (the per-chunk
 // maxima and the tensor maximum) that it has nowhere to take from.
 //
-// The scratch therefore lives in this library image: one file-scope __device__ array that every
-// GPU loading the library carries until the process exits (128 KiB + 256 B).  Its size bounds
-// the tensor: at most B2_STATIC_MAX_ELEMENTS values per call.
+// The scratch therefore lives in this library image: one file-scope __device__ array (128 KiB +
+// 256 B) that every GPU carries, from the moment this module is loaded onto it until the process
+// exits.  Its size bounds the tensor: at most B2_STATIC_MAX_ELEMENTS values per call.
+//
+// First call on a device: the CUDA runtime loads modules lazily by default, so the module holding the
+// array is created on a device by the first cudaGetSymbolAddress there, and that is when the driver sets
+// the 128 KiB aside.  A caller whose device memory is about to be fully reserved therefore makes one
+// warm-up call per device (len = 0 is enough) at start-up, before the reservation and outside any
+// stream capture; from the second call on nothing is looked up, loaded or reserved.  The address is
+// cached for the life of the process and is stale after cudaDeviceReset.
 #include <cuda_runtime.h>
 
 #include <mutex>

@@ -215,10 +215,15 @@ template <int BN, bool PAIR, int SLABS>
 __global__ void __launch_bounds__((Cfg<BN, PAIR, SLABS>::kThreads), 1)
 k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__ tiles,
           uint32_t tile_count, uint32_t epilogue, int f16, float ca, float cb, float cc,
-          uint32_t *status, uint32_t debug_flags) {
+          const float *__restrict__ slot_scale, uint32_t scale_pow, uint32_t *status, uint32_t debug_flags) {
     using C = Cfg<BN, PAIR, SLABS>;
-    const bool dbg_no_store = debug_flags & 1u;   // measurement only: drop every epilogue store
-    const bool dbg_no_global = debug_flags & 8u;  // measurement only: stage in shared memory but issue no global store
+#ifdef B2_MEASURE
+    const bool dbg_no_store = debug_flags & 1u;   // drop every epilogue store
+    const bool dbg_no_global = debug_flags & 8u;  // stage in shared memory but issue no global store
+#else
+    constexpr bool dbg_no_store = false, dbg_no_global = false;
+    (void)debug_flags;
+#endif
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *stage_base = smem;
@@ -415,6 +420,14 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
             const uint32_t taddr = tmem_base + ((uint32_t)(32 * q) << 16) + acc * BN + c0;
             const uint32_t tempty = tempty_leader0 + 8u * acc;
             const bool in_range = n0 + c0 < (int)N && slab_row0 < (int)M && !dbg_no_store;   // warp-uniform
+            // One-pass prepare: the operand of the first iteration is the un-normalised update, and
+            // s = 1 / (1.01 |u| + 1e-7) of the tile's matrix enters here: G = (s s) X X^T, X1 = s (Q X).
+            float out_scale = 1.0f;
+            if (slot_scale != nullptr && epilogue != kEpiPoly) {
+                const float sv = __ldcg(slot_scale + tl.problem);
+                out_scale = scale_pow == 2u ? sv * sv : sv;
+            }
+            const bool scaled = out_scale != 1.0f;   // warp-uniform
 
             if (epilogue == kEpiApplyLast) {
                 // FP32 result in the storage layout: 32 columns (128 bytes) per staged slab
@@ -429,6 +442,10 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
                         if (lane == 0) mbar_arrive_cluster(tempty);
                     }
                     if (!in_range || n0 + c0 + 32 * sub >= (int)N) continue;
+                    if (scaled) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * out_scale);
+                    }
                     slab_wait();
                     uint8_t *slab = slab_pair + sb * kSlabBytes;
 #pragma unroll
@@ -456,6 +473,10 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
                         tc_fence_before();
                         __syncwarp();
                         if (lane == 0) mbar_arrive_cluster(tempty);
+                    }
+                    if (scaled) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * out_scale);
                     }
                     if ((epilogue == kEpiGram || epilogue == kEpiPoly) && !dbg_no_store) {
                         const size_t unit = unit0 + 8 * sub;
@@ -556,12 +577,16 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
 
 template <int BN, bool PAIR, int SLABS>
 cudaError_t launch_impl(const GemmProblem *problems, const GemmTile *tiles, uint32_t tile_count, uint32_t epilogue,
-                        int f16, float ca, float cb, float cc, uint32_t *status, uint32_t debug_flags, int grid,
-                        cudaStream_t s) {
+                        int f16, float ca, float cb, float cc, const float *slot_scale, uint32_t scale_pow,
+                        uint32_t *status, uint32_t debug_flags, int grid, cudaStream_t s) {
     cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute attr[2];
     unsigned n_attr = 0;
-    if (!(debug_flags & 32u)) {  // flag 32: measurement only, plain stream order
+    bool chained = true;
+#ifdef B2_MEASURE
+    chained = !(debug_flags & 32u);   // plain stream order
+#endif
+    if (chained) {
         attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
         ++n_attr;
@@ -585,8 +610,8 @@ cudaError_t launch_impl(const GemmProblem *problems, const GemmTile *tiles, uint
     cfg.blockDim = dim3((unsigned)Cfg<BN, PAIR, SLABS>::kThreads, 1, 1);
     cfg.dynamicSmemBytes = Cfg<BN, PAIR, SLABS>::kSmemBytes;
     cfg.stream = s;
-    return cudaLaunchKernelEx(&cfg, k_ns_gemm<BN, PAIR, SLABS>, problems, tiles, tile_count, epilogue, f16, ca, cb, cc, status,
-                              debug_flags);
+    return cudaLaunchKernelEx(&cfg, k_ns_gemm<BN, PAIR, SLABS>, problems, tiles, tile_count, epilogue, f16, ca, cb, cc,
+                              slot_scale, scale_pow, status, debug_flags);
 }
 
 }  // namespace
@@ -606,15 +631,16 @@ cudaError_t gemm_configure(int block_n, int pair) {
 }
 cudaError_t launch_ns_gemm(int block_n, int pair, const GemmProblem *problems, const GemmTile *tiles,
                            uint32_t tile_count, uint32_t epilogue, int f16, float ca, float cb,
-                           float cc, uint32_t *status, uint32_t debug_flags, int grid, cudaStream_t s) {
+                           float cc, const float *slot_scale, uint32_t scale_pow, uint32_t *status,
+                           uint32_t debug_flags, int grid, cudaStream_t s) {
     if (tile_count == 0) return cudaSuccess;
     if (pair && block_n == 256) {
-        return launch_impl<256, true, 1>(problems, tiles, tile_count, epilogue, f16, ca, cb, cc, status, debug_flags, grid, s);
+        return launch_impl<256, true, 1>(problems, tiles, tile_count, epilogue, f16, ca, cb, cc, slot_scale, scale_pow, status, debug_flags, grid, s);
     }
     if (!pair && block_n == 256)
-        return launch_impl<256, false, 1>(problems, tiles, tile_count, epilogue, f16, ca, cb, cc, status, debug_flags, grid, s);
+        return launch_impl<256, false, 1>(problems, tiles, tile_count, epilogue, f16, ca, cb, cc, slot_scale, scale_pow, status, debug_flags, grid, s);
     if (!pair && block_n == 128)
-        return launch_impl<128, false, 1>(problems, tiles, tile_count, epilogue, f16, ca, cb, cc, status, debug_flags, grid, s);
+        return launch_impl<128, false, 1>(problems, tiles, tile_count, epilogue, f16, ca, cb, cc, slot_scale, scale_pow, status, debug_flags, grid, s);
     return cudaErrorInvalidValue;
 }
 

@@ -222,6 +222,79 @@ k_muon_momentum_normalize(const b2_muon_slot_descriptor *slots, const uint32_t *
     }
 }
 
+// Stages M+N in ONE pass over the gradients: BF16 momentum state, the UN-normalised 16-bit operand
+// X0 = r16(u) in the storage layout, and the chunk's sum of u^2 (taken over the FP32 u, as
+// normalize.rs:35-79 does).  The Frobenius scale s = 1 / (1.01 |u| + 1e-7) is not known until every chunk of
+// the matrix has been summed, so it is left to the first Newton-Schulz iteration, which is linear in it:
+// G = (s s) X0 X0^T and X1 = s (Q X0) (the Gram and Apply epilogues multiply by the slot's scalar).  10 bytes
+// per element cross the memory interface instead of 16.  The operand is rounded before instead of after the
+// scaling, which is not the reference's rounding point; the two-pass kernels above keep that one.  BF16
+// operands only: an un-normalised F16 operand could leave F16's range.
+// Two chunks per trip, like k_muon_sumsq.  Also clears the two amax words of each slot.
+template <int VS>
+__global__ void __launch_bounds__(kThreads, VS ? 4 : 6)
+k_muon_momentum_sumsq(const b2_muon_slot_descriptor *slots, const uint32_t *prefix, uint32_t slot_count,
+                      uint32_t total_chunks, MomentumParams mp, const uint64_t *x0_ptrs, double *partials,
+                      float *amax_x) {
+    __shared__ double warp_part[2][kThreads / 32];
+    const int tid = threadIdx.x;
+    if (mp.d_grad_scale) mp.grad_scale = __ldg(mp.d_grad_scale);
+    for (uint32_t c0 = 2 * blockIdx.x; c0 < total_chunks; c0 += 2 * gridDim.x) {
+        float local[2] = {0.0f, 0.0f};
+        uint32_t reset_slot[2] = {0xffffffffu, 0xffffffffu};
+        uint64_t reset_amax[2] = {0, 0};
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const uint32_t c = c0 + k;
+            if (c >= total_chunks) break;   // CTA-uniform
+            ChunkCtx cx = chunk_ctx(slots, prefix, slot_count, c);
+            const float *grad = reinterpret_cast<const float *>(cx.d.grad);
+            uint16_t *mom = reinterpret_cast<uint16_t *>(cx.d.momentum);
+            uint16_t *var = reinterpret_cast<uint16_t *>(cx.d.variance);
+            uint16_t *x0 = reinterpret_cast<uint16_t *>(x0_ptrs[cx.slot]);
+            const uint32_t base = cx.local_chunk * kChunk;
+            if (cx.local_chunk == 0) {
+                reset_slot[k] = cx.slot;
+                reset_amax[k] = cx.d.schedule_amax;
+            }
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const uint32_t i = base + h * (kChunk / 2) + tid * 4;
+                if (i < cx.len) {
+                    const Quad q = momentum_quad<VS>(grad, mom, var, i, mp, true);
+                    *reinterpret_cast<uint2 *>(mom + i) = pack_bf16x4(q.m);
+                    if (VS) *reinterpret_cast<uint2 *>(var + i) = pack_bf16x4(q.v);
+                    uint2 xo;
+                    xo.x = pack_operands(q.u[0], q.u[1], 0);
+                    xo.y = pack_operands(q.u[2], q.u[3], 0);
+                    *reinterpret_cast<uint2 *>(x0 + i) = xo;
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) local[k] = fmaf(q.u[e], q.u[e], local[k]);
+                }
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const double acc = warp_sum((double)local[k]);
+            if ((tid & 31) == 0) warp_part[k][tid >> 5] = acc;
+        }
+        __syncthreads();
+        if (tid < 2 && c0 + tid < total_chunks) {
+            double s = 0.0;
+#pragma unroll
+            for (int w = 0; w < kThreads / 32; ++w) s += warp_part[tid][w];
+            partials[c0 + tid] = s;
+            const uint32_t rs = tid == 0 ? reset_slot[0] : reset_slot[1];
+            const uint64_t ra = tid == 0 ? reset_amax[0] : reset_amax[1];
+            if (rs != 0xffffffffu) {
+                amax_x[rs] = 0.0f;
+                *reinterpret_cast<float *>(ra) = 0.0f;
+            }
+        }
+        __syncthreads();
+    }
+}
+
 // Per-slot SymExpLin scalars for the update kernels (tma_split.rs:38-55): identity unless the step
 // asks for the transform; unit scales unless the slot's entry carries scale scalars.
 __device__ __forceinline__ SymExpLin symexp_for_slot(const UpdateParams &up, uint32_t slot) {
@@ -1011,12 +1084,12 @@ struct FusedSync {   // all zero between launches: the last CTA to leave clears 
 };
 constexpr uint32_t kItemEncode = 0x80000000u;
 constexpr uint32_t kEncodeSpan = B2_FUSED_ENCODE_SPAN;  // chunks per encode item (list built by the plan)
-constexpr uint64_t kFusedWaitNs = 2000000000ull;
 
 __global__ void __launch_bounds__(kThreads, 5)
 k_muon_update_encode(const b2_muon_slot_descriptor *slots, const uint32_t *prefix, uint32_t slot_count,
                      const uint32_t *items, uint32_t item_count, const uint64_t *u_ptrs, float *amax_x,
-                     UpdateParams up, int quantize_y, int scale_layout, FusedSync *sync, uint32_t *status) {
+                     UpdateParams up, int quantize_y, int scale_layout, FusedSync *sync, uint32_t *status,
+                     uint64_t wait_ns) {
     __shared__ float warp_ax[kThreads / 32], warp_ay[kThreads / 32];
     __shared__ uint32_t s_ticket[2], s_ok;
     const int tid = threadIdx.x;
@@ -1048,7 +1121,7 @@ k_muon_update_encode(const b2_muon_slot_descriptor *slots, const uint32_t *prefi
                 if (ld_acquire_u32(&sync->done[cx.slot]) < need) {
                     const uint64_t start = stream_globaltimer();
                     while (ld_acquire_u32(&sync->done[cx.slot]) < need) {
-                        if (ld_acquire_u32(&sync->abort) != 0 || stream_globaltimer() - start > kFusedWaitNs) {
+                        if (ld_acquire_u32(&sync->abort) != 0 || stream_globaltimer() - start > wait_ns) {
                             ok = 0;
                             break;
                         }
@@ -1528,6 +1601,17 @@ cudaError_t launch_muon_sumsq(const SlotView &v, const MomentumParams &mp, doubl
             v.slots, v.chunk_prefix, v.slot_count, v.total_chunks, mp, partials, amax_x);
     return cudaGetLastError();
 }
+cudaError_t launch_muon_momentum_sumsq(const SlotView &v, const MomentumParams &mp, const uint64_t *x0_ptrs,
+                                       double *partials, float *amax_x, cudaStream_t s) {
+    if (v.total_chunks == 0) return cudaSuccess;
+    if (mp.variance_adaptive)
+        k_muon_momentum_sumsq<1><<<clamp_grid((v.total_chunks + 1) / 2, v.grid), kThreads, 0, s>>>(
+            v.slots, v.chunk_prefix, v.slot_count, v.total_chunks, mp, x0_ptrs, partials, amax_x);
+    else
+        k_muon_momentum_sumsq<0><<<clamp_grid((v.total_chunks + 1) / 2, v.grid), kThreads, 0, s>>>(
+            v.slots, v.chunk_prefix, v.slot_count, v.total_chunks, mp, x0_ptrs, partials, amax_x);
+    return cudaGetLastError();
+}
 cudaError_t launch_muon_inv_norm(const SlotView &v, const double *partials, float *inv_norm,
                                  cudaStream_t s) {
     if (v.slot_count == 0) return cudaSuccess;
@@ -1659,14 +1743,15 @@ cudaError_t launch_scales_to_sm100(const uint8_t *src, int src_csf, uint32_t row
 size_t fused_sync_bytes(uint32_t slot_count) { return sizeof(FusedSync) + sizeof(uint32_t) * slot_count; }
 cudaError_t launch_muon_update_encode(const SlotView &v, const uint32_t *items, uint32_t item_count,
                                       const uint64_t *u_ptrs, float *amax_x, const UpdateParams &up, int quantize_y,
-                                      int scale_layout, void *sync, uint32_t *status, cudaStream_t s) {
+                                      int scale_layout, void *sync, uint32_t *status, uint64_t wait_ns,
+                                      cudaStream_t s) {
     if (item_count == 0) return cudaSuccess;
     // the plain update only: with NorMuon factors or qk-clip the two-launch form measured faster
     if (up.normuon || up.d_qk_clip_factors || up.symexp_beta > 0.0f) return cudaErrorInvalidValue;
     const int grid = clamp_grid(item_count, v.grid);
     k_muon_update_encode<<<grid, kThreads, 0, s>>>(v.slots, v.chunk_prefix, v.slot_count, items, item_count, u_ptrs,
                                                   amax_x, up, quantize_y, scale_layout,
-                                                  static_cast<FusedSync *>(sync), status);
+                                                  static_cast<FusedSync *>(sync), status, wait_ns);
     return cudaGetLastError();
 }
 cudaError_t launch_normuon_stats(const SlotView &v, const NeuronView &nv, const uint64_t *u_ptrs, int hyperball,

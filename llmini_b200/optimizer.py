@@ -16,7 +16,7 @@ import torch
 
 from . import _ffi
 from ._ffi import (AdamWSlotDescriptor, AdamWUpdateArgs as _CAdam, GradientClipArgs as _CClip, MuonOptions, MuonSlotDescriptor, MuonStepArgs, OPERAND_BF16,
-                   OPERAND_F16, QUANTIZE_X, QUANTIZE_Y, SCALES_CSF, SCALES_RAW, SCALES_SM100,
+                   NORMALIZE_DEFERRED, NORMALIZE_TWO_PASS, OPERAND_F16, QUANTIZE_X, QUANTIZE_Y, SCALES_CSF, SCALES_RAW, SCALES_SM100,
                    ScheduleFreeMaterializeArgs as _CSf, check)
 from .nvfp4 import Nvfp4QuantModule, sm100_scales_bytes, zero_scales
 
@@ -124,13 +124,17 @@ class MuonPlan:
 
     def __init__(self, shapes: Sequence[tuple[int, int]], operand_format: int = OPERAND_BF16,
                  scale_layout: int = SCALES_CSF, quantize_target: int = QUANTIZE_X, max_iterations: int = 5,
-                 tile_n: int = 0, device="cuda", debug_phase_mask: int = 0, debug_flags: int = 0):
+                 tile_n: int = 0, device="cuda", debug_phase_mask: int = 0, debug_flags: int = 0,
+                 normalize_mode: int = NORMALIZE_TWO_PASS):
+        """`normalize_mode`: NORMALIZE_TWO_PASS keeps the reference's rounding point X0 = r16(u * s);
+        NORMALIZE_DEFERRED reads the gradients once and lets s enter through the first iteration (BF16
+        operands only).  `debug_*` are read only by a library built with -DB2_MEASURE."""
         self._lib = _ffi.lib()
         self.shapes = [(int(r), int(c)) for r, c in shapes]
         n = len(self.shapes)
         self._rows = (C.c_uint32 * n)(*[r for r, _ in self.shapes])
         self._cols = (C.c_uint32 * n)(*[c for _, c in self.shapes])
-        self.options = MuonOptions(operand_format, scale_layout, quantize_target, max_iterations, (C.c_uint32 * 4)(tile_n, debug_phase_mask, debug_flags, 0))
+        self.options = MuonOptions(operand_format, scale_layout, quantize_target, max_iterations, tile_n, debug_phase_mask, debug_flags, normalize_mode)
         nbytes = self._lib.b2_muon_workspace_bytes(self._rows, self._cols, n, C.byref(self.options))
         if nbytes == 0:
             raise _ffi.B2Error(_ffi.ERROR_INVALID_VALUE, "muon_workspace_bytes")
@@ -164,13 +168,19 @@ class MuonPlan:
     def status(self) -> int:
         return int(self._lib.b2_muon_plan_status(self._handle, _stream()))
 
+    def debug_fused_wait_expiry(self, slots: torch.Tensor, slot: int, wait_ns: int) -> None:
+        """Test hook: one CTA of the update + encode launch waits `wait_ns` for a completion count that cannot
+        arrive, gives up and reports through the status word (b2_debug_muon_fused_wait_expiry)."""
+        check(self._lib.b2_debug_muon_fused_wait_expiry(self._handle, _ptr(slots), slot, wait_ns, _stream()),
+              "debug_muon_fused_wait_expiry")
+
     def scratch(self, slot: int, which: int) -> torch.Tensor:
         """View of a scratch buffer as a torch tensor (see b2_muon_plan_scratch)."""
         p, n = C.c_void_p(), C.c_size_t()
         check(self._lib.b2_muon_plan_scratch(self._handle, slot, which, C.byref(p), C.byref(n)), "muon_plan_scratch")
         off = p.value - self._buf.data_ptr()
         raw = self._buf[off:off + n.value]
-        rows, cols = self.shapes[slot] if which != 4 else (0, 0)
+        rows, cols = self.shapes[slot] if which not in (4, 10) else (0, 0)
         if which in (0, 7):
             dt = torch.float16 if self.options.operand_format == OPERAND_F16 else torch.bfloat16
             return raw.view(dt).view(rows, cols)
@@ -180,7 +190,7 @@ class MuonPlan:
             dt = torch.float16 if self.options.operand_format == OPERAND_F16 else torch.bfloat16
             n_ = min(rows, cols)
             return raw.view(dt).view(n_, -1)[:, :n_]
-        if which == 4:
+        if which in (4, 10):
             return raw.view(torch.int32)
         return raw.view(torch.float32)
 

@@ -25,6 +25,9 @@
 #include "oracle.h"
 
 #include <math.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
 #include <stdlib.h>
 #include <string.h>
 
@@ -672,6 +675,22 @@ void orc_sign_update(float *grad_inout_y, uint16_t *momentum_bf16, uint16_t *var
     amax[0] = ax; amax[1] = ay;
 }
 
+/* Number of host threads the OpenMP loops below use (0 = leave the runtime's default). */
+void orc_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+int orc_max_threads(void) {
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+
 /* Stage N scalar: crates/cuda-kernels/src/gpt/optimizer/muon/polar/fused/normalize.rs:8-9,82-86. */
 float orc_inv_norm(float sumsq, int contract) {
     float r = sqrtf(sumsq);
@@ -745,6 +764,17 @@ static void round_into(const float *src, float *dst, size_t n, int mode) {
  * staging (.../polar/fused/stage.rs:51-55,74-83).  X is [n][m] row-major with n <= m,
  * overwritten with the result.  coeffs holds `iterations` triples (a, b, c). */
 void orc_polar_gram(float *X, int n, int m, int iterations, const float *coeffs, int round_mode) {
+    orc_polar_gram_scaled(X, n, m, iterations, coeffs, round_mode, 1.0f);
+}
+
+/* The same recurrence with the Frobenius normalisation deferred into the first iteration
+ * (the one-pass form of stages M+N in the CUDA library): X arrives UN-normalised, is rounded to
+ * 16 bits as it is, and s = 1 / (1.01 |X| + 1e-7) enters through the first iteration's outputs,
+ *     G = (s * s) * (r16(X) r16(X)^T),   X1 = s * (r16(Q) r16(X)),
+ * which is algebraically the reference's normalize.rs:137-143 followed by fused.rs:64-92 but rounds the
+ * operand before instead of after the scaling.  first_scale = 1 gives the reference's order. */
+void orc_polar_gram_scaled(float *X, int n, int m, int iterations, const float *coeffs, int round_mode,
+                           float first_scale) {
     size_t nm = (size_t)n * m, nn = (size_t)n * n;
     float *Xr = (float *)malloc(nm * 4), *G = (float *)malloc(nn * 4);
     float *Gr = (float *)malloc(nn * 4), *Q = (float *)malloc(nn * 4);
@@ -753,6 +783,11 @@ void orc_polar_gram(float *X, int n, int m, int iterations, const float *coeffs,
         float a = coeffs[3 * it], b = coeffs[3 * it + 1], c = coeffs[3 * it + 2];
         round_into(X, Xr, nm, round_mode);
         gemm_nt(Xr, Xr, G, n, n, m);
+        if (it == 0 && first_scale != 1.0f) {
+            const float s2 = first_scale * first_scale;
+#pragma omp parallel for schedule(static)
+            for (size_t i = 0; i < nn; ++i) G[i] = G[i] * s2;
+        }
         round_into(G, Gr, nn, round_mode);
         gemm_nt(Gr, Gr, Q, n, n, n); /* G symmetric: G*G == G*G^T */
 #pragma omp parallel for schedule(static)
@@ -763,6 +798,10 @@ void orc_polar_gram(float *X, int n, int m, int iterations, const float *coeffs,
             }
         round_into(Q, Gr, nn, round_mode);
         gemm_nn(Gr, Xr, Y, n, m, n);
+        if (it == 0 && first_scale != 1.0f) {
+#pragma omp parallel for schedule(static)
+            for (size_t i = 0; i < nm; ++i) Y[i] = Y[i] * first_scale;
+        }
         memcpy(X, Y, nm * 4);
     }
     free(Xr); free(G); free(Gr); free(Q); free(Y);
@@ -772,11 +811,15 @@ void orc_polar_gram(float *X, int n, int m, int iterations, const float *coeffs,
  * recurrence on Y^T without materialising it: G = Y^T Y, Y <- Y Q.  (The CUDA library
  * works on the storage orientation; this mirrors its operand order.) */
 void orc_polar_gram_tall(float *Y, int m, int n, int iterations, const float *coeffs, int round_mode) {
+    orc_polar_gram_tall_scaled(Y, m, n, iterations, coeffs, round_mode, 1.0f);
+}
+void orc_polar_gram_tall_scaled(float *Y, int m, int n, int iterations, const float *coeffs, int round_mode,
+                                float first_scale) {
     size_t nm = (size_t)n * m;
     float *Xt = (float *)malloc(nm * 4);
     for (int i = 0; i < m; ++i)
         for (int j = 0; j < n; ++j) Xt[(size_t)j * m + i] = Y[(size_t)i * n + j];
-    orc_polar_gram(Xt, n, m, iterations, coeffs, round_mode);
+    orc_polar_gram_scaled(Xt, n, m, iterations, coeffs, round_mode, first_scale);
     for (int i = 0; i < m; ++i)
         for (int j = 0; j < n; ++j) Y[(size_t)i * n + j] = Xt[(size_t)j * m + i];
     free(Xt);
@@ -966,9 +1009,13 @@ uint64_t orc_muon_step(float *grad_inout_y, uint16_t *momentum, float *z, float 
     double s = orc_momentum(grad_inout_y, momentum, u, len, p->mu, p->grad_scale, p->nesterov,
                             p->contract);
     float inv = orc_inv_norm((float)s, p->contract);
-    for (uint64_t i = 0; i < len; ++i) u[i] = u[i] * inv;
-    if (rows > cols) orc_polar_gram_tall(u, (int)rows, (int)cols, p->iterations, p->coeffs, p->round_mode);
-    else orc_polar_gram(u, (int)rows, (int)cols, p->iterations, p->coeffs, p->round_mode);
+    float first_scale = 1.0f;
+    if (p->deferred_normalize) first_scale = inv;   /* one-pass prepare: s enters through iteration 0 */
+    else for (uint64_t i = 0; i < len; ++i) u[i] = u[i] * inv;
+    if (rows > cols)
+        orc_polar_gram_tall_scaled(u, (int)rows, (int)cols, p->iterations, p->coeffs, p->round_mode, first_scale);
+    else
+        orc_polar_gram_scaled(u, (int)rows, (int)cols, p->iterations, p->coeffs, p->round_mode, first_scale);
     if (U_out) memcpy(U_out, u, len * 4);
     float amax[2];
     orc_update(u, z, x, grad_inout_y, len, rows, cols, p->learning_rate, p->weight_decay,

@@ -24,7 +24,8 @@ typedef struct orc_muon_params {
     int32_t round_mode;  /* ORC_ROUND_* applied to every GEMM operand */
     int32_t contract;    /* 1: a*b+c expressions fused to FMA */
     int32_t quantize_y;  /* 0: quantise x' (mega path); 1: quantise y */
-    int32_t reserved;
+    int32_t deferred_normalize; /* 1: operands rounded before the Frobenius scaling, which enters through the
+                                   first iteration (orc_polar_gram_scaled); 0: the reference's order */
     const float *coeffs; /* iterations x (a, b, c) */
 } orc_muon_params;
 
@@ -79,6 +80,12 @@ void orc_hyperball_update(const float *U, float *z, float *x, float *y, uint16_t
                           uint32_t offset, uint32_t head_dim, float *amax);
 void orc_polar_gram(float *X, int n, int m, int iterations, const float *coeffs, int round_mode);
 void orc_polar_gram_tall(float *Y, int m, int n, int iterations, const float *coeffs, int round_mode);
+void orc_polar_gram_scaled(float *X, int n, int m, int iterations, const float *coeffs, int round_mode,
+                           float first_scale);
+void orc_polar_gram_tall_scaled(float *Y, int m, int n, int iterations, const float *coeffs, int round_mode,
+                                float first_scale);
+void orc_set_threads(int n);
+int orc_max_threads(void);
 void orc_polar_three_product(float *X, int n, int m, int iterations, const float *coeffs,
                              int round_mode);
 void orc_update(const float *U, float *z, float *x, float *y, uint64_t len, uint32_t rows,

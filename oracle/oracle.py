@@ -39,7 +39,7 @@ class _MuonParams(C.Structure):
         ("mu", C.c_float), ("grad_scale", C.c_float), ("learning_rate", C.c_float),
         ("weight_decay", C.c_float), ("average_coefficient", C.c_float), ("schedule_beta", C.c_float),
         ("iterations", C.c_int32), ("nesterov", C.c_int32), ("round_mode", C.c_int32),
-        ("contract", C.c_int32), ("quantize_y", C.c_int32), ("reserved", C.c_int32),
+        ("contract", C.c_int32), ("quantize_y", C.c_int32), ("deferred_normalize", C.c_int32),
         ("coeffs", C.POINTER(C.c_float)),
     ]
 
@@ -87,6 +87,10 @@ def lib() -> C.CDLL:
             "orc_polar_gram": (None, [f32p, C.c_int, C.c_int, C.c_int, f32p, C.c_int]),
             "orc_polar_gram_tall": (None, [f32p, C.c_int, C.c_int, C.c_int, f32p, C.c_int]),
             "orc_polar_three_product": (None, [f32p, C.c_int, C.c_int, C.c_int, f32p, C.c_int]),
+            "orc_polar_gram_scaled": (None, [f32p, C.c_int, C.c_int, C.c_int, f32p, C.c_int, C.c_float]),
+            "orc_polar_gram_tall_scaled": (None, [f32p, C.c_int, C.c_int, C.c_int, f32p, C.c_int, C.c_float]),
+            "orc_set_threads": (None, [C.c_int]),
+            "orc_max_threads": (C.c_int, []),
             "orc_update": (None, [f32p, f32p, f32p, f32p, C.c_uint64, C.c_uint32, C.c_uint32] + [C.c_float] * 4 + [C.c_int, f32p]),
             "orc_schedule_free_values": (C.c_float, [f32p, f32p, f32p, C.c_uint64, C.c_float, C.c_int]),
             "orc_adamw": (C.c_float, [f32p, f32p, f32p, f32p, f32p, f32p, C.c_uint64] + [C.c_float] * 10 + [C.c_int]),
@@ -348,18 +352,26 @@ def inv_norm(sumsq, contract=False) -> np.float32:
     return np.float32(lib().orc_inv_norm(np.float32(sumsq), int(contract)))
 
 
-def polar(X, iterations, coeffs, round_mode=ROUND_BF16, form="gram"):
-    """Newton-Schulz on a storage-layout matrix [rows][cols]; returns a new array."""
+def set_threads(n: int) -> int:
+    """Host threads for the OpenMP loops (the CPU-baseline legs of bench.py); returns the count in effect."""
+    lib().orc_set_threads(int(n))
+    return int(lib().orc_max_threads())
+
+
+def polar(X, iterations, coeffs, round_mode=ROUND_BF16, form="gram", first_scale=1.0):
+    """Newton-Schulz on a storage-layout matrix [rows][cols]; returns a new array.  `first_scale` != 1:
+    X is un-normalised and the Frobenius scale enters through the first iteration (one-pass prepare)."""
     X = _f32(X).copy()
     rows, cols = X.shape
     co = _f32(coeffs).reshape(-1)
     assert co.size >= 3 * iterations
     L = lib()
     if form == "gram":
+        fs = np.float32(first_scale)
         if rows > cols:
-            L.orc_polar_gram_tall(_p(X, C.c_float), rows, cols, iterations, _p(co, C.c_float), round_mode)
+            L.orc_polar_gram_tall_scaled(_p(X, C.c_float), rows, cols, iterations, _p(co, C.c_float), round_mode, fs)
         else:
-            L.orc_polar_gram(_p(X, C.c_float), rows, cols, iterations, _p(co, C.c_float), round_mode)
+            L.orc_polar_gram_scaled(_p(X, C.c_float), rows, cols, iterations, _p(co, C.c_float), round_mode, fs)
         return X
     assert form == "three_product"
     if rows > cols:
@@ -430,14 +442,14 @@ class MuonResult:
 
 def muon_step(grad, momentum_bits, z, x, rows, cols, *, mu, grad_scale, lr, wd, c_avg, sched_beta,
               iterations, coeffs, nesterov=True, round_mode=ROUND_BF16, contract=False,
-              quantize_y=False, rcp_table=None) -> MuonResult:
+              quantize_y=False, rcp_table=None, deferred_normalize=False) -> MuonResult:
     g = _f32(grad).reshape(-1).copy()
     m = np.ascontiguousarray(momentum_bits, dtype=np.uint16).reshape(-1).copy()
     z = _f32(z).reshape(-1).copy(); x = _f32(x).reshape(-1).copy()
     n = rows * cols
     co = _f32(coeffs).reshape(-1)
     prm = _MuonParams(mu, grad_scale, lr, wd, c_avg, sched_beta, iterations, int(nesterov), round_mode,
-                      int(contract), int(quantize_y), 0, _p(co, C.c_float))
+                      int(contract), int(quantize_y), int(deferred_normalize), _p(co, C.c_float))
     codes = np.zeros(n // 2, dtype=np.uint8); sc = np.zeros(n // 16, dtype=np.uint8)
     gs = C.c_float(0); sa = C.c_float(0)
     U = np.zeros(n, dtype=np.float32)

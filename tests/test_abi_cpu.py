@@ -86,6 +86,48 @@ def test_argument_validation():
     assert L.b2_muon_workspace_bytes(rows, cols, 1, None) == 0
     cols = (C.c_uint32 * 1)(48)  # CSF needs a multiple of 128
     assert L.b2_muon_workspace_bytes(rows, cols, 1, None) == 0
-    opt = _ffi.MuonOptions(0, _ffi.SCALES_RAW, 0, 5, (C.c_uint32 * 4)())
+    opt = _ffi.MuonOptions(0, _ffi.SCALES_RAW, 0, 5, 0, 0, 0, 0)
     assert L.b2_muon_workspace_bytes(rows, cols, 1, C.byref(opt)) > 0
     assert L.b2_muon_workspace_bytes(rows, cols, 0, None) == 0
+
+
+def test_sizes_beyond_the_32_bit_limits_are_refused():
+    # elements and 2048-value chunks are indexed in 32 bits and GEMM tile indices in 16: anything larger is
+    # refused up front instead of wrapping inside a kernel
+    L = b2.lib()
+    INVALID = _ffi.ERROR_INVALID_VALUE
+    raw = _ffi.MuonOptions(0, _ffi.SCALES_RAW, 0, 5, 0, 0, 0, 0)
+    one = lambda r, c: ((C.c_uint32 * 1)(r), (C.c_uint32 * 1)(c))
+    rows, cols = one(16 * 1024 * 1024, 16)          # 131072 row tiles of 128: beyond a 16-bit tile index
+    assert L.b2_muon_workspace_bytes(rows, cols, 1, C.byref(raw)) == 0
+    rows, cols = one(65535 * 128, 16)               # the largest admissible extent
+    assert L.b2_muon_workspace_bytes(rows, cols, 1, C.byref(raw)) > 0
+    rows, cols = one(65536, 65536)                  # 2^32 elements
+    assert L.b2_muon_workspace_bytes(rows, cols, 1, C.byref(raw)) == 0
+    big = 0xfffff800                                 # (len + 2047) / 2048 would wrap in 32 bits
+    fake = 4096                                      # never dereferenced: the size check comes first
+    assert L.b2_tensor_amax_f32(fake, fake, fake, big, None) == INVALID
+    assert L.b2_materialize_master(fake, fake, fake, fake, fake, fake, big, _ffi.SCALES_RAW, None) == INVALID
+    assert L.b2_fp32_to_nvfp4_four_six(fake, fake, fake, fake, fake, big // 16, _ffi.SCALES_RAW, None) == INVALID
+    assert L.b2_materialize_master_static(fake, fake, fake, fake, (1 << 26) + 16, _ffi.SCALES_RAW, None) == INVALID
+    sf = _ffi.ScheduleFreeMaterializeArgs(fake, fake, fake, fake, fake, None, fake, big, 1 << 16, 1 << 16, 0.5, 0.0,
+                                          _ffi.SCALES_RAW, (C.c_void_p * 6)())
+    assert L.b2_materialize_schedule_free(C.byref(sf), None) == INVALID
+    ad = _ffi.AdamWUpdateArgs()
+    ad.z_master = ad.x_master = ad.grad = ad.first_moment = ad.second_moment = fake
+    ad.len = big
+    assert L.b2_apply_fp32_adamw_update(C.byref(ad), None) == INVALID
+    t = (_ffi.AdamWSlotDescriptor * 1)()
+    t[0].z_master = t[0].x_master = t[0].grad = t[0].first_moment = t[0].second_moment = fake
+    t[0].len = big
+    total = C.c_uint32(0)
+    assert L.b2_adamw_table_prepare(t, 1, C.byref(total)) == INVALID
+
+
+def test_one_pass_prepare_is_refused_for_f16_operands():
+    L = b2.lib()
+    rows, cols = (C.c_uint32 * 1)(64), (C.c_uint32 * 1)(64)
+    opt = _ffi.MuonOptions(_ffi.OPERAND_F16, _ffi.SCALES_RAW, 0, 5, 0, 0, 0, _ffi.NORMALIZE_DEFERRED)
+    h = C.c_void_p()
+    n = L.b2_muon_workspace_bytes(rows, cols, 1, C.byref(opt))
+    assert L.b2_muon_plan_create(C.byref(h), rows, cols, 1, C.byref(opt), 1024, n, None) == _ffi.ERROR_INVALID_VALUE

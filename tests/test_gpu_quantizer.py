@@ -77,9 +77,15 @@ def test_flat_quantiser_bit_exact(rows, k, layout):
     q = b2.Nvfp4QuantModule()
     l4, ls, lg = q.debug_quantize_literal(dev(x), dev(np.array([amax], F)))
     assert np.array_equal(host(l4), fp4) and np.array_equal(host(ls), raw) and host(lg)[0] == gs
-    # how often the correctly rounded reciprocal would have differed (reported, not asserted)
+    # The oracle on its own, with the correctly rounded reciprocal in place of the device's `rcp.approx.ftz`:
+    # a result can differ only where v * inv sits within an ulp of an E2M1 rounding boundary, or the block
+    # maximum within an ulp of an E4M3 tie.  Measured: 1 code in 16.7 M values, no scale byte.  Held here at
+    # two codes per 2^24 values (rounded up to a whole value for small tensors) and no scale byte.
     c2, r2, _, _ = o.nvfp4_quantize(x, amax=amax)
-    print(f"exact-rcp mismatches: codes {int(np.count_nonzero(c2 != codes))} scales {int(np.count_nonzero(r2 != raw))} of {x.size}")
+    code_diff = int(np.count_nonzero((c2 & 0xF) != (codes & 0xF)) + np.count_nonzero((c2 >> 4) != (codes >> 4)))
+    scale_diff = int(np.count_nonzero(r2 != raw))
+    print(f"exact-rcp mismatches: codes {code_diff} scales {scale_diff} of {x.size}")
+    assert code_diff <= 2 * -(-x.size // (1 << 24)) and scale_diff == 0
 
 
 def test_all_zero_tensor_and_empty():

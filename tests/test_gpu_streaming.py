@@ -56,6 +56,51 @@ def test_prepare_matches_oracle(shapes, layout):
     plan.close()
 
 
+@pytest.mark.parametrize("variance_adaptive", [False, True])
+def test_one_pass_prepare_matches_oracle(variance_adaptive):
+    # NORMALIZE_DEFERRED: momentum state bit-exact, operand = r16(u) without the Frobenius scale, the scale
+    # itself within 1e-6 of the oracle's
+    rng = np.random.default_rng(12)
+    shapes = [(64, 128), (300, 1040), (0, 0), (7, 16), (256, 64)]
+    opt = b2.OptimizerModule()
+    slots = [b2.MuonSlot.allocate(r, c, b2.SCALES_RAW) for r, c in shapes]
+    inputs = []
+    for s, (r, c) in zip(slots, shapes):
+        g = U.gradients(rng, r * c)
+        m = o.bf16_bits(U.weights(rng, r * c, 1e-3))
+        v = o.bf16_bits(np.abs(U.weights(rng, r * c, 1e-6)) + F(1e-8))
+        _fill_slot(s, g, m, np.zeros(r * c, F), np.zeros(r * c, F))
+        if variance_adaptive:
+            s.variance = bf16_from_bits(v).view(r, c) if r * c else None
+        inputs.append((g, m, v))
+    plan = b2.MuonPlan(shapes, scale_layout=b2.SCALES_RAW, normalize_mode=b2.NORMALIZE_DEFERRED)
+    table = b2.slot_table(slots)
+    for s in slots:   # the prepare pass clears both maxima of every slot
+        s.schedule_amax.fill_(7.0)
+    for nesterov in (True, False):
+        args = b2.MuonMegaUpdateArgs(mu=0.9, grad_scale=0.125, iterations=1, nesterov=nesterov,
+                                     variance_adaptive=variance_adaptive, bias_correction_inv=1.25)
+        opt.muon_tma_prepare_polar(plan, table, args)
+        torch.cuda.synchronize()
+        for i, (s, (r, c)) in enumerate(zip(slots, shapes)):
+            if r * c == 0:
+                continue
+            g, m, v = inputs[i]
+            if variance_adaptive:
+                m2, v2, u, ss = o.momentum_vs(g, m, v, 0.9, 0.125, nesterov, 1.25)
+                assert np.array_equal(bf16_bits(s.variance).ravel(), v2)
+            else:
+                m2, u, ss = o.momentum(g, m, 0.9, 0.125, nesterov=nesterov)
+                v2 = v
+            assert np.array_equal(bf16_bits(s.momentum).ravel(), m2)
+            inv = o.inv_norm(ss)
+            assert abs(host(plan.scratch(i, 2))[0] - inv) <= 1e-6 * inv
+            assert np.array_equal(host(plan.scratch(i, 0).float()).ravel(), o.round_bf16(u))
+            assert host(s.schedule_amax)[0] == 0.0 and host(plan.scratch(i, 3))[0] == 0.0
+            inputs[i] = (g, m2, v2)
+    plan.close()
+
+
 def test_momentum_chain_reference_case():
     # crates/cuda-kernels/tests/optimizer/muon/tma_prepare.rs:87-208 (non-variance branch)
     opt = b2.OptimizerModule()
