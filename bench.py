@@ -272,6 +272,12 @@ class GpuJob:
         self.torch, self.b2 = torch, b2
         self.name, self.world, self.rank, self.dev = name, world, rank, dev
         self.mats, emb, vec = model_shapes(name)
+        if args.shard_of > 1 and world == 1:
+            # measurement aid: this GPU plays rank 0 of an N-way sharded run (its matrices and its slice of the
+            # embeddings), without the collective
+            own, _ = shard_plan(self.mats, args.shard_of)
+            self.mats = [m for m, r in zip(self.mats, own) if r == 0]
+            emb = [((rows + args.shard_of - 1) // args.shard_of // 128 * 128, cols) for rows, cols in emb]
         d_model = MODELS[name][1]
         layout = self.layout = b2.SCALES_CSF if d_model % 128 == 0 else b2.SCALES_RAW
         self.owner, _ = shard_plan(self.mats, world)
@@ -306,8 +312,11 @@ class GpuJob:
                 s.scales.copy_(headers[(r, c)])
             self.slots.append(s)
         self.normalize = b2.NORMALIZE_TWO_PASS if args.two_pass_prepare else b2.NORMALIZE_DEFERRED
+        self.schedule = b2.NS_CHAINED if args.ns_chained else b2.NS_PER_PHASE
+        self.update_input = b2.UPDATE_16BIT if args.update_16bit else b2.UPDATE_F32
         self.plan = b2.MuonPlan(self.my_shapes, scale_layout=layout, device=dev, debug_flags=args.plan_flags,
-                                normalize_mode=self.normalize) if self.my_shapes else None
+                                normalize_mode=self.normalize, ns_schedule=self.schedule,
+                                update_input=self.update_input) if self.my_shapes else None
         self.table = b2.slot_table(self.slots, dev) if self.slots else None
         self.opt = b2.OptimizerModule()
         self.margs = b2.MuonMegaUpdateArgs(coefficients=np.tile(np.asarray(FIXED_TRIPLE, np.float32), (5, 1)), **HP)
@@ -341,7 +350,8 @@ class GpuJob:
         self.launches_per_step = 0
         if self.plan is not None:
             prepare = 3 if self.normalize == b2.NORMALIZE_TWO_PASS else 2
-            self.launches_per_step += prepare + 3 * HP["iterations"] + (2 if args.plan_flags & 16 else 1)
+            gemms = 1 if self.schedule == b2.NS_CHAINED else 3 * HP["iterations"]
+            self.launches_per_step += prepare + gemms + (2 if args.plan_flags & 16 else 1)
         self.launches_per_step += 3 if self.adam_sets else 0
         self.gather_stream = torch.cuda.Stream(device=dev) if world > 1 else None
         self.stage_events = []
@@ -430,8 +440,10 @@ class GpuJob:
         flops = ns_flops(self.my_shapes, HP["iterations"])
         rate = lambda units, ms: units / (ms * 1e-3) if ms > 0 else 0.0
         ns_tflops = rate(flops, ns_ms) / 1e12
-        # stage U+Q: reads U,z,x; writes z,x,y(schedule cache),codes,scales = 24.5625 B per element
-        fin_gbs = rate(elems * 24.5625, fin_ms) / 1e9
+        # stage U+Q: reads U,z,x; writes z,x,y(schedule cache),codes,scales = 24.5625 B per element (22.5625 when the
+        # Newton-Schulz result arrives in 16 bits)
+        fin_bytes = 22.5625 if self.update_input else 24.5625
+        fin_gbs = rate(elems * fin_bytes, fin_ms) / 1e9
         prep_gbs = rate(elems * 10.0, prep_ms) / 1e9
         adam_elems = sum(t["len"] for _, t in self.adam_sets)
         adam_gbs = rate(adam_elems * 36.0, adam_ms) / 1e9
@@ -442,6 +454,8 @@ class GpuJob:
             "update_quantise_gbs": fin_gbs, "update_quantise_frac_of_hbm": fin_gbs / peaks["hbm"],
             "adamw_gbs": adam_gbs, "hbm_peak_gbs": peaks["hbm"], "update_quantise_frac_of_nominal_8000": fin_gbs / 8000.0,
             "prepare": "one pass (scale folded into the first iteration)" if self.normalize else "two passes (reference rounding point)",
+            "newton_schulz": "one chained launch for the whole loop" if self.schedule else "three launches per iteration",
+            "update_quantise_bytes_per_element": fin_bytes,
         }
 
     # -- checks -----------------------------------------------------------------------------
@@ -499,7 +513,8 @@ class GpuJob:
         bad = []
         if not np.array_equal(host(s.momentum.view(torch.int16)).view(np.uint16).ravel(), ref.momentum_bits):
             bad.append("momentum")
-        Ug = host(self.plan.scratch(i, 1))
+        # five iterations: the 16-bit result, when that is what stage U reads, is in the second operand buffer
+        Ug = host(self.plan.scratch(i, 7).float()) if self.update_input else host(self.plan.scratch(i, 1))
         rel = float(np.linalg.norm(Ug.astype(np.float64) - ref.U) / np.linalg.norm(ref.U.astype(np.float64)))
         if not rel <= 2e-2:
             bad.append(f"Newton-Schulz rel L2 {rel:.3e}")
@@ -766,7 +781,9 @@ def run_gpu(args):
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": workload_config(args.workload, world),
         "roofline": {
-            "bound": "tensor", "kernel": "k_ns_gemm (15 launches per step)", "achieved": ns_tflops,
+            "bound": "tensor", "kernel": "k_ns_gemm (all 15 GEMMs of the step" + (" as one chained launch)" if args.ns_chained else
+                                                                                  ", one launch each)"),
+            "achieved": ns_tflops,
             "peak": peaks["tf_burst"], "unit": "TFLOP/s", "frac": ns_tflops / peaks["tf_burst"],
             "traffic": profiled_traffic(args.workload, world),
             "peak_source": f"{peaks['source']} bf16 burst (timed region well under a second at full clocks)",
@@ -994,6 +1011,14 @@ def main():
     ap.add_argument("--two-pass-prepare", action="store_true",
                     help="stages M+N with the reference's rounding point (the gradients are read twice) instead of "
                          "the one-pass form")
+    ap.add_argument("--ns-chained", action="store_true",
+                    help="Newton-Schulz as one chained persistent launch instead of three launches per iteration")
+    ap.add_argument("--update-16bit", action="store_true",
+                    help="the last Newton-Schulz iteration stores BF16 and the update reads it (default: FP32, as the "
+                         "reference's update input)")
+    ap.add_argument("--shard-of", type=int, default=1,
+                    help="with one GPU: run rank 0's share of an N-way sharded step (no collective), to time the "
+                         "per-rank kernels of a multi-GPU run")
     ap.add_argument("--plan-flags", type=int, default=0,
                     help="kernel variants of a library built with -DB2_MEASURE (ignored otherwise)")
     ap.add_argument("--sweep", action="store_true", help="update+quantise bandwidth sweep over [R, 4096] tensors")

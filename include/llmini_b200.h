@@ -31,7 +31,7 @@
 extern "C" {
 #endif
 
-#define B2_ABI_VERSION 1u
+#define B2_ABI_VERSION 2u
 /* crates/cuda-kernels/src/gpt/optimizer/storage.rs:4 (MUON_STORAGE_LAYOUT_VERSION) */
 #define B2_MUON_STORAGE_LAYOUT_VERSION 1u
 
@@ -93,6 +93,27 @@ enum { B2_QUANTIZE_X = 0, B2_QUANTIZE_Y = 1 };
  *   Newton-Schulz iteration, which is linear in it (G = s^2 X0 X0^T, X1 = s Q X0).  Same algebra, the operand
  *   is rounded before instead of after the scaling; BF16 operands only. */
 enum { B2_NORMALIZE_TWO_PASS = 0, B2_NORMALIZE_DEFERRED = 1 };
+/* How the Newton-Schulz loop is launched.
+ * B2_NS_PER_PHASE: three launches per iteration (Gram, polynomial, apply), each over all matrices, chained with
+ *   programmatic dependent launch.
+ * B2_NS_CHAINED: every GEMM of every iteration of every matrix as ONE persistent grid (the reference runs its loop
+ *   inside one cooperative kernel with grid-wide barriers, .../muon/polar/fused.rs:64-92).  CTAs claim tiles
+ *   from one work list with an atomic ticket; a matrix's Gram, polynomial and apply tiles are ordered by a
+ *   progress count of that matrix instead of launch boundaries, so phases of different matrices overlap.  Used
+ *   when a step runs exactly `max_iterations` iterations (at most 8); other steps take the per-phase form.
+ *   Bit-identical results; measured equal to the per-phase form on one GPU and slower when a rank owns few
+ *   matrices, so it is not the default. */
+enum { B2_NS_PER_PHASE = 0, B2_NS_CHAINED = 1 };
+/* Precision in which the Newton-Schulz result reaches stage U.
+ * B2_UPDATE_F32: the last Apply GEMM stores FP32 (the reference's `polar_update` is f32:
+ *   crates/cuda-kernels/src/gpt/optimizer/muon/fused/update/one.rs:46-85).
+ * B2_UPDATE_16BIT: it stores the operand type (BF16 or F16) like the other iterations, and stage U reads that:
+ *   two bytes per element less to write and to read (18.56 instead of 20.56 bytes per element in the
+ *   update + quantise pass, before the schedule cache).  The update direction carries one more 16-bit rounding.
+ *   Plain finish entry points only (b2_muon_finish_update[_deferred_quantization], b2_muon_mega_update): steps
+ *   with NorMuon scaling or the Hyperball finish, whose statistics read the FP32 result, are refused with
+ *   B2_ERROR_NOT_SUPPORTED. */
+enum { B2_UPDATE_F32 = 0, B2_UPDATE_16BIT = 1 };
 
 typedef struct b2_muon_options {
     uint32_t operand_format;  /* B2_OPERAND_*: 16-bit type the Newton-Schulz GEMM operands are
@@ -108,6 +129,9 @@ typedef struct b2_muon_options {
     uint32_t measure_phase_mask; /* leave 0.  Read only by a library built with -DB2_MEASURE: which GEMMs of an */
     uint32_t measure_flags;      /* iteration run, and kernel variants used to attribute time */
     uint32_t normalize_mode;  /* B2_NORMALIZE_* */
+    uint32_t ns_schedule;     /* B2_NS_* */
+    uint32_t update_input;    /* B2_UPDATE_* */
+    uint32_t reserved[2];     /* must be 0 */
 } b2_muon_options;
 
 /* Step scalars: `MuonMegaUpdateArgs` (.../optimizer/args/muon.rs:25-44) and
@@ -202,13 +226,15 @@ int b2_muon_sign_update_deferred_quantization(b2_muon_plan *plan, const b2_muon_
                                               const b2_muon_step_args *args, void *stream);
 /* Scratch views for tests and tracing (the reference's `MUON_TMA_TRACE`,
  * src/training/optimizer_muon/tma.rs:1210-1276).  which: 0 = X0 (16-bit, [rows][cols]),
- * 1 = Newton-Schulz result U (f32, [rows][cols]), 2 = inverse norm (f32[1]),
+ * 1 = Newton-Schulz result U (f32, [rows][cols]; with B2_UPDATE_16BIT the result is in the operand buffer 0 or 7
+ * that the last iteration wrote: 7 for an odd iteration count, 0 for an even one), 2 = inverse norm (f32[1]),
  * 3 = max|x'| (f32[1]), 4 = device status word (u32[1], plan-wide).
  * 5 = Gram (16-bit, [n][ld]) and 6 = polynomial Q (16-bit, [n][ld]) of the LAST iteration,
  * 7 = the second operand buffer X1, 8 = NorMuon factors (f32[max(rows, cols)]),
  * 9 = NorMuon / Hyperball slot scalars (f32[4]: normuon_scale, update_norm, radius, dot),
  * 10 = the ticket, abort and completion words of the one-launch update + encode (u32[4 + slots], plan-wide;
- * all zero between launches). */
+ * all zero between launches), 11 = the abort, exit and per-matrix progress words of the chained Newton-Schulz
+ * launch (u32[4 + slots], plan-wide; all zero between launches). */
 int b2_muon_plan_scratch(b2_muon_plan *plan, uint32_t slot, uint32_t which, void **d_ptr,
                          size_t *bytes);
 /* Reads back and clears the plan's device status word (synchronises `stream`): 0 when no

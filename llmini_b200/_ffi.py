@@ -17,6 +17,8 @@ SCALES_CSF, SCALES_RAW, SCALES_SM100 = 0, 1, 2
 OPERAND_BF16, OPERAND_F16 = 0, 1
 QUANTIZE_X, QUANTIZE_Y = 0, 1
 NORMALIZE_TWO_PASS, NORMALIZE_DEFERRED = 0, 1
+NS_PER_PHASE, NS_CHAINED = 0, 1
+UPDATE_F32, UPDATE_16BIT = 0, 1
 ERROR_INVALID_VALUE, ERROR_NOT_SUPPORTED, ERROR_LAUNCH_TIMEOUT = 1, 801, 702
 
 
@@ -35,7 +37,8 @@ class MuonSlotDescriptor(C.Structure):
 class MuonOptions(C.Structure):
     _fields_ = [("operand_format", C.c_uint32), ("scale_layout", C.c_uint32), ("quantize_target", C.c_uint32),
                 ("max_iterations", C.c_uint32), ("tile_override", C.c_uint32), ("measure_phase_mask", C.c_uint32),
-                ("measure_flags", C.c_uint32), ("normalize_mode", C.c_uint32)]
+                ("measure_flags", C.c_uint32), ("normalize_mode", C.c_uint32), ("ns_schedule", C.c_uint32),
+                ("update_input", C.c_uint32), ("reserved", C.c_uint32 * 2)]
 
 
 class MuonStepArgs(C.Structure):

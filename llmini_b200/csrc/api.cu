@@ -117,14 +117,16 @@ struct Layout {
     std::vector<uint32_t> chunk_prefix;  // slot_count + 1
     std::vector<uint32_t> unit_prefix;   // slot_count + 1: NorMuon work units (32 rows or 128 columns)
     std::vector<uint32_t> items;         // work list of the fused update + encode launch
+    uint32_t chain_tiles = 0;            // entries of the chained Newton-Schulz work list (0: not built)
+    uint32_t chain_iterations = 0;
     uint32_t total_chunks = 0;
     int bn = 256;
     int pair = 0;   // 1: two-CTA 256 x 256 tiles
     int symmetric = 0;  // 1: Gram / Poly compute the upper triangle of tiles only
     int tile_m = 128;
-    size_t off_prefix, off_partials, off_inv_norm, off_amax_x, off_status, off_x0_ptrs, off_u_ptrs, off_maps,
+    size_t off_prefix, off_partials, off_inv_norm, off_amax_x, off_status, off_x0_ptrs, off_x1_ptrs, off_u_ptrs, off_maps,
         off_problems, off_tiles_nn, off_tiles_out, off_unit_prefix, off_factor_ptrs, off_unit_partials, off_slot_stats,
-        off_items, off_fused_sync, off_meta_end, total;
+        off_items, off_fused_sync, off_chain, off_chain_sync, off_meta_end, total;
     uint32_t tiles_nn = 0, tiles_out = 0;
 };
 
@@ -200,6 +202,7 @@ bool build_layout(const uint32_t *rows, const uint32_t *cols, uint32_t count, co
     L.off_prefix = take((count + 1) * sizeof(uint32_t));
     L.off_x0_ptrs = take(count * sizeof(uint64_t));
     L.off_u_ptrs = take(count * sizeof(uint64_t));
+    L.off_x1_ptrs = take(count * sizeof(uint64_t));
     // Fused update + encode: update chunks in slot order; the encode spans (B2_FUSED_ENCODE_SPAN
     // chunks each) of a matrix become eligible kLag update chunks after its last one -- late enough
     // that they never wait in practice, early enough that the updated weights are still in L2 -- and
@@ -248,15 +251,24 @@ bool build_layout(const uint32_t *rows, const uint32_t *cols, uint32_t count, co
     }
     L.off_tiles_nn = take((size_t)std::max(L.tiles_nn, 1u) * sizeof(GemmTile));
     L.off_tiles_out = take((size_t)std::max(L.tiles_out, 1u) * sizeof(GemmTile));
+    // the whole Newton-Schulz loop as one work list, for the iteration count the plan is made for
+    L.chain_iterations = 0;
+    L.chain_tiles = 0;
+    if (o.ns_schedule == B2_NS_CHAINED && o.max_iterations <= kMaxChainIterations && count <= 0xffffu) {
+        L.chain_iterations = o.max_iterations;
+        L.chain_tiles = o.max_iterations * (2 * L.tiles_nn + L.tiles_out);
+    }
+    L.off_chain = take((size_t)std::max(L.chain_tiles, 1u) * sizeof(ChainTile));
     L.off_meta_end = off;
     // ---- per-step scratch ----
-    L.off_partials = take((size_t)std::max(chunks, 1u) * sizeof(double));
+    L.off_partials = take((size_t)std::max(chunks, 1u) * B2_ONE_PASS_PARTIALS * sizeof(double));
     L.off_inv_norm = take(count * sizeof(float));
     L.off_amax_x = take(count * sizeof(float));
     L.off_status = take(sizeof(uint32_t));
     L.off_unit_partials = take((size_t)std::max(L.unit_prefix[count], 1u) * 4 * sizeof(double));
     L.off_slot_stats = take((size_t)count * 4 * sizeof(float));
     L.off_fused_sync = take(fused_sync_bytes(count));
+    L.off_chain_sync = take(chain_sync_bytes(count));
     for (uint32_t s = 0; s < count; ++s) {
         SlotLayout &sl = L.slots[s];
         if (sl.len == 0) continue;
@@ -361,7 +373,7 @@ int b2_muon_plan_create(b2_muon_plan **out, const uint32_t *rows, const uint32_t
     if (reinterpret_cast<uintptr_t>(d_workspace) % 1024 != 0) return B2_ERROR_INVALID_VALUE;
     b2_muon_options o = normalized(options);
     if (o.operand_format > B2_OPERAND_F16 || o.scale_layout > B2_SCALES_SM100 || o.quantize_target > B2_QUANTIZE_Y ||
-        o.normalize_mode > B2_NORMALIZE_DEFERRED)
+        o.normalize_mode > B2_NORMALIZE_DEFERRED || o.ns_schedule > B2_NS_CHAINED || o.update_input > B2_UPDATE_16BIT)
         return B2_ERROR_INVALID_VALUE;
     // an un-normalised update can leave F16's range: the one-pass prepare is for BF16 operands
     if (o.normalize_mode == B2_NORMALIZE_DEFERRED && o.operand_format != B2_OPERAND_BF16) return B2_ERROR_INVALID_VALUE;
@@ -381,6 +393,7 @@ int b2_muon_plan_create(b2_muon_plan **out, const uint32_t *rows, const uint32_t
     std::memcpy(h + L.off_prefix, L.chunk_prefix.data(), (slot_count + 1) * sizeof(uint32_t));
     uint64_t *x0p = reinterpret_cast<uint64_t *>(h + L.off_x0_ptrs);
     uint64_t *up = reinterpret_cast<uint64_t *>(h + L.off_u_ptrs);
+    uint64_t *x1p = reinterpret_cast<uint64_t *>(h + L.off_x1_ptrs);
     uint64_t *fp = reinterpret_cast<uint64_t *>(h + L.off_factor_ptrs);
     std::memcpy(h + L.off_unit_prefix, L.unit_prefix.data(), (slot_count + 1) * sizeof(uint32_t));
     if (!L.items.empty()) std::memcpy(h + L.off_items, L.items.data(), L.items.size() * sizeof(uint32_t));
@@ -396,6 +409,7 @@ int b2_muon_plan_create(b2_muon_plan **out, const uint32_t *rows, const uint32_t
         p->flops_per_iteration += slot_flops(sl.rows, sl.cols);
         x0p[s] = reinterpret_cast<uint64_t>(p->ws + sl.off_x[0]);
         up[s] = reinterpret_cast<uint64_t>(p->ws + sl.off_u);
+        x1p[s] = reinterpret_cast<uint64_t>(p->ws + sl.off_x[1]);
         fp[s] = reinterpret_cast<uint64_t>(p->ws + sl.off_factors);
         CUtensorMap *ms = maps + (size_t)s * kMapsPerSlot;
         const uint64_t xp = (uint64_t)sl.cols * 2, gp = (uint64_t)sl.ldg * 2;
@@ -480,8 +494,45 @@ int b2_muon_plan_create(b2_muon_plan **out, const uint32_t *rows, const uint32_t
         for (uint32_t i = 0; i < tm; ++i)
             for (uint32_t j = 0; j < tn; ++j) tout[iout++] = GemmTile{(uint16_t)s, (uint16_t)i, (uint16_t)j, 0};
     }
+    if (L.chain_tiles) {
+        // Phase after phase, iteration after iteration, each phase in the order of its per-phase list.  `need`
+        // of a tile = progress increments of its matrix's earlier phases (every tile is finished by `warps`
+        // epilogue warps).
+        ChainTile *ct = reinterpret_cast<ChainTile *>(h + L.off_chain);
+        const uint32_t warps = chain_epilogue_warps(L.bn, L.pair);
+        std::vector<uint32_t> done(slot_count, 0), nn_tiles(slot_count, 0), out_tiles(slot_count, 0);
+        for (uint32_t i = 0; i < inn; ++i) ++nn_tiles[tnn[i].problem];
+        for (uint32_t i = 0; i < iout; ++i) ++out_tiles[tout[i].problem];
+        const bool deferred = o.normalize_mode == B2_NORMALIZE_DEFERRED;
+        uint32_t n = 0;
+        auto emit = [&](const GemmTile &t, uint32_t type, uint32_t epi, uint32_t scale_pow, uint32_t it) {
+            ChainTile c;
+            c.problem = type * slot_count + t.problem;
+            c.tile_m = t.tile_m;
+            c.tile_n = t.tile_n;
+            c.slot = t.problem;
+            c.epilogue = (uint8_t)epi;
+            c.flags = (uint8_t)((t.reserved ? 1u : 0u) | (scale_pow << 1) | (it << 3));
+            c.need = warps * done[t.problem];
+            ct[n++] = c;
+        };
+        for (uint32_t it = 0; it < L.chain_iterations; ++it) {
+            const uint32_t b = it & 1u;
+            const bool last32 = it + 1 == L.chain_iterations && o.update_input == B2_UPDATE_F32;   // FP32 result
+            const bool first_scaled = it == 0 && deferred;
+            for (uint32_t i = 0; i < inn; ++i) emit(tnn[i], kGram0 + b, kEpiGram, first_scaled ? 2u : 0u, it);
+            for (uint32_t s = 0; s < slot_count; ++s) done[s] += nn_tiles[s];
+            for (uint32_t i = 0; i < inn; ++i) emit(tnn[i], kPoly, kEpiPoly, 0u, it);
+            for (uint32_t s = 0; s < slot_count; ++s) done[s] += nn_tiles[s];
+            for (uint32_t i = 0; i < iout; ++i)
+                emit(tout[i], (last32 ? kLast0 : kApply0) + b, last32 ? kEpiApplyLast : kEpiApply, first_scaled ? 1u : 0u, it);
+            for (uint32_t s = 0; s < slot_count; ++s) done[s] += out_tiles[s];
+        }
+    }
     e = cudaMemcpyAsync(p->ws, h, L.off_meta_end, cudaMemcpyHostToDevice, as_stream(stream));
     if (e == cudaSuccess) e = cudaMemsetAsync(p->ws + L.off_status, 0, sizeof(uint32_t), as_stream(stream));
+    if (e == cudaSuccess)
+        e = cudaMemsetAsync(p->ws + L.off_chain_sync, 0, chain_sync_bytes(slot_count), as_stream(stream));
     if (e == cudaSuccess)
         e = cudaMemsetAsync(p->ws + L.off_fused_sync, 0, fused_sync_bytes(slot_count), as_stream(stream));
     if (e != cudaSuccess) { delete p; return (int)e; }
@@ -511,6 +562,7 @@ static MomentumParams momentum_params(const b2_muon_step_args *a) {
 }
 static UpdateParams update_params(const b2_muon_step_args *a) {
     UpdateParams up;
+    up.update_format = 0;
     up.lr = a->learning_rate;
     up.wd = a->weight_decay;
     up.c_avg = a->average_coefficient;
@@ -537,11 +589,11 @@ int b2_muon_prepare_polar(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_s
         // one pass over the gradients; the scalar goes to the first Newton-Schulz iteration (b2_muon_polar)
         cudaError_t e = launch_muon_momentum_sumsq(v, mp, plan->at<uint64_t>(L.off_x0_ptrs), partials,
                                                    plan->at<float>(L.off_amax_x), s);
-        if (e == cudaSuccess) e = launch_muon_inv_norm(v, partials, inv, s);
+        if (e == cudaSuccess) e = launch_muon_inv_norm(v, partials, inv, B2_ONE_PASS_PARTIALS, s);
         return (int)e;
     }
     cudaError_t e = launch_muon_sumsq(v, mp, partials, plan->at<float>(L.off_amax_x), s);
-    if (e == cudaSuccess) e = launch_muon_inv_norm(v, partials, inv, s);
+    if (e == cudaSuccess) e = launch_muon_inv_norm(v, partials, inv, 1u, s);
     if (e == cudaSuccess)
         e = launch_muon_momentum_normalize(v, mp, inv, plan->at<uint64_t>(L.off_x0_ptrs),
                                            plan->options.operand_format == B2_OPERAND_F16, s);
@@ -560,6 +612,24 @@ int b2_muon_polar(b2_muon_plan *plan, const b2_muon_step_args *a, void *stream) 
     const int f16 = plan->options.operand_format == B2_OPERAND_F16;
     const int grid = plan->dev.sm_count;
     cudaError_t e = cudaSuccess;
+    bool whole_loop = L.chain_tiles != 0 && a->iterations == L.chain_iterations;
+#ifdef B2_MEASURE
+    if (plan->options.measure_phase_mask) whole_loop = false;
+#endif
+    if (whole_loop) {
+        // every GEMM of every iteration as one grid, ordered by per-matrix progress counts
+        GemmCoefficients coef = {};
+        for (uint32_t it = 0; it < a->iterations; ++it) {
+            if (a->coefficients) {
+                for (int k = 0; k < 3; ++k) coef.v[3 * it + k] = a->coefficients[3 * it + k];
+            } else {
+                reference_coefficients(it, coef.v[3 * it], coef.v[3 * it + 1], coef.v[3 * it + 2]);
+            }
+        }
+        const float *scale = plan->options.normalize_mode == B2_NORMALIZE_DEFERRED ? plan->at<float>(L.off_inv_norm) : nullptr;
+        return (int)launch_ns_chain(L.bn, L.pair, probs, plan->at<ChainTile>(L.off_chain), L.chain_tiles, f16, coef, scale,
+                                    status, plan->ws + L.off_chain_sync, count, plan->options.measure_flags, grid, s);
+    }
     for (uint32_t it = 0; it < a->iterations && e == cudaSuccess; ++it) {
         float ca, cb, cc;
         if (a->coefficients) {
@@ -568,7 +638,7 @@ int b2_muon_polar(b2_muon_plan *plan, const b2_muon_step_args *a, void *stream) 
             reference_coefficients(it, ca, cb, cc);
         }
         const uint32_t b = it & 1u;
-        const bool last = it + 1 == a->iterations;
+        const bool last = it + 1 == a->iterations && plan->options.update_input == B2_UPDATE_F32;   // FP32 result
         // measurement builds only: phase mask (1 Gram, 2 Poly, 4 Apply; 0 = all) and kernel flags
         const uint32_t mask = plan->options.measure_phase_mask ? plan->options.measure_phase_mask : 7u;
         const uint32_t dbg = plan->options.measure_flags;
@@ -598,6 +668,14 @@ static int finish_impl(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_slot
     float *amax_x = plan->at<float>(L.off_amax_x);
     UpdateParams up = update_params(a);
     cudaError_t e = cudaSuccess;
+    // where the Newton-Schulz result is: the FP32 buffer, or the 16-bit operand buffer the last iteration wrote
+    const uint64_t *u_ptrs = plan->at<uint64_t>(L.off_u_ptrs);
+    if (plan->options.update_input == B2_UPDATE_16BIT) {
+        if (a->normuon) return B2_ERROR_NOT_SUPPORTED;
+        if (a->iterations == 0 || a->iterations > plan->options.max_iterations) return B2_ERROR_INVALID_VALUE;
+        u_ptrs = plan->at<uint64_t>((a->iterations & 1u) ? L.off_x1_ptrs : L.off_x0_ptrs);
+        up.update_format = plan->options.operand_format == B2_OPERAND_F16 ? 2 : 1;
+    }
     if (a->normuon) {
         const NeuronView nv = plan->neurons();
         e = launch_normuon_stats(v, nv, plan->at<uint64_t>(L.off_u_ptrs), 0, s);
@@ -611,12 +689,12 @@ static int finish_impl(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_slot
         up.symexp_beta == 0.0f) {
         if (e == cudaSuccess)
             e = launch_muon_update_encode(v, plan->at<uint32_t>(L.off_items), (uint32_t)L.items.size(),
-                                          plan->at<uint64_t>(L.off_u_ptrs), amax_x, up, quantize_y,
+                                          u_ptrs, amax_x, up, quantize_y,
                                           (int)plan->options.scale_layout, plan->ws + L.off_fused_sync,
                                           plan->at<uint32_t>(L.off_status), plan->fused_wait_ns, s);
         return (int)e;
     }
-    if (e == cudaSuccess) e = launch_muon_update(v, plan->at<uint64_t>(L.off_u_ptrs), amax_x, up, s);
+    if (e == cudaSuccess) e = launch_muon_update(v, u_ptrs, amax_x, up, s);
     if (e == cudaSuccess && quantize)
         e = launch_muon_encode(v, amax_x, quantize_y, (int)plan->options.scale_layout, s);
     return (int)e;
@@ -641,6 +719,7 @@ int b2_muon_finish_hyperball_update_deferred_quantization(b2_muon_plan *plan, co
                                                           const b2_muon_step_args *a, uint32_t use_schedule_free,
                                                           void *stream) {
     if (!plan || !a || !d_slots) return B2_ERROR_INVALID_VALUE;
+    if (plan->options.update_input != B2_UPDATE_F32) return B2_ERROR_NOT_SUPPORTED;   // its statistics read FP32
     const Layout &L = plan->layout;
     cudaStream_t s = as_stream(stream);
     SlotView v = plan->view(d_slots);
@@ -679,6 +758,11 @@ int b2_muon_plan_scratch(b2_muon_plan *plan, uint32_t slot, uint32_t which, void
     if (!plan || !d_ptr || !bytes) return B2_ERROR_INVALID_VALUE;
     const Layout &L = plan->layout;
     if (which == 4) { *d_ptr = plan->ws + L.off_status; *bytes = 4; return B2_SUCCESS; }
+    if (which == 11) {
+        *d_ptr = plan->ws + L.off_chain_sync;
+        *bytes = chain_sync_bytes((uint32_t)L.slots.size());
+        return B2_SUCCESS;
+    }
     if (which == 10) {
         *d_ptr = plan->ws + L.off_fused_sync;
         *bytes = fused_sync_bytes((uint32_t)L.slots.size());

@@ -40,6 +40,7 @@ struct UpdateParams {
     int normuon;                   // 1: scale U by factor[neuron] * normuon_scale
     const uint64_t *factor_ptrs;
     const float *slot_stats;
+    int update_format;             // how `u_ptrs` buffers hold the Newton-Schulz result: 0 f32, 1 bf16, 2 f16
     float symexp_beta;             // > 0: SymExpLin forward on y, scales from the slot table (or unit)
     const b2_symexp_lin_slot_descriptor *symexp_slots;
 };
@@ -48,8 +49,10 @@ cudaError_t launch_muon_sumsq(const SlotView &v, const MomentumParams &mp, doubl
 // One-pass form of stages M+N: momentum state, un-normalised BF16 operand and the chunk sums in one launch.
 cudaError_t launch_muon_momentum_sumsq(const SlotView &v, const MomentumParams &mp, const uint64_t *x0_ptrs,
                                        double *partials, float *amax_x, cudaStream_t s);
+// `partials_per_chunk`: 1 after launch_muon_sumsq, B2_ONE_PASS_PARTIALS after launch_muon_momentum_sumsq.
+#define B2_ONE_PASS_PARTIALS 8
 cudaError_t launch_muon_inv_norm(const SlotView &v, const double *partials, float *inv_norm,
-                                 cudaStream_t s);
+                                 uint32_t partials_per_chunk, cudaStream_t s);
 cudaError_t launch_muon_momentum_normalize(const SlotView &v, const MomentumParams &mp, const float *inv_norm,
                                            const uint64_t *x0_ptrs, int f16, cudaStream_t s);
 cudaError_t launch_muon_update(const SlotView &v, const uint64_t *u_ptrs, float *amax_x, const UpdateParams &up,
@@ -145,6 +148,27 @@ struct GemmTile {
 constexpr int kGemmBlockM = 128;
 constexpr int kGemmBlockK = 64;
 
+// Polynomial coefficients (a, b, c) per Newton-Schulz iteration, passed by value to the kernel.
+constexpr uint32_t kMaxChainIterations = 8;
+struct GemmCoefficients {
+    float v[3 * kMaxChainIterations];
+};
+// One entry of the work list of the chained launch, which runs every GEMM of every iteration of the plan's
+// matrices as ONE grid: `need` is the value the matrix's progress count (epilogue warps that have finished a
+// tile of the matrix, over all earlier phases) must have reached before this tile's operands are read.  A
+// matrix's phases follow one another strictly (Gram -> Poly -> Apply -> next Gram), so one count per matrix
+// orders every read after the writes it depends on, and every overwrite after the reads of the old contents.
+struct alignas(16) ChainTile {
+    uint32_t problem;      // index into the plan's GemmProblem array (type * slot_count + slot)
+    uint16_t tile_m, tile_n;
+    uint16_t slot;
+    uint8_t epilogue;      // GemmEpilogue
+    uint8_t flags;         // bit 0: also store the transposed tile; bits 1-2: power of the slot scale applied to
+                           // the accumulator (one-pass prepare); bits 3-7: iteration (coefficient triple)
+    uint32_t need;
+};
+static_assert(sizeof(ChainTile) == 16, "ChainTile is read as one 16-byte word");
+
 cudaError_t gemm_configure(int block_n, int pair);
 // `slot_scale` (may be null): per-slot scalars s; the Gram epilogue multiplies the accumulator by s^scale_pow
 // (scale_pow = 2) and the Apply epilogues by s (scale_pow = 1).  Used by the first iteration after a
@@ -153,5 +177,14 @@ cudaError_t launch_ns_gemm(int block_n, int pair, const GemmProblem *problems, c
                            uint32_t tile_count, uint32_t epilogue, int f16, float ca, float cb,
                            float cc, const float *slot_scale, uint32_t scale_pow, uint32_t *status,
                            uint32_t debug_flags, int grid, cudaStream_t s);
+
+// The chained launch (see ChainTile).  `sync` is chain_sync_bytes(slot_count) of device memory, zeroed once by
+// the owner; every launch leaves it zeroed.  chain_epilogue_warps: progress-count increments per finished tile.
+size_t chain_sync_bytes(uint32_t slot_count);
+uint32_t chain_epilogue_warps(int block_n, int pair);
+cudaError_t launch_ns_chain(int block_n, int pair, const GemmProblem *problems, const ChainTile *tiles,
+                            uint32_t tile_count, int f16, const GemmCoefficients &coef, const float *slot_scale,
+                            uint32_t *status, void *sync, uint32_t slot_count, uint32_t debug_flags, int grid,
+                            cudaStream_t s);
 
 }  // namespace b2

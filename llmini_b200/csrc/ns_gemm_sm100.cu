@@ -54,7 +54,7 @@ struct Cfg {
     static constexpr int kThreads = 32 * (2 + kEpiWarps);
     static constexpr int kStagingBytes = SLABS * kEpiWarps * kSlabBytes;
     static constexpr int kTmemCols = 2 * BN;
-    static constexpr int kBarrierBytes = 256;
+    static constexpr int kBarrierBytes = 512;   // mbarriers, flags, and the tile ring of the chained launch
     static constexpr int kStages = (kSmemLimit - kStagingBytes - kBarrierBytes - 1024) / kStageBytes;
     static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + kBarrierBytes + 1024;
     static constexpr int kTileM = PAIR ? 256 : 128;  // rows of the (cluster) tile
@@ -118,6 +118,86 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
     *abort_flag = 1;
     return false;
+}
+
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint32_t ld_relaxed_gpu(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+// orders this thread's generic-proxy accesses against its async-proxy ones (TMA loads and stores)
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
+// Chained launch: words shared by every CTA.  All zero between launches; the last CTA to leave clears them.
+struct ChainSync {
+    uint32_t abort;      // a bounded wait ran out somewhere: everybody leaves
+    uint32_t exited;
+    uint32_t ticket;     // next unclaimed entry of the work list
+    uint32_t reserved;
+    uint32_t progress[1];  // per slot: epilogue warps that have finished a tile of the slot, over all phases
+};
+// Bounded wait until `*counter >= need`.  Returns false when the limit ran out or the launch is aborting.
+//
+// How a tile's outputs reach the CTA that reads them.  The writer's epilogue warps wait for their TMA stores
+// to complete (cp.async.bulk.wait_group 0: the data is in L2), fence their plain stores (the FP32 Gram tile),
+// and only then raise the matrix's progress count with an atomic, which is performed at L2 as well.  The reader
+// polls the count with loads that bypass L1 and issues its first copy under a branch on the value it saw.  TMA
+// copies and ld.global.cg read L2, the one point every SM shares, so data that was there before the count rose
+// is what they get; no L1 line of the reader can hold an older copy.  A polling loop of acquire loads followed
+// by fence.proxy.async, which is what the PTX memory model's letter asks for between a generic-proxy flag and
+// async-proxy copies, drained the producer's copies in flight at every tile (measured: the chained launch took
+// 1.3x the time of the launches it replaces), so the reader relies on the control dependency instead.
+__device__ __forceinline__ bool chain_wait(const uint32_t *counter, uint32_t need, uint32_t *launch_abort,
+                                           volatile uint32_t *abort_flag) {
+    if (ld_relaxed_gpu(counter) >= need) return true;
+    const uint64_t start = global_timer_ns();
+#pragma unroll 1
+    for (uint32_t it = 0; it < kSpinLimit; ++it) {
+        if (ld_relaxed_gpu(counter) >= need) return true;
+        if (*abort_flag || ld_relaxed_gpu(launch_abort) != 0u) break;
+        if (global_timer_ns() - start > kWaitLimitNs) break;
+        __nanosleep(it >= 64 ? 128 : 20);
+    }
+    *abort_flag = 1;
+    atomicExch(launch_abort, 1u);
+    return false;
+}
+
+// Chained launch: which tile a CTA (pair) works on next is decided at run time (an atomic ticket over the work
+// list, claimed by the leader's producer thread), so the roles of the CTA, and the peer CTA of a pair, learn it
+// through a small ring in shared memory: entry k holds (k + 1) << 32 | tile for the k-th tile of this CTA.  No
+// role is ever more than stages + 2 tiles behind the producer, far less than the ring's length.
+constexpr uint32_t kTileRing = 16;
+constexpr uint32_t kNoTile = 0xffffffffu;
+__device__ __forceinline__ void ring_put_local(volatile uint64_t *ring, uint32_t seq, uint32_t tile) {
+    ring[seq % kTileRing] = ((uint64_t)(seq + 1u) << 32) | tile;
+}
+__device__ __forceinline__ void ring_put_remote(uint32_t ring_cluster_addr, uint32_t seq, uint32_t tile) {
+    const uint64_t v = ((uint64_t)(seq + 1u) << 32) | tile;
+    asm volatile("st.volatile.shared::cluster.u64 [%0], %1;" ::"r"(ring_cluster_addr + 8u * (seq % kTileRing)), "l"(v)
+                 : "memory");
+}
+// Bounded: gives kNoTile when the CTA is aborting or nothing arrives within the wait limit.
+__device__ __forceinline__ uint32_t ring_get(volatile uint64_t *ring, uint32_t seq, volatile uint32_t *abort_flag) {
+    const uint64_t want = (uint64_t)(seq + 1u);
+    uint64_t v = ring[seq % kTileRing];
+    if ((v >> 32) == want) return (uint32_t)v;
+    const uint64_t start = global_timer_ns();
+#pragma unroll 1
+    for (uint32_t it = 0; it < kSpinLimit; ++it) {
+        v = ring[seq % kTileRing];
+        if ((v >> 32) == want) return (uint32_t)v;
+        if (*abort_flag) return kNoTile;
+        if (global_timer_ns() - start > kWaitLimitNs) break;
+        __nanosleep(20);
+    }
+    *abort_flag = 1;
+    return kNoTile;
 }
 
 template <bool PAIR>
@@ -211,17 +291,58 @@ __device__ __forceinline__ uint32_t instr_desc(int m, int n, int f16, uint32_t a
            ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
-template <int BN, bool PAIR, int SLABS>
+// What one role needs to know about the tile it works on.  Plain launch: one GEMM flavour for the whole grid
+// (epilogue, coefficients and scaling are launch arguments).  Chained launch: every entry of the list carries
+// its own flavour, iteration and the progress count of its matrix that must be reached before its operands
+// may be read.
+struct TileWork {
+    uint32_t problem, tile_m, tile_n, mirror, epilogue, slot, need, scale_pow, iter;
+};
+template <bool CHAINED>
+__device__ __forceinline__ TileWork tile_work(const void *tiles, uint32_t t, uint32_t epilogue, uint32_t scale_pow) {
+    TileWork w;
+    if (CHAINED) {
+        const uint4 c = __ldg(reinterpret_cast<const uint4 *>(tiles) + t);
+        w.problem = c.x;
+        w.tile_m = c.y & 0xffffu;
+        w.tile_n = c.y >> 16;
+        w.slot = c.z & 0xffffu;
+        w.epilogue = (c.z >> 16) & 0xffu;
+        w.mirror = (c.z >> 24) & 1u;
+        w.scale_pow = (c.z >> 25) & 3u;
+        w.iter = (c.z >> 27) & 31u;
+        w.need = c.w;
+    } else {
+        const GemmTile tl = reinterpret_cast<const GemmTile *>(tiles)[t];
+        w.problem = tl.problem;
+        w.tile_m = tl.tile_m;
+        w.tile_n = tl.tile_n;
+        w.mirror = tl.reserved;
+        w.epilogue = epilogue;
+        w.slot = tl.problem;
+        w.need = 0;
+        w.scale_pow = scale_pow;
+        w.iter = 0;
+    }
+    return w;
+}
+
+template <int BN, bool PAIR, int SLABS, bool CHAINED>
 __global__ void __launch_bounds__((Cfg<BN, PAIR, SLABS>::kThreads), 1)
-k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__ tiles,
-          uint32_t tile_count, uint32_t epilogue, int f16, float ca, float cb, float cc,
-          const float *__restrict__ slot_scale, uint32_t scale_pow, uint32_t *status, uint32_t debug_flags) {
+k_ns_gemm(const GemmProblem *__restrict__ problems, const void *__restrict__ tiles,
+          uint32_t tile_count, uint32_t epilogue_arg, int f16, GemmCoefficients coef,
+          const float *__restrict__ slot_scale, uint32_t scale_pow_arg, uint32_t *status, ChainSync *sync,
+          uint32_t slot_count, uint32_t debug_flags) {
     using C = Cfg<BN, PAIR, SLABS>;
 #ifdef B2_MEASURE
     const bool dbg_no_store = debug_flags & 1u;   // drop every epilogue store
     const bool dbg_no_global = debug_flags & 8u;  // stage in shared memory but issue no global store
+    const bool dbg_reader_fence = debug_flags & 64u;   // chained: acquire + proxy fence after a dependency wait
+    const bool dbg_writer_fence = debug_flags & 128u;  // chained: proxy fence before a progress count is raised
+    const bool dbg_no_order = debug_flags & 256u;      // chained: neither wait nor publish (wrong results; timing only)
 #else
     constexpr bool dbg_no_store = false, dbg_no_global = false;
+    constexpr bool dbg_reader_fence = false, dbg_writer_fence = false, dbg_no_order = false;
     (void)debug_flags;
 #endif
     extern __shared__ uint8_t smem_raw[];
@@ -232,6 +353,10 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
     // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * C::kStages + 4);
     volatile uint32_t *abort_flag = tmem_slot + 1;
+    // chained: one more than the index of the last tile whose dependency wait this CTA's producer has passed
+    volatile uint32_t *passed_tile = tmem_slot + 2;
+    volatile uint64_t *tile_ring = reinterpret_cast<volatile uint64_t *>(reinterpret_cast<uint8_t *>(bars) + 256);
+    static_assert((2 * C::kStages + 4) * 8 + 16 <= 256 && 256 + kTileRing * 8 <= C::kBarrierBytes, "barrier region layout");
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -254,6 +379,8 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
             mbar_init(tempty_bar(a), PAIR ? 2 * C::kEpiWarps : C::kEpiWarps);
         }
         *abort_flag = 0;
+        *passed_tile = 0;
+        for (uint32_t k = 0; k < kTileRing; ++k) tile_ring[k] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_async_smem();
     }
@@ -284,8 +411,54 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            for (uint32_t t = first_tile; ok && t < tile_count; t += tile_stride) {
-                const GemmTile tl = tiles[t];
+            // Plain launch: tile first_tile + k * tile_stride.  Chained launch: the leader claims list entries in
+            // order with an atomic ticket (a tile only ever waits for tiles with smaller tickets, which running
+            // CTAs hold, so the launch makes progress however many CTAs are resident; the CTAs stay within one
+            // wave of each other in the list, which keeps a matrix's operands in L2 while its tiles are worked
+            // on; and a slower SM simply takes fewer tiles).  The ticket for the tile after next is claimed, and
+            // the next tile's description and progress count fetched, while this tile's copies are issued.
+            uint32_t seq = 0, t = first_tile, t_next = kNoTile;
+            const bool claims = CHAINED && (!PAIR || rank == 0);
+            const uint32_t peer_ring = (CHAINED && PAIR) ? map_to_cta(smem_u32(const_cast<uint64_t *>(tile_ring)), 1) : 0u;
+            auto announce = [&](uint32_t tile) {   // leader: tell this CTA's roles (and the peer CTA) the seq-th tile
+                ring_put_local(tile_ring, seq, tile);
+                if (PAIR) ring_put_remote(peer_ring, seq, tile);
+            };
+            if (CHAINED) {
+                if (claims) {
+                    t = atomicAdd(&sync->ticket, 1u);
+                    announce(t);
+                    if (t < tile_count) t_next = atomicAdd(&sync->ticket, 1u);
+                } else {
+                    t = ring_get(tile_ring, seq, abort_flag);
+                }
+            }
+            TileWork next = {};
+            uint32_t next_seen = 0;
+            if (t < tile_count) {
+                next = tile_work<CHAINED>(tiles, t, epilogue_arg, scale_pow_arg);
+                if (CHAINED && next.need != 0u) next_seen = ld_relaxed_gpu(&sync->progress[next.slot]);
+            }
+            while (ok && t < tile_count) {
+                const TileWork tl = next;
+                const uint32_t seen = next_seen;
+                const uint32_t t_now = t;
+                // the tile after this one
+                if (!CHAINED) {
+                    t += tile_stride;
+                } else if (claims) {
+                    t = t_next;
+                    ++seq;
+                    announce(t);
+                    if (t < tile_count) t_next = atomicAdd(&sync->ticket, 1u);
+                } else {
+                    ++seq;
+                    t = ring_get(tile_ring, seq, abort_flag);
+                }
+                if (t < tile_count) {
+                    next = tile_work<CHAINED>(tiles, t, epilogue_arg, scale_pow_arg);
+                    if (CHAINED && next.need != 0u) next_seen = ld_relaxed_gpu(&sync->progress[next.slot]);
+                }
                 const GemmProblem *p = problems + tl.problem;
                 const uint64_t map_a = p->map_a, map_b = p->map_b;
                 const uint32_t a_mn = p->a_mn_major, b_mn = p->b_mn_major, K = p->K;
@@ -295,6 +468,17 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
                 // A diagonal tile of X X^T or G G: this CTA's 128 rows of B are its 128 rows of A, in
                 // the same shared-memory layout.  They are loaded once and the MMA reads them twice.
                 const bool shared_operand = PAIR && tl.tile_m == tl.tile_n && map_a == map_b && a_mn == b_mn;
+                if (CHAINED && tl.need != 0u && !dbg_no_order) {
+                    // the operands are the outputs of the matrix's previous phase: every tile of that phase
+                    // has been stored and published before the first copy is issued
+                    if (seen < tl.need &&
+                        !chain_wait(&sync->progress[tl.slot], tl.need, &sync->abort, abort_flag)) { ok = false; break; }
+                    if (dbg_reader_fence) {
+                        (void)ld_acquire_gpu(&sync->progress[tl.slot]);
+                        fence_proxy_async_all();
+                    }
+                }
+                if (CHAINED) *passed_tile = t_now + 1u;
                 const uint32_t stage_tx = shared_operand ? 2u * (uint32_t)kABytes
                                                          : (uint32_t)C::kStageBytes * (PAIR ? 2u : 1u);
                 for (int kb = 0; kb < num_kb; ++kb) {
@@ -331,8 +515,10 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
         if (lane == 0 && rank == 0) {
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
-            for (uint32_t t = first_tile; ok && t < tile_count; t += tile_stride) {
-                const GemmTile tl = tiles[t];
+            uint32_t seq = 0;
+            for (uint32_t t = CHAINED ? ring_get(tile_ring, 0u, abort_flag) : first_tile; ok && t < tile_count;
+                 t = CHAINED ? ring_get(tile_ring, ++seq, abort_flag) : t + tile_stride) {
+                const TileWork tl = tile_work<CHAINED>(tiles, t, epilogue_arg, scale_pow_arg);
                 const GemmProblem *p = problems + tl.problem;
                 const uint32_t a_mn = p->a_mn_major, b_mn = p->b_mn_major, K = p->K;
                 const int num_kb = (int)((K + kGemmBlockK - 1) / kGemmBlockK);
@@ -386,14 +572,40 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
         auto slab_next = [&]() { if (SLABS == 2) sb ^= 1u; };
         const uint32_t tempty_leader0 = PAIR ? map_to_cta(tempty_bar(0), 0) : tempty_bar(0);
         uint32_t acc = 0, acc_phase = 0;
-        for (uint32_t t = first_tile; t < tile_count; t += tile_stride) {
-            const GemmTile tl = tiles[t];
+        // Chained launch: a finished tile is published to the other CTAs by raising its matrix's progress count
+        // once this warp's stores have completed.  The wait for that completion is put off until the next tile's
+        // accumulator has been read (the stores then had that long to land) unless the next accumulator is not
+        // ready yet, in which case it is done first: a warp never blocks on other CTAs with a count unpublished.
+        constexpr uint32_t kNoSlot = 0xffffffffu;
+        uint32_t unpublished = kNoSlot;
+        auto publish = [&]() {
+            __syncwarp();
+            if (lane == 0 && !dbg_no_order) {
+                tma_store_wait_all();
+                if (dbg_writer_fence) fence_proxy_async_all();
+                __threadfence();
+                atomicAdd(&sync->progress[unpublished], 1u);
+            }
+            unpublished = kNoSlot;
+        };
+        uint32_t seq = 0;
+        for (uint32_t t = CHAINED ? ring_get(tile_ring, 0u, abort_flag) : first_tile; t < tile_count;
+             t = CHAINED ? ring_get(tile_ring, ++seq, abort_flag) : t + tile_stride) {
+            const TileWork tl = tile_work<CHAINED>(tiles, t, epilogue_arg, scale_pow_arg);
+            const uint32_t epilogue = tl.epilogue;
+            // the iteration's coefficient triple, picked without indexing the argument block by a register
+            float ca = coef.v[0], cb = coef.v[1], cc = coef.v[2];
+            if (CHAINED) {
+#pragma unroll
+                for (uint32_t i = 1; i < kMaxChainIterations; ++i)
+                    if (tl.iter == i) { ca = coef.v[3 * i]; cb = coef.v[3 * i + 1]; cc = coef.v[3 * i + 2]; }
+            }
             const GemmProblem *p = problems + tl.problem;
             const uint32_t M = p->M, N = p->N;
             const uint64_t map16 = p->map_out16, map32 = p->map_out32, map16t = p->map_out16t;
             // symmetric outputs (Gram, Poly): tiles below the diagonal are not computed; the tile
             // above writes them as its transpose (reference: tiles/symmetric.rs:76-92)
-            const bool mirror = tl.reserved != 0;
+            const bool mirror = tl.mirror != 0;
             const float4 *frag = reinterpret_cast<const float4 *>(p->frag32);
             // fragment scratch is indexed by 128-row sub-tiles
             const uint32_t sub_m = PAIR ? (uint32_t)tl.tile_m * 2 + rank : tl.tile_m;
@@ -408,24 +620,33 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
             // The polynomial epilogue needs the FP32 Gram tile: fetch the first 32 columns before
             // the accumulator is ready so the latency hides behind the MMAs.
             float4 g[8];
-            if (epilogue == kEpiPoly && !dbg_no_store) {
+            // chained: the Gram tile may be read early only if the matrix's Gram phase is already complete
+            bool g_fetched = epilogue == kEpiPoly && !dbg_no_store;
+            if (CHAINED && g_fetched) g_fetched = *passed_tile > t;   // this CTA's producer has seen the phase complete
+            if (g_fetched) {
 #pragma unroll
                 for (int j = 0; j < 8; ++j) g[j] = __ldcg(frag + (unit0 + j) * kGemmBlockM + row_in_tile);
             }
+            if (CHAINED && unpublished != kNoSlot && !mbar_try_wait(tfull_bar(acc), acc_phase)) publish();
 
             bool ready = mbar_wait(tfull_bar(acc), acc_phase, abort_flag);
             ready = __all_sync(0xffffffffu, ready);
             if (!ready) break;
             tc_fence_after();
+            if (CHAINED && epilogue == kEpiPoly && !dbg_no_store && !g_fetched) {
+                // the accumulator is complete, so the producer has seen the Gram phase complete
+#pragma unroll
+                for (int j = 0; j < 8; ++j) g[j] = __ldcg(frag + (unit0 + j) * kGemmBlockM + row_in_tile);
+            }
             const uint32_t taddr = tmem_base + ((uint32_t)(32 * q) << 16) + acc * BN + c0;
             const uint32_t tempty = tempty_leader0 + 8u * acc;
             const bool in_range = n0 + c0 < (int)N && slab_row0 < (int)M && !dbg_no_store;   // warp-uniform
             // One-pass prepare: the operand of the first iteration is the un-normalised update, and
             // s = 1 / (1.01 |u| + 1e-7) of the tile's matrix enters here: G = (s s) X X^T, X1 = s (Q X).
             float out_scale = 1.0f;
-            if (slot_scale != nullptr && epilogue != kEpiPoly) {
-                const float sv = __ldcg(slot_scale + tl.problem);
-                out_scale = scale_pow == 2u ? sv * sv : sv;
+            if (slot_scale != nullptr && tl.scale_pow != 0u && epilogue != kEpiPoly) {
+                const float sv = __ldcg(slot_scale + tl.slot);
+                out_scale = tl.scale_pow == 2u ? sv * sv : sv;
             }
             const bool scaled = out_scale != 1.0f;   // warp-uniform
 
@@ -442,6 +663,7 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
                         if (lane == 0) mbar_arrive_cluster(tempty);
                     }
                     if (!in_range || n0 + c0 + 32 * sub >= (int)N) continue;
+                    if (CHAINED && sub == 1 && unpublished != kNoSlot) publish();
                     if (scaled) {
 #pragma unroll
                         for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * out_scale);
@@ -512,6 +734,7 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
                     for (int j = 0; j < 16; ++j)
                         packed[16 * sub + j] = pack_operands(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]), f16);
                 }
+                if (CHAINED && unpublished != kNoSlot) publish();
                 if (in_range) {
                     slab_wait();
                     uint8_t *slab = slab_pair + sb * kSlabBytes;
@@ -549,9 +772,14 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
                     }
                 }
             }
+            if (CHAINED) {
+                if (unpublished != kNoSlot) publish();   // (a tile whose stores were all skipped)
+                unpublished = tl.slot;
+            }
             acc ^= 1u;
             if (acc == 0) acc_phase ^= 1u;
         }
+        if (CHAINED && unpublished != kNoSlot) publish();
         if (lane == 0) tma_store_wait_all();
         __syncwarp();
     }
@@ -565,6 +793,17 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
         __syncthreads();
     }
     if (PAIR) cluster_sync_all();  // neither CTA leaves while its peer may still touch it
+    if (CHAINED && threadIdx.x == 0) {
+        // leave the shared words as the next launch expects them
+        if (*abort_flag) atomicExch(&sync->abort, 1u);
+        __threadfence();
+        if (atomicAdd(&sync->exited, 1u) == gridDim.x - 1) {
+            for (uint32_t k = 0; k < slot_count; ++k) sync->progress[k] = 0;
+            sync->abort = 0;
+            sync->ticket = 0;
+            sync->exited = 0;
+        }
+    }
     if (warp == 1) {
         if (PAIR)
             asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
@@ -575,10 +814,11 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const GemmTile *__restrict__
     }
 }
 
-template <int BN, bool PAIR, int SLABS>
-cudaError_t launch_impl(const GemmProblem *problems, const GemmTile *tiles, uint32_t tile_count, uint32_t epilogue,
-                        int f16, float ca, float cb, float cc, const float *slot_scale, uint32_t scale_pow,
-                        uint32_t *status, uint32_t debug_flags, int grid, cudaStream_t s) {
+template <int BN, bool PAIR, int SLABS, bool CHAINED>
+cudaError_t launch_impl(const GemmProblem *problems, const void *tiles, uint32_t tile_count, uint32_t epilogue,
+                        int f16, const GemmCoefficients &coef, const float *slot_scale, uint32_t scale_pow,
+                        uint32_t *status, void *sync, uint32_t slot_count, uint32_t debug_flags, int grid,
+                        cudaStream_t s) {
     cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute attr[2];
     unsigned n_attr = 0;
@@ -610,38 +850,62 @@ cudaError_t launch_impl(const GemmProblem *problems, const GemmTile *tiles, uint
     cfg.blockDim = dim3((unsigned)Cfg<BN, PAIR, SLABS>::kThreads, 1, 1);
     cfg.dynamicSmemBytes = Cfg<BN, PAIR, SLABS>::kSmemBytes;
     cfg.stream = s;
-    return cudaLaunchKernelEx(&cfg, k_ns_gemm<BN, PAIR, SLABS>, problems, tiles, tile_count, epilogue, f16, ca, cb, cc,
-                              slot_scale, scale_pow, status, debug_flags);
+    return cudaLaunchKernelEx(&cfg, k_ns_gemm<BN, PAIR, SLABS, CHAINED>, problems, tiles, tile_count, epilogue, f16, coef,
+                              slot_scale, scale_pow, status, static_cast<ChainSync *>(sync), slot_count, debug_flags);
+}
+
+template <bool CHAINED>
+cudaError_t dispatch(int block_n, int pair, const GemmProblem *problems, const void *tiles, uint32_t tile_count,
+                     uint32_t epilogue, int f16, const GemmCoefficients &coef, const float *slot_scale,
+                     uint32_t scale_pow, uint32_t *status, void *sync, uint32_t slot_count, uint32_t debug_flags,
+                     int grid, cudaStream_t s) {
+    if (tile_count == 0) return cudaSuccess;
+    if (pair && block_n == 256)
+        return launch_impl<256, true, 1, CHAINED>(problems, tiles, tile_count, epilogue, f16, coef, slot_scale, scale_pow,
+                                                  status, sync, slot_count, debug_flags, grid, s);
+    if (!pair && block_n == 256)
+        return launch_impl<256, false, 1, CHAINED>(problems, tiles, tile_count, epilogue, f16, coef, slot_scale, scale_pow,
+                                                   status, sync, slot_count, debug_flags, grid, s);
+    if (!pair && block_n == 128)
+        return launch_impl<128, false, 1, CHAINED>(problems, tiles, tile_count, epilogue, f16, coef, slot_scale, scale_pow,
+                                                   status, sync, slot_count, debug_flags, grid, s);
+    return cudaErrorInvalidValue;
+}
+
+template <int BN, bool PAIR>
+cudaError_t configure_both() {
+    cudaError_t e = cudaFuncSetAttribute(k_ns_gemm<BN, PAIR, 1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg<BN, PAIR, 1>::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(k_ns_gemm<BN, PAIR, 1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                Cfg<BN, PAIR, 1>::kSmemBytes);
 }
 
 }  // namespace
 
 cudaError_t gemm_configure(int block_n, int pair) {
-    if (pair && block_n == 256) {
-        return cudaFuncSetAttribute(k_ns_gemm<256, true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    Cfg<256, true, 1>::kSmemBytes);
-    }
-    if (!pair && block_n == 256)
-        return cudaFuncSetAttribute(k_ns_gemm<256, false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    Cfg<256, false, 1>::kSmemBytes);
-    if (!pair && block_n == 128)
-        return cudaFuncSetAttribute(k_ns_gemm<128, false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    Cfg<128, false, 1>::kSmemBytes);
+    if (pair && block_n == 256) return configure_both<256, true>();
+    if (!pair && block_n == 256) return configure_both<256, false>();
+    if (!pair && block_n == 128) return configure_both<128, false>();
     return cudaErrorInvalidValue;
 }
 cudaError_t launch_ns_gemm(int block_n, int pair, const GemmProblem *problems, const GemmTile *tiles,
                            uint32_t tile_count, uint32_t epilogue, int f16, float ca, float cb,
                            float cc, const float *slot_scale, uint32_t scale_pow, uint32_t *status,
                            uint32_t debug_flags, int grid, cudaStream_t s) {
-    if (tile_count == 0) return cudaSuccess;
-    if (pair && block_n == 256) {
-        return launch_impl<256, true, 1>(problems, tiles, tile_count, epilogue, f16, ca, cb, cc, slot_scale, scale_pow, status, debug_flags, grid, s);
-    }
-    if (!pair && block_n == 256)
-        return launch_impl<256, false, 1>(problems, tiles, tile_count, epilogue, f16, ca, cb, cc, slot_scale, scale_pow, status, debug_flags, grid, s);
-    if (!pair && block_n == 128)
-        return launch_impl<128, false, 1>(problems, tiles, tile_count, epilogue, f16, ca, cb, cc, slot_scale, scale_pow, status, debug_flags, grid, s);
-    return cudaErrorInvalidValue;
+    GemmCoefficients coef = {};
+    coef.v[0] = ca; coef.v[1] = cb; coef.v[2] = cc;
+    return dispatch<false>(block_n, pair, problems, tiles, tile_count, epilogue, f16, coef, slot_scale, scale_pow, status,
+                           nullptr, 0u, debug_flags, grid, s);
+}
+size_t chain_sync_bytes(uint32_t slot_count) { return sizeof(ChainSync) + sizeof(uint32_t) * slot_count; }
+uint32_t chain_epilogue_warps(int block_n, int pair) { return (uint32_t)(4 * (block_n / 64)) * (pair ? 2u : 1u); }
+cudaError_t launch_ns_chain(int block_n, int pair, const GemmProblem *problems, const ChainTile *tiles,
+                            uint32_t tile_count, int f16, const GemmCoefficients &coef, const float *slot_scale,
+                            uint32_t *status, void *sync, uint32_t slot_count, uint32_t debug_flags, int grid,
+                            cudaStream_t s) {
+    return dispatch<true>(block_n, pair, problems, tiles, tile_count, 0u, f16, coef, slot_scale, 0u, status, sync,
+                          slot_count, debug_flags, grid, s);
 }
 
 }  // namespace b2

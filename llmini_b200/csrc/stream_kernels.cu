@@ -9,6 +9,8 @@
 // which is how the reference's Rust expressions behave.
 #include <algorithm>
 
+#include <cuda_fp16.h>
+
 #include "common.cuh"
 #include "internal.h"
 
@@ -170,10 +172,10 @@ k_muon_sumsq(const b2_muon_slot_descriptor *slots, const uint32_t *prefix, uint3
 // inv = 1 / (sqrt(S) * 1.01 + 1e-7)
 // (crates/cuda-kernels/src/gpt/optimizer/muon/polar/fused/normalize.rs:8-9,82-86).
 __global__ void __launch_bounds__(kThreads)
-k_muon_inv_norm(const uint32_t *prefix, const double *partials, float *inv_norm) {
+k_muon_inv_norm(const uint32_t *prefix, const double *partials, float *inv_norm, uint32_t per_chunk) {
     __shared__ double warp_part[kThreads / 32];
     const uint32_t s = blockIdx.x;
-    const uint32_t begin = prefix[s], end = prefix[s + 1];
+    const uint32_t begin = prefix[s] * per_chunk, end = prefix[s + 1] * per_chunk;
     double acc = 0.0;
     for (uint32_t c = begin + threadIdx.x; c < end; c += kThreads) acc += partials[c];
     acc = warp_sum(acc);
@@ -223,26 +225,27 @@ k_muon_momentum_normalize(const b2_muon_slot_descriptor *slots, const uint32_t *
 }
 
 // Stages M+N in ONE pass over the gradients: BF16 momentum state, the UN-normalised 16-bit operand
-// X0 = r16(u) in the storage layout, and the chunk's sum of u^2 (taken over the FP32 u, as
-// normalize.rs:35-79 does).  The Frobenius scale s = 1 / (1.01 |u| + 1e-7) is not known until every chunk of
-// the matrix has been summed, so it is left to the first Newton-Schulz iteration, which is linear in it:
-// G = (s s) X0 X0^T and X1 = s (Q X0) (the Gram and Apply epilogues multiply by the slot's scalar).  10 bytes
-// per element cross the memory interface instead of 16.  The operand is rounded before instead of after the
-// scaling, which is not the reference's rounding point; the two-pass kernels above keep that one.  BF16
-// operands only: an un-normalised F16 operand could leave F16's range.
-// Two chunks per trip, like k_muon_sumsq.  Also clears the two amax words of each slot.
+// X0 = r16(u) in the storage layout, and the sum of u^2 (taken over the FP32 u, as normalize.rs:35-79 does).
+// The Frobenius scale s = 1 / (1.01 |u| + 1e-7) is not known until every chunk of the matrix has been
+// summed, so it is left to the first Newton-Schulz iteration, which is linear in it: G = (s s) X0 X0^T and
+// X1 = s (Q X0) (the Gram and Apply epilogues multiply by the slot's scalar).  10 bytes per element cross
+// the memory interface instead of 16.  The operand is rounded before instead of after the scaling, which is
+// not the reference's rounding point; the two-pass kernels above keep that one.  BF16 operands only: an
+// un-normalised F16 operand could leave F16's range.
+// Every warp leaves its own f64 partial per chunk (kThreads / 32 per chunk, summed in a fixed order by
+// k_muon_inv_norm), so no CTA-wide barrier sits between a chunk's loads and the next chunk's.  Two chunks
+// per trip keep eight 128-bit loads per thread in flight.  Also clears the two amax words of each slot.
+constexpr uint32_t kWarpsPerCta = kThreads / 32;
+static_assert(kWarpsPerCta == B2_ONE_PASS_PARTIALS, "partials per chunk of the one-pass prepare");
 template <int VS>
-__global__ void __launch_bounds__(kThreads, VS ? 4 : 6)
+__global__ void __launch_bounds__(kThreads, VS ? 4 : 8)
 k_muon_momentum_sumsq(const b2_muon_slot_descriptor *slots, const uint32_t *prefix, uint32_t slot_count,
                       uint32_t total_chunks, MomentumParams mp, const uint64_t *x0_ptrs, double *partials,
                       float *amax_x) {
-    __shared__ double warp_part[2][kThreads / 32];
     const int tid = threadIdx.x;
     if (mp.d_grad_scale) mp.grad_scale = __ldg(mp.d_grad_scale);
     for (uint32_t c0 = 2 * blockIdx.x; c0 < total_chunks; c0 += 2 * gridDim.x) {
         float local[2] = {0.0f, 0.0f};
-        uint32_t reset_slot[2] = {0xffffffffu, 0xffffffffu};
-        uint64_t reset_amax[2] = {0, 0};
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
             const uint32_t c = c0 + k;
@@ -253,9 +256,9 @@ k_muon_momentum_sumsq(const b2_muon_slot_descriptor *slots, const uint32_t *pref
             uint16_t *var = reinterpret_cast<uint16_t *>(cx.d.variance);
             uint16_t *x0 = reinterpret_cast<uint16_t *>(x0_ptrs[cx.slot]);
             const uint32_t base = cx.local_chunk * kChunk;
-            if (cx.local_chunk == 0) {
-                reset_slot[k] = cx.slot;
-                reset_amax[k] = cx.d.schedule_amax;
+            if (cx.local_chunk == 0 && tid == 0) {
+                amax_x[cx.slot] = 0.0f;
+                *reinterpret_cast<float *>(cx.d.schedule_amax) = 0.0f;
             }
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
@@ -275,23 +278,10 @@ k_muon_momentum_sumsq(const b2_muon_slot_descriptor *slots, const uint32_t *pref
         }
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
+            if (c0 + k >= total_chunks) break;
             const double acc = warp_sum((double)local[k]);
-            if ((tid & 31) == 0) warp_part[k][tid >> 5] = acc;
+            if ((tid & 31) == 0) partials[(size_t)(c0 + k) * kWarpsPerCta + (tid >> 5)] = acc;
         }
-        __syncthreads();
-        if (tid < 2 && c0 + tid < total_chunks) {
-            double s = 0.0;
-#pragma unroll
-            for (int w = 0; w < kThreads / 32; ++w) s += warp_part[tid][w];
-            partials[c0 + tid] = s;
-            const uint32_t rs = tid == 0 ? reset_slot[0] : reset_slot[1];
-            const uint64_t ra = tid == 0 ? reset_amax[0] : reset_amax[1];
-            if (rs != 0xffffffffu) {
-                amax_x[rs] = 0.0f;
-                *reinterpret_cast<float *>(ra) = 0.0f;
-            }
-        }
-        __syncthreads();
     }
 }
 
@@ -343,12 +333,26 @@ __device__ __forceinline__ void neuron_factors(const ChunkCtx &cx, const UpdateP
 // 2048-value chunk, including the CTA's contribution to both maxima.  EXT = 1: NorMuon factors,
 // qk-clip or the SymExpLin transform are in play.  keep_y: y is the tensor that gets quantised
 // next, so y stays cacheable and x' is streamed; otherwise the other way round.
-template <int EXT>
+// UFMT: how the Newton-Schulz result arrives: 0 = FP32, 1 = BF16, 2 = F16 (the 16-bit output of an Apply GEMM,
+// two bytes per element less to write there and to read here).
+__device__ __forceinline__ float4 load_update16(const uint16_t *U, uint32_t i, int f16) {
+    uint2 w;
+    asm volatile("ld.global.cs.v2.u32 {%0, %1}, [%2];" : "=r"(w.x), "=r"(w.y) : "l"(U + i));
+    if (f16) {
+        const __half2 a = *reinterpret_cast<const __half2 *>(&w.x), b = *reinterpret_cast<const __half2 *>(&w.y);
+        const float2 fa = __half22float2(a), fb = __half22float2(b);
+        return make_float4(fa.x, fa.y, fb.x, fb.y);
+    }
+    return make_float4(bf16_bits_to_f32(w.x & 0xffffu), bf16_bits_to_f32(w.x >> 16), bf16_bits_to_f32(w.y & 0xffffu),
+                       bf16_bits_to_f32(w.y >> 16));
+}
+template <int EXT, int UFMT = 0>
 __device__ __forceinline__ void update_chunk(const ChunkCtx &cx, const uint64_t *u_ptrs, float *amax_x,
                                              const UpdateParams &up, bool keep_y, float *warp_ax, float *warp_ay) {
     const float lr = up.lr, wd = up.wd, c_avg = up.c_avg, beta = up.beta;
     const int tid = threadIdx.x;
     const float *U = reinterpret_cast<const float *>(u_ptrs[cx.slot]);
+    const uint16_t *U16 = reinterpret_cast<const uint16_t *>(u_ptrs[cx.slot]);
     float *z = reinterpret_cast<float *>(cx.d.z_master);
     float *x = reinterpret_cast<float *>(cx.d.x_master);
     float *y = reinterpret_cast<float *>(cx.d.grad);
@@ -365,7 +369,7 @@ __device__ __forceinline__ void update_chunk(const ChunkCtx &cx, const uint64_t 
     for (int h = 0; h < 2; ++h) {
         const uint32_t i = base + h * (kChunk / 2) + tid * 4;
         if (i < cx.len) {
-            lu[h] = ld_stream(U + i);
+            lu[h] = UFMT == 0 ? ld_stream(U + i) : load_update16(U16, i, UFMT == 2);
             lz[h] = ld_stream(z + i);
             lx[h] = ld_stream(x + i);
         }
@@ -446,14 +450,14 @@ __device__ __forceinline__ void update_chunk(const ChunkCtx &cx, const uint64_t 
     }
 }
 
-template <int EXT>
+template <int EXT, int UFMT>
 __global__ void __launch_bounds__(kThreads, 5)
 k_muon_update(const b2_muon_slot_descriptor *slots, const uint32_t *prefix, uint32_t slot_count,
               uint32_t total_chunks, const uint64_t *u_ptrs, float *amax_x, UpdateParams up) {
     __shared__ float warp_ax[kThreads / 32], warp_ay[kThreads / 32];
     for (uint32_t c = blockIdx.x; c < total_chunks; c += gridDim.x) {
         ChunkCtx cx = chunk_ctx(slots, prefix, slot_count, c);
-        update_chunk<EXT>(cx, u_ptrs, amax_x, up, false, warp_ax, warp_ay);
+        update_chunk<EXT, UFMT>(cx, u_ptrs, amax_x, up, false, warp_ax, warp_ay);
         __syncthreads();
     }
 }
@@ -1085,6 +1089,7 @@ struct FusedSync {   // all zero between launches: the last CTA to leave clears 
 constexpr uint32_t kItemEncode = 0x80000000u;
 constexpr uint32_t kEncodeSpan = B2_FUSED_ENCODE_SPAN;  // chunks per encode item (list built by the plan)
 
+template <int UFMT>
 __global__ void __launch_bounds__(kThreads, 5)
 k_muon_update_encode(const b2_muon_slot_descriptor *slots, const uint32_t *prefix, uint32_t slot_count,
                      const uint32_t *items, uint32_t item_count, const uint64_t *u_ptrs, float *amax_x,
@@ -1105,7 +1110,7 @@ k_muon_update_encode(const b2_muon_slot_descriptor *slots, const uint32_t *prefi
         const uint32_t c = item & ~kItemEncode;
         ChunkCtx cx = chunk_ctx(slots, prefix, slot_count, c);
         if (!(item & kItemEncode)) {
-            update_chunk<0>(cx, u_ptrs, amax_x, up, quantize_y != 0, warp_ax, warp_ay);
+            update_chunk<0, UFMT>(cx, u_ptrs, amax_x, up, quantize_y != 0, warp_ax, warp_ay);
             // Publish.  The barrier orders every thread's stores before thread 0's fence, which is
             // cumulative; thread 0 raised the two maxima before it.  (Letting the other warps run
             // ahead of the fence, or publishing one item late, both measured slower.)
@@ -1613,9 +1618,9 @@ cudaError_t launch_muon_momentum_sumsq(const SlotView &v, const MomentumParams &
     return cudaGetLastError();
 }
 cudaError_t launch_muon_inv_norm(const SlotView &v, const double *partials, float *inv_norm,
-                                 cudaStream_t s) {
+                                 uint32_t partials_per_chunk, cudaStream_t s) {
     if (v.slot_count == 0) return cudaSuccess;
-    k_muon_inv_norm<<<v.slot_count, kThreads, 0, s>>>(v.chunk_prefix, partials, inv_norm);
+    k_muon_inv_norm<<<v.slot_count, kThreads, 0, s>>>(v.chunk_prefix, partials, inv_norm, partials_per_chunk);
     return cudaGetLastError();
 }
 cudaError_t launch_muon_momentum_normalize(const SlotView &v, const MomentumParams &mp, const float *inv_norm,
@@ -1632,12 +1637,15 @@ cudaError_t launch_muon_momentum_normalize(const SlotView &v, const MomentumPara
 cudaError_t launch_muon_update(const SlotView &v, const uint64_t *u_ptrs, float *amax_x, const UpdateParams &up,
                                cudaStream_t s) {
     if (v.total_chunks == 0) return cudaSuccess;
-    if (up.normuon || up.d_qk_clip_factors || up.symexp_beta > 0.0f)
-        k_muon_update<1><<<clamp_grid(v.total_chunks, v.grid), kThreads, 0, s>>>(
-            v.slots, v.chunk_prefix, v.slot_count, v.total_chunks, u_ptrs, amax_x, up);
-    else
-        k_muon_update<0><<<clamp_grid(v.total_chunks, v.grid), kThreads, 0, s>>>(
-            v.slots, v.chunk_prefix, v.slot_count, v.total_chunks, u_ptrs, amax_x, up);
+    const bool ext = up.normuon || up.d_qk_clip_factors || up.symexp_beta > 0.0f;
+    const int grid = clamp_grid(v.total_chunks, v.grid);
+#define B2_LAUNCH_UPDATE(EXT, UFMT)                                                                          \
+    k_muon_update<EXT, UFMT><<<grid, kThreads, 0, s>>>(v.slots, v.chunk_prefix, v.slot_count, v.total_chunks, \
+                                                       u_ptrs, amax_x, up)
+    if (up.update_format == 0) { if (ext) B2_LAUNCH_UPDATE(1, 0); else B2_LAUNCH_UPDATE(0, 0); }
+    else if (up.update_format == 1) { if (ext) B2_LAUNCH_UPDATE(1, 1); else B2_LAUNCH_UPDATE(0, 1); }
+    else { if (ext) B2_LAUNCH_UPDATE(1, 2); else B2_LAUNCH_UPDATE(0, 2); }
+#undef B2_LAUNCH_UPDATE
     return cudaGetLastError();
 }
 // ---- SymExpLin scale scalars (crates/cuda-kernels/src/gpt/optimizer/symexp_lin.rs:98-283) -----
@@ -1749,9 +1757,14 @@ cudaError_t launch_muon_update_encode(const SlotView &v, const uint32_t *items, 
     // the plain update only: with NorMuon factors or qk-clip the two-launch form measured faster
     if (up.normuon || up.d_qk_clip_factors || up.symexp_beta > 0.0f) return cudaErrorInvalidValue;
     const int grid = clamp_grid(item_count, v.grid);
-    k_muon_update_encode<<<grid, kThreads, 0, s>>>(v.slots, v.chunk_prefix, v.slot_count, items, item_count, u_ptrs,
-                                                  amax_x, up, quantize_y, scale_layout,
-                                                  static_cast<FusedSync *>(sync), status, wait_ns);
+#define B2_LAUNCH_FUSED(UFMT)                                                                                     \
+    k_muon_update_encode<UFMT><<<grid, kThreads, 0, s>>>(v.slots, v.chunk_prefix, v.slot_count, items, item_count,   \
+                                                         u_ptrs, amax_x, up, quantize_y, scale_layout,               \
+                                                         static_cast<FusedSync *>(sync), status, wait_ns)
+    if (up.update_format == 0) B2_LAUNCH_FUSED(0);
+    else if (up.update_format == 1) B2_LAUNCH_FUSED(1);
+    else B2_LAUNCH_FUSED(2);
+#undef B2_LAUNCH_FUSED
     return cudaGetLastError();
 }
 cudaError_t launch_normuon_stats(const SlotView &v, const NeuronView &nv, const uint64_t *u_ptrs, int hyperball,

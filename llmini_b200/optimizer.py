@@ -16,7 +16,7 @@ import torch
 
 from . import _ffi
 from ._ffi import (AdamWSlotDescriptor, AdamWUpdateArgs as _CAdam, GradientClipArgs as _CClip, MuonOptions, MuonSlotDescriptor, MuonStepArgs, OPERAND_BF16,
-                   NORMALIZE_DEFERRED, NORMALIZE_TWO_PASS, OPERAND_F16, QUANTIZE_X, QUANTIZE_Y, SCALES_CSF, SCALES_RAW, SCALES_SM100,
+                   NORMALIZE_DEFERRED, NORMALIZE_TWO_PASS, NS_CHAINED, NS_PER_PHASE, OPERAND_F16, UPDATE_16BIT, UPDATE_F32, QUANTIZE_X, QUANTIZE_Y, SCALES_CSF, SCALES_RAW, SCALES_SM100,
                    ScheduleFreeMaterializeArgs as _CSf, check)
 from .nvfp4 import Nvfp4QuantModule, sm100_scales_bytes, zero_scales
 
@@ -125,16 +125,21 @@ class MuonPlan:
     def __init__(self, shapes: Sequence[tuple[int, int]], operand_format: int = OPERAND_BF16,
                  scale_layout: int = SCALES_CSF, quantize_target: int = QUANTIZE_X, max_iterations: int = 5,
                  tile_n: int = 0, device="cuda", debug_phase_mask: int = 0, debug_flags: int = 0,
-                 normalize_mode: int = NORMALIZE_TWO_PASS):
+                 normalize_mode: int = NORMALIZE_TWO_PASS, ns_schedule: int = NS_PER_PHASE,
+                 update_input: int = UPDATE_F32):
         """`normalize_mode`: NORMALIZE_TWO_PASS keeps the reference's rounding point X0 = r16(u * s);
         NORMALIZE_DEFERRED reads the gradients once and lets s enter through the first iteration (BF16
-        operands only).  `debug_*` are read only by a library built with -DB2_MEASURE."""
+        operands only).  `ns_schedule`: NS_PER_PHASE runs three launches per iteration, NS_CHAINED the whole
+        Newton-Schulz loop as one persistent grid ordered by per-matrix progress counts (steps of exactly
+        `max_iterations` iterations).  `update_input`: UPDATE_16BIT lets the last iteration store the 16-bit operand type instead of
+        FP32 and the update read that (plain finish only).  `debug_*` are read only by a library built with -DB2_MEASURE."""
         self._lib = _ffi.lib()
         self.shapes = [(int(r), int(c)) for r, c in shapes]
         n = len(self.shapes)
         self._rows = (C.c_uint32 * n)(*[r for r, _ in self.shapes])
         self._cols = (C.c_uint32 * n)(*[c for _, c in self.shapes])
-        self.options = MuonOptions(operand_format, scale_layout, quantize_target, max_iterations, tile_n, debug_phase_mask, debug_flags, normalize_mode)
+        self.options = MuonOptions(operand_format, scale_layout, quantize_target, max_iterations, tile_n, debug_phase_mask, debug_flags, normalize_mode, ns_schedule,
+                                   update_input, (C.c_uint32 * 2)())
         nbytes = self._lib.b2_muon_workspace_bytes(self._rows, self._cols, n, C.byref(self.options))
         if nbytes == 0:
             raise _ffi.B2Error(_ffi.ERROR_INVALID_VALUE, "muon_workspace_bytes")
@@ -180,7 +185,7 @@ class MuonPlan:
         check(self._lib.b2_muon_plan_scratch(self._handle, slot, which, C.byref(p), C.byref(n)), "muon_plan_scratch")
         off = p.value - self._buf.data_ptr()
         raw = self._buf[off:off + n.value]
-        rows, cols = self.shapes[slot] if which not in (4, 10) else (0, 0)
+        rows, cols = self.shapes[slot] if which not in (4, 10, 11) else (0, 0)
         if which in (0, 7):
             dt = torch.float16 if self.options.operand_format == OPERAND_F16 else torch.bfloat16
             return raw.view(dt).view(rows, cols)
@@ -190,7 +195,7 @@ class MuonPlan:
             dt = torch.float16 if self.options.operand_format == OPERAND_F16 else torch.bfloat16
             n_ = min(rows, cols)
             return raw.view(dt).view(n_, -1)[:, :n_]
-        if which in (4, 10):
+        if which in (4, 10, 11):
             return raw.view(torch.int32)
         return raw.view(torch.float32)
 

@@ -43,8 +43,10 @@ pub mod ffi {
     pub const B2_QUANTIZE_Y: u32 = 1;
     pub const B2_NORMALIZE_TWO_PASS: u32 = 0;
     pub const B2_NORMALIZE_DEFERRED: u32 = 1;
-    pub const B2_NS_CHAINED: u32 = 0;
-    pub const B2_NS_PER_PHASE: u32 = 1;
+    pub const B2_NS_PER_PHASE: u32 = 0;
+    pub const B2_NS_CHAINED: u32 = 1;
+    pub const B2_UPDATE_F32: u32 = 0;
+    pub const B2_UPDATE_16BIT: u32 = 1;
     pub const B2_STATIC_MAX_ELEMENTS: u32 = 1 << 26;
 
     #[repr(C)]
@@ -105,7 +107,8 @@ pub mod ffi {
         pub measure_flags: u32,
         pub normalize_mode: u32,
         pub ns_schedule: u32,
-        pub reserved: [u32; 3],
+        pub update_input: u32,
+        pub reserved: [u32; 2],
     }
 
     #[repr(C)]

@@ -20,7 +20,7 @@ def test_library_is_in_tree_and_exports_every_declared_symbol():
     assert len(names) >= 35
     for n in names:
         assert hasattr(L, n), n
-    assert L.b2_abi_version() == 1
+    assert L.b2_abi_version() == 2
     assert C.sizeof(_ffi.MuonSlotDescriptor) == 104  # args/muon.rs:3-21, padded
 
 
@@ -86,7 +86,7 @@ def test_argument_validation():
     assert L.b2_muon_workspace_bytes(rows, cols, 1, None) == 0
     cols = (C.c_uint32 * 1)(48)  # CSF needs a multiple of 128
     assert L.b2_muon_workspace_bytes(rows, cols, 1, None) == 0
-    opt = _ffi.MuonOptions(0, _ffi.SCALES_RAW, 0, 5, 0, 0, 0, 0)
+    opt = _ffi.MuonOptions(0, _ffi.SCALES_RAW, 0, 5)
     assert L.b2_muon_workspace_bytes(rows, cols, 1, C.byref(opt)) > 0
     assert L.b2_muon_workspace_bytes(rows, cols, 0, None) == 0
 
@@ -96,7 +96,7 @@ def test_sizes_beyond_the_32_bit_limits_are_refused():
     # refused up front instead of wrapping inside a kernel
     L = b2.lib()
     INVALID = _ffi.ERROR_INVALID_VALUE
-    raw = _ffi.MuonOptions(0, _ffi.SCALES_RAW, 0, 5, 0, 0, 0, 0)
+    raw = _ffi.MuonOptions(0, _ffi.SCALES_RAW, 0, 5)
     one = lambda r, c: ((C.c_uint32 * 1)(r), (C.c_uint32 * 1)(c))
     rows, cols = one(16 * 1024 * 1024, 16)          # 131072 row tiles of 128: beyond a 16-bit tile index
     assert L.b2_muon_workspace_bytes(rows, cols, 1, C.byref(raw)) == 0

@@ -68,7 +68,7 @@ def test_reference_nonconstant_wide_recurrence():
 
 
 def _check_step(shapes, layout, fmt, coeffs, target=b2.QUANTIZE_X, seed=0, outliers=True,
-                normalize=b2.NORMALIZE_TWO_PASS):
+                normalize=b2.NORMALIZE_TWO_PASS, update_input=b2.UPDATE_F32, schedule=b2.NS_PER_PHASE):
     rng = np.random.default_rng(seed)
     hp = dict(mu=0.95, grad_scale=1.0, learning_rate=0.02, weight_decay=0.025, average_coefficient=0.5,
               schedule_beta=0.2, iterations=5)
@@ -81,7 +81,8 @@ def _check_step(shapes, layout, fmt, coeffs, target=b2.QUANTIZE_X, seed=0, outli
         data.append((g, m, z, x))
         slots.append(_slot(r, c, g, m, z, x, layout))
     deferred = normalize == b2.NORMALIZE_DEFERRED
-    plan = b2.MuonPlan(shapes, operand_format=fmt, scale_layout=layout, quantize_target=target, normalize_mode=normalize)
+    plan = b2.MuonPlan(shapes, operand_format=fmt, scale_layout=layout, quantize_target=target, normalize_mode=normalize,
+                       update_input=update_input, ns_schedule=schedule)
     b2.OptimizerModule().muon_mega_update(plan, b2.slot_table(slots), b2.MuonMegaUpdateArgs(coefficients=coeffs, **hp))
     torch.cuda.synchronize()
     assert plan.status() == 0
@@ -96,7 +97,8 @@ def _check_step(shapes, layout, fmt, coeffs, target=b2.QUANTIZE_X, seed=0, outli
                           iterations=5, coeffs=coeffs, round_mode=mode, quantize_y=(target == b2.QUANTIZE_Y),
                           deferred_normalize=deferred)
         assert np.array_equal(bf16_bits(s.momentum).ravel(), ref.momentum_bits)   # bit-exact in both orders
-        Ug = host(plan.scratch(i, 1))
+        # the Newton-Schulz result as stage U reads it: FP32, or the 16-bit buffer the fifth iteration wrote
+        Ug = host(plan.scratch(i, 1)) if update_input == b2.UPDATE_F32 else host(plan.scratch(i, 7).float())
         r2, mx = U.rel_l2(Ug, ref.U), U.max_rel_to_peak(Ug, ref.U)
         print(f"slot {i} {r}x{c}: NS rel_l2 {r2:.3e} max/peak {mx:.3e}")
         assert r2 <= 2e-2 and mx <= 1e-1          # Newton-Schulz in 16-bit operands (see test_gpu_ns_gemm)
@@ -156,6 +158,44 @@ def test_config1_one_pass_prepare():
 def test_one_gpt2_layer_one_pass_prepare():
     _check_step([(2304, 768), (768, 768), (3072, 768), (768, 3072), (0, 0)], b2.SCALES_CSF, b2.OPERAND_BF16,
                 o.fixed_coefficients(5), seed=4, normalize=b2.NORMALIZE_DEFERRED)
+
+
+@pytest.mark.parametrize("fmt,coeffs", [(b2.OPERAND_BF16, "fixed"), (b2.OPERAND_F16, "table")])
+def test_update_reads_the_16_bit_result(fmt, coeffs):
+    # B2_UPDATE_16BIT: the last Apply stores the operand type and stage U reads it; everything downstream of that
+    # buffer is still bit-exact against the oracle
+    co = o.fixed_coefficients(5) if coeffs == "fixed" else o.polar_express_coefficients(5)
+    _check_step([(2304, 768), (768, 768), (768, 3072), (200, 208)], b2.SCALES_RAW, fmt, co, seed=8,
+                update_input=b2.UPDATE_16BIT)
+
+
+def test_16_bit_result_with_one_pass_prepare_and_y_target():
+    _check_step([(3072, 768), (768, 3072)], b2.SCALES_CSF, b2.OPERAND_BF16, o.fixed_coefficients(5),
+                target=b2.QUANTIZE_Y, seed=9, normalize=b2.NORMALIZE_DEFERRED, update_input=b2.UPDATE_16BIT)
+
+
+def test_16_bit_result_is_refused_where_statistics_need_fp32():
+    shapes = [(128, 256)]
+    s = _slot(128, 256, np.zeros(128 * 256, F), np.zeros(128 * 256, np.uint16), np.zeros(128 * 256, F),
+              np.zeros(128 * 256, F), b2.SCALES_CSF)
+    s.second_momentum = torch.zeros(256, device="cuda")
+    plan = b2.MuonPlan(shapes, update_input=b2.UPDATE_16BIT)
+    opt, table = b2.OptimizerModule(), b2.slot_table([s])
+    with pytest.raises(b2.B2Error) as e:
+        opt.muon_tma_finish_update(plan, table, b2.MuonMegaUpdateArgs(normuon=True))
+    assert e.value.code == b2._ffi.ERROR_NOT_SUPPORTED
+    with pytest.raises(b2.B2Error) as e:
+        opt.muon_tma_finish_hyperball_update_deferred_quantization(plan, table, b2.MuonMegaUpdateArgs())
+    assert e.value.code == b2._ffi.ERROR_NOT_SUPPORTED
+    plan.close()
+
+
+def test_one_gpt2_layer_chained_newton_schulz():
+    # the whole step with the Newton-Schulz loop as one persistent launch, one-pass prepare feeding its first iteration
+    _check_step([(2304, 768), (768, 768), (3072, 768), (768, 3072), (0, 0)], b2.SCALES_CSF, b2.OPERAND_BF16,
+                o.fixed_coefficients(5), seed=10, normalize=b2.NORMALIZE_DEFERRED, schedule=b2.NS_CHAINED)
+    _check_step([(1600, 320), (48, 1600), (200, 208)], b2.SCALES_RAW, b2.OPERAND_F16, o.polar_express_coefficients(5),
+                seed=11, schedule=b2.NS_CHAINED, update_input=b2.UPDATE_16BIT)
 
 
 def test_one_pass_prepare_needs_bf16_operands():

@@ -28,9 +28,10 @@ def _x0(rng, rows, cols, fmt):
     return o.round_bf16(x) if fmt == b2.OPERAND_BF16 else x.astype(np.float16).astype(F)
 
 
-def _run(shapes, fmt, iterations, coeffs, tile_n, xs):
+def _run(shapes, fmt, iterations, coeffs, tile_n, xs, schedule=b2.NS_PER_PHASE):
     opt = b2.OptimizerModule()
-    plan = b2.MuonPlan(shapes, operand_format=fmt, scale_layout=b2.SCALES_RAW, tile_n=tile_n)
+    plan = b2.MuonPlan(shapes, operand_format=fmt, scale_layout=b2.SCALES_RAW, tile_n=tile_n, max_iterations=iterations,
+                       ns_schedule=schedule)
     for i, x in enumerate(xs):
         t = plan.scratch(i, 0)
         t.copy_(dev(x).to(t.dtype))
@@ -40,14 +41,15 @@ def _run(shapes, fmt, iterations, coeffs, tile_n, xs):
     return plan
 
 
+@pytest.mark.parametrize("schedule", [b2.NS_CHAINED, b2.NS_PER_PHASE])
 @pytest.mark.parametrize("tile_n", [128, 256, 512])  # 512 = two-CTA 256 x 256 tiles
 @pytest.mark.parametrize("fmt", [b2.OPERAND_BF16, b2.OPERAND_F16])
 @pytest.mark.parametrize("rows,cols", [(64, 256), (256, 64), (128, 128), (96, 160), (160, 96), (320, 832), (832, 320)])
-def test_single_iteration_intermediates(rows, cols, fmt, tile_n):
+def test_single_iteration_intermediates(rows, cols, fmt, tile_n, schedule):
     rng = np.random.default_rng(rows * 7 + cols)
     x = _x0(rng, rows, cols, fmt)
     co = o.polar_express_coefficients(1) if fmt == b2.OPERAND_F16 else o.fixed_coefficients(1)
-    plan = _run([(rows, cols)], fmt, 1, co, tile_n, [x])
+    plan = _run([(rows, cols)], fmt, 1, co, tile_n, [x], schedule)
     mode = o.ROUND_BF16 if fmt == b2.OPERAND_BF16 else o.ROUND_F16
     rnd = (lambda a: o.round_bf16(a)) if fmt == b2.OPERAND_BF16 else (lambda a: np.asarray(a, F).astype(np.float16).astype(F))
     xs = x if rows <= cols else np.ascontiguousarray(x.T)   # polar orientation [n][m]
@@ -69,16 +71,17 @@ def test_single_iteration_intermediates(rows, cols, fmt, tile_n):
     plan.close()
 
 
+@pytest.mark.parametrize("schedule", [b2.NS_CHAINED, b2.NS_PER_PHASE])
 @pytest.mark.parametrize("tile_n", [0, 256])
 @pytest.mark.parametrize("shapes", [
     [(768, 768), (768, 3072), (3072, 768), (2304, 768)],
     [(1600, 1600), (1600, 320), (48, 1600)],
 ])
-def test_five_iterations_multi_slot(shapes, tile_n):
+def test_five_iterations_multi_slot(shapes, tile_n, schedule):
     rng = np.random.default_rng(len(shapes) * 97 + shapes[0][0])
     xs = [_x0(rng, r, c, b2.OPERAND_BF16) for r, c in shapes]
     co = o.fixed_coefficients(5)
-    plan = _run(shapes, b2.OPERAND_BF16, 5, co, tile_n, xs)
+    plan = _run(shapes, b2.OPERAND_BF16, 5, co, tile_n, xs, schedule)
     for i, x in enumerate(xs):
         want = o.polar(x, 5, co, round_mode=o.ROUND_BF16)
         got = host(plan.scratch(i, 1))
@@ -90,3 +93,61 @@ def test_five_iterations_multi_slot(shapes, tile_n):
         sv = np.linalg.svd(got.astype(np.float64), compute_uv=False)
         assert sv.max() < 1.6 and np.median(sv) > 0.5
     plan.close()
+
+
+@pytest.mark.parametrize("tile_n", [0, 128, 256])
+@pytest.mark.parametrize("shapes", [
+    [(768, 768), (768, 3072), (3072, 768), (2304, 768), (0, 0), (768, 768)],
+    [(1600, 1600), (1600, 320), (48, 1600), (4800, 1600)],
+    [(64, 64)],
+])
+def test_chained_launch_equals_the_per_phase_launches_bit_for_bit(shapes, tile_n):
+    # The chained launch runs the same tiles with the same k order as the fifteen per-phase launches; only the
+    # ordering between tiles differs (per-matrix progress counts instead of launch boundaries), so every
+    # intermediate and the result must be identical, and its progress words must be zero again afterwards.
+    rng = np.random.default_rng(31 + len(shapes))
+    xs = [_x0(rng, r, c, b2.OPERAND_BF16) if r * c else np.zeros((0, 0), F) for r, c in shapes]
+    co = o.fixed_coefficients(5)
+    live = [(i, x) for i, x in enumerate(xs) if x.size]
+
+    def run(schedule):
+        opt = b2.OptimizerModule()
+        plan = b2.MuonPlan(shapes, scale_layout=b2.SCALES_RAW, tile_n=tile_n, ns_schedule=schedule)
+        for i, x in live:
+            t = plan.scratch(i, 0)
+            t.copy_(dev(x).to(t.dtype))
+        for _ in range(2):   # twice: the second run starts from the words the first one left
+            for i, x in live:
+                t = plan.scratch(i, 0)
+                t.copy_(dev(x).to(t.dtype))
+            opt.muon_polar(plan, b2.MuonMegaUpdateArgs(iterations=5, coefficients=co))
+        torch.cuda.synchronize()
+        assert plan.status() == 0
+        assert not host(plan.scratch(0, 11)).any()
+        out = [[host(plan.scratch(i, w).float()).copy() for w in (1, 5, 6, 7)] for i, _ in live]
+        plan.close()
+        return out
+
+    a, b = run(b2.NS_CHAINED), run(b2.NS_PER_PHASE)
+    for (i, _), ra, rb in zip(live, a, b):
+        for w, ta, tb in zip(("U", "Gram", "Q", "X1"), ra, rb):
+            assert np.array_equal(ta, tb), (shapes[i], w)
+
+
+def test_steps_with_fewer_iterations_take_the_per_phase_launches():
+    # a plan made for five iterations asked for three: the chained list does not apply, the result must not change
+    rng = np.random.default_rng(5)
+    shapes = [(256, 512), (512, 256)]
+    xs = [_x0(rng, r, c, b2.OPERAND_BF16) for r, c in shapes]
+    co = o.fixed_coefficients(3)
+    plan = _run(shapes, b2.OPERAND_BF16, 3, co, 0, xs, b2.NS_CHAINED)                     # max_iterations = 3: chained
+    plan5 = b2.MuonPlan(shapes, scale_layout=b2.SCALES_RAW, ns_schedule=b2.NS_CHAINED)     # made for 5: per phase for 3
+    for i, x in enumerate(xs):
+        t = plan5.scratch(i, 0)
+        t.copy_(dev(x).to(t.dtype))
+    b2.OptimizerModule().muon_polar(plan5, b2.MuonMegaUpdateArgs(iterations=3, coefficients=co))
+    torch.cuda.synchronize()
+    for i in range(len(shapes)):
+        assert torch.equal(plan.scratch(i, 1), plan5.scratch(i, 1))
+    plan.close()
+    plan5.close()

@@ -114,7 +114,7 @@ def test_forwarding_layer_has_every_reference_method_of_the_path():
     text = _strip_rust_comments(SHIM)
     for name in ("b2_muon_step_args", "b2_adamw_update_args", "b2_gradient_clip_args", "b2_symexp_lin_adamw_args",
                  "b2_schedule_free_materialize_args"):
-        literals = re.findall(rf"[^a-z_]{name} \{{(.*?)\n        \}}", text, flags=re.S)
+        literals = re.findall(rf"(?<!struct )(?<!-> )\b{name} \{{\n(.*?)\n        \}}", text, flags=re.S)
         assert literals, name
         for body in literals:
             named = re.findall(r"^\s*([a-z0-9_]+)\s*[:,]", body, flags=re.M)
