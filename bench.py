@@ -573,10 +573,11 @@ def secondary_workload(name, args, world, rank, dev, peaks):
     consistent = job.gathered_arena_consistent() if world > 1 else None
     if consistent is False:
         raise SystemExit(f"{name}: the ranks do not hold the same gathered arena")
+    parity = job.parity_against_oracle(compare=(rank == 0))   # one matrix of this workload against the CPU oracle
     out = {"workload": workload_config(name, world)["workload"], "ms_per_step": ms_step, "eager_ms_per_step": ms_eager,
            "steps": steps, "warmup": 3, "cuda_graph": graphed, "n_gpus": world,
            "ns_tflop_per_step": ns_flops(job.mats) / 1e12, "stages_rank0": job.stage_summary(peaks),
-           "gathered_arena_consistent": consistent}
+           "gathered_arena_consistent": consistent, "parity_checked": parity is not None, "parity": parity}
     job.close()
     del job
     torch.cuda.empty_cache()

@@ -144,14 +144,12 @@ struct ChainSync {
 // Bounded wait until `*counter >= need`.  Returns false when the limit ran out or the launch is aborting.
 //
 // How a tile's outputs reach the CTA that reads them.  The writer's epilogue warps wait for their TMA stores
-// to complete (cp.async.bulk.wait_group 0: the data is in L2), fence their plain stores (the FP32 Gram tile),
-// and only then raise the matrix's progress count with an atomic, which is performed at L2 as well.  The reader
-// polls the count with loads that bypass L1 and issues its first copy under a branch on the value it saw.  TMA
-// copies and ld.global.cg read L2, the one point every SM shares, so data that was there before the count rose
-// is what they get; no L1 line of the reader can hold an older copy.  A polling loop of acquire loads followed
-// by fence.proxy.async, which is what the PTX memory model's letter asks for between a generic-proxy flag and
-// async-proxy copies, drained the producer's copies in flight at every tile (measured: the chained launch took
-// 1.3x the time of the launches it replaces), so the reader relies on the control dependency instead.
+// to complete (cp.async.bulk.wait_group 0), order them and their plain stores (the FP32 Gram tile) before what
+// follows (fence.proxy.async, __threadfence) and only then raise the matrix's progress count with an atomic.
+// The reader polls the count with relaxed loads that bypass L1; once it is high enough it reads it once more
+// with acquire semantics and issues fence.proxy.async before its first TMA copy, which is what the PTX memory
+// model asks for between a generic-proxy flag and async-proxy accesses.  Both fences were measured against a
+// build without them: no difference beyond run-to-run noise.
 __device__ __forceinline__ bool chain_wait(const uint32_t *counter, uint32_t need, uint32_t *launch_abort,
                                            volatile uint32_t *abort_flag) {
     if (ld_relaxed_gpu(counter) >= need) return true;
@@ -337,12 +335,8 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const void *__restrict__ til
 #ifdef B2_MEASURE
     const bool dbg_no_store = debug_flags & 1u;   // drop every epilogue store
     const bool dbg_no_global = debug_flags & 8u;  // stage in shared memory but issue no global store
-    const bool dbg_reader_fence = debug_flags & 64u;   // chained: acquire + proxy fence after a dependency wait
-    const bool dbg_writer_fence = debug_flags & 128u;  // chained: proxy fence before a progress count is raised
-    const bool dbg_no_order = debug_flags & 256u;      // chained: neither wait nor publish (wrong results; timing only)
 #else
     constexpr bool dbg_no_store = false, dbg_no_global = false;
-    constexpr bool dbg_reader_fence = false, dbg_writer_fence = false, dbg_no_order = false;
     (void)debug_flags;
 #endif
     extern __shared__ uint8_t smem_raw[];
@@ -468,15 +462,13 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const void *__restrict__ til
                 // A diagonal tile of X X^T or G G: this CTA's 128 rows of B are its 128 rows of A, in
                 // the same shared-memory layout.  They are loaded once and the MMA reads them twice.
                 const bool shared_operand = PAIR && tl.tile_m == tl.tile_n && map_a == map_b && a_mn == b_mn;
-                if (CHAINED && tl.need != 0u && !dbg_no_order) {
+                if (CHAINED && tl.need != 0u) {
                     // the operands are the outputs of the matrix's previous phase: every tile of that phase
                     // has been stored and published before the first copy is issued
                     if (seen < tl.need &&
                         !chain_wait(&sync->progress[tl.slot], tl.need, &sync->abort, abort_flag)) { ok = false; break; }
-                    if (dbg_reader_fence) {
-                        (void)ld_acquire_gpu(&sync->progress[tl.slot]);
-                        fence_proxy_async_all();
-                    }
+                    (void)ld_acquire_gpu(&sync->progress[tl.slot]);
+                    fence_proxy_async_all();
                 }
                 if (CHAINED) *passed_tile = t_now + 1u;
                 const uint32_t stage_tx = shared_operand ? 2u * (uint32_t)kABytes
@@ -580,9 +572,9 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const void *__restrict__ til
         uint32_t unpublished = kNoSlot;
         auto publish = [&]() {
             __syncwarp();
-            if (lane == 0 && !dbg_no_order) {
+            if (lane == 0) {
                 tma_store_wait_all();
-                if (dbg_writer_fence) fence_proxy_async_all();
+                fence_proxy_async_all();
                 __threadfence();
                 atomicAdd(&sync->progress[unpublished], 1u);
             }
