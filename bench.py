@@ -460,30 +460,11 @@ class GpuJob:
 
     # -- checks -----------------------------------------------------------------------------
     def gathered_arena_consistent(self):
-        """After one step + all-gather every rank must hold the same arena: per-slice checksums (a plain byte
-        sum and a position-weighted one) are reduced with MIN and MAX over the ranks and must agree, and every
-        slice that has payload must be non-zero.  Plain NCCL collectives only."""
-        import torch.distributed as dist
+        """After one step + all-gather every rank must hold the same arena (per-slice checksums reduced with MIN
+        and MAX over the ranks must agree, slices with payload must be non-zero).  Plain NCCL collectives only."""
+        from llmini_b200.dist import gathered_arena_consistent
 
-        torch = self.torch
-        n, w = self.arena.bytes_per_rank, self.world
-        sums = torch.zeros(2, w, dtype=torch.int64, device=self.dev)
-        piece = 32 << 20
-        for r in range(w):
-            for a in range(0, n, piece):
-                v = self.arena_v[r * n + a:r * n + min(a + piece, n)].to(torch.int64)
-                weight = ((torch.arange(v.numel(), device=self.dev, dtype=torch.int64) + a) % 251) + 1
-                sums[0, r] += v.sum()
-                sums[1, r] += (v * weight).sum()
-        lo, hi = sums.clone(), sums.clone()
-        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
-        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
-        used = torch.zeros(w, dtype=torch.bool, device=self.dev)
-        for e in self.arena.entries:
-            if e.codes_bytes:
-                used[e.rank] = True
-        filled = bool(((sums[0] != 0) | ~used).all().item())
-        return bool(torch.equal(lo, hi)) and filled
+        return gathered_arena_consistent(self.arena_v, self.arena)
 
     def parity_against_oracle(self, compare):
         """One matrix of the timed workload, one more step from its current state, against the CPU oracle:

@@ -88,6 +88,43 @@ def all_gather_arena(arena_tensor, arena: Nvfp4Arena, group=None):
             p.copy_(g)
 
 
+def arena_slice_checksums(arena_tensor, arena: Nvfp4Arena, piece: int = 32 << 20):
+    """Two checksums per rank slice of a gathered arena (a plain byte sum and a position-weighted one), as an
+    int64 tensor [2, world] on the arena's device.  Ranks that hold the same arena get the same numbers."""
+    import torch
+
+    n, w = arena.bytes_per_rank, arena.world
+    dev = arena_tensor.device
+    sums = torch.zeros(2, w, dtype=torch.int64, device=dev)
+    for r in range(w):
+        for a in range(0, n, piece):
+            v = arena_tensor[r * n + a:r * n + min(a + piece, n)].to(torch.int64)
+            weight = ((torch.arange(v.numel(), device=dev, dtype=torch.int64) + a) % 251) + 1
+            sums[0, r] += v.sum()
+            sums[1, r] += (v * weight).sum()
+    return sums
+
+
+def gathered_arena_consistent(arena_tensor, arena: Nvfp4Arena, group=None) -> bool:
+    """After the all-gather every rank must hold the same arena: the per-slice checksums are reduced with MIN
+    and MAX over the ranks and must agree, and every slice that carries payload must be non-zero (a rank whose
+    slice never arrived would otherwise agree with everybody on zeros only if all were empty).  Collective:
+    every rank of `group` calls it."""
+    import torch
+    import torch.distributed as dist
+
+    sums = arena_slice_checksums(arena_tensor, arena)
+    lo, hi = sums.clone(), sums.clone()
+    dist.all_reduce(lo, op=dist.ReduceOp.MIN, group=group)
+    dist.all_reduce(hi, op=dist.ReduceOp.MAX, group=group)
+    used = torch.zeros(arena.world, dtype=torch.bool, device=arena_tensor.device)
+    for e in arena.entries:
+        if e.codes_bytes:
+            used[e.rank] = True
+    filled = bool(((sums[0] != 0) | ~used).all().item())
+    return bool(torch.equal(lo, hi)) and filled
+
+
 class Communicator:
     """The library's own NCCL communicator (b2_comm_*), bootstrapped over torch.distributed."""
 

@@ -68,6 +68,49 @@ def _worker(rank, world, port, fail_rank, out):
         dist.destroy_process_group()
 
 
+def _checksum_worker(rank, world, port, corrupt, out):
+    from llmini_b200.dist import gathered_arena_consistent
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        owner, _ = shard_plan(SHAPES, world)
+        arena = Nvfp4Arena(SHAPES, owner, world, _scales_bytes)
+        buf = torch.zeros(arena.total_bytes, dtype=torch.uint8)
+        for slot, (rows, cols) in enumerate(SHAPES):
+            if owner[slot] != rank or rows * cols == 0:
+                continue
+            codes, raw, gs = _payload(slot, rows, cols)
+            co, so, go = arena.offsets(slot)
+            buf[co:co + codes.size] = torch.from_numpy(codes)
+            buf[so:so + raw.size] = torch.from_numpy(raw)
+        if corrupt != "never_gathered":
+            all_gather_arena(buf, arena)
+        if corrupt == "one_byte" and rank == 1:
+            buf[arena.offsets(0)[0] + 5] ^= 1       # one flipped bit in a slice this rank does not own
+        if corrupt == "swapped" and rank == 1:
+            a, b = arena.offsets(0)[0], arena.offsets(0)[0] + 1
+            if buf[a] != buf[b]:
+                buf[a], buf[b] = buf[b].clone(), buf[a].clone()   # same byte sum, different positions
+            else:
+                buf[a] ^= 3
+        out[rank] = gathered_arena_consistent(buf, arena)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("corrupt,expected", [("nothing", True), ("one_byte", False), ("swapped", False),
+                                              ("never_gathered", False)])
+def test_gathered_arena_check_catches_a_rank_that_differs(corrupt, expected):
+    # the check bench.py runs after a multi-GPU step, on CPU ranks: identical arenas pass; one flipped bit, two
+    # swapped bytes, or slices that never arrived are caught on every rank
+    world = 2
+    with mp.Manager() as mgr:
+        out = mgr.dict()
+        mp.spawn(_checksum_worker, args=(world, _free_port(), corrupt, out), nprocs=world, join=True)
+        assert dict(out) == {0: expected, 1: expected}
+
+
 def test_arena_layout_is_disjoint_and_aligned():
     owner, _ = shard_plan(SHAPES, 2)
     arena = Nvfp4Arena(SHAPES, owner, 2, _scales_bytes)
