@@ -105,7 +105,7 @@ double slot_flops(uint32_t rows, uint32_t cols) {
 
 enum ProblemType { kGram0 = 0, kGram1, kPoly, kApply0, kApply1, kLast0, kLast1, kProblemTypes };
 // load maps: *K = box 64 (K) x 128 rows for K-major use, *M = box 64 x 64 for MN-major use
-enum MapKind { kLX0K = 0, kLX1K, kLX0M, kLX1M, kLG, kLQ, kSX0, kSX1, kSG, kSQ, kSU, kSGT, kSQT, kMapsPerSlot };
+enum MapKind { kLX0K = 0, kLX1K, kLX0M, kLX1M, kLG, kLQ, kMapsPerSlot };
 
 struct SlotLayout {
     uint32_t rows, cols, n, m, ldg, tiles_m_nn, tiles_n_nn, sub_m_nn;
@@ -419,20 +419,13 @@ int b2_muon_plan_create(b2_muon_plan **out, const uint32_t *rows, const uint32_t
         ok &= make_map(ms + kLX1M, p->ws + sl.off_x[1], 2, sl.rows, sl.cols, xp, 64, 64);
         ok &= make_map(ms + kLG, p->ws + sl.off_g16, 2, sl.n, sl.n, gp, 64, 128);
         ok &= make_map(ms + kLQ, p->ws + sl.off_q16, 2, sl.n, sl.n, gp, 64, 128);
-        ok &= make_map(ms + kSX0, p->ws + sl.off_x[0], 2, sl.rows, sl.cols, xp, 64, 32);
-        ok &= make_map(ms + kSX1, p->ws + sl.off_x[1], 2, sl.rows, sl.cols, xp, 64, 32);
-        ok &= make_map(ms + kSG, p->ws + sl.off_g16, 2, sl.n, sl.n, gp, 64, 32);
-        ok &= make_map(ms + kSQ, p->ws + sl.off_q16, 2, sl.n, sl.n, gp, 64, 32);
-        ok &= make_map(ms + kSU, p->ws + sl.off_u, 4, sl.rows, sl.cols, (uint64_t)sl.cols * 4, 32, 32);
-        ok &= make_map(ms + kSGT, p->ws + sl.off_g16, 2, sl.n, sl.n, gp, 32, 64, false);
-        ok &= make_map(ms + kSQT, p->ws + sl.off_q16, 2, sl.n, sl.n, gp, 32, 64, false);
         const bool tall = sl.rows > sl.cols;
         const uint64_t frag = reinterpret_cast<uint64_t>(p->ws + sl.off_frag);
         for (int b = 0; b < 2; ++b) {
             GemmProblem &g = probs[(size_t)(kGram0 + b) * slot_count + s];
             g.map_a = g.map_b = dmap(s, (tall ? kLX0M : kLX0K) + b);
-            g.map_out16 = dmap(s, kSG);
-            g.map_out16t = dmap(s, kSGT);
+            g.out16 = reinterpret_cast<uint64_t>(p->ws + sl.off_g16);
+            g.pitch16 = sl.ldg;
             g.frag32 = frag;
             g.M = g.N = sl.n; g.K = sl.m;
             g.a_mn_major = g.b_mn_major = tall ? 1u : 0u;
@@ -449,15 +442,17 @@ int b2_muon_plan_create(b2_muon_plan **out, const uint32_t *rows, const uint32_t
                     a.M = sl.n; a.N = sl.m;
                 }
                 a.K = sl.n;
-                a.map_out16 = dmap(s, kSX0 + (1 - b));
-                a.map_out32 = dmap(s, kSU);
+                a.out16 = reinterpret_cast<uint64_t>(p->ws + sl.off_x[1 - b]);
+                a.pitch16 = sl.cols;
+                a.out32 = reinterpret_cast<uint64_t>(p->ws + sl.off_u);
+                a.pitch32 = sl.cols;
                 a.tiles_n = (a.N + L.bn - 1) / L.bn;
             }
         }
         GemmProblem &q = probs[(size_t)kPoly * slot_count + s];
         q.map_a = q.map_b = dmap(s, kLG);
-        q.map_out16 = dmap(s, kSQ);
-        q.map_out16t = dmap(s, kSQT);
+        q.out16 = reinterpret_cast<uint64_t>(p->ws + sl.off_q16);
+        q.pitch16 = sl.ldg;
         q.frag32 = frag;
         q.M = q.N = q.K = sl.n;
         q.tiles_n = sl.tiles_n_nn;

@@ -128,15 +128,15 @@ struct alignas(16) GemmProblem {
     uint64_t map_a;      // device address of the CUtensorMap of operand A (16-bit; box 64 x 128
                          // rows when K-major, 64 x 64 when MN-major)
     uint64_t map_b;
-    uint64_t map_out16;  // store map, box 64 x 32 (16-bit) — unused for kEpiApplyLast
-    uint64_t map_out32;  // store map, box 32 x 32 (f32) — kEpiApplyLast only
-    uint64_t map_out16t; // store map of the same 16-bit tensor, box 32 x 64, no swizzle: mirrored
-                         // (transposed) blocks of symmetric outputs
+    uint64_t out16;      // 16-bit result, row-major with `pitch16` elements per row — unused for kEpiApplyLast
+    uint64_t out32;      // f32 result, row-major with `pitch32` elements per row — kEpiApplyLast only
     uint64_t frag32;     // f32 accumulator tiles in fragment order (Gram writes, Poly reads)
     uint32_t M, N, K;
     uint32_t a_mn_major;  // 0: A is [M][K] K-contiguous; 1: A is [K][M] M-contiguous
     uint32_t b_mn_major;  // 0: B is [N][K]; 1: B is [K][N]
     uint32_t tiles_n;     // number of BN-wide tile columns (for frag32 addressing)
+    uint32_t pitch16;     // >= N, a multiple of 8 (columns N .. pitch16 of a row are padding and may be written)
+    uint32_t pitch32;
 };
 struct GemmTile {
     uint16_t problem;

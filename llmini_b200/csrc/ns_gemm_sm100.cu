@@ -97,6 +97,18 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
         : "memory");
     return ok;
 }
+// Non-blocking probe of a barrier phase.  (mbarrier.try_wait may suspend the thread for a system-dependent time,
+// measured here at about 5 us, before it reports that the phase is not complete; that is right for a wait, not
+// for a probe.)
+__device__ __forceinline__ uint32_t mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{ .reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
 __device__ __forceinline__ uint64_t global_timer_ns() {
     uint64_t t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -211,16 +223,6 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, uint64_t map, uint32_t
             ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
             : "memory");
 }
-__device__ __forceinline__ void tma_store_2d(uint64_t map, uint32_t src, int x, int y) {
-    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
-                 ::"l"(map), "r"(src), "r"(x), "r"(y)
-                 : "memory");
-}
-__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void tma_store_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-// all but the most recent store of this thread have read their shared-memory source
-__device__ __forceinline__ void tma_store_wait_read_older() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
-__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -549,35 +551,49 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const void *__restrict__ til
         const int q = warp & 3;
         const int chunk = (warp - 2) >> 2;
         const int c0 = chunk * 64;
-        // With two slabs per warp they are used in turn: before one is refilled only the store
-        // before the last has to be done with it, so a store's shared-memory read overlaps the
-        // next fill.
-        uint8_t *slab_pair = staging + (size_t)(warp - 2) * SLABS * kSlabBytes;
-        uint32_t sb = 0;
-        auto slab_wait = [&]() {
-            if (lane == 0) {
-                if (SLABS == 2) tma_store_wait_read_older();
-                else tma_store_wait_read_all();
+        // Results leave through a per-warp 4 KB slab in shared memory and plain 128-bit global stores: the warp
+        // writes its 32 rows into the slab (one row per lane, 16-byte chunks XOR-swizzled by the row so that the
+        // fill and the copy-out are both conflict-free), then copies it out with eight lanes per row, so every
+        // store instruction writes whole 128-byte lines.  (TMA stores were measured to take about 5 us from issue
+        // to completion, cp.async.bulk.wait_group 0, even on an idle GPU: that wait sat at the end of every launch
+        // and, in the chained launch, between every tile and the tiles that depend on it.  Plain stores are
+        // complete after a fence.)
+        uint8_t *slab = staging + (size_t)(warp - 2) * SLABS * kSlabBytes;
+        // 32 rows x 128 bytes, swizzled -> row-major tensor; rows >= row_limit and bytes >= byte_limit are dropped
+        auto slab_to_global = [&](uint8_t *base, size_t pitch_bytes, int row0, int row_limit, int byte0, int byte_limit) {
+#pragma unroll 2
+            for (int i = 0; i < 8; ++i) {
+                const int r = 4 * i + (lane >> 3), c = lane & 7;
+                const uint4 w = *reinterpret_cast<const uint4 *>(slab + r * 128 + ((c ^ (r & 7)) << 4));
+                const int gr = row0 + r, gb = byte0 + 16 * c;
+                if (gr < row_limit && gb < byte_limit)
+                    *reinterpret_cast<uint4 *>(base + (size_t)gr * pitch_bytes + gb) = w;
             }
-            __syncwarp();
         };
-        auto slab_next = [&]() { if (SLABS == 2) sb ^= 1u; };
+        // 64 rows x 64 bytes, plain row-major (the transposed block of a symmetric output)
+        auto slab_t_to_global = [&](uint8_t *base, size_t pitch_bytes, int row0, int row_limit, int byte0, int byte_limit) {
+#pragma unroll 2
+            for (int i = 0; i < 8; ++i) {
+                const int r = 8 * i + (lane >> 2), c = lane & 3;
+                const uint4 w = *reinterpret_cast<const uint4 *>(slab + r * 64 + 16 * c);
+                const int gr = row0 + r, gb = byte0 + 16 * c;
+                if (gr < row_limit && gb < byte_limit)
+                    *reinterpret_cast<uint4 *>(base + (size_t)gr * pitch_bytes + gb) = w;
+            }
+        };
         const uint32_t tempty_leader0 = PAIR ? map_to_cta(tempty_bar(0), 0) : tempty_bar(0);
         uint32_t acc = 0, acc_phase = 0;
         // Chained launch: a finished tile is published to the other CTAs by raising its matrix's progress count
-        // once this warp's stores have completed.  The wait for that completion is put off until the next tile's
-        // accumulator has been read (the stores then had that long to land) unless the next accumulator is not
-        // ready yet, in which case it is done first: a warp never blocks on other CTAs with a count unpublished.
+        // once this warp's stores are ordered before it (every lane fences its own).  The fence is put off until
+        // the next tile's accumulator has been read (the stores then had that long to land) unless the next
+        // accumulator is not ready yet, in which case it is done first: a warp never blocks on other CTAs with a
+        // count unpublished.
         constexpr uint32_t kNoSlot = 0xffffffffu;
         uint32_t unpublished = kNoSlot;
         auto publish = [&]() {
+            __threadfence();
             __syncwarp();
-            if (lane == 0) {
-                tma_store_wait_all();
-                fence_proxy_async_all();
-                __threadfence();
-                atomicAdd(&sync->progress[unpublished], 1u);
-            }
+            if (lane == 0) atomicAdd(&sync->progress[unpublished], 1u);
             unpublished = kNoSlot;
         };
         uint32_t seq = 0;
@@ -594,7 +610,8 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const void *__restrict__ til
             }
             const GemmProblem *p = problems + tl.problem;
             const uint32_t M = p->M, N = p->N;
-            const uint64_t map16 = p->map_out16, map32 = p->map_out32, map16t = p->map_out16t;
+            uint8_t *out16 = reinterpret_cast<uint8_t *>(p->out16), *out32 = reinterpret_cast<uint8_t *>(p->out32);
+            const size_t pitch16 = (size_t)p->pitch16 * 2, pitch32 = (size_t)p->pitch32 * 4;
             // symmetric outputs (Gram, Poly): tiles below the diagonal are not computed; the tile
             // above writes them as its transpose (reference: tiles/symmetric.rs:76-92)
             const bool mirror = tl.mirror != 0;
@@ -619,7 +636,7 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const void *__restrict__ til
 #pragma unroll
                 for (int j = 0; j < 8; ++j) g[j] = __ldcg(frag + (unit0 + j) * kGemmBlockM + row_in_tile);
             }
-            if (CHAINED && unpublished != kNoSlot && !mbar_try_wait(tfull_bar(acc), acc_phase)) publish();
+            if (CHAINED && unpublished != kNoSlot && !mbar_test(tfull_bar(acc), acc_phase)) publish();
 
             bool ready = mbar_wait(tfull_bar(acc), acc_phase, abort_flag);
             ready = __all_sync(0xffffffffu, ready);
@@ -660,20 +677,15 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const void *__restrict__ til
 #pragma unroll
                         for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * out_scale);
                     }
-                    slab_wait();
-                    uint8_t *slab = slab_pair + sb * kSlabBytes;
+                    __syncwarp();   // the copy-out of the previous slab is done in every lane
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
                         uint4 w = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
                         *reinterpret_cast<uint4 *>(slab + lane * 128 + ((j ^ (lane & 7)) << 4)) = w;
                     }
-                    fence_async_smem();
                     __syncwarp();
-                    if (lane == 0 && !dbg_no_global) {
-                        tma_store_2d(map32, smem_u32(slab), n0 + c0 + 32 * sub, slab_row0);
-                        tma_store_commit();
-                    }
-                    slab_next();
+                    if (!dbg_no_global)
+                        slab_to_global(out32, pitch32, slab_row0, (int)M, (n0 + c0 + 32 * sub) * 4, (int)pitch32);
                 }
             } else {
                 // 16-bit result: the chunk's 64 columns are read in two halves of 32 and packed
@@ -728,39 +740,28 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const void *__restrict__ til
                 }
                 if (CHAINED && unpublished != kNoSlot) publish();
                 if (in_range) {
-                    slab_wait();
-                    uint8_t *slab = slab_pair + sb * kSlabBytes;
+                    __syncwarp();   // the copy-out of the previous slab is done in every lane
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
                         const uint4 w = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
                         *reinterpret_cast<uint4 *>(slab + lane * 128 + ((j ^ (lane & 7)) << 4)) = w;
                     }
-                    fence_async_smem();
                     __syncwarp();
-                    if (lane == 0 && !dbg_no_global) {
-                        tma_store_2d(map16, smem_u32(slab), n0 + c0, slab_row0);
-                        tma_store_commit();
-                    }
-                    slab_next();
+                    if (!dbg_no_global) slab_to_global(out16, pitch16, slab_row0, (int)M, (n0 + c0) * 2, (int)pitch16);
                     if (mirror) {
                         // transposed 64 x 32 block (rows = this chunk's columns), plain row-major
                         // 64-byte rows: lanes pair up so every lane stores two rows of one column
-                        slab_wait();
-                        uint8_t *slab_t = slab_pair + sb * kSlabBytes;
+                        __syncwarp();
 #pragma unroll
                         for (int c = 0; c < 64; c += 2) {
                             const uint32_t mine = packed[c >> 1];
                             const uint32_t other = __shfl_xor_sync(0xffffffffu, mine, 1);
                             const uint32_t out = (lane & 1) ? __byte_perm(other, mine, 0x7632) : __byte_perm(mine, other, 0x5410);
-                            *reinterpret_cast<uint32_t *>(slab_t + (c + (lane & 1)) * 64 + (lane & ~1) * 2) = out;
+                            *reinterpret_cast<uint32_t *>(slab + (c + (lane & 1)) * 64 + (lane & ~1) * 2) = out;
                         }
-                        fence_async_smem();
                         __syncwarp();
-                        if (lane == 0 && !dbg_no_global) {
-                            tma_store_2d(map16t, smem_u32(slab_t), slab_row0, n0 + c0);
-                            tma_store_commit();
-                        }
-                        slab_next();
+                        if (!dbg_no_global)
+                            slab_t_to_global(out16, pitch16, n0 + c0, (int)M, slab_row0 * 2, (int)pitch16);
                     }
                 }
             }
@@ -772,8 +773,6 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const void *__restrict__ til
             if (acc == 0) acc_phase ^= 1u;
         }
         if (CHAINED && unpublished != kNoSlot) publish();
-        if (lane == 0) tma_store_wait_all();
-        __syncwarp();
     }
 
     __syncthreads();
