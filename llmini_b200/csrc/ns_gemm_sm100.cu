@@ -11,7 +11,7 @@
 //   Apply  X' = Q X                      (reference: tiles.rs:14-38)
 // Operands are read in their storage orientation: an operand whose reduction dimension is
 // the slow one is described to the tensor core as MN-major, so no transpose is ever
-// materialised.  16-bit results leave through shared memory and TMA stores; the FP32 Gram
+// materialised.  16-bit results leave through a shared-memory slab and coalesced stores; the FP32 Gram
 // tile that the polynomial epilogue needs is kept in a private fragment-ordered scratch so
 // both sides access it fully coalesced.
 //
@@ -40,10 +40,7 @@ constexpr int kSmemLimit = 227 * 1024;
 constexpr uint32_t kSpinLimit = 1u << 24;    // hard cap on polls, whatever the timer says
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
-// SLABS = 2: every epilogue warp has two store slabs and fills one while the TMA store engine
-// still reads the other; it costs one pipeline stage.  Used where the epilogue, not the
-// mainloop, bounds the tile (the symmetric Gram / polynomial launches of the pair kernel).
-template <int BN, bool PAIR, int SLABS = 1>
+template <int BN, bool PAIR>
 struct Cfg {
     static constexpr int kBRows = PAIR ? 128 : BN;   // rows of B this CTA stages per k-block
     static constexpr int kBBytes = (kBRows / 64) * kBoxBytes;
@@ -52,7 +49,7 @@ struct Cfg {
     // quarter) for every 64 columns of the tile
     static constexpr int kEpiWarps = 4 * (BN / 64);
     static constexpr int kThreads = 32 * (2 + kEpiWarps);
-    static constexpr int kStagingBytes = SLABS * kEpiWarps * kSlabBytes;
+    static constexpr int kStagingBytes = kEpiWarps * kSlabBytes;
     static constexpr int kTmemCols = 2 * BN;
     static constexpr int kBarrierBytes = 512;   // mbarriers, flags, and the tile ring of the chained launch
     static constexpr int kStages = (kSmemLimit - kStagingBytes - kBarrierBytes - 1024) / kStageBytes;
@@ -155,9 +152,9 @@ struct ChainSync {
 };
 // Bounded wait until `*counter >= need`.  Returns false when the limit ran out or the launch is aborting.
 //
-// How a tile's outputs reach the CTA that reads them.  The writer's epilogue warps wait for their TMA stores
-// to complete (cp.async.bulk.wait_group 0), order them and their plain stores (the FP32 Gram tile) before what
-// follows (fence.proxy.async, __threadfence) and only then raise the matrix's progress count with an atomic.
+// How a tile's outputs reach the CTA that reads them.  Every lane of the writer's epilogue warp orders its
+// stores before what follows (__threadfence), the warp converges, and one lane raises the matrix's progress
+// count with an atomic.
 // The reader polls the count with relaxed loads that bypass L1; once it is high enough it reads it once more
 // with acquire semantics and issues fence.proxy.async before its first TMA copy, which is what the PTX memory
 // model asks for between a generic-proxy flag and async-proxy accesses.  Both fences were measured against a
@@ -327,13 +324,13 @@ __device__ __forceinline__ TileWork tile_work(const void *tiles, uint32_t t, uin
     return w;
 }
 
-template <int BN, bool PAIR, int SLABS, bool CHAINED>
-__global__ void __launch_bounds__((Cfg<BN, PAIR, SLABS>::kThreads), 1)
+template <int BN, bool PAIR, bool CHAINED>
+__global__ void __launch_bounds__((Cfg<BN, PAIR>::kThreads), 1)
 k_ns_gemm(const GemmProblem *__restrict__ problems, const void *__restrict__ tiles,
           uint32_t tile_count, uint32_t epilogue_arg, int f16, GemmCoefficients coef,
           const float *__restrict__ slot_scale, uint32_t scale_pow_arg, uint32_t *status, ChainSync *sync,
           uint32_t slot_count, uint32_t debug_flags) {
-    using C = Cfg<BN, PAIR, SLABS>;
+    using C = Cfg<BN, PAIR>;
 #ifdef B2_MEASURE
     const bool dbg_no_store = debug_flags & 1u;   // drop every epilogue store
     const bool dbg_no_global = debug_flags & 8u;  // stage in shared memory but issue no global store
@@ -554,11 +551,9 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const void *__restrict__ til
         // Results leave through a per-warp 4 KB slab in shared memory and plain 128-bit global stores: the warp
         // writes its 32 rows into the slab (one row per lane, 16-byte chunks XOR-swizzled by the row so that the
         // fill and the copy-out are both conflict-free), then copies it out with eight lanes per row, so every
-        // store instruction writes whole 128-byte lines.  (TMA stores were measured to take about 5 us from issue
-        // to completion, cp.async.bulk.wait_group 0, even on an idle GPU: that wait sat at the end of every launch
-        // and, in the chained launch, between every tile and the tiles that depend on it.  Plain stores are
-        // complete after a fence.)
-        uint8_t *slab = staging + (size_t)(warp - 2) * SLABS * kSlabBytes;
+        // store instruction writes whole 128-byte lines.  Plain stores need no bulk-group wait before the slab
+        // is refilled or the launch ends, and a fence orders them before the progress count of a chained launch.
+        uint8_t *slab = staging + (size_t)(warp - 2) * kSlabBytes;
         // 32 rows x 128 bytes, swizzled -> row-major tensor; rows >= row_limit and bytes >= byte_limit are dropped
         auto slab_to_global = [&](uint8_t *base, size_t pitch_bytes, int row0, int row_limit, int byte0, int byte_limit) {
 #pragma unroll 2
@@ -805,7 +800,7 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const void *__restrict__ til
     }
 }
 
-template <int BN, bool PAIR, int SLABS, bool CHAINED>
+template <int BN, bool PAIR, bool CHAINED>
 cudaError_t launch_impl(const GemmProblem *problems, const void *tiles, uint32_t tile_count, uint32_t epilogue,
                         int f16, const GemmCoefficients &coef, const float *slot_scale, uint32_t scale_pow,
                         uint32_t *status, void *sync, uint32_t slot_count, uint32_t debug_flags, int grid,
@@ -838,10 +833,10 @@ cudaError_t launch_impl(const GemmProblem *problems, const void *tiles, uint32_t
     cfg.attrs = attr;
     cfg.numAttrs = n_attr;
     cfg.gridDim = dim3((unsigned)grid, 1, 1);
-    cfg.blockDim = dim3((unsigned)Cfg<BN, PAIR, SLABS>::kThreads, 1, 1);
-    cfg.dynamicSmemBytes = Cfg<BN, PAIR, SLABS>::kSmemBytes;
+    cfg.blockDim = dim3((unsigned)Cfg<BN, PAIR>::kThreads, 1, 1);
+    cfg.dynamicSmemBytes = Cfg<BN, PAIR>::kSmemBytes;
     cfg.stream = s;
-    return cudaLaunchKernelEx(&cfg, k_ns_gemm<BN, PAIR, SLABS, CHAINED>, problems, tiles, tile_count, epilogue, f16, coef,
+    return cudaLaunchKernelEx(&cfg, k_ns_gemm<BN, PAIR, CHAINED>, problems, tiles, tile_count, epilogue, f16, coef,
                               slot_scale, scale_pow, status, static_cast<ChainSync *>(sync), slot_count, debug_flags);
 }
 
@@ -852,24 +847,24 @@ cudaError_t dispatch(int block_n, int pair, const GemmProblem *problems, const v
                      int grid, cudaStream_t s) {
     if (tile_count == 0) return cudaSuccess;
     if (pair && block_n == 256)
-        return launch_impl<256, true, 1, CHAINED>(problems, tiles, tile_count, epilogue, f16, coef, slot_scale, scale_pow,
+        return launch_impl<256, true, CHAINED>(problems, tiles, tile_count, epilogue, f16, coef, slot_scale, scale_pow,
                                                   status, sync, slot_count, debug_flags, grid, s);
     if (!pair && block_n == 256)
-        return launch_impl<256, false, 1, CHAINED>(problems, tiles, tile_count, epilogue, f16, coef, slot_scale, scale_pow,
+        return launch_impl<256, false, CHAINED>(problems, tiles, tile_count, epilogue, f16, coef, slot_scale, scale_pow,
                                                    status, sync, slot_count, debug_flags, grid, s);
     if (!pair && block_n == 128)
-        return launch_impl<128, false, 1, CHAINED>(problems, tiles, tile_count, epilogue, f16, coef, slot_scale, scale_pow,
+        return launch_impl<128, false, CHAINED>(problems, tiles, tile_count, epilogue, f16, coef, slot_scale, scale_pow,
                                                    status, sync, slot_count, debug_flags, grid, s);
     return cudaErrorInvalidValue;
 }
 
 template <int BN, bool PAIR>
 cudaError_t configure_both() {
-    cudaError_t e = cudaFuncSetAttribute(k_ns_gemm<BN, PAIR, 1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         Cfg<BN, PAIR, 1>::kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(k_ns_gemm<BN, PAIR, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg<BN, PAIR>::kSmemBytes);
     if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(k_ns_gemm<BN, PAIR, 1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                Cfg<BN, PAIR, 1>::kSmemBytes);
+    return cudaFuncSetAttribute(k_ns_gemm<BN, PAIR, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                Cfg<BN, PAIR>::kSmemBytes);
 }
 
 }  // namespace
