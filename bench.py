@@ -312,7 +312,8 @@ class GpuJob:
                 s.scales.copy_(headers[(r, c)])
             self.slots.append(s)
         self.normalize = b2.NORMALIZE_TWO_PASS if args.two_pass_prepare else b2.NORMALIZE_DEFERRED
-        self.schedule = b2.NS_CHAINED if args.ns_chained else b2.NS_PER_PHASE
+        self.schedule = {"per-phase": b2.NS_PER_PHASE, "chained": b2.NS_CHAINED,
+                         "fused": b2.NS_FUSED_GRAM_POLY}[args.ns_schedule]
         self.update_input = b2.UPDATE_16BIT if args.update_16bit else b2.UPDATE_F32
         self.plan = b2.MuonPlan(self.my_shapes, scale_layout=layout, device=dev, debug_flags=args.plan_flags,
                                 normalize_mode=self.normalize, ns_schedule=self.schedule,
@@ -350,7 +351,7 @@ class GpuJob:
         self.launches_per_step = 0
         if self.plan is not None:
             prepare = 3 if self.normalize == b2.NORMALIZE_TWO_PASS else 2
-            gemms = 1 if self.schedule == b2.NS_CHAINED else 3 * HP["iterations"]
+            gemms = {b2.NS_CHAINED: 1, b2.NS_FUSED_GRAM_POLY: 2 * HP["iterations"]}.get(self.schedule, 3 * HP["iterations"])
             self.launches_per_step += prepare + gemms + (2 if args.plan_flags & 16 else 1)
         self.launches_per_step += 3 if self.adam_sets else 0
         self.gather_stream = torch.cuda.Stream(device=dev) if world > 1 else None
@@ -763,8 +764,9 @@ def run_gpu(args):
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": workload_config(args.workload, world),
         "roofline": {
-            "bound": "tensor", "kernel": "k_ns_gemm (all 15 GEMMs of the step" + (" as one chained launch)" if args.ns_chained else
-                                                                                  ", one launch each)"),
+            "bound": "tensor", "kernel": "k_ns_gemm (all 15 GEMMs of the step" + {
+                "chained": " as one chained launch)", "per-phase": ", one launch each)",
+                "fused": ": per iteration one launch of fused Gram + polynomial tiles and one of apply tiles)"}[args.ns_schedule],
             "achieved": ns_tflops,
             "peak": peaks["tf_burst"], "unit": "TFLOP/s", "frac": ns_tflops / peaks["tf_burst"],
             "traffic": profiled_traffic(args.workload, world),
@@ -993,8 +995,9 @@ def main():
     ap.add_argument("--two-pass-prepare", action="store_true",
                     help="stages M+N with the reference's rounding point (the gradients are read twice) instead of "
                          "the one-pass form")
-    ap.add_argument("--ns-chained", action="store_true",
-                    help="Newton-Schulz as one chained persistent launch instead of three launches per iteration")
+    ap.add_argument("--ns-schedule", choices=["per-phase", "chained", "fused"], default="per-phase",
+                    help="Newton-Schulz launches: three per iteration, one chained persistent launch for the whole loop, "
+                         "or two per iteration with the Gram and polynomial tile of a position fused on one CTA pair")
     ap.add_argument("--update-16bit", action="store_true",
                     help="the last Newton-Schulz iteration stores BF16 and the update reads it (default: FP32, as the "
                          "reference's update input)")

@@ -102,8 +102,15 @@ enum { B2_NORMALIZE_TWO_PASS = 0, B2_NORMALIZE_DEFERRED = 1 };
  *   progress count of that matrix instead of launch boundaries, so phases of different matrices overlap.  Used
  *   when a step runs exactly `max_iterations` iterations (at most 8); other steps take the per-phase form.
  *   Bit-identical results; measured equal to the per-phase form on one GPU and slower when a rank owns few
- *   matrices, so it is not the default. */
-enum { B2_NS_PER_PHASE = 0, B2_NS_CHAINED = 1 };
+ *   matrices, so it is not the default.
+ * B2_NS_FUSED_GRAM_POLY: two launches per iteration.  In the first, the CTA (pair) that computes a Gram tile keeps
+ *   its FP32 accumulator in tensor memory, stores the 16-bit tile, waits (bounded) until the matrix's other Gram
+ *   tiles are stored, computes the polynomial tile of the same position into the second accumulator buffer and
+ *   combines the two in registers: the FP32 Gram tile never goes through memory.  Tiles are drawn with an atomic
+ *   ticket as in the chained form.  Needs every Gram tile of a matrix in flight at once, so a plan with a matrix
+ *   of more Gram tiles than the GPU has CTA slots (pairs: SMs / 2) takes the per-phase form.  Bit-identical
+ *   results. */
+enum { B2_NS_PER_PHASE = 0, B2_NS_CHAINED = 1, B2_NS_FUSED_GRAM_POLY = 2 };
 /* Precision in which the Newton-Schulz result reaches stage U.
  * B2_UPDATE_F32: the last Apply GEMM stores FP32 (the reference's `polar_update` is f32:
  *   crates/cuda-kernels/src/gpt/optimizer/muon/fused/update/one.rs:46-85).

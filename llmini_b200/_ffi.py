@@ -17,7 +17,7 @@ SCALES_CSF, SCALES_RAW, SCALES_SM100 = 0, 1, 2
 OPERAND_BF16, OPERAND_F16 = 0, 1
 QUANTIZE_X, QUANTIZE_Y = 0, 1
 NORMALIZE_TWO_PASS, NORMALIZE_DEFERRED = 0, 1
-NS_PER_PHASE, NS_CHAINED = 0, 1
+NS_PER_PHASE, NS_CHAINED, NS_FUSED_GRAM_POLY = 0, 1, 2
 UPDATE_F32, UPDATE_16BIT = 0, 1
 ERROR_INVALID_VALUE, ERROR_NOT_SUPPORTED, ERROR_LAUNCH_TIMEOUT = 1, 801, 702
 

@@ -119,6 +119,8 @@ struct Layout {
     std::vector<uint32_t> items;         // work list of the fused update + encode launch
     uint32_t chain_tiles = 0;            // entries of the chained Newton-Schulz work list (0: not built)
     uint32_t chain_iterations = 0;
+    uint32_t gp_tiles = 0;               // entries of ONE fused Gram + polynomial work list (0: not built); three lists
+    uint32_t gp_widest = 0;              // most Gram tiles any one matrix has
     uint32_t total_chunks = 0;
     int bn = 256;
     int pair = 0;   // 1: two-CTA 256 x 256 tiles
@@ -126,7 +128,7 @@ struct Layout {
     int tile_m = 128;
     size_t off_prefix, off_partials, off_inv_norm, off_amax_x, off_status, off_x0_ptrs, off_x1_ptrs, off_u_ptrs, off_maps,
         off_problems, off_tiles_nn, off_tiles_out, off_unit_prefix, off_factor_ptrs, off_unit_partials, off_slot_stats,
-        off_items, off_fused_sync, off_chain, off_chain_sync, off_meta_end, total;
+        off_items, off_fused_sync, off_chain, off_gp, off_chain_sync, off_meta_end, total;
     uint32_t tiles_nn = 0, tiles_out = 0;
 };
 
@@ -259,6 +261,9 @@ bool build_layout(const uint32_t *rows, const uint32_t *cols, uint32_t count, co
         L.chain_tiles = o.max_iterations * (2 * L.tiles_nn + L.tiles_out);
     }
     L.off_chain = take((size_t)std::max(L.chain_tiles, 1u) * sizeof(ChainTile));
+    // fused Gram + polynomial tiles: one list for the first iteration, one for odd and one for later even ones
+    L.gp_tiles = (o.ns_schedule == B2_NS_FUSED_GRAM_POLY && count <= 0xffffu) ? L.tiles_nn : 0u;
+    L.off_gp = take((size_t)std::max(3u * L.gp_tiles, 1u) * sizeof(ChainTile));
     L.off_meta_end = off;
     // ---- per-step scratch ----
     L.off_partials = take((size_t)std::max(chunks, 1u) * B2_ONE_PASS_PARTIALS * sizeof(double));
@@ -305,6 +310,7 @@ struct b2_muon_plan {
     std::vector<uint8_t> meta;  // host image of the metadata region
     double flops_per_iteration = 0.0;
     uint64_t fused_wait_ns = 2000000000ull;   // limit of the completion-counter wait in the update + encode launch
+    uint32_t resident_groups = 0;             // CTAs (pairs) of the ticketed GEMM kernel the device runs at once
 
     template <typename T>
     T *at(size_t off) const { return reinterpret_cast<T *>(ws + off); }
@@ -373,7 +379,7 @@ int b2_muon_plan_create(b2_muon_plan **out, const uint32_t *rows, const uint32_t
     if (reinterpret_cast<uintptr_t>(d_workspace) % 1024 != 0) return B2_ERROR_INVALID_VALUE;
     b2_muon_options o = normalized(options);
     if (o.operand_format > B2_OPERAND_F16 || o.scale_layout > B2_SCALES_SM100 || o.quantize_target > B2_QUANTIZE_Y ||
-        o.normalize_mode > B2_NORMALIZE_DEFERRED || o.ns_schedule > B2_NS_CHAINED || o.update_input > B2_UPDATE_16BIT)
+        o.normalize_mode > B2_NORMALIZE_DEFERRED || o.ns_schedule > B2_NS_FUSED_GRAM_POLY || o.update_input > B2_UPDATE_16BIT)
         return B2_ERROR_INVALID_VALUE;
     // an un-normalised update can leave F16's range: the one-pass prepare is for BF16 operands
     if (o.normalize_mode == B2_NORMALIZE_DEFERRED && o.operand_format != B2_OPERAND_BF16) return B2_ERROR_INVALID_VALUE;
@@ -387,6 +393,7 @@ int b2_muon_plan_create(b2_muon_plan **out, const uint32_t *rows, const uint32_t
     p->ws = static_cast<uint8_t *>(d_workspace);
     e = gemm_configure(L.bn, L.pair);
     if (e != cudaSuccess) { delete p; return (int)e; }
+    p->resident_groups = (uint32_t)std::max(gemm_resident_groups(L.bn, L.pair, p->dev.sm_count), 0);
 
     p->meta.assign(L.off_meta_end, 0);
     uint8_t *h = p->meta.data();
@@ -501,7 +508,7 @@ int b2_muon_plan_create(b2_muon_plan **out, const uint32_t *rows, const uint32_t
         const bool deferred = o.normalize_mode == B2_NORMALIZE_DEFERRED;
         uint32_t n = 0;
         auto emit = [&](const GemmTile &t, uint32_t type, uint32_t epi, uint32_t scale_pow, uint32_t it) {
-            ChainTile c;
+            ChainTile c = {};
             c.problem = type * slot_count + t.problem;
             c.tile_m = t.tile_m;
             c.tile_n = t.tile_n;
@@ -522,6 +529,35 @@ int b2_muon_plan_create(b2_muon_plan **out, const uint32_t *rows, const uint32_t
             for (uint32_t i = 0; i < iout; ++i)
                 emit(tout[i], (last32 ? kLast0 : kApply0) + b, last32 ? kEpiApplyLast : kEpiApply, first_scaled ? 1u : 0u, it);
             for (uint32_t s = 0; s < slot_count; ++s) done[s] += out_tiles[s];
+        }
+    }
+    if (L.gp_tiles) {
+        // One entry per Gram tile, a matrix's entries next to each other: the CTA (pair) that draws it computes the
+        // Gram tile, publishes its 16-bit form, waits for the matrix's other Gram tiles (need2) and goes on to the
+        // polynomial tile of the same position.  The progress counts start from zero in every launch.
+        ChainTile *gp = reinterpret_cast<ChainTile *>(h + L.off_gp);
+        const uint32_t warps = chain_epilogue_warps(L.bn, L.pair);
+        std::vector<uint32_t> nn_tiles(slot_count, 0);
+        for (uint32_t i = 0; i < inn; ++i) ++nn_tiles[tnn[i].problem];
+        L.gp_widest = 0;
+        for (uint32_t s = 0; s < slot_count; ++s) L.gp_widest = std::max(L.gp_widest, nn_tiles[s]);
+        const bool deferred = o.normalize_mode == B2_NORMALIZE_DEFERRED;
+        for (uint32_t list = 0; list < 3; ++list) {
+            const uint32_t b = list == 1 ? 1u : 0u;
+            const uint32_t scale_pow = (list == 0 && deferred) ? 2u : 0u;
+            for (uint32_t i = 0; i < inn; ++i) {
+                ChainTile c = {};
+                c.problem = (kGram0 + b) * slot_count + tnn[i].problem;
+                c.tile_m = tnn[i].tile_m;
+                c.tile_n = tnn[i].tile_n;
+                c.slot = tnn[i].problem;
+                c.epilogue = (uint8_t)kEpiGramPoly;
+                c.flags = (uint8_t)((tnn[i].reserved ? 1u : 0u) | (scale_pow << 1));
+                c.need = 0;
+                c.problem2 = kPoly * slot_count + tnn[i].problem;
+                c.need2 = warps * nn_tiles[tnn[i].problem];
+                gp[(size_t)list * L.gp_tiles + i] = c;
+            }
         }
     }
     e = cudaMemcpyAsync(p->ws, h, L.off_meta_end, cudaMemcpyHostToDevice, as_stream(stream));
@@ -625,6 +661,8 @@ int b2_muon_polar(b2_muon_plan *plan, const b2_muon_step_args *a, void *stream) 
         return (int)launch_ns_chain(L.bn, L.pair, probs, plan->at<ChainTile>(L.off_chain), L.chain_tiles, f16, coef, scale,
                                     status, plan->ws + L.off_chain_sync, count, plan->options.measure_flags, grid, s);
     }
+    // The fused form needs all Gram tiles of a matrix in flight at once: one CTA (pair) each.
+    const bool fused_gram_poly = L.gp_tiles != 0 && L.gp_widest <= plan->resident_groups;
     for (uint32_t it = 0; it < a->iterations && e == cudaSuccess; ++it) {
         float ca, cb, cc;
         if (a->coefficients) {
@@ -641,12 +679,21 @@ int b2_muon_polar(b2_muon_plan *plan, const b2_muon_step_args *a, void *stream) 
         // s^2 and its Apply output s, s = inv_norm[slot]
         const float *scale = (it == 0 && plan->options.normalize_mode == B2_NORMALIZE_DEFERRED)
                                  ? plan->at<float>(L.off_inv_norm) : nullptr;
-        if (mask & 1u)
-            e = launch_ns_gemm(L.bn, L.pair, probs + (size_t)(kGram0 + b) * count, tnn, L.tiles_nn, kEpiGram, f16, ca, cb, cc,
-                               scale, 2u, status, dbg, grid, s);
-        if (e == cudaSuccess && (mask & 2u))
-            e = launch_ns_gemm(L.bn, L.pair, probs + (size_t)kPoly * count, tnn, L.tiles_nn, kEpiPoly, f16, ca, cb, cc,
-                               nullptr, 0u, status, dbg, grid, s);
+        if (fused_gram_poly && (mask & 3u) == 3u) {
+            // Gram and polynomial tile of one position on one CTA (pair): the FP32 Gram tile stays in tensor memory
+            GemmCoefficients coef = {};
+            coef.v[0] = ca; coef.v[1] = cb; coef.v[2] = cc;
+            const uint32_t list = it == 0 ? 0u : ((it & 1u) ? 1u : 2u);
+            e = launch_ns_chain(L.bn, L.pair, probs, plan->at<ChainTile>(L.off_gp) + (size_t)list * L.gp_tiles, L.gp_tiles,
+                                f16, coef, scale, status, plan->ws + L.off_chain_sync, count, dbg, grid, s, true);
+        } else {
+            if (mask & 1u)
+                e = launch_ns_gemm(L.bn, L.pair, probs + (size_t)(kGram0 + b) * count, tnn, L.tiles_nn, kEpiGram, f16, ca, cb,
+                                   cc, scale, 2u, status, dbg, grid, s);
+            if (e == cudaSuccess && (mask & 2u))
+                e = launch_ns_gemm(L.bn, L.pair, probs + (size_t)kPoly * count, tnn, L.tiles_nn, kEpiPoly, f16, ca, cb, cc,
+                                   nullptr, 0u, status, dbg, grid, s);
+        }
         if (e == cudaSuccess && (mask & 4u))
             e = launch_ns_gemm(L.bn, L.pair, probs + (size_t)((last ? kLast0 : kApply0) + b) * count, tout, L.tiles_out,
                                last ? kEpiApplyLast : kEpiApply, f16, ca, cb, cc, scale, 1u, status, dbg, grid, s);

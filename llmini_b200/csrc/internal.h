@@ -120,6 +120,13 @@ enum GemmEpilogue : uint32_t {
     kEpiPoly = 1,   // out16 = r16(fma(c, acc, fma(b, frag32, a * delta_ij)))
     kEpiApply = 2,  // out16 = r16(acc)
     kEpiApplyLast = 3,  // out32 = acc (f32, storage layout)
+    // Work-list entries of the ticketed launch only.  kEpiGramPoly: the CTA (pair) computes the Gram tile, keeps its
+    // FP32 accumulator in tensor memory, waits until every Gram tile of the matrix has been stored, computes the
+    // polynomial tile of the same position into the other accumulator buffer and combines the two in registers,
+    // so the FP32 Gram tile never leaves the SM.  The kernel runs it as the two parts below.
+    kEpiGramPoly = 4,
+    kEpiGramHold = 5,   // out16 = r16(acc); the accumulator buffer stays occupied
+    kEpiPolyFused = 6,  // out16 = r16(fma(c, acc, fma(b, held Gram accumulator, a * delta_ij))); frees both buffers
 };
 
 // One GEMM of one slot: D[M][N] = A * B^T with A, B described by TMA maps.  Lives in device
@@ -166,10 +173,18 @@ struct alignas(16) ChainTile {
     uint8_t flags;         // bit 0: also store the transposed tile; bits 1-2: power of the slot scale applied to
                            // the accumulator (one-pass prepare); bits 3-7: iteration (coefficient triple)
     uint32_t need;
+    // kEpiGramPoly only: the polynomial GEMM of the tile and the progress count at which every Gram tile of the
+    // matrix has been stored (need + epilogue warps x Gram tiles of the matrix)
+    uint32_t problem2;
+    uint32_t need2;
+    uint32_t reserved[2];
 };
-static_assert(sizeof(ChainTile) == 16, "ChainTile is read as one 16-byte word");
+static_assert(sizeof(ChainTile) == 32, "ChainTile is read as two 16-byte words");
 
 cudaError_t gemm_configure(int block_n, int pair);
+// CTAs (pairs of CTAs when `pair`) of the ticketed kernel that the device runs at the same time, 0 if unknown.
+// Call after gemm_configure.
+int gemm_resident_groups(int block_n, int pair, int sm_count);
 // `slot_scale` (may be null): per-slot scalars s; the Gram epilogue multiplies the accumulator by s^scale_pow
 // (scale_pow = 2) and the Apply epilogues by s (scale_pow = 1).  Used by the first iteration after a
 // one-pass prepare, whose operand is not normalised yet.
@@ -178,13 +193,16 @@ cudaError_t launch_ns_gemm(int block_n, int pair, const GemmProblem *problems, c
                            float cc, const float *slot_scale, uint32_t scale_pow, uint32_t *status,
                            uint32_t debug_flags, int grid, cudaStream_t s);
 
-// The chained launch (see ChainTile).  `sync` is chain_sync_bytes(slot_count) of device memory, zeroed once by
+// The ticketed launch over a ChainTile list.  `fused_list`: the list holds kEpiGramPoly entries, whose second part
+// waits for tiles with LARGER tickets of the same matrix; a CTA then never holds a ticket it has not started
+// while it waits, every matrix's entries must be contiguous in the list, and no matrix may have more Gram tiles
+// than the launch has CTAs (pairs).  `sync` is chain_sync_bytes(slot_count) of device memory, zeroed once by
 // the owner; every launch leaves it zeroed.  chain_epilogue_warps: progress-count increments per finished tile.
 size_t chain_sync_bytes(uint32_t slot_count);
 uint32_t chain_epilogue_warps(int block_n, int pair);
 cudaError_t launch_ns_chain(int block_n, int pair, const GemmProblem *problems, const ChainTile *tiles,
                             uint32_t tile_count, int f16, const GemmCoefficients &coef, const float *slot_scale,
                             uint32_t *status, void *sync, uint32_t slot_count, uint32_t debug_flags, int grid,
-                            cudaStream_t s);
+                            cudaStream_t s, bool fused_list = false);
 
 }  // namespace b2

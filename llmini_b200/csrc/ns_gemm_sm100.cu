@@ -263,6 +263,16 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t *r) {
         : "r"(taddr)
         : "memory");
 }
+// 32 lanes x 16 consecutive 32-bit columns
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t *r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
 __device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1 (sm_100).
@@ -294,12 +304,32 @@ __device__ __forceinline__ uint32_t instr_desc(int m, int n, int f16, uint32_t a
 // may be read.
 struct TileWork {
     uint32_t problem, tile_m, tile_n, mirror, epilogue, slot, need, scale_pow, iter;
+    uint32_t problem2, need2;   // second part of a kEpiGramPoly entry
 };
+// A work-list entry runs as one GEMM, or (kEpiGramPoly) as two on the same CTA (pair): part 0 the Gram tile,
+// whose accumulator stays in tensor memory, part 1 the polynomial tile that consumes it.
+struct TilePart {
+    uint32_t problem, epilogue, need;
+};
+__device__ __forceinline__ uint32_t tile_parts(const TileWork &w) { return w.epilogue == kEpiGramPoly ? 2u : 1u; }
+__device__ __forceinline__ TilePart tile_part(const TileWork &w, uint32_t part) {
+    TilePart p;
+    if (w.epilogue != kEpiGramPoly) {
+        p.problem = w.problem; p.epilogue = w.epilogue; p.need = w.need;
+    } else if (part == 0u) {
+        p.problem = w.problem; p.epilogue = kEpiGramHold; p.need = w.need;
+    } else {
+        p.problem = w.problem2; p.epilogue = kEpiPolyFused; p.need = w.need2;
+    }
+    return p;
+}
 template <bool CHAINED>
 __device__ __forceinline__ TileWork tile_work(const void *tiles, uint32_t t, uint32_t epilogue, uint32_t scale_pow) {
     TileWork w;
+    w.problem2 = 0;
+    w.need2 = 0;
     if (CHAINED) {
-        const uint4 c = __ldg(reinterpret_cast<const uint4 *>(tiles) + t);
+        const uint4 c = __ldg(reinterpret_cast<const uint4 *>(tiles) + 2 * (size_t)t);
         w.problem = c.x;
         w.tile_m = c.y & 0xffffu;
         w.tile_n = c.y >> 16;
@@ -309,6 +339,11 @@ __device__ __forceinline__ TileWork tile_work(const void *tiles, uint32_t t, uin
         w.scale_pow = (c.z >> 25) & 3u;
         w.iter = (c.z >> 27) & 31u;
         w.need = c.w;
+        if (w.epilogue == kEpiGramPoly) {
+            const uint4 d = __ldg(reinterpret_cast<const uint4 *>(tiles) + 2 * (size_t)t + 1);
+            w.problem2 = d.x;
+            w.need2 = d.y;
+        }
     } else {
         const GemmTile tl = reinterpret_cast<const GemmTile *>(tiles)[t];
         w.problem = tl.problem;
@@ -412,6 +447,10 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const void *__restrict__ til
             // the next tile's description and progress count fetched, while this tile's copies are issued.
             uint32_t seq = 0, t = first_tile, t_next = kNoTile;
             const bool claims = CHAINED && (!PAIR || rank == 0);
+            // A list with fused Gram + polynomial entries: their second part waits for tiles with larger tickets, so
+            // a CTA must not sit on a ticket it has not started.  The next ticket is then drawn only once the last
+            // wait of the current tile has passed, and looked at after the tile's copies have been issued.
+            const bool fused_list = CHAINED && epilogue_arg != 0u;
             const uint32_t peer_ring = (CHAINED && PAIR) ? map_to_cta(smem_u32(const_cast<uint64_t *>(tile_ring)), 1) : 0u;
             auto announce = [&](uint32_t tile) {   // leader: tell this CTA's roles (and the peer CTA) the seq-th tile
                 ring_put_local(tile_ring, seq, tile);
@@ -421,83 +460,107 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const void *__restrict__ til
                 if (claims) {
                     t = atomicAdd(&sync->ticket, 1u);
                     announce(t);
-                    if (t < tile_count) t_next = atomicAdd(&sync->ticket, 1u);
+                    if (!fused_list && t < tile_count) t_next = atomicAdd(&sync->ticket, 1u);
                 } else {
                     t = ring_get(tile_ring, seq, abort_flag);
                 }
             }
             TileWork next = {};
             uint32_t next_seen = 0;
-            if (t < tile_count) {
-                next = tile_work<CHAINED>(tiles, t, epilogue_arg, scale_pow_arg);
-                if (CHAINED && next.need != 0u) next_seen = ld_relaxed_gpu(&sync->progress[next.slot]);
-            }
-            while (ok && t < tile_count) {
-                const TileWork tl = next;
-                const uint32_t seen = next_seen;
-                const uint32_t t_now = t;
-                // the tile after this one
-                if (!CHAINED) {
-                    t += tile_stride;
-                } else if (claims) {
-                    t = t_next;
-                    ++seq;
-                    announce(t);
-                    if (t < tile_count) t_next = atomicAdd(&sync->ticket, 1u);
-                } else {
-                    ++seq;
-                    t = ring_get(tile_ring, seq, abort_flag);
-                }
+            auto describe_next = [&]() {
                 if (t < tile_count) {
                     next = tile_work<CHAINED>(tiles, t, epilogue_arg, scale_pow_arg);
                     if (CHAINED && next.need != 0u) next_seen = ld_relaxed_gpu(&sync->progress[next.slot]);
                 }
-                const GemmProblem *p = problems + tl.problem;
-                const uint64_t map_a = p->map_a, map_b = p->map_b;
-                const uint32_t a_mn = p->a_mn_major, b_mn = p->b_mn_major, K = p->K;
-                const int m0 = tl.tile_m * C::kTileM + (int)rank * 128;
-                const int n0 = tl.tile_n * BN + (PAIR ? (int)rank * 128 : 0);
-                const int num_kb = (int)((K + kGemmBlockK - 1) / kGemmBlockK);
-                // A diagonal tile of X X^T or G G: this CTA's 128 rows of B are its 128 rows of A, in
-                // the same shared-memory layout.  They are loaded once and the MMA reads them twice.
-                const bool shared_operand = PAIR && tl.tile_m == tl.tile_n && map_a == map_b && a_mn == b_mn;
-                if (CHAINED && tl.need != 0u) {
-                    // the operands are the outputs of the matrix's previous phase: every tile of that phase
-                    // has been stored and published before the first copy is issued
-                    if (seen < tl.need &&
-                        !chain_wait(&sync->progress[tl.slot], tl.need, &sync->abort, abort_flag)) { ok = false; break; }
-                    (void)ld_acquire_gpu(&sync->progress[tl.slot]);
-                    fence_proxy_async_all();
+            };
+            describe_next();
+            while (ok && t < tile_count) {
+                const TileWork tl = next;
+                const uint32_t seen = next_seen;
+                const uint32_t t_now = t;
+                const uint32_t parts = CHAINED ? tile_parts(tl) : 1u;
+                // the tile after this one
+                if (!CHAINED) {
+                    t += tile_stride;
+                    describe_next();
+                } else if (!fused_list) {
+                    if (claims) {
+                        t = t_next;
+                        ++seq;
+                        announce(t);
+                        if (t < tile_count) t_next = atomicAdd(&sync->ticket, 1u);
+                    } else {
+                        ++seq;
+                        t = ring_get(tile_ring, seq, abort_flag);
+                    }
+                    describe_next();
                 }
-                if (CHAINED) *passed_tile = t_now + 1u;
-                const uint32_t stage_tx = shared_operand ? 2u * (uint32_t)kABytes
-                                                         : (uint32_t)C::kStageBytes * (PAIR ? 2u : 1u);
-                for (int kb = 0; kb < num_kb; ++kb) {
-                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
-                    // PAIR: both CTAs' copies complete on the leader's barrier, which expects
-                    // the bytes of both
-                    const uint32_t fb = PAIR ? map_to_cta(full_bar(stage), 0) : full_bar(stage);
-                    if (!PAIR || rank == 0) mbar_expect_tx(full_bar(stage), stage_tx);
-                    const uint32_t sa = smem_u32(stage_base + stage * C::kStageBytes);
-                    const uint32_t sb = sa + kABytes;
-                    const int k0 = kb * kGemmBlockK;
-                    if (a_mn) {  // 64 x 64 boxes: x = M index, y = K index
-                        tma_load_2d<PAIR>(sa, map_a, fb, m0, k0);
-                        tma_load_2d<PAIR>(sa + kBoxBytes, map_a, fb, m0 + 64, k0);
-                    } else {     // one 64 (K) x 128 (rows) box
-                        tma_load_2d<PAIR>(sa, map_a, fb, k0, m0);
+                uint32_t drawn = kNoTile;
+                for (uint32_t part = 0; ok && part < parts; ++part) {
+                    TilePart tp;
+                    if (CHAINED) {
+                        tp = tile_part(tl, part);
+                    } else {
+                        tp.problem = tl.problem; tp.epilogue = tl.epilogue; tp.need = 0u;
                     }
-#pragma unroll
-                    for (int j = 0; j < C::kBRows / 128; ++j) {
-                        if (shared_operand) break;
-                        if (b_mn) {
-                            tma_load_2d<PAIR>(sb + (2 * j) * kBoxBytes, map_b, fb, n0 + 128 * j, k0);
-                            tma_load_2d<PAIR>(sb + (2 * j + 1) * kBoxBytes, map_b, fb, n0 + 128 * j + 64, k0);
-                        } else {
-                            tma_load_2d<PAIR>(sb + (2 * j) * kBoxBytes, map_b, fb, k0, n0 + 128 * j);
+                    const GemmProblem *p = problems + tp.problem;
+                    const uint64_t map_a = p->map_a, map_b = p->map_b;
+                    const uint32_t a_mn = p->a_mn_major, b_mn = p->b_mn_major, K = p->K;
+                    const int m0 = tl.tile_m * C::kTileM + (int)rank * 128;
+                    const int n0 = tl.tile_n * BN + (PAIR ? (int)rank * 128 : 0);
+                    const int num_kb = (int)((K + kGemmBlockK - 1) / kGemmBlockK);
+                    // A diagonal tile of X X^T or G G: this CTA's 128 rows of B are its 128 rows of A, in
+                    // the same shared-memory layout.  They are loaded once and the MMA reads them twice.
+                    const bool shared_operand = PAIR && tl.tile_m == tl.tile_n && map_a == map_b && a_mn == b_mn;
+                    if (CHAINED && tp.need != 0u) {
+                        // the operands are the outputs of the matrix's previous phase: every tile of that phase
+                        // has been stored and published before the first copy is issued
+                        if ((part != 0u || seen < tp.need) &&
+                            !chain_wait(&sync->progress[tl.slot], tp.need, &sync->abort, abort_flag)) { ok = false; break; }
+                        (void)ld_acquire_gpu(&sync->progress[tl.slot]);
+                        fence_proxy_async_all();
+                    }
+                    if (CHAINED && part == 0u) *passed_tile = t_now + 1u;
+                    if (fused_list && claims && part + 1u == parts) drawn = atomicAdd(&sync->ticket, 1u);
+                    const uint32_t stage_tx = shared_operand ? 2u * (uint32_t)kABytes
+                                                             : (uint32_t)C::kStageBytes * (PAIR ? 2u : 1u);
+                    for (int kb = 0; kb < num_kb; ++kb) {
+                        if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
+                        // PAIR: both CTAs' copies complete on the leader's barrier, which expects
+                        // the bytes of both
+                        const uint32_t fb = PAIR ? map_to_cta(full_bar(stage), 0) : full_bar(stage);
+                        if (!PAIR || rank == 0) mbar_expect_tx(full_bar(stage), stage_tx);
+                        const uint32_t sa = smem_u32(stage_base + stage * C::kStageBytes);
+                        const uint32_t sb = sa + kABytes;
+                        const int k0 = kb * kGemmBlockK;
+                        if (a_mn) {  // 64 x 64 boxes: x = M index, y = K index
+                            tma_load_2d<PAIR>(sa, map_a, fb, m0, k0);
+                            tma_load_2d<PAIR>(sa + kBoxBytes, map_a, fb, m0 + 64, k0);
+                        } else {     // one 64 (K) x 128 (rows) box
+                            tma_load_2d<PAIR>(sa, map_a, fb, k0, m0);
                         }
+#pragma unroll
+                        for (int j = 0; j < C::kBRows / 128; ++j) {
+                            if (shared_operand) break;
+                            if (b_mn) {
+                                tma_load_2d<PAIR>(sb + (2 * j) * kBoxBytes, map_b, fb, n0 + 128 * j, k0);
+                                tma_load_2d<PAIR>(sb + (2 * j + 1) * kBoxBytes, map_b, fb, n0 + 128 * j + 64, k0);
+                            } else {
+                                tma_load_2d<PAIR>(sb + (2 * j) * kBoxBytes, map_b, fb, k0, n0 + 128 * j);
+                            }
+                        }
+                        if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
                     }
-                    if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+                }
+                if (fused_list && ok) {
+                    ++seq;
+                    if (claims) {
+                        t = drawn;
+                        announce(t);
+                    } else {
+                        t = ring_get(tile_ring, seq, abort_flag);
+                    }
+                    describe_next();
                 }
             }
         }
@@ -510,34 +573,37 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const void *__restrict__ til
             for (uint32_t t = CHAINED ? ring_get(tile_ring, 0u, abort_flag) : first_tile; ok && t < tile_count;
                  t = CHAINED ? ring_get(tile_ring, ++seq, abort_flag) : t + tile_stride) {
                 const TileWork tl = tile_work<CHAINED>(tiles, t, epilogue_arg, scale_pow_arg);
-                const GemmProblem *p = problems + tl.problem;
-                const uint32_t a_mn = p->a_mn_major, b_mn = p->b_mn_major, K = p->K;
-                const int num_kb = (int)((K + kGemmBlockK - 1) / kGemmBlockK);
-                const uint32_t idesc = instr_desc(C::kTileM, BN, f16, a_mn, b_mn);
-                const bool shared_operand = PAIR && tl.tile_m == tl.tile_n && p->map_a == p->map_b && a_mn == b_mn;
-                if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
-                tc_fence_after();
-                const uint32_t d_tmem = tmem_base + acc * BN;
-                for (int kb = 0; kb < num_kb; ++kb) {
-                    if (!mbar_wait(full_bar(stage), phase, abort_flag)) { ok = false; break; }
+                const uint32_t parts = CHAINED ? tile_parts(tl) : 1u;
+                for (uint32_t part = 0; ok && part < parts; ++part) {
+                    const GemmProblem *p = problems + (CHAINED ? tile_part(tl, part).problem : tl.problem);
+                    const uint32_t a_mn = p->a_mn_major, b_mn = p->b_mn_major, K = p->K;
+                    const int num_kb = (int)((K + kGemmBlockK - 1) / kGemmBlockK);
+                    const uint32_t idesc = instr_desc(C::kTileM, BN, f16, a_mn, b_mn);
+                    const bool shared_operand = PAIR && tl.tile_m == tl.tile_n && p->map_a == p->map_b && a_mn == b_mn;
+                    if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t sa = smem_u32(stage_base + stage * C::kStageBytes);
-                    const uint32_t sb = shared_operand ? sa : sa + kABytes;
+                    const uint32_t d_tmem = tmem_base + acc * BN;
+                    for (int kb = 0; kb < num_kb; ++kb) {
+                        if (!mbar_wait(full_bar(stage), phase, abort_flag)) { ok = false; break; }
+                        tc_fence_after();
+                        const uint32_t sa = smem_u32(stage_base + stage * C::kStageBytes);
+                        const uint32_t sb = shared_operand ? sa : sa + kABytes;
 #pragma unroll
-                    for (int k = 0; k < kGemmBlockK / 16; ++k) {
-                        const uint64_t ad = a_mn ? smem_desc(sa + k * 2048, kBoxBytes, 1024)
-                                                 : smem_desc(sa + k * 32, 16, 1024);
-                        const uint64_t bd = b_mn ? smem_desc(sb + k * 2048, kBoxBytes, 1024)
-                                                 : smem_desc(sb + k * 32, 16, 1024);
-                        tc_mma<PAIR>(d_tmem, ad, bd, idesc, (uint32_t)((kb | k) != 0));
+                        for (int k = 0; k < kGemmBlockK / 16; ++k) {
+                            const uint64_t ad = a_mn ? smem_desc(sa + k * 2048, kBoxBytes, 1024)
+                                                     : smem_desc(sa + k * 32, 16, 1024);
+                            const uint64_t bd = b_mn ? smem_desc(sb + k * 2048, kBoxBytes, 1024)
+                                                     : smem_desc(sb + k * 32, 16, 1024);
+                            tc_mma<PAIR>(d_tmem, ad, bd, idesc, (uint32_t)((kb | k) != 0));
+                        }
+                        tc_commit<PAIR>(empty_bar(stage));
+                        if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
                     }
-                    tc_commit<PAIR>(empty_bar(stage));
-                    if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+                    if (!ok) break;
+                    tc_commit<PAIR>(tfull_bar(acc));
+                    acc ^= 1u;
+                    if (acc == 0) acc_phase ^= 1u;
                 }
-                if (!ok) break;
-                tc_commit<PAIR>(tfull_bar(acc));
-                acc ^= 1u;
-                if (acc == 0) acc_phase ^= 1u;
             }
         }
     } else {
@@ -592,10 +658,10 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const void *__restrict__ til
             unpublished = kNoSlot;
         };
         uint32_t seq = 0;
-        for (uint32_t t = CHAINED ? ring_get(tile_ring, 0u, abort_flag) : first_tile; t < tile_count;
+        bool alive = true;
+        for (uint32_t t = CHAINED ? ring_get(tile_ring, 0u, abort_flag) : first_tile; alive && t < tile_count;
              t = CHAINED ? ring_get(tile_ring, ++seq, abort_flag) : t + tile_stride) {
             const TileWork tl = tile_work<CHAINED>(tiles, t, epilogue_arg, scale_pow_arg);
-            const uint32_t epilogue = tl.epilogue;
             // the iteration's coefficient triple, picked without indexing the argument block by a register
             float ca = coef.v[0], cb = coef.v[1], cc = coef.v[2];
             if (CHAINED) {
@@ -603,7 +669,13 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const void *__restrict__ til
                 for (uint32_t i = 1; i < kMaxChainIterations; ++i)
                     if (tl.iter == i) { ca = coef.v[3 * i]; cb = coef.v[3 * i + 1]; cc = coef.v[3 * i + 2]; }
             }
-            const GemmProblem *p = problems + tl.problem;
+            const uint32_t parts = CHAINED ? tile_parts(tl) : 1u;
+#pragma unroll 1
+            for (uint32_t part = 0; part < parts; ++part) {
+            const uint32_t epilogue = CHAINED ? tile_part(tl, part).epilogue : tl.epilogue;
+            const GemmProblem *p = problems + (CHAINED ? tile_part(tl, part).problem : tl.problem);
+            const bool hold = CHAINED && epilogue == kEpiGramHold;    // the accumulator stays for the next part
+            const bool fused = CHAINED && epilogue == kEpiPolyFused;  // combines with the held accumulator
             const uint32_t M = p->M, N = p->N;
             uint8_t *out16 = reinterpret_cast<uint8_t *>(p->out16), *out32 = reinterpret_cast<uint8_t *>(p->out32);
             const size_t pitch16 = (size_t)p->pitch16 * 2, pitch32 = (size_t)p->pitch32 * 4;
@@ -635,7 +707,7 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const void *__restrict__ til
 
             bool ready = mbar_wait(tfull_bar(acc), acc_phase, abort_flag);
             ready = __all_sync(0xffffffffu, ready);
-            if (!ready) break;
+            if (!ready) { alive = false; break; }
             tc_fence_after();
             if (CHAINED && epilogue == kEpiPoly && !dbg_no_store && !g_fetched) {
                 // the accumulator is complete, so the producer has seen the Gram phase complete
@@ -643,10 +715,14 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const void *__restrict__ til
                 for (int j = 0; j < 8; ++j) g[j] = __ldcg(frag + (unit0 + j) * kGemmBlockM + row_in_tile);
             }
             const uint32_t taddr = tmem_base + ((uint32_t)(32 * q) << 16) + acc * BN + c0;
+            // fused: the Gram accumulator of this tile sits in the other buffer
+            const uint32_t held_taddr = tmem_base + ((uint32_t)(32 * q) << 16) + (acc ^ 1u) * BN + c0;
             const uint32_t tempty = tempty_leader0 + 8u * acc;
+            const uint32_t held_tempty = tempty_leader0 + 8u * (acc ^ 1u);
             const bool in_range = n0 + c0 < (int)N && slab_row0 < (int)M && !dbg_no_store;   // warp-uniform
             // One-pass prepare: the operand of the first iteration is the un-normalised update, and
             // s = 1 / (1.01 |u| + 1e-7) of the tile's matrix enters here: G = (s s) X X^T, X1 = s (Q X).
+            // (A fused polynomial part scales the held Gram accumulator, not its own.)
             float out_scale = 1.0f;
             if (slot_scale != nullptr && tl.scale_pow != 0u && epilogue != kEpiPoly) {
                 const float sv = __ldcg(slot_scale + tl.slot);
@@ -685,12 +761,39 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const void *__restrict__ til
             } else {
                 // 16-bit result: the chunk's 64 columns are read in two halves of 32 and packed
                 uint32_t packed[32];
+                if (fused) {
+                    // four quarters of 16 columns: this tile's accumulator and the held Gram accumulator, which
+                    // enters as the unfused form would have read it back from memory
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        uint32_t v[16], h[16];
+                        tc_ld16(taddr + 16 * k, v);
+                        tc_ld16(held_taddr + 16 * k, h);
+                        tc_ld_wait();
+                        if (k == 3) {
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) { mbar_arrive_cluster(tempty); mbar_arrive_cluster(held_tempty); }
+                        }
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int gcol = n0 + c0 + 16 * k + j;
+                            const float ident = (gcol == grow) ? ca : 0.0f;
+                            const float base = scaled ? __uint_as_float(h[j]) * out_scale : __uint_as_float(h[j]);
+                            // store/plain.rs:175-178: fma(c, acc, fma(b, base, identity))
+                            v[j] = __float_as_uint(fmaf(cc, __uint_as_float(v[j]), fmaf(cb, base, ident)));
+                        }
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            packed[8 * k + j] = pack_operands(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]), f16);
+                    }
+                } else {
 #pragma unroll
                 for (int sub = 0; sub < 2; ++sub) {
                     uint32_t v[32];
                     tc_ld32(taddr + 32 * sub, v);
                     tc_ld_wait();
-                    if (sub == 1) {
+                    if (sub == 1 && !hold) {
                         tc_fence_before();
                         __syncwarp();
                         if (lane == 0) mbar_arrive_cluster(tempty);
@@ -733,6 +836,7 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const void *__restrict__ til
                     for (int j = 0; j < 16; ++j)
                         packed[16 * sub + j] = pack_operands(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]), f16);
                 }
+                }
                 if (CHAINED && unpublished != kNoSlot) publish();
                 if (in_range) {
                     __syncwarp();   // the copy-out of the previous slab is done in every lane
@@ -763,9 +867,12 @@ k_ns_gemm(const GemmProblem *__restrict__ problems, const void *__restrict__ til
             if (CHAINED) {
                 if (unpublished != kNoSlot) publish();   // (a tile whose stores were all skipped)
                 unpublished = tl.slot;
+                // the other CTAs wait for a held Gram tile before they can go on: publish it at once
+                if (hold) publish();
             }
             acc ^= 1u;
             if (acc == 0) acc_phase ^= 1u;
+            }
         }
         if (CHAINED && unpublished != kNoSlot) publish();
     }
@@ -875,6 +982,43 @@ cudaError_t gemm_configure(int block_n, int pair) {
     if (!pair && block_n == 128) return configure_both<128, false>();
     return cudaErrorInvalidValue;
 }
+namespace {
+template <int BN, bool PAIR>
+int resident_groups(int sm_count) {
+    if (PAIR) {
+        cudaLaunchConfig_t cfg = {};
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        cfg.gridDim = dim3((unsigned)(sm_count & ~1), 1, 1);
+        cfg.blockDim = dim3((unsigned)Cfg<BN, PAIR>::kThreads, 1, 1);
+        cfg.dynamicSmemBytes = Cfg<BN, PAIR>::kSmemBytes;
+        int clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&clusters, k_ns_gemm<BN, PAIR, true>, &cfg) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return 0;
+        }
+        return clusters;
+    }
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_ns_gemm<BN, PAIR, true>, Cfg<BN, PAIR>::kThreads,
+                                                      Cfg<BN, PAIR>::kSmemBytes) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return 0;
+    }
+    return per_sm > 0 ? sm_count : 0;   // one CTA per SM is all a launch ever uses
+}
+}  // namespace
+int gemm_resident_groups(int block_n, int pair, int sm_count) {
+    if (pair && block_n == 256) return resident_groups<256, true>(sm_count);
+    if (!pair && block_n == 256) return resident_groups<256, false>(sm_count);
+    if (!pair && block_n == 128) return resident_groups<128, false>(sm_count);
+    return 0;
+}
 cudaError_t launch_ns_gemm(int block_n, int pair, const GemmProblem *problems, const GemmTile *tiles,
                            uint32_t tile_count, uint32_t epilogue, int f16, float ca, float cb,
                            float cc, const float *slot_scale, uint32_t scale_pow, uint32_t *status,
@@ -889,9 +1033,10 @@ uint32_t chain_epilogue_warps(int block_n, int pair) { return (uint32_t)(4 * (bl
 cudaError_t launch_ns_chain(int block_n, int pair, const GemmProblem *problems, const ChainTile *tiles,
                             uint32_t tile_count, int f16, const GemmCoefficients &coef, const float *slot_scale,
                             uint32_t *status, void *sync, uint32_t slot_count, uint32_t debug_flags, int grid,
-                            cudaStream_t s) {
-    return dispatch<true>(block_n, pair, problems, tiles, tile_count, 0u, f16, coef, slot_scale, 0u, status, sync,
-                          slot_count, debug_flags, grid, s);
+                            cudaStream_t s, bool fused_list) {
+    // the epilogue argument of the plain launch carries the list kind here
+    return dispatch<true>(block_n, pair, problems, tiles, tile_count, fused_list ? 1u : 0u, f16, coef, slot_scale, 0u,
+                          status, sync, slot_count, debug_flags, grid, s);
 }
 
 }  // namespace b2

@@ -16,7 +16,7 @@ import torch
 
 from . import _ffi
 from ._ffi import (AdamWSlotDescriptor, AdamWUpdateArgs as _CAdam, GradientClipArgs as _CClip, MuonOptions, MuonSlotDescriptor, MuonStepArgs, OPERAND_BF16,
-                   NORMALIZE_DEFERRED, NORMALIZE_TWO_PASS, NS_CHAINED, NS_PER_PHASE, OPERAND_F16, UPDATE_16BIT, UPDATE_F32, QUANTIZE_X, QUANTIZE_Y, SCALES_CSF, SCALES_RAW, SCALES_SM100,
+                   NORMALIZE_DEFERRED, NORMALIZE_TWO_PASS, NS_CHAINED, NS_FUSED_GRAM_POLY, NS_PER_PHASE, OPERAND_F16, UPDATE_16BIT, UPDATE_F32, QUANTIZE_X, QUANTIZE_Y, SCALES_CSF, SCALES_RAW, SCALES_SM100,
                    ScheduleFreeMaterializeArgs as _CSf, check)
 from .nvfp4 import Nvfp4QuantModule, sm100_scales_bytes, zero_scales
 
@@ -131,7 +131,8 @@ class MuonPlan:
         NORMALIZE_DEFERRED reads the gradients once and lets s enter through the first iteration (BF16
         operands only).  `ns_schedule`: NS_PER_PHASE runs three launches per iteration, NS_CHAINED the whole
         Newton-Schulz loop as one persistent grid ordered by per-matrix progress counts (steps of exactly
-        `max_iterations` iterations).  `update_input`: UPDATE_16BIT lets the last iteration store the 16-bit operand type instead of
+        `max_iterations` iterations), NS_FUSED_GRAM_POLY two launches per iteration, the Gram and polynomial tile of a
+        position computed by one CTA pair with the FP32 Gram tile kept in tensor memory.  `update_input`: UPDATE_16BIT lets the last iteration store the 16-bit operand type instead of
         FP32 and the update read that (plain finish only).  `debug_*` are read only by a library built with -DB2_MEASURE."""
         self._lib = _ffi.lib()
         self.shapes = [(int(r), int(c)) for r, c in shapes]

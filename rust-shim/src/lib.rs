@@ -45,6 +45,7 @@ pub mod ffi {
     pub const B2_NORMALIZE_DEFERRED: u32 = 1;
     pub const B2_NS_PER_PHASE: u32 = 0;
     pub const B2_NS_CHAINED: u32 = 1;
+    pub const B2_NS_FUSED_GRAM_POLY: u32 = 2;
     pub const B2_UPDATE_F32: u32 = 0;
     pub const B2_UPDATE_16BIT: u32 = 1;
     pub const B2_STATIC_MAX_ELEMENTS: u32 = 1 << 26;

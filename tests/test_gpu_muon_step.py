@@ -198,6 +198,18 @@ def test_one_gpt2_layer_chained_newton_schulz():
                 seed=11, schedule=b2.NS_CHAINED, update_input=b2.UPDATE_16BIT)
 
 
+def test_one_gpt2_layer_fused_gram_poly_newton_schulz():
+    # the whole step with the Gram and polynomial tile of a position fused on one CTA pair, against the oracle: with
+    # the one-pass prepare (the held Gram accumulator takes s^2 in the first iteration) and with the reference's
+    # F16 recipe on ragged shapes; then a GPT-2 XL layer, whose 1600-wide matrices have 28 tiles each
+    _check_step([(2304, 768), (768, 768), (3072, 768), (768, 3072), (0, 0)], b2.SCALES_CSF, b2.OPERAND_BF16,
+                o.fixed_coefficients(5), seed=12, normalize=b2.NORMALIZE_DEFERRED, schedule=b2.NS_FUSED_GRAM_POLY)
+    _check_step([(1600, 320), (48, 1600), (200, 208)], b2.SCALES_RAW, b2.OPERAND_F16, o.polar_express_coefficients(5),
+                seed=13, schedule=b2.NS_FUSED_GRAM_POLY)
+    _check_step([(4800, 1600), (1600, 1600), (6400, 1600), (1600, 6400)], b2.SCALES_RAW, b2.OPERAND_BF16,
+                o.fixed_coefficients(5), seed=14, normalize=b2.NORMALIZE_DEFERRED, schedule=b2.NS_FUSED_GRAM_POLY)
+
+
 def test_one_pass_prepare_needs_bf16_operands():
     with pytest.raises(b2.B2Error):
         b2.MuonPlan([(64, 64)], operand_format=b2.OPERAND_F16, scale_layout=b2.SCALES_RAW,

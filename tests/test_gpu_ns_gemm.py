@@ -41,7 +41,7 @@ def _run(shapes, fmt, iterations, coeffs, tile_n, xs, schedule=b2.NS_PER_PHASE):
     return plan
 
 
-@pytest.mark.parametrize("schedule", [b2.NS_CHAINED, b2.NS_PER_PHASE])
+@pytest.mark.parametrize("schedule", [b2.NS_CHAINED, b2.NS_PER_PHASE, b2.NS_FUSED_GRAM_POLY])
 @pytest.mark.parametrize("tile_n", [128, 256, 512])  # 512 = two-CTA 256 x 256 tiles
 @pytest.mark.parametrize("fmt", [b2.OPERAND_BF16, b2.OPERAND_F16])
 @pytest.mark.parametrize("rows,cols", [(64, 256), (256, 64), (128, 128), (96, 160), (160, 96), (320, 832), (832, 320)])
@@ -71,7 +71,7 @@ def test_single_iteration_intermediates(rows, cols, fmt, tile_n, schedule):
     plan.close()
 
 
-@pytest.mark.parametrize("schedule", [b2.NS_CHAINED, b2.NS_PER_PHASE])
+@pytest.mark.parametrize("schedule", [b2.NS_CHAINED, b2.NS_PER_PHASE, b2.NS_FUSED_GRAM_POLY])
 @pytest.mark.parametrize("tile_n", [0, 256])
 @pytest.mark.parametrize("shapes", [
     [(768, 768), (768, 3072), (3072, 768), (2304, 768)],
@@ -128,10 +128,14 @@ def test_chained_launch_equals_the_per_phase_launches_bit_for_bit(shapes, tile_n
         plan.close()
         return out
 
-    a, b = run(b2.NS_CHAINED), run(b2.NS_PER_PHASE)
-    for (i, _), ra, rb in zip(live, a, b):
-        for w, ta, tb in zip(("U", "Gram", "Q", "X1"), ra, rb):
-            assert np.array_equal(ta, tb), (shapes[i], w)
+    b = run(b2.NS_PER_PHASE)
+    # (the fused Gram + polynomial form draws its tiles the same way and keeps the FP32 Gram tile in tensor memory
+    # instead of reading it back: the same arithmetic again)
+    for schedule in (b2.NS_CHAINED, b2.NS_FUSED_GRAM_POLY):
+        a = run(schedule)
+        for (i, _), ra, rb in zip(live, a, b):
+            for w, ta, tb in zip(("U", "Gram", "Q", "X1"), ra, rb):
+                assert np.array_equal(ta, tb), (schedule, shapes[i], w)
 
 
 def test_steps_with_fewer_iterations_take_the_per_phase_launches():
