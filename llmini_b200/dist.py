@@ -28,10 +28,41 @@ def shard_plan(shapes: Sequence[tuple[int, int]], world: int):
     return list(owner), list(load)
 
 
+def bucket_plan(shapes: Sequence[tuple[int, int]], world: int, buckets: int):
+    """-> (bucket per slot, owner rank per slot).  The matrices, in their given order, are cut into `buckets`
+    contiguous runs of about equal Newton-Schulz FLOPs, and every run is spread over the ranks by itself
+    (shard_plan).  A rank then works through the buckets one after the other, and the all-gather of a bucket's
+    packed weights runs while the next bucket is computed: only the last bucket's gather is left uncovered."""
+    n = len(shapes)
+    buckets = max(1, min(int(buckets), max(1, sum(1 for r, c in shapes if r * c))))
+    flops = []
+    for r, c in shapes:
+        lo, hi = float(min(r, c)), float(max(r, c))
+        flops.append(4.0 * lo * lo * hi + 2.0 * lo * lo * lo)
+    total = sum(flops)
+    bucket, acc, b = [0] * n, 0.0, 0
+    for i in range(n):
+        # a matrix goes to the bucket in which its midpoint falls
+        mid = acc + 0.5 * flops[i]
+        b = max(b, min(buckets - 1, int(mid * buckets / total))) if total > 0 else 0
+        bucket[i] = b
+        acc += flops[i]
+    owner = [0] * n
+    for b in range(buckets):
+        ids = [i for i in range(n) if bucket[i] == b]
+        if not ids:
+            continue
+        own, _ = shard_plan([shapes[i] for i in ids], world)
+        for i, r in zip(ids, own):
+            owner[i] = r
+    return bucket, owner
+
+
 @dataclass
 class ArenaEntry:
     slot: int
     rank: int
+    bucket: int
     codes_off: int      # byte offsets inside the owner's arena slice
     scales_off: int
     gscale_off: int
@@ -40,68 +71,95 @@ class ArenaEntry:
 
 
 class Nvfp4Arena:
-    """Layout of the all-gather buffer: `world` equal slices; rank r's matrices packed back to
-    back (codes, scales, 4-byte tensor scale; 16-byte aligned) inside slice r."""
+    """Layout of the all-gather buffer.  One region per bucket (one bucket unless `bucket` is given); a region is
+    `world` equal slices, rank r's matrices of that bucket packed back to back (codes, scales, 4-byte tensor
+    scale; 16-byte aligned) inside slice r.  Every region is gathered by one all-gather."""
 
-    def __init__(self, shapes: Sequence[tuple[int, int]], owner: Sequence[int], world: int, scales_bytes_fn):
+    def __init__(self, shapes: Sequence[tuple[int, int]], owner: Sequence[int], world: int, scales_bytes_fn,
+                 bucket: Sequence[int] | None = None):
         self.world = world
+        bucket = list(bucket) if bucket is not None else [0] * len(shapes)
+        self.buckets = (max(bucket) + 1) if bucket else 1
         self.entries: list[ArenaEntry] = []
-        used = [0] * world
-        for s, ((rows, cols), r) in enumerate(zip(shapes, owner)):
+        used = [[0] * world for _ in range(self.buckets)]
+        for s, ((rows, cols), r, b) in enumerate(zip(shapes, owner, bucket)):
             n = rows * cols
             cb, sb = n // 2, int(scales_bytes_fn(rows, cols))
-            off = used[r]
+            off = used[b][r]
             co = off
             so = _align(co + cb, 16)
             go = _align(so + sb, 16)
-            used[r] = _align(go + 4, 16)
-            self.entries.append(ArenaEntry(s, r, co, so, go, cb, sb))
-        self.bytes_per_rank = _align(max(used) if used else 0, 256)
+            used[b][r] = _align(go + 4, 16)
+            self.entries.append(ArenaEntry(s, r, b, co, so, go, cb, sb))
+        self.bucket_bytes_per_rank = [_align(max(u) if u else 0, 256) for u in used]
+        self.bucket_base = [0] * self.buckets
+        for b in range(1, self.buckets):
+            self.bucket_base[b] = self.bucket_base[b - 1] + self.bucket_bytes_per_rank[b - 1] * world
+        self.bytes_per_rank = sum(self.bucket_bytes_per_rank)   # (one slice per bucket: see rank_slices)
         self.total_bytes = self.bytes_per_rank * world
         self.payload_bytes = sum(e.codes_bytes + e.scales_bytes + 4 for e in self.entries)
 
     def offsets(self, slot: int):
         e = self.entries[slot]
-        base = e.rank * self.bytes_per_rank
+        base = self.bucket_base[e.bucket] + e.rank * self.bucket_bytes_per_rank[e.bucket]
         return base + e.codes_off, base + e.scales_off, base + e.gscale_off
+
+    def region(self, bucket: int):
+        """(byte offset, bytes) of a bucket's region = `world` slices of bucket_bytes_per_rank[bucket]."""
+        return self.bucket_base[bucket], self.bucket_bytes_per_rank[bucket] * self.world
+
+    def rank_slices(self, rank: int):
+        """[(byte offset, bytes)] of the slices rank `rank` fills, one per bucket."""
+        return [(self.bucket_base[b] + rank * n, n) for b, n in enumerate(self.bucket_bytes_per_rank)]
 
 
 def _align(v: int, a: int) -> int:
     return (v + a - 1) // a * a
 
 
-def all_gather_arena(arena_tensor, arena: Nvfp4Arena, group=None):
-    """In-place all-gather of the per-rank slices with torch.distributed (NCCL on GPUs, gloo on
-    CPU ranks).  `arena_tensor` is a uint8 tensor of arena.total_bytes."""
+def all_gather_bucket(arena_tensor, arena: Nvfp4Arena, bucket: int, group=None):
+    """In-place all-gather of one bucket's region (NCCL on GPUs, gloo on CPU ranks)."""
     import torch.distributed as dist
 
     rank = dist.get_rank(group)
-    n = arena.bytes_per_rank
-    mine = arena_tensor[rank * n:(rank + 1) * n]
+    base, size = arena.region(bucket)
+    n = arena.bucket_bytes_per_rank[bucket]
+    if n == 0:
+        return
+    region = arena_tensor[base:base + size]
+    mine = region[rank * n:(rank + 1) * n]
     if arena_tensor.is_cuda:
-        dist.all_gather_into_tensor(arena_tensor, mine, group=group)
+        dist.all_gather_into_tensor(region, mine, group=group)
     else:
-        parts = [arena_tensor[r * n:(r + 1) * n] for r in range(arena.world)]
+        parts = [region[r * n:(r + 1) * n] for r in range(arena.world)]
         gathered = [p.clone() for p in parts]
         dist.all_gather(gathered, mine.clone(), group=group)
         for p, g in zip(parts, gathered):
             p.copy_(g)
 
 
+def all_gather_arena(arena_tensor, arena: Nvfp4Arena, group=None):
+    """In-place all-gather of every bucket's region.  `arena_tensor` is a uint8 tensor of arena.total_bytes."""
+    for b in range(arena.buckets):
+        all_gather_bucket(arena_tensor, arena, b, group)
+
+
 def arena_slice_checksums(arena_tensor, arena: Nvfp4Arena, piece: int = 32 << 20):
-    """Two checksums per rank slice of a gathered arena (a plain byte sum and a position-weighted one), as an
-    int64 tensor [2, world] on the arena's device.  Ranks that hold the same arena get the same numbers."""
+    """Two checksums per rank (a plain byte sum and a position-weighted one over the rank's slices of all
+    buckets), as an int64 tensor [2, world] on the arena's device.  Ranks that hold the same arena get the same
+    numbers."""
     import torch
 
-    n, w = arena.bytes_per_rank, arena.world
+    w = arena.world
     dev = arena_tensor.device
     sums = torch.zeros(2, w, dtype=torch.int64, device=dev)
     for r in range(w):
-        for a in range(0, n, piece):
-            v = arena_tensor[r * n + a:r * n + min(a + piece, n)].to(torch.int64)
-            weight = ((torch.arange(v.numel(), device=dev, dtype=torch.int64) + a) % 251) + 1
-            sums[0, r] += v.sum()
-            sums[1, r] += (v * weight).sum()
+        for start, n in arena.rank_slices(r):
+            for a in range(0, n, piece):
+                v = arena_tensor[start + a:start + min(a + piece, n)].to(torch.int64)
+                weight = ((torch.arange(v.numel(), device=dev, dtype=torch.int64) + start + a) % 251) + 1
+                sums[0, r] += v.sum()
+                sums[1, r] += (v * weight).sum()
     return sums
 
 
