@@ -267,7 +267,7 @@ class GpuJob:
         import torch
 
         import llmini_b200 as b2
-        from llmini_b200.dist import Nvfp4Arena, shard_plan
+        from llmini_b200.dist import Nvfp4Arena, bucket_plan, shard_plan
 
         self.torch, self.b2 = torch, b2
         self.name, self.world, self.rank, self.dev = name, world, rank, dev
@@ -280,14 +280,29 @@ class GpuJob:
             emb = [((rows + args.shard_of - 1) // args.shard_of // 128 * 128, cols) for rows, cols in emb]
         d_model = MODELS[name][1]
         layout = self.layout = b2.SCALES_CSF if d_model % 128 == 0 else b2.SCALES_RAW
-        self.owner, _ = shard_plan(self.mats, world)
-        self.mine = [i for i, r in enumerate(self.owner) if r == rank]
+        # Buckets: contiguous runs of matrices, each spread over all ranks.  Stages M, N and P run over all of the
+        # rank's matrices at once; stage U + Q runs bucket by bucket, and the all-gather of one bucket's packed
+        # weights runs while the next bucket is updated; the last bucket's gather runs beside AdamW.  So: as many
+        # buckets as it takes for the last gather to fit behind AdamW (estimated from the bytes either moves: 600 GB/s
+        # into a rank, AdamW at 5 TB/s), at most four, none smaller than 10 M elements per rank.
+        self.n_buckets = 1
+        if world > 1:
+            elems = sum(r * c for r, c in self.mats)
+            gather_ms = elems * 0.5625 * (world - 1) / world / 600e9 * 1e3 + 0.02
+            adam_ms = (sum(r * c for r, c in emb) + vec) / world * 36.0 / 5e12 * 1e3
+            auto = int(np.ceil(gather_ms / max(adam_ms, 1e-3)))
+            auto = max(1, min(4, auto, int(elems / world / 10e6)))
+            self.n_buckets = args.gather_buckets if args.gather_buckets > 0 else auto
+        self.bucket, self.owner = bucket_plan(self.mats, world, self.n_buckets)
+        self.n_buckets = max(self.bucket) + 1 if self.bucket else 1
+        self.mine = [i for b in range(self.n_buckets) for i, r in enumerate(self.owner)
+                     if r == rank and self.bucket[i] == b]   # bucket by bucket
         self.my_shapes = [self.mats[i] for i in self.mine]
 
         def scales_bytes(rows, cols):
             return b2.csf_encoded_len(rows, cols) if layout == b2.SCALES_CSF else rows * cols // 16
 
-        self.arena = Nvfp4Arena(self.mats, self.owner, world, scales_bytes)
+        self.arena = Nvfp4Arena(self.mats, self.owner, world, scales_bytes, self.bucket)
         self.arena_t = torch.zeros(self.arena.total_bytes + 1024, dtype=torch.uint8, device=dev)
         abase = (-self.arena_t.data_ptr()) % 256
         self.arena_v = self.arena_t[abase:abase + self.arena.total_bytes]
@@ -315,10 +330,14 @@ class GpuJob:
         self.schedule = {"per-phase": b2.NS_PER_PHASE, "chained": b2.NS_CHAINED,
                          "fused": b2.NS_FUSED_GRAM_POLY}[args.ns_schedule]
         self.update_input = b2.UPDATE_16BIT if args.update_16bit else b2.UPDATE_F32
+        # one plan for all of this rank's matrices; its finish groups are the buckets (a rank may own nothing of one)
         self.plan = b2.MuonPlan(self.my_shapes, scale_layout=layout, device=dev, debug_flags=args.plan_flags,
                                 normalize_mode=self.normalize, ns_schedule=self.schedule,
                                 update_input=self.update_input) if self.my_shapes else None
         self.table = b2.slot_table(self.slots, dev) if self.slots else None
+        if self.plan is not None and self.n_buckets > 1:
+            first = [sum(1 for i in self.mine if self.bucket[i] < b) for b in range(self.n_buckets)]
+            self.plan.set_finish_groups(first)
         self.opt = b2.OptimizerModule()
         self.margs = b2.MuonMegaUpdateArgs(coefficients=np.tile(np.asarray(FIXED_TRIPLE, np.float32), (5, 1)), **HP)
 
@@ -352,49 +371,87 @@ class GpuJob:
         if self.plan is not None:
             prepare = 3 if self.normalize == b2.NORMALIZE_TWO_PASS else 2
             gemms = {b2.NS_CHAINED: 1, b2.NS_FUSED_GRAM_POLY: 2 * HP["iterations"]}.get(self.schedule, 3 * HP["iterations"])
-            self.launches_per_step += prepare + gemms + (2 if args.plan_flags & 16 else 1)
+            finish = 2 if args.plan_flags & 16 else sum(1 for b in range(self.n_buckets)
+                                                       if any(self.bucket[i] == b for i in self.mine))
+            self.launches_per_step += prepare + gemms + finish
         self.launches_per_step += 3 if self.adam_sets else 0
         self.gather_stream = torch.cuda.Stream(device=dev) if world > 1 else None
         self.stage_events = []
 
     # -- the step ---------------------------------------------------------------------------
-    def step_muon(self, marks=None):
-        stream = self.torch.cuda.current_stream()
-        if marks: marks[0].record(stream)
-        if self.plan is not None:
-            self.opt.muon_tma_prepare_polar(self.plan, self.table, self.margs)
-        if marks: marks[1].record(stream)
-        if self.plan is not None:
-            self.opt.muon_polar(self.plan, self.margs)
-        if marks: marks[2].record(stream)
-        if self.plan is not None:
-            self.opt.muon_tma_finish_update(self.plan, self.table, self.margs)
-        if marks: marks[3].record(stream)
+    def gather_bucket(self, b):
+        """All-gather of bucket b's region on the side stream, ordered after what the current stream has done so
+        far.  Returns nothing; `join_gathers` makes the current stream wait for all of them."""
+        import torch.distributed as dist
 
-    def step_adam(self, marks=None):
-        """AdamW on this rank's tensors; for N > 1 the all-gather of the packed matrices runs beside it on a
-        second stream (forked after the Muon stages, joined before the step ends)."""
+        torch = self.torch
+        fork = torch.cuda.Event()
+        fork.record(torch.cuda.current_stream())
+        self.gather_stream.wait_event(fork)
+        base, size = self.arena.region(b)
+        n = self.arena.bucket_bytes_per_rank[b]
+        if n == 0:
+            return
+        with torch.cuda.stream(self.gather_stream):
+            region = self.arena_v[base:base + size]
+            dist.all_gather_into_tensor(region, region[self.rank * n:(self.rank + 1) * n])
+
+    def join_gathers(self):
+        torch = self.torch
+        join = torch.cuda.Event()
+        join.record(self.gather_stream)
+        torch.cuda.current_stream().wait_event(join)
+
+    def step_muon(self, marks=None, standalone=False):
+        """The Muon stages.  With more than one bucket, stage U + Q runs bucket by bucket and the all-gather of a
+        finished bucket runs on the side stream while the next bucket is updated; the last bucket's gather is left
+        to step_adam.  `marks`, when given, receives the four events around the three stages.  `standalone`: the
+        gathers started here are also waited for here (a capture of this half alone must not end with work pending
+        on the side stream)."""
         torch = self.torch
         stream = torch.cuda.current_stream()
-        if self.world > 1:
-            import torch.distributed as dist
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(4)] if marks is not None else None
+        if e: e[0].record(stream)
+        if self.plan is not None:
+            self.opt.muon_tma_prepare_polar(self.plan, self.table, self.margs)
+        if e: e[1].record(stream)
+        if self.plan is not None:
+            self.opt.muon_polar(self.plan, self.margs)
+        if e: e[2].record(stream)
+        if self.n_buckets == 1:
+            if self.plan is not None:
+                self.opt.muon_tma_finish_update(self.plan, self.table, self.margs)
+        else:
+            for b in range(self.n_buckets):
+                if self.plan is not None:
+                    self.opt.muon_tma_finish_update_group(self.plan, self.table, self.margs, b)
+                if self.world > 1 and b + 1 < self.n_buckets:
+                    self.gather_bucket(b)
+        if e: e[3].record(stream)
+        if e: marks.append(e)
+        if standalone and self.world > 1 and self.n_buckets > 1:
+            self.join_gathers()
 
-            fork = torch.cuda.Event()
-            fork.record(stream)
-            self.gather_stream.wait_event(fork)
-            with torch.cuda.stream(self.gather_stream):
-                n = self.arena.bytes_per_rank
-                dist.all_gather_into_tensor(self.arena_v, self.arena_v[self.rank * n:(self.rank + 1) * n])
-                join = torch.cuda.Event()
-                join.record(self.gather_stream)
+    def step_adam(self, marks=None):
+        """AdamW on this rank's tensors; for N > 1 the all-gather of the (last) bucket of packed matrices runs
+        beside it on a second stream (forked after the Muon stages, joined before the step ends)."""
+        torch = self.torch
+        stream = torch.cuda.current_stream()
+        e0 = torch.cuda.Event(enable_timing=True) if marks is not None else None
+        if e0: e0.record(stream)
+        if self.world > 1:
+            self.gather_bucket(self.n_buckets - 1)   # (every rank gathers every bucket, also one it owns nothing of)
         if self.adam_sets:
             self.opt.apply_adamw_update_multi(self.adam_table, self.adam_count, self.adam_chunks, **ADAM)
-        if marks: marks[4].record(stream)
+        if marks is not None:
+            e1 = torch.cuda.Event(enable_timing=True)
+            e1.record(stream)
+            marks.append([e0, e1])
         if self.world > 1:
-            stream.wait_event(join)
+            self.join_gathers()
 
     def step(self, record=False):
-        marks = [self.torch.cuda.Event(enable_timing=True) for _ in range(5)] if record else None
+        marks = [] if record else None
         self.step_muon(marks)
         self.step_adam(marks)
         if record:
@@ -434,8 +491,15 @@ class GpuJob:
     def stage_summary(self, peaks):
         """Mean device time of the four stages over the eager timed pass (this rank), and the rates."""
         self.torch.cuda.synchronize()
-        ev = self.stage_events
-        st = np.array([[m[i].elapsed_time(m[i + 1]) for i in range(4)] for m in ev]) if ev else np.zeros((1, 4))
+        # per recorded step: the four events around prepare, Newton-Schulz and finish, then the two around AdamW
+        rows = []
+        for m in self.stage_events:
+            parts = np.zeros(4)
+            for e in m[:-1]:
+                parts[:3] += [e[i].elapsed_time(e[i + 1]) for i in range(3)]
+            parts[3] = m[-1][0].elapsed_time(m[-1][1])
+            rows.append(parts)
+        st = np.array(rows) if rows else np.zeros((1, 4))
         prep_ms, ns_ms, fin_ms, adam_ms = (float(v) for v in st.mean(axis=0))
         elems = sum(r * c for r, c in self.my_shapes)
         flops = ns_flops(self.my_shapes, HP["iterations"])
@@ -455,7 +519,10 @@ class GpuJob:
             "update_quantise_gbs": fin_gbs, "update_quantise_frac_of_hbm": fin_gbs / peaks["hbm"],
             "adamw_gbs": adam_gbs, "hbm_peak_gbs": peaks["hbm"], "update_quantise_frac_of_nominal_8000": fin_gbs / 8000.0,
             "prepare": "one pass (scale folded into the first iteration)" if self.normalize else "two passes (reference rounding point)",
-            "newton_schulz": "one chained launch for the whole loop" if self.schedule else "three launches per iteration",
+            "newton_schulz": {self.b2.NS_CHAINED: "one chained launch for the whole loop",
+                              self.b2.NS_FUSED_GRAM_POLY: "two launches per iteration (fused Gram + polynomial tiles, apply)"
+                              }.get(self.schedule, "three launches per iteration"),
+            "gather_buckets": self.n_buckets,
             "update_quantise_bytes_per_element": fin_bytes,
         }
 
@@ -649,7 +716,7 @@ def run_gpu(args):
             # the two halves on their own, for the pipelined end-to-end step below
             graph_muon, graph_adam = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph_muon):
-                step_muon()
+                step_muon(None, True)
             with torch.cuda.graph(graph_adam):
                 step_adam()
         except SystemExit:
@@ -667,8 +734,9 @@ def run_gpu(args):
     n_slots = len(slots)
     grad_dev = [s.grad for s in slots] + [t["grad"] for _, t in adam_sets]
     grad_host = [torch.empty(g.shape, dtype=g.dtype, pin_memory=True).copy_(g) for g in grad_dev]
-    n_mine = arena.bytes_per_rank
-    out_dev = [arena_v[rank * n_mine:(rank + 1) * n_mine]] + \
+    packed_dev = [arena_v[o_:o_ + n_] for o_, n_ in arena.rank_slices(rank) if n_]   # this rank's slice of every bucket
+    n_packed = len(packed_dev)
+    out_dev = packed_dev + \
               [t[k] for kind, t in adam_sets if kind == "quant" for k in ("bytes", "scales", "global_scale")]
     out_host = [torch.empty(o_.shape, dtype=o_.dtype, pin_memory=True) for o_ in out_dev]
     h2d = sum(g.numel() * g.element_size() for g in grad_dev)
@@ -699,7 +767,8 @@ def run_gpu(args):
         muon_done.record(stream)
         down_stream.wait_event(muon_done)
         with torch.cuda.stream(down_stream):
-            out_host[0].copy_(out_dev[0], non_blocking=True)
+            for od, oh in zip(out_dev[:n_packed], out_host[:n_packed]):
+                oh.copy_(od, non_blocking=True)
             down_done = torch.cuda.Event()
             down_done.record(down_stream)
         stream.wait_event(adam_up)
@@ -708,7 +777,7 @@ def run_gpu(args):
         else:
             step_adam()
         adam_done.record(stream)
-        for od, oh in zip(out_dev[1:], out_host[1:]):
+        for od, oh in zip(out_dev[n_packed:], out_host[n_packed:]):
             oh.copy_(od, non_blocking=True)
         stream.wait_event(down_done)
 
@@ -1001,6 +1070,10 @@ def main():
     ap.add_argument("--update-16bit", action="store_true",
                     help="the last Newton-Schulz iteration stores BF16 and the update reads it (default: FP32, as the "
                          "reference's update input)")
+    ap.add_argument("--gather-buckets", type=int, default=0,
+                    help="N > 1: cut the matrices into this many buckets; the all-gather of a bucket overlaps the next "
+                         "bucket's update + quantise launch (0: as many as it takes for the last gather to fit behind AdamW, "
+                         "at most four)")
     ap.add_argument("--shard-of", type=int, default=1,
                     help="with one GPU: run rank 0's share of an N-way sharded step (no collective), to time the "
                          "per-rank kernels of a multi-GPU run")

@@ -217,6 +217,19 @@ int b2_muon_finish_update(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_s
 int b2_muon_finish_update_deferred_quantization(b2_muon_plan *plan,
                                                 const b2_muon_slot_descriptor *d_slots,
                                                 const b2_muon_step_args *args, void *stream);
+/* Finish groups: the plan's slots cut into `group_count` contiguous runs, run g starting at slot first_slot[g]
+ * (first_slot[0] = 0, ascending; a run may be empty), so that stage U + Q can be launched run by run and whatever
+ * consumes a run's packed weights (the all-gather of a multi-GPU step) can start while the next run is updated.
+ * `b2_muon_plan_set_finish_groups` rebuilds the work list of the fused update + encode launch accordingly and
+ * uploads it on `stream` (call it once after plan creation, with no finish launch of the plan in flight; a new
+ * plan has one group).  `b2_muon_finish_update_group` is `b2_muon_finish_update` for the slots of one group:
+ * plain steps only (no NorMuon / qk-clip / SymExpLin; B2_ERROR_NOT_SUPPORTED otherwise), an empty group is a
+ * no-op.  `b2_muon_finish_update` still runs all groups in one launch.  No counterpart in the reference, whose
+ * finish works per slot (.../launcher/muon_mega.rs:139-165). */
+int b2_muon_plan_set_finish_groups(b2_muon_plan *plan, const uint32_t *first_slot, uint32_t group_count,
+                                   void *stream);
+int b2_muon_finish_update_group(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_slots,
+                                const b2_muon_step_args *args, uint32_t group, void *stream);
 /* `OptimizerModule::muon_tma_finish_hyperball_update_deferred_quantization`
  * (.../launcher/muon_mega.rs:166-228): NorMuon factors, then a step of relative size
  * learning_rate along the update followed by projection back onto the sphere of the matrix's

@@ -119,6 +119,8 @@ def _declare(L: C.CDLL) -> None:
         "b2_muon_polar": (i, [vp, C.POINTER(MuonStepArgs), vp]),
         "b2_muon_finish_update": (i, [vp, vp, C.POINTER(MuonStepArgs), vp]),
         "b2_muon_finish_update_deferred_quantization": (i, [vp, vp, C.POINTER(MuonStepArgs), vp]),
+        "b2_muon_plan_set_finish_groups": (i, [vp, C.POINTER(C.c_uint32), C.c_uint32, vp]),
+        "b2_muon_finish_update_group": (i, [vp, vp, C.POINTER(MuonStepArgs), C.c_uint32, vp]),
         "b2_muon_finish_hyperball_update_deferred_quantization": (i, [vp, vp, C.POINTER(MuonStepArgs), C.c_uint32, vp]),
         "b2_muon_sign_update_deferred_quantization": (i, [vp, vp, C.POINTER(MuonStepArgs), vp]),
         "b2_nvfp4_sm100_scales_bytes": (C.c_size_t, [C.c_uint32, C.c_uint32]),

@@ -117,6 +117,7 @@ struct Layout {
     std::vector<uint32_t> chunk_prefix;  // slot_count + 1
     std::vector<uint32_t> unit_prefix;   // slot_count + 1: NorMuon work units (32 rows or 128 columns)
     std::vector<uint32_t> items;         // work list of the fused update + encode launch
+    std::vector<uint32_t> group_item_begin;   // groups + 1 entries: where each finish group's part of `items` begins
     uint32_t chain_tiles = 0;            // entries of the chained Newton-Schulz work list (0: not built)
     uint32_t chain_iterations = 0;
     uint32_t gp_tiles = 0;               // entries of ONE fused Gram + polynomial work list (0: not built); three lists
@@ -171,6 +172,39 @@ void pick_tiles(const uint32_t *rows, const uint32_t *cols, uint32_t count, cons
     pair = best == 2;
 }
 
+// Work list of the fused update + encode launch, for the slot groups [first[g], first[g + 1]): the lists of the
+// groups follow one another in L.items, group g's being items[group_item_begin[g] .. group_item_begin[g + 1]).
+// Within a group: update chunks in slot order; the encode spans (B2_FUSED_ENCODE_SPAN chunks each) of a matrix
+// become eligible kLag update chunks after its last one -- late enough that they never wait in practice, early
+// enough that the updated weights are still in L2 -- and are then fed in one per kEvery update chunks (they
+// arrive at one per B2_FUSED_ENCODE_SPAN), so that the issue-bound encode work is spread over the memory-bound
+// update work instead of arriving as a block (measured 390 us against 405 us; with kLag 4000, or a feed slower
+// than the arrival, the weights have left L2 and it is 420 us).  A group's list ends with the encode spans still
+// pending, so every group is complete in itself and the total length does not depend on the grouping.
+void build_items(Layout &L, const std::vector<uint32_t> &first) {
+    const uint32_t kLag = 1200, kEvery = 3, kEncodeFlag = 0x80000000u;
+    L.items.clear();
+    L.group_item_begin.assign(1, 0u);
+    for (size_t g = 0; g + 1 < first.size(); ++g) {
+        std::vector<std::pair<uint32_t, uint32_t>> pending;   // (eligible at update position, encode item)
+        size_t head = 0;
+        uint32_t since = 0;
+        for (uint32_t s = first[g]; s < first[g + 1]; ++s) {
+            const uint32_t lo = L.chunk_prefix[s], hi = L.chunk_prefix[s + 1];
+            for (uint32_t c = lo; c < hi; ++c) {
+                L.items.push_back(c);
+                if (++since >= kEvery && head < pending.size() && pending[head].first <= c) {
+                    L.items.push_back(pending[head++].second);
+                    since = 0;
+                }
+            }
+            for (uint32_t c = lo; c < hi; c += B2_FUSED_ENCODE_SPAN) pending.emplace_back(hi - 1 + kLag, kEncodeFlag | c);
+        }
+        while (head < pending.size()) L.items.push_back(pending[head++].second);
+        L.group_item_begin.push_back((uint32_t)L.items.size());
+    }
+}
+
 bool build_layout(const uint32_t *rows, const uint32_t *cols, uint32_t count, const b2_muon_options &o, Layout &L) {
     pick_tiles(rows, cols, count, o, L.bn, L.pair);
     L.tile_m = L.pair ? 256 : 128;
@@ -205,32 +239,7 @@ bool build_layout(const uint32_t *rows, const uint32_t *cols, uint32_t count, co
     L.off_x0_ptrs = take(count * sizeof(uint64_t));
     L.off_u_ptrs = take(count * sizeof(uint64_t));
     L.off_x1_ptrs = take(count * sizeof(uint64_t));
-    // Fused update + encode: update chunks in slot order; the encode spans (B2_FUSED_ENCODE_SPAN
-    // chunks each) of a matrix become eligible kLag update chunks after its last one -- late enough
-    // that they never wait in practice, early enough that the updated weights are still in L2 -- and
-    // are then fed in one per kEvery update chunks (they arrive at one per B2_FUSED_ENCODE_SPAN), so
-    // that the issue-bound encode work is spread over the memory-bound update work instead of
-    // arriving as a block (measured 390 us against 405 us; with kLag 4000, or a feed slower than the
-    // arrival, the weights have left L2 and it is 420 us).
-    {
-        const uint32_t kLag = 1200, kEvery = 3, kEncodeFlag = 0x80000000u;
-        L.items.clear();
-        std::vector<std::pair<uint32_t, uint32_t>> pending;   // (eligible at update position, encode item)
-        size_t head = 0;
-        uint32_t since = 0;
-        for (uint32_t s = 0; s < count; ++s) {
-            const uint32_t lo = L.chunk_prefix[s], hi = L.chunk_prefix[s + 1];
-            for (uint32_t c = lo; c < hi; ++c) {
-                L.items.push_back(c);
-                if (++since >= kEvery && head < pending.size() && pending[head].first <= c) {
-                    L.items.push_back(pending[head++].second);
-                    since = 0;
-                }
-            }
-            for (uint32_t c = lo; c < hi; c += B2_FUSED_ENCODE_SPAN) pending.emplace_back(hi - 1 + kLag, kEncodeFlag | c);
-        }
-        while (head < pending.size()) L.items.push_back(pending[head++].second);
-    }
+    build_items(L, std::vector<uint32_t>{0u, count});
     L.off_items = take(std::max<size_t>(L.items.size(), 1) * sizeof(uint32_t));
     L.off_unit_prefix = take((count + 1) * sizeof(uint32_t));
     L.off_factor_ptrs = take(count * sizeof(uint64_t));
@@ -701,10 +710,12 @@ int b2_muon_polar(b2_muon_plan *plan, const b2_muon_step_args *a, void *stream) 
     return (int)e;
 }
 
+// group < 0: every slot of the plan; otherwise the slots of that finish group (fused update + encode launch only)
 static int finish_impl(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_slots, const b2_muon_step_args *a,
-                       bool quantize, void *stream) {
+                       bool quantize, void *stream, int group = -1) {
     if (!plan || !a || !d_slots) return B2_ERROR_INVALID_VALUE;
     const Layout &L = plan->layout;
+    if (group >= 0 && (size_t)group + 1 >= L.group_item_begin.size()) return B2_ERROR_INVALID_VALUE;
     cudaStream_t s = as_stream(stream);
     SlotView v = plan->view(d_slots);
     float *amax_x = plan->at<float>(L.off_amax_x);
@@ -729,13 +740,16 @@ static int finish_impl(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_slot
     // one launch for the plain update; NorMuon / qk-clip steps (and measurement flag 16) take two
     if (quantize && !(plan->options.measure_flags & 16u) && !up.normuon && !up.d_qk_clip_factors &&
         up.symexp_beta == 0.0f) {
-        if (e == cudaSuccess)
-            e = launch_muon_update_encode(v, plan->at<uint32_t>(L.off_items), (uint32_t)L.items.size(),
+        const uint32_t begin = group < 0 ? 0u : L.group_item_begin[group];
+        const uint32_t end = group < 0 ? (uint32_t)L.items.size() : L.group_item_begin[group + 1];
+        if (e == cudaSuccess && end > begin)
+            e = launch_muon_update_encode(v, plan->at<uint32_t>(L.off_items) + begin, end - begin,
                                           u_ptrs, amax_x, up, quantize_y,
                                           (int)plan->options.scale_layout, plan->ws + L.off_fused_sync,
                                           plan->at<uint32_t>(L.off_status), plan->fused_wait_ns, s);
         return (int)e;
     }
+    if (group >= 0) return B2_ERROR_NOT_SUPPORTED;   // the two-launch forms work on the whole plan
     if (e == cudaSuccess) e = launch_muon_update(v, u_ptrs, amax_x, up, s);
     if (e == cudaSuccess && quantize)
         e = launch_muon_encode(v, amax_x, quantize_y, (int)plan->options.scale_layout, s);
@@ -748,6 +762,27 @@ int b2_muon_finish_update(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_s
 int b2_muon_finish_update_deferred_quantization(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_slots,
                                                 const b2_muon_step_args *a, void *stream) {
     return finish_impl(plan, d_slots, a, false, stream);
+}
+int b2_muon_plan_set_finish_groups(b2_muon_plan *plan, const uint32_t *first_slot, uint32_t group_count, void *stream) {
+    if (!plan || !first_slot || group_count == 0) return B2_ERROR_INVALID_VALUE;
+    Layout &L = plan->layout;
+    const uint32_t count = (uint32_t)L.slots.size();
+    std::vector<uint32_t> first(first_slot, first_slot + group_count);
+    if (first[0] != 0) return B2_ERROR_INVALID_VALUE;
+    for (uint32_t g = 1; g < group_count; ++g)
+        if (first[g] < first[g - 1] || first[g] > count) return B2_ERROR_INVALID_VALUE;
+    first.push_back(count);
+    const size_t before = L.items.size();
+    build_items(L, first);
+    if (L.items.size() != before) return B2_ERROR_INVALID_VALUE;   // (cannot happen: the grouping only reorders)
+    if (L.items.empty()) return B2_SUCCESS;
+    return (int)cudaMemcpyAsync(plan->ws + L.off_items, L.items.data(), L.items.size() * sizeof(uint32_t),
+                                cudaMemcpyHostToDevice, as_stream(stream));
+}
+int b2_muon_finish_update_group(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_slots, const b2_muon_step_args *a,
+                                uint32_t group, void *stream) {
+    if (group > 0x7fffffffu) return B2_ERROR_INVALID_VALUE;
+    return finish_impl(plan, d_slots, a, true, stream, (int)group);
 }
 
 int b2_muon_materialize_master_weights(b2_muon_plan *plan, const b2_muon_slot_descriptor *d_slots, void *stream) {

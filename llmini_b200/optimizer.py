@@ -174,6 +174,13 @@ class MuonPlan:
     def status(self) -> int:
         return int(self._lib.b2_muon_plan_status(self._handle, _stream()))
 
+    def set_finish_groups(self, first_slots: Sequence[int]) -> None:
+        """Cuts the plan's slots into contiguous runs starting at `first_slots` (first entry 0, ascending; a run
+        may be empty) for OptimizerModule.muon_tma_finish_update_group (b2_muon_plan_set_finish_groups)."""
+        arr = (C.c_uint32 * len(first_slots))(*[int(v) for v in first_slots])
+        check(self._lib.b2_muon_plan_set_finish_groups(self._handle, arr, len(first_slots), _stream()),
+              "muon_plan_set_finish_groups")
+
     def debug_fused_wait_expiry(self, slots: torch.Tensor, slot: int, wait_ns: int) -> None:
         """Test hook: one CTA of the update + encode launch waits `wait_ns` for a completion count that cannot
         arrive, gives up and reports through the status word (b2_debug_muon_fused_wait_expiry)."""
@@ -233,6 +240,14 @@ class OptimizerModule:
     def muon_tma_finish_update(self, plan: MuonPlan, slots: torch.Tensor, args: MuonMegaUpdateArgs) -> None:
         a, keep = args.c_args()
         check(self._lib.b2_muon_finish_update(plan.handle, _ptr(slots), C.byref(a), _stream()), "muon_finish_update")
+        del keep
+
+    def muon_tma_finish_update_group(self, plan: MuonPlan, slots: torch.Tensor, args: MuonMegaUpdateArgs,
+                                     group: int) -> None:
+        """muon_tma_finish_update for the slots of one finish group of the plan (MuonPlan.set_finish_groups)."""
+        a, keep = args.c_args()
+        check(self._lib.b2_muon_finish_update_group(plan.handle, _ptr(slots), C.byref(a), int(group), _stream()),
+              "muon_finish_update_group")
         del keep
 
     # launcher/muon_mega.rs:159-165

@@ -257,6 +257,10 @@ pub mod ffi {
                                      stream: CUstream) -> i32;
         pub fn b2_muon_finish_update_deferred_quantization(plan: *mut b2_muon_plan, d_slots: CUdeviceptr,
                                                            args: *const b2_muon_step_args, stream: CUstream) -> i32;
+        pub fn b2_muon_plan_set_finish_groups(plan: *mut b2_muon_plan, first_slot: *const u32, group_count: u32,
+                                              stream: CUstream) -> i32;
+        pub fn b2_muon_finish_update_group(plan: *mut b2_muon_plan, d_slots: CUdeviceptr, args: *const b2_muon_step_args,
+                                           group: u32, stream: CUstream) -> i32;
         pub fn b2_muon_finish_hyperball_update_deferred_quantization(plan: *mut b2_muon_plan, d_slots: CUdeviceptr,
                                                                      args: *const b2_muon_step_args,
                                                                      use_schedule_free: u32, stream: CUstream) -> i32;
@@ -613,6 +617,12 @@ impl MuonPlan {
         let first_slot = rows.iter().zip(cols).position(|(r, c)| (*r as u64) * (*c as u64) != 0).unwrap_or(0) as u32;
         Ok(Self { raw, first_slot, options, _workspace: workspace })
     }
+    /// Cuts the plan's slots into contiguous runs for `OptimizerModule::muon_tma_finish_update_group`.
+    pub fn set_finish_groups(&self, stream: &CudaStream, first_slot: &[u32]) -> Result<(), DriverError> {
+        check(unsafe {
+            b2_muon_plan_set_finish_groups(self.raw, first_slot.as_ptr(), first_slot.len() as u32, stream.cu_stream())
+        })
+    }
     /// Whether a bounded device-side wait ran out since the last call (synchronises the stream).
     pub fn status(&self, stream: &CudaStream) -> Result<(), DriverError> {
         check(unsafe { b2_muon_plan_status(self.raw, stream.cu_stream()) })
@@ -734,6 +744,15 @@ impl OptimizerModule {
         }
         let step = self.finish_args(&args, 1);
         check(unsafe { b2_muon_finish_update(self.plan.raw, ptr(args.slots), &step, args.stream.cu_stream()) })
+    }
+    /// `muon_tma_finish_update` for the slots of one finish group (multi-GPU steps gather a group's packed weights
+    /// while the next group is updated); called once per group, whatever `args.slot_index` is.
+    pub fn muon_tma_finish_update_group(&self, args: MuonTmaFinishArgs<'_>, group: u32) -> Result<(), DriverError> {
+        if args.apply_polar_sqrt_bound != 0 {
+            return Err(DriverError(B2_ERROR_INVALID_VALUE as u32));
+        }
+        let step = self.finish_args(&args, 0);
+        check(unsafe { b2_muon_finish_update_group(self.plan.raw, ptr(args.slots), &step, group, args.stream.cu_stream()) })
     }
     /// launcher/muon_mega.rs:159-165
     pub fn muon_tma_finish_update_deferred_quantization(&self, args: MuonTmaFinishArgs<'_>) -> Result<(), DriverError> {

@@ -10,7 +10,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from llmini_b200.dist import Nvfp4Arena, all_gather_arena, shard_plan
+from llmini_b200.dist import Nvfp4Arena, all_gather_arena, all_gather_bucket, bucket_plan, shard_plan
 
 SHAPES = [(256, 128), (128, 128), (384, 128), (128, 512), (0, 0), (64, 256)]
 
@@ -34,16 +34,19 @@ def _payload(slot, rows, cols):
     return codes, raw, np.float32(gs)
 
 
-def _worker(rank, world, port, fail_rank, out):
+def _worker(rank, world, port, buckets, out):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        owner, load = shard_plan(SHAPES, world)
+        if buckets > 1:
+            bucket, owner = bucket_plan(SHAPES, world, buckets)
+        else:
+            bucket, (owner, load) = None, shard_plan(SHAPES, world)
         # every rank derives the same plan without communicating
         gathered = [None] * world
-        dist.all_gather_object(gathered, owner)
-        assert all(g == owner for g in gathered)
-        arena = Nvfp4Arena(SHAPES, owner, world, _scales_bytes)
+        dist.all_gather_object(gathered, (bucket, owner))
+        assert all(g == (bucket, owner) for g in gathered)
+        arena = Nvfp4Arena(SHAPES, owner, world, _scales_bytes, bucket)
         buf = torch.zeros(arena.total_bytes, dtype=torch.uint8)
         for slot, (rows, cols) in enumerate(SHAPES):
             if owner[slot] != rank or rows * cols == 0:
@@ -53,7 +56,14 @@ def _worker(rank, world, port, fail_rank, out):
             buf[co:co + codes.size] = torch.from_numpy(codes)
             buf[so:so + raw.size] = torch.from_numpy(raw)
             buf[go:go + 4] = torch.from_numpy(np.frombuffer(gs.tobytes(), np.uint8).copy())
-        all_gather_arena(buf, arena)
+        if buckets > 1:
+            # bucket by bucket, as a step does it: after bucket b's gather only its region is complete
+            for b in range(arena.buckets):
+                all_gather_bucket(buf, arena, b)
+                later = [e for e in arena.entries if e.bucket > b and e.rank != rank and e.codes_bytes]
+                assert all(not buf[arena.offsets(e.slot)[0]:arena.offsets(e.slot)[0] + e.codes_bytes].any() for e in later)
+        else:
+            all_gather_arena(buf, arena)
         ok = True
         for slot, (rows, cols) in enumerate(SHAPES):
             if rows * cols == 0:
@@ -130,8 +140,50 @@ def test_two_rank_all_gather_of_packed_weights():
     world, port = 2, _free_port()
     with mp.Manager() as mgr:
         out = mgr.dict()
-        mp.spawn(_worker, args=(world, port, -1, out), nprocs=world, join=True)
+        mp.spawn(_worker, args=(world, port, 1, out), nprocs=world, join=True)
         assert dict(out) == {0: True, 1: True}
+
+
+def test_two_rank_all_gather_bucket_by_bucket():
+    # the matrices cut into two buckets, each spread over both ranks and gathered by its own all-gather
+    world, port = 2, _free_port()
+    with mp.Manager() as mgr:
+        out = mgr.dict()
+        mp.spawn(_worker, args=(world, port, 2, out), nprocs=world, join=True)
+        assert dict(out) == {0: True, 1: True}
+
+
+def test_bucket_plan_cuts_contiguous_runs_and_balances_each():
+    gpt2_layer = [(2304, 768), (768, 768), (3072, 768), (768, 3072)]
+    shapes = gpt2_layer * 12
+    for world in (2, 4, 8):
+        for buckets in (1, 2, 4):
+            bucket, owner = bucket_plan(shapes, world, buckets)
+            assert bucket == sorted(bucket) and bucket[0] == 0 and bucket[-1] == buckets - 1
+            assert all(0 <= r < world for r in owner)
+            flops = [4.0 * min(r, c) ** 2 * max(r, c) + 2.0 * min(r, c) ** 3 for r, c in shapes]
+            per_bucket = [sum(f for f, b in zip(flops, bucket) if b == k) for k in range(buckets)]
+            assert max(per_bucket) <= 1.2 * min(per_bucket)
+            for k in range(buckets):
+                load = [sum(f for f, b, r in zip(flops, bucket, owner) if b == k and r == w) for w in range(world)]
+                assert max(load) <= 1.35 * (sum(load) / world)
+            # the layout puts a slot inside its owner's slice of its bucket's region, regions back to back
+            arena = Nvfp4Arena(shapes, owner, world, _scales_bytes, bucket)
+            end = 0
+            for k in range(arena.buckets):
+                base, size = arena.region(k)
+                assert base == end and size == arena.bucket_bytes_per_rank[k] * world
+                end = base + size
+            assert end == arena.total_bytes
+            for slot in range(len(shapes)):
+                e = arena.entries[slot]
+                base, _ = arena.region(e.bucket)
+                lo = base + e.rank * arena.bucket_bytes_per_rank[e.bucket]
+                co, so, go = arena.offsets(slot)
+                assert lo <= co and go + 4 <= lo + arena.bucket_bytes_per_rank[e.bucket]
+    # more buckets than matrices, and padding slots
+    bucket, owner = bucket_plan([(128, 128), (0, 0), (256, 128)], 2, 8)
+    assert max(bucket) <= 1 and len(owner) == 3
 
 
 def _raising_worker(rank, world, port):

@@ -54,21 +54,26 @@ def _run_slots(device, slot_ids, arena, arena_t, data):
     plan.close()
 
 
-def _worker(rank, world, port, out):
+def _layout(world, buckets):
+    from llmini_b200.dist import Nvfp4Arena, bucket_plan
+
+    bucket, owner = bucket_plan(SHAPES, world, buckets)
+    return bucket, owner, Nvfp4Arena(SHAPES, owner, world, lambda r, c: r * c // 16, bucket)
+
+
+def _worker(rank, world, port, buckets, out):
     import torch.distributed as dist
 
-    from llmini_b200.dist import Communicator, Nvfp4Arena, shard_plan
+    from llmini_b200.dist import Communicator
 
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
     device = torch.device("cuda", rank)
     dist.init_process_group("gloo", rank=rank, world_size=world)   # rendezvous only
     try:
-        owner, _ = shard_plan(SHAPES, world)
-        arena = Nvfp4Arena(SHAPES, owner, world, lambda r, c: r * c // 16)
+        bucket, owner, arena = _layout(world, buckets)
         arena_t = torch.zeros(arena.total_bytes, dtype=torch.uint8, device=device)
         data = _make_inputs()
-        _run_slots(device, [i for i, o_ in enumerate(owner) if o_ == rank], arena, arena_t, data)
 
         def bcast(b):
             box = [b]
@@ -76,7 +81,15 @@ def _worker(rank, world, port, out):
             return box[0]
 
         comm = Communicator(rank, world, bcast)
-        comm.all_gather(arena_t.data_ptr(), arena.bytes_per_rank, torch.cuda.current_stream().cuda_stream)
+        # bucket by bucket: this rank's matrices of the bucket, then the bucket's all-gather on a second stream
+        # while the next bucket is computed
+        side = torch.cuda.Stream(device=device)
+        for b in range(arena.buckets):
+            _run_slots(device, [i for i, o_ in enumerate(owner) if o_ == rank and bucket[i] == b], arena, arena_t, data)
+            base, _ = arena.region(b)
+            side.wait_stream(torch.cuda.current_stream())
+            comm.all_gather(arena_t.data_ptr() + base, arena.bucket_bytes_per_rank[b], side.cuda_stream)
+        torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize(device)
         comm.close()
         out[rank] = arena_t.cpu().numpy().tobytes()
@@ -85,20 +98,18 @@ def _worker(rank, world, port, out):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_sharded_step_and_library_all_gather_match_single_gpu():
+@pytest.mark.parametrize("buckets", [1, 2])
+def test_sharded_step_and_library_all_gather_match_single_gpu(buckets):
     import torch.multiprocessing as mp
-
-    from llmini_b200.dist import Nvfp4Arena, shard_plan
 
     world = 2
     with mp.Manager() as mgr:
         out = mgr.dict()
-        mp.spawn(_worker, args=(world, _free_port(), out), nprocs=world, join=True)
+        mp.spawn(_worker, args=(world, _free_port(), buckets, out), nprocs=world, join=True)
         got = {k: np.frombuffer(v, np.uint8) for k, v in out.items()}
     assert np.array_equal(got[0], got[1])
     # single-GPU run of every matrix into the same arena layout
-    owner, _ = shard_plan(SHAPES, world)
-    arena = Nvfp4Arena(SHAPES, owner, world, lambda r, c: r * c // 16)
+    _, _, arena = _layout(world, buckets)
     device = torch.device("cuda", 0)
     arena_t = torch.zeros(arena.total_bytes, dtype=torch.uint8, device=device)
     _run_slots(device, list(range(len(SHAPES))), arena, arena_t, _make_inputs())

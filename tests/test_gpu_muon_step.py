@@ -210,6 +210,50 @@ def test_one_gpt2_layer_fused_gram_poly_newton_schulz():
                 o.fixed_coefficients(5), seed=14, normalize=b2.NORMALIZE_DEFERRED, schedule=b2.NS_FUSED_GRAM_POLY)
 
 
+def test_finish_by_groups_equals_one_finish_launch():
+    # stage U + Q launched group by group (what a multi-GPU step does to start a bucket's all-gather early) must
+    # leave exactly what the single launch leaves; groups may be empty and a group index must exist
+    shapes = [(256, 512), (384, 128), (128, 128), (0, 0), (640, 256), (128, 1024)]
+    rng = np.random.default_rng(21)
+    data = [((rng.standard_normal(r * c) * 1e-3).astype(F), (rng.standard_normal(r * c) * 0.02).astype(F),
+             (rng.standard_normal(r * c) * 0.02).astype(F)) for r, c in shapes]
+    args = b2.MuonMegaUpdateArgs(learning_rate=0.02, coefficients=o.fixed_coefficients(5))
+
+    def run(groups):
+        slots = [_slot(r, c, g, np.zeros(r * c, np.uint16), z, x, b2.SCALES_RAW) for (r, c), (g, z, x) in zip(shapes, data)]
+        plan = b2.MuonPlan(shapes, scale_layout=b2.SCALES_RAW, normalize_mode=b2.NORMALIZE_DEFERRED)
+        opt, table = b2.OptimizerModule(), b2.slot_table(slots)
+        if groups:
+            plan.set_finish_groups(groups)
+        for _ in range(2):   # twice: the second step starts from the counters the first one left
+            opt.muon_tma_prepare_polar(plan, table, args)
+            opt.muon_polar(plan, args)
+            if groups:
+                for g in range(len(groups)):
+                    opt.muon_tma_finish_update_group(plan, table, args, g)
+            else:
+                opt.muon_tma_finish_update(plan, table, args)
+        torch.cuda.synchronize()
+        assert plan.status() == 0
+        if groups:
+            with pytest.raises(b2.B2Error):
+                opt.muon_tma_finish_update_group(plan, table, args, len(groups))
+            with pytest.raises(b2.B2Error):
+                plan.set_finish_groups([1, 2])          # must start at slot 0
+            with pytest.raises(b2.B2Error):
+                plan.set_finish_groups([0, 4, 2])       # must ascend
+        out = [[host(t).copy() for t in (s.z_master, s.x_master, s.grad, s.momentum.view(torch.int16), s.bytes, s.scales,
+                                         s.global_scale, s.schedule_amax)] for s in slots if s.rows * s.cols]
+        plan.close()
+        return out
+
+    whole = run(None)
+    for groups in ([0, 2, 2, 5], [0, 1, 2, 3, 4, 5], [0]):
+        for a, b in zip(run(groups), whole):
+            for ta, tb in zip(a, b):
+                assert np.array_equal(ta, tb), groups
+
+
 def test_one_pass_prepare_needs_bf16_operands():
     with pytest.raises(b2.B2Error):
         b2.MuonPlan([(64, 64)], operand_format=b2.OPERAND_F16, scale_layout=b2.SCALES_RAW,
