@@ -282,16 +282,15 @@ class GpuJob:
         layout = self.layout = b2.SCALES_CSF if d_model % 128 == 0 else b2.SCALES_RAW
         # Buckets: contiguous runs of matrices, each spread over all ranks.  Stages M, N and P run over all of the
         # rank's matrices at once; stage U + Q runs bucket by bucket, and the all-gather of one bucket's packed
-        # weights runs while the next bucket is updated; the last bucket's gather runs beside AdamW.  So: as many
-        # buckets as it takes for the last gather to fit behind AdamW (estimated from the bytes either moves: 600 GB/s
-        # into a rank, AdamW at 5 TB/s), at most four, none smaller than 10 M elements per rank.
+        # weights runs while the next bucket is updated; the last bucket's gather runs beside AdamW.  A gather has a
+        # fixed cost of 50-80 us, so a bucket's gather should take a quarter of a millisecond or more (estimated
+        # from its bytes at 600 GB/s into a rank): one bucket per 0.25 ms of gathering, at most four.  (Measured on
+        # four GPUs: GPT-2 XL 14.56 -> 14.13 ms with four buckets, GPT-2 small 0.70 -> 0.78 ms with two.)
         self.n_buckets = 1
         if world > 1:
             elems = sum(r * c for r, c in self.mats)
-            gather_ms = elems * 0.5625 * (world - 1) / world / 600e9 * 1e3 + 0.02
-            adam_ms = (sum(r * c for r, c in emb) + vec) / world * 36.0 / 5e12 * 1e3
-            auto = int(np.ceil(gather_ms / max(adam_ms, 1e-3)))
-            auto = max(1, min(4, auto, int(elems / world / 10e6)))
+            gather_ms = elems * 0.5625 * (world - 1) / world / 600e9 * 1e3
+            auto = max(1, min(4, int(gather_ms / 0.25)))
             self.n_buckets = args.gather_buckets if args.gather_buckets > 0 else auto
         self.bucket, self.owner = bucket_plan(self.mats, world, self.n_buckets)
         self.n_buckets = max(self.bucket) + 1 if self.bucket else 1
@@ -1072,8 +1071,7 @@ def main():
                          "reference's update input)")
     ap.add_argument("--gather-buckets", type=int, default=0,
                     help="N > 1: cut the matrices into this many buckets; the all-gather of a bucket overlaps the next "
-                         "bucket's update + quantise launch (0: as many as it takes for the last gather to fit behind AdamW, "
-                         "at most four)")
+                         "bucket's update + quantise launch (0: one per estimated 0.25 ms of gathering, at most four)")
     ap.add_argument("--shard-of", type=int, default=1,
                     help="with one GPU: run rank 0's share of an N-way sharded step (no collective), to time the "
                          "per-rank kernels of a multi-GPU run")
