@@ -100,6 +100,9 @@ def test_five_iterations_multi_slot(shapes, tile_n, schedule):
     [(768, 768), (768, 3072), (3072, 768), (2304, 768), (0, 0), (768, 768)],
     [(1600, 1600), (1600, 320), (48, 1600), (4800, 1600)],
     [(64, 64)],
+    # 13 x 13 pair tiles = 91 Gram tiles, more than the device runs CTA pairs at once: the fused form must step
+    # aside (a pair waiting for tiles that no resident pair can take would wait for ever)
+    [(3328, 3328), (256, 512)],
 ])
 def test_chained_launch_equals_the_per_phase_launches_bit_for_bit(shapes, tile_n):
     # The chained launch runs the same tiles with the same k order as the fifteen per-phase launches; only the
