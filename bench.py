@@ -290,7 +290,8 @@ class GpuJob:
         if world > 1:
             elems = sum(r * c for r, c in self.mats)
             gather_ms = elems * 0.5625 * (world - 1) / world / 600e9 * 1e3
-            auto = max(1, min(4, int(gather_ms / 0.25)))
+            # (the library's own copy kernel has a fixed cost of a few microseconds: smaller buckets pay)
+            auto = max(1, min(4, int(gather_ms / (0.06 if args.gather == "p2p" else 0.25))))
             self.n_buckets = args.gather_buckets if args.gather_buckets > 0 else auto
         self.bucket, self.owner = bucket_plan(self.mats, world, self.n_buckets)
         self.n_buckets = max(self.bucket) + 1 if self.bucket else 1
@@ -302,9 +303,24 @@ class GpuJob:
             return b2.csf_encoded_len(rows, cols) if layout == b2.SCALES_CSF else rows * cols // 16
 
         self.arena = Nvfp4Arena(self.mats, self.owner, world, scales_bytes, self.bucket)
-        self.arena_t = torch.zeros(self.arena.total_bytes + 1024, dtype=torch.uint8, device=dev)
-        abase = (-self.arena_t.data_ptr()) % 256
-        self.arena_v = self.arena_t[abase:abase + self.arena.total_bytes]
+        self.peers = None
+        if world > 1 and args.gather == "p2p":
+            # the arena in memory that the other ranks map: a bucket is exchanged by copying this rank's slice into
+            # every peer's arena (b2_peer_push) instead of an NCCL all-gather
+            import torch.distributed as dist
+            from llmini_b200.dist import PeerArena
+
+            def exchange(obj):
+                got = [None] * world
+                dist.all_gather_object(got, obj)
+                return got
+
+            self.peers = PeerArena(self.arena.total_bytes, rank, world, exchange, dev)
+            self.arena_t = self.arena_v = self.peers.tensor
+        else:
+            self.arena_t = torch.zeros(self.arena.total_bytes + 1024, dtype=torch.uint8, device=dev)
+            abase = (-self.arena_t.data_ptr()) % 256
+            self.arena_v = self.arena_t[abase:abase + self.arena.total_bytes]
 
         gen = torch.Generator(device=dev).manual_seed(1234 + rank)
         randn = lambda n, std: torch.randn(n, device=dev, generator=gen) * std
@@ -389,6 +405,9 @@ class GpuJob:
         self.gather_stream.wait_event(fork)
         base, size = self.arena.region(b)
         n = self.arena.bucket_bytes_per_rank[b]
+        if self.peers is not None:
+            self.peers.push(base + self.rank * n, n, self.gather_stream.cuda_stream)   # (an empty slice still counts)
+            return
         if n == 0:
             return
         with torch.cuda.stream(self.gather_stream):
@@ -397,6 +416,8 @@ class GpuJob:
 
     def join_gathers(self):
         torch = self.torch
+        if self.peers is not None:
+            self.peers.wait(self.gather_stream.cuda_stream)   # every rank's copies of this step have landed here
         join = torch.cuda.Event()
         join.record(self.gather_stream)
         torch.cuda.current_stream().wait_event(join)
@@ -486,6 +507,8 @@ class GpuJob:
     def check_status(self, when):
         if self.plan is not None and self.plan.status() != 0:
             raise SystemExit(f"a bounded device-side wait ran out {when}")
+        if self.peers is not None and self.peers.status(self.torch.cuda.current_stream().cuda_stream) != 0:
+            raise SystemExit(f"the bounded wait for the other ranks' copies ran out {when}")
 
     def stage_summary(self, peaks):
         """Mean device time of the four stages over the eager timed pass (this rank), and the rates."""
@@ -522,6 +545,8 @@ class GpuJob:
                               self.b2.NS_FUSED_GRAM_POLY: "two launches per iteration (fused Gram + polynomial tiles, apply)"
                               }.get(self.schedule, "three launches per iteration"),
             "gather_buckets": self.n_buckets,
+            "gather": None if self.world == 1 else ("copies into the other ranks' arenas through peer memory"
+                                                    if self.peers is not None else "ncclAllGather"),
             "update_quantise_bytes_per_element": fin_bytes,
         }
 
@@ -591,6 +616,11 @@ class GpuJob:
     def close(self):
         if self.plan is not None:
             self.plan.close()
+        if self.peers is not None:
+            self.barrier()          # nobody unmaps or frees while another rank may still be copying
+            self.slots, self.table, self.arena_t, self.arena_v = [], None, None, None
+            self.peers.close()
+            self.peers = None
 
 
 def secondary_workload(name, args, world, rank, dev, peaks):
@@ -1069,6 +1099,9 @@ def main():
     ap.add_argument("--update-16bit", action="store_true",
                     help="the last Newton-Schulz iteration stores BF16 and the update reads it (default: FP32, as the "
                          "reference's update input)")
+    ap.add_argument("--gather", choices=["nccl", "p2p"], default="nccl",
+                    help="N > 1: how the packed weights are exchanged: ncclAllGather per bucket, or this library's own "
+                         "copy kernels into the other ranks' arenas through peer memory (CUDA IPC)")
     ap.add_argument("--gather-buckets", type=int, default=0,
                     help="N > 1: cut the matrices into this many buckets; the all-gather of a bucket overlaps the next "
                          "bucket's update + quantise launch (0: one per estimated 0.25 ms of gathering, at most four)")

@@ -492,6 +492,35 @@ void b2_comm_destroy(b2_comm *comm);
  * tensor scales live at d_arena + r * bytes_per_rank. */
 int b2_allgather_nvfp4(b2_comm *comm, void *d_arena, size_t bytes_per_rank, void *stream);
 
+/* The same exchange without a library collective: every rank's arena lives in a buffer that the other ranks map
+ * (one process per GPU, CUDA IPC, NVLink peer access), and a rank copies its slice into the same offset of every
+ * peer's buffer with plain stores from one small kernel, which ends by telling every peer how many copies this
+ * rank has completed.  All ranks issue the same sequence of copies; `b2_peer_wait` returns (on the stream) once
+ * every peer's count has reached this rank's own, i.e. every copy enqueued before it, by any rank, has landed
+ * here.  The wait is bounded (`wait_ns`, at most and by default 2e9): when it runs out the kernel sets a status
+ * word and returns, and `b2_peer_status` (synchronises) reports B2_ERROR_LAUNCH_TIMEOUT once.  The fixed cost of
+ * a copy is a few microseconds, against 50-80 us for an ncclAllGather, so small buckets pay.
+ *   b2_peer_buffer_alloc: cudaMalloc of arena_bytes plus a 256-byte control block, zeroed; `handle` is the
+ *     64-byte IPC handle to send to the other ranks.  b2_peer_buffer_open maps another rank's buffer
+ *     (b2_peer_buffer_close unmaps it); b2_peer_buffer_free releases one's own.
+ *   b2_peer_group: world, rank, the arena size given to b2_peer_buffer_alloc, and base[r] = the address at which
+ *     this process sees rank r's buffer (its own allocation for r == rank).
+ *   b2_peer_push: offset and bytes are multiples of 16 inside the arena; `ctas` caps the grid (0: 32).  Copies and
+ *     the wait of one group go on ONE stream. */
+#define B2_MAX_PEERS 16
+typedef struct b2_peer_group {
+    uint32_t world, rank;
+    uint64_t arena_bytes;
+    uint64_t base[B2_MAX_PEERS];
+} b2_peer_group;
+int b2_peer_buffer_alloc(size_t arena_bytes, void **d_ptr, uint8_t handle[64]);
+int b2_peer_buffer_open(const uint8_t handle[64], void **d_ptr);
+int b2_peer_buffer_close(void *d_ptr);
+int b2_peer_buffer_free(void *d_ptr);
+int b2_peer_push(const b2_peer_group *group, size_t offset, size_t bytes, uint32_t ctas, void *stream);
+int b2_peer_wait(const b2_peer_group *group, uint64_t wait_ns, void *stream);
+int b2_peer_status(const b2_peer_group *group, void *stream);
+
 /* ---- debug helpers used by the parity tests ------------------------------------------- */
 /* Makes the bounded completion-counter wait of the one-launch update + encode run out, harmlessly:
  * launches that kernel as ONE CTA on a one-item list (the encode span at `slot`'s first chunk, none of the

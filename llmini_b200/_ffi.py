@@ -90,6 +90,14 @@ class AdamWSlotDescriptor(C.Structure):
                 ("len", C.c_uint32), ("chunk_begin", C.c_uint32), ("mode", C.c_uint32), ("scale_layout", C.c_uint32)]
 
 
+MAX_PEERS = 16
+
+
+class PeerGroup(C.Structure):
+    _fields_ = [("world", C.c_uint32), ("rank", C.c_uint32), ("arena_bytes", C.c_uint64),
+                ("base", C.c_uint64 * MAX_PEERS)]
+
+
 class GradientClipArgs(C.Structure):
     _fields_ = [("chunk_ptrs", C.c_void_p), ("chunk_lens", C.c_void_p), ("chunk_sums", C.c_void_p),
                 ("extra_sums", C.c_void_p), ("scale", C.c_void_p), ("norm", C.c_void_p),
@@ -159,6 +167,13 @@ def _declare(L: C.CDLL) -> None:
         "b2_comm_create": (i, [C.POINTER(vp), u8p, i, i]),
         "b2_comm_destroy": (None, [vp]),
         "b2_allgather_nvfp4": (i, [vp, vp, sz, vp]),
+        "b2_peer_buffer_alloc": (i, [sz, C.POINTER(vp), u8p]),
+        "b2_peer_buffer_open": (i, [u8p, C.POINTER(vp)]),
+        "b2_peer_buffer_close": (i, [vp]),
+        "b2_peer_buffer_free": (i, [vp]),
+        "b2_peer_push": (i, [C.POINTER(PeerGroup), sz, sz, u32, vp]),
+        "b2_peer_wait": (i, [C.POINTER(PeerGroup), u64, vp]),
+        "b2_peer_status": (i, [C.POINTER(PeerGroup), vp]),
         "b2_debug_muon_fused_wait_expiry": (i, [vp, vp, u32, u64, vp]),
         "b2_debug_rcp_approx_ftz": (i, [vp, vp, u32, vp]),
         "b2_debug_quantize_literal": (i, [vp, vp, vp, vp, vp, u32, vp]),

@@ -13,7 +13,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT_DIR = os.path.join(HERE, "_lib")
 LIB_PATH = os.path.join(OUT_DIR, "libllmini_b200.so")
-SOURCES = ["stream_kernels.cu", "ns_gemm_sm100.cu", "api.cu", "host.cu", "no_alloc.cu"]
+SOURCES = ["stream_kernels.cu", "ns_gemm_sm100.cu", "api.cu", "host.cu", "peer_gather.cu", "no_alloc.cu"]
 HEADERS = ["common.cuh", "internal.h", os.path.join("..", "..", "include", "llmini_b200.h")]
 # -fmad=false: `a*b + c` is fused only where the source says fmaf, matching the reference's
 # Rust arithmetic.  B2_MEASURE=1 in the environment adds -DB2_MEASURE: the kernel variants used to

@@ -183,6 +183,65 @@ def gathered_arena_consistent(arena_tensor, arena: Nvfp4Arena, group=None) -> bo
     return bool(torch.equal(lo, hi)) and filled
 
 
+class _DeviceBytes:
+    """A raw device allocation seen by torch through the CUDA array interface."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+class PeerArena:
+    """The gathered arena in memory that the other ranks map (b2_peer_*): `tensor` is this rank's copy of the whole
+    arena (a uint8 torch view of the library's allocation); `push(offset, bytes)` copies a piece of it to the same
+    place in every peer's copy with one small kernel; `wait()` makes the stream wait until every copy that any
+    rank enqueued before its own wait has arrived here.  One process per GPU; `exchange(obj) -> list` gathers one
+    picklable object from every rank (torch.distributed.all_gather_object does)."""
+
+    def __init__(self, arena_bytes: int, rank: int, world: int, exchange, device):
+        import torch
+
+        if world > _ffi.MAX_PEERS:
+            raise ValueError(f"at most {_ffi.MAX_PEERS} ranks")
+        L = _ffi.lib()
+        self._lib, self.rank, self.world, self.arena_bytes = L, rank, world, int(arena_bytes)
+        self._own, self._opened = C.c_void_p(), []
+        handle = (C.c_uint8 * 64)()
+        with torch.cuda.device(device):
+            _ffi.check(L.b2_peer_buffer_alloc(self.arena_bytes, C.byref(self._own), handle), "peer_buffer_alloc")
+            handles = exchange(bytes(handle))
+            self.group = _ffi.PeerGroup()
+            self.group.world, self.group.rank, self.group.arena_bytes = world, rank, self.arena_bytes
+            for r in range(world):
+                if r == rank:
+                    self.group.base[r] = self._own.value
+                    continue
+                p = C.c_void_p()
+                h = (C.c_uint8 * 64)(*handles[r])
+                _ffi.check(L.b2_peer_buffer_open(h, C.byref(p)), "peer_buffer_open")
+                self._opened.append(p)
+                self.group.base[r] = p.value
+        self.tensor = torch.as_tensor(_DeviceBytes(self._own.value, max(self.arena_bytes, 1)), device=device)[:self.arena_bytes]
+
+    def push(self, offset: int, nbytes: int, stream: int, ctas: int = 0) -> None:
+        _ffi.check(self._lib.b2_peer_push(C.byref(self.group), offset, nbytes, ctas, stream), "peer_push")
+
+    def wait(self, stream: int, wait_ns: int = 0) -> None:
+        _ffi.check(self._lib.b2_peer_wait(C.byref(self.group), wait_ns, stream), "peer_wait")
+
+    def status(self, stream: int) -> int:
+        return int(self._lib.b2_peer_status(C.byref(self.group), stream))
+
+    def close(self) -> None:
+        """Every rank must have finished with the others' buffers (a barrier) before any rank frees its own."""
+        for p in self._opened:
+            self._lib.b2_peer_buffer_close(p)
+        self._opened = []
+        if self._own.value:
+            self.tensor = None
+            self._lib.b2_peer_buffer_free(self._own)
+            self._own = C.c_void_p()
+
+
 class Communicator:
     """The library's own NCCL communicator (b2_comm_*), bootstrapped over torch.distributed."""
 

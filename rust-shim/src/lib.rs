@@ -49,6 +49,7 @@ pub mod ffi {
     pub const B2_UPDATE_F32: u32 = 0;
     pub const B2_UPDATE_16BIT: u32 = 1;
     pub const B2_STATIC_MAX_ELEMENTS: u32 = 1 << 26;
+    pub const B2_MAX_PEERS: usize = 16;
 
     #[repr(C)]
     #[derive(Clone, Copy, Default)]
@@ -179,6 +180,15 @@ pub mod ffi {
         pub average_coefficient: f32,
         pub schedule_beta: f32,
         pub d_grad_scale: CUdeviceptr,
+    }
+
+    #[repr(C)]
+    #[derive(Clone, Copy, Default)]
+    pub struct b2_peer_group {
+        pub world: u32,
+        pub rank: u32,
+        pub arena_bytes: u64,
+        pub base: [u64; B2_MAX_PEERS],
     }
 
     #[repr(C)]
@@ -320,6 +330,13 @@ pub mod ffi {
         pub fn b2_comm_create(comm: *mut *mut b2_comm, unique_id: *const u8, rank: i32, world: i32) -> i32;
         pub fn b2_comm_destroy(comm: *mut b2_comm);
         pub fn b2_allgather_nvfp4(comm: *mut b2_comm, d_arena: CUdeviceptr, bytes_per_rank: usize, stream: CUstream) -> i32;
+        pub fn b2_peer_buffer_alloc(arena_bytes: usize, d_ptr: *mut CUdeviceptr, handle: *mut u8) -> i32;
+        pub fn b2_peer_buffer_open(handle: *const u8, d_ptr: *mut CUdeviceptr) -> i32;
+        pub fn b2_peer_buffer_close(d_ptr: CUdeviceptr) -> i32;
+        pub fn b2_peer_buffer_free(d_ptr: CUdeviceptr) -> i32;
+        pub fn b2_peer_push(group: *const b2_peer_group, offset: usize, bytes: usize, ctas: u32, stream: CUstream) -> i32;
+        pub fn b2_peer_wait(group: *const b2_peer_group, wait_ns: u64, stream: CUstream) -> i32;
+        pub fn b2_peer_status(group: *const b2_peer_group, stream: CUstream) -> i32;
         pub fn b2_debug_muon_fused_wait_expiry(plan: *mut b2_muon_plan, d_slots: CUdeviceptr, slot: u32, wait_ns: u64,
                                                stream: CUstream) -> i32;
         pub fn b2_debug_rcp_approx_ftz(d_in: CUdeviceptr, d_out: CUdeviceptr, count: u32, stream: CUstream) -> i32;

@@ -1,7 +1,7 @@
 """Two-GPU run of the sharded step: every rank updates the matrices it owns, writes packed
 NVFP4 weights into its arena slice, and the arenas are all-gathered with the library's own NCCL
-communicator (b2_comm_* / b2_allgather_nvfp4).  The gathered weights must equal a single-GPU run
-of all matrices bit for bit.  Skipped when fewer than two GPUs are visible."""
+communicator (b2_comm_* / b2_allgather_nvfp4) or copied into the other rank's arena through peer memory
+(b2_peer_*).  The gathered weights must equal a single-GPU run of all matrices bit for bit.  Skipped when fewer than two GPUs are visible."""
 import os
 import socket
 
@@ -61,10 +61,10 @@ def _layout(world, buckets):
     return bucket, owner, Nvfp4Arena(SHAPES, owner, world, lambda r, c: r * c // 16, bucket)
 
 
-def _worker(rank, world, port, buckets, out):
+def _worker(rank, world, port, buckets, gather, out):
     import torch.distributed as dist
 
-    from llmini_b200.dist import Communicator
+    from llmini_b200.dist import Communicator, PeerArena
 
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
@@ -72,7 +72,6 @@ def _worker(rank, world, port, buckets, out):
     dist.init_process_group("gloo", rank=rank, world_size=world)   # rendezvous only
     try:
         bucket, owner, arena = _layout(world, buckets)
-        arena_t = torch.zeros(arena.total_bytes, dtype=torch.uint8, device=device)
         data = _make_inputs()
 
         def bcast(b):
@@ -80,32 +79,56 @@ def _worker(rank, world, port, buckets, out):
             dist.broadcast_object_list(box, src=0)
             return box[0]
 
-        comm = Communicator(rank, world, bcast)
-        # bucket by bucket: this rank's matrices of the bucket, then the bucket's all-gather on a second stream
-        # while the next bucket is computed
+        def exchange(obj):
+            got = [None] * world
+            dist.all_gather_object(got, obj)
+            return got
+
         side = torch.cuda.Stream(device=device)
+        if gather == "p2p":
+            # the arena in memory the other rank maps; a bucket is copied into the peer's arena by one small kernel
+            peers = PeerArena(arena.total_bytes, rank, world, exchange, device)
+            arena_t = peers.tensor
+        else:
+            comm = Communicator(rank, world, bcast)
+            arena_t = torch.zeros(arena.total_bytes, dtype=torch.uint8, device=device)
+        # bucket by bucket: this rank's matrices of the bucket, then the bucket's exchange on a second stream
+        # while the next bucket is computed
         for b in range(arena.buckets):
             _run_slots(device, [i for i, o_ in enumerate(owner) if o_ == rank and bucket[i] == b], arena, arena_t, data)
             base, _ = arena.region(b)
+            n = arena.bucket_bytes_per_rank[b]
             side.wait_stream(torch.cuda.current_stream())
-            comm.all_gather(arena_t.data_ptr() + base, arena.bucket_bytes_per_rank[b], side.cuda_stream)
+            if gather == "p2p":
+                peers.push(base + rank * n, n, side.cuda_stream)
+            else:
+                comm.all_gather(arena_t.data_ptr() + base, n, side.cuda_stream)
+        if gather == "p2p":
+            peers.wait(side.cuda_stream)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize(device)
-        comm.close()
         out[rank] = arena_t.cpu().numpy().tobytes()
+        if gather == "p2p":
+            assert peers.status(torch.cuda.current_stream().cuda_stream) == 0
+            dist.barrier()          # nobody unmaps or frees while the other may still be copying
+            arena_t = None
+            peers.close()
+        else:
+            comm.close()
     finally:
         dist.destroy_process_group()
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("gather", ["nccl", "p2p"])
 @pytest.mark.parametrize("buckets", [1, 2])
-def test_sharded_step_and_library_all_gather_match_single_gpu(buckets):
+def test_sharded_step_and_library_all_gather_match_single_gpu(buckets, gather):
     import torch.multiprocessing as mp
 
     world = 2
     with mp.Manager() as mgr:
         out = mgr.dict()
-        mp.spawn(_worker, args=(world, _free_port(), buckets, out), nprocs=world, join=True)
+        mp.spawn(_worker, args=(world, _free_port(), buckets, gather, out), nprocs=world, join=True)
         got = {k: np.frombuffer(v, np.uint8) for k, v in out.items()}
     assert np.array_equal(got[0], got[1])
     # single-GPU run of every matrix into the same arena layout

@@ -76,7 +76,7 @@ def test_every_struct_has_the_same_fields_in_the_same_order():
     h, s = header_structs(), shim_structs()
     assert set(h) == {"b2_muon_slot_descriptor", "b2_symexp_lin_slot_descriptor", "b2_muon_options", "b2_muon_step_args",
                       "b2_schedule_free_materialize_args", "b2_adamw_update_args", "b2_adamw_slot_descriptor",
-                      "b2_symexp_lin_adamw_args", "b2_gradient_clip_args"}
+                      "b2_symexp_lin_adamw_args", "b2_gradient_clip_args", "b2_peer_group"}
     for name, fields in h.items():
         assert s.get(name) == fields, name
 
