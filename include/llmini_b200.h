@@ -505,7 +505,7 @@ int b2_allgather_nvfp4(b2_comm *comm, void *d_arena, size_t bytes_per_rank, void
  *     (b2_peer_buffer_close unmaps it); b2_peer_buffer_free releases one's own.
  *   b2_peer_group: world, rank, the arena size given to b2_peer_buffer_alloc, and base[r] = the address at which
  *     this process sees rank r's buffer (its own allocation for r == rank).
- *   b2_peer_push: offset and bytes are multiples of 16 inside the arena; `ctas` caps the grid (0: 32).  Copies and
+ *   b2_peer_push: offset and bytes are multiples of 16 inside the arena; `ctas` caps the grid (0: 48).  Copies and
  *     the wait of one group go on ONE stream. */
 #define B2_MAX_PEERS 16
 typedef struct b2_peer_group {

@@ -52,11 +52,25 @@ __global__ void __launch_bounds__(kPushThreads)
 k_peer_push(PeerTable peers, uint32_t world, uint32_t rank, size_t offset, size_t bytes, size_t ctrl_offset) {
     const uint4 *src = reinterpret_cast<const uint4 *>(peers.base[rank] + offset);
     const size_t n = bytes / 16;
-    for (size_t i = (size_t)blockIdx.x * kPushThreads + threadIdx.x; i < n; i += (size_t)gridDim.x * kPushThreads) {
-        const uint4 v = __ldcg(src + i);   // written moments ago by the encode: still in L2
+    // four 16-byte pieces per thread and turn, all loads before the first store: one load's latency per 64 bytes
+    // and peer would leave the links idle
+    constexpr int kUnroll = 4;
+    const size_t stride = (size_t)gridDim.x * kPushThreads;
+    for (size_t i0 = (size_t)blockIdx.x * kPushThreads + threadIdx.x; i0 < n; i0 += kUnroll * stride) {
+        uint4 v[kUnroll];
 #pragma unroll
-        for (uint32_t p = 0; p < B2_MAX_PEERS; ++p)
-            if (p < world && p != rank) *reinterpret_cast<uint4 *>(peers.base[p] + offset + 16 * i) = v;
+        for (int u = 0; u < kUnroll; ++u) {
+            const size_t i = i0 + u * stride;
+            if (i < n) v[u] = __ldcg(src + i);   // written moments ago by the encode: mostly still in L2
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const size_t i = i0 + u * stride;
+            if (i >= n) continue;
+#pragma unroll
+            for (uint32_t p = 0; p < B2_MAX_PEERS; ++p)
+                if (p < world && p != rank) *reinterpret_cast<uint4 *>(peers.base[p] + offset + 16 * i) = v[u];
+        }
     }
     __threadfence_system();
     __syncthreads();
@@ -141,8 +155,8 @@ int b2_peer_push(const b2_peer_group *group, size_t offset, size_t bytes, uint32
     std::memset(&t, 0, sizeof(t));
     for (uint32_t p = 0; p < group->world; ++p) t.base[p] = group->base[p];
     // enough CTAs to keep the links busy, few enough to leave the SMs to the kernels this copy runs beside
-    size_t want = (bytes / 16 + kPushThreads - 1) / kPushThreads;
-    if (ctas == 0) ctas = 32;
+    size_t want = (bytes / 16 + 4 * kPushThreads - 1) / (4 * kPushThreads);
+    if (ctas == 0) ctas = 48;
     if (want < 1) want = 1;
     const unsigned grid = (unsigned)(want < ctas ? want : ctas);
     k_peer_push<<<grid, kPushThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(t, group->world, group->rank, offset,

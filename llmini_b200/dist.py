@@ -204,22 +204,34 @@ class PeerArena:
             raise ValueError(f"at most {_ffi.MAX_PEERS} ranks")
         L = _ffi.lib()
         self._lib, self.rank, self.world, self.arena_bytes = L, rank, world, int(arena_bytes)
-        self._own, self._opened = C.c_void_p(), []
+        self._own, self._opened, self.tensor = C.c_void_p(), [], None
         handle = (C.c_uint8 * 64)()
+        # Every rank goes through both exchanges whatever happens to it, so that all of them succeed or all of them
+        # raise: a rank that left early would leave the others waiting.
         with torch.cuda.device(device):
-            _ffi.check(L.b2_peer_buffer_alloc(self.arena_bytes, C.byref(self._own), handle), "peer_buffer_alloc")
-            handles = exchange(bytes(handle))
-            self.group = _ffi.PeerGroup()
-            self.group.world, self.group.rank, self.group.arena_bytes = world, rank, self.arena_bytes
-            for r in range(world):
-                if r == rank:
-                    self.group.base[r] = self._own.value
-                    continue
-                p = C.c_void_p()
-                h = (C.c_uint8 * 64)(*handles[r])
-                _ffi.check(L.b2_peer_buffer_open(h, C.byref(p)), "peer_buffer_open")
-                self._opened.append(p)
-                self.group.base[r] = p.value
+            rc = L.b2_peer_buffer_alloc(self.arena_bytes, C.byref(self._own), handle)
+            handles = exchange(bytes(handle) if rc == 0 else None)
+            problem = None
+            if any(h is None for h in handles):
+                problem = "a rank could not allocate its buffer"
+            else:
+                self.group = _ffi.PeerGroup()
+                self.group.world, self.group.rank, self.group.arena_bytes = world, rank, self.arena_bytes
+                for r in range(world):
+                    if r == rank:
+                        self.group.base[r] = self._own.value
+                        continue
+                    p = C.c_void_p()
+                    rc = L.b2_peer_buffer_open((C.c_uint8 * 64)(*handles[r]), C.byref(p))
+                    if rc != 0:
+                        problem = f"rank {rank} could not map rank {r}'s buffer (error {rc})"
+                        break
+                    self._opened.append(p)
+                    self.group.base[r] = p.value
+            problems = [q for q in exchange(problem) if q]
+            if problems:
+                self.close()
+                raise RuntimeError(problems[0])
         self.tensor = torch.as_tensor(_DeviceBytes(self._own.value, max(self.arena_bytes, 1)), device=device)[:self.arena_bytes]
 
     def push(self, offset: int, nbytes: int, stream: int, ctas: int = 0) -> None:
