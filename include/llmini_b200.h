@@ -13,8 +13,9 @@
  *  - `stream` is a `cudaStream_t` / `CUstream` passed as `void*`; all work is enqueued on
  *    it in program order and nothing synchronises unless stated.
  *  - All pointers named `d_*` or typed as device buffers are device pointers owned by the
- *    caller.  The library allocates no device memory: scratch comes from the caller-sized
- *    workspace (`b2_muon_workspace_bytes`).
+ *    caller.  No compute call allocates device memory: scratch comes from the caller-sized
+ *    workspace (`b2_muon_workspace_bytes`).  (`b2_peer_buffer_alloc` allocates, because that is what it is asked
+ *    for: a buffer other processes can map.)
  *  - No CPU fallback exists.  Without a CUDA device every compute entry point returns an
  *    error.
  *  - Sizes: a tensor has at most 0xfffff000 elements (elements and 2048-value chunks are indexed in
