@@ -30,8 +30,8 @@ def shard_plan(shapes: Sequence[tuple[int, int]], world: int):
 
 def bucket_plan(shapes: Sequence[tuple[int, int]], world: int, buckets: int):
     """-> (bucket per slot, owner rank per slot).  The matrices, in their given order, are cut into `buckets`
-    contiguous runs of about equal Newton-Schulz FLOPs, and every run is spread over the ranks by itself
-    (shard_plan).  A rank then works through the buckets one after the other, and the all-gather of a bucket's
+    contiguous runs of about equal Newton-Schulz FLOPs, and every run is spread over the ranks (one bucket:
+    shard_plan; more: see below).  A rank then works through the buckets one after the other, and the all-gather of a bucket's
     packed weights runs while the next bucket is computed: only the last bucket's gather is left uncovered."""
     n = len(shapes)
     buckets = max(1, min(int(buckets), max(1, sum(1 for r, c in shapes if r * c))))
@@ -47,14 +47,18 @@ def bucket_plan(shapes: Sequence[tuple[int, int]], world: int, buckets: int):
         b = max(b, min(buckets - 1, int(mid * buckets / total))) if total > 0 else 0
         bucket[i] = b
         acc += flops[i]
-    owner = [0] * n
+    if buckets == 1:
+        return bucket, shard_plan(shapes, world)[0]
+    # Bucket after bucket, largest matrix first, each to the rank with the least work SO FAR (over all buckets up
+    # to here; ties to the lowest rank): every bucket is spread over the ranks, and what a bucket leaves uneven the
+    # next one evens out, so the ranks' totals (one Newton-Schulz pass over everything) stay balanced.
+    owner, load = [0] * n, [0.0] * world
     for b in range(buckets):
-        ids = [i for i in range(n) if bucket[i] == b]
-        if not ids:
-            continue
-        own, _ = shard_plan([shapes[i] for i in ids], world)
-        for i, r in zip(ids, own):
+        ids = sorted((i for i in range(n) if bucket[i] == b), key=lambda i: (-flops[i], i))
+        for i in ids:
+            r = min(range(world), key=lambda k: (load[k], k))
             owner[i] = r
+            load[r] += flops[i]
     return bucket, owner
 
 

@@ -164,9 +164,13 @@ def test_bucket_plan_cuts_contiguous_runs_and_balances_each():
             flops = [4.0 * min(r, c) ** 2 * max(r, c) + 2.0 * min(r, c) ** 3 for r, c in shapes]
             per_bucket = [sum(f for f, b in zip(flops, bucket) if b == k) for k in range(buckets)]
             assert max(per_bucket) <= 1.2 * min(per_bucket)
+            # what counts is a rank's total (stages M, N and P run once over all buckets): within 10 % of the mean;
+            # a single bucket may be less even, the next one makes up for it
+            total = [sum(f for f, r in zip(flops, owner) if r == w) for w in range(world)]
+            assert max(total) <= 1.10 * (sum(total) / world)
             for k in range(buckets):
                 load = [sum(f for f, b, r in zip(flops, bucket, owner) if b == k and r == w) for w in range(world)]
-                assert max(load) <= 1.35 * (sum(load) / world)
+                assert max(load) <= 1.6 * (sum(load) / world)
             # the layout puts a slot inside its owner's slice of its bucket's region, regions back to back
             arena = Nvfp4Arena(shapes, owner, world, _scales_bytes, bucket)
             end = 0
