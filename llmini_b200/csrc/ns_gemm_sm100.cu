@@ -22,8 +22,16 @@
 //           path, and this raises FLOPs per loaded byte by 1.5x.  No multicast load is used.
 //   single: one CTA computes 128 x BN (BN = 128 or 256).
 //
-// Every mbarrier wait is bounded: on expiry the CTA raises a status word, drains and frees
-// its TMEM before returning.
+// Three ways to launch the loop (the template parameter CHAINED separates the first from the other two):
+//   per phase : one launch per GEMM flavour and iteration, tiles dealt round-robin, launches chained with
+//               programmatic dependent launch.  The default.
+//   chained   : one persistent grid over a work list of every tile of every iteration; CTAs draw tiles with an
+//               atomic ticket and a per-matrix progress count orders a tile after the tiles it reads from.
+//   fused     : a ticketed launch whose entries are a Gram tile AND the polynomial tile of the same position:
+//               the FP32 Gram accumulator stays in tensor memory between the two.
+//
+// Every mbarrier wait, ring read and dependency wait is bounded: on expiry the CTA raises a status word, drains
+// and frees its TMEM before returning.
 #include <cuda.h>
 
 #include "common.cuh"
